@@ -1,0 +1,156 @@
+/*
+ * b200q -- C ABI of the B200 (sm_100a) quantized-weight matmul library.
+ *
+ * This is the boundary a ROCmForge backend binds instead of the HIP runtime + HSACO
+ * kernels it uses today for its quantized-weight path. Every entry point returns an
+ * int status (0 = success, negative = b200q_status) the way the reference's FFI
+ * returns HIP status codes (src/backend/hip_backend/ffi.rs:10-72, HIP_SUCCESS = 0);
+ * the text of the last failure on the calling thread is b200q_last_error(). Nothing
+ * throws, aborts or traps. File:line citations name the reference interface each
+ * entry point replaces, by path inside the ROCmForge tree.
+ *
+ * Pointers named d_* are device pointers on the context's device, h_* are host
+ * pointers. All work of a context is ordered on its one stream (the reference backend
+ * is a single-stream singleton, src/backend/hip_backend/backend.rs:83-105).
+ */
+#ifndef B200Q_H
+#define B200Q_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200q_ctx b200q_ctx;       /* device + stream + scratch; replaces HipBackend (backend.rs:83-105) */
+typedef struct b200q_weight b200q_weight; /* device-resident packed tensor; replaces Arc<DeviceTensor> of a quantized weight */
+
+/* Status codes; names follow HipError (src/backend/hip_backend/error.rs:6-28). */
+typedef enum {
+    B200Q_OK = 0,
+    B200Q_ERR_INIT = -1,          /* InitializationFailed */
+    B200Q_ERR_NO_DEVICE = -2,     /* DeviceNotFound */
+    B200Q_ERR_ALLOC = -3,         /* MemoryAllocationFailed (recoverable) */
+    B200Q_ERR_COPY = -4,          /* MemoryCopyFailed (recoverable) */
+    B200Q_ERR_LAUNCH = -5,        /* KernelLaunchFailed (recoverable) */
+    B200Q_ERR_DEVICE = -6,        /* DeviceError (recoverable) */
+    B200Q_ERR_INVALID = -7,       /* GenericError: bad argument, size or shape; nothing was launched */
+    B200Q_ERR_UNSUPPORTED = -8,   /* GenericError: valid request this build has no kernel for */
+    B200Q_ERR_TIMEOUT = -9        /* a bounded device-side wait gave up; the context stays usable */
+} b200q_status;
+
+/* Tensor types. Values in comments are GgufTensorType ids (src/loader/tensor_type.rs:16-32). */
+typedef enum {
+    B200Q_Q4_0 = 0,        /* 2  */
+    B200Q_Q8_0 = 1,        /* 8  */
+    B200Q_Q4_K = 2,        /* 12 */
+    B200Q_Q6_K = 3,        /* 14 */
+    B200Q_MXFP4 = 4,       /* 20 */
+    B200Q_MXFP6_E2M3 = 5,  /* 21 */
+    B200Q_MXFP6_E3M2 = 6   /* 22 */
+} b200q_qtype;
+
+/* Byte layout of the blocks.
+ * RF   = what the reference's CPU dequant parses: Q4_0 20 B (f32 scale), Q8_0 36 B, Q4_K 256 B,
+ *        Q6_K 256 B, MXFP4 17 B (int8 exponent, high nibble first), MXFP6 25 B
+ *        (src/kernels/quant/{q4_0,q8_0,q4_k,q6_k}.rs, src/loader/dequant.rs:41-132).
+ * GGUF = llama.cpp blocks: 18 / 34 / 144 / 210 / 17 / 25 bytes. */
+typedef enum { B200Q_LAYOUT_RF = 0, B200Q_LAYOUT_GGUF = 1 } b200q_layout;
+
+/* How the flat element stream maps to the [n, k] weight matrix.
+ * NK: n rows of k contiguous weights (blocks run along k) -- the documented operand of matmul_q4_0
+ *     (src/kernels/matmul/quantized/q4_0.rs:139-148).
+ * KN: flat [k, n] stream, W[l*n + j], as the reference kernels and its CPU composition index it
+ *     (kernels/q4_0_matmul.hip:242, src/tensor/matmul.rs:219-233). */
+typedef enum { B200Q_ORIENT_NK = 0, B200Q_ORIENT_KN = 1 } b200q_orient;
+
+typedef enum { B200Q_F32 = 0, B200Q_BF16 = 1 } b200q_dtype;
+
+/* b200q_matmul flags */
+#define B200Q_MM_DEFAULT 0u
+#define B200Q_MM_SEQUENTIAL 1u /* one thread per output, ascending k, multiply then add: bit-identical to cpu_matmul_f32 */
+#define B200Q_MM_NO_TENSOR 2u  /* never take the tcgen05 path (CUDA-core kernels only) */
+
+typedef struct {
+    char name[128];
+    int sm_count;
+    int cc_major, cc_minor;
+    size_t total_mem, free_mem;
+    size_t smem_per_block_optin;
+    int l2_bytes;
+} b200q_device_info;
+
+/* ---- context: replaces HipBackend::new / the hip* runtime calls of ffi.rs:10-72 ---------------- */
+int b200q_init(int device, b200q_ctx** out);                         /* hipInit+hipSetDevice+hipStreamCreate */
+int b200q_init_on_stream(int device, void* cuda_stream, b200q_ctx** out); /* run on a stream the caller owns */
+void b200q_destroy(b200q_ctx* ctx);
+const char* b200q_last_error(void);                                  /* hipGetErrorString(hipGetLastError()) */
+int b200q_is_recoverable(int status);                                /* HipError::is_recoverable, error.rs:67-76 */
+int b200q_get_device_info(b200q_ctx* ctx, b200q_device_info* out);   /* hipGetDeviceProperties, hipMemGetInfo */
+int b200q_malloc(b200q_ctx* ctx, size_t bytes, void** d_out);        /* hipMalloc (HipBackend::allocate_buffer, backend.rs:704) */
+int b200q_free(b200q_ctx* ctx, void* d_ptr);                         /* hipFree */
+int b200q_memcpy_h2d(b200q_ctx* ctx, void* d_dst, const void* h_src, size_t bytes); /* hipMemcpyHtoD (HipBuffer::copy_from_host) */
+int b200q_memcpy_d2h(b200q_ctx* ctx, void* h_dst, const void* d_src, size_t bytes); /* hipMemcpyDtoH (HipBuffer::copy_to_host) */
+int b200q_memset(b200q_ctx* ctx, void* d_dst, int value, size_t bytes);             /* hipMemset */
+int b200q_synchronize(b200q_ctx* ctx);                               /* HipBackend::synchronize, backend.rs:753 */
+void* b200q_stream(b200q_ctx* ctx);                                  /* the cudaStream_t work is ordered on */
+/* CUDA-event timing on the context's stream (KernelTimer, src/profiling/kernel_timer.rs:58-340). */
+int b200q_timer_start(b200q_ctx* ctx);
+int b200q_timer_stop_ms(b200q_ctx* ctx, float* ms_out);              /* synchronises; elapsed since timer_start */
+
+/* ---- sizes: GgufTensorType::block_size, calculate_tensor_size (src/loader/gguf/tensor_info.rs:104-133) */
+int b200q_block_elems(int qtype);
+size_t b200q_block_bytes(int qtype, int layout);
+size_t b200q_tensor_bytes(int qtype, int layout, int64_t n_elements);
+
+/* ---- upload: replaces GgufLoader::load_tensor_to_gpu / gpu_dequantize_upload
+ *      (src/loader/gguf/types.rs:199-254, src/loader/gguf/gpu_upload.rs:22-125). The packed bytes stay
+ *      packed on the device (re-arranged into 16-byte-aligned planes of the same total size).
+ *      shard_count > 1 keeps only rows [shard_rank*n/shard_count, (shard_rank+1)*n/shard_count) of an NK
+ *      tensor; n must divide evenly and the slice must start and end on a block boundary. */
+int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
+                        int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out);
+int b200q_weight_free(b200q_weight* w);
+int b200q_weight_info(const b200q_weight* w, int* qtype, int* layout, int* orient, int64_t* n_local, int64_t* k,
+                      int64_t* row0, int64_t* n_total, size_t* packed_bytes);
+
+/* ---- dequantise to fp32 on the device, bit-exact with the reference CPU dequant. Replaces
+ *      dequantize_q4_0_kernel_cached (src/kernels/quant/q4_0.rs:107-153), dequantize_q4_k_gpu_kernel
+ *      (q4_k.rs:99-148), dequantize_q6_k_gpu_kernel (q6_k.rs:102-149) and the HIP kernels under them
+ *      (kernels/q4_0_dequant.hip:72, q8_0_dequant.hip:40, q4_k_dequant.hip:81, q6_k_dequant.hip:82,
+ *      mxfp_dequant.hip:85,147). n_elements may stop inside a block. */
+int b200q_dequantize(b200q_ctx* ctx, const b200q_weight* w, float* d_out, int64_t n_elements);
+/* Host bytes in, device fp32 out (the exact shape of the reference wrappers: &[u8] -> HipBuffer). A byte
+ * stream shorter than n_elements needs leaves the uncovered outputs 0.0, as the CPU functions do. */
+int b200q_dequantize_bytes(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout,
+                           float* d_out, int64_t n_elements);
+
+/* ---- fused dequant + matmul: y[m, n_local] = x[m, k] * W^T. Replaces matmul_q4_0 / matmul_q4_k /
+ *      matmul_q6_k / matmul_q8_0 (src/kernels/matmul/quantized/q4_0.rs:153, q4_k.rs:173, q6_k.rs:163,
+ *      q8_0.rs:69), their kernels (kernels/q4_0_matmul.hip:153, q4_k_matmul.hip:216, q6_k_matmul.hip:216)
+ *      and the IR ops MatMulQ4_0 / MatMulQ8_0 (src/ggml/hip_backend/op_dispatch.rs:951-1082).
+ *      m <= 8 takes the HBM-bound decode kernels, larger m the tensor-core kernel. x is [m, ldx] and y is
+ *      [m, ldy] row-major (ld in elements; 0 means dense: k and n_local). */
+int b200q_matmul(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* d_y, int y_dtype,
+                 int m, unsigned flags);
+int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, int64_t ldx, void* d_y,
+                    int y_dtype, int64_t ldy, int m, unsigned flags);
+/* Host activations in, host result out; copies ride the context's stream (pinned or pageable memory). */
+int b200q_matmul_host(b200q_ctx* ctx, const b200q_weight* w, const float* h_x, float* h_y, int m, unsigned flags);
+
+/* ---- batch front end: replaces BatchQuantizedMatmul::process_batch / process_batch_profiled
+ *      (src/ggml/hip_backend/ops/batch_quantized.rs:147-190). One launch covers every op of the batch.
+ *      d_x[i] is op i's [m, k_i] fp32 input (the reference shares one input; pass the same pointer),
+ *      d_y[i] its [m, n_i] fp32 output. ms_out (optional) receives the device time of the batch. */
+typedef struct b200q_batch b200q_batch;
+int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, const float* const* d_x,
+                       float* const* d_y, int m, b200q_batch** out);
+int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out);
+int b200q_batch_free(b200q_batch* batch);
+/* Bytes of packed weights one run of the batch streams (BatchQuantizedMatmul::calculate_throughput, :277-289). */
+size_t b200q_batch_weight_bytes(const b200q_batch* batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,374 @@
+// C ABI of the library (include/b200q.h): context, memory, upload, dequantise, matmul dispatch.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200q {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(int code, cudaError_t e, const char* what) {
+    // a failed launch leaves a sticky "last error"; clear it so later calls report their own
+    cudaGetLastError();
+    if (e == cudaErrorMemoryAllocation) code = B200Q_ERR_ALLOC;
+    return fail(code, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+int ensure_scratch(b200q_ctx* ctx, size_t bytes, int which) {
+    void** p = which == 0 ? &ctx->scratch : &ctx->scratch2;
+    size_t* sz = which == 0 ? &ctx->scratch_bytes : &ctx->scratch2_bytes;
+    if (*sz >= bytes) return B200Q_OK;
+    if (*p) {
+        B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+        cudaFree(*p);
+        *p = nullptr;
+        *sz = 0;
+    }
+    size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+    B200Q_CUDA(cudaMalloc(p, want), B200Q_ERR_ALLOC);
+    *sz = want;
+    return B200Q_OK;
+}
+
+static bool valid_qtype(int q) { return q >= 0 && q < NUM_QTYPES; }
+static bool valid_layout(int l) { return l == RF || l == GGUF; }
+
+// Carve the planes of `n_blocks` blocks out of one allocation (256-byte aligned sub-allocations).
+static size_t plane_layout(int fmt, int64_t n_blocks, size_t off[4]) {
+    FmtInfo I = fmt_info(fmt);
+    size_t total = 0;
+    for (int j = 0; j < I.nplanes; j++) {
+        off[j] = total;
+        size_t sz = (size_t)n_blocks * I.plane_bytes[j] + 64;  // slack: vector loads may over-read a tail
+        total += (sz + 255) & ~(size_t)255;
+    }
+    return total ? total : 256;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+const char* b200q_last_error(void) { return g_err; }
+
+int b200q_is_recoverable(int status) {
+    return status == B200Q_ERR_ALLOC || status == B200Q_ERR_COPY || status == B200Q_ERR_LAUNCH ||
+           status == B200Q_ERR_DEVICE || status == B200Q_ERR_TIMEOUT;
+}
+
+int b200q_init_on_stream(int device, void* cuda_stream, b200q_ctx** out) {
+    if (!out) return fail(B200Q_ERR_INVALID, "init: out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(B200Q_ERR_NO_DEVICE, "init: no CUDA device (%s)", e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= count) return fail(B200Q_ERR_NO_DEVICE, "init: device %d of %d", device, count);
+    B200Q_CUDA(cudaSetDevice(device), B200Q_ERR_INIT);
+    b200q_ctx* ctx = new b200q_ctx();
+    ctx->device = device;
+    if (cuda_stream == (void*)(intptr_t)-1) {
+        e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { delete ctx; return cuda_fail(B200Q_ERR_INIT, e, "cudaStreamCreate"); }
+        ctx->own_stream = true;
+    } else {
+        ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    }
+    cudaEventCreate(&ctx->ev0);
+    cudaEventCreate(&ctx->ev1);
+    cudaDeviceProp p{};
+    e = cudaGetDeviceProperties(&p, device);
+    if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_INIT, e, "cudaGetDeviceProperties"); }
+    snprintf(ctx->info.name, sizeof(ctx->info.name), "%.127s", p.name);
+    ctx->info.sm_count = p.multiProcessorCount;
+    ctx->info.cc_major = p.major;
+    ctx->info.cc_minor = p.minor;
+    ctx->info.total_mem = p.totalGlobalMem;
+    ctx->info.smem_per_block_optin = p.sharedMemPerBlockOptin;
+    ctx->info.l2_bytes = p.l2CacheSize;
+    if (p.major != 10) {
+        int maj = p.major, min = p.minor;
+        b200q_destroy(ctx);
+        return fail(B200Q_ERR_INIT, "init: device is sm_%d%d; this library is built for sm_100a only", maj, min);
+    }
+    e = cudaMalloc(&ctx->d_status, sizeof(int) * 4);
+    if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaMalloc(status)"); }
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int) * 4, ctx->stream);
+    *out = ctx;
+    return B200Q_OK;
+}
+
+int b200q_init(int device, b200q_ctx** out) { return b200q_init_on_stream(device, (void*)(intptr_t)-1, out); }
+
+void b200q_destroy(b200q_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->scratch2) cudaFree(ctx->scratch2);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+    if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    cudaGetLastError();
+    delete ctx;
+}
+
+#define CTX_GUARD(name)                                              \
+    if (!ctx) return fail(B200Q_ERR_INVALID, name ": ctx is null");  \
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE)
+
+int b200q_get_device_info(b200q_ctx* ctx, b200q_device_info* out) {
+    CTX_GUARD("get_device_info");
+    if (!out) return fail(B200Q_ERR_INVALID, "get_device_info: out is null");
+    size_t fr = 0, tot = 0;
+    B200Q_CUDA(cudaMemGetInfo(&fr, &tot), B200Q_ERR_DEVICE);
+    *out = ctx->info;
+    out->free_mem = fr;
+    out->total_mem = tot;
+    return B200Q_OK;
+}
+
+int b200q_malloc(b200q_ctx* ctx, size_t bytes, void** d_out) {
+    CTX_GUARD("malloc");
+    if (!d_out) return fail(B200Q_ERR_INVALID, "malloc: d_out is null");
+    *d_out = nullptr;
+    if (bytes == 0) bytes = 1;
+    B200Q_CUDA(cudaMalloc(d_out, bytes), B200Q_ERR_ALLOC);
+    return B200Q_OK;
+}
+
+int b200q_free(b200q_ctx* ctx, void* d_ptr) {
+    CTX_GUARD("free");
+    if (!d_ptr) return B200Q_OK;
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+    B200Q_CUDA(cudaFree(d_ptr), B200Q_ERR_DEVICE);
+    return B200Q_OK;
+}
+
+int b200q_memcpy_h2d(b200q_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+    CTX_GUARD("memcpy_h2d");
+    if (bytes == 0) return B200Q_OK;
+    if (!d_dst || !h_src) return fail(B200Q_ERR_INVALID, "memcpy_h2d: null pointer");
+    B200Q_CUDA(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream), B200Q_ERR_COPY);
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_COPY);
+    return B200Q_OK;
+}
+
+int b200q_memcpy_d2h(b200q_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+    CTX_GUARD("memcpy_d2h");
+    if (bytes == 0) return B200Q_OK;
+    if (!h_dst || !d_src) return fail(B200Q_ERR_INVALID, "memcpy_d2h: null pointer");
+    B200Q_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_COPY);
+    return B200Q_OK;
+}
+
+int b200q_memset(b200q_ctx* ctx, void* d_dst, int value, size_t bytes) {
+    CTX_GUARD("memset");
+    if (bytes == 0) return B200Q_OK;
+    if (!d_dst) return fail(B200Q_ERR_INVALID, "memset: null pointer");
+    B200Q_CUDA(cudaMemsetAsync(d_dst, value, bytes, ctx->stream), B200Q_ERR_COPY);
+    return B200Q_OK;
+}
+
+int b200q_synchronize(b200q_ctx* ctx) {
+    CTX_GUARD("synchronize");
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+    return B200Q_OK;
+}
+
+void* b200q_stream(b200q_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int b200q_timer_start(b200q_ctx* ctx) {
+    CTX_GUARD("timer_start");
+    B200Q_CUDA(cudaEventRecord(ctx->ev0, ctx->stream), B200Q_ERR_DEVICE);
+    return B200Q_OK;
+}
+
+int b200q_timer_stop_ms(b200q_ctx* ctx, float* ms_out) {
+    CTX_GUARD("timer_stop_ms");
+    B200Q_CUDA(cudaEventRecord(ctx->ev1, ctx->stream), B200Q_ERR_DEVICE);
+    B200Q_CUDA(cudaEventSynchronize(ctx->ev1), B200Q_ERR_DEVICE);
+    float ms = 0;
+    B200Q_CUDA(cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1), B200Q_ERR_DEVICE);
+    if (ms_out) *ms_out = ms;
+    return B200Q_OK;
+}
+
+int b200q_block_elems(int qtype) { return valid_qtype(qtype) ? fmt_info(fmt_of(qtype, 0)).block_elems : 0; }
+
+size_t b200q_block_bytes(int qtype, int layout) {
+    return (valid_qtype(qtype) && valid_layout(layout)) ? (size_t)fmt_info(fmt_of(qtype, layout)).block_bytes : 0;
+}
+
+size_t b200q_tensor_bytes(int qtype, int layout, int64_t n_elements) {
+    if (!valid_qtype(qtype) || !valid_layout(layout) || n_elements < 0) return 0;
+    FmtInfo I = fmt_info(fmt_of(qtype, layout));
+    return (size_t)((n_elements + I.block_elems - 1) / I.block_elems) * I.block_bytes;
+}
+
+// Allocates the planes for n_blocks blocks, copies `avail` bytes of file blocks from the host (zero
+// filling the rest) and splits them into planes. Used by upload and by dequantize_bytes.
+static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t avail, int64_t n_blocks, void** base_out,
+                       WView* view_out) {
+    FmtInfo I = fmt_info(fmt);
+    size_t off[4] = {0, 0, 0, 0};
+    size_t total = plane_layout(fmt, n_blocks, off);
+    void* base = nullptr;
+    B200Q_CUDA(cudaMalloc(&base, total), B200Q_ERR_ALLOC);
+    WView v{};
+    for (int j = 0; j < I.nplanes; j++) v.p[j] = static_cast<uint8_t*>(base) + off[j];
+    size_t raw_bytes = (size_t)n_blocks * I.block_bytes;
+    if (avail > raw_bytes) avail = raw_bytes;
+    cudaError_t e = cudaSuccess;
+    int rc = B200Q_OK;
+    if (I.nplanes == 1) {
+        // the file layout is the device layout
+        e = cudaMemsetAsync(static_cast<uint8_t*>(base) + avail, 0, total - avail, ctx->stream);
+        if (e == cudaSuccess && avail) e = cudaMemcpyAsync(base, h_bytes, avail, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = cuda_fail(B200Q_ERR_COPY, e, "upload copy");
+    } else {
+        void* stage = nullptr;
+        e = cudaMalloc(&stage, raw_bytes ? raw_bytes : 1);
+        if (e != cudaSuccess) {
+            cudaFree(base);
+            return cuda_fail(B200Q_ERR_ALLOC, e, "upload staging");
+        }
+        e = cudaMemsetAsync(base, 0, total, ctx->stream);
+        if (e == cudaSuccess && avail < raw_bytes)
+            e = cudaMemsetAsync(static_cast<uint8_t*>(stage) + avail, 0, raw_bytes - avail, ctx->stream);
+        if (e == cudaSuccess && avail) e = cudaMemcpyAsync(stage, h_bytes, avail, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) rc = cuda_fail(B200Q_ERR_COPY, e, "upload copy");
+        if (rc == B200Q_OK) rc = launch_repack(ctx, fmt, static_cast<const uint8_t*>(stage), n_blocks, v);
+        e = cudaStreamSynchronize(ctx->stream);
+        if (rc == B200Q_OK && e != cudaSuccess) rc = cuda_fail(B200Q_ERR_DEVICE, e, "upload repack");
+        cudaFree(stage);
+    }
+    if (rc != B200Q_OK) {
+        cudaFree(base);
+        return rc;
+    }
+    *base_out = base;
+    *view_out = v;
+    return B200Q_OK;
+}
+
+int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
+                        int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out) {
+    CTX_GUARD("weight_upload");
+    if (!out) return fail(B200Q_ERR_INVALID, "weight_upload: out is null");
+    *out = nullptr;
+    if (!valid_qtype(qtype) || !valid_layout(layout)) return fail(B200Q_ERR_INVALID, "weight_upload: unknown qtype %d / layout %d", qtype, layout);
+    if (orient != B200Q_ORIENT_NK && orient != B200Q_ORIENT_KN) return fail(B200Q_ERR_INVALID, "weight_upload: unknown orientation %d", orient);
+    if (n <= 0 || k <= 0) return fail(B200Q_ERR_INVALID, "weight_upload: n=%lld k=%lld must be positive", (long long)n, (long long)k);
+    if (!h_bytes) return fail(B200Q_ERR_INVALID, "weight_upload: h_bytes is null");
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count)
+        return fail(B200Q_ERR_INVALID, "weight_upload: shard %d of %d", shard_rank, shard_count);
+    int fmt = fmt_of(qtype, layout);
+    FmtInfo I = fmt_info(fmt);
+    size_t need = b200q_tensor_bytes(qtype, layout, n * k);
+    // same check as execute_matmul_q4_0 (src/ggml/hip_backend/op_dispatch.rs:973-979): byte count must match the shape
+    if (nbytes != need)
+        return fail(B200Q_ERR_INVALID, "weight_upload: %zu bytes given, %lld x %lld weights need %zu", nbytes, (long long)n, (long long)k, need);
+    int64_t row0 = 0, n_local = n;
+    if (shard_count > 1) {
+        if (orient != B200Q_ORIENT_NK) return fail(B200Q_ERR_UNSUPPORTED, "weight_upload: only NK tensors can be sharded by output feature");
+        if (n % shard_count) return fail(B200Q_ERR_INVALID, "weight_upload: n=%lld does not divide into %d shards", (long long)n, shard_count);
+        n_local = n / shard_count;
+        row0 = n_local * shard_rank;
+        if ((n_local * k) % I.block_elems)
+            return fail(B200Q_ERR_INVALID, "weight_upload: a shard of %lld rows x %lld does not end on a %d-weight block", (long long)n_local, (long long)k, I.block_elems);
+    }
+    int64_t n_el = n_local * k;
+    int64_t n_blocks = (n_el + I.block_elems - 1) / I.block_elems;
+    const uint8_t* src = static_cast<const uint8_t*>(h_bytes) + (size_t)((row0 * k) / I.block_elems) * I.block_bytes;
+    b200q_weight* w = new b200q_weight();
+    w->ctx = ctx;
+    w->qtype = qtype; w->layout = layout; w->orient = orient; w->fmt = fmt;
+    w->n_local = n_local; w->k = k; w->row0 = row0; w->n_total = n;
+    w->n_elements = n_el; w->n_blocks = n_blocks;
+    w->packed_bytes = (size_t)n_blocks * I.block_bytes;
+    int rc = make_planes(ctx, fmt, src, w->packed_bytes, n_blocks, &w->base, &w->view);
+    if (rc != B200Q_OK) { delete w; return rc; }
+    *out = w;
+    return B200Q_OK;
+}
+
+int b200q_weight_free(b200q_weight* w) {
+    if (!w) return B200Q_OK;
+    b200q_ctx* ctx = w->ctx;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(w->base);
+    cudaGetLastError();
+    delete w;
+    return B200Q_OK;
+}
+
+int b200q_weight_info(const b200q_weight* w, int* qtype, int* layout, int* orient, int64_t* n_local, int64_t* k,
+                      int64_t* row0, int64_t* n_total, size_t* packed_bytes) {
+    if (!w) return fail(B200Q_ERR_INVALID, "weight_info: handle is null");
+    if (qtype) *qtype = w->qtype;
+    if (layout) *layout = w->layout;
+    if (orient) *orient = w->orient;
+    if (n_local) *n_local = w->n_local;
+    if (k) *k = w->k;
+    if (row0) *row0 = w->row0;
+    if (n_total) *n_total = w->n_total;
+    if (packed_bytes) *packed_bytes = w->packed_bytes;
+    return B200Q_OK;
+}
+
+int b200q_dequantize(b200q_ctx* ctx, const b200q_weight* w, float* d_out, int64_t n_elements) {
+    CTX_GUARD("dequantize");
+    if (!w) return fail(B200Q_ERR_INVALID, "dequantize: weight handle is null");
+    if (w->ctx->device != ctx->device) return fail(B200Q_ERR_INVALID, "dequantize: weight lives on device %d, ctx on %d", w->ctx->device, ctx->device);
+    if (n_elements < 0 || n_elements > w->n_elements)
+        return fail(B200Q_ERR_INVALID, "dequantize: %lld elements asked, tensor holds %lld", (long long)n_elements, (long long)w->n_elements);
+    if (n_elements == 0) return B200Q_OK;
+    if (!d_out) return fail(B200Q_ERR_INVALID, "dequantize: d_out is null");
+    return launch_dequant(ctx, w->fmt, w->view, d_out, n_elements, (int64_t)w->packed_bytes);
+}
+
+int b200q_dequantize_bytes(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, float* d_out,
+                           int64_t n_elements) {
+    CTX_GUARD("dequantize_bytes");
+    if (!valid_qtype(qtype) || !valid_layout(layout)) return fail(B200Q_ERR_INVALID, "dequantize_bytes: unknown qtype %d / layout %d", qtype, layout);
+    if (n_elements < 0) return fail(B200Q_ERR_INVALID, "dequantize_bytes: negative element count");
+    if (n_elements == 0) return B200Q_OK;
+    if (!d_out) return fail(B200Q_ERR_INVALID, "dequantize_bytes: d_out is null");
+    if (!h_bytes && nbytes) return fail(B200Q_ERR_INVALID, "dequantize_bytes: h_bytes is null");
+    int fmt = fmt_of(qtype, layout);
+    FmtInfo I = fmt_info(fmt);
+    int64_t n_blocks = (n_elements + I.block_elems - 1) / I.block_elems;
+    void* base = nullptr;
+    WView v{};
+    int rc = make_planes(ctx, fmt, static_cast<const uint8_t*>(h_bytes), nbytes, n_blocks, &base, &v);
+    if (rc != B200Q_OK) return rc;
+    rc = launch_dequant(ctx, fmt, v, d_out, n_elements, (int64_t)nbytes);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(base);
+    if (rc != B200Q_OK) return rc;
+    if (e != cudaSuccess) return cuda_fail(B200Q_ERR_DEVICE, e, "dequantize_bytes");
+    return B200Q_OK;
+}
+
+}  // extern "C"

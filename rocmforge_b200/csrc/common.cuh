@@ -1,0 +1,61 @@
+// Shared host-side declarations of the library: context, weight handle, error plumbing.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/b200q.h"
+#include "formats.cuh"
+
+struct b200q_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    b200q_device_info info{};
+    // grow-only device scratch (activation conversion, host staging of matmul_host, split buffers)
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void* scratch2 = nullptr;
+    size_t scratch2_bytes = 0;
+    int* d_status = nullptr;  // device word the tensor-core kernel reports bounded-wait failures in
+};
+
+struct b200q_weight {
+    b200q_ctx* ctx = nullptr;
+    int qtype = 0, layout = 0, orient = 0, fmt = 0;
+    int64_t n_local = 0, k = 0, row0 = 0, n_total = 0;
+    int64_t n_elements = 0;  // n_local * k
+    int64_t n_blocks = 0;
+    size_t packed_bytes = 0;  // bytes of the file blocks this handle holds
+    void* base = nullptr;     // one allocation holding every plane
+    b200q::WView view{};
+};
+
+namespace b200q {
+
+int fail(int code, const char* fmt, ...);
+int cuda_fail(int code, cudaError_t e, const char* what);
+int ensure_scratch(b200q_ctx* ctx, size_t bytes, int which = 0);
+
+#define B200Q_CUDA(call, code)                                        \
+    do {                                                              \
+        cudaError_t e__ = (call);                                     \
+        if (e__ != cudaSuccess) return b200q::cuda_fail((code), e__, #call); \
+    } while (0)
+
+// Expands `X(F)` for every format index (qtype*2+layout).
+#define B200Q_FOR_EACH_FMT(X) X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13)
+
+// kernels_dequant.cu
+int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_t n, int64_t valid_bytes);
+int launch_repack(b200q_ctx* ctx, int fmt, const uint8_t* d_raw, int64_t n_blocks, const WView& v);
+// kernels_gemv.cu
+int launch_gemv(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, int64_t ldx, float* d_y, int64_t ldy, int m);
+int launch_matmul_seq(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, int64_t ldx, float* d_y, int64_t ldy, int m);
+int launch_convert_bf16_to_f32(b200q_ctx* ctx, const void* d_in, int64_t ld_in, float* d_out, int64_t ld_out, int rows, int64_t cols);
+int launch_convert_f32_to_bf16(b200q_ctx* ctx, const float* d_in, int64_t ld_in, void* d_out, int64_t ld_out, int rows, int64_t cols);
+bool gemv_fast_supported(const b200q_weight* w);
+
+}  // namespace b200q

@@ -1,0 +1,94 @@
+// Dequantise-to-fp32 kernels and the upload-time plane split.
+//
+// Replaces kernels/q4_0_dequant.hip:72, q8_0_dequant.hip:40, q4_k_dequant.hip:81, q6_k_dequant.hip:82 and
+// mxfp_dequant.hip:85,147 of the reference (one thread per ELEMENT there). Here one thread decodes 8
+// consecutive weights and writes one 32-byte sector, so a warp writes 1 KB of contiguous fp32: the
+// kernel is bound by the 4 B/weight it writes to HBM.
+#include "common.cuh"
+
+namespace b200q {
+
+template <int F>
+__global__ void __launch_bounds__(256) dequant_kernel(WView v, float* __restrict__ out, int64_t n, int64_t valid_bytes) {
+    int64_t piece = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t e0 = piece * 8;
+    if (e0 >= n) return;
+    float w[8];
+    decode8<F>(v, piece >> 2, (int)(piece & 3), w);
+    if (need_end<F>(e0 + 7) > valid_bytes || need_end<F>(e0) > valid_bytes) {
+        // the file stream ends inside or before this piece: uncovered elements stay 0.0
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (need_end<F>(e0 + i) > valid_bytes) w[i] = 0.0f;
+    }
+    float* o = out + e0;
+    if (e0 + 8 <= n && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+        reinterpret_cast<float4*>(o)[0] = make_float4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<float4*>(o)[1] = make_float4(w[4], w[5], w[6], w[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (e0 + i < n) o[i] = w[i];
+    }
+}
+
+int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_t n, int64_t valid_bytes) {
+    if (n <= 0) return B200Q_OK;
+    int64_t pieces = (n + 7) / 8;
+    int64_t grid = (pieces + 255) / 256;
+    if (grid > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "dequantize: tensor too large for one launch");
+    switch (fmt) {
+#define X(F) \
+    case F: dequant_kernel<F><<<(unsigned)grid, 256, 0, ctx->stream>>>(v, d_out, n, valid_bytes); break;
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+        default: return fail(B200Q_ERR_INVALID, "dequantize: unknown format %d", fmt);
+    }
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
+// File blocks (header and codes interleaved) -> planes. The block sizes are not word multiples, so
+// this moves single bytes; it runs once per tensor at load time.
+struct RepackArgs {
+    uint8_t* dst[4];
+    int plane_bytes[4];
+    int plane_off[4];
+    int nplanes;
+    int block_bytes;
+};
+
+__global__ void __launch_bounds__(256) repack_kernel(const uint8_t* __restrict__ raw, int64_t total_bytes, RepackArgs a) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total_bytes) return;
+    int64_t b = i / a.block_bytes;
+    int o = (int)(i - b * a.block_bytes);
+    int j = 0;
+#pragma unroll
+    for (int t = 1; t < 4; t++)
+        if (t < a.nplanes && o >= a.plane_off[t]) j = t;
+    a.dst[j][b * a.plane_bytes[j] + (o - a.plane_off[j])] = raw[i];
+}
+
+int launch_repack(b200q_ctx* ctx, int fmt, const uint8_t* d_raw, int64_t n_blocks, const WView& v) {
+    FmtInfo I = fmt_info(fmt);
+    RepackArgs a{};
+    a.nplanes = I.nplanes;
+    a.block_bytes = I.block_bytes;
+    int off = 0;
+    for (int j = 0; j < I.nplanes; j++) {
+        a.dst[j] = const_cast<uint8_t*>(v.p[j]);
+        a.plane_bytes[j] = I.plane_bytes[j];
+        a.plane_off[j] = off;
+        off += I.plane_bytes[j];
+    }
+    int64_t total = n_blocks * I.block_bytes;
+    if (total == 0) return B200Q_OK;
+    int64_t grid = (total + 255) / 256;
+    if (grid > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "upload: tensor too large for one repack launch");
+    repack_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(d_raw, total, a);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
+}  // namespace b200q
