@@ -149,6 +149,8 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out);
 int b200q_batch_free(b200q_batch* batch);
 /* Bytes of packed weights one run of the batch streams (BatchQuantizedMatmul::calculate_throughput, :277-289). */
 size_t b200q_batch_weight_bytes(const b200q_batch* batch);
+/* Kernel launches one run of the batch issues (1 when every product has a grouped decode kernel). */
+int b200q_batch_launches(const b200q_batch* batch);
 
 #ifdef __cplusplus
 }

@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200q_batch_run": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float)]),
     "b200q_batch_free": (_i, [_vp]),
     "b200q_batch_weight_bytes": (_sz, [_vp]),
+    "b200q_batch_launches": (_i, [_vp]),
 }
 
 _lib = None

@@ -2,6 +2,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "gemv_mma.cuh"
 
 using namespace b200q;
 
@@ -12,7 +13,24 @@ struct b200q_batch {
     std::vector<const float*> x;
     std::vector<float*> y;
     size_t weight_bytes = 0;
+    // grouped launch (every product has a tensor-core decode kernel): device copies of the plan
+    bool grouped = false;
+    GOp* d_ops = nullptr;
+    int2* d_ranges = nullptr;
+    int n_ctas = 0, total_tiles = 0;
+    size_t smem = 0;
+    GOp single{};
 };
+
+static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
+    GOp op{};
+    op.v = w->view;
+    op.x = x; op.y = y; op.ldx = ldx; op.ldy = ldy;
+    op.n_rows = (int)w->n_local; op.k = (int)w->k; op.fmt = w->fmt;
+    return op;
+}
+
+static int ctas_per_sm(size_t smem) { return smem <= 100 * 1024 ? 2 : 1; }
 
 static int check_matmul_args(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, const void* d_y, int m) {
     if (!w) return fail(B200Q_ERR_INVALID, "matmul: weight handle is null");
@@ -30,7 +48,18 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
     if (!aligned) return launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
     for (int i = 0; i < m; i += 8) {
         int mm = m - i < 8 ? m - i : 8;
-        int rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
+        int rc;
+        if (gemv_mma_supported(w, mm)) {
+            GOp op = make_gop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
+            gemv_mma_plan(&op, true);
+            op.tile0 = 0;
+            size_t smem = gemv_mma_smem_bytes(w->fmt, (int)w->k, mm);
+            int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
+            if (n_ctas > op.ntiles) n_ctas = op.ntiles;
+            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem);
+        } else {
+            rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
+        }
         if (rc != B200Q_OK) return rc;
     }
     return B200Q_OK;
@@ -115,6 +144,57 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
         b->y.push_back(d_y[i]);
         b->weight_bytes += w[i]->packed_bytes;
     }
+    // plan one grouped launch when every product has a tensor-core decode kernel
+    bool all = count > 0;
+    for (int i = 0; i < count; i++) all = all && gemv_mma_supported(w[i], m);
+    if (all) {
+        std::vector<GOp> ops(count);
+        std::vector<double> tile_cost;
+        int total = 0;
+        size_t smem = 0;
+        for (int i = 0; i < count; i++) {
+            ops[i] = make_gop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
+            gemv_mma_plan(&ops[i], count == 1);
+            ops[i].tile0 = total;
+            total += ops[i].ntiles;
+            FmtInfo I = fmt_info(w[i]->fmt);
+            double c = (double)(8 >> ops[i].kw_log2) * 16 * w[i]->k * I.block_bytes / I.block_elems + 2048.0;
+            for (int t = 0; t < ops[i].ntiles; t++) tile_cost.push_back(c);
+            size_t sm = gemv_mma_smem_bytes(w[i]->fmt, (int)w[i]->k, m);
+            if (sm > smem) smem = sm;
+        }
+        int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
+        if (n_ctas > total) n_ctas = total;
+        // contiguous tile ranges of (nearly) equal cost
+        double sum = 0;
+        for (double c : tile_cost) sum += c;
+        std::vector<int2> ranges(n_ctas);
+        double acc = 0;
+        int t = 0;
+        for (int c = 0; c < n_ctas; c++) {
+            ranges[c].x = t;
+            double limit = sum * (c + 1) / n_ctas;
+            while (t < total && (acc + tile_cost[t] * 0.5 <= limit || c == n_ctas - 1)) acc += tile_cost[t++];
+            ranges[c].y = t;
+        }
+        cudaError_t e = cudaSetDevice(ctx->device);
+        if (e == cudaSuccess) e = cudaMalloc(&b->d_ops, sizeof(GOp) * count);
+        if (e == cudaSuccess) e = cudaMalloc(&b->d_ranges, sizeof(int2) * n_ctas);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ops, ops.data(), sizeof(GOp) * count, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ranges, ranges.data(), sizeof(int2) * n_ctas, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            if (b->d_ops) cudaFree(b->d_ops);
+            if (b->d_ranges) cudaFree(b->d_ranges);
+            delete b;
+            return cuda_fail(B200Q_ERR_ALLOC, e, "batch_create");
+        }
+        b->grouped = true;
+        b->n_ctas = n_ctas;
+        b->total_tiles = total;
+        b->smem = smem;
+        b->single = ops[0];
+    }
     *out = b;
     return B200Q_OK;
 }
@@ -123,9 +203,16 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (!ctx || !batch) return fail(B200Q_ERR_INVALID, "batch_run: null argument");
     B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
     if (ms_out) B200Q_CUDA(cudaEventRecord(ctx->ev0, ctx->stream), B200Q_ERR_DEVICE);
-    for (size_t i = 0; i < batch->w.size(); i++) {
-        int rc = launch_gemv(ctx, batch->w[i], batch->x[i], batch->w[i]->k, batch->y[i], batch->w[i]->n_local, batch->m);
+    if (batch->grouped) {
+        int n = (int)batch->w.size();
+        int rc = launch_gemv_mma(ctx, &batch->single, batch->d_ops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
+                                 batch->total_tiles, batch->m, batch->smem);
         if (rc != B200Q_OK) return rc;
+    } else {
+        for (size_t i = 0; i < batch->w.size(); i++) {
+            int rc = launch_gemv(ctx, batch->w[i], batch->x[i], batch->w[i]->k, batch->y[i], batch->w[i]->n_local, batch->m);
+            if (rc != B200Q_OK) return rc;
+        }
     }
     if (ms_out) {
         B200Q_CUDA(cudaEventRecord(ctx->ev1, ctx->stream), B200Q_ERR_DEVICE);
@@ -136,9 +223,19 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
 }
 
 int b200q_batch_free(b200q_batch* batch) {
+    if (!batch) return B200Q_OK;
+    if (batch->d_ops || batch->d_ranges) {
+        cudaSetDevice(batch->ctx->device);
+        cudaStreamSynchronize(batch->ctx->stream);
+        if (batch->d_ops) cudaFree(batch->d_ops);
+        if (batch->d_ranges) cudaFree(batch->d_ranges);
+        cudaGetLastError();
+    }
     delete batch;
     return B200Q_OK;
 }
+
+int b200q_batch_launches(const b200q_batch* batch) { return batch ? (batch->grouped ? 1 : (int)batch->w.size()) : 0; }
 
 size_t b200q_batch_weight_bytes(const b200q_batch* batch) { return batch ? batch->weight_bytes : 0; }
 
