@@ -130,6 +130,29 @@ def run_reference(args, rank, world):
         "gpu_launches": 0}))
 
 
+def run_matrix(args, be, peaks):
+    """One packed tensor, m activation rows, timed launch by launch (a small case for profiler captures)."""
+    from rocmforge_b200.backend import QuantizedWeight
+    qt = synth.QNAMES.index(args.qtype)
+    rng = synth.rng_for(4242)
+    data = synth.gen_packed(qt, synth.GGUF, args.n * args.k, rng)
+    x = synth.gen_activations(args.m, args.k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, args.n, args.k)
+    xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
+    yb = be.allocate_buffer(args.m * args.n * 4)
+    for _ in range(max(args.warmup, 1)):
+        w.matmul(xb, yb, args.m)
+    be.synchronize()
+    be.timer_start()
+    for _ in range(args.steps):
+        w.matmul(xb, yb, args.m)
+    ms = be.timer_stop_ms() / args.steps
+    gbs = w.packed_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"workload": "matrix", "qtype": args.qtype, "n": args.n, "k": args.k, "m": args.m,
+                      "packed_bytes": w.packed_bytes, "ms_per_launch": ms, "GB/s": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
+                      "tflops": 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -138,6 +161,11 @@ def main():
     ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--skip-extras", action="store_true", help="headline only (no e2e / cpu baseline / gemm / shard legs)")
+    ap.add_argument("--workload", default="step", choices=["step", "matrix"],
+                    help="step: the decode step (headline); matrix: one [--n, --k] tensor of --qtype (profiling aid)")
+    ap.add_argument("--qtype", default="Q4_K")
+    ap.add_argument("--n", type=int, default=65536)
+    ap.add_argument("--k", type=int, default=4096)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -159,6 +187,9 @@ def main():
     be = B200Backend(local_rank)
     lib = be.lib
     m = args.m
+    if args.workload == "matrix":
+        run_matrix(args, be, peaks)
+        return
     ops, weights, acts = build_step(m)
     W = [QuantizedWeight(be, w, qt, synth.GGUF, n, k) for (_, qt, n, k), w in zip(ops, weights)]
     assert sum(w.packed_bytes for w in W) == STEP_BYTES

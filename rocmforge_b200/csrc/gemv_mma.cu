@@ -4,21 +4,29 @@
 // q6_k_matmul.hip:216: one thread block per ACTIVATION row, one 4-bit code per inner iteration) and the
 // serial per-op loop of BatchQuantizedMatmul::process_batch (src/ggml/hip_backend/ops/batch_quantized.rs:147-161).
 //
-// Design. Streaming 4.5-bit weights at HBM speed leaves ~1 integer instruction per weight, which rules out
-// converting every code to fp32 on the CUDA cores. Instead the raw integer codes are fed to the tensor
-// cores as f16 SUBNORMALS: a 4- or 6-bit code q masked into the low bits of an f16 lane is the number
-// q * 2^-24 (q * 2^-20 for a nibble left in bits 4..7), exactly. One mma.sync.m16n8k16 then multiplies 16
-// weight rows x 16 codes with up to 8 activation rows; the block scale (d * sc, an exact fp32 product) and
-// the 2^24 are applied to the fp32 accumulator afterwards, once per 16/32-weight scale group, and the
-// "- dmin * m" / "- 32" offsets become one FMA with the pre-computed sum of the activations of that group.
-// Activations are split into f16 hi + lo parts (x = s * (hi + lo), s a per-group power of two), so the
-// products carry 22 mantissa bits and accumulate in fp32: the result stays within 1e-4 of the fp32 oracle.
+// Why tensor cores for a GEMV. A B200 SM has to consume ~40 4.5-bit weights per clock to keep up with HBM
+// but issues at most 4 warp instructions per clock, so the budget is ~2.5 thread instructions per weight:
+// converting every code to fp32 and multiplying it on the CUDA cores does not fit. Here the raw integer
+// codes go to the tensor cores as f16 SUBNORMALS: a 4- or 6-bit code q masked into the low bits of an f16
+// lane is exactly q * 2^-24 (q * 2^-20 for a nibble left in bits 4..7). Extraction is one AND per pair of
+// weights; everything else is per 16-weight run.
+//
+// Block-diagonal B operand. In mma.sync.m16n8k16 thread t of a quad supplies k-slots {2t,2t+1,2t+8,2t+9}
+// of the 16 weight rows. Each thread streams its OWN 16-weight runs (16 contiguous bytes of one row), so
+// the 16 k-slots of one MMA belong to four different runs with four different block scales. The 8 columns
+// of B are therefore used as 4 threads x {hi, lo}: column 2t holds the f16 "hi" part of the activations for
+// the k-slots of thread t and zeros elsewhere, column 2t+1 the "lo" part. The accumulator fragment that
+// thread t receives (columns 2t, 2t+1) is then exactly the dot product of ITS run with hi and lo, and the
+// block scale (d * sc, exact in fp32), the 2^24 and the "- dmin * m" / "- 32" offsets (one FMA with the
+// pre-computed sum of the run's activations) are applied once per run by the thread that owns it.
+// Activations are x = s * (hi + lo) with s a power of two per 16-weight run, so products carry 22 mantissa
+// bits and accumulate in fp32: results stay within 1e-4 of the fp32 oracle. More activation rows repeat
+// the MMAs (the extracted codes are reused), so cost grows slowly with m.
 //
 // Work decomposition. A CTA tile is (8 >> kw_log2) tiles of 16 weight rows x the whole k, the 8 warps of
-// the CTA being arranged as row-tiles x k-parts; partial sums of the k-parts meet in shared memory. A
-// launch covers any number of products (a whole decode step): CTAs are persistent and own a contiguous
-// range of CTA tiles balanced by bytes, so each CTA prepares the activations of only the products it
-// touches. Weight loads are software-pipelined 4 chunks deep in registers.
+// the CTA arranged as row-tiles x k-parts; partial sums meet in shared memory. A launch covers any number
+// of products (a whole decode step): CTAs are persistent and own a contiguous range of CTA tiles balanced
+// by bytes, so each CTA prepares the activations of only the products it touches.
 #include <cuda_fp16.h>
 
 #include "gemv_mma.cuh"
@@ -29,6 +37,7 @@ namespace {
 
 constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
+constexpr int RED_FLOATS = 8 * 16 * 8;   // 8 warps x 16 rows x up to 8 activation rows
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -39,91 +48,80 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 __device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ uint2 ldg64(const uint8_t* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
-__device__ __forceinline__ uint32_t ldg32(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
 __device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
+__device__ __forceinline__ uint32_t ldg8(const uint8_t* p) { return __ldg(p); }
 
-// Shared-memory image of one product's activations.
-//   hi / lo : per x-group (4*EPT weights), activation row n and quad lane t: EPT f16 values, in the order
-//             the MMA B fragments want them
-//   ss      : per x-group and row: {2^e scale of the group, sum of the fp32 activations of the group}
-struct XSmem {
-    uint8_t* hi;
-    uint8_t* lo;
+// Shared-memory image of one product's activations, per 16-weight run R and activation row n:
+//   img[(R*m + n)*4 + {0,1}] : f16 hi parts of the 16 activations, in MMA order (4 per MMA)
+//   img[(R*m + n)*4 + {2,3}] : f16 lo parts
+//   ss[R*m + n]              : {power-of-two scale of the run, sum of its fp32 activations}
+struct XImg {
+    uint4* img;
     float2* ss;
 };
 
-template <int EPT>
-__device__ __forceinline__ XSmem xsmem_carve(uint8_t* base, int k, int m) {
-    int nxg = k / (4 * EPT);
-    size_t frag = (size_t)nxg * m * 4 * EPT * 2;
-    XSmem s;
-    s.hi = base;
-    s.lo = base + frag;
-    s.ss = reinterpret_cast<float2*>(base + 2 * frag);
+__device__ __forceinline__ XImg ximg_carve(uint8_t* base, int k, int m) {
+    XImg s;
+    s.img = reinterpret_cast<uint4*>(base);
+    s.ss = reinterpret_cast<float2*>(base + (size_t)(k >> 4) * m * 64);
     return s;
 }
 
-// Converts x[m, k] (fp32, global) into the hi/lo fragment image. One quad of threads per (x-group, row).
-template <int EPT, bool PERM>
-__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const XSmem& s) {
-    const int nq = (k / (4 * EPT)) * m;
-    const int t = threadIdx.x & 3;
-    for (int base = 0; base < nq; base += (int)(blockDim.x >> 2)) {
-        int q = base + (int)(threadIdx.x >> 2);
-        bool valid = q < nq;
-        int qq = valid ? q : 0;
-        int G = qq / m, n = qq - G * m;
-        const float* xp = x + (int64_t)n * ldx + (int64_t)G * 4 * EPT + t * EPT;
-        float v[EPT];
+// x[m, k] (fp32, global) -> image. PERM: MMA j of a run takes elements (4j, 4j+2 | 4j+1, 4j+3), the pairs
+// the nibble masks produce from bytes (0,2) and (1,3); otherwise natural order.
+template <bool PERM>
+__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const XImg& s) {
+    const int total = (k >> 4) * m;
+    for (int q = threadIdx.x; q < total; q += blockDim.x) {
+        int R = q / m, n = q - R * m;
+        const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)R * 16);
+        float v[16];
 #pragma unroll
-        for (int i = 0; i < EPT; i += 4) {
-            float4 f = __ldg(reinterpret_cast<const float4*>(xp + i));
-            v[i] = f.x; v[i + 1] = f.y; v[i + 2] = f.z; v[i + 3] = f.w;
+        for (int i = 0; i < 4; i++) {
+            float4 f = __ldg(xp + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
         }
         float mx = 0.0f, sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < EPT; i++) { mx = fmaxf(mx, fabsf(v[i])); sum += v[i]; }
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-        // power-of-two normalisation of the group so the f16 split never overflows or underflows badly
+        for (int i = 0; i < 16; i++) { mx = fmaxf(mx, fabsf(v[i])); sum += v[i]; }
         int e = (int)((__float_as_uint(mx) >> 23) & 255u);
         e = mx == 0.0f ? 127 : min(max(e, 1), 253);
-        float sdown = __uint_as_float((uint32_t)(254 - e) << 23);
+        float sdown = __uint_as_float((uint32_t)(254 - e) << 23);   // 2^(127-e): the run lands in (-2, 2)
         float sup = __uint_as_float((uint32_t)e << 23);
-        __align__(16) __half h[EPT], l[EPT];
+        __align__(16) __half h[16];
+        __align__(16) __half l[16];
 #pragma unroll
-        for (int i = 0; i < EPT; i++) {
-            float xs = v[i] * sdown;
+        for (int i = 0; i < 16; i++) {
+            int src = PERM ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;   // 0,2,1,3 inside each group of 4
+            float xs = v[src] * sdown;
             h[i] = __float2half_rn(xs);
             l[i] = __float2half_rn(xs - __half2float(h[i]));
         }
-        if (valid) {
-            size_t idx = ((size_t)qq * 4 + t);
-            if constexpr (EPT == 8) {
-                // order e0,e2,e1,e3,e4,e6,e5,e7: the pairs the nibble masks (bytes 0/2, bytes 1/3) produce
-                constexpr int P[8] = {0, 2, 1, 3, 4, 6, 5, 7};
-                __align__(16) __half hp[8], lp[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) { hp[i] = h[PERM ? P[i] : i]; lp[i] = l[PERM ? P[i] : i]; }
-                reinterpret_cast<uint4*>(s.hi)[idx] = *reinterpret_cast<uint4*>(hp);
-                reinterpret_cast<uint4*>(s.lo)[idx] = *reinterpret_cast<uint4*>(lp);
-            } else {
-                reinterpret_cast<uint2*>(s.hi)[idx] = *reinterpret_cast<uint2*>(h);
-                reinterpret_cast<uint2*>(s.lo)[idx] = *reinterpret_cast<uint2*>(l);
-            }
-            if (t == 0) s.ss[qq] = make_float2(sup, sum);
-        }
+        uint4* dst = s.img + (size_t)q * 4;
+        dst[0] = reinterpret_cast<uint4*>(h)[0];
+        dst[1] = reinterpret_cast<uint4*>(h)[1];
+        dst[2] = reinterpret_cast<uint4*>(l)[0];
+        dst[3] = reinterpret_cast<uint4*>(l)[1];
+        s.ss[q] = make_float2(sup, sum);
+    }
+}
+
+// B fragments (4 MMAs x {b0, b1}) of run R for activation row n. Only the two lanes of each quad-owner
+// pair (g == 2t: hi, g == 2t+1: lo) carry data; the other lanes of the warp supply zero columns.
+__device__ __forceinline__ void load_b(const XImg& xs, int R, int m, int n, bool active, int part, uint4& b01, uint4& b23) {
+    b01 = make_uint4(0, 0, 0, 0);
+    b23 = b01;
+    if (active) {
+        const uint4* p = xs.img + ((size_t)R * m + n) * 4 + part * 2;
+        b01 = p[0];
+        b23 = p[1];
     }
 }
 
 // ------------------------------------------------------------------------------------------- Q4_K (GGUF)
-// Decoded super-block header of one weight row: d * 2^20, dmin and the eight 6-bit scales / mins as bytes.
 struct Q4KHdr {
-    float d20, dmin;
-    uint32_t sc_lo, sc_hi, m_lo, m_hi;
+    float d20, dmin;                       // d * 2^20, dmin
+    uint32_t sc_lo, sc_hi, m_lo, m_hi;     // eight 6-bit scales / mins as bytes
 };
 
 __device__ __forceinline__ Q4KHdr q4k_decode_hdr(uint4 h) {
@@ -137,92 +135,88 @@ __device__ __forceinline__ Q4KHdr q4k_decode_hdr(uint4 h) {
     return r;
 }
 
-// One 16-row tile x chunk range [cb, ce) of 64-weight chunks. acc: rows (g, g+8) x activation rows (2t, 2t+1).
-__device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int cb, int ce, const XSmem& xs, float (&acc)[4]) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+// One 16-row tile x halves [hb, he) (a half = 128 weights of a row). Thread (g, t) owns, in every half and
+// for rows g and g+8, bytes [16*(t&1), +16) of chunk (t>>1): 16 weights of a low-nibble sub-block and 16 of
+// the high-nibble sub-block. acc[i][n]: partial sum of row g+8i, activation row n, over this thread's runs.
+template <int MT>
+__device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
+                                         float (&acc)[2][MT]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
+    if (hb >= he) return;
     const uint8_t* base = op.v.p[0];
-    int64_t r[2];
-    r[0] = min((int64_t)rtile * 16 + g, (int64_t)op.n_rows - 1);
-    r[1] = min((int64_t)rtile * 16 + g + 8, (int64_t)op.n_rows - 1);
-    int64_t ci[2] = {(r[0] * op.k) >> 6, (r[1] * op.k) >> 6};   // index of the row's first chunk in the stream
-    Q4KHdr cur[2];
-    uint4 nxt[2];
-    uint2 wb[4][2];
-    if (cb >= ce) return;
+    int64_t hs0[2];   // stream index of the row's first half
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-        cur[i] = q4k_decode_hdr(ldg128(base + ((ci[i] + cb) >> 2) * 144));
-        nxt[i] = make_uint4(0, 0, 0, 0);
+        int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
+        hs0[i] = (r * op.k) >> 7;
     }
-    auto load_w = [&](int c, int i) -> uint2 {
-        int64_t s = ci[i] + c;
-        return ldg64(base + (s >> 2) * 144 + 16 + (int)(s & 3) * 32 + t * 8);
+    const int qoff = 16 + tp * 32 + (t & 1) * 16;   // this thread's 16 bytes inside the first chunk pair
+    auto wptr = [&](int i, int h) -> const uint8_t* {
+        int64_t hs = hs0[i] + h;
+        return base + (hs >> 1) * 144 + (int)(hs & 1) * 64 + qoff;
     };
+    Q4KHdr hdr[2];
+    uint4 wn[2][2];   // two halves of look-ahead
 #pragma unroll
-    for (int j = 0; j < 4; j++)
-        if (cb + j < ce) { wb[j][0] = load_w(cb + j, 0); wb[j][1] = load_w(cb + j, 1); }
-
-    const uint4* xhi = reinterpret_cast<const uint4*>(xs.hi);
-    const uint4* xlo = reinterpret_cast<const uint4*>(xs.lo);
-    const bool have_b = g < m;
-    const int tok0 = 2 * t, tok1 = 2 * t + 1;
-
-    for (int c0 = cb; c0 < ce; c0 += 4) {
+    for (int i = 0; i < 2; i++) {
+        hdr[i] = q4k_decode_hdr(ldg128(base + ((hs0[i] + hb) >> 1) * 144));
+        wn[0][i] = ldg128(wptr(i, hb));
+        wn[1][i] = make_uint4(0, 0, 0, 0);
+        if (hb + 1 < he) wn[1][i] = ldg128(wptr(i, hb + 1));
+    }
+    const bool b_active = (g >> 1) == t;
+    const int b_part = g & 1;
+    for (int h0 = hb; h0 < he; h0 += 2) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            int c = c0 + j;
-            if (c < ce) {
-                uint2 w[2] = {wb[j][0], wb[j][1]};
-                if (c + 4 < ce) { wb[j][0] = load_w(c + 4, 0); wb[j][1] = load_w(c + 4, 1); }
-                int cc[2];
+        for (int j2 = 0; j2 < 2; j2++) {
+            const int h = h0 + j2;
+            if (h < he) {
+                uint4 w[2] = {wn[j2][0], wn[j2][1]};
+                float dA[2], dB[2], nA[2], nB[2];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
-                    int64_t s = ci[i] + c;
-                    cc[i] = (int)(s & 3);
-                    if (cc[i] == 0 && c != cb) cur[i] = q4k_decode_hdr(nxt[i]);
-                    if (cc[i] == 0 || c == cb) {
-                        // prefetch the header of the following super-block if this warp will reach it
-                        int64_t nsb = (s >> 2) + 1;
-                        if (nsb * 4 - ci[i] < ce) nxt[i] = ldg128(base + nsb * 144);
+                    int64_t hs = hs0[i] + h;
+                    int half = (int)(hs & 1);
+                    if (half == 0 && h != hb) hdr[i] = q4k_decode_hdr(ldg128(base + (hs >> 1) * 144));
+                    if (h + 2 < he) wn[j2][i] = ldg128(wptr(i, h + 2));
+                    // this thread's chunk c = 2*half + tp holds sub-blocks 2c (low nibbles) and 2c+1 (high)
+                    uint32_t scw = half ? hdr[i].sc_hi : hdr[i].sc_lo;
+                    uint32_t mw = half ? hdr[i].m_hi : hdr[i].m_lo;
+                    int sh = tp * 16;
+                    dA[i] = hdr[i].d20 * 16.0f * (float)((scw >> sh) & 0xFFu);     // d * sc * 2^24
+                    dB[i] = hdr[i].d20 * (float)((scw >> (sh + 8)) & 0xFFu);       // d * sc * 2^20
+                    nA[i] = hdr[i].dmin * (float)((mw >> sh) & 0xFFu);
+                    nB[i] = hdr[i].dmin * (float)((mw >> (sh + 8)) & 0xFFu);
+                }
+                const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
+                const uint32_t w0[4] = {w[0].x, w[0].y, w[0].z, w[0].w};
+                const uint32_t w1[4] = {w[1].x, w[1].y, w[1].z, w[1].w};
+                uint32_t s0[4], s1[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
+                const int RA = 8 * h + 4 * tp + (t & 1);   // run of the low-nibble weights; high nibbles: RA + 2
+#pragma unroll
+                for (int n = 0; n < MT; n++) {
+                    if (n < m) {
+                        uint4 b01, b23;
+                        float cA[4] = {0.f, 0.f, 0.f, 0.f}, cB[4] = {0.f, 0.f, 0.f, 0.f};
+                        load_b(xs, RA, m, n, b_active, b_part, b01, b23);
+                        mma16816(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
+                        mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
+                        mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
+                        mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
+                        load_b(xs, RA + 2, m, n, b_active, b_part, b01, b23);
+                        mma16816(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
+                        mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
+                        mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
+                        mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
+                        float2 sa = xs.ss[(size_t)RA * m + n], sb = xs.ss[(size_t)(RA + 2) * m + n];
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
+                            acc[i][n] += va * (dA[i] * sa.x) - nA[i] * sa.y + vb * (dB[i] * sb.x) - nB[i] * sb.y;
+                        }
                     }
-                }
-                // B fragments of the two 32-weight groups of this chunk
-                uint4 bhA = make_uint4(0, 0, 0, 0), blA = bhA, bhB = bhA, blB = bhA;
-                if (have_b) {
-                    size_t ia = ((size_t)(2 * c) * m + g) * 4 + t, ib = ((size_t)(2 * c + 1) * m + g) * 4 + t;
-                    bhA = xhi[ia]; blA = xlo[ia]; bhB = xhi[ib]; blB = xlo[ib];
-                }
-                float cA[4] = {0.f, 0.f, 0.f, 0.f}, cB[4] = {0.f, 0.f, 0.f, 0.f};
-                {
-                    // low nibbles -> sub-block 2cc (codes * 2^-24), high nibbles -> sub-block 2cc+1 (codes * 2^-20)
-                    uint32_t x0 = w[0].x, x1 = w[1].x, y0 = w[0].y, y1 = w[1].y;
-                    uint32_t x0s = x0 >> 8, x1s = x1 >> 8, y0s = y0 >> 8, y1s = y1 >> 8;
-                    const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
-                    mma16816(cA, x0 & ML, x1 & ML, x0s & ML, x1s & ML, bhA.x, bhA.y);
-                    mma16816(cA, y0 & ML, y1 & ML, y0s & ML, y1s & ML, bhA.z, bhA.w);
-                    mma16816(cA, x0 & ML, x1 & ML, x0s & ML, x1s & ML, blA.x, blA.y);
-                    mma16816(cA, y0 & ML, y1 & ML, y0s & ML, y1s & ML, blA.z, blA.w);
-                    mma16816(cB, x0 & MH, x1 & MH, x0s & MH, x1s & MH, bhB.x, bhB.y);
-                    mma16816(cB, y0 & MH, y1 & MH, y0s & MH, y1s & MH, bhB.z, bhB.w);
-                    mma16816(cB, x0 & MH, x1 & MH, x0s & MH, x1s & MH, blB.x, blB.y);
-                    mma16816(cB, y0 & MH, y1 & MH, y0s & MH, y1s & MH, blB.z, blB.w);
-                }
-                // scales of the activations (2^e, sum) for the activation rows this thread accumulates
-                float2 sA0 = make_float2(0.f, 0.f), sA1 = sA0, sB0 = sA0, sB1 = sA0;
-                if (tok0 < m) { sA0 = xs.ss[(size_t)(2 * c) * m + tok0]; sB0 = xs.ss[(size_t)(2 * c + 1) * m + tok0]; }
-                if (tok1 < m) { sA1 = xs.ss[(size_t)(2 * c) * m + tok1]; sB1 = xs.ss[(size_t)(2 * c + 1) * m + tok1]; }
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    uint32_t scw = cc[i] < 2 ? cur[i].sc_lo : cur[i].sc_hi;
-                    uint32_t mw = cc[i] < 2 ? cur[i].m_lo : cur[i].m_hi;
-                    int sh = (cc[i] & 1) * 16;
-                    float scA = (float)((scw >> sh) & 0xFFu), scB = (float)((scw >> (sh + 8)) & 0xFFu);
-                    float mA = (float)((mw >> sh) & 0xFFu), mB = (float)((mw >> (sh + 8)) & 0xFFu);
-                    float dA = cur[i].d20 * 16.0f * scA;   // d * sc * 2^24
-                    float dB = cur[i].d20 * scB;           // d * sc * 2^20
-                    float nA = cur[i].dmin * mA, nB = cur[i].dmin * mB;
-                    acc[2 * i] += cA[2 * i] * (dA * sA0.x) - nA * sA0.y + cB[2 * i] * (dB * sB0.x) - nB * sB0.y;
-                    acc[2 * i + 1] += cA[2 * i + 1] * (dA * sA1.x) - nA * sA1.y + cB[2 * i + 1] * (dB * sB1.x) - nB * sB1.y;
                 }
             }
         }
@@ -230,87 +224,91 @@ __device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int cb
 }
 
 // ------------------------------------------------------------------------------------------- Q6_K (GGUF)
-struct Q6KUnit {      // the bytes one thread needs of one 128-weight half of one row
-    uint32_t ql[4];   // [a*2 + lh]: ql word at a*32 + lh*16 + 4t
-    uint32_t qh[2];   // [lh]
-    uint2 sc;         // 8 int8 scales of the half
-    uint32_t d;       // f16 bits
+// Thread (g, t) owns, in every 128-weight half and for rows g and g+8, 16 bytes of ql (32-run a = t>>1 in
+// its low nibbles, 32-run a+2 in its high nibbles; 16-weight half lh = t&1 of each) and the matching 16
+// bytes of qh: two runs of 16 weights with one int8 scale each.
+struct Q6KW {
+    uint4 ql, qh;
+    uint32_t s_lo, s_hi;   // int8 scales of the two runs
+    uint32_t d;            // f16 bits
 };
 
-__device__ __forceinline__ Q6KUnit q6k_load(const WView& v, int64_t unit, int t) {
-    int64_t blk = unit >> 1;
-    int half = (int)(unit & 1);
-    const uint8_t* ql = v.p[0] + blk * 128 + half * 64 + 4 * t;
-    const uint8_t* qh = v.p[1] + blk * 64 + half * 32 + 4 * t;
-    Q6KUnit u;
-    u.ql[0] = ldg32(ql); u.ql[1] = ldg32(ql + 16); u.ql[2] = ldg32(ql + 32); u.ql[3] = ldg32(ql + 48);
-    u.qh[0] = ldg32(qh); u.qh[1] = ldg32(qh + 16);
-    u.sc = ldg64(v.p[2] + blk * 16 + half * 8);
-    u.d = ldg16(v.p[3] + blk * 2);
-    return u;
+__device__ __forceinline__ Q6KW q6k_load(const WView& v, int64_t hs, int t) {
+    int64_t blk = hs >> 1;
+    int half = (int)(hs & 1), a = t >> 1, lh = t & 1;
+    Q6KW w;
+    w.ql = ldg128(v.p[0] + blk * 128 + half * 64 + a * 32 + lh * 16);
+    w.qh = ldg128(v.p[1] + blk * 64 + half * 32 + lh * 16);
+    const uint8_t* sc = v.p[2] + blk * 16 + half * 8 + 2 * a + lh;
+    w.s_lo = ldg8(sc);
+    w.s_hi = ldg8(sc + 4);
+    w.d = ldg16(v.p[3] + blk * 2);
+    return w;
 }
 
-__device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int ub, int ue, const XSmem& xs, float (&acc)[4]) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    int64_t r[2];
-    r[0] = min((int64_t)rtile * 16 + g, (int64_t)op.n_rows - 1);
-    r[1] = min((int64_t)rtile * 16 + g + 8, (int64_t)op.n_rows - 1);
-    int64_t ui[2] = {(r[0] * op.k) >> 7, (r[1] * op.k) >> 7};
-    if (ub >= ue) return;
-    Q6KUnit nb[2][2];
+template <int MT>
+__device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
+                                         float (&acc)[2][MT]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, a = t >> 1, lh = t & 1;
+    if (hb >= he) return;
+    int64_t hs0[2];
 #pragma unroll
-    for (int j = 0; j < 2; j++)
-        if (ub + j < ue) { nb[j][0] = q6k_load(op.v, ui[0] + ub + j, t); nb[j][1] = q6k_load(op.v, ui[1] + ub + j, t); }
-    const uint2* xhi = reinterpret_cast<const uint2*>(xs.hi);
-    const uint2* xlo = reinterpret_cast<const uint2*>(xs.lo);
-    const bool have_b = g < m;
-    const int tok0 = 2 * t, tok1 = 2 * t + 1;
-    for (int u0 = ub; u0 < ue; u0 += 2) {
+    for (int i = 0; i < 2; i++) {
+        int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
+        hs0[i] = (r * op.k) >> 7;
+    }
+    Q6KW wn[2];   // one half of look-ahead
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            int u = u0 + j;
-            if (u < ue) {
-                Q6KUnit w[2] = {nb[j][0], nb[j][1]};
-                if (u + 2 < ue) { nb[j][0] = q6k_load(op.v, ui[0] + u + 2, t); nb[j][1] = q6k_load(op.v, ui[1] + u + 2, t); }
-                float d24[2];
+    for (int i = 0; i < 2; i++) wn[i] = q6k_load(op.v, hs0[i] + hb, t);
+    const bool b_active = (g >> 1) == t;
+    const int b_part = g & 1;
+    const int shl = 4 - 2 * a, shr = 2 * a;
+    for (int h = hb; h < he; h++) {
+        Q6KW w[2] = {wn[0], wn[1]};
+        if (h + 1 < he) {
+            wn[0] = q6k_load(op.v, hs0[0] + h + 1, t);
+            wn[1] = q6k_load(op.v, hs0[1] + h + 1, t);
+        }
+        uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
+        float dL[2], dH[2];
 #pragma unroll
-                for (int i = 0; i < 2; i++)
-                    d24[i] = __half2float(__ushort_as_half((unsigned short)w[i].d)) * 16777216.0f;
+        for (int i = 0; i < 2; i++) {
+            const uint32_t ql[4] = {w[i].ql.x, w[i].ql.y, w[i].ql.z, w[i].ql.w};
+            const uint32_t qh[4] = {w[i].qh.x, w[i].qh.y, w[i].qh.z, w[i].qh.w};
 #pragma unroll
-                for (int gg = 0; gg < 4; gg++) {
+            for (int j = 0; j < 4; j++) {
+                uint32_t cl = (ql[j] & 0x0F0F0F0Fu) | ((qh[j] << shl) & 0x30303030u);          // 32-run a
+                uint32_t ch = ((ql[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> shr) & 0x30303030u);   // 32-run a+2
+                aL[i][j][0] = __byte_perm(cl, 0, 0x4140); aL[i][j][1] = __byte_perm(cl, 0, 0x4342);
+                aH[i][j][0] = __byte_perm(ch, 0, 0x4140); aH[i][j][1] = __byte_perm(ch, 0, 0x4342);
+            }
+            float d24 = __half2float(__ushort_as_half((unsigned short)w[i].d)) * 16777216.0f;
+            dL[i] = d24 * (float)(int)(int8_t)w[i].s_lo;   // d * scale * 2^24
+            dH[i] = d24 * (float)(int)(int8_t)w[i].s_hi;
+        }
+        const int RL = 8 * h + 2 * a + lh;   // run of the low-nibble codes; high nibbles: RL + 4
 #pragma unroll
-                    for (int lh = 0; lh < 2; lh++) {
-                        const int s = 2 * gg + lh;                 // scale group inside the half
-                        uint32_t c4[2];
+        for (int n = 0; n < MT; n++) {
+            if (n < m) {
+                uint4 b01, b23;
+                float cL[4] = {0.f, 0.f, 0.f, 0.f}, cH[4] = {0.f, 0.f, 0.f, 0.f};
+                load_b(xs, RL, m, n, b_active, b_part, b01, b23);
+                mma16816(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
+                mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
+                mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
+                mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
+                load_b(xs, RL + 4, m, n, b_active, b_part, b01, b23);
+                mma16816(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
+                mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
+                mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
+                mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
+                float2 sl = xs.ss[(size_t)RL * m + n], sh = xs.ss[(size_t)(RL + 4) * m + n];
+                const float k32 = 32.0f / 16777216.0f;
 #pragma unroll
-                        for (int i = 0; i < 2; i++) {
-                            uint32_t qlw = w[i].ql[(gg & 1) * 2 + lh], qhw = w[i].qh[lh];
-                            uint32_t lo4 = gg < 2 ? (qlw & 0x0F0F0F0Fu) : ((qlw >> 4) & 0x0F0F0F0Fu);
-                            uint32_t hs = gg == 0 ? (qhw << 4) : gg == 1 ? (qhw << 2) : gg == 2 ? qhw : (qhw >> 2);
-                            c4[i] = lo4 | (hs & 0x30303030u);      // four 6-bit codes, one per byte
-                        }
-                        // bytes -> f16 lanes (code * 2^-24): (b0,b1) and (b2,b3)
-                        uint32_t a0 = __byte_perm(c4[0], 0, 0x4140), a2 = __byte_perm(c4[0], 0, 0x4342);
-                        uint32_t a1 = __byte_perm(c4[1], 0, 0x4140), a3 = __byte_perm(c4[1], 0, 0x4342);
-                        size_t xg = (size_t)u * 8 + s;
-                        uint2 bh = make_uint2(0, 0), bl = bh;
-                        if (have_b) { size_t ix = (xg * m + g) * 4 + t; bh = xhi[ix]; bl = xlo[ix]; }
-                        float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma16816(c, a0, a1, a2, a3, bh.x, bh.y);
-                        mma16816(c, a0, a1, a2, a3, bl.x, bl.y);
-                        float2 s0 = make_float2(0.f, 0.f), s1 = s0;
-                        if (tok0 < m) s0 = xs.ss[xg * m + tok0];
-                        if (tok1 < m) s1 = xs.ss[xg * m + tok1];
-#pragma unroll
-                        for (int i = 0; i < 2; i++) {
-                            uint32_t scw = s < 4 ? w[i].sc.x : w[i].sc.y;
-                            float sc = (float)(int)(int8_t)((scw >> (8 * (s & 3))) & 0xFFu);
-                            float ds = d24[i] * sc;                     // d * scale * 2^24
-                            float off = ds * (32.0f / 16777216.0f);     // 32 * d * scale
-                            acc[2 * i] += c[2 * i] * (ds * s0.x) - off * s0.y;
-                            acc[2 * i + 1] += c[2 * i + 1] * (ds * s1.x) - off * s1.y;
-                        }
-                    }
+                for (int i = 0; i < 2; i++) {
+                    float vl = cL[2 * i] + cL[2 * i + 1], vh = cH[2 * i] + cH[2 * i + 1];
+                    // d * sc * (sum q x - 32 sum x)
+                    acc[i][n] += dL[i] * (vl * sl.x - k32 * sl.y) + dH[i] * (vh * sh.x - k32 * sh.y);
                 }
             }
         }
@@ -318,11 +316,12 @@ __device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int ub
 }
 
 // --------------------------------------------------------------------------------------------- kernel
+template <int MT>
 __global__ void __launch_bounds__(256, 2)
 gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_tiles, int m) {
     extern __shared__ __align__(16) uint8_t smem[];
-    float* red = reinterpret_cast<float*>(smem);          // 8 warps x 32 lanes x 4 partial sums
-    uint8_t* xbase = smem + 8 * 32 * 4 * sizeof(float);
+    float* red = reinterpret_cast<float*>(smem);
+    uint8_t* xbase = smem + RED_FLOATS * sizeof(float);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int tb, te;
     if (ranges) {
@@ -342,7 +341,7 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         opi = lo;
     }
     GOp op = single;
-    XSmem xs{};
+    XImg xs{};
     for (int tile = tb; tile < te; tile++) {
         if (n_ops > 1) {
             while (opi < n_ops - 1 && tile >= ops[opi].tile0 + ops[opi].ntiles) opi++;
@@ -350,80 +349,91 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         if (opi != cur) {
             if (n_ops > 1) op = ops[opi];
             __syncthreads();   // everyone is done with the previous product's activations
-            if (op.fmt == F_Q4K) {
-                xs = xsmem_carve<8>(xbase, op.k, m);
-                prep_x<8, true>(op.x, op.ldx, op.k, m, xs);
-            } else {
-                xs = xsmem_carve<4>(xbase, op.k, m);
-                prep_x<4, false>(op.x, op.ldx, op.k, m, xs);
-            }
+            xs = ximg_carve(xbase, op.k, m);
+            if (op.fmt == F_Q4K) prep_x<true>(op.x, op.ldx, op.k, m, xs);
+            else prep_x<false>(op.x, op.ldx, op.k, m, xs);
             __syncthreads();
             cur = opi;
         }
         const int kw = 1 << op.kw_log2;
         const int rtile = (tile - op.tile0) * (8 >> op.kw_log2) + (warp >> op.kw_log2);
         const int kpart = warp & (kw - 1);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[2][MT];
+#pragma unroll
+        for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
         const bool live = (int64_t)rtile * 16 < op.n_rows;
         if (live) {
-            if (op.fmt == F_Q4K) {
-                int n = op.k >> 6, per = (n + kw - 1) >> op.kw_log2;
-                tile_q4k(op, m, rtile, kpart * per, min(n, (kpart + 1) * per), xs, acc);
-            } else {
-                int n = op.k >> 7, per = (n + kw - 1) >> op.kw_log2;
-                tile_q6k(op, m, rtile, kpart * per, min(n, (kpart + 1) * per), xs, acc);
-            }
+            int nh = op.k >> 7, per = (nh + kw - 1) >> op.kw_log2;
+            int hb = kpart * per, he = min(nh, (kpart + 1) * per);
+            if (op.fmt == F_Q4K) tile_q4k<MT>(op, m, rtile, hb, he, xs, acc);
+            else tile_q6k<MT>(op, m, rtile, hb, he, xs, acc);
         }
-        if (kw > 1) {
-            if (kpart != 0) {
-                float4* dst = reinterpret_cast<float4*>(red) + warp * 32 + lane;
-                *dst = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            }
-            __syncthreads();
-            if (kpart == 0) {
-                for (int j = 1; j < kw; j++) {
-                    float4 p = reinterpret_cast<const float4*>(red)[(warp + j) * 32 + lane];
-                    acc[0] += p.x; acc[1] += p.y; acc[2] += p.z; acc[3] += p.w;
-                }
-            }
-        }
-        if (kpart == 0 && live) {
-            const int g = lane >> 2, t = lane & 3;
+        // the four threads of a quad hold partial sums of the same two rows
+#pragma unroll
+        for (int n = 0; n < MT; n++) {
 #pragma unroll
             for (int i = 0; i < 2; i++) {
-                int64_t row = (int64_t)rtile * 16 + g + 8 * i;
-                if (row < op.n_rows) {
-                    if (2 * t < m) op.y[(int64_t)(2 * t) * op.ldy + row] = acc[2 * i];
-                    if (2 * t + 1 < m) op.y[(int64_t)(2 * t + 1) * op.ldy + row] = acc[2 * i + 1];
+                float s = acc[i][n];
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+                acc[i][n] = s;
+            }
+        }
+        const int g = lane >> 2, t = lane & 3;
+        if (kw > 1) {
+            if (t == 0) {
+#pragma unroll
+                for (int n = 0; n < MT; n++) {
+                    red[(warp * 16 + g) * MT + n] = acc[0][n];
+                    red[(warp * 16 + g + 8) * MT + n] = acc[1][n];
+                }
+            }
+            __syncthreads();
+            if (kpart == 0 && live) {
+                for (int o = lane; o < 16 * MT; o += 32) {
+                    int r = o / MT, n = o - r * MT;
+                    float s = 0.f;
+                    for (int j = 0; j < kw; j++) s += red[((warp + j) * 16 + r) * MT + n];
+                    int64_t row = (int64_t)rtile * 16 + r;
+                    if (row < op.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = s;
+                }
+            }
+            __syncthreads();   // the reduction buffer is free again
+        } else if (live && t == 0) {
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                if (n < m) {
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        int64_t row = (int64_t)rtile * 16 + g + 8 * i;
+                        if (row < op.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n];
+                    }
                 }
             }
         }
-        if (kw > 1) __syncthreads();   // the reduction buffer is free again
     }
 }
 
 }  // namespace
 
+size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
+    (void)fmt;
+    return RED_FLOATS * sizeof(float) + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
+}
+
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24)) return false;
-    if (w->fmt == F_Q4K) { if (w->k % 64) return false; }
-    else if (w->fmt == F_Q6K) { if (w->k % 128) return false; }
-    else return false;
+    if (w->fmt != F_Q4K && w->fmt != F_Q6K) return false;
+    if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 200 * 1024;
-}
-
-size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
-    int ept = fmt == F_Q4K ? 8 : 4;
-    size_t nxg = (size_t)k / (4 * ept);
-    return 8 * 32 * 4 * sizeof(float) + 2 * nxg * m * 4 * ept * 2 + nxg * m * sizeof(float2) + 16;
 }
 
 void gemv_mma_plan(GOp* op, bool few_tiles) {
     FmtInfo I = fmt_info(op->fmt);
     double row_bytes = (double)op->k * I.block_bytes / I.block_elems;
-    int units = op->fmt == F_Q4K ? op->k / 64 : op->k / 128;
-    // aim at ~48 KB of packed weights per CTA tile, at least one k-unit per warp
+    int units = op->k / 128;
+    // aim at ~48 KB of packed weights per CTA tile, at least one 128-weight half per warp
     int rt = 8;
     while (rt > 1 && rt * 16 * row_bytes > 48.0 * 1024) rt >>= 1;
     int row_tiles = (op->n_rows + 15) / 16;
@@ -440,15 +450,28 @@ void gemv_mma_plan(GOp* op, bool few_tiles) {
 int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
                     int total_tiles, int m, size_t smem_bytes) {
     if (total_tiles <= 0) return B200Q_OK;
-    static size_t configured[64] = {0};
-    if (smem_bytes > configured[ctx->device & 63]) {
-        B200Q_CUDA(cudaFuncSetAttribute(gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024 + 8192)),
-                   B200Q_ERR_LAUNCH);
-        configured[ctx->device & 63] = 200 * 1024 + 8192;
+    static bool configured[64][4] = {};
+    const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
+    const int smem_cap = 200 * 1024 + 8192;
+    if (!configured[ctx->device & 63][mi]) {
+        cudaError_t e = cudaSuccess;
+        switch (mi) {
+            case 0: e = cudaFuncSetAttribute(gemv_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
+            case 1: e = cudaFuncSetAttribute(gemv_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
+            case 2: e = cudaFuncSetAttribute(gemv_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
+            default: e = cudaFuncSetAttribute(gemv_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
+        }
+        B200Q_CUDA(e, B200Q_ERR_LAUNCH);
+        configured[ctx->device & 63][mi] = true;
     }
     GOp single{};
     if (h_single) single = *h_single;
-    gemv_mma_kernel<<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m);
+    switch (mi) {
+        case 0: gemv_mma_kernel<1><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
+        case 1: gemv_mma_kernel<2><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
+        case 2: gemv_mma_kernel<4><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
+        default: gemv_mma_kernel<8><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
+    }
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }

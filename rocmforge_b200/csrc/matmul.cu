@@ -46,10 +46,15 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
     if ((flags & B200Q_MM_SEQUENTIAL) || !gemv_fast_supported(w)) return launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
     bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx % 4) == 0;
     if (!aligned) return launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
-    for (int i = 0; i < m; i += 8) {
-        int mm = m - i < 8 ? m - i : 8;
+    // largest activation-row chunk whose shared-memory image fits the tensor-core decode kernel
+    int chunk = 8;
+    while (chunk > 1 && !gemv_mma_supported(w, chunk)) chunk >>= 1;
+    const bool mma = gemv_mma_supported(w, chunk);
+    if (!mma) chunk = 8;
+    for (int i = 0; i < m; i += chunk) {
+        int mm = m - i < chunk ? m - i : chunk;
         int rc;
-        if (gemv_mma_supported(w, mm)) {
+        if (mma) {
             GOp op = make_gop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
             gemv_mma_plan(&op, true);
             op.tile0 = 0;
@@ -138,6 +143,7 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
     for (int i = 0; i < count; i++) {
         int rc = check_matmul_args(ctx, w[i], d_x[i], d_y[i], m);
         if (rc == B200Q_OK && !gemv_fast_supported(w[i])) rc = fail(B200Q_ERR_UNSUPPORTED, "batch_create: op %d is not an NK tensor with k %% 8 == 0", i);
+        if (rc == B200Q_OK && (reinterpret_cast<uintptr_t>(d_x[i]) & 15) != 0) rc = fail(B200Q_ERR_INVALID, "batch_create: activations of op %d are not 16-byte aligned", i);
         if (rc != B200Q_OK) { delete b; return rc; }
         b->w.push_back(w[i]);
         b->x.push_back(d_x[i]);

@@ -44,7 +44,7 @@ def test_grouped_launch_of_mixed_products(oracle, m):
     rng = synth.rng_for(500 + m)
     ops = [(synth.Q4_K, 896, 896), (synth.Q4_K, 128, 896), (synth.Q4_K, 100, 896), (synth.Q6_K, 896, 4864),
            (synth.Q4_K, 4864, 896), (synth.Q6_K, 1000, 896), (synth.Q4_K, 48, 4096), (synth.Q6_K, 17, 128),
-           (synth.Q4_K, 1, 64)]
+           (synth.Q4_K, 1, 128)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(m, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, m)
