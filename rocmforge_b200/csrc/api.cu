@@ -27,8 +27,8 @@ int cuda_fail(int code, cudaError_t e, const char* what) {
 }
 
 int ensure_scratch(b200q_ctx* ctx, size_t bytes, int which) {
-    void** p = which == 0 ? &ctx->scratch : &ctx->scratch2;
-    size_t* sz = which == 0 ? &ctx->scratch_bytes : &ctx->scratch2_bytes;
+    void** p = which == 0 ? &ctx->scratch : which == 1 ? &ctx->scratch2 : &ctx->scratch3;
+    size_t* sz = which == 0 ? &ctx->scratch_bytes : which == 1 ? &ctx->scratch2_bytes : &ctx->scratch3_bytes;
     if (*sz >= bytes) return B200Q_OK;
     if (*p) {
         B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
@@ -122,6 +122,7 @@ void b200q_destroy(b200q_ctx* ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->scratch2) cudaFree(ctx->scratch2);
+    if (ctx->scratch3) cudaFree(ctx->scratch3);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
@@ -191,6 +192,10 @@ int b200q_memset(b200q_ctx* ctx, void* d_dst, int value, size_t bytes) {
 int b200q_synchronize(b200q_ctx* ctx) {
     CTX_GUARD("synchronize");
     B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+    if (ctx->tc_pending) {
+        ctx->tc_pending = false;
+        return gemm_tc_check_status(ctx);
+    }
     return B200Q_OK;
 }
 

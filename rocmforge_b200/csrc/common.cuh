@@ -20,6 +20,9 @@ struct b200q_ctx {
     void* scratch2 = nullptr;
     size_t scratch2_bytes = 0;
     int* d_status = nullptr;  // device word the tensor-core kernel reports bounded-wait failures in
+    bool tc_pending = false;  // a tensor-core launch has not had its status word read yet
+    void* scratch3 = nullptr; // f16 copy of the activations + row scales for the tensor-core path
+    size_t scratch3_bytes = 0;
 };
 
 struct b200q_weight {
@@ -57,5 +60,9 @@ int launch_matmul_seq(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, i
 int launch_convert_bf16_to_f32(b200q_ctx* ctx, const void* d_in, int64_t ld_in, float* d_out, int64_t ld_out, int rows, int64_t cols);
 int launch_convert_f32_to_bf16(b200q_ctx* ctx, const float* d_in, int64_t ld_in, void* d_out, int64_t ld_out, int rows, int64_t cols);
 bool gemv_fast_supported(const b200q_weight* w);
+// gemm_tc.cu
+bool gemm_tc_supported(const b200q_weight* w, int m);
+int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m);
+int gemm_tc_check_status(b200q_ctx* ctx);
 
 }  // namespace b200q

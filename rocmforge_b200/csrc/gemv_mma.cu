@@ -47,7 +47,21 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// First MMA of a run: the accumulator input is the constant zero (no register initialisation needed).
+__device__ __forceinline__ void mma16816_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 __device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// Pulls the line into L2 ahead of use; costs no register and may point past the end of a row (never past
+// the tensor's allocation: callers clamp to `lim`).
+__device__ __forceinline__ void prefetch_l2(const uint8_t* p, const uint8_t* lim) {
+    if (p < lim) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
 __device__ __forceinline__ uint32_t ldg8(const uint8_t* p) { return __ldg(p); }
 
@@ -60,11 +74,35 @@ struct XImg {
     float2* ss;
 };
 
+// The first 32 bytes of the activation area stay zero: lanes that supply the zero columns of B read them.
+constexpr int XZERO_BYTES = 32;
+
 __device__ __forceinline__ XImg ximg_carve(uint8_t* base, int k, int m) {
     XImg s;
-    s.img = reinterpret_cast<uint4*>(base);
-    s.ss = reinterpret_cast<float2*>(base + (size_t)(k >> 4) * m * 64);
+    s.img = reinterpret_cast<uint4*>(base + XZERO_BYTES);
+    s.ss = reinterpret_cast<float2*>(base + XZERO_BYTES + (size_t)(k >> 4) * m * 64);
     return s;
+}
+
+// Per-lane view of the B operand: lanes g == 2t (hi) and g == 2t+1 (lo) read the image of their run, every
+// other lane reads the zero region (stride 0), so the loads need no predicate.
+struct BLane {
+    const uint4* base;
+    int mult;   // 4 uint4 per (run, activation row) for data lanes, 0 for zero lanes
+};
+
+__device__ __forceinline__ BLane blane_make(const XImg& xs, uint8_t* xbase, int g, int t) {
+    BLane b;
+    bool active = (g >> 1) == t;
+    b.base = active ? xs.img + (g & 1) * 2 : reinterpret_cast<const uint4*>(xbase);
+    b.mult = active ? 4 : 0;
+    return b;
+}
+
+__device__ __forceinline__ void load_b(const BLane& bl, int run_row, uint4& b01, uint4& b23) {
+    const uint4* p = bl.base + run_row * bl.mult;
+    b01 = p[0];
+    b23 = p[1];
 }
 
 // x[m, k] (fp32, global) -> image. PERM: MMA j of a run takes elements (4j, 4j+2 | 4j+1, 4j+3), the pairs
@@ -106,33 +144,35 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
     }
 }
 
-// B fragments (4 MMAs x {b0, b1}) of run R for activation row n. Only the two lanes of each quad-owner
-// pair (g == 2t: hi, g == 2t+1: lo) carry data; the other lanes of the warp supply zero columns.
-__device__ __forceinline__ void load_b(const XImg& xs, int R, int m, int n, bool active, int part, uint4& b01, uint4& b23) {
-    b01 = make_uint4(0, 0, 0, 0);
-    b23 = b01;
-    if (active) {
-        const uint4* p = xs.img + ((size_t)R * m + n) * 4 + part * 2;
-        b01 = p[0];
-        b23 = p[1];
-    }
+// ------------------------------------------------------------------------------------------- Q4_K (GGUF)
+// A byte placed in an f16 lane is the subnormal byte * 2^-24: integer -> float without the integer pipe.
+__device__ __forceinline__ float2 bytes_as_f16x2(uint32_t bits) {
+    __half2 h;
+    *reinterpret_cast<uint32_t*>(&h) = bits;
+    return __half22float2(h);
 }
 
-// ------------------------------------------------------------------------------------------- Q4_K (GGUF)
-struct Q4KHdr {
-    float d20, dmin;                       // d * 2^20, dmin
-    uint32_t sc_lo, sc_hi, m_lo, m_hi;     // eight 6-bit scales / mins as bytes
+// The block scales one thread needs from one super-block header of one weight row, multiplied out:
+// per 128-weight half, d*sc*2^24 (low-nibble sub-block), d*sc*2^20 (high-nibble sub-block) and dmin*m of both.
+struct Q4KHalfScales {
+    float dA, dB, nA, nB;
 };
 
-__device__ __forceinline__ Q4KHdr q4k_decode_hdr(uint4 h) {
-    Q4KHdr r;
-    r.d20 = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu))) * 1048576.0f;
-    r.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    r.sc_lo = h.y & 0x3F3F3F3Fu;
-    r.m_lo = h.z & 0x3F3F3F3Fu;
-    r.sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-    r.m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-    return r;
+// sel picks the chunk of each half the thread owns: sub-blocks 2tp, 2tp+1 (half 0) and 4+2tp, 5+2tp (half 1).
+__device__ __forceinline__ void q4k_decode_hdr(uint4 h, uint32_t sel, Q4KHalfScales& h0, Q4KHalfScales& h1) {
+    float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
+    float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+    uint32_t sc_lo = h.y & 0x3F3F3F3Fu, m_lo = h.z & 0x3F3F3F3Fu;
+    uint32_t sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+    uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    // bytes {A of half 0, B of half 0, A of half 1, B of half 1}
+    uint32_t sc4 = __byte_perm(sc_lo, sc_hi, sel), m4 = __byte_perm(m_lo, m_hi, sel);
+    float2 s01 = bytes_as_f16x2(__byte_perm(sc4, 0, 0x4140)), s23 = bytes_as_f16x2(__byte_perm(sc4, 0, 0x4342));
+    float2 m01 = bytes_as_f16x2(__byte_perm(m4, 0, 0x4140)), m23 = bytes_as_f16x2(__byte_perm(m4, 0, 0x4342));
+    const float T24 = 16777216.0f;
+    float d48 = d * T24 * T24, d44 = d * T24 * 1048576.0f, dm24 = dmin * T24;
+    h0.dA = d48 * s01.x; h0.dB = d44 * s01.y; h0.nA = dm24 * m01.x; h0.nB = dm24 * m01.y;
+    h1.dA = d48 * s23.x; h1.dB = d44 * s23.y; h1.nA = dm24 * m23.x; h1.nB = dm24 * m23.y;
 }
 
 // One 16-row tile x halves [hb, he) (a half = 128 weights of a row). Thread (g, t) owns, in every half and
@@ -140,53 +180,63 @@ __device__ __forceinline__ Q4KHdr q4k_decode_hdr(uint4 h) {
 // the high-nibble sub-block. acc[i][n]: partial sum of row g+8i, activation row n, over this thread's runs.
 template <int MT>
 __device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
-                                         float (&acc)[2][MT]) {
+                                         const BLane& bl, float (&acc)[2][MT]) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
     if (hb >= he) return;
     const uint8_t* base = op.v.p[0];
-    int64_t hs0[2];   // stream index of the row's first half
+    const uint8_t* plim = base + ((((int64_t)op.n_rows * op.k) >> 8) * 144);   // end of the packed tensor
+    const int qoff = 16 + tp * 32 + (t & 1) * 16;   // this thread's 16 bytes inside the first chunk pair
+    const uint32_t sel = tp ? 0x7632u : 0x5410u;
+    // Two look-ahead slots per row; slot s always holds halves of one parity, so its pointer advances by one
+    // whole super-block (144 bytes) per use and whether it sees FIRST halves of super-blocks never changes.
+    const uint8_t* ps[2][2];      // [slot][row]
+    bool first_half[2][2];
+    const uint8_t* hp[2];         // header of the super-block whose first half comes next
+    uint4 hraw[2];                // ... prefetched
+    Q4KHalfScales sc[2][2];       // [slot][row] scales of the half the slot processes next
+    uint4 wn[2][2];
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
-        hs0[i] = (r * op.k) >> 7;
-    }
-    const int qoff = 16 + tp * 32 + (t & 1) * 16;   // this thread's 16 bytes inside the first chunk pair
-    auto wptr = [&](int i, int h) -> const uint8_t* {
-        int64_t hs = hs0[i] + h;
-        return base + (hs >> 1) * 144 + (int)(hs & 1) * 64 + qoff;
-    };
-    Q4KHdr hdr[2];
-    uint4 wn[2][2];   // two halves of look-ahead
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        hdr[i] = q4k_decode_hdr(ldg128(base + ((hs0[i] + hb) >> 1) * 144));
-        wn[0][i] = ldg128(wptr(i, hb));
+        int64_t hs = ((r * op.k) >> 7) + hb;   // stream index of the first half
+        const uint8_t* sb = base + (hs >> 1) * 144;
+        const bool par = (hs & 1) != 0;
+        ps[0][i] = sb + (par ? 64 : 0) + qoff;
+        ps[1][i] = sb + (par ? 144 : 64) + qoff;
+        first_half[0][i] = !par;
+        first_half[1][i] = par;
+        hraw[i] = make_uint4(0, 0, 0, 0);
+        if (par) {   // the row starts in the second half of a super-block: its header is needed at once
+            Q4KHalfScales unused;
+            q4k_decode_hdr(ldg128(sb), sel, unused, sc[0][i]);
+            hp[i] = sb + 144;
+            if (hb + 1 < he) hraw[i] = ldg128(hp[i]);
+        } else {
+            hp[i] = sb;
+            hraw[i] = ldg128(hp[i]);
+        }
+        wn[0][i] = ldg128(ps[0][i]);
         wn[1][i] = make_uint4(0, 0, 0, 0);
-        if (hb + 1 < he) wn[1][i] = ldg128(wptr(i, hb + 1));
+        if (hb + 1 < he) wn[1][i] = ldg128(ps[1][i]);
     }
-    const bool b_active = (g >> 1) == t;
-    const int b_part = g & 1;
     for (int h0 = hb; h0 < he; h0 += 2) {
 #pragma unroll
         for (int j2 = 0; j2 < 2; j2++) {
             const int h = h0 + j2;
             if (h < he) {
                 uint4 w[2] = {wn[j2][0], wn[j2][1]};
-                float dA[2], dB[2], nA[2], nB[2];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
-                    int64_t hs = hs0[i] + h;
-                    int half = (int)(hs & 1);
-                    if (half == 0 && h != hb) hdr[i] = q4k_decode_hdr(ldg128(base + (hs >> 1) * 144));
-                    if (h + 2 < he) wn[j2][i] = ldg128(wptr(i, h + 2));
-                    // this thread's chunk c = 2*half + tp holds sub-blocks 2c (low nibbles) and 2c+1 (high)
-                    uint32_t scw = half ? hdr[i].sc_hi : hdr[i].sc_lo;
-                    uint32_t mw = half ? hdr[i].m_hi : hdr[i].m_lo;
-                    int sh = tp * 16;
-                    dA[i] = hdr[i].d20 * 16.0f * (float)((scw >> sh) & 0xFFu);     // d * sc * 2^24
-                    dB[i] = hdr[i].d20 * (float)((scw >> (sh + 8)) & 0xFFu);       // d * sc * 2^20
-                    nA[i] = hdr[i].dmin * (float)((mw >> sh) & 0xFFu);
-                    nB[i] = hdr[i].dmin * (float)((mw >> (sh + 8)) & 0xFFu);
+                    if (first_half[j2][i]) {
+                        q4k_decode_hdr(hraw[i], sel, sc[j2][i], sc[j2 ^ 1][i]);
+                        hp[i] += 144;
+                        if (h + 2 < he) hraw[i] = ldg128(hp[i]);
+                    }
+                    if (h + 2 < he) {
+                        ps[j2][i] += 144;
+                        wn[j2][i] = ldg128(ps[j2][i]);
+                        prefetch_l2(ps[j2][i] + 6 * 144, plim);
+                    }
                 }
                 const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
                 const uint32_t w0[4] = {w[0].x, w[0].y, w[0].z, w[0].w};
@@ -199,22 +249,23 @@ __device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int hb
                 for (int n = 0; n < MT; n++) {
                     if (n < m) {
                         uint4 b01, b23;
-                        float cA[4] = {0.f, 0.f, 0.f, 0.f}, cB[4] = {0.f, 0.f, 0.f, 0.f};
-                        load_b(xs, RA, m, n, b_active, b_part, b01, b23);
-                        mma16816(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
+                        float cA[4], cB[4];
+                        load_b(bl, RA * m + n, b01, b23);
+                        mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
                         mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
                         mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
                         mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
-                        load_b(xs, RA + 2, m, n, b_active, b_part, b01, b23);
-                        mma16816(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
+                        load_b(bl, (RA + 2) * m + n, b01, b23);
+                        mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
                         mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
                         mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
                         mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
-                        float2 sa = xs.ss[(size_t)RA * m + n], sb = xs.ss[(size_t)(RA + 2) * m + n];
+                        float2 sa = xs.ss[RA * m + n], sb = xs.ss[(RA + 2) * m + n];
 #pragma unroll
                         for (int i = 0; i < 2; i++) {
                             float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
-                            acc[i][n] += va * (dA[i] * sa.x) - nA[i] * sa.y + vb * (dB[i] * sb.x) - nB[i] * sb.y;
+                            const Q4KHalfScales& q = sc[j2][i];
+                            acc[i][n] += va * (q.dA * sa.x) - q.nA * sa.y + vb * (q.dB * sb.x) - q.nB * sb.y;
                         }
                     }
                 }
@@ -226,48 +277,57 @@ __device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int hb
 // ------------------------------------------------------------------------------------------- Q6_K (GGUF)
 // Thread (g, t) owns, in every 128-weight half and for rows g and g+8, 16 bytes of ql (32-run a = t>>1 in
 // its low nibbles, 32-run a+2 in its high nibbles; 16-weight half lh = t&1 of each) and the matching 16
-// bytes of qh: two runs of 16 weights with one int8 scale each.
+// bytes of qh: two runs of 16 weights with one int8 scale each. All four planes are linear in the stream
+// index of the half, so every pointer advances by a constant per half.
 struct Q6KW {
     uint4 ql, qh;
     uint32_t s_lo, s_hi;   // int8 scales of the two runs
     uint32_t d;            // f16 bits
 };
 
-__device__ __forceinline__ Q6KW q6k_load(const WView& v, int64_t hs, int t) {
-    int64_t blk = hs >> 1;
-    int half = (int)(hs & 1), a = t >> 1, lh = t & 1;
+struct Q6KPtr {
+    const uint8_t *ql, *qh, *sc, *d0;   // d0: d plane; indexed with the block number
+    int hs;                             // stream index of the half the pointers address
+};
+
+__device__ __forceinline__ Q6KW q6k_load(const Q6KPtr& p) {
     Q6KW w;
-    w.ql = ldg128(v.p[0] + blk * 128 + half * 64 + a * 32 + lh * 16);
-    w.qh = ldg128(v.p[1] + blk * 64 + half * 32 + lh * 16);
-    const uint8_t* sc = v.p[2] + blk * 16 + half * 8 + 2 * a + lh;
-    w.s_lo = ldg8(sc);
-    w.s_hi = ldg8(sc + 4);
-    w.d = ldg16(v.p[3] + blk * 2);
+    w.ql = ldg128(p.ql);
+    w.qh = ldg128(p.qh);
+    w.s_lo = ldg8(p.sc);
+    w.s_hi = ldg8(p.sc + 4);
+    w.d = ldg16(p.d0 + (p.hs >> 1) * 2);
     return w;
+}
+
+__device__ __forceinline__ void q6k_advance(Q6KPtr& p) {
+    p.ql += 64; p.qh += 32; p.sc += 8; p.hs += 1;
 }
 
 template <int MT>
 __device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
-                                         float (&acc)[2][MT]) {
+                                         const BLane& bl, float (&acc)[2][MT]) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, a = t >> 1, lh = t & 1;
     if (hb >= he) return;
-    int64_t hs0[2];
+    Q6KPtr pp[2];
+    Q6KW wn[2];   // one half of look-ahead
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
-        hs0[i] = (r * op.k) >> 7;
+        int64_t hs = ((r * op.k) >> 7) + hb;
+        pp[i].ql = op.v.p[0] + hs * 64 + a * 32 + lh * 16;
+        pp[i].qh = op.v.p[1] + hs * 32 + lh * 16;
+        pp[i].sc = op.v.p[2] + hs * 8 + 2 * a + lh;
+        pp[i].d0 = op.v.p[3];
+        pp[i].hs = (int)hs;
+        wn[i] = q6k_load(pp[i]);
     }
-    Q6KW wn[2];   // one half of look-ahead
-#pragma unroll
-    for (int i = 0; i < 2; i++) wn[i] = q6k_load(op.v, hs0[i] + hb, t);
-    const bool b_active = (g >> 1) == t;
-    const int b_part = g & 1;
     const int shl = 4 - 2 * a, shr = 2 * a;
     for (int h = hb; h < he; h++) {
         Q6KW w[2] = {wn[0], wn[1]};
         if (h + 1 < he) {
-            wn[0] = q6k_load(op.v, hs0[0] + h + 1, t);
-            wn[1] = q6k_load(op.v, hs0[1] + h + 1, t);
+#pragma unroll
+            for (int i = 0; i < 2; i++) { q6k_advance(pp[i]); wn[i] = q6k_load(pp[i]); }
         }
         uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
         float dL[2], dH[2];
@@ -291,18 +351,18 @@ __device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int hb
         for (int n = 0; n < MT; n++) {
             if (n < m) {
                 uint4 b01, b23;
-                float cL[4] = {0.f, 0.f, 0.f, 0.f}, cH[4] = {0.f, 0.f, 0.f, 0.f};
-                load_b(xs, RL, m, n, b_active, b_part, b01, b23);
-                mma16816(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
+                float cL[4], cH[4];
+                load_b(bl, RL * m + n, b01, b23);
+                mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
                 mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
                 mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
                 mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
-                load_b(xs, RL + 4, m, n, b_active, b_part, b01, b23);
-                mma16816(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
+                load_b(bl, (RL + 4) * m + n, b01, b23);
+                mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
                 mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
                 mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
                 mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
-                float2 sl = xs.ss[(size_t)RL * m + n], sh = xs.ss[(size_t)(RL + 4) * m + n];
+                float2 sl = xs.ss[RL * m + n], sh = xs.ss[(RL + 4) * m + n];
                 const float k32 = 32.0f / 16777216.0f;
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
@@ -342,6 +402,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
     }
     GOp op = single;
     XImg xs{};
+    BLane bl{};
+    if (threadIdx.x < XZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xbase)[threadIdx.x] = 0u;   // published by the first barrier
     for (int tile = tb; tile < te; tile++) {
         if (n_ops > 1) {
             while (opi < n_ops - 1 && tile >= ops[opi].tile0 + ops[opi].ntiles) opi++;
@@ -350,6 +412,7 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
             if (n_ops > 1) op = ops[opi];
             __syncthreads();   // everyone is done with the previous product's activations
             xs = ximg_carve(xbase, op.k, m);
+            bl = blane_make(xs, xbase, lane >> 2, lane & 3);
             if (op.fmt == F_Q4K) prep_x<true>(op.x, op.ldx, op.k, m, xs);
             else prep_x<false>(op.x, op.ldx, op.k, m, xs);
             __syncthreads();
@@ -365,8 +428,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         if (live) {
             int nh = op.k >> 7, per = (nh + kw - 1) >> op.kw_log2;
             int hb = kpart * per, he = min(nh, (kpart + 1) * per);
-            if (op.fmt == F_Q4K) tile_q4k<MT>(op, m, rtile, hb, he, xs, acc);
-            else tile_q6k<MT>(op, m, rtile, hb, he, xs, acc);
+            if (op.fmt == F_Q4K) tile_q4k<MT>(op, m, rtile, hb, he, xs, bl, acc);
+            else tile_q6k<MT>(op, m, rtile, hb, he, xs, bl, acc);
         }
         // the four threads of a quad hold partial sums of the same two rows
 #pragma unroll
@@ -418,32 +481,32 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
 
 size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
     (void)fmt;
-    return RED_FLOATS * sizeof(float) + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
+    return RED_FLOATS * sizeof(float) + XZERO_BYTES + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
-    if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24)) return false;
+    if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
     if (w->fmt != F_Q4K && w->fmt != F_Q6K) return false;
     if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 200 * 1024;
 }
 
 void gemv_mma_plan(GOp* op, bool few_tiles) {
-    FmtInfo I = fmt_info(op->fmt);
-    double row_bytes = (double)op->k * I.block_bytes / I.block_elems;
-    int units = op->k / 128;
-    // aim at ~48 KB of packed weights per CTA tile, at least one 128-weight half per warp
-    int rt = 8;
-    while (rt > 1 && rt * 16 * row_bytes > 48.0 * 1024) rt >>= 1;
-    int row_tiles = (op->n_rows + 15) / 16;
-    if (few_tiles) {
-        while (rt > 1 && (row_tiles + rt - 1) / rt < 2 * 148) rt >>= 1;
-    }
-    while (rt < 8 && (8 / rt) > units) rt <<= 1;
+    // Fewest k-parts (most work per warp, no cross-warp reduction) that still give the launch enough CTA
+    // tiles; a warp never gets less than two 128-weight halves when k allows it.
+    const int units = op->k / 128;
+    const int row_tiles = (op->n_rows + 15) / 16;
+    const int want_tiles = few_tiles ? 4 * 148 : 1;
     int kw_log2 = 0;
-    while ((8 >> kw_log2) > rt) kw_log2++;
+    while (kw_log2 < 3 && (row_tiles * (1 << kw_log2) + 7) / 8 < want_tiles && units / (2 << kw_log2) >= 2) kw_log2++;
+    // very long rows: keep a CTA tile under ~160 KB of packed weights so tiles stay balanceable
+    FmtInfo I = fmt_info(op->fmt);
+    const double row_bytes = (double)op->k * I.block_bytes / I.block_elems;
+    while (kw_log2 < 3 && (8 >> kw_log2) * 16 * row_bytes > 160.0 * 1024 && units / (2 << kw_log2) >= 2) kw_log2++;
+    while (kw_log2 > 0 && (1 << kw_log2) > units) kw_log2--;
     op->kw_log2 = kw_log2;
+    const int rt = 8 >> kw_log2;
     op->ntiles = (row_tiles + rt - 1) / rt;
 }
 

@@ -84,16 +84,6 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
     if (ldy == 0) ldy = w->n_local;
     if (ldx < w->k || ldy < w->n_local) return fail(B200Q_ERR_INVALID, "matmul: ldx=%lld < k=%lld or ldy=%lld < n=%lld", (long long)ldx, (long long)w->k, (long long)ldy, (long long)w->n_local);
     if (m == 0) return B200Q_OK;
-    const float* x32 = static_cast<const float*>(d_x);
-    int64_t ldx32 = ldx;
-    if (x_dtype == B200Q_BF16) {
-        rc = ensure_scratch(ctx, (size_t)m * w->k * sizeof(float), 0);
-        if (rc != B200Q_OK) return rc;
-        rc = launch_convert_bf16_to_f32(ctx, d_x, ldx, static_cast<float*>(ctx->scratch), w->k, m, w->k);
-        if (rc != B200Q_OK) return rc;
-        x32 = static_cast<const float*>(ctx->scratch);
-        ldx32 = w->k;
-    }
     float* y32 = static_cast<float*>(d_y);
     int64_t ldy32 = ldy;
     if (y_dtype == B200Q_BF16) {
@@ -102,8 +92,26 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
         y32 = static_cast<float*>(ctx->scratch2);
         ldy32 = w->n_local;
     }
-    rc = matmul_f32(ctx, w, x32, ldx32, y32, ldy32, m, flags);
-    if (rc != B200Q_OK) return rc;
+    const bool tensor = m > 8 && !(flags & (B200Q_MM_SEQUENTIAL | B200Q_MM_NO_TENSOR)) && gemm_tc_supported(w, m);
+    if (tensor) {
+        // tcgen05 path: activations are copied to f16 (row-scaled) and fetched by TMA
+        rc = launch_gemm_tc(ctx, w, d_x, x_dtype == B200Q_BF16, ldx, y32, ldy32, m);
+        if (rc != B200Q_OK) return rc;
+        ctx->tc_pending = true;
+    } else {
+        const float* x32 = static_cast<const float*>(d_x);
+        int64_t ldx32 = ldx;
+        if (x_dtype == B200Q_BF16) {
+            rc = ensure_scratch(ctx, (size_t)m * w->k * sizeof(float), 0);
+            if (rc != B200Q_OK) return rc;
+            rc = launch_convert_bf16_to_f32(ctx, d_x, ldx, static_cast<float*>(ctx->scratch), w->k, m, w->k);
+            if (rc != B200Q_OK) return rc;
+            x32 = static_cast<const float*>(ctx->scratch);
+            ldx32 = w->k;
+        }
+        rc = matmul_f32(ctx, w, x32, ldx32, y32, ldy32, m, flags);
+        if (rc != B200Q_OK) return rc;
+    }
     if (y_dtype == B200Q_BF16) rc = launch_convert_f32_to_bf16(ctx, y32, ldy32, d_y, ldy, m, w->n_local);
     return rc;
 }
@@ -123,11 +131,10 @@ int b200q_matmul_host(b200q_ctx* ctx, const b200q_weight* w, const float* h_x, f
     if ((rc = ensure_scratch(ctx, xb, 0)) != B200Q_OK) return rc;
     if ((rc = ensure_scratch(ctx, yb, 1)) != B200Q_OK) return rc;
     B200Q_CUDA(cudaMemcpyAsync(ctx->scratch, h_x, xb, cudaMemcpyHostToDevice, ctx->stream), B200Q_ERR_COPY);
-    rc = matmul_f32(ctx, w, static_cast<const float*>(ctx->scratch), w->k, static_cast<float*>(ctx->scratch2), w->n_local, m, flags);
+    rc = b200q_matmul_ex(ctx, w, ctx->scratch, B200Q_F32, w->k, ctx->scratch2, B200Q_F32, w->n_local, m, flags);
     if (rc != B200Q_OK) return rc;
     B200Q_CUDA(cudaMemcpyAsync(h_y, ctx->scratch2, yb, cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
-    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
-    return B200Q_OK;
+    return b200q_synchronize(ctx);
 }
 
 int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, const float* const* d_x,

@@ -1,0 +1,118 @@
+"""Prefill path (m > 8): the tcgen05 tensor-core kernel against the CPU oracle.
+
+Tolerance 2e-3 (max |y - ref| / max |ref|) against the fp32 oracle on the same activation values. Inside the
+kernel weights and activations are rounded once to f16 (activations with a power-of-two scale per row);
+accumulation is fp32 in tensor memory. bf16 activations convert to f16 exactly, so for them the oracle runs
+on the bf16 values widened to fp32.
+"""
+import numpy as np
+import pytest
+import torch
+
+from rocmforge_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+from gpu_util import ALL_FMTS, FMT_IDS, QuantizedWeight, backend, gpu_matmul, rel_err  # noqa: E402
+
+
+def bf16_round(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(torch.bfloat16).float().numpy()
+
+
+def reference(oracle, qt, lay, data, n, k, x, rows=None):
+    w = oracle.dequantize(qt, lay, data, n * k, threads=8).reshape(n, k)
+    if rows is not None:
+        w = np.ascontiguousarray(w[rows])
+    return oracle.matmul_f32(x, w, nk=True, threads=8)
+
+
+def test_smallest_tile_first(oracle):
+    """One CTA, four k-blocks: the first thing to run on a new build."""
+    be = backend()
+    rng = synth.rng_for(3100)
+    n, k, m = 128, 256, 64
+    data = synth.gen_packed(synth.Q8_0, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.Q8_0, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    assert rel_err(y, reference(oracle, synth.Q8_0, synth.GGUF, data, n, k, x)) <= TOL
+    w.free()
+
+
+@pytest.mark.parametrize("qt,lay", ALL_FMTS, ids=FMT_IDS)
+def test_every_format_ragged_tiles(oracle, qt, lay):
+    """n and m are not tile multiples; k = 5 super-blocks."""
+    be = backend()
+    rng = synth.rng_for(3200 + qt * 2 + lay)
+    n, k, m = 300, 1280, 100
+    data = synth.gen_packed(qt, lay, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, lay, n, k)
+    y = gpu_matmul(be, w, x, m)
+    assert rel_err(y, reference(oracle, qt, lay, data, n, k, x)) <= TOL
+    # CUDA-core path on the same input agrees with the fp32 oracle much more tightly
+    y2 = gpu_matmul(be, w, x, m, flags=_lib.MM_NO_TENSOR)
+    wf = oracle.dequantize(qt, lay, data, n * k).reshape(n, k)
+    assert rel_err(y2, oracle.matmul_f32(x, wf, nk=True, threads=8)) <= 1e-4
+    w.free()
+
+
+@pytest.mark.parametrize("m", [9, 16, 17, 255, 256, 257, 512])
+def test_token_counts_around_the_tile_edges(oracle, m):
+    be = backend()
+    rng = synth.rng_for(3300 + m)
+    n, k = 256, 896
+    data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    assert rel_err(y, reference(oracle, synth.Q4_K, synth.GGUF, data, n, k, x)) <= TOL
+    w.free()
+
+
+def test_bf16_activations_and_outputs(oracle):
+    be = backend()
+    rng = synth.rng_for(3400)
+    n, k, m = 384, 1024, 128
+    data = synth.gen_packed(synth.Q6_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    xbf = torch.from_numpy(x).to(torch.bfloat16)
+    w = QuantizedWeight(be, data, synth.Q6_K, synth.GGUF, n, k)
+    xb = be.allocate_buffer(m * k * 2); xb.copy_from_host(xbf.view(torch.int16).numpy())
+    yb = be.allocate_buffer(m * n * 4)
+    w.matmul(xb, yb, m, x_dtype=_lib.BF16)
+    be.synchronize()
+    y = yb.to_numpy(np.float32, m * n).reshape(m, n)
+    ref = reference(oracle, synth.Q6_K, synth.GGUF, data, n, k, bf16_round(x))
+    assert rel_err(y, ref) <= TOL
+    y16 = be.allocate_buffer(m * n * 2)
+    w.matmul(xb, y16, m, x_dtype=_lib.BF16, y_dtype=_lib.BF16)
+    be.synchronize()
+    got = torch.from_numpy(y16.to_numpy(np.int16, m * n)).view(torch.bfloat16).float().numpy().reshape(m, n)
+    assert rel_err(got, ref) <= 8e-3
+    for b in (xb, yb, y16):
+        b.free()
+    w.free()
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (11008, 4096), (4096, 11008)])
+@pytest.mark.parametrize("m", [256, 512])
+def test_config4_llama7b_q4k_prefill(oracle, n, k, m):
+    """Full-size Llama-2-7B-shaped Q4_K projections; 96 sampled weight rows (plus the last) against the oracle."""
+    be = backend()
+    rng = synth.rng_for(synth.CONFIG_SEEDS[4] + n + m)
+    data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    rows = np.unique(np.concatenate([rng.integers(0, n, size=96), [0, n - 1]]))
+    blocks = data.reshape(-1, 144)
+    sel = np.concatenate([blocks[r * k // 256:(r + 1) * k // 256] for r in rows]).reshape(-1)
+    wsel = oracle.dequantize(synth.Q4_K, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    ref = oracle.matmul_f32(x, wsel, nk=True, threads=8)
+    scale = float(np.max(np.abs(y)))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / scale <= TOL
+    assert np.all(np.isfinite(y))
+    w.free()
