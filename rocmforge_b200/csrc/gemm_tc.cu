@@ -8,7 +8,7 @@
 //
 //   y[m, n] = x[m, k] * W[n, k]^T   computed as   D[128 weight rows, BN activation rows] += A * B^T
 //
-//   A (UMMA M side) : 128 weight rows x 64 k, f16, K-major, 128-byte swizzle, written by 4 dequant warps
+//   A (UMMA M side) : 128 weight rows x 64 k, f16, K-major, 128-byte swizzle, written by 8 dequant warps
 //                     (decode8 gives the exact fp32 values; one round-to-nearest to f16, whose 11-bit
 //                     mantissa keeps the result well inside the 2e-3 tolerance; bf16 weights do not)
 //   B (UMMA N side) : BN <= 256 activation rows x 64 k, f16, loaded by TMA (cp.async.bulk.tensor, no
@@ -18,9 +18,10 @@
 //   D               : fp32 in tensor memory, 128 lanes x BN columns; read back with tcgen05.ld by the four
 //                     dequant warps (one lane quarter each) and stored to y, coalesced along n
 //
-// Warp roles (192 threads): warp 0 = TMA producer + TMEM allocator, warp 1 = MMA issuer (one elected
-// thread), warps 2..5 = dequant producers, then epilogue. A 4-stage ring of {A, B} tiles is handed over
-// with mbarriers: full_a (4 warp arrivals), full_b (TMA transaction bytes), empty (tcgen05.commit).
+// Warp roles (384 threads): warp 0 = TMA producer + TMEM allocator, warp 1 = MMA issuer (one elected
+// thread, alone on its scheduler), 8 weight-tile producer warps, 8 epilogue warps. A 4-stage ring of {A, B}
+// tiles is handed over with mbarriers: full_a (8 warp arrivals), full_b (TMA transaction bytes), empty
+// (tcgen05.commit).
 // Every wait is bounded by a clock budget; on expiry the kernel raises a status word, all roles leave
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
 #include <cuda.h>
@@ -35,7 +36,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;   // power of two: stage = kb & 3, phase = (kb >> 2) & 1
+constexpr int NTHREADS = 384;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr long long WAIT_BUDGET = 1ll << 31; // clock cycles (~1 s) before a wait gives up
 
@@ -61,18 +63,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity. Gives up after WAIT_BUDGET cycles or when another role already
-// gave up; then raises the CTA's abort flag and the launch's status word and returns false.
+// Waits for the phase with the given parity. The fast path is a bare try_wait loop; every 4096 failed tries
+// it looks at the clock and at the CTA's abort flag, gives up after WAIT_BUDGET cycles (or when another role
+// already gave up), raises the abort flag and the launch's status word and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = clock64();
-    for (;;) {
+    long long t0 = 0;
+    for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag != 0) return false;
-        if (clock64() - t0 > WAIT_BUDGET) {
-            *abort_flag = 1;
-            atomicCAS(status, 0, code);
-            return false;
+        if ((spin & 4095u) == 0) {
+            if (*abort_flag != 0) return false;
+            long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_BUDGET) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -87,12 +93,24 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// MMA issue: D[tmem] (+)= A[smem desc] * B[smem desc]^T. Descriptors are passed as {lo word computed per
+// stage, constant hi word}; the first MMA of a tile overwrites the accumulator, the others accumulate.
+__device__ __forceinline__ void umma_f16_acc(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi, uint32_t idesc) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        "{\n\t.reg .b64 da, db;\n\t.reg .pred p;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_first(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .b64 da, db;\n\t.reg .pred p;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -124,6 +142,68 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Specialised A-tile producer for GGUF Q4_K: two threads expand the 64 weights of one row of the k-block
+// (one 32-byte chunk: low nibbles = sub-block 2c, high nibbles = sub-block 2c+1) to f16, 16 bytes each.
+//   (w & 0x000F000F) | 0x64006400  is the f16 pair (1024 + q_byte0, 1024 + q_byte2); minus 1024 gives q exactly;
+//   one HFMA2 forms q * (d*sc) - dmin*m with a single rounding. High nibbles stay in bits 4..7 (1024 + 16 q)
+//   and use (d*sc)/16. Weights come out in the order 0,2,1,3 inside each group of four; the f16 copy of the
+//   activations is stored in the same order, so no byte shuffles are needed.
+struct Q4KRaw {
+    uint4 hdr, q;
+    int c;   // chunk of the super-block (0..3)
+};
+
+__device__ __forceinline__ Q4KRaw q4k_load_raw(const uint8_t* __restrict__ base, int64_t chunk_index, int half) {
+    const uint8_t* sb = base + (chunk_index >> 2) * 144;
+    Q4KRaw r;
+    r.c = (int)(chunk_index & 3);
+    r.hdr = __ldg(reinterpret_cast<const uint4*>(sb));
+    r.q = __ldg(reinterpret_cast<const uint4*>(sb + 16 + r.c * 32 + half * 16));
+    return r;
+}
+
+// half: which 16 bytes of the chunk (weights 16*half .. 16*half+15 of both sub-blocks); r: row inside the tile.
+__device__ __forceinline__ void q4k_convert(const Q4KRaw& raw, int half, int r, uint8_t* tile) {
+    const uint4 hdr = raw.hdr;
+    const int c = raw.c;
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    uint32_t scA, scB, mA, mB;
+    {
+        const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, m_lo = hdr.z & 0x3F3F3F3Fu;
+        const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+        const uint32_t m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+        const uint32_t scw = c < 2 ? sc_lo : sc_hi, mw = c < 2 ? m_lo : m_hi;
+        const int sh = (c & 1) * 16;
+        scA = (scw >> sh) & 0xFFu; scB = (scw >> (sh + 8)) & 0xFFu;
+        mA = (mw >> sh) & 0xFFu; mB = (mw >> (sh + 8)) & 0xFFu;
+    }
+    const __half2 dsA = __float2half2_rn(d * (float)scA), dsB = __float2half2_rn(d * (float)scB * 0.0625f);
+    const __half2 ndA = __float2half2_rn(-dmin * (float)mA), ndB = __float2half2_rn(-dmin * (float)mB);
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    const uint32_t MAGIC = 0x64006400u, ML = 0x000F000Fu, MH = 0x00F000F0u;
+    const uint32_t w[4] = {raw.q.x, raw.q.y, raw.q.z, raw.q.w};
+    uint32_t lo[8], hi[8];   // f16x2 weights of sub-block A (k 0..31 of the block) and B (k 32..63)
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t v = w[j], vs = v >> 8;
+        uint32_t t0 = (v & ML) | MAGIC, t1 = (vs & ML) | MAGIC, t2 = (v & MH) | MAGIC, t3 = (vs & MH) | MAGIC;
+        __half2 a0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), dsA, ndA);
+        __half2 a1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), dsA, ndA);
+        __half2 b0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), dsB, ndB);
+        __half2 b1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), dsB, ndB);
+        lo[2 * j] = *reinterpret_cast<uint32_t*>(&a0); lo[2 * j + 1] = *reinterpret_cast<uint32_t*>(&a1);
+        hi[2 * j] = *reinterpret_cast<uint32_t*>(&b0); hi[2 * j + 1] = *reinterpret_cast<uint32_t*>(&b1);
+    }
+    uint8_t* rowp = tile + r * 128;
+#pragma unroll
+    for (int cc = 0; cc < 2; cc++) {   // 16-byte chunks 2*half+cc (sub-block A) and 4+2*half+cc (sub-block B)
+        const int ca = 2 * half + cc;
+        *reinterpret_cast<uint4*>(rowp + ((ca ^ (r & 7)) << 4)) = make_uint4(lo[4 * cc], lo[4 * cc + 1], lo[4 * cc + 2], lo[4 * cc + 3]);
+        *reinterpret_cast<uint4*>(rowp + (((ca + 4) ^ (r & 7)) << 4)) = make_uint4(hi[4 * cc], hi[4 * cc + 1], hi[4 * cc + 2], hi[4 * cc + 3]);
+    }
+}
+
 struct GemmArgs {
     WView v;
     const float* xscale;   // per activation row: the power of two its f16 copy was divided by
@@ -133,8 +213,18 @@ struct GemmArgs {
     int* status;
 };
 
+// Warp roles (384 threads = 12 warps; a warp may only read the TMEM lane quarter warp_id % 4):
+//   warp 0          TMA producer for the activation tiles, TMEM allocator
+//   warp 1          MMA issuer (one thread). Warps 5 and 9 share its scheduler and therefore stay asleep on a
+//                   hardware barrier during the main loop: the issuer's instruction stream is the critical path
+//   warps 2,3,4,6,7,8,10,11   weight-tile producers (two threads per weight row)
+//   epilogue        warps 4,5,6,7 (lane quarters 0,1,2,3) take the even 32-column groups, warps 8,9,10,11 the odd
+__device__ __forceinline__ bool is_producer_warp(int warp) { return warp >= 2 && warp != 5 && warp != 9; }
+// dense index 0..7 of a producer warp
+__device__ __forceinline__ int producer_index(int warp) { return warp - 2 - (warp > 5) - (warp > 9); }
+
 template <int F>
-__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a) {
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int b_stage_bytes = a.bn * BK * 2;
@@ -155,8 +245,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(&full_a[s]), 4);
-            mbar_init(smem_u32(&full_b[s]), 1);
+            mbar_init(smem_u32(&full_a[s]), 9);   // 8 producer warps + the TMA thread's expect_tx arrival
+            mbar_init(smem_u32(&full_b[s]), 1);   // unused (kept so the barrier block keeps its layout)
             mbar_init(smem_u32(&empty[s]), 1);
         }
         mbar_init(smem_u32(accum), 1);
@@ -171,25 +261,26 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (activations)
         if (lane == 0) {
             int issued = 0;
             for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
+                const int s = kb & (STAGES - 1);
+                const uint32_t ph = (kb >> 2) & 1;
                 if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 1)) break;
-                mbar_arrive_expect_tx(smem_u32(&full_b[s]), (uint32_t)b_stage_bytes);
-                tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, smem_u32(&full_b[s]));
+                mbar_arrive_expect_tx(smem_u32(&full_a[s]), (uint32_t)b_stage_bytes);
+                tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, smem_u32(&full_a[s]));
                 issued = kb + 1;
             }
             // do not leave copies in flight behind: the last STAGES tiles issued must have landed
             for (int kb = max(0, issued - STAGES); kb < issued; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
+                const int s = kb & (STAGES - 1);
+                const uint32_t ph = (kb >> 2) & 1;
                 long long t0 = clock64();
-                while (!mbar_try_wait(smem_u32(&full_b[s]), ph)) {
+                while (!mbar_try_wait(smem_u32(&full_a[s]), ph)) {
                     if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 5); break; }
                 }
             }
@@ -200,60 +291,84 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             // D fp32, A and B f16. The two operand formats of kind::f16 must be equal: f16 weights with bf16
             // activations raise an illegal-instruction fault on sm_100a.
             const uint32_t idesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                ok = mbar_wait(smem_u32(&full_a[s]), ph, abort_flag, a.status, 2) &&
-                     mbar_wait(smem_u32(&full_b[s]), ph, abort_flag, a.status, 3);
-                if (!ok) break;
+            const uint64_t adesc0 = umma_desc_sw128(smem_u32(sA));
+            const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sB));
+            const uint32_t ahi = (uint32_t)(adesc0 >> 32), bhi = (uint32_t)(bdesc0 >> 32);
+            const uint32_t alo0 = (uint32_t)adesc0, blo0 = (uint32_t)bdesc0;
+            const uint32_t a_step = (uint32_t)(A_STAGE_BYTES >> 4), b_step = (uint32_t)(b_stage_bytes >> 4);
+            const uint32_t fu0 = smem_u32(full_a), em0 = smem_u32(empty);
+            for (int kb = 0; kb < nkb; kb++) {
+                const uint32_t s = (uint32_t)kb & (STAGES - 1);
+                const uint32_t ph = ((uint32_t)kb >> 2) & 1;
+                if (!mbar_wait(fu0 + s * 8, ph, abort_flag, a.status, 2)) break;
                 tc_fence_after();
-                const uint64_t adesc = umma_desc_sw128(smem_u32(sA + s * A_STAGE_BYTES));
-                const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + s * b_stage_bytes));
-#pragma unroll
-                for (int kk = 0; kk < BK / 16; kk++) {
-                    // 16 bf16 = 32 bytes further along k inside the swizzle atom: +2 in the encoded address
-                    umma_bf16(tmem_base, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc, (kb | kk) != 0);
-                }
-                umma_commit(smem_u32(&empty[s]));
+                const uint32_t al = alo0 + s * a_step, bl = blo0 + s * b_step;
+                // 16 f16 = 32 bytes further along k inside the swizzle atom: +2 in the encoded address
+                if (kb == 0) umma_f16_first(tmem_base, al, ahi, bl, bhi, idesc);
+                else umma_f16_acc(tmem_base, al, ahi, bl, bhi, idesc);
+                umma_f16_acc(tmem_base, al + 2, ahi, bl + 2, bhi, idesc);
+                umma_f16_acc(tmem_base, al + 4, ahi, bl + 4, bhi, idesc);
+                umma_f16_acc(tmem_base, al + 6, ahi, bl + 6, bhi, idesc);
+                umma_commit(em0 + s * 8);
             }
             umma_commit(smem_u32(accum));   // arrives once every MMA issued so far has completed
         }
-    } else {
-        // ---------------------------------------------------------------- dequant producers, then epilogue
-        const int dt = tid - 64;   // 0..127
-        bool ok = true;
+    } else if (is_producer_warp(warp)) {
+        // ---------------------------------------------------------------- weight-tile producers
+        const int dt = producer_index(warp) * 32 + lane;   // 0..255
+        constexpr bool FAST = F == fmt_of(Q4_K, GGUF);
+        Q4KRaw pre{};
+        const int64_t frow = min((int64_t)row0 + (dt >> 1), (int64_t)a.n_rows - 1);
+        const int64_t fchunk0 = (frow * a.k) >> 6;
+        if (FAST && nkb > 0) pre = q4k_load_raw(a.v.p[0], fchunk0, dt & 1);
         for (int kb = 0; kb < nkb && ok; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+            const int s = kb & (STAGES - 1);
+            const uint32_t ph = (kb >> 2) & 1;
+            Q4KRaw cur = pre;
+            if (FAST && kb + 1 < nkb) pre = q4k_load_raw(a.v.p[0], fchunk0 + kb + 1, dt & 1);   // next block's bytes fly while this one converts
+            // one lane polls, the warp follows: keeps the shared-memory pipe free for the MMA issuer
+            if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             uint8_t* tile = sA + s * A_STAGE_BYTES;
+            if constexpr (FAST) {
+                q4k_convert(cur, dt & 1, dt >> 1, tile);
+            } else {
 #pragma unroll 2
-            for (int it = 0; it < (BM * BK / 8) / 128; it++) {
-                const int idx = it * 128 + dt;
-                const int r = idx >> 3, c = idx & 7;
-                const int64_t row = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
-                const int64_t piece = (row * a.k + (int64_t)kb * BK + c * 8) >> 3;
-                float w[8];
-                decode8<F>(a.v, piece >> 2, (int)(piece & 3), w);
-                __half2 p0 = __floats2half2_rn(w[0], w[1]), p1 = __floats2half2_rn(w[2], w[3]);
-                __half2 p2 = __floats2half2_rn(w[4], w[5]), p3 = __floats2half2_rn(w[6], w[7]);
-                uint4 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+                for (int it = 0; it < (BM * BK / 8) / 256; it++) {
+                    const int idx = it * 256 + dt;
+                    const int r = idx >> 3, c = idx & 7;
+                    const int64_t row = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
+                    const int64_t piece = (row * a.k + (int64_t)kb * BK + c * 8) >> 3;
+                    float w[8];
+                    decode8<F>(a.v, piece >> 2, (int)(piece & 3), w);
+                    __half2 p0 = __floats2half2_rn(w[0], w[1]), p1 = __floats2half2_rn(w[2], w[3]);
+                    __half2 p2 = __floats2half2_rn(w[4], w[5]), p3 = __floats2half2_rn(w[6], w[7]);
+                    uint4 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                    *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&full_a[s]));
         }
-        if (ok) ok = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, 6);
-        if (ok) {
+    }
+    // ---------------------------------------------------------------- epilogue: warps 4..11
+    if (warp >= 4) {
+        // warp 4 waits for the accumulator, everyone else sleeps on hardware barrier 1 until it is released
+        if (warp == 4) {
+            if (lane == 0 && ok) ok = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, 6);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) *abort_flag = 1;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*abort_flag == 0) {
             tc_fence_after();
             const int q = warp & 3;                       // the lane quarter this warp may read
             const int row = row0 + q * 32 + lane;
-            for (int c0 = 0; c0 < a.bn; c0 += 32) {
+            for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 if (row < a.n_rows) {
@@ -276,9 +391,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 }
 
 // Activation rows -> f16 with a power-of-two scale per row (max |x| of the row lands in [1, 2)).
+// perm: inside every aligned group of four k positions the order becomes 0,2,1,3 -- the order in which the
+// nibble masks of the specialised Q4_K tile producer emit weights (bytes 0 and 2, then bytes 1 and 3).
 template <typename T>
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
-                                                       float* __restrict__ scale, int k) {
+                                                       float* __restrict__ scale, int k, int perm) {
     const int row = blockIdx.x;
     const T* xr = x + (int64_t)row * ldx;
     float mx = 0.0f;
@@ -292,7 +409,10 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     int e = (int)((__float_as_uint(mx) >> 23) & 255u);
     e = (mx == 0.0f || !(mx <= 3.0e38f)) ? 127 : min(max(e, 1), 253);
     const float sdown = __uint_as_float((uint32_t)(254 - e) << 23);
-    for (int i = threadIdx.x; i < k; i += blockDim.x) out[(int64_t)row * k + i] = __float2half_rn((float)xr[i] * sdown);
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        int src = perm ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;
+        out[(int64_t)row * k + i] = __float2half_rn((float)xr[src] * sdown);
+    }
     if (threadIdx.x == 0) scale[row] = __uint_as_float((uint32_t)e << 23);
 }
 
@@ -319,7 +439,7 @@ int launch_fmt(b200q_ctx* ctx, const CUtensorMap& map, const GemmArgs& a, dim3 g
         B200Q_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
         configured[ctx->device & 63] = true;
     }
-    gemm_tc_kernel<F><<<grid, 192, smem, ctx->stream>>>(map, a);
+    gemm_tc_kernel<F><<<grid, NTHREADS, smem, ctx->stream>>>(map, a);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
@@ -339,8 +459,9 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     if (rc != B200Q_OK) return rc;
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
-    if (x_is_bf16) x_to_f16_kernel<__nv_bfloat16><<<m, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, (int)w->k);
-    else x_to_f16_kernel<float><<<m, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_x16, d_scale, (int)w->k);
+    const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
+    if (x_is_bf16) x_to_f16_kernel<__nv_bfloat16><<<m, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, (int)w->k, perm);
+    else x_to_f16_kernel<float><<<m, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_x16, d_scale, (int)w->k, perm);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     const void* d_x_bf16 = d_x16;
     ldx = w->k;
