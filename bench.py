@@ -1,18 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-weight matmul path on B200.
 
-Headline (BASELINE.json metric): Q4_K-model decode GEMV packed-weight GB/s at M=1. One "step" is one
-Qwen2-0.5B-shaped Q4_K_M decode step, matmul only: 24 layers x {Q,K,V,O,gate,up in Q4_K, down in Q6_K}
-plus the Q6_K lm_head = 169 fused dequant+matmul products streaming 339,916,416 bytes of GGUF-layout
-packed weights (more than the 126 MB L2, so every step re-reads HBM). Inputs are seeded synthetic tensors
-(rocmforge_b200.synth); no model file is used.
+Headline (BASELINE.json metric, first half): Q4_K-model decode GEMV packed-weight GB/s at M=1. One "step" is one
+Qwen2-0.5B-shaped Q4_K_M decode step, matmul only: 24 layers x {Q,K,V,O,gate,up in Q4_K, down in Q6_K} plus the
+Q6_K lm_head = 169 fused dequant+matmul products streaming 339,916,416 bytes of GGUF-layout packed weights per
+step (more than the 126 MB L2, so every step re-reads HBM), issued as ONE grouped launch through the batch
+front end. The second half of the metric (prefill GEMM TFLOP/s at M=512, Llama-2-7B-shaped Q4_K) is reported in
+the "gemm" object of the same line. Inputs are seeded synthetic tensors (rocmforge_b200.synth); no model file or
+public dataset is used.
 
-  python bench.py [--gpus N --steps K --warmup W]          this library (one process per GPU under torchrun)
-  python bench.py --impl reference [...]                   the reference's CPU algorithm (oracle port) on host cores
+  python bench.py [--gpus N --steps K --warmup W]      this library (one process per GPU under torchrun)
+  python bench.py --impl reference [...]               the reference's CPU algorithm (oracle port) on the host cores
+  python bench.py --workload matrix --qtype Q4_K --n 65536 --k 4096 [--m M]   one tensor (profiling aid)
 
-Prints ONE JSON line (rank 0). N > 1: every rank runs the same step on its own replica of the weights
-(independent decode streams; the path has no exchange step at M=1), "scaling": "weak"; the column-split +
-all-gather of the large projections is measured separately in the "shard" object.
+Prints ONE JSON line (rank 0). N > 1: every rank runs the step on its own replica of the weights (independent
+decode streams; a decode step has no exchange between GPUs), "scaling": "weak". The column split of a large
+projection across the ranks followed by an NCCL all-gather of the output slices is measured in the "shard"
+object of the same line.
 """
 import argparse
 import ctypes
@@ -30,6 +34,7 @@ sys.path.insert(0, ROOT)
 from rocmforge_b200 import synth  # noqa: E402
 
 STEP_BYTES = 339_916_416
+METRIC = "Q4_K-model decode GEMV packed-weight GB/s at M=%d"
 
 
 def load_peaks():
@@ -94,16 +99,13 @@ def build_step(m, seed=synth.CONFIG_SEEDS[3]):
     return ops, weights, acts
 
 
-def run_reference(args, rank, world):
-    """The reference's CPU path (oracle port: dequantise to fp32, then cpu_matmul_f32) on all host threads."""
-    if rank != 0:
-        return
+def cpu_step_sample(m, threads):
+    """Layer 0 of the step (7 products) on the CPU oracle: dequantise to fp32, then cpu_matmul_f32."""
     from oracle import cpu_oracle as orc
-    threads = orc.max_threads()
-    ops = synth.qwen2_0p5b_step()[:7]          # bounded sample: layer 0 (7 products, 9.5 MB packed)
+    ops = synth.qwen2_0p5b_step()[:7]
     rng = synth.rng_for(synth.CONFIG_SEEDS[3])
     ws = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for _, qt, n, k in ops]
-    xs = [synth.gen_activations(args.m, k, rng) for _, _, _, k in ops]
+    xs = [synth.gen_activations(m, k, rng) for _, _, _, k in ops]
     nbytes = sum(w.size for w in ws)
 
     def step():
@@ -111,6 +113,16 @@ def run_reference(args, rank, world):
             wf = orc.dequantize(qt, synth.GGUF, w, n * k, threads=threads).reshape(n, k)
             orc.matmul_f32(x, wf, nk=True, threads=threads)
 
+    return step, nbytes
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU path (oracle port of its dequant + cpu_matmul_f32 composition) on all host threads."""
+    if rank != 0:
+        return
+    from oracle import cpu_oracle as orc
+    threads = orc.max_threads()
+    step, nbytes = cpu_step_sample(args.m, threads)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
@@ -118,16 +130,34 @@ def run_reference(args, rank, world):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     gbs = nbytes / dt / 1e9
-    sample = f"layer 0 of the step (7 products, {nbytes} packed bytes) per step"
+    sample = f"layer 0 of the step (7 products, {nbytes} packed bytes) per step, all {threads} host threads"
     print(json.dumps({
-        "impl": "reference", "metric": "Q4_K-model decode GEMV packed-weight GB/s at M=%d" % args.m, "value": gbs,
-        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "impl": "reference", "metric": METRIC % args.m, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "m": args.m, "layout": "GGUF",
-                   "l2": "inputs larger than L2"},
+                   "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
+
+
+def time_matmul(be, w, m, steps, warmup, x_dtype=0):
+    """Device time per launch of one fused dequant+matmul (CUDA events on the library's stream)."""
+    rng = synth.rng_for(4243)
+    x = synth.gen_activations(m, w.k, rng)
+    xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
+    yb = be.allocate_buffer(m * w.n_local * 4)
+    for _ in range(max(warmup, 1)):
+        w.matmul(xb, yb, m)
+    be.synchronize()
+    be.timer_start()
+    for _ in range(steps):
+        w.matmul(xb, yb, m)
+    ms = be.timer_stop_ms() / steps
+    be.synchronize()
+    xb.free(); yb.free()
+    return ms
 
 
 def run_matrix(args, be, peaks):
@@ -136,21 +166,99 @@ def run_matrix(args, be, peaks):
     qt = synth.QNAMES.index(args.qtype)
     rng = synth.rng_for(4242)
     data = synth.gen_packed(qt, synth.GGUF, args.n * args.k, rng)
-    x = synth.gen_activations(args.m, args.k, rng)
     w = QuantizedWeight(be, data, qt, synth.GGUF, args.n, args.k)
-    xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
-    yb = be.allocate_buffer(args.m * args.n * 4)
-    for _ in range(max(args.warmup, 1)):
-        w.matmul(xb, yb, args.m)
-    be.synchronize()
-    be.timer_start()
-    for _ in range(args.steps):
-        w.matmul(xb, yb, args.m)
-    ms = be.timer_stop_ms() / args.steps
+    ms = time_matmul(be, w, args.m, args.steps, args.warmup)
     gbs = w.packed_bytes / (ms * 1e-3) / 1e9
     print(json.dumps({"workload": "matrix", "qtype": args.qtype, "n": args.n, "k": args.k, "m": args.m,
                       "packed_bytes": w.packed_bytes, "ms_per_launch": ms, "GB/s": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
                       "tflops": 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12}))
+
+
+def gemm_leg(be, peaks, steps):
+    """Second half of the metric: Llama-2-7B-shaped Q4_K prefill GEMM at M=512 (device-resident operands)."""
+    from rocmforge_b200.backend import QuantizedWeight
+    rows = []
+    rng = synth.rng_for(synth.CONFIG_SEEDS[4])
+    for n, k in synth.LLAMA7B_SHAPES:
+        data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+        w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+        for m in (512, 2048):
+            ms = time_matmul(be, w, m, steps, 3)
+            rows.append({"n": n, "k": k, "m": m, "ms": ms, "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12})
+        w.free()
+    head = rows[0]
+    return {"metric": "Q4_K prefill GEMM TFLOP/s at M=512", "workload": "llama-2-7b ffn_up Q4_K [11008,4096], M=512",
+            "value": head["tflops"], "unit": "TFLOP/s", "peak": peaks["bf16_tflops"], "frac": head["tflops"] / peaks["bf16_tflops"],
+            "peak_source": peaks["source"], "operands": "f16 x f16 -> fp32 (tcgen05, TMEM accumulators)", "shapes": rows}
+
+
+def shard_leg(be, rank, world, steps):
+    """Column split of the Llama-70B-shaped FFN projection [28672, 8192] over the ranks + NCCL all-gather."""
+    import torch
+    import torch.distributed as dist
+    from rocmforge_b200.backend import QuantizedWeight
+    n, k = synth.LLAMA70B_FFN_SHAPES[0]
+    out = {"workload": "llama-70b ffn [28672,8192], output features split over the ranks, all-gather of the slices",
+           "cases": []}
+    for qname in ("Q4_K", "MXFP4"):
+        qt = synth.QNAMES.index(qname)
+        rng = synth.rng_for(synth.CONFIG_SEEDS[5] + qt)
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+        w = QuantizedWeight(be, data, qt, synth.GGUF, n, k, shard_rank=rank, shard_count=world)
+        full = QuantizedWeight(be, data, qt, synth.GGUF, n, k) if rank == 0 else None
+        for m in (1, 512):
+            x = synth.gen_activations(m, k, synth.rng_for(77 + m))
+            xt = torch.from_numpy(x).cuda()
+            y_slice = torch.empty((m, n // world), dtype=torch.float32, device="cuda")
+            y_all = torch.empty((world, m, n // world), dtype=torch.float32, device="cuda")
+            cur = torch.cuda.current_stream()
+
+            def kernel():
+                w.matmul(xt.data_ptr(), y_slice.data_ptr(), m)
+
+            def timed(fn, reps):
+                torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(cur)
+                for _ in range(reps):
+                    fn()
+                e1.record(cur)
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t.item())
+
+            def with_gather():
+                kernel()
+                dist.all_gather_into_tensor(y_all.view(world * m, -1), y_slice)
+
+            for _ in range(3):
+                with_gather()
+            t_kernel = timed(kernel, steps)
+            t_total = timed(with_gather, steps)
+            case = {"qtype": qname, "m": m, "ranks": world, "ms_kernel": t_kernel, "ms_kernel_plus_allgather": t_total,
+                    "gathered_bytes_per_rank": int(m * n * 4 * (world - 1) / world)}
+            if rank == 0:
+                yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
+                for _ in range(3):
+                    full.matmul(xt.data_ptr(), yb.data_ptr(), m)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(cur)
+                for _ in range(steps):
+                    full.matmul(xt.data_ptr(), yb.data_ptr(), m)
+                e1.record(cur)
+                torch.cuda.synchronize()
+                case["ms_one_gpu_unsharded"] = e0.elapsed_time(e1) / steps
+                # the gathered result equals the unsharded one (same kernel, same per-row arithmetic)
+                got = y_all.permute(1, 0, 2).reshape(m, n)
+                case["max_abs_diff_vs_unsharded"] = float((got - yb).abs().max().item())
+            dist.barrier()
+            out["cases"].append(case)
+        w.free()
+        if full is not None:
+            full.free()
+    return out
 
 
 def main():
@@ -177,15 +285,15 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from rocmforge_b200 import _lib
     from rocmforge_b200.backend import B200Backend, QuantizedWeight
+    from rocmforge_b200.batch import DeviceBatch
 
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = load_peaks()
-    be = B200Backend(local_rank)
-    lib = be.lib
+    # the library works on torch's current stream so that torch.cuda events and NCCL see its kernels
+    be = B200Backend(local_rank, stream=torch.cuda.current_stream().cuda_stream)
     m = args.m
     if args.workload == "matrix":
         run_matrix(args, be, peaks)
@@ -193,17 +301,8 @@ def main():
     ops, weights, acts = build_step(m)
     W = [QuantizedWeight(be, w, qt, synth.GGUF, n, k) for (_, qt, n, k), w in zip(ops, weights)]
     assert sum(w.packed_bytes for w in W) == STEP_BYTES
-    X, Y = [], []
-    for (_, _, n, k), a in zip(ops, acts):
-        xb = be.allocate_buffer(a.nbytes); xb.copy_from_host(a); X.append(xb)
-        Y.append(be.allocate_buffer(m * n * 4))
-    cnt = len(W)
-    arr_w = (ctypes.c_void_p * cnt)(*[w.handle.value for w in W])
-    arr_x = (ctypes.c_void_p * cnt)(*[x.ptr for x in X])
-    arr_y = (ctypes.c_void_p * cnt)(*[y.ptr for y in Y])
-    batch = ctypes.c_void_p()
-    _lib.check(lib.b200q_batch_create(be.ctx, cnt, arr_w, arr_x, arr_y, m, ctypes.byref(batch)))
-    launches_per_step = int(lib.b200q_batch_launches(batch)) if hasattr(lib, "b200q_batch_launches") else cnt
+    batch = DeviceBatch(be, W, m)
+    batch.set_inputs(acts)
 
     def barrier():
         be.synchronize()
@@ -213,19 +312,19 @@ def main():
             torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        _lib.check(lib.b200q_batch_run(be.ctx, batch, None))
+        batch.run()
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
     be.timer_start()
     for _ in range(args.steps):
-        _lib.check(lib.b200q_batch_run(be.ctx, batch, None))
+        batch.run()
     ms = be.timer_stop_ms()
     barrier()
-    # keep the GPU busy long enough for a few clock samples
-    t_end = time.time() + 1.0
+    t_end = time.time() + 1.0          # keep the GPU busy long enough for a few clock samples
     while time.time() < t_end:
-        _lib.check(lib.b200q_batch_run(be.ctx, batch, None))
+        for _ in range(50):
+            batch.run()
         be.synchronize()
     clocks = sampler.stop()
     if world > 1:
@@ -233,69 +332,73 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_step = ms / args.steps
-    value = world * STEP_BYTES / (ms_step * 1e-3) / 1e9
     per_gpu = STEP_BYTES / (ms_step * 1e-3) / 1e9
+    value = world * per_gpu
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tp):
+        tr = json.load(open(tp))
+        traffic = int(tr["dram_bytes_per_algorithmic_byte"] * STEP_BYTES)
 
     out = {
-        "metric": "Q4_K-model decode GEMV packed-weight GB/s at M=%d" % m, "value": value, "unit": "GB/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "products": cnt, "m": m, "layout": "GGUF",
+        "metric": METRIC % m, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "products": len(W), "m": m, "layout": "GGUF",
                    "packed_bytes_per_step": STEP_BYTES, "parallelism": "replicas" if world > 1 else "single",
                    "l2": "inputs larger than L2 (340 MB streamed per step)"},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": per_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "decode step (all launches of one step)", "launches_per_step": launches_per_step},
-        "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+                     "frac": per_gpu / peaks["hbm_gbs"], "traffic": traffic, "peak_source": peaks["source"],
+                     "kernel": "gemv_mma_kernel<1> (one grouped launch = one step)", "launches_per_step": batch.launches},
+        "clocks": clocks, "gpu_launches": batch.launches * args.steps,
     }
 
     if not args.skip_extras:
-        # ---- end to end: host activations in, host results out, through the C ABI, every step -----------------
-        hx = [torch.from_numpy(a).pin_memory() for a in acts]
-        hy = [torch.empty((m, n), dtype=torch.float32).pin_memory() for (_, _, n, _) in ops]
-        h2d = sum(a.nbytes for a in acts)
-        d2h = sum(m * n * 4 for (_, _, n, _) in ops)
-
-        def e2e_step():
-            for w, x, y in zip(W, hx, hy):
-                _lib.check(lib.b200q_matmul_host(be.ctx, w.handle, x.data_ptr(), y.data_ptr(), m, 0))
-
+        # ---- end to end through the C ABI: pinned host activations in, host results out, every step ------------
+        hx = torch.from_numpy(np.concatenate([a.reshape(-1) for a in acts])).pin_memory()
+        hy = torch.empty(sum(batch.ysizes), dtype=torch.float32).pin_memory()
         for _ in range(3):
-            e2e_step()
+            batch.run_host(hx.data_ptr(), hy.data_ptr())
         barrier()
-        e2e_steps = max(3, min(args.steps, 20))
+        e2e_steps = max(3, args.steps)
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            e2e_step()
-        be.synchronize()
+            batch.run_host(hx.data_ptr(), hy.data_ptr())
         dt = (time.perf_counter() - t0) / e2e_steps
         if world > 1:
             t = torch.tensor([dt], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
-        out["e2e"] = {"value": world * STEP_BYTES / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                      "d2h_bytes_per_step": d2h, "ms_per_step": dt * 1e3,
-                      "api": "b200q_matmul_host per product (pinned host activations in, host outputs out; weights resident)"}
-        # ---- CPU baseline (oracle port of the reference path) on rank 0 at N = 1 ---------------------------------
-        if rank == 0 and world == 1:
+        out["e2e"] = {"value": world * STEP_BYTES / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(hx.numel() * 4),
+                      "d2h_bytes_per_step": int(hy.numel() * 4), "ms_per_step": dt * 1e3,
+                      "api": "b200q_batch_run_host: pinned host activations in, host outputs out, weights resident (uploaded once)"}
+        if world == 1:
+            # ---- prefill GEMM (second half of the metric) and a single large Q4_K GEMV --------------------------
+            out["gemm"] = gemm_leg(be, peaks, 10)
+            rng = synth.rng_for(4242)
+            big = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, 65536 * 4096, rng), synth.Q4_K, synth.GGUF, 65536, 4096)
+            msb = time_matmul(be, big, 1, 20, 3)
+            out["gemv_single"] = {"workload": "Q4_K [65536,4096], M=1, one launch", "GB/s": big.packed_bytes / (msb * 1e-3) / 1e9,
+                                  "frac_of_hbm": big.packed_bytes / (msb * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+            big.free()
+            # ---- CPU baseline (oracle port of the reference path) on the host cores ---------------------------
             from oracle import cpu_oracle as orc
             threads = orc.max_threads()
-            sub = list(range(7))
-            nb = sum(weights[i].size for i in sub)
+            step, nb = cpu_step_sample(m, threads)
+            step()
             t0 = time.perf_counter()
             reps = 0
-            while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 200):
-                for i in sub:
-                    _, qt, n, k = ops[i]
-                    wf = orc.dequantize(qt, synth.GGUF, weights[i], n * k, threads=threads).reshape(n, k)
-                    orc.matmul_f32(acts[i], wf, nk=True, threads=threads)
+            while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 500):
+                step()
                 reps += 1
-            dt = (time.perf_counter() - t0) / reps
-            out["cpu_baseline"] = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            dtc = (time.perf_counter() - t0) / reps
+            out["cpu_baseline"] = {"value": nb / dtc / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                    "sample": f"layer 0 of the step (7 products, {nb} packed bytes), {reps} repetitions"}
+        else:
+            out["shard"] = shard_leg(be, rank, world, 10)
     if rank == 0:
         print(json.dumps(out))
-    _lib.check(lib.b200q_batch_free(batch))
+    batch.free()
     if world > 1:
         dist.destroy_process_group()
 

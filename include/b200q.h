@@ -146,6 +146,12 @@ typedef struct b200q_batch b200q_batch;
 int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, const float* const* d_x,
                        float* const* d_y, int m, b200q_batch** out);
 int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out);
+/* Host activations in, host results out for the whole batch: h_x_all is the [m, k_i] inputs of the products
+ * back to back in batch order, h_y_all receives the [m, n_i] outputs the same way. Copies ride the context's
+ * stream (one copy each way when the batch's device buffers are contiguous) and the call returns after the
+ * results have landed. The reference's process_batch takes a device input and returns device buffers
+ * (batch_quantized.rs:147-161); this is the same call for a caller whose tensors live on the host. */
+int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_all, float* h_y_all);
 int b200q_batch_free(b200q_batch* batch);
 /* Bytes of packed weights one run of the batch streams (BatchQuantizedMatmul::calculate_throughput, :277-289). */
 size_t b200q_batch_weight_bytes(const b200q_batch* batch);

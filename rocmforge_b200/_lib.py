@@ -58,6 +58,7 @@ SIGNATURES = {
     "b200q_matmul_host": (_i, [_vp, _vp, _vp, _vp, _i, _u]),
     "b200q_batch_create": (_i, [_vp, _i, _pvp, _pvp, _pvp, _i, _pvp]),
     "b200q_batch_run": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float)]),
+    "b200q_batch_run_host": (_i, [_vp, _vp, _vp, _vp]),
     "b200q_batch_free": (_i, [_vp]),
     "b200q_batch_weight_bytes": (_sz, [_vp]),
     "b200q_batch_launches": (_i, [_vp]),

@@ -235,6 +235,47 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     return B200Q_OK;
 }
 
+int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_all, float* h_y_all) {
+    if (!ctx || !batch) return fail(B200Q_ERR_INVALID, "batch_run_host: null argument");
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    const size_t cnt = batch->w.size();
+    if (cnt == 0) return B200Q_OK;
+    if (!h_x_all || !h_y_all) return fail(B200Q_ERR_INVALID, "batch_run_host: null host buffer");
+    // one copy each way when the device buffers of the batch are laid out back to back, else one per product
+    bool xc = true, yc = true;
+    size_t xtot = 0, ytot = 0;
+    for (size_t i = 0; i < cnt; i++) {
+        size_t xb = (size_t)batch->m * batch->w[i]->k, yb = (size_t)batch->m * batch->w[i]->n_local;
+        if (batch->x[i] != batch->x[0] + xtot) xc = false;
+        if (batch->y[i] != batch->y[0] + ytot) yc = false;
+        xtot += xb; ytot += yb;
+    }
+    if (xc) {
+        B200Q_CUDA(cudaMemcpyAsync(const_cast<float*>(batch->x[0]), h_x_all, xtot * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), B200Q_ERR_COPY);
+    } else {
+        size_t off = 0;
+        for (size_t i = 0; i < cnt; i++) {
+            size_t xb = (size_t)batch->m * batch->w[i]->k;
+            B200Q_CUDA(cudaMemcpyAsync(const_cast<float*>(batch->x[i]), h_x_all + off, xb * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), B200Q_ERR_COPY);
+            off += xb;
+        }
+    }
+    int rc = b200q_batch_run(ctx, batch, nullptr);
+    if (rc != B200Q_OK) return rc;
+    if (yc) {
+        B200Q_CUDA(cudaMemcpyAsync(h_y_all, batch->y[0], ytot * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
+    } else {
+        size_t off = 0;
+        for (size_t i = 0; i < cnt; i++) {
+            size_t yb = (size_t)batch->m * batch->w[i]->n_local;
+            B200Q_CUDA(cudaMemcpyAsync(h_y_all + off, batch->y[i], yb * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
+            off += yb;
+        }
+    }
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+    return B200Q_OK;
+}
+
 int b200q_batch_free(b200q_batch* batch) {
     if (!batch) return B200Q_OK;
     if (batch->d_ops || batch->d_ranges) {
