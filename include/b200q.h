@@ -135,6 +135,17 @@ int b200q_matmul(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_d
                  int m, unsigned flags);
 int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, int64_t ldx, void* d_y,
                     int y_dtype, int64_t ldy, int m, unsigned flags);
+/* No counterpart in the reference: y[m, n_local] = x[m, k] * W^T (fp32 in, fp32 out, dense, tensor-core
+ * kernel) for callers that cannot allocate device memory when they need the product -- a server whose own
+ * pool already holds the rest of HBM, or a loop that cannot take cudaMalloc's device-wide synchronisation.
+ * The call performs no cudaMalloc / cudaFree: its scratch (the f16 copy of the activations) is a fixed
+ * 16 MiB + 64 KiB array inside the library image, held by every GPU that loads the library until exit.
+ * Limits: m * k <= 8,388,608, m <= 16,384, NK tensor with k a multiple of 64; anything larger is refused
+ * with B200Q_ERR_INVALID before any launch. The first call on a device looks up the array's device address;
+ * make that first call before any stream capture begins. All calls share the one array, which keeps the
+ * previous call's contents (every element a call reads is rewritten by that call first): two such calls
+ * that overlap on the same GPU (different streams or contexts) race. */
+int b200q_matmul_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m);
 /* Host activations in, host result out; copies ride the context's stream (pinned or pageable memory). */
 int b200q_matmul_host(b200q_ctx* ctx, const b200q_weight* w, const float* h_x, float* h_y, int m, unsigned flags);
 

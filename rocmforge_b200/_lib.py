@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200q_dequantize_bytes": (_i, [_vp, _vp, _sz, _i, _i, _vp, _i64]),
     "b200q_matmul": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _u]),
     "b200q_matmul_ex": (_i, [_vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _u]),
+    "b200q_matmul_noalloc": (_i, [_vp, _vp, _vp, _vp, _i]),
     "b200q_matmul_host": (_i, [_vp, _vp, _vp, _vp, _i, _u]),
     "b200q_batch_create": (_i, [_vp, _i, _pvp, _pvp, _pvp, _i, _pvp]),
     "b200q_batch_run": (_i, [_vp, _vp, ctypes.POINTER(ctypes.c_float)]),

@@ -494,6 +494,70 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     return fail(B200Q_ERR_INVALID, "gemm: unknown format %d", w->fmt);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Prefill product for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need a product: a serving process
+// whose own pool has already claimed the rest of HBM (the allocation would simply fail), or a latency-
+// critical loop that cannot afford cudaMalloc's implicit device-wide synchronisation. The ordinary entry
+// points grow a per-context scratch buffer on demand (the f16 copy of the activations and their row
+// scales); this variant keeps that scratch in a fixed array that is part of the library image instead.
+// Every GPU that loads the library carries the array (16 MiB + 64 KiB) until the process exits.
+constexpr size_t NOALLOC_X16_BYTES = 16u << 20;     // f16 copy of the activations: m * k <= 8,388,608
+constexpr size_t NOALLOC_SCALE_BYTES = 64u << 10;   // one fp32 scale per activation row: m <= 16,384
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_X16_BYTES + NOALLOC_SCALE_BYTES];
+
+// In host code the array's name is only a stand-in; the device address has to be asked for, once per
+// device, with that device current.
+static void* g_noalloc_dev_ptr[64] = {};
+
+int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m) {
+    if (!gemm_tc_supported(w, m)) return fail(B200Q_ERR_UNSUPPORTED, "matmul_noalloc: needs an NK tensor with k %% 64 == 0");
+    if (ctx->device < 0 || ctx->device >= 64) return fail(B200Q_ERR_INVALID, "matmul_noalloc: device index %d out of range", ctx->device);
+    if ((size_t)m * (size_t)w->k * 2 > NOALLOC_X16_BYTES || (size_t)m * sizeof(float) > NOALLOC_SCALE_BYTES)
+        return fail(B200Q_ERR_INVALID,
+                    "matmul_noalloc: m=%d x k=%lld needs %zu bytes of scratch; the built-in scratch holds m*k <= %zu elements and m <= %zu rows",
+                    m, (long long)w->k, (size_t)m * (size_t)w->k * 2, NOALLOC_X16_BYTES / 2, NOALLOC_SCALE_BYTES / sizeof(float));
+    if (!g_noalloc_dev_ptr[ctx->device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return cuda_fail(B200Q_ERR_INIT, e, "cudaGetSymbolAddress(built-in scratch)");
+        g_noalloc_dev_ptr[ctx->device] = p;
+    }
+    __half* d_x16 = static_cast<__half*>(g_noalloc_dev_ptr[ctx->device]);
+    float* d_scale = reinterpret_cast<float*>(static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device]) + NOALLOC_X16_BYTES);
+    // nothing in the scratch has to start at zero: the conversion below rewrites every element the GEMM reads
+    const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
+    x_to_f16_kernel<float><<<m, 256, 0, ctx->stream>>>(d_x, w->k, d_x16, d_scale, (int)w->k, perm);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(B200Q_ERR_INIT, "matmul_noalloc: cuTensorMapEncodeTiled is not available from this driver");
+    int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+    int tmem_cols = 32;
+    while (tmem_cols < bn) tmem_cols <<= 1;
+    CUtensorMap map;
+    cuuint64_t gdim[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
+    cuuint64_t gstr[1] = {(cuuint64_t)w->k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d_x16, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul_noalloc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    GemmArgs a{};
+    a.v = w->view; a.xscale = d_scale; a.y = d_y; a.ldy = w->n_local;
+    a.n_rows = (int)w->n_local; a.k = (int)w->k; a.m = m; a.bn = bn; a.tmem_cols = tmem_cols;
+    a.status = ctx->d_status;
+    dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
+    size_t smem = 1024 + (size_t)STAGES * (A_STAGE_BYTES + (size_t)bn * BK * 2) + (3 * STAGES + 1) * 8 + 16;
+    switch (w->fmt) {
+#define X(F) \
+    case F: return launch_fmt<F>(ctx, map, a, grid, smem);
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+    }
+    return fail(B200Q_ERR_INVALID, "matmul_noalloc: unknown format %d", w->fmt);
+}
+
 // Reads and clears the status word the tensor-core kernel raises when a bounded wait expires.
 int gemm_tc_check_status(b200q_ctx* ctx) {
     int h[1] = {0};

@@ -116,6 +116,17 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
     return rc;
 }
 
+int b200q_matmul_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m) {
+    if (!ctx) return fail(B200Q_ERR_INVALID, "matmul_noalloc: ctx is null");
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    int rc = check_matmul_args(ctx, w, d_x, d_y, m);
+    if (rc != B200Q_OK) return rc;
+    if (m == 0) return B200Q_OK;
+    rc = launch_gemm_tc_noalloc(ctx, w, d_x, d_y, m);
+    if (rc == B200Q_OK) ctx->tc_pending = true;
+    return rc;
+}
+
 int b200q_matmul(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* d_y, int y_dtype, int m,
                  unsigned flags) {
     return b200q_matmul_ex(ctx, w, d_x, x_dtype, 0, d_y, y_dtype, 0, m, flags);
