@@ -26,7 +26,8 @@
 // Work decomposition. A CTA tile is (8 >> kw_log2) tiles of 16 weight rows x the whole k, the 8 warps of
 // the CTA arranged as row-tiles x k-parts; partial sums meet in shared memory. A launch covers any number
 // of products (a whole decode step): CTAs are persistent and own a contiguous range of CTA tiles balanced
-// by bytes, so each CTA prepares the activations of only the products it touches.
+// by bytes, so each CTA prepares the activations of only the products it touches. Weights reach the warps
+// through per-warp cp.async rings in shared memory (see "weight streaming" below).
 #include <cuda_fp16.h>
 
 #include "gemv_mma.cuh"
@@ -55,15 +56,6 @@ __device__ __forceinline__ void mma16816_z(float (&c)[4], uint32_t a0, uint32_t 
         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
-
-__device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-// Pulls the line into L2 ahead of use; costs no register and may point past the end of a row (never past
-// the tensor's allocation: callers clamp to `lim`).
-__device__ __forceinline__ void prefetch_l2(const uint8_t* p, const uint8_t* lim) {
-    if (p < lim) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
-__device__ __forceinline__ uint32_t ldg16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); }
-__device__ __forceinline__ uint32_t ldg8(const uint8_t* p) { return __ldg(p); }
 
 // Shared-memory image of one product's activations, per 16-weight run R and activation row n:
 //   img[(R*m + n)*4 + {0,1}] : f16 hi parts of the 16 activations, in MMA order (4 per MMA)
@@ -175,214 +167,95 @@ __device__ __forceinline__ void q4k_decode_hdr(uint4 h, uint32_t sel, Q4KHalfSca
     h1.dA = d48 * s23.x; h1.dB = d44 * s23.y; h1.nA = dm24 * m23.x; h1.nB = dm24 * m23.y;
 }
 
-// One 16-row tile x halves [hb, he) (a half = 128 weights of a row). Thread (g, t) owns, in every half and
-// for rows g and g+8, bytes [16*(t&1), +16) of chunk (t>>1): 16 weights of a low-nibble sub-block and 16 of
-// the high-nibble sub-block. acc[i][n]: partial sum of row g+8i, activation row n, over this thread's runs.
-template <int MT>
-__device__ __forceinline__ void tile_q4k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
-                                         const BLane& bl, float (&acc)[2][MT]) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
-    if (hb >= he) return;
-    const uint8_t* base = op.v.p[0];
-    const uint8_t* plim = base + ((((int64_t)op.n_rows * op.k) >> 8) * 144);   // end of the packed tensor
-    const int qoff = 16 + tp * 32 + (t & 1) * 16;   // this thread's 16 bytes inside the first chunk pair
-    const uint32_t sel = tp ? 0x7632u : 0x5410u;
-    // Two look-ahead slots per row; slot s always holds halves of one parity, so its pointer advances by one
-    // whole super-block (144 bytes) per use and whether it sees FIRST halves of super-blocks never changes.
-    const uint8_t* ps[2][2];      // [slot][row]
-    bool first_half[2][2];
-    const uint8_t* hp[2];         // header of the super-block whose first half comes next
-    uint4 hraw[2];                // ... prefetched
-    Q4KHalfScales sc[2][2];       // [slot][row] scales of the half the slot processes next
-    uint4 wn[2][2];
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
-        int64_t hs = ((r * op.k) >> 7) + hb;   // stream index of the first half
-        const uint8_t* sb = base + (hs >> 1) * 144;
-        const bool par = (hs & 1) != 0;
-        ps[0][i] = sb + (par ? 64 : 0) + qoff;
-        ps[1][i] = sb + (par ? 144 : 64) + qoff;
-        first_half[0][i] = !par;
-        first_half[1][i] = par;
-        hraw[i] = make_uint4(0, 0, 0, 0);
-        if (par) {   // the row starts in the second half of a super-block: its header is needed at once
-            Q4KHalfScales unused;
-            q4k_decode_hdr(ldg128(sb), sel, unused, sc[0][i]);
-            hp[i] = sb + 144;
-            if (hb + 1 < he) hraw[i] = ldg128(hp[i]);
-        } else {
-            hp[i] = sb;
-            hraw[i] = ldg128(hp[i]);
-        }
-        wn[0][i] = ldg128(ps[0][i]);
-        wn[1][i] = make_uint4(0, 0, 0, 0);
-        if (hb + 1 < he) wn[1][i] = ldg128(ps[1][i]);
-    }
-    for (int h0 = hb; h0 < he; h0 += 2) {
-#pragma unroll
-        for (int j2 = 0; j2 < 2; j2++) {
-            const int h = h0 + j2;
-            if (h < he) {
-                uint4 w[2] = {wn[j2][0], wn[j2][1]};
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    if (first_half[j2][i]) {
-                        q4k_decode_hdr(hraw[i], sel, sc[j2][i], sc[j2 ^ 1][i]);
-                        hp[i] += 144;
-                        if (h + 2 < he) hraw[i] = ldg128(hp[i]);
-                    }
-                    if (h + 2 < he) {
-                        ps[j2][i] += 144;
-                        wn[j2][i] = ldg128(ps[j2][i]);
-                        prefetch_l2(ps[j2][i] + 6 * 144, plim);
-                    }
-                }
-                const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
-                const uint32_t w0[4] = {w[0].x, w[0].y, w[0].z, w[0].w};
-                const uint32_t w1[4] = {w[1].x, w[1].y, w[1].z, w[1].w};
-                uint32_t s0[4], s1[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
-                const int RA = 8 * h + 4 * tp + (t & 1);   // run of the low-nibble weights; high nibbles: RA + 2
-#pragma unroll
-                for (int n = 0; n < MT; n++) {
-                    if (n < m) {
-                        uint4 b01, b23;
-                        float cA[4], cB[4];
-                        load_b(bl, RA * m + n, b01, b23);
-                        mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
-                        mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
-                        mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
-                        mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
-                        load_b(bl, (RA + 2) * m + n, b01, b23);
-                        mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
-                        mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
-                        mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
-                        mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
-                        float2 sa = xs.ss[RA * m + n], sb = xs.ss[(RA + 2) * m + n];
-#pragma unroll
-                        for (int i = 0; i < 2; i++) {
-                            float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
-                            const Q4KHalfScales& q = sc[j2][i];
-                            acc[i][n] += va * (q.dA * sa.x) - q.nA * sa.y + vb * (q.dB * sb.x) - q.nB * sb.y;
-                        }
-                    }
-                }
-            }
-        }
-    }
+// ------------------------------------------------------------------------------------ weight streaming
+// Every warp streams its weights through a private ring in shared memory filled with cp.async (16 bytes
+// per thread and copy), `ring_d` items deep. An item is one 128-weight half of the warp's 16 rows; the
+// producer cursor runs ring_d items ahead of the consumer over a FLAT stream of (tile, half) items, so the
+// prefetch crosses tile boundaries and no load latency is exposed when a warp starts a new tile. No
+// registers are held for look-ahead. Slot layout (per warp): [row g / g+8][piece 0/1][lane] x 16 B of codes,
+// then [row][quad] x 16 B of block header written by the quad's first lane.
+constexpr int RING_DATA_BYTES = 2 * 2 * 32 * 16;
+constexpr int RING_HDR_BYTES = 2 * 8 * 16;
+constexpr int RING_SLOT_BYTES = RING_DATA_BYTES + RING_HDR_BYTES;   // 2304
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_wait_keep(int keep) {   // wait until at most `keep` groups are pending
+    if (keep >= 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+    else asm volatile("cp.async.wait_group 1;" ::: "memory");
 }
 
-// ------------------------------------------------------------------------------------------- Q6_K (GGUF)
-// Thread (g, t) owns, in every 128-weight half and for rows g and g+8, 16 bytes of ql (32-run a = t>>1 in
-// its low nibbles, 32-run a+2 in its high nibbles; 16-weight half lh = t&1 of each) and the matching 16
-// bytes of qh: two runs of 16 weights with one int8 scale each. All four planes are linear in the stream
-// index of the half, so every pointer advances by a constant per half.
-struct Q6KW {
-    uint4 ql, qh;
-    uint32_t s_lo, s_hi;   // int8 scales of the two runs
-    uint32_t d;            // f16 bits
+// ---- Q4_K: thread (g, t) owns, in every half and for rows g and g+8, bytes [16*(t&1), +16) of chunk (t>>1):
+// 16 weights of a low-nibble sub-block and 16 of the high-nibble sub-block.
+struct Q4KCursor {
+    const uint8_t* p;   // this thread's 16 bytes of the half the cursor is on
+    bool second;        // the half is the second half of its super-block
 };
 
-struct Q6KPtr {
-    const uint8_t *ql, *qh, *sc, *d0;   // d0: d plane; indexed with the block number
-    int hs;                             // stream index of the half the pointers address
+__device__ __forceinline__ Q4KCursor q4k_cursor(const GOp& op, int64_t row, int h, int qoff) {
+    int64_t hs = ((row * op.k) >> 7) + h;
+    Q4KCursor c;
+    c.second = (hs & 1) != 0;
+    c.p = op.v.p[0] + (hs >> 1) * 144 + (c.second ? 64 : 0) + qoff;
+    return c;
+}
+// copies the cursor's half (and the super-block header, by the quad's first lane, when the consumer will
+// need it: first half of a super-block or first item of a tile) into ring slot `slot`, row index i
+__device__ __forceinline__ void q4k_issue(Q4KCursor& c, uint32_t slot, int i, int lane, bool tile_start) {
+    cp_async16(slot + (i * 2) * 512 + lane * 16, c.p);
+    if ((lane & 3) == 0 && (tile_start || !c.second))
+        cp_async16(slot + RING_DATA_BYTES + (i * 8 + (lane >> 2)) * 16, c.p - 16 - (c.second ? 64 : 0));
+    c.p += c.second ? 80 : 64;
+    c.second = !c.second;
+}
+
+// ---- Q6_K: thread (g, t) owns 16 bytes of ql (32-run a = t>>1 in the low nibbles, a+2 in the high nibbles,
+// 16-weight half lh = t&1 of each) and the matching 16 bytes of qh; header = 8 int8 scales + the f16 d pair.
+struct Q6KCursor {
+    const uint8_t *ql, *qh, *sc;
+    int hs;
 };
 
-__device__ __forceinline__ Q6KW q6k_load(const Q6KPtr& p) {
-    Q6KW w;
-    w.ql = ldg128(p.ql);
-    w.qh = ldg128(p.qh);
-    w.s_lo = ldg8(p.sc);
-    w.s_hi = ldg8(p.sc + 4);
-    w.d = ldg16(p.d0 + (p.hs >> 1) * 2);
-    return w;
+__device__ __forceinline__ Q6KCursor q6k_cursor(const GOp& op, int64_t row, int h, int t) {
+    int64_t hs = ((row * op.k) >> 7) + h;
+    Q6KCursor c;
+    c.ql = op.v.p[0] + hs * 64 + (t >> 1) * 32 + (t & 1) * 16;
+    c.qh = op.v.p[1] + hs * 32 + (t & 1) * 16;
+    c.sc = op.v.p[2] + hs * 8;
+    c.hs = (int)hs;
+    return c;
 }
-
-__device__ __forceinline__ void q6k_advance(Q6KPtr& p) {
-    p.ql += 64; p.qh += 32; p.sc += 8; p.hs += 1;
-}
-
-template <int MT>
-__device__ __forceinline__ void tile_q6k(const GOp& op, int m, int rtile, int hb, int he, const XImg& xs,
-                                         const BLane& bl, float (&acc)[2][MT]) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, a = t >> 1, lh = t & 1;
-    if (hb >= he) return;
-    Q6KPtr pp[2];
-    Q6KW wn[2];   // one half of look-ahead
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        int64_t r = min((int64_t)rtile * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
-        int64_t hs = ((r * op.k) >> 7) + hb;
-        pp[i].ql = op.v.p[0] + hs * 64 + a * 32 + lh * 16;
-        pp[i].qh = op.v.p[1] + hs * 32 + lh * 16;
-        pp[i].sc = op.v.p[2] + hs * 8 + 2 * a + lh;
-        pp[i].d0 = op.v.p[3];
-        pp[i].hs = (int)hs;
-        wn[i] = q6k_load(pp[i]);
+__device__ __forceinline__ void q6k_issue(Q6KCursor& c, const uint8_t* dplane, uint32_t slot, int i, int lane) {
+    cp_async16(slot + (i * 2) * 512 + lane * 16, c.ql);
+    cp_async16(slot + (i * 2 + 1) * 512 + lane * 16, c.qh);
+    if ((lane & 3) == 0) {
+        uint32_t h = slot + RING_DATA_BYTES + (i * 8 + (lane >> 2)) * 16;
+        cp_async8(h, c.sc);
+        cp_async4(h + 8, dplane + ((c.hs >> 2) << 2));   // the 4 aligned bytes holding d of this block pair
     }
-    const int shl = 4 - 2 * a, shr = 2 * a;
-    for (int h = hb; h < he; h++) {
-        Q6KW w[2] = {wn[0], wn[1]};
-        if (h + 1 < he) {
-#pragma unroll
-            for (int i = 0; i < 2; i++) { q6k_advance(pp[i]); wn[i] = q6k_load(pp[i]); }
-        }
-        uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
-        float dL[2], dH[2];
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint32_t ql[4] = {w[i].ql.x, w[i].ql.y, w[i].ql.z, w[i].ql.w};
-            const uint32_t qh[4] = {w[i].qh.x, w[i].qh.y, w[i].qh.z, w[i].qh.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint32_t cl = (ql[j] & 0x0F0F0F0Fu) | ((qh[j] << shl) & 0x30303030u);          // 32-run a
-                uint32_t ch = ((ql[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> shr) & 0x30303030u);   // 32-run a+2
-                aL[i][j][0] = __byte_perm(cl, 0, 0x4140); aL[i][j][1] = __byte_perm(cl, 0, 0x4342);
-                aH[i][j][0] = __byte_perm(ch, 0, 0x4140); aH[i][j][1] = __byte_perm(ch, 0, 0x4342);
-            }
-            float d24 = __half2float(__ushort_as_half((unsigned short)w[i].d)) * 16777216.0f;
-            dL[i] = d24 * (float)(int)(int8_t)w[i].s_lo;   // d * scale * 2^24
-            dH[i] = d24 * (float)(int)(int8_t)w[i].s_hi;
-        }
-        const int RL = 8 * h + 2 * a + lh;   // run of the low-nibble codes; high nibbles: RL + 4
-#pragma unroll
-        for (int n = 0; n < MT; n++) {
-            if (n < m) {
-                uint4 b01, b23;
-                float cL[4], cH[4];
-                load_b(bl, RL * m + n, b01, b23);
-                mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
-                mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
-                mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
-                mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
-                load_b(bl, (RL + 4) * m + n, b01, b23);
-                mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
-                mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
-                mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
-                mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
-                float2 sl = xs.ss[RL * m + n], sh = xs.ss[(RL + 4) * m + n];
-                const float k32 = 32.0f / 16777216.0f;
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    float vl = cL[2 * i] + cL[2 * i + 1], vh = cH[2 * i] + cH[2 * i + 1];
-                    // d * sc * (sum q x - 32 sum x)
-                    acc[i][n] += dL[i] * (vl * sl.x - k32 * sl.y) + dH[i] * (vh * sh.x - k32 * sh.y);
-                }
-            }
-        }
-    }
+    c.ql += 64; c.qh += 32; c.sc += 8; c.hs += 1;
 }
 
-// --------------------------------------------------------------------------------------------- kernel
+// ---------------------------------------------------------------------------------------------- kernel
 template <int MT>
 __global__ void __launch_bounds__(256, 2)
-gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_tiles, int m) {
+gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_tiles, int m,
+                int ring_d) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* red = reinterpret_cast<float*>(smem);
-    uint8_t* xbase = smem + RED_FLOATS * sizeof(float);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
+    uint8_t* ring_gen = smem + RED_FLOATS * sizeof(float) + warp * ring_d * RING_SLOT_BYTES;
+    const uint32_t ring = smem_addr(ring_gen);
+    uint8_t* xbase = smem + RED_FLOATS * sizeof(float) + 8 * ring_d * RING_SLOT_BYTES;
     int tb, te;
     if (ranges) {
         int2 rg = ranges[blockIdx.x];
@@ -391,7 +264,7 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         tb = (int)(((int64_t)blockIdx.x * total_tiles) / gridDim.x);
         te = (int)(((int64_t)(blockIdx.x + 1) * total_tiles) / gridDim.x);
     }
-    int opi = 0, cur = -1;
+    int opi = 0;
     if (n_ops > 1) {   // first product whose tile range reaches tb
         int lo = 0, hi = n_ops - 1;
         while (lo < hi) {
@@ -400,88 +273,242 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         }
         opi = lo;
     }
-    GOp op = single;
-    XImg xs{};
-    BLane bl{};
     if (threadIdx.x < XZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xbase)[threadIdx.x] = 0u;   // published by the first barrier
-    for (int tile = tb; tile < te; tile++) {
+    const int qoff = 16 + tp * 32 + (t & 1) * 16;        // Q4_K: this thread's 16 bytes inside the first chunk pair
+    const uint32_t sel = tp ? 0x7632u : 0x5410u;         // Q4_K: which scale bytes of a header belong to this thread
+    const int a6 = t >> 1, lh6 = t & 1, shl6 = 4 - 2 * a6, shr6 = 2 * a6;   // Q6_K
+    const int keep = ring_d - 1;
+
+    for (int seg_b = tb; seg_b < te;) {
+        // ---- one product: tiles [seg_b, seg_e) of this CTA belong to it
+        GOp op = single;
         if (n_ops > 1) {
-            while (opi < n_ops - 1 && tile >= ops[opi].tile0 + ops[opi].ntiles) opi++;
+            while (opi < n_ops - 1 && seg_b >= ops[opi].tile0 + ops[opi].ntiles) opi++;
+            op = ops[opi];
         }
-        if (opi != cur) {
-            if (n_ops > 1) op = ops[opi];
-            __syncthreads();   // everyone is done with the previous product's activations
-            xs = ximg_carve(xbase, op.k, m);
-            bl = blane_make(xs, xbase, lane >> 2, lane & 3);
-            if (op.fmt == F_Q4K) prep_x<true>(op.x, op.ldx, op.k, m, xs);
-            else prep_x<false>(op.x, op.ldx, op.k, m, xs);
-            __syncthreads();
-            cur = opi;
-        }
-        const int kw = 1 << op.kw_log2;
-        const int rtile = (tile - op.tile0) * (8 >> op.kw_log2) + (warp >> op.kw_log2);
+        const int seg_e = min(te, op.tile0 + op.ntiles);
+        __syncthreads();   // everyone is done with the previous product's activations
+        XImg xs = ximg_carve(xbase, op.k, m);
+        BLane bl = blane_make(xs, xbase, g, t);
+        const bool q4 = op.fmt == F_Q4K;
+        if (q4) prep_x<true>(op.x, op.ldx, op.k, m, xs);
+        else prep_x<false>(op.x, op.ldx, op.k, m, xs);
+        __syncthreads();
+
+        const int kw = 1 << op.kw_log2, rt = 8 >> op.kw_log2;
         const int kpart = warp & (kw - 1);
-        float acc[2][MT];
-#pragma unroll
-        for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
-        const bool live = (int64_t)rtile * 16 < op.n_rows;
-        if (live) {
-            int nh = op.k >> 7, per = (nh + kw - 1) >> op.kw_log2;
-            int hb = kpart * per, he = min(nh, (kpart + 1) * per);
-            if (op.fmt == F_Q4K) tile_q4k<MT>(op, m, rtile, hb, he, xs, bl, acc);
-            else tile_q6k<MT>(op, m, rtile, hb, he, xs, bl, acc);
-        }
-        // the four threads of a quad hold partial sums of the same two rows
-#pragma unroll
-        for (int n = 0; n < MT; n++) {
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                float s = acc[i][n];
-                s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-                s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-                acc[i][n] = s;
-            }
-        }
-        const int g = lane >> 2, t = lane & 3;
-        if (kw > 1) {
-            if (t == 0) {
-#pragma unroll
-                for (int n = 0; n < MT; n++) {
-                    red[(warp * 16 + g) * MT + n] = acc[0][n];
-                    red[(warp * 16 + g + 8) * MT + n] = acc[1][n];
+        const int nh = op.k >> 7, per = (nh + kw - 1) >> op.kw_log2;
+        const int hb = kpart * per, he = min(nh, (kpart + 1) * per);
+        const bool has_items = hb < he;
+        auto row_of = [&](int tile, int i) -> int64_t {
+            return min(((int64_t)(tile - op.tile0) * rt + (warp >> op.kw_log2)) * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
+        };
+
+        // ---- producer cursor over the flat (tile, half) stream
+        int pt = seg_b, ph = hb, pslot = 0;
+        Q4KCursor c4[2] = {};
+        Q6KCursor c6[2] = {};
+        auto cursor_init = [&]() {
+            if (q4) { c4[0] = q4k_cursor(op, row_of(pt, 0), ph, qoff); c4[1] = q4k_cursor(op, row_of(pt, 1), ph, qoff); }
+            else { c6[0] = q6k_cursor(op, row_of(pt, 0), ph, t); c6[1] = q6k_cursor(op, row_of(pt, 1), ph, t); }
+        };
+        auto issue_next = [&]() {
+            if (has_items && pt < seg_e) {
+                const uint32_t slot = ring + pslot * RING_SLOT_BYTES;
+                if (q4) { q4k_issue(c4[0], slot, 0, lane, ph == hb); q4k_issue(c4[1], slot, 1, lane, ph == hb); }
+                else { q6k_issue(c6[0], op.v.p[3], slot, 0, lane); q6k_issue(c6[1], op.v.p[3], slot, 1, lane); }
+                if (++ph == he) {
+                    ph = hb;
+                    if (++pt < seg_e) cursor_init();
                 }
             }
-            __syncthreads();
-            if (kpart == 0 && live) {
-                for (int o = lane; o < 16 * MT; o += 32) {
-                    int r = o / MT, n = o - r * MT;
-                    float s = 0.f;
-                    for (int j = 0; j < kw; j++) s += red[((warp + j) * 16 + r) * MT + n];
-                    int64_t row = (int64_t)rtile * 16 + r;
-                    if (row < op.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = s;
-                }
-            }
-            __syncthreads();   // the reduction buffer is free again
-        } else if (live && t == 0) {
+            cp_commit();
+            pslot = pslot + 1 == ring_d ? 0 : pslot + 1;
+        };
+        if (has_items && pt < seg_e) cursor_init();
+        for (int d = 0; d < ring_d; d++) issue_next();
+        int cslot = 0;
+
+        for (int tile = seg_b; tile < seg_e; tile++) {
+            const int rtile = (tile - op.tile0) * rt + (warp >> op.kw_log2);
+            const bool live = (int64_t)rtile * 16 < op.n_rows;
+            float acc[2][MT];
 #pragma unroll
-            for (int n = 0; n < MT; n++) {
-                if (n < m) {
+            for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+            // stream index of the current half of each row (its parity = position inside the super-block)
+            int hs_c[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) hs_c[i] = (int)(((row_of(tile, i) * op.k) >> 7) + hb);
+            Q4KHalfScales cur[2], nxt[2];
+            for (int h = hb; h < he; h++) {
+                cp_wait_keep(keep);
+                __syncwarp();   // the quad leader's header copy is visible to its quad
+                const uint8_t* slot = ring_gen + cslot * RING_SLOT_BYTES;
+                const uint4* sd = reinterpret_cast<const uint4*>(slot);
+                const uint4* sh = reinterpret_cast<const uint4*>(slot + RING_DATA_BYTES);
+                if (q4) {
+                    const uint4 wa = sd[lane], wb = sd[64 + lane];
 #pragma unroll
                     for (int i = 0; i < 2; i++) {
-                        int64_t row = (int64_t)rtile * 16 + g + 8 * i;
-                        if (row < op.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n];
+                        const bool second = (hs_c[i] & 1) != 0;
+                        if (h == hb || !second) {
+                            Q4KHalfScales h0, h1;
+                            q4k_decode_hdr(sh[i * 8 + g], sel, h0, h1);
+                            cur[i] = second ? h1 : h0;
+                            nxt[i] = h1;
+                        } else {
+                            cur[i] = nxt[i];
+                        }
+                    }
+                    const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
+                    const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
+                    const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
+                    uint32_t s0[4], s1[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
+                    const int RA = 8 * h + 4 * tp + (t & 1);   // run of the low-nibble weights; high nibbles: RA + 2
+#pragma unroll
+                    for (int n = 0; n < MT; n++) {
+                        if (n < m) {
+                            uint4 b01, b23;
+                            float cA[4], cB[4];
+                            load_b(bl, RA * m + n, b01, b23);
+                            mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
+                            mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
+                            mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
+                            mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
+                            load_b(bl, (RA + 2) * m + n, b01, b23);
+                            mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
+                            mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
+                            mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
+                            mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
+                            const float2 sa = xs.ss[RA * m + n], sb = xs.ss[(RA + 2) * m + n];
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                const float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
+                                acc[i][n] += va * (cur[i].dA * sa.x) - cur[i].nA * sa.y + vb * (cur[i].dB * sb.x) - cur[i].nB * sb.y;
+                            }
+                        }
+                    }
+                } else {
+                    uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
+                    float dL[2], dH[2];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint4 qlv = sd[(i * 2) * 32 + lane], qhv = sd[(i * 2 + 1) * 32 + lane];
+                        const uint4 hd = sh[i * 8 + g];   // x,y: eight int8 scales of the half; z: f16 d of two blocks
+                        const uint32_t ql[4] = {qlv.x, qlv.y, qlv.z, qlv.w};
+                        const uint32_t qh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint32_t cl = (ql[j] & 0x0F0F0F0Fu) | ((qh[j] << shl6) & 0x30303030u);          // 32-run a
+                            uint32_t ch = ((ql[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> shr6) & 0x30303030u);   // 32-run a+2
+                            aL[i][j][0] = __byte_perm(cl, 0, 0x4140); aL[i][j][1] = __byte_perm(cl, 0, 0x4342);
+                            aH[i][j][0] = __byte_perm(ch, 0, 0x4140); aH[i][j][1] = __byte_perm(ch, 0, 0x4342);
+                        }
+                        // block = hs >> 1 picks the f16 d inside the copied pair
+                        const uint32_t dbits = (hs_c[i] & 2) ? (hd.z >> 16) : (hd.z & 0xFFFFu);
+                        const float d24 = __half2float(__ushort_as_half((unsigned short)dbits)) * 16777216.0f;
+                        const uint32_t scw = a6 ? hd.x >> 16 : hd.x;     // scales 2a+lh (low run) ...
+                        const uint32_t scw2 = a6 ? hd.y >> 16 : hd.y;    // ... and 2a+4+lh (high run)
+                        dL[i] = d24 * (float)(int)(int8_t)((scw >> (8 * lh6)) & 0xFFu);
+                        dH[i] = d24 * (float)(int)(int8_t)((scw2 >> (8 * lh6)) & 0xFFu);
+                    }
+                    const int RL = 8 * h + 2 * a6 + lh6;   // run of the low-nibble codes; high nibbles: RL + 4
+#pragma unroll
+                    for (int n = 0; n < MT; n++) {
+                        if (n < m) {
+                            uint4 b01, b23;
+                            float cL[4], cH[4];
+                            load_b(bl, RL * m + n, b01, b23);
+                            mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
+                            mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
+                            mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
+                            mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
+                            load_b(bl, (RL + 4) * m + n, b01, b23);
+                            mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
+                            mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
+                            mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
+                            mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
+                            const float2 sl = xs.ss[RL * m + n], sh2 = xs.ss[(RL + 4) * m + n];
+                            const float k32 = 32.0f / 16777216.0f;
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                const float vl = cL[2 * i] + cL[2 * i + 1], vh = cH[2 * i] + cH[2 * i + 1];
+                                // d * sc * (sum q x - 32 sum x)
+                                acc[i][n] += dL[i] * (vl * sl.x - k32 * sl.y) + dH[i] * (vh * sh2.x - k32 * sh2.y);
+                            }
+                        }
+                    }
+                }
+                hs_c[0]++; hs_c[1]++;
+                __syncwarp();   // every lane has read the slot before it is refilled
+                issue_next();
+                cslot = cslot + 1 == ring_d ? 0 : cslot + 1;
+            }
+            // the four threads of a quad hold partial sums of the same two rows
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    float sacc = acc[i][n];
+                    sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 1);
+                    sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 2);
+                    acc[i][n] = sacc;
+                }
+            }
+            if (kw > 1) {
+                if (t == 0) {
+#pragma unroll
+                    for (int n = 0; n < MT; n++) {
+                        red[(warp * 16 + g) * MT + n] = acc[0][n];
+                        red[(warp * 16 + g + 8) * MT + n] = acc[1][n];
+                    }
+                }
+                __syncthreads();
+                if (kpart == 0 && live) {
+                    for (int o = lane; o < 16 * MT; o += 32) {
+                        int r = o / MT, n = o - r * MT;
+                        float sacc = 0.f;
+                        for (int j = 0; j < kw; j++) sacc += red[((warp + j) * 16 + r) * MT + n];
+                        int64_t row = (int64_t)rtile * 16 + r;
+                        if (row < op.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = sacc;
+                    }
+                }
+                __syncthreads();   // the reduction buffer is free again
+            } else if (live && t == 0) {
+#pragma unroll
+                for (int n = 0; n < MT; n++) {
+                    if (n < m) {
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            int64_t row = (int64_t)rtile * 16 + g + 8 * i;
+                            if (row < op.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n];
+                        }
                     }
                 }
             }
         }
+        // drain: nothing of this product's ring may still be in flight when the next product reuses it
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        seg_b = seg_e;
     }
 }
 
 }  // namespace
 
+// Ring depth: 4 items when that still lets two CTAs share an SM (or when nothing smaller helps), else 2.
+int gemv_mma_ring_depth(int k, int m) {
+    size_t image = XZERO_BYTES + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16 + RED_FLOATS * sizeof(float);
+    if (image + 8 * 4 * RING_SLOT_BYTES <= 110 * 1024) return 4;
+    if (image + 8 * 2 * RING_SLOT_BYTES <= 110 * 1024) return 2;
+    return image + 8 * 4 * RING_SLOT_BYTES <= 220 * 1024 ? 4 : 2;
+}
+
 size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
     (void)fmt;
-    return RED_FLOATS * sizeof(float) + XZERO_BYTES + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
+    return RED_FLOATS * sizeof(float) + 8 * (size_t)gemv_mma_ring_depth(k, m) * RING_SLOT_BYTES + XZERO_BYTES +
+           (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
 bool gemv_mma_supported(const b200q_weight* w, int m) {
@@ -489,7 +516,7 @@ bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
     if (w->fmt != F_Q4K && w->fmt != F_Q6K) return false;
     if (w->k % 128) return false;
-    return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 200 * 1024;
+    return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 220 * 1024;
 }
 
 void gemv_mma_plan(GOp* op, bool few_tiles) {
@@ -510,12 +537,17 @@ void gemv_mma_plan(GOp* op, bool few_tiles) {
     op->ntiles = (row_tiles + rt - 1) / rt;
 }
 
+size_t gemv_mma_smem_for(int ring_d, int kmax, int m) {
+    return RED_FLOATS * sizeof(float) + 8 * (size_t)ring_d * RING_SLOT_BYTES + XZERO_BYTES +
+           (size_t)(kmax >> 4) * m * (64 + sizeof(float2)) + 16;
+}
+
 int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
-                    int total_tiles, int m, size_t smem_bytes) {
+                    int total_tiles, int m, size_t smem_bytes, int ring_d) {
     if (total_tiles <= 0) return B200Q_OK;
     static bool configured[64][4] = {};
     const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
-    const int smem_cap = 200 * 1024 + 8192;
+    const int smem_cap = 226 * 1024;
     if (!configured[ctx->device & 63][mi]) {
         cudaError_t e = cudaSuccess;
         switch (mi) {
@@ -530,10 +562,10 @@ int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n
     GOp single{};
     if (h_single) single = *h_single;
     switch (mi) {
-        case 0: gemv_mma_kernel<1><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
-        case 1: gemv_mma_kernel<2><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
-        case 2: gemv_mma_kernel<4><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
-        default: gemv_mma_kernel<8><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m); break;
+        case 0: gemv_mma_kernel<1><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        case 1: gemv_mma_kernel<2><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        case 2: gemv_mma_kernel<4><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        default: gemv_mma_kernel<8><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
     }
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;

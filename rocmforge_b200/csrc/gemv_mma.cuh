@@ -23,7 +23,11 @@ size_t gemv_mma_smem_bytes(int fmt, int k, int m);
 // Fills kw_log2 / ntiles of `op` from its shape; `few_tiles` trades tile size for parallelism (single launches).
 void gemv_mma_plan(GOp* op, bool few_tiles);
 // ops/ranges are device pointers when n_ops > 1; for n_ops == 1 the product travels as a kernel argument.
+// Depth (2 or 4 items) of the per-warp weight ring for inner dimension k and m activation rows, and the
+// dynamic shared memory of a launch with that depth whose largest product has inner dimension kmax.
+int gemv_mma_ring_depth(int k, int m);
+size_t gemv_mma_smem_for(int ring_d, int kmax, int m);
 int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
-                    int total_tiles, int m, size_t smem_bytes);
+                    int total_tiles, int m, size_t smem_bytes, int ring_d);
 
 }  // namespace b200q

@@ -17,7 +17,7 @@ struct b200q_batch {
     bool grouped = false;
     GOp* d_ops = nullptr;
     int2* d_ranges = nullptr;
-    int n_ctas = 0, total_tiles = 0;
+    int n_ctas = 0, total_tiles = 0, ring_d = 4;
     size_t smem = 0;
     GOp single{};
 };
@@ -30,7 +30,7 @@ static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y
     return op;
 }
 
-static int ctas_per_sm(size_t smem) { return smem <= 100 * 1024 ? 2 : 1; }
+static int ctas_per_sm(size_t smem) { return smem <= 112 * 1024 ? 2 : 1; }
 
 static int check_matmul_args(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, const void* d_y, int m) {
     if (!w) return fail(B200Q_ERR_INVALID, "matmul: weight handle is null");
@@ -58,10 +58,11 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
             GOp op = make_gop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
             gemv_mma_plan(&op, true);
             op.tile0 = 0;
-            size_t smem = gemv_mma_smem_bytes(w->fmt, (int)w->k, mm);
+            const int ring_d = gemv_mma_ring_depth((int)w->k, mm);
+            size_t smem = gemv_mma_smem_for(ring_d, (int)w->k, mm);
             int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
             if (n_ctas > op.ntiles) n_ctas = op.ntiles;
-            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem);
+            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem, ring_d);
         } else {
             rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
         }
@@ -174,7 +175,7 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
     if (all) {
         std::vector<GOp> ops(count);
         std::vector<double> tile_cost;
-        int total = 0;
+        int total = 0, kmax = 0, ring_d = 4;
         size_t smem = 0;
         for (int i = 0; i < count; i++) {
             ops[i] = make_gop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
@@ -184,9 +185,12 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
             FmtInfo I = fmt_info(w[i]->fmt);
             double c = (double)(8 >> ops[i].kw_log2) * 16 * w[i]->k * I.block_bytes / I.block_elems + 2048.0;
             for (int t = 0; t < ops[i].ntiles; t++) tile_cost.push_back(c);
-            size_t sm = gemv_mma_smem_bytes(w[i]->fmt, (int)w[i]->k, m);
-            if (sm > smem) smem = sm;
+            if (w[i]->k > kmax) kmax = (int)w[i]->k;
+            int rd = gemv_mma_ring_depth((int)w[i]->k, m);
+            if (rd < ring_d) ring_d = rd;
         }
+        smem = gemv_mma_smem_for(ring_d, kmax, m);
+        b->ring_d = ring_d;
         int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
         if (n_ctas > total) n_ctas = total;
         // contiguous tile ranges of (nearly) equal cost
@@ -230,7 +234,7 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (batch->grouped) {
         int n = (int)batch->w.size();
         int rc = launch_gemv_mma(ctx, &batch->single, batch->d_ops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
-                                 batch->total_tiles, batch->m, batch->smem);
+                                 batch->total_tiles, batch->m, batch->smem, batch->ring_d);
         if (rc != B200Q_OK) return rc;
     } else {
         for (size_t i = 0; i < batch->w.size(); i++) {
