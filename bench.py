@@ -21,6 +21,7 @@ object of the same line.
 import argparse
 import ctypes
 import json
+import re
 import os
 import subprocess
 import sys
@@ -335,10 +336,12 @@ def main():
     per_gpu = STEP_BYTES / (ms_step * 1e-3) / 1e9
     value = world * per_gpu
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    # DRAM bytes per algorithmic byte of the step kernel, from the committed ncu capture of this workload
+    tp = os.path.join(ROOT, "profiles", "gemv_mma_kernel_qwen2_decode_step.md")
     if os.path.exists(tp):
-        tr = json.load(open(tp))
-        traffic = int(tr["dram_bytes_per_algorithmic_byte"] * STEP_BYTES)
+        hit = re.search(r"dram_bytes_per_algorithmic_byte\s*=\s*([0-9.]+)", open(tp).read())
+        if hit:
+            traffic = int(float(hit.group(1)) * STEP_BYTES)
 
     out = {
         "metric": METRIC % m, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -117,6 +117,37 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// A operand read from tensor memory (lanes = rows, two f16 per 32-bit column), B from a shared-memory descriptor.
+__device__ __forceinline__ void umma_ts_f16_acc(uint32_t tmem_d, uint32_t tmem_a, uint32_t blo, uint32_t bhi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .b64 db;\n\t.reg .pred p;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.b32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(blo), "r"(bhi), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts_f16_first(uint32_t tmem_d, uint32_t tmem_a, uint32_t blo, uint32_t bhi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .b64 db;\n\t.reg .pred p;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(blo), "r"(bhi), "r"(idesc)
+        : "memory");
+}
+
+// Each thread of the warp writes 16 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // K-major operand tile with 128-byte swizzle: rows at a 128-byte pitch, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -210,6 +241,7 @@ struct GemmArgs {
     float* y;
     int64_t ldy;
     int n_rows, k, m, bn, tmem_cols;
+    int a_col0;            // first TMEM column of the weight-operand slots (kernel with the A operand in TMEM)
     int* status;
 };
 
@@ -390,16 +422,255 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// GGUF Q4_K with the weight operand in tensor memory.
+//
+// With both operands in shared memory the kernel above is bound by the SM's shared-memory data pipe: per 64-k
+// block it carries the TMA writes and tensor-core reads of the activation tile (32 KB each), the producers'
+// scattered global loads, their 16 KB of f16 stores and the tensor-core reads of those. Here the weights never
+// exist as f16 in shared memory:
+//   * warp 2 copies the raw super-blocks (144 bytes per row per 256 k) with one tiled TMA copy per 128 rows
+//     into a 3-deep ring: 18 KB per 256 k instead of 64 KB of f16 (one copy per row was tried first and was
+//     bound by the copy engine's request rate);
+//   * warps 4..11 (thread = weight row; warps 4-7 take the low nibbles = first 32 k of each 64-k chunk, warps
+//     8-11 the high nibbles = last 32 k) expand 32 weights to 16 packed f16x2 registers and write them with
+//     tcgen05.st into the TMEM slot of the stage (32 columns per stage: lane = row, column c = k 2c, 2c+1);
+//   * the MMA takes A from TMEM ([taddr] operand) and B from the swizzled shared-memory tile as before.
+// TMEM columns: [0, bn) accumulator, [a_col0, a_col0 + 32 * STAGES) weight slots.
+constexpr int RAW_STAGES = 3;
+constexpr int RAW_ROW_BYTES = 144;
+constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;   // 18,432
+constexpr int A_SLOT_COLS = BK / 2;                   // 32
+
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_q4k_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int b_stage_bytes = a.bn * BK * 2;
+    uint8_t* sB = smem;
+    uint8_t* sRaw = sB + STAGES * b_stage_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RAW_STAGES * RAW_STAGE_BYTES);
+    uint64_t* full = bars;                            // 8 converter warps + the TMA thread's expect_tx arrival
+    uint64_t* empty = bars + STAGES;                  // tcgen05.commit
+    uint64_t* raw_full = bars + 2 * STAGES;           // bulk-copy bytes
+    uint64_t* raw_empty = raw_full + RAW_STAGES;      // 8 converter warps
+    uint64_t* accum = raw_empty + RAW_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * BM;
+    const int tok0 = blockIdx.y * a.bn;
+    const int nkb = a.k / BK;
+    const int nsb = a.k >> 8;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&full[s]), 9);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int s = 0; s < RAW_STAGES; s++) {
+            mbar_init(smem_u32(&raw_full[s]), 1);
+            mbar_init(smem_u32(&raw_empty[s]), 8);
+        }
+        mbar_init(smem_u32(accum), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (activations)
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb & (STAGES - 1);
+                const uint32_t ph = (kb >> 2) & 1;
+                if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 1)) break;
+                mbar_arrive_expect_tx(smem_u32(&full[s]), (uint32_t)b_stage_bytes);
+                tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, smem_u32(&full[s]));
+                issued = kb + 1;
+            }
+            for (int kb = max(0, issued - STAGES); kb < issued; kb++) {   // nothing stays in flight behind us
+                const int s = kb & (STAGES - 1);
+                const uint32_t ph = (kb >> 2) & 1;
+                long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&full[s]), ph)) {
+                    if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 5); break; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sB));
+            const uint32_t bhi = (uint32_t)(bdesc0 >> 32), blo0 = (uint32_t)bdesc0;
+            const uint32_t b_step = (uint32_t)(b_stage_bytes >> 4);
+            const uint32_t fu0 = smem_u32(full), em0 = smem_u32(empty);
+            const uint32_t at0 = tmem_base + (uint32_t)a.a_col0;
+            for (int kb = 0; kb < nkb; kb++) {
+                const uint32_t s = (uint32_t)kb & (STAGES - 1);
+                const uint32_t ph = ((uint32_t)kb >> 2) & 1;
+                if (!mbar_wait(fu0 + s * 8, ph, abort_flag, a.status, 2)) break;
+                tc_fence_after();
+                const uint32_t at = at0 + s * A_SLOT_COLS, bl = blo0 + s * b_step;
+                // 16 k further: 8 TMEM columns on the A side, 32 bytes (+2 encoded) inside the swizzle atom on the B side
+                if (kb == 0) umma_ts_f16_first(tmem_base, at, bl, bhi, idesc);
+                else umma_ts_f16_acc(tmem_base, at, bl, bhi, idesc);
+                umma_ts_f16_acc(tmem_base, at + 8, bl + 2, bhi, idesc);
+                umma_ts_f16_acc(tmem_base, at + 16, bl + 4, bhi, idesc);
+                umma_ts_f16_acc(tmem_base, at + 24, bl + 6, bhi, idesc);
+                umma_commit(em0 + s * 8);
+            }
+            umma_commit(smem_u32(accum));
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- raw super-block loader
+        // The packed tensor is a 2-D byte array [n_rows, k / 256 * 144]; one tiled copy brings the 144-byte
+        // super-block of each of the 128 rows (rows past the end of the tensor read as zeros = zero weights).
+        if (lane == 0) {
+            int issued = 0;
+            for (int sb = 0; sb < nsb; sb++) {
+                const int rs = sb % RAW_STAGES;
+                const uint32_t ph = (uint32_t)(sb / RAW_STAGES) & 1;
+                if (!mbar_wait(smem_u32(&raw_empty[rs]), ph ^ 1, abort_flag, a.status, 7)) break;
+                mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), (uint32_t)RAW_STAGE_BYTES);
+                tma_load_2d(smem_u32(sRaw + rs * RAW_STAGE_BYTES), &tmap_w, sb * RAW_ROW_BYTES, row0, smem_u32(&raw_full[rs]));
+                issued = sb + 1;
+            }
+            for (int sb = max(0, issued - RAW_STAGES); sb < issued; sb++) {   // every copy issued has landed
+                const int rs = sb % RAW_STAGES;
+                const uint32_t ph = (uint32_t)(sb / RAW_STAGES) & 1;
+                long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&raw_full[rs]), ph)) {
+                    if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 9); break; }
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- converters: raw bytes -> f16 in TMEM
+        const int q = warp & 3;                 // TMEM lane quarter this warp may touch
+        const int nib = (warp - 4) >> 2;        // 0: low nibbles (k 0..31 of a chunk), 1: high nibbles (k 32..63)
+        const int r = q * 32 + lane;
+        const uint32_t slot0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)a.a_col0 + (uint32_t)nib * 16;
+        const uint32_t mask = nib ? 0x00F000F0u : 0x000F000Fu;
+        const float nibscale = nib ? 0.0625f : 1.0f;
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        for (int sb = 0; sb < nsb && ok; sb++) {
+            const int rs = sb % RAW_STAGES;
+            const uint32_t rph = (uint32_t)(sb / RAW_STAGES) & 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
+            const uint4 hdr = *reinterpret_cast<const uint4*>(rowp);
+            const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+            const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, m_lo = hdr.z & 0x3F3F3F3Fu;
+            const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+            const uint32_t m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int kb = sb * 4 + c;
+                const int s = kb & (STAGES - 1);
+                const uint32_t ph = (uint32_t)(kb >> 2) & 1;
+                // sub-block 2c + nib of the super-block: byte (2 (c & 1) + nib) of the low or high scale word
+                const int sh = ((c & 1) * 2 + nib) * 8;
+                const uint32_t sc = ((c < 2 ? sc_lo : sc_hi) >> sh) & 0xFFu, mn = ((c < 2 ? m_lo : m_hi) >> sh) & 0xFFu;
+                const __half2 ds = __float2half2_rn(d * (float)sc * nibscale);
+                const __half2 nd = __float2half2_rn(-dmin * (float)mn);
+                const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + c * 32);
+                const uint4 qb = *reinterpret_cast<const uint4*>(rowp + 32 + c * 32);
+                const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                uint32_t v[16];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint32_t t0 = (w[j] & mask) | 0x64006400u, t1 = ((w[j] >> 8) & mask) | 0x64006400u;
+                    __half2 h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), ds, nd);
+                    __half2 h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), ds, nd);
+                    v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                    v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                }
+                if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+            }
+            if (!ok) break;
+            __syncwarp();   // every lane has read its bytes of this raw stage
+            if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+        }
+        // ------------------------------------------------------------ epilogue (same warps)
+        if (warp == 4) {
+            if (lane == 0 && ok) ok = mbar_wait(smem_u32(accum), 0, abort_flag, a.status, 6);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) *abort_flag = 1;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*abort_flag == 0) {
+            tc_fence_after();
+            const int row = row0 + q * 32 + lane;
+            for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (row < a.n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = tok0 + c0 + j;
+                        if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                    }
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown (every path ends here)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols) : "memory");
+    }
+}
+
 // Activation rows -> f16 with a power-of-two scale per row (max |x| of the row lands in [1, 2)).
 // perm: inside every aligned group of four k positions the order becomes 0,2,1,3 -- the order in which the
-// nibble masks of the specialised Q4_K tile producer emit weights (bytes 0 and 2, then bytes 1 and 3).
-template <typename T>
+// nibble masks of the Q4_K tile producers emit weights (bytes 0 and 2, then bytes 1 and 3).
+// One CTA per row; VEC = 4 reads 16 bytes (fp32) or 8 bytes (bf16) per thread and needs k % 4 == 0 with
+// aligned rows, VEC = 1 is the general path. The second pass re-reads the row from L1/L2.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xFFFF0000u));
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
                                                        float* __restrict__ scale, int k, int perm) {
     const int row = blockIdx.x;
     const T* xr = x + (int64_t)row * ldx;
     float mx = 0.0f;
-    for (int i = threadIdx.x; i < k; i += blockDim.x) mx = fmaxf(mx, fabsf((float)xr[i]));
+    if constexpr (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < k; i += 1024) {
+            const float4 v = load4(xr + i);
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+    } else {
+        for (int i = threadIdx.x; i < k; i += 256) mx = fmaxf(mx, fabsf((float)xr[i]));
+    }
     __shared__ float red[8];
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
@@ -409,11 +680,33 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     int e = (int)((__float_as_uint(mx) >> 23) & 255u);
     e = (mx == 0.0f || !(mx <= 3.0e38f)) ? 127 : min(max(e, 1), 253);
     const float sdown = __uint_as_float((uint32_t)(254 - e) << 23);
-    for (int i = threadIdx.x; i < k; i += blockDim.x) {
-        int src = perm ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;
-        out[(int64_t)row * k + i] = __float2half_rn((float)xr[src] * sdown);
+    __half* orow = out + (int64_t)row * k;
+    if constexpr (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < k; i += 1024) {
+            const float4 v = load4(xr + i);
+            const __half2 a = perm ? __floats2half2_rn(v.x * sdown, v.z * sdown) : __floats2half2_rn(v.x * sdown, v.y * sdown);
+            const __half2 b = perm ? __floats2half2_rn(v.y * sdown, v.w * sdown) : __floats2half2_rn(v.z * sdown, v.w * sdown);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&a);
+            pk.y = *reinterpret_cast<const uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(orow + i) = pk;
+        }
+    } else {
+        for (int i = threadIdx.x; i < k; i += 256) {
+            const int src = perm ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;
+            orow[i] = __float2half_rn((float)xr[src] * sdown);
+        }
     }
     if (threadIdx.x == 0) scale[row] = __uint_as_float((uint32_t)e << 23);
+}
+
+template <typename T>
+int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float* scale, int m, int k, int perm) {
+    const bool vec = (k % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0;
+    if (vec) x_to_f16_kernel<T, 4><<<m, 256, 0, ctx->stream>>>(x, ldx, out, scale, k, perm);
+    else x_to_f16_kernel<T, 1><<<m, 256, 0, ctx->stream>>>(x, ldx, out, scale, k, perm);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -432,16 +725,78 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+template <typename K>
+int configure_once(b200q_ctx* ctx, K kernel, bool* configured) {
+    if (!configured[ctx->device & 63]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
+        configured[ctx->device & 63] = true;
+    }
+    return B200Q_OK;
+}
+
 template <int F>
 int launch_fmt(b200q_ctx* ctx, const CUtensorMap& map, const GemmArgs& a, dim3 grid, size_t smem) {
     static bool configured[64] = {};
-    if (!configured[ctx->device & 63]) {
-        B200Q_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
-        configured[ctx->device & 63] = true;
-    }
+    int rc = configure_once(ctx, gemm_tc_kernel<F>, configured);
+    if (rc != B200Q_OK) return rc;
     gemm_tc_kernel<F><<<grid, NTHREADS, smem, ctx->stream>>>(map, a);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
+}
+
+// The product itself, once the f16 copy of the activations (row-major [m, k]) and their row scales exist.
+int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
+                     int m, const char* who) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(B200Q_ERR_INIT, "%s: cuTensorMapEncodeTiled is not available from this driver", who);
+    const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+    CUtensorMap map;
+    cuuint64_t gdim[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
+    cuuint64_t gstr[1] = {(cuuint64_t)w->k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(d_x16), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled failed with code %d", who, (int)r);
+    GemmArgs a{};
+    a.v = w->view; a.xscale = d_scale; a.y = d_y; a.ldy = ldy;
+    a.n_rows = (int)w->n_local; a.k = (int)w->k; a.m = m; a.bn = bn;
+    a.status = ctx->d_status;
+    dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
+    if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
+        // weight operand in tensor memory
+        a.a_col0 = (bn + 31) & ~31;
+        a.tmem_cols = 32;
+        while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * RAW_STAGE_BYTES +
+                            (2 * STAGES + 2 * RAW_STAGES + 1) * 8 + 16;
+        static bool configured[64] = {};
+        int rc = configure_once(ctx, gemm_q4k_tmem_kernel, configured);
+        if (rc != B200Q_OK) return rc;
+        CUtensorMap wmap;
+        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 256) * RAW_ROW_BYTES;
+        cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
+        cuuint64_t wstr[1] = {row_bytes};
+        cuuint32_t wbox[2] = {(cuuint32_t)RAW_ROW_BYTES, (cuuint32_t)BM};
+        r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w->view.p[0]), wdim, wstr, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (weights) failed with code %d", who, (int)r);
+        gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
+        B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+        return B200Q_OK;
+    }
+    a.tmem_cols = 32;
+    while (a.tmem_cols < bn) a.tmem_cols <<= 1;
+    const size_t smem = 1024 + (size_t)STAGES * (A_STAGE_BYTES + (size_t)bn * BK * 2) + (3 * STAGES + 1) * 8 + 16;
+    switch (w->fmt) {
+#define X(F) \
+    case F: return launch_fmt<F>(ctx, map, a, grid, smem);
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+    }
+    return fail(B200Q_ERR_INVALID, "%s: unknown format %d", who, w->fmt);
 }
 
 }  // namespace
@@ -460,38 +815,10 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
     const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
-    if (x_is_bf16) x_to_f16_kernel<__nv_bfloat16><<<m, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, (int)w->k, perm);
-    else x_to_f16_kernel<float><<<m, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_x16, d_scale, (int)w->k, perm);
-    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
-    const void* d_x_bf16 = d_x16;
-    ldx = w->k;
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return fail(B200Q_ERR_INIT, "gemm: cuTensorMapEncodeTiled is not available from this driver");
-    int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
-    int tmem_cols = 32;
-    while (tmem_cols < bn) tmem_cols <<= 1;
-    CUtensorMap map;
-    cuuint64_t gdim[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
-    cuuint64_t gstr[1] = {(cuuint64_t)ldx * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(d_x_bf16), gdim, gstr, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    GemmArgs a{};
-    a.v = w->view; a.xscale = d_scale; a.y = d_y; a.ldy = ldy;
-    a.n_rows = (int)w->n_local; a.k = (int)w->k; a.m = m; a.bn = bn; a.tmem_cols = tmem_cols;
-    a.status = ctx->d_status;
-    dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
-    size_t smem = 1024 + (size_t)STAGES * (A_STAGE_BYTES + (size_t)bn * BK * 2) + (3 * STAGES + 1) * 8 + 16;
-    switch (w->fmt) {
-#define X(F) \
-    case F: return launch_fmt<F>(ctx, map, a, grid, smem);
-        B200Q_FOR_EACH_FMT(X)
-#undef X
-    }
-    return fail(B200Q_ERR_INVALID, "gemm: unknown format %d", w->fmt);
+    if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
+    else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
+    if (rc != B200Q_OK) return rc;
+    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, ldy, m, "gemm");
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -528,34 +855,9 @@ int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d
     float* d_scale = reinterpret_cast<float*>(static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device]) + NOALLOC_X16_BYTES);
     // nothing in the scratch has to start at zero: the conversion below rewrites every element the GEMM reads
     const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
-    x_to_f16_kernel<float><<<m, 256, 0, ctx->stream>>>(d_x, w->k, d_x16, d_scale, (int)w->k, perm);
-    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return fail(B200Q_ERR_INIT, "matmul_noalloc: cuTensorMapEncodeTiled is not available from this driver");
-    int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
-    int tmem_cols = 32;
-    while (tmem_cols < bn) tmem_cols <<= 1;
-    CUtensorMap map;
-    cuuint64_t gdim[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
-    cuuint64_t gstr[1] = {(cuuint64_t)w->k * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d_x16, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul_noalloc: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    GemmArgs a{};
-    a.v = w->view; a.xscale = d_scale; a.y = d_y; a.ldy = w->n_local;
-    a.n_rows = (int)w->n_local; a.k = (int)w->k; a.m = m; a.bn = bn; a.tmem_cols = tmem_cols;
-    a.status = ctx->d_status;
-    dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
-    size_t smem = 1024 + (size_t)STAGES * (A_STAGE_BYTES + (size_t)bn * BK * 2) + (3 * STAGES + 1) * 8 + 16;
-    switch (w->fmt) {
-#define X(F) \
-    case F: return launch_fmt<F>(ctx, map, a, grid, smem);
-        B200Q_FOR_EACH_FMT(X)
-#undef X
-    }
-    return fail(B200Q_ERR_INVALID, "matmul_noalloc: unknown format %d", w->fmt);
+    int rc = launch_x_to_f16(ctx, d_x, w->k, d_x16, d_scale, m, (int)w->k, perm);
+    if (rc != B200Q_OK) return rc;
+    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, w->n_local, m, "matmul_noalloc");
 }
 
 // Reads and clears the status word the tensor-core kernel raises when a bounded wait expires.

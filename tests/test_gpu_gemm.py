@@ -41,6 +41,21 @@ def test_smallest_tile_first(oracle):
     w.free()
 
 
+@pytest.mark.parametrize("k", [256, 512, 2048])
+def test_q4k_weights_in_tensor_memory_smallest(oracle, k):
+    """GGUF Q4_K with k % 256 == 0 takes the kernel whose weight operand lives in tensor memory: one CTA,
+    1 / 2 / 8 super-blocks per row (fewer, as many and more k-blocks than pipeline stages)."""
+    be = backend()
+    rng = synth.rng_for(3150 + k)
+    n, m = 128, 64
+    data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    assert rel_err(y, reference(oracle, synth.Q4_K, synth.GGUF, data, n, k, x)) <= TOL
+    w.free()
+
+
 @pytest.mark.parametrize("qt,lay", ALL_FMTS, ids=FMT_IDS)
 def test_every_format_ragged_tiles(oracle, qt, lay):
     """n and m are not tile multiples; k = 5 super-blocks."""
@@ -59,11 +74,13 @@ def test_every_format_ragged_tiles(oracle, qt, lay):
     w.free()
 
 
+@pytest.mark.parametrize("k", [896, 1024])
 @pytest.mark.parametrize("m", [9, 16, 17, 255, 256, 257, 512])
-def test_token_counts_around_the_tile_edges(oracle, m):
+def test_token_counts_around_the_tile_edges(oracle, m, k):
+    """k = 896 runs the shared-memory-operand kernel, k = 1024 the tensor-memory-operand one."""
     be = backend()
-    rng = synth.rng_for(3300 + m)
-    n, k = 256, 896
+    rng = synth.rng_for(3300 + m + k)
+    n = 256
     data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
     x = synth.gen_activations(m, k, rng)
     w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
