@@ -57,13 +57,17 @@ __device__ __forceinline__ void mma16816_z(float (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-// Shared-memory image of one product's activations, per 16-weight run R and activation row n:
-//   img[(R*m + n)*4 + {0,1}] : f16 hi parts of the 16 activations, in MMA order (4 per MMA)
-//   img[(R*m + n)*4 + {2,3}] : f16 lo parts
-//   ss[R*m + n]              : {power-of-two scale of the run, sum of its fp32 activations}
+// Shared-memory image of one product's activations. Activation row n is first scaled by a power of two so that
+// its largest magnitude lies in [256, 512); per 16-weight run R and activation row n:
+//   img[(R*m + n)*4 + {0,1}] : f16 hi parts of the 16 scaled activations, in MMA order (4 per MMA)
+//   img[(R*m + n)*4 + {2,3}] : f16 lo parts (scaled value minus hi)
+//   sum[R*m + n]             : sum of the run's activations times `sum_mul`, in the units of the accumulators
+//   fin[n]                   : factor that takes an accumulator back to real units (2^24 / the row's scale)
+// Runs that Q4_K multiplies with high nibbles (left in bits 4..7, i.e. 16 q) are stored divided by 16.
 struct XImg {
     uint4* img;
-    float2* ss;
+    float* sum;
+    float* fin;
 };
 
 // The first 32 bytes of the activation area stay zero: lanes that supply the zero columns of B read them.
@@ -72,38 +76,39 @@ constexpr int XZERO_BYTES = 32;
 __device__ __forceinline__ XImg ximg_carve(uint8_t* base, int k, int m) {
     XImg s;
     s.img = reinterpret_cast<uint4*>(base + XZERO_BYTES);
-    s.ss = reinterpret_cast<float2*>(base + XZERO_BYTES + (size_t)(k >> 4) * m * 64);
+    s.sum = reinterpret_cast<float*>(base + XZERO_BYTES + (size_t)(k >> 4) * m * 64);
+    s.fin = s.sum + (size_t)(k >> 4) * m;
     return s;
 }
 
-// Per-lane view of the B operand: lanes g == 2t (hi) and g == 2t+1 (lo) read the image of their run, every
-// other lane reads the zero region (stride 0), so the loads need no predicate.
-struct BLane {
-    const uint4* base;
-    int mult;   // 4 uint4 per (run, activation row) for data lanes, 0 for zero lanes
-};
-
-__device__ __forceinline__ BLane blane_make(const XImg& xs, uint8_t* xbase, int g, int t) {
-    BLane b;
-    bool active = (g >> 1) == t;
-    b.base = active ? xs.img + (g & 1) * 2 : reinterpret_cast<const uint4*>(xbase);
-    b.mult = active ? 4 : 0;
-    return b;
-}
-
-__device__ __forceinline__ void load_b(const BLane& bl, int run_row, uint4& b01, uint4& b23) {
-    const uint4* p = bl.base + run_row * bl.mult;
-    b01 = p[0];
-    b23 = p[1];
-}
-
-// x[m, k] (fp32, global) -> image. PERM: MMA j of a run takes elements (4j, 4j+2 | 4j+1, 4j+3), the pairs
-// the nibble masks produce from bytes (0,2) and (1,3); otherwise natural order.
-template <bool PERM>
-__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const XImg& s) {
+// x[m, k] (fp32, global) -> image. Q4: MMA j of a run takes elements (4j, 4j+2 | 4j+1, 4j+3), the pairs the
+// nibble masks produce from bytes (0,2) and (1,3), and high-nibble runs carry 1/16; otherwise natural order.
+// `red` is scratch for the row maxima (8 warps x up to 8 rows); the caller synchronises before and after.
+template <bool Q4>
+__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const XImg& s, float* red,
+                                       float sum_mul) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int n = 0; n < m; n++) {
+        const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)n * ldx);
+        float mx = 0.0f;
+        for (int i = threadIdx.x; i < (k >> 2); i += 256) {
+            const float4 f = __ldg(xr + i);
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(f.x), fabsf(f.y))), fmaxf(fabsf(f.z), fabsf(f.w)));
+        }
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        if (lane == 0) red[warp * 8 + n] = mx;
+    }
+    __syncthreads();
     const int total = (k >> 4) * m;
-    for (int q = threadIdx.x; q < total; q += blockDim.x) {
-        int R = q / m, n = q - R * m;
+    for (int q = threadIdx.x; q < total; q += 256) {
+        const int R = q / m, n = q - R * m;
+        float mx = red[n];
+#pragma unroll
+        for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w * 8 + n]);
+        int e = (int)((__float_as_uint(mx) >> 23) & 255u);
+        e = mx == 0.0f ? 127 : min(max(e, 9), 238);
+        const float sdown = __uint_as_float((uint32_t)(262 - e) << 23);   // 2^(135-e): the row's maximum lands in [256, 512)
+        const float run_mul = (Q4 && (R & 2)) ? sdown * 0.0625f : sdown;
         const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)R * 16);
         float v[16];
 #pragma unroll
@@ -111,19 +116,15 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
             float4 f = __ldg(xp + i);
             v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
         }
-        float mx = 0.0f, sum = 0.0f;
+        float sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 16; i++) { mx = fmaxf(mx, fabsf(v[i])); sum += v[i]; }
-        int e = (int)((__float_as_uint(mx) >> 23) & 255u);
-        e = mx == 0.0f ? 127 : min(max(e, 1), 253);
-        float sdown = __uint_as_float((uint32_t)(254 - e) << 23);   // 2^(127-e): the run lands in (-2, 2)
-        float sup = __uint_as_float((uint32_t)e << 23);
+        for (int i = 0; i < 16; i++) sum += v[i];
         __align__(16) __half h[16];
         __align__(16) __half l[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            int src = PERM ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;   // 0,2,1,3 inside each group of 4
-            float xs = v[src] * sdown;
+            const int src = Q4 ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;   // 0,2,1,3 inside each group of 4
+            const float xs = v[src] * run_mul;
             h[i] = __float2half_rn(xs);
             l[i] = __float2half_rn(xs - __half2float(h[i]));
         }
@@ -132,48 +133,20 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
         dst[1] = reinterpret_cast<uint4*>(h)[1];
         dst[2] = reinterpret_cast<uint4*>(l)[0];
         dst[3] = reinterpret_cast<uint4*>(l)[1];
-        s.ss[q] = make_float2(sup, sum);
+        s.sum[q] = sum * (sdown * (1.0f / 16777216.0f)) * sum_mul;
+        if (R == 0) s.fin[n] = __uint_as_float((uint32_t)(e + 16) << 23);   // 2^24 / sdown = 2^(e-111)
     }
-}
-
-// ------------------------------------------------------------------------------------------- Q4_K (GGUF)
-// A byte placed in an f16 lane is the subnormal byte * 2^-24: integer -> float without the integer pipe.
-__device__ __forceinline__ float2 bytes_as_f16x2(uint32_t bits) {
-    __half2 h;
-    *reinterpret_cast<uint32_t*>(&h) = bits;
-    return __half22float2(h);
-}
-
-// The block scales one thread needs from one super-block header of one weight row, multiplied out:
-// per 128-weight half, d*sc*2^24 (low-nibble sub-block), d*sc*2^20 (high-nibble sub-block) and dmin*m of both.
-struct Q4KHalfScales {
-    float dA, dB, nA, nB;
-};
-
-// sel picks the chunk of each half the thread owns: sub-blocks 2tp, 2tp+1 (half 0) and 4+2tp, 5+2tp (half 1).
-__device__ __forceinline__ void q4k_decode_hdr(uint4 h, uint32_t sel, Q4KHalfScales& h0, Q4KHalfScales& h1) {
-    float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
-    float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    uint32_t sc_lo = h.y & 0x3F3F3F3Fu, m_lo = h.z & 0x3F3F3F3Fu;
-    uint32_t sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-    uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-    // bytes {A of half 0, B of half 0, A of half 1, B of half 1}
-    uint32_t sc4 = __byte_perm(sc_lo, sc_hi, sel), m4 = __byte_perm(m_lo, m_hi, sel);
-    float2 s01 = bytes_as_f16x2(__byte_perm(sc4, 0, 0x4140)), s23 = bytes_as_f16x2(__byte_perm(sc4, 0, 0x4342));
-    float2 m01 = bytes_as_f16x2(__byte_perm(m4, 0, 0x4140)), m23 = bytes_as_f16x2(__byte_perm(m4, 0, 0x4342));
-    const float T24 = 16777216.0f;
-    float d48 = d * T24 * T24, d44 = d * T24 * 1048576.0f, dm24 = dmin * T24;
-    h0.dA = d48 * s01.x; h0.dB = d44 * s01.y; h0.nA = dm24 * m01.x; h0.nB = dm24 * m01.y;
-    h1.dA = d48 * s23.x; h1.dB = d44 * s23.y; h1.nA = dm24 * m23.x; h1.nB = dm24 * m23.y;
 }
 
 // ------------------------------------------------------------------------------------ weight streaming
 // Every warp streams its weights through a private ring in shared memory filled with cp.async (16 bytes
-// per thread and copy), `ring_d` items deep. An item is one 128-weight half of the warp's 16 rows; the
-// producer cursor runs ring_d items ahead of the consumer over a FLAT stream of (tile, half) items, so the
-// prefetch crosses tile boundaries and no load latency is exposed when a warp starts a new tile. No
-// registers are held for look-ahead. Slot layout (per warp): [row g / g+8][piece 0/1][lane] x 16 B of codes,
-// then [row][quad] x 16 B of block header written by the quad's first lane.
+// per thread and copy), `ring_d` items deep. An item is one 128-weight half of the warp's 16 rows together
+// with the block headers it needs; the producer cursor runs ring_d items ahead of the consumer over a FLAT
+// stream of (tile, half) items, so the prefetch crosses tile boundaries and no load latency is exposed when
+// a warp starts a new tile. No registers are held for look-ahead. Slot layout (per warp):
+// [row g / g+8][piece 0/1][lane] x 16 B of codes, then [row][quad] x 16 B of block header written by the
+// quad's first lane. Rows g and g+8 of a thread are a whole number of super-blocks apart, so one cursor plus
+// a constant byte distance serves both.
 constexpr int RING_DATA_BYTES = 2 * 2 * 32 * 16;
 constexpr int RING_HDR_BYTES = 2 * 8 * 16;
 constexpr int RING_SLOT_BYTES = RING_DATA_BYTES + RING_HDR_BYTES;   // 2304
@@ -194,55 +167,355 @@ __device__ __forceinline__ void cp_wait_keep(int keep) {   // wait until at most
     else asm volatile("cp.async.wait_group 1;" ::: "memory");
 }
 
-// ---- Q4_K: thread (g, t) owns, in every half and for rows g and g+8, bytes [16*(t&1), +16) of chunk (t>>1):
-// 16 weights of a low-nibble sub-block and 16 of the high-nibble sub-block.
-struct Q4KCursor {
-    const uint8_t* p;   // this thread's 16 bytes of the half the cursor is on
-    bool second;        // the half is the second half of its super-block
+// What a warp knows about the product segment it is working on.
+struct Seg {
+    int seg_b, seg_e;     // CTA tiles of this product owned by the CTA
+    int hb, he;           // 128-weight halves of every row owned by this warp (its k-part)
+    int rt_shift;         // log2 of the row tiles per CTA tile
+    int wrow;             // this warp's row tile inside a CTA tile
+    int tile0;            // first CTA tile of the product
+    int n_rows, nh;       // rows of the tensor, halves per row
 };
 
-__device__ __forceinline__ Q4KCursor q4k_cursor(const GOp& op, int64_t row, int h, int qoff) {
-    int64_t hs = ((row * op.k) >> 7) + h;
-    Q4KCursor c;
-    c.second = (hs & 1) != 0;
-    c.p = op.v.p[0] + (hs >> 1) * 144 + (c.second ? 64 : 0) + qoff;
-    return c;
+__device__ __forceinline__ int seg_row_base(const Seg& sg, int tile) { return (((tile - sg.tile0) << sg.rt_shift) + sg.wrow) * 16; }
+
+// ---- Q4_K cursor: thread (g, t) owns, in every half and for rows g and g+8, bytes [16*(t&1), +16) of chunk
+// (t>>1): 16 weights of a low-nibble sub-block and 16 of the high-nibble sub-block.
+struct Q4KCursor {
+    const uint8_t* p;   // this thread's 16 bytes of the half the cursor is on (row g)
+    int64_t d1;         // byte distance to the same piece of row g+8 (0 when that row is past the end)
+    int sec;            // 1 when the half is the second half of its super-block
+};
+
+__device__ __forceinline__ void q4k_seek(Q4KCursor& c, const uint8_t* base, const Seg& sg, int tile, int g, int qo) {
+    const int rb = seg_row_base(sg, tile) + g;
+    const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
+    const int64_t hs = r0 * sg.nh + sg.hb;
+    c.sec = (int)(hs & 1);
+    c.p = base + (hs >> 1) * 144 + 16 + c.sec * 64 + qo;
+    c.d1 = (rb + 8 <= sg.n_rows - 1) ? (int64_t)sg.nh * (4 * 144) : 0;
 }
-// copies the cursor's half (and the super-block header, by the quad's first lane, when the consumer will
-// need it: first half of a super-block or first item of a tile) into ring slot `slot`, row index i
-__device__ __forceinline__ void q4k_issue(Q4KCursor& c, uint32_t slot, int i, int lane, bool tile_start) {
-    cp_async16(slot + (i * 2) * 512 + lane * 16, c.p);
-    if ((lane & 3) == 0 && (tile_start || !c.second))
-        cp_async16(slot + RING_DATA_BYTES + (i * 8 + (lane >> 2)) * 16, c.p - 16 - (c.second ? 64 : 0));
-    c.p += c.second ? 80 : 64;
-    c.second = !c.second;
+// Copies the cursor's half of both rows (and, by the quad's first lane, the two super-block headers) into
+// the ring slot and steps to the next half.
+__device__ __forceinline__ void q4k_issue(Q4KCursor& c, uint32_t slot, int lane) {
+    cp_async16(slot + lane * 16, c.p);
+    cp_async16(slot + 1024 + lane * 16, c.p + c.d1);
+    if ((lane & 3) == 0) {
+        const uint8_t* h = c.p - 16 - c.sec * 64;
+        cp_async16(slot + RING_DATA_BYTES + (lane >> 2) * 16, h);
+        cp_async16(slot + RING_DATA_BYTES + 128 + (lane >> 2) * 16, h + c.d1);
+    }
+    c.p += 64 + c.sec * 16;
+    c.sec ^= 1;
 }
 
-// ---- Q6_K: thread (g, t) owns 16 bytes of ql (32-run a = t>>1 in the low nibbles, a+2 in the high nibbles,
-// 16-weight half lh = t&1 of each) and the matching 16 bytes of qh; header = 8 int8 scales + the f16 d pair.
+// ---- Q6_K cursor: thread (g, t) owns 16 bytes of ql (32-run a = t>>1 in the low nibbles, a+2 in the high
+// nibbles, 16-weight half lh = t&1 of each) and the matching 16 bytes of qh; header = 8 int8 scales + the
+// aligned 4 bytes that hold the f16 d of the block.
 struct Q6KCursor {
     const uint8_t *ql, *qh, *sc;
-    int hs;
+    int64_t hs;          // index of the half in the tensor's flat stream (row g)
+    int64_t dh;          // halves between row g and row g+8 (0 when that row is past the end)
 };
 
-__device__ __forceinline__ Q6KCursor q6k_cursor(const GOp& op, int64_t row, int h, int t) {
-    int64_t hs = ((row * op.k) >> 7) + h;
-    Q6KCursor c;
-    c.ql = op.v.p[0] + hs * 64 + (t >> 1) * 32 + (t & 1) * 16;
-    c.qh = op.v.p[1] + hs * 32 + (t & 1) * 16;
-    c.sc = op.v.p[2] + hs * 8;
-    c.hs = (int)hs;
-    return c;
+__device__ __forceinline__ void q6k_seek(Q6KCursor& c, const GOp& op, const Seg& sg, int tile, int g, int t) {
+    const int rb = seg_row_base(sg, tile) + g;
+    const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
+    c.hs = r0 * sg.nh + sg.hb;
+    c.ql = op.v.p[0] + c.hs * 64 + (t >> 1) * 32 + (t & 1) * 16;
+    c.qh = op.v.p[1] + c.hs * 32 + (t & 1) * 16;
+    c.sc = op.v.p[2] + c.hs * 8;
+    c.dh = (rb + 8 <= sg.n_rows - 1) ? (int64_t)sg.nh * 8 : 0;
 }
-__device__ __forceinline__ void q6k_issue(Q6KCursor& c, const uint8_t* dplane, uint32_t slot, int i, int lane) {
-    cp_async16(slot + (i * 2) * 512 + lane * 16, c.ql);
-    cp_async16(slot + (i * 2 + 1) * 512 + lane * 16, c.qh);
+__device__ __forceinline__ void q6k_issue(Q6KCursor& c, const uint8_t* dplane, uint32_t slot, int lane) {
+    cp_async16(slot + lane * 16, c.ql);
+    cp_async16(slot + 512 + lane * 16, c.qh);
+    cp_async16(slot + 1024 + lane * 16, c.ql + c.dh * 64);
+    cp_async16(slot + 1536 + lane * 16, c.qh + c.dh * 32);
     if ((lane & 3) == 0) {
-        uint32_t h = slot + RING_DATA_BYTES + (i * 8 + (lane >> 2)) * 16;
+        const uint32_t h = slot + RING_DATA_BYTES + (lane >> 2) * 16;
+        const uint8_t* dp = dplane + (c.hs & ~(int64_t)3);
         cp_async8(h, c.sc);
-        cp_async4(h + 8, dplane + ((c.hs >> 2) << 2));   // the 4 aligned bytes holding d of this block pair
+        cp_async4(h + 8, dp);
+        cp_async8(h + 128, c.sc + c.dh * 8);
+        cp_async4(h + 136, dp + c.dh);
     }
     c.ql += 64; c.qh += 32; c.sc += 8; c.hs += 1;
+}
+
+// Reduction of the k-parts of a tile through shared memory, or the direct store when a warp owns whole rows.
+template <int MT>
+__device__ __forceinline__ void finish_tile(float (&acc)[2][MT], const GOp& op, const Seg& sg, const XImg& xs, int tile, int m,
+                                            int kw, float* red, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int row_base = seg_row_base(sg, tile);
+    const bool live = row_base < sg.n_rows;
+#pragma unroll
+    for (int n = 0; n < MT; n++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {   // the four threads of a quad hold partial sums of the same two rows
+            float sacc = acc[i][n];
+            sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 1);
+            sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 2);
+            acc[i][n] = sacc;
+        }
+    }
+    if (kw > 1) {
+        if (t == 0) {
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                red[(warp * 16 + g) * MT + n] = acc[0][n];
+                red[(warp * 16 + g + 8) * MT + n] = acc[1][n];
+            }
+        }
+        __syncthreads();
+        if ((warp & (kw - 1)) == 0 && live) {
+            for (int o = lane; o < 16 * MT; o += 32) {
+                const int r = o / MT, n = o - r * MT;
+                float sacc = 0.f;
+                for (int j = 0; j < kw; j++) sacc += red[((warp + j) * 16 + r) * MT + n];
+                const int row = row_base + r;
+                if (row < sg.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = sacc * xs.fin[n];
+            }
+        }
+        __syncthreads();   // the reduction buffer is free again
+    } else if (live && t == 0) {
+#pragma unroll
+        for (int n = 0; n < MT; n++) {
+            if (n < m) {
+                const float f = xs.fin[n];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int row = row_base + g + 8 * i;
+                    if (row < sg.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n] * f;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------- Q4_K (GGUF)
+// One product segment, Q4_K. Per item and row: the two 6-bit scales and minima of the thread's chunk are cut
+// out of the 12 packed bytes (different bit positions in the first and second half of a super-block), the 64
+// codes become 16 A registers (one AND per pair of weights), 8 MMAs per activation row, and the block
+// scales are folded into the accumulator: acc += d * (scA * vA + scB * vB) - dmin * (mA * sumA + mB * sumB).
+template <int MT>
+__device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
+                                        int ring_d, int m, int kw, float* red) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * RING_SLOT_BYTES;
+    const int keep = ring_d - 1;
+    const int qo = tp * 32 + (t & 1) * 16;
+    const int sh16 = tp * 16;
+    const bool has_items = sg.hb < sg.he;
+    // B operand: lanes g == 2t (hi) and g == 2t+1 (lo) read the image of their run, all other lanes the zero
+    // region (stride 0), so the loads need no predicate
+    const bool active = (g >> 1) == t;
+    const uint4* bbase = active ? xs.img + (g & 1) * 2 + (4 * tp + (t & 1)) * m * 4 : reinterpret_cast<const uint4*>(xzero);
+    const int bstep = active ? 8 * m * 4 : 0;       // uint4 per half
+    const int bhigh = active ? 2 * m * 4 : 0;       // from the low-nibble run to the high-nibble run
+    const int bn = active ? 4 : 0;                  // per activation row
+    const float* sbase = xs.sum + (4 * tp + (t & 1)) * m;
+
+    // ---- producer
+    Q4KCursor cur{};
+    int pt = sg.seg_b, ph = sg.hb;
+    uint32_t pslot = ring;
+    if (has_items && pt < sg.seg_e) q4k_seek(cur, op.v.p[0], sg, pt, g, qo);
+    auto issue_next = [&]() {
+        if (has_items && pt < sg.seg_e) {
+            q4k_issue(cur, pslot, lane);
+            if (++ph == sg.he) {
+                ph = sg.hb;
+                if (++pt < sg.seg_e) q4k_seek(cur, op.v.p[0], sg, pt, g, qo);
+            }
+        }
+        cp_commit();
+        pslot += RING_SLOT_BYTES;
+        if (pslot == ring_end) pslot = ring;
+    };
+    for (int d = 0; d < ring_d; d++) issue_next();
+    const uint8_t* cslot = ring_gen;
+    const uint8_t* cend = ring_gen + ring_d * RING_SLOT_BYTES;
+
+    for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
+        float acc[2][MT];
+#pragma unroll
+        for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+        const int64_t r0 = min((int64_t)seg_row_base(sg, tile) + g, (int64_t)sg.n_rows - 1);
+        int csec = (int)((r0 * sg.nh + sg.hb) & 1);
+        const uint4* bp = bbase + sg.hb * bstep;
+        const float* sp = sbase + sg.hb * 8 * m;
+        for (int h = sg.hb; h < sg.he; h++) {
+            cp_wait_keep(keep);
+            __syncwarp();   // the quad leader's header copies are visible to its quad
+            const uint4* sd = reinterpret_cast<const uint4*>(cslot);
+            const uint4* sh = reinterpret_cast<const uint4*>(cslot + RING_DATA_BYTES);
+            const uint4 wa = sd[lane], wb = sd[64 + lane];
+            const uint4 hd[2] = {sh[g], sh[8 + g]};
+            const uint32_t MA = csec ? 0x0F0Fu : 0x3F3Fu, MB = csec ? 0x3030u : 0u;
+            float dd[2], dmn[2], scA[2], scB[2], mnA[2], mnB[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&hd[i].x));
+                dd[i] = df.x; dmn[i] = -df.y;
+                const uint32_t y1 = hd[i].y >> sh16, z1 = hd[i].z >> sh16, w1 = hd[i].w >> sh16;
+                const uint32_t scp = ((csec ? w1 : y1) & MA) | ((y1 >> 2) & MB);
+                const uint32_t mp = ((csec ? (w1 >> 4) : z1) & MA) | ((z1 >> 2) & MB);
+                scA[i] = (float)(scp & 0xFFu); scB[i] = (float)(scp >> 8);
+                mnA[i] = (float)(mp & 0xFFu); mnB[i] = (float)(mp >> 8);
+            }
+            const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
+            const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
+            const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
+            uint32_t s0[4], s1[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                if (n < m) {
+                    float cA[4], cB[4];
+                    const uint4* bq = bp + n * bn;
+                    uint4 b01 = bq[0], b23 = bq[1];
+                    mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
+                    mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
+                    mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
+                    mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
+                    b01 = bq[bhigh]; b23 = bq[bhigh + 1];
+                    mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
+                    mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
+                    mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
+                    mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
+                    const float sa = sp[n], sb = sp[2 * m + n];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
+                        const float u = fmaf(scB[i], vb, scA[i] * va);
+                        const float mn = fmaf(mnB[i], sb, mnA[i] * sa);
+                        acc[i][n] = fmaf(dmn[i], mn, fmaf(dd[i], u, acc[i][n]));
+                    }
+                }
+            }
+            csec ^= 1;
+            bp += bstep;
+            sp += 8 * m;
+            __syncwarp();   // every lane has read the slot before it is refilled
+            issue_next();
+            cslot += RING_SLOT_BYTES;
+            if (cslot == cend) cslot = ring_gen;
+        }
+        finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
+    }
+    // drain: nothing of this product's ring may still be in flight when the next product reuses it
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------- Q6_K (GGUF)
+// One product segment, Q6_K: acc += d * sc * (sum q x - 32 sum x) per 16-weight run (the activation image
+// stores 32 sum x).
+template <int MT>
+__device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
+                                        int ring_d, int m, int kw, float* red) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * RING_SLOT_BYTES;
+    const int keep = ring_d - 1;
+    const int a6 = t >> 1, lh6 = t & 1, shl6 = 4 - 2 * a6, shr6 = 2 * a6;
+    const int scsh = 16 * a6 + 8 * lh6;   // bit position of scale 2a+lh inside its word of four
+    const bool has_items = sg.hb < sg.he;
+    const bool active = (g >> 1) == t;
+    const uint4* bbase = active ? xs.img + (g & 1) * 2 + (2 * a6 + lh6) * m * 4 : reinterpret_cast<const uint4*>(xzero);
+    const int bstep = active ? 8 * m * 4 : 0;
+    const int bhigh = active ? 4 * m * 4 : 0;
+    const int bn = active ? 4 : 0;
+    const float* sbase = xs.sum + (2 * a6 + lh6) * m;
+
+    Q6KCursor cur{};
+    int pt = sg.seg_b, ph = sg.hb;
+    uint32_t pslot = ring;
+    if (has_items && pt < sg.seg_e) q6k_seek(cur, op, sg, pt, g, t);
+    auto issue_next = [&]() {
+        if (has_items && pt < sg.seg_e) {
+            q6k_issue(cur, op.v.p[3], pslot, lane);
+            if (++ph == sg.he) {
+                ph = sg.hb;
+                if (++pt < sg.seg_e) q6k_seek(cur, op, sg, pt, g, t);
+            }
+        }
+        cp_commit();
+        pslot += RING_SLOT_BYTES;
+        if (pslot == ring_end) pslot = ring;
+    };
+    for (int d = 0; d < ring_d; d++) issue_next();
+    const uint8_t* cslot = ring_gen;
+    const uint8_t* cend = ring_gen + ring_d * RING_SLOT_BYTES;
+
+    for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
+        float acc[2][MT];
+#pragma unroll
+        for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+        const int64_t r0 = min((int64_t)seg_row_base(sg, tile) + g, (int64_t)sg.n_rows - 1);
+        int chs = (int)((r0 * sg.nh + sg.hb) & 3);   // bit 1: which f16 of the copied d pair
+        const uint4* bp = bbase + sg.hb * bstep;
+        const float* sp = sbase + sg.hb * 8 * m;
+        for (int h = sg.hb; h < sg.he; h++) {
+            cp_wait_keep(keep);
+            __syncwarp();
+            const uint4* sd = reinterpret_cast<const uint4*>(cslot);
+            const uint4* sh = reinterpret_cast<const uint4*>(cslot + RING_DATA_BYTES);
+            uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
+            float dL[2], dH[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint4 qlv = sd[(i * 2) * 32 + lane], qhv = sd[(i * 2 + 1) * 32 + lane];
+                const uint4 hd = sh[i * 8 + g];   // x,y: eight int8 scales of the half; z: f16 d of two blocks
+                const uint32_t ql[4] = {qlv.x, qlv.y, qlv.z, qlv.w};
+                const uint32_t qh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t cl = (ql[j] & 0x0F0F0F0Fu) | ((qh[j] << shl6) & 0x30303030u);          // 32-run a
+                    const uint32_t ch = ((ql[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> shr6) & 0x30303030u);   // 32-run a+2
+                    aL[i][j][0] = __byte_perm(cl, 0, 0x4140); aL[i][j][1] = __byte_perm(cl, 0, 0x4342);
+                    aH[i][j][0] = __byte_perm(ch, 0, 0x4140); aH[i][j][1] = __byte_perm(ch, 0, 0x4342);
+                }
+                const uint32_t dbits = (chs & 2) ? (hd.z >> 16) : (hd.z & 0xFFFFu);
+                const float d = __half2float(__ushort_as_half((unsigned short)dbits));
+                dL[i] = d * (float)(int)(int8_t)((hd.x >> scsh) & 0xFFu);    // scale 2a+lh (low run)
+                dH[i] = d * (float)(int)(int8_t)((hd.y >> scsh) & 0xFFu);    // scale 2a+4+lh (high run)
+            }
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                if (n < m) {
+                    float cL[4], cH[4];
+                    const uint4* bq = bp + n * bn;
+                    uint4 b01 = bq[0], b23 = bq[1];
+                    mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
+                    mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
+                    mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
+                    mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
+                    b01 = bq[bhigh]; b23 = bq[bhigh + 1];
+                    mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
+                    mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
+                    mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
+                    mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
+                    const float s32l = sp[n], s32h = sp[4 * m + n];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const float vl = cL[2 * i] + cL[2 * i + 1] - s32l, vh = cH[2 * i] + cH[2 * i + 1] - s32h;
+                        acc[i][n] = fmaf(dH[i], vh, fmaf(dL[i], vl, acc[i][n]));
+                    }
+                }
+            }
+            chs++;
+            bp += bstep;
+            sp += 8 * m;
+            __syncwarp();
+            issue_next();
+            cslot += RING_SLOT_BYTES;
+            if (cslot == cend) cslot = ring_gen;
+        }
+        finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------------------------- kernel
@@ -252,9 +525,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
                 int ring_d) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* red = reinterpret_cast<float*>(smem);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
+    const int warp = threadIdx.x >> 5;
     uint8_t* ring_gen = smem + RED_FLOATS * sizeof(float) + warp * ring_d * RING_SLOT_BYTES;
-    const uint32_t ring = smem_addr(ring_gen);
     uint8_t* xbase = smem + RED_FLOATS * sizeof(float) + 8 * ring_d * RING_SLOT_BYTES;
     int tb, te;
     if (ranges) {
@@ -274,10 +546,6 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         opi = lo;
     }
     if (threadIdx.x < XZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xbase)[threadIdx.x] = 0u;   // published by the first barrier
-    const int qoff = 16 + tp * 32 + (t & 1) * 16;        // Q4_K: this thread's 16 bytes inside the first chunk pair
-    const uint32_t sel = tp ? 0x7632u : 0x5410u;         // Q4_K: which scale bytes of a header belong to this thread
-    const int a6 = t >> 1, lh6 = t & 1, shl6 = 4 - 2 * a6, shr6 = 2 * a6;   // Q6_K
-    const int keep = ring_d - 1;
 
     for (int seg_b = tb; seg_b < te;) {
         // ---- one product: tiles [seg_b, seg_e) of this CTA belong to it
@@ -287,210 +555,25 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
             op = ops[opi];
         }
         const int seg_e = min(te, op.tile0 + op.ntiles);
-        __syncthreads();   // everyone is done with the previous product's activations
+        __syncthreads();   // everyone is done with the previous product's activations and the reduction scratch
         XImg xs = ximg_carve(xbase, op.k, m);
-        BLane bl = blane_make(xs, xbase, g, t);
         const bool q4 = op.fmt == F_Q4K;
-        if (q4) prep_x<true>(op.x, op.ldx, op.k, m, xs);
-        else prep_x<false>(op.x, op.ldx, op.k, m, xs);
+        if (q4) prep_x<true>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
+        else prep_x<false>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
         __syncthreads();
 
-        const int kw = 1 << op.kw_log2, rt = 8 >> op.kw_log2;
+        const int kw = 1 << op.kw_log2;
         const int kpart = warp & (kw - 1);
         const int nh = op.k >> 7, per = (nh + kw - 1) >> op.kw_log2;
-        const int hb = kpart * per, he = min(nh, (kpart + 1) * per);
-        const bool has_items = hb < he;
-        auto row_of = [&](int tile, int i) -> int64_t {
-            return min(((int64_t)(tile - op.tile0) * rt + (warp >> op.kw_log2)) * 16 + g + 8 * i, (int64_t)op.n_rows - 1);
-        };
-
-        // ---- producer cursor over the flat (tile, half) stream
-        int pt = seg_b, ph = hb, pslot = 0;
-        Q4KCursor c4[2] = {};
-        Q6KCursor c6[2] = {};
-        auto cursor_init = [&]() {
-            if (q4) { c4[0] = q4k_cursor(op, row_of(pt, 0), ph, qoff); c4[1] = q4k_cursor(op, row_of(pt, 1), ph, qoff); }
-            else { c6[0] = q6k_cursor(op, row_of(pt, 0), ph, t); c6[1] = q6k_cursor(op, row_of(pt, 1), ph, t); }
-        };
-        auto issue_next = [&]() {
-            if (has_items && pt < seg_e) {
-                const uint32_t slot = ring + pslot * RING_SLOT_BYTES;
-                if (q4) { q4k_issue(c4[0], slot, 0, lane, ph == hb); q4k_issue(c4[1], slot, 1, lane, ph == hb); }
-                else { q6k_issue(c6[0], op.v.p[3], slot, 0, lane); q6k_issue(c6[1], op.v.p[3], slot, 1, lane); }
-                if (++ph == he) {
-                    ph = hb;
-                    if (++pt < seg_e) cursor_init();
-                }
-            }
-            cp_commit();
-            pslot = pslot + 1 == ring_d ? 0 : pslot + 1;
-        };
-        if (has_items && pt < seg_e) cursor_init();
-        for (int d = 0; d < ring_d; d++) issue_next();
-        int cslot = 0;
-
-        for (int tile = seg_b; tile < seg_e; tile++) {
-            const int rtile = (tile - op.tile0) * rt + (warp >> op.kw_log2);
-            const bool live = (int64_t)rtile * 16 < op.n_rows;
-            float acc[2][MT];
-#pragma unroll
-            for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
-            // stream index of the current half of each row (its parity = position inside the super-block)
-            int hs_c[2];
-#pragma unroll
-            for (int i = 0; i < 2; i++) hs_c[i] = (int)(((row_of(tile, i) * op.k) >> 7) + hb);
-            Q4KHalfScales cur[2], nxt[2];
-            for (int h = hb; h < he; h++) {
-                cp_wait_keep(keep);
-                __syncwarp();   // the quad leader's header copy is visible to its quad
-                const uint8_t* slot = ring_gen + cslot * RING_SLOT_BYTES;
-                const uint4* sd = reinterpret_cast<const uint4*>(slot);
-                const uint4* sh = reinterpret_cast<const uint4*>(slot + RING_DATA_BYTES);
-                if (q4) {
-                    const uint4 wa = sd[lane], wb = sd[64 + lane];
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const bool second = (hs_c[i] & 1) != 0;
-                        if (h == hb || !second) {
-                            Q4KHalfScales h0, h1;
-                            q4k_decode_hdr(sh[i * 8 + g], sel, h0, h1);
-                            cur[i] = second ? h1 : h0;
-                            nxt[i] = h1;
-                        } else {
-                            cur[i] = nxt[i];
-                        }
-                    }
-                    const uint32_t ML = 0x000F000Fu, MH = 0x00F000F0u;
-                    const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
-                    const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
-                    uint32_t s0[4], s1[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
-                    const int RA = 8 * h + 4 * tp + (t & 1);   // run of the low-nibble weights; high nibbles: RA + 2
-#pragma unroll
-                    for (int n = 0; n < MT; n++) {
-                        if (n < m) {
-                            uint4 b01, b23;
-                            float cA[4], cB[4];
-                            load_b(bl, RA * m + n, b01, b23);
-                            mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
-                            mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
-                            mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
-                            mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
-                            load_b(bl, (RA + 2) * m + n, b01, b23);
-                            mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
-                            mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
-                            mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
-                            mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
-                            const float2 sa = xs.ss[RA * m + n], sb = xs.ss[(RA + 2) * m + n];
-#pragma unroll
-                            for (int i = 0; i < 2; i++) {
-                                const float va = cA[2 * i] + cA[2 * i + 1], vb = cB[2 * i] + cB[2 * i + 1];   // hi + lo columns
-                                acc[i][n] += va * (cur[i].dA * sa.x) - cur[i].nA * sa.y + vb * (cur[i].dB * sb.x) - cur[i].nB * sb.y;
-                            }
-                        }
-                    }
-                } else {
-                    uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
-                    float dL[2], dH[2];
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        const uint4 qlv = sd[(i * 2) * 32 + lane], qhv = sd[(i * 2 + 1) * 32 + lane];
-                        const uint4 hd = sh[i * 8 + g];   // x,y: eight int8 scales of the half; z: f16 d of two blocks
-                        const uint32_t ql[4] = {qlv.x, qlv.y, qlv.z, qlv.w};
-                        const uint32_t qh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint32_t cl = (ql[j] & 0x0F0F0F0Fu) | ((qh[j] << shl6) & 0x30303030u);          // 32-run a
-                            uint32_t ch = ((ql[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> shr6) & 0x30303030u);   // 32-run a+2
-                            aL[i][j][0] = __byte_perm(cl, 0, 0x4140); aL[i][j][1] = __byte_perm(cl, 0, 0x4342);
-                            aH[i][j][0] = __byte_perm(ch, 0, 0x4140); aH[i][j][1] = __byte_perm(ch, 0, 0x4342);
-                        }
-                        // block = hs >> 1 picks the f16 d inside the copied pair
-                        const uint32_t dbits = (hs_c[i] & 2) ? (hd.z >> 16) : (hd.z & 0xFFFFu);
-                        const float d24 = __half2float(__ushort_as_half((unsigned short)dbits)) * 16777216.0f;
-                        const uint32_t scw = a6 ? hd.x >> 16 : hd.x;     // scales 2a+lh (low run) ...
-                        const uint32_t scw2 = a6 ? hd.y >> 16 : hd.y;    // ... and 2a+4+lh (high run)
-                        dL[i] = d24 * (float)(int)(int8_t)((scw >> (8 * lh6)) & 0xFFu);
-                        dH[i] = d24 * (float)(int)(int8_t)((scw2 >> (8 * lh6)) & 0xFFu);
-                    }
-                    const int RL = 8 * h + 2 * a6 + lh6;   // run of the low-nibble codes; high nibbles: RL + 4
-#pragma unroll
-                    for (int n = 0; n < MT; n++) {
-                        if (n < m) {
-                            uint4 b01, b23;
-                            float cL[4], cH[4];
-                            load_b(bl, RL * m + n, b01, b23);
-                            mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
-                            mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
-                            mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
-                            mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
-                            load_b(bl, (RL + 4) * m + n, b01, b23);
-                            mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
-                            mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
-                            mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
-                            mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
-                            const float2 sl = xs.ss[RL * m + n], sh2 = xs.ss[(RL + 4) * m + n];
-                            const float k32 = 32.0f / 16777216.0f;
-#pragma unroll
-                            for (int i = 0; i < 2; i++) {
-                                const float vl = cL[2 * i] + cL[2 * i + 1], vh = cH[2 * i] + cH[2 * i + 1];
-                                // d * sc * (sum q x - 32 sum x)
-                                acc[i][n] += dL[i] * (vl * sl.x - k32 * sl.y) + dH[i] * (vh * sh2.x - k32 * sh2.y);
-                            }
-                        }
-                    }
-                }
-                hs_c[0]++; hs_c[1]++;
-                __syncwarp();   // every lane has read the slot before it is refilled
-                issue_next();
-                cslot = cslot + 1 == ring_d ? 0 : cslot + 1;
-            }
-            // the four threads of a quad hold partial sums of the same two rows
-#pragma unroll
-            for (int n = 0; n < MT; n++) {
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    float sacc = acc[i][n];
-                    sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 1);
-                    sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, 2);
-                    acc[i][n] = sacc;
-                }
-            }
-            if (kw > 1) {
-                if (t == 0) {
-#pragma unroll
-                    for (int n = 0; n < MT; n++) {
-                        red[(warp * 16 + g) * MT + n] = acc[0][n];
-                        red[(warp * 16 + g + 8) * MT + n] = acc[1][n];
-                    }
-                }
-                __syncthreads();
-                if (kpart == 0 && live) {
-                    for (int o = lane; o < 16 * MT; o += 32) {
-                        int r = o / MT, n = o - r * MT;
-                        float sacc = 0.f;
-                        for (int j = 0; j < kw; j++) sacc += red[((warp + j) * 16 + r) * MT + n];
-                        int64_t row = (int64_t)rtile * 16 + r;
-                        if (row < op.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = sacc;
-                    }
-                }
-                __syncthreads();   // the reduction buffer is free again
-            } else if (live && t == 0) {
-#pragma unroll
-                for (int n = 0; n < MT; n++) {
-                    if (n < m) {
-#pragma unroll
-                        for (int i = 0; i < 2; i++) {
-                            int64_t row = (int64_t)rtile * 16 + g + 8 * i;
-                            if (row < op.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n];
-                        }
-                    }
-                }
-            }
-        }
-        // drain: nothing of this product's ring may still be in flight when the next product reuses it
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        Seg sg;
+        sg.seg_b = seg_b; sg.seg_e = seg_e;
+        sg.hb = kpart * per; sg.he = min(nh, (kpart + 1) * per);
+        sg.rt_shift = 3 - op.kw_log2;
+        sg.wrow = warp >> op.kw_log2;
+        sg.tile0 = op.tile0;
+        sg.n_rows = op.n_rows; sg.nh = nh;
+        if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
+        else run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
         seg_b = seg_e;
     }
 }
