@@ -38,6 +38,7 @@ namespace {
 
 constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
+constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 constexpr int RED_FLOATS = 8 * 16 * 8;   // 8 warps x 16 rows x up to 8 activation rows
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -81,10 +82,11 @@ __device__ __forceinline__ XImg ximg_carve(uint8_t* base, int k, int m) {
     return s;
 }
 
-// x[m, k] (fp32, global) -> image. Q4: MMA j of a run takes elements (4j, 4j+2 | 4j+1, 4j+3), the pairs the
-// nibble masks produce from bytes (0,2) and (1,3), and high-nibble runs carry 1/16; otherwise natural order.
+// x[m, k] (fp32, global) -> image. MODE 1 (Q4_K) and 2 (MXFP4): MMA j of a run takes elements
+// (4j, 4j+2 | 4j+1, 4j+3), the pairs the nibble masks produce from bytes (0,2) and (1,3); MODE 1 also stores
+// the runs that meet high nibbles divided by 16. MODE 0 (Q6_K): natural order.
 // `red` is scratch for the row maxima (8 warps x up to 8 rows); the caller synchronises before and after.
-template <bool Q4>
+template <int MODE>
 __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const XImg& s, float* red,
                                        float sum_mul) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,7 +110,7 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
         int e = (int)((__float_as_uint(mx) >> 23) & 255u);
         e = mx == 0.0f ? 127 : min(max(e, 9), 238);
         const float sdown = __uint_as_float((uint32_t)(262 - e) << 23);   // 2^(135-e): the row's maximum lands in [256, 512)
-        const float run_mul = (Q4 && (R & 2)) ? sdown * 0.0625f : sdown;
+        const float run_mul = (MODE == 1 && (R & 2)) ? sdown * 0.0625f : sdown;
         const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)R * 16);
         float v[16];
 #pragma unroll
@@ -123,7 +125,7 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
         __align__(16) __half l[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            const int src = Q4 ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;   // 0,2,1,3 inside each group of 4
+            const int src = MODE != 0 ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;   // 0,2,1,3 inside each group of 4
             const float xs = v[src] * run_mul;
             h[i] = __float2half_rn(xs);
             l[i] = __float2half_rn(xs - __half2float(h[i]));
@@ -147,9 +149,14 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
 // [row g / g+8][piece 0/1][lane] x 16 B of codes, then [row][quad] x 16 B of block header written by the
 // quad's first lane. Rows g and g+8 of a thread are a whole number of super-blocks apart, so one cursor plus
 // a constant byte distance serves both.
-constexpr int RING_DATA_BYTES = 2 * 2 * 32 * 16;
+// Q6_K slots hold two pieces (ql, qh) per row, Q4_K slots one, so a warp's ring (ring_d units of
+// RING_UNIT_BYTES) is ring_d items deep for Q6_K and 2 * ring_d items deep for Q4_K: about 9 KB of weights
+// in flight per warp either way, which is what hides the HBM latency.
 constexpr int RING_HDR_BYTES = 2 * 8 * 16;
-constexpr int RING_SLOT_BYTES = RING_DATA_BYTES + RING_HDR_BYTES;   // 2304
+constexpr int Q6K_DATA_BYTES = 2 * 2 * 32 * 16, Q6K_SLOT_BYTES = Q6K_DATA_BYTES + RING_HDR_BYTES;   // 2304
+constexpr int Q4K_DATA_BYTES = 2 * 32 * 16, Q4K_SLOT_BYTES = Q4K_DATA_BYTES + RING_HDR_BYTES;       // 1280
+constexpr int RING_UNIT_BYTES = 2 * Q4K_SLOT_BYTES;                                                // 2560 >= 2304
+constexpr int MX4_DATA_BYTES = 2 * 32 * 16, MX4_SLOT_BYTES = MX4_DATA_BYTES + 2 * 8 * 4;           // 1088
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -163,7 +170,8 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_wait_keep(int keep) {   // wait until at most `keep` groups are pending
-    if (keep >= 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+    if (keep >= 7) asm volatile("cp.async.wait_group 7;" ::: "memory");
+    else if (keep >= 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
     else asm volatile("cp.async.wait_group 1;" ::: "memory");
 }
 
@@ -199,11 +207,11 @@ __device__ __forceinline__ void q4k_seek(Q4KCursor& c, const uint8_t* base, cons
 // the ring slot and steps to the next half.
 __device__ __forceinline__ void q4k_issue(Q4KCursor& c, uint32_t slot, int lane) {
     cp_async16(slot + lane * 16, c.p);
-    cp_async16(slot + 1024 + lane * 16, c.p + c.d1);
+    cp_async16(slot + 512 + lane * 16, c.p + c.d1);
     if ((lane & 3) == 0) {
         const uint8_t* h = c.p - 16 - c.sec * 64;
-        cp_async16(slot + RING_DATA_BYTES + (lane >> 2) * 16, h);
-        cp_async16(slot + RING_DATA_BYTES + 128 + (lane >> 2) * 16, h + c.d1);
+        cp_async16(slot + Q4K_DATA_BYTES + (lane >> 2) * 16, h);
+        cp_async16(slot + Q4K_DATA_BYTES + 128 + (lane >> 2) * 16, h + c.d1);
     }
     c.p += 64 + c.sec * 16;
     c.sec ^= 1;
@@ -233,7 +241,7 @@ __device__ __forceinline__ void q6k_issue(Q6KCursor& c, const uint8_t* dplane, u
     cp_async16(slot + 1024 + lane * 16, c.ql + c.dh * 64);
     cp_async16(slot + 1536 + lane * 16, c.qh + c.dh * 32);
     if ((lane & 3) == 0) {
-        const uint32_t h = slot + RING_DATA_BYTES + (lane >> 2) * 16;
+        const uint32_t h = slot + Q6K_DATA_BYTES + (lane >> 2) * 16;
         const uint8_t* dp = dplane + (c.hs & ~(int64_t)3);
         cp_async8(h, c.sc);
         cp_async4(h + 8, dp);
@@ -303,8 +311,9 @@ template <int MT>
 __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
                                         int ring_d, int m, int kw, float* red) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
-    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * RING_SLOT_BYTES;
-    const int keep = ring_d - 1;
+    const int depth = 2 * ring_d;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * Q4K_SLOT_BYTES;
+    const int keep = depth - 1;
     const int qo = tp * 32 + (t & 1) * 16;
     const int sh16 = tp * 16;
     const bool has_items = sg.hb < sg.he;
@@ -331,12 +340,12 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             }
         }
         cp_commit();
-        pslot += RING_SLOT_BYTES;
+        pslot += Q4K_SLOT_BYTES;
         if (pslot == ring_end) pslot = ring;
     };
-    for (int d = 0; d < ring_d; d++) issue_next();
+    for (int d = 0; d < depth; d++) issue_next();
     const uint8_t* cslot = ring_gen;
-    const uint8_t* cend = ring_gen + ring_d * RING_SLOT_BYTES;
+    const uint8_t* cend = ring_gen + depth * Q4K_SLOT_BYTES;
 
     for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
         float acc[2][MT];
@@ -350,8 +359,8 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             cp_wait_keep(keep);
             __syncwarp();   // the quad leader's header copies are visible to its quad
             const uint4* sd = reinterpret_cast<const uint4*>(cslot);
-            const uint4* sh = reinterpret_cast<const uint4*>(cslot + RING_DATA_BYTES);
-            const uint4 wa = sd[lane], wb = sd[64 + lane];
+            const uint4* sh = reinterpret_cast<const uint4*>(cslot + Q4K_DATA_BYTES);
+            const uint4 wa = sd[lane], wb = sd[32 + lane];
             const uint4 hd[2] = {sh[g], sh[8 + g]};
             const uint32_t MA = csec ? 0x0F0Fu : 0x3F3Fu, MB = csec ? 0x3030u : 0u;
             float dd[2], dmn[2], scA[2], scB[2], mnA[2], mnB[2];
@@ -401,7 +410,7 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             sp += 8 * m;
             __syncwarp();   // every lane has read the slot before it is refilled
             issue_next();
-            cslot += RING_SLOT_BYTES;
+            cslot += Q4K_SLOT_BYTES;
             if (cslot == cend) cslot = ring_gen;
         }
         finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
@@ -417,7 +426,7 @@ template <int MT>
 __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
                                         int ring_d, int m, int kw, float* red) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * RING_SLOT_BYTES;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * Q6K_SLOT_BYTES;
     const int keep = ring_d - 1;
     const int a6 = t >> 1, lh6 = t & 1, shl6 = 4 - 2 * a6, shr6 = 2 * a6;
     const int scsh = 16 * a6 + 8 * lh6;   // bit position of scale 2a+lh inside its word of four
@@ -442,12 +451,12 @@ __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg
             }
         }
         cp_commit();
-        pslot += RING_SLOT_BYTES;
+        pslot += Q6K_SLOT_BYTES;
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < ring_d; d++) issue_next();
     const uint8_t* cslot = ring_gen;
-    const uint8_t* cend = ring_gen + ring_d * RING_SLOT_BYTES;
+    const uint8_t* cend = ring_gen + ring_d * Q6K_SLOT_BYTES;
 
     for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
         float acc[2][MT];
@@ -461,7 +470,7 @@ __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg
             cp_wait_keep(keep);
             __syncwarp();
             const uint4* sd = reinterpret_cast<const uint4*>(cslot);
-            const uint4* sh = reinterpret_cast<const uint4*>(cslot + RING_DATA_BYTES);
+            const uint4* sh = reinterpret_cast<const uint4*>(cslot + Q6K_DATA_BYTES);
             uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][pair] f16x2 codes * 2^-24
             float dL[2], dH[2];
 #pragma unroll
@@ -510,7 +519,137 @@ __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg
             sp += 8 * m;
             __syncwarp();
             issue_next();
-            cslot += RING_SLOT_BYTES;
+            cslot += Q6K_SLOT_BYTES;
+            if (cslot == cend) cslot = ring_gen;
+        }
+        finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------ MXFP4 (GGUF)
+// Blocks of 32: one E8M0 exponent byte (plane 0) and 16 code bytes (plane 1), byte i = element i in the low
+// nibble and element i+16 in the high nibble. An E2M1 code s|ee|m is itself a tiny float: placed at bits
+// 15|11..9 of an f16 lane it is exactly value * 2^-14 (ee = 0 lands in the f16 subnormals, as E2M1 demands),
+// so codes go to the tensor cores after two ANDs and two shift-adds per pair, and the block scale
+// 2^(e-127) * 2^14 is applied once per 32 weights. Thread (g, t) owns block t of the half for rows g, g+8:
+// its low nibbles are 16-weight run 2t, its high nibbles run 2t+1.
+struct MX4Cursor {
+    const uint8_t *q, *e;   // this thread's 16 code bytes; the four exponents of the half (row g)
+    int64_t dq, de;         // byte distances to row g+8 (0 when that row is past the end)
+};
+
+__device__ __forceinline__ void mx4_seek(MX4Cursor& c, const GOp& op, const Seg& sg, int tile, int g, int t) {
+    const int rb = seg_row_base(sg, tile) + g;
+    const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
+    const int64_t hs = r0 * sg.nh + sg.hb;
+    c.q = op.v.p[1] + hs * 64 + t * 16;
+    c.e = op.v.p[0] + hs * 4;
+    const bool two = rb + 8 <= sg.n_rows - 1;
+    c.dq = two ? (int64_t)sg.nh * 8 * 64 : 0;
+    c.de = two ? (int64_t)sg.nh * 8 * 4 : 0;
+}
+__device__ __forceinline__ void mx4_issue(MX4Cursor& c, uint32_t slot, int lane) {
+    cp_async16(slot + lane * 16, c.q);
+    cp_async16(slot + 512 + lane * 16, c.q + c.dq);
+    if ((lane & 3) == 0) {
+        cp_async4(slot + MX4_DATA_BYTES + (lane >> 2) * 4, c.e);
+        cp_async4(slot + MX4_DATA_BYTES + 32 + (lane >> 2) * 4, c.e + c.de);
+    }
+    c.q += 64; c.e += 4;
+}
+
+// two E2M1 codes (bits 0..3 and 16..19 of v) -> f16x2 holding value * 2^-14
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t v) {
+    return (v & 0x00070007u) * 512u + (v & 0x00080008u) * 4096u;
+}
+
+template <int MT>
+__device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
+                                        int ring_d, int m, int kw, float* red) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int depth = min(8, ring_d * RING_UNIT_BYTES / MX4_SLOT_BYTES) >= 8 ? 8 : 4;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * MX4_SLOT_BYTES;
+    const int keep = depth - 1;
+    const bool has_items = sg.hb < sg.he;
+    const bool active = (g >> 1) == t;
+    const uint4* bbase = active ? xs.img + (g & 1) * 2 + (2 * t) * m * 4 : reinterpret_cast<const uint4*>(xzero);
+    const int bstep = active ? 8 * m * 4 : 0;
+    const int bhigh = active ? m * 4 : 0;
+    const int bn = active ? 4 : 0;
+
+    MX4Cursor cur{};
+    int pt = sg.seg_b, ph = sg.hb;
+    uint32_t pslot = ring;
+    if (has_items && pt < sg.seg_e) mx4_seek(cur, op, sg, pt, g, t);
+    auto issue_next = [&]() {
+        if (has_items && pt < sg.seg_e) {
+            mx4_issue(cur, pslot, lane);
+            if (++ph == sg.he) {
+                ph = sg.hb;
+                if (++pt < sg.seg_e) mx4_seek(cur, op, sg, pt, g, t);
+            }
+        }
+        cp_commit();
+        pslot += MX4_SLOT_BYTES;
+        if (pslot == ring_end) pslot = ring;
+    };
+    for (int d = 0; d < depth; d++) issue_next();
+    const uint8_t* cslot = ring_gen;
+    const uint8_t* cend = ring_gen + depth * MX4_SLOT_BYTES;
+
+    for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
+        float acc[2][MT];
+#pragma unroll
+        for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+        const uint4* bp = bbase + sg.hb * bstep;
+        for (int h = sg.hb; h < sg.he; h++) {
+            cp_wait_keep(keep);
+            __syncwarp();
+            const uint4* sd = reinterpret_cast<const uint4*>(cslot);
+            const uint32_t* se = reinterpret_cast<const uint32_t*>(cslot + MX4_DATA_BYTES);
+            const uint4 wa = sd[lane], wb = sd[32 + lane];
+            float S[2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint32_t eb = (se[i * 8 + g] >> (8 * t)) & 0xFFu;
+                // 2^(e-127) * 2^14, over the 2^24 every product's final factor carries for the integer-coded formats
+                S[i] = gguf_e8m0_half((uint8_t)eb) * (1.0f / 512.0f);
+            }
+            const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
+            const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
+            uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][bytes (0,2) | (1,3)]
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                aL[0][j][0] = e2m1x2_to_f16x2(w0[j]);       aL[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 8);
+                aH[0][j][0] = e2m1x2_to_f16x2(w0[j] >> 4);  aH[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 12);
+                aL[1][j][0] = e2m1x2_to_f16x2(w1[j]);       aL[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 8);
+                aH[1][j][0] = e2m1x2_to_f16x2(w1[j] >> 4);  aH[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 12);
+            }
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                if (n < m) {
+                    float cL[4], cH[4];
+                    const uint4* bq = bp + n * bn;
+                    uint4 b01 = bq[0], b23 = bq[1];
+                    mma16816_z(cL, aL[0][0][0], aL[1][0][0], aL[0][0][1], aL[1][0][1], b01.x, b01.y);
+                    mma16816(cL, aL[0][1][0], aL[1][1][0], aL[0][1][1], aL[1][1][1], b01.z, b01.w);
+                    mma16816(cL, aL[0][2][0], aL[1][2][0], aL[0][2][1], aL[1][2][1], b23.x, b23.y);
+                    mma16816(cL, aL[0][3][0], aL[1][3][0], aL[0][3][1], aL[1][3][1], b23.z, b23.w);
+                    b01 = bq[bhigh]; b23 = bq[bhigh + 1];
+                    mma16816_z(cH, aH[0][0][0], aH[1][0][0], aH[0][0][1], aH[1][0][1], b01.x, b01.y);
+                    mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
+                    mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
+                    mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+                        acc[i][n] = fmaf(S[i], (cL[2 * i] + cL[2 * i + 1]) + (cH[2 * i] + cH[2 * i + 1]), acc[i][n]);
+                }
+            }
+            bp += bstep;
+            __syncwarp();
+            issue_next();
+            cslot += MX4_SLOT_BYTES;
             if (cslot == cend) cslot = ring_gen;
         }
         finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
@@ -526,8 +665,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
     extern __shared__ __align__(16) uint8_t smem[];
     float* red = reinterpret_cast<float*>(smem);
     const int warp = threadIdx.x >> 5;
-    uint8_t* ring_gen = smem + RED_FLOATS * sizeof(float) + warp * ring_d * RING_SLOT_BYTES;
-    uint8_t* xbase = smem + RED_FLOATS * sizeof(float) + 8 * ring_d * RING_SLOT_BYTES;
+    uint8_t* ring_gen = smem + RED_FLOATS * sizeof(float) + warp * ring_d * RING_UNIT_BYTES;
+    uint8_t* xbase = smem + RED_FLOATS * sizeof(float) + 8 * ring_d * RING_UNIT_BYTES;
     int tb, te;
     if (ranges) {
         int2 rg = ranges[blockIdx.x];
@@ -558,8 +697,9 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         __syncthreads();   // everyone is done with the previous product's activations and the reduction scratch
         XImg xs = ximg_carve(xbase, op.k, m);
         const bool q4 = op.fmt == F_Q4K;
-        if (q4) prep_x<true>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
-        else prep_x<false>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
+        if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
+        else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
+        else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
         __syncthreads();
 
         const int kw = 1 << op.kw_log2;
@@ -573,31 +713,33 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         sg.tile0 = op.tile0;
         sg.n_rows = op.n_rows; sg.nh = nh;
         if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
-        else run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
+        else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
+        else run_mx4<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
         seg_b = seg_e;
     }
 }
 
 }  // namespace
 
-// Ring depth: 4 items when that still lets two CTAs share an SM (or when nothing smaller helps), else 2.
+// Ring depth in units of RING_UNIT_BYTES per warp: 4 when that still lets two CTAs share an SM (or when
+// nothing smaller helps), else 2. (Three CTAs per SM with a shallower ring measured slower.)
 int gemv_mma_ring_depth(int k, int m) {
     size_t image = XZERO_BYTES + (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16 + RED_FLOATS * sizeof(float);
-    if (image + 8 * 4 * RING_SLOT_BYTES <= 110 * 1024) return 4;
-    if (image + 8 * 2 * RING_SLOT_BYTES <= 110 * 1024) return 2;
-    return image + 8 * 4 * RING_SLOT_BYTES <= 220 * 1024 ? 4 : 2;
+    if (image + 8 * 4 * RING_UNIT_BYTES <= 110 * 1024) return 4;
+    if (image + 8 * 2 * RING_UNIT_BYTES <= 110 * 1024) return 2;
+    return image + 8 * 4 * RING_UNIT_BYTES <= 220 * 1024 ? 4 : 2;
 }
 
 size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
     (void)fmt;
-    return RED_FLOATS * sizeof(float) + 8 * (size_t)gemv_mma_ring_depth(k, m) * RING_SLOT_BYTES + XZERO_BYTES +
+    return RED_FLOATS * sizeof(float) + 8 * (size_t)gemv_mma_ring_depth(k, m) * RING_UNIT_BYTES + XZERO_BYTES +
            (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
-    if (w->fmt != F_Q4K && w->fmt != F_Q6K) return false;
+    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4) return false;
     if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 220 * 1024;
 }
@@ -621,7 +763,7 @@ void gemv_mma_plan(GOp* op, bool few_tiles) {
 }
 
 size_t gemv_mma_smem_for(int ring_d, int kmax, int m) {
-    return RED_FLOATS * sizeof(float) + 8 * (size_t)ring_d * RING_SLOT_BYTES + XZERO_BYTES +
+    return RED_FLOATS * sizeof(float) + 8 * (size_t)ring_d * RING_UNIT_BYTES + XZERO_BYTES +
            (size_t)(kmax >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
