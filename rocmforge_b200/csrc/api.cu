@@ -123,6 +123,7 @@ void b200q_destroy(b200q_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->scratch2) cudaFree(ctx->scratch2);
     if (ctx->scratch3) cudaFree(ctx->scratch3);
+    if (ctx->sk_ws) cudaFree(ctx->sk_ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);

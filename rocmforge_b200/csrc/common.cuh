@@ -23,6 +23,11 @@ struct b200q_ctx {
     bool tc_pending = false;  // a tensor-core launch has not had its status word read yet
     void* scratch3 = nullptr; // f16 copy of the activations + row scales for the tensor-core path
     size_t scratch3_bytes = 0;
+    // split-tile workspace of the persistent prefill kernel: one partial accumulator tile per CTA, then one
+    // flag word per CTA; a flag holds the number of the launch that last published the slot
+    void* sk_ws = nullptr;
+    int sk_ctas = 0;
+    int sk_epoch = 0;
 };
 
 struct b200q_weight {

@@ -24,6 +24,8 @@
 // (tcgen05.commit).
 // Every wait is bounded by a clock budget; on expiry the kernel raises a status word, all roles leave
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
+#include <algorithm>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -645,6 +647,314 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_q4k_tmem_kernel(const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Persistent form of the kernel above: one CTA per SM, work split evenly in units of one super-block step
+// (128 weight rows x bn activation rows x 256 k) over ALL tiles, so 172 tiles on 148 SMs cost 1.16 tile
+// times instead of 2. A CTA's range is a run of consecutive (tile, super-block) units: it may begin in the
+// middle of a tile and end in the middle of another.
+//   * A segment that does not start at k = 0 is a partial sum: it is written raw (fp32, unscaled) to the
+//     CTA's workspace slot and published with a flag that carries the launch number.
+//   * The CTA whose segment starts at k = 0 owns the tile: after its own part it adds the partial sums of
+//     the following CTAs, in CTA order (deterministic), scales and stores. Those CTAs computed their parts
+//     first thing in their ranges, the owner computes its part last, so the owner normally finds the flags
+//     already set; the wait is bounded like every other wait.
+// Only the first segment of a CTA can be a partial one, hence one workspace slot per CTA.
+struct SkArgs {
+    GemmArgs a;
+    int tiles_x;         // tiles along the weight rows; tile t = (t % tiles_x, t / tiles_x)
+    int nsb;             // super-blocks (256 k) per tile
+    int total_units;     // tiles * nsb
+    float* ws;           // [gridDim.x][bn][128] partial accumulators
+    int* flags;          // [gridDim.x]
+    int epoch;
+};
+
+constexpr int SK_SLOT_FLOATS = BM * 256;
+
+__device__ __forceinline__ int sk_unit_begin(int cta, int total, int ctas) { return (int)(((int64_t)cta * total) / ctas); }
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, SkArgs k) {
+    const GemmArgs& a = k.a;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int b_stage_bytes = a.bn * BK * 2;
+    uint8_t* sB = smem;
+    uint8_t* sRaw = sB + STAGES * b_stage_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RAW_STAGES * RAW_STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* raw_full = bars + 2 * STAGES;
+    uint64_t* raw_empty = raw_full + RAW_STAGES;
+    uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
+    uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dfree + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, nctas = gridDim.x;
+    const int u0 = sk_unit_begin(cta, k.total_units, nctas), u1 = sk_unit_begin(cta + 1, k.total_units, nctas);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&full[s]), 9);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int s = 0; s < RAW_STAGES; s++) {
+            mbar_init(smem_u32(&raw_full[s]), 1);
+            mbar_init(smem_u32(&raw_empty[s]), 8);
+        }
+        mbar_init(smem_u32(accum), 1);
+        mbar_init(smem_u32(dfree), 8);
+        *abort_flag = 0;
+        *stored = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (activations)
+        if (lane == 0) {
+            int it = 0;
+            for (int u = u0; u < u1 && ok;) {
+                const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
+                const int tok0 = (tile / k.tiles_x) * a.bn;
+                for (int kb = 4 * sb0; kb < 4 * sb1; kb++, it++) {
+                    const int s = it & (STAGES - 1);
+                    const uint32_t ph = (it >> 2) & 1;
+                    if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+                    mbar_arrive_expect_tx(smem_u32(&full[s]), (uint32_t)b_stage_bytes);
+                    tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, smem_u32(&full[s]));
+                }
+                u += sb1 - sb0;
+            }
+            for (int j = max(0, it - STAGES); j < it; j++) {   // nothing stays in flight behind us
+                const int s = j & (STAGES - 1);
+                const uint32_t ph = (j >> 2) & 1;
+                long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&full[s]), ph)) {
+                    if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 5); break; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint64_t bdesc0 = umma_desc_sw128(smem_u32(sB));
+            const uint32_t bhi = (uint32_t)(bdesc0 >> 32), blo0 = (uint32_t)bdesc0;
+            const uint32_t b_step = (uint32_t)(b_stage_bytes >> 4);
+            const uint32_t fu0 = smem_u32(full), em0 = smem_u32(empty);
+            const uint32_t at0 = tmem_base + (uint32_t)a.a_col0;
+            int it = 0, seg = 0;
+            for (int u = u0; u < u1 && ok; seg++) {
+                const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
+                // the previous segment's accumulator must have been read out
+                if (!mbar_wait(smem_u32(dfree), (uint32_t)(seg & 1) ^ 1, abort_flag, a.status, 10)) break;
+                tc_fence_after();
+                for (int kb = 4 * sb0; kb < 4 * sb1; kb++, it++) {
+                    const uint32_t s = (uint32_t)it & (STAGES - 1);
+                    const uint32_t ph = ((uint32_t)it >> 2) & 1;
+                    if (!mbar_wait(fu0 + s * 8, ph, abort_flag, a.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t at = at0 + s * A_SLOT_COLS, bl = blo0 + s * b_step;
+                    if (kb == 4 * sb0) umma_ts_f16_first(tmem_base, at, bl, bhi, idesc);
+                    else umma_ts_f16_acc(tmem_base, at, bl, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at + 8, bl + 2, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at + 16, bl + 4, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at + 24, bl + 6, bhi, idesc);
+                    umma_commit(em0 + s * 8);
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(accum));
+                u += sb1 - sb0;
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- raw super-block loader
+        if (lane == 0) {
+            int rit = 0;
+            for (int u = u0; u < u1 && ok;) {
+                const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
+                const int row0 = (tile % k.tiles_x) * BM;
+                for (int sb = sb0; sb < sb1; sb++, rit++) {
+                    const int rs = rit % RAW_STAGES;
+                    const uint32_t ph = (uint32_t)(rit / RAW_STAGES) & 1;
+                    if (!mbar_wait(smem_u32(&raw_empty[rs]), ph ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
+                    mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), (uint32_t)RAW_STAGE_BYTES);
+                    tma_load_2d(smem_u32(sRaw + rs * RAW_STAGE_BYTES), &tmap_w, sb * RAW_ROW_BYTES, row0, smem_u32(&raw_full[rs]));
+                }
+                u += sb1 - sb0;
+            }
+            for (int j = max(0, rit - RAW_STAGES); j < rit; j++) {
+                const int rs = j % RAW_STAGES;
+                const uint32_t ph = (uint32_t)(j / RAW_STAGES) & 1;
+                long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&raw_full[rs]), ph)) {
+                    if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 9); break; }
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- converters, then epilogue, per segment
+        const int q = warp & 3;
+        const int nib = (warp - 4) >> 2;
+        const int r = q * 32 + lane;
+        const uint32_t slot0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)a.a_col0 + (uint32_t)nib * 16;
+        const uint32_t mask = nib ? 0x00F000F0u : 0x000F000Fu;
+        const float nibscale = nib ? 0.0625f : 1.0f;
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        int it = 0, rit = 0, seg = 0;
+        for (int u = u0; u < u1 && ok; seg++) {
+            const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
+            const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
+            for (int sb = sb0; sb < sb1 && ok; sb++, rit++) {
+                const int rs = rit % RAW_STAGES;
+                const uint32_t rph = (uint32_t)(rit / RAW_STAGES) & 1;
+                if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
+                const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
+                const uint4 hdr = *reinterpret_cast<const uint4*>(rowp);
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, m_lo = hdr.z & 0x3F3F3F3Fu;
+                const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+                const uint32_t m_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+#pragma unroll
+                for (int c = 0; c < 4; c++, it++) {
+                    const int s = it & (STAGES - 1);
+                    const uint32_t ph = (uint32_t)(it >> 2) & 1;
+                    const int sh = ((c & 1) * 2 + nib) * 8;
+                    const uint32_t sc = ((c < 2 ? sc_lo : sc_hi) >> sh) & 0xFFu, mn = ((c < 2 ? m_lo : m_hi) >> sh) & 0xFFu;
+                    const __half2 ds = __float2half2_rn(d * (float)sc * nibscale);
+                    const __half2 nd = __float2half2_rn(-dmin * (float)mn);
+                    const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + c * 32);
+                    const uint4 qb = *reinterpret_cast<const uint4*>(rowp + 32 + c * 32);
+                    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                    uint32_t v[16];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        uint32_t t0 = (w[j] & mask) | 0x64006400u, t1 = ((w[j] >> 8) & mask) | 0x64006400u;
+                        __half2 h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), ds, nd);
+                        __half2 h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), ds, nd);
+                        v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                        v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                    }
+                    if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+            }
+            if (!ok) break;
+            // ------------------------------------------------------------ epilogue of this segment
+            if (lane == 0) ok = mbar_wait(smem_u32(accum), (uint32_t)(seg & 1), abort_flag, a.status, 6);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            const bool head = sb0 == 0, whole = head && sb1 == k.nsb;
+            const int row = row0 + r;
+            // partial sums this (owning) CTA has to add: the CTAs after it, until the tile's k range is covered
+            int p_end = cta + 1;
+            if (head && !whole) {
+                const int tile_end = (tile + 1) * k.nsb;
+                while (p_end < nctas && sk_unit_begin(p_end, k.total_units, nctas) < tile_end) p_end++;
+                for (int p = cta + 1; p < p_end && ok; p++) {
+                    if (lane == 0) {
+                        long long t0 = clock64();
+                        while (ld_acquire_gpu(k.flags + p) != k.epoch) {
+                            if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) {
+                                *abort_flag = 1;
+                                atomicCAS(a.status, 0, 11);
+                                ok = false;
+                                break;
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                }
+            }
+            float* myslot = k.ws + (size_t)cta * SK_SLOT_FLOATS;
+            for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (!ok) continue;
+                if (!head) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) __stcg(myslot + (c0 + j) * BM + r, __uint_as_float(v[j]));
+                } else {
+                    for (int p = cta + 1; p < p_end; p++) {
+                        const float* ps = k.ws + (size_t)p * SK_SLOT_FLOATS + c0 * BM + r;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(ps + j * BM));
+                    }
+                    if (row < a.n_rows) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int tok = tok0 + c0 + j;
+                            if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                        }
+                    }
+                }
+            }
+            // every TMEM read of this warp is complete: the accumulator may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(dfree));
+            if (!head) {
+                // publish the partial sums: every epilogue warp fences its stores and counts itself in shared
+                // memory; one thread waits (bounded) for all eight and releases the flag
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(stored, 1);
+                if (warp == 4 && lane == 0 && ok) {
+                    long long t0 = clock64();
+                    bool all = true;
+                    while (*reinterpret_cast<volatile int*>(stored) < 8) {
+                        if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) { all = false; atomicCAS(a.status, 0, 12); break; }
+                    }
+                    if (all) st_release_gpu(k.flags + cta, k.epoch);
+                }
+            }
+            u += sb1 - sb0;
+        }
+    }
+    // ---------------------------------------------------------------- teardown (every path ends here)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols) : "memory");
+    }
+}
+
 // Activation rows -> f16 with a power-of-two scale per row (max |x| of the row lands in [1, 2)).
 // perm: inside every aligned group of four k positions the order becomes 0,2,1,3 -- the order in which the
 // nibble masks of the Q4_K tile producers emit weights (bytes 0 and 2, then bytes 1 and 3).
@@ -745,8 +1055,25 @@ int launch_fmt(b200q_ctx* ctx, const CUtensorMap& map, const GemmArgs& a, dim3 g
 }
 
 // The product itself, once the f16 copy of the activations (row-major [m, k]) and their row scales exist.
+// Workspace of the persistent kernel: `ctas` partial tiles, then `ctas` flag words (zeroed when allocated).
+int ensure_sk_workspace(b200q_ctx* ctx, int ctas) {
+    if (ctx->sk_ws && ctx->sk_ctas >= ctas) return B200Q_OK;
+    if (ctx->sk_ws) {
+        B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+        cudaFree(ctx->sk_ws);
+        ctx->sk_ws = nullptr;
+        ctx->sk_ctas = 0;
+    }
+    const size_t slots = (size_t)ctas * SK_SLOT_FLOATS * sizeof(float);
+    B200Q_CUDA(cudaMalloc(&ctx->sk_ws, slots + (size_t)ctas * sizeof(int)), B200Q_ERR_ALLOC);
+    B200Q_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(ctx->sk_ws) + slots, 0, (size_t)ctas * sizeof(int), ctx->stream), B200Q_ERR_DEVICE);
+    ctx->sk_ctas = ctas;
+    ctx->sk_epoch = 0;
+    return B200Q_OK;
+}
+
 int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
-                     int m, const char* who) {
+                     int m, const char* who, bool may_allocate) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return fail(B200Q_ERR_INIT, "%s: cuTensorMapEncodeTiled is not available from this driver", who);
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
@@ -783,6 +1110,27 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (weights) failed with code %d", who, (int)r);
+        const int nsb = (int)(w->k / 256);
+        const int64_t units = (int64_t)grid.x * grid.y * nsb;
+        if (may_allocate && units < (1ll << 30)) {
+            // persistent kernel: one CTA per SM, all co-resident (one CTA fills an SM's shared memory)
+            const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
+            rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
+            if (rc != B200Q_OK) return rc;
+            static bool configured_sk[64] = {};
+            rc = configure_once(ctx, gemm_q4k_tmem_sk_kernel, configured_sk);
+            if (rc != B200Q_OK) return rc;
+            SkArgs k{};
+            k.a = a;
+            k.tiles_x = (int)grid.x; k.nsb = nsb; k.total_units = (int)units;
+            k.ws = static_cast<float*>(ctx->sk_ws);
+            k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
+            if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
+            k.epoch = ctx->sk_epoch;
+            gemm_q4k_tmem_sk_kernel<<<ctas, NTHREADS, smem + 16, ctx->stream>>>(map, wmap, k);
+            B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+            return B200Q_OK;
+        }
         gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
@@ -818,7 +1166,7 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
-    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, ldy, m, "gemm");
+    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, ldy, m, "gemm", true);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -857,7 +1205,7 @@ int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d
     const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
     int rc = launch_x_to_f16(ctx, d_x, w->k, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
-    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, w->n_local, m, "matmul_noalloc");
+    return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, w->n_local, m, "matmul_noalloc", false);
 }
 
 // Reads and clears the status word the tensor-core kernel raises when a bounded wait expires.
