@@ -169,6 +169,50 @@ size_t b200q_batch_weight_bytes(const b200q_batch* batch);
 /* Kernel launches one run of the batch issues (1 when every product has a grouped decode kernel). */
 int b200q_batch_launches(const b200q_batch* batch);
 
+/* ---- GGUF container: replaces the parser and lazy loader in front of load_tensor_to_gpu
+ *      (src/loader/gguf/header.rs:28-79 magic + version-3-only check, src/loader/gguf/metadata.rs:20-269
+ *      key/value pairs, src/loader/gguf/tensor_info.rs:37-101 tensor directory -> LazyTensor,
+ *      src/loader/mmap.rs:38-100 read-only mapping with bounds-checked slices). Host-only except
+ *      b200q_gguf_upload_tensor. The file stays mapped until b200q_gguf_close; name and data pointers
+ *      returned below live as long as the handle. */
+typedef struct b200q_gguf b200q_gguf;
+
+/* flags of b200q_gguf_open. Default (0) reads files the way ggml writes them: tensor offsets relative to the
+ * data section (aligned to general.alignment, default 32), the contiguous dimension first, llama.cpp block
+ * sizes. B200Q_GGUF_REFERENCE_FIXTURE reads files the way the reference's own fixtures are written and its
+ * loader reads them (tests/common/fixtures.rs:125-183, src/loader/gguf/gpu_upload.rs:37): absolute offsets,
+ * rows first, RF block sizes. */
+enum { B200Q_GGUF_REFERENCE_FIXTURE = 1 };
+
+typedef struct {
+    const char* name;
+    int n_dims;
+    int64_t dims[4];      /* as stored in the file; unused entries are 1 */
+    int ggml_type;        /* id in the file (GgufTensorType, src/loader/tensor_type.rs:16-32; 39 = ggml's MXFP4) */
+    int qtype;            /* b200q_qtype, or -1 when this library has no packed kernel for the type (F32, F16, Q2_K, Q3_K, Q5_K) */
+    int layout;           /* b200q_layout the bytes are in */
+    int64_t n, k;         /* rows x row length as b200q_weight_upload wants them */
+    int64_t file_offset;  /* absolute */
+    size_t nbytes;        /* calculate_tensor_size (src/loader/gguf/tensor_info.rs:104-133) with this library's block sizes */
+} b200q_gguf_tensor;
+
+int b200q_gguf_open(const char* path, int flags, b200q_gguf** out);
+void b200q_gguf_close(b200q_gguf* file);
+int64_t b200q_gguf_tensor_count(const b200q_gguf* file);
+int64_t b200q_gguf_kv_count(const b200q_gguf* file);
+int64_t b200q_gguf_find_tensor(const b200q_gguf* file, const char* name);   /* index, or -1 */
+int b200q_gguf_tensor_info(const b200q_gguf* file, int64_t index, b200q_gguf_tensor* out);
+int b200q_gguf_kv_key(const b200q_gguf* file, int64_t index, const char** key, int* value_type);
+/* Value of a key as text, the way the reference keeps every value (metadata.rs:56-143): numbers in decimal,
+ * bools "true"/"false", strings verbatim, arrays "" (they are skipped). needed = length + 1. */
+int b200q_gguf_meta_string(const b200q_gguf* file, const char* key, char* buf, size_t buflen, size_t* needed);
+/* LazyTensor -> mapped bytes (MmapGguf::get_slice) */
+int b200q_gguf_tensor_data(const b200q_gguf* file, int64_t index, const void** h_ptr, size_t* nbytes);
+/* GgufLoader::load_tensor_to_gpu (src/loader/gguf/types.rs:199-254) for a quantized tensor: the mapped
+ * bytes go to b200q_weight_upload as an NK tensor and stay packed. */
+int b200q_gguf_upload_tensor(b200q_ctx* ctx, const b200q_gguf* file, int64_t index, int shard_rank, int shard_count,
+                             b200q_weight** out);
+
 #ifdef __cplusplus
 }
 #endif

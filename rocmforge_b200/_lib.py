@@ -24,6 +24,17 @@ class DeviceInfo(ctypes.Structure):
                 ("smem_per_block_optin", ctypes.c_size_t), ("l2_bytes", ctypes.c_int)]
 
 
+GGUF_REFERENCE_FIXTURE = 1
+
+
+class GgufTensorInfo(ctypes.Structure):
+    """b200q_gguf_tensor"""
+    _fields_ = [("name", ctypes.c_char_p), ("n_dims", ctypes.c_int), ("dims", ctypes.c_int64 * 4),
+                ("ggml_type", ctypes.c_int), ("qtype", ctypes.c_int), ("layout", ctypes.c_int),
+                ("n", ctypes.c_int64), ("k", ctypes.c_int64), ("file_offset", ctypes.c_int64),
+                ("nbytes", ctypes.c_size_t)]
+
+
 _vp, _i, _sz, _i64, _u = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_int64, ctypes.c_uint
 _pvp = ctypes.POINTER(ctypes.c_void_p)
 
@@ -63,6 +74,16 @@ SIGNATURES = {
     "b200q_batch_free": (_i, [_vp]),
     "b200q_batch_weight_bytes": (_sz, [_vp]),
     "b200q_batch_launches": (_i, [_vp]),
+    "b200q_gguf_open": (_i, [ctypes.c_char_p, _i, _pvp]),
+    "b200q_gguf_close": (None, [_vp]),
+    "b200q_gguf_tensor_count": (_i64, [_vp]),
+    "b200q_gguf_kv_count": (_i64, [_vp]),
+    "b200q_gguf_find_tensor": (_i64, [_vp, ctypes.c_char_p]),
+    "b200q_gguf_tensor_info": (_i, [_vp, _i64, ctypes.POINTER(GgufTensorInfo)]),
+    "b200q_gguf_kv_key": (_i, [_vp, _i64, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(_i)]),
+    "b200q_gguf_meta_string": (_i, [_vp, ctypes.c_char_p, ctypes.c_char_p, _sz, ctypes.POINTER(_sz)]),
+    "b200q_gguf_tensor_data": (_i, [_vp, _i64, _pvp, ctypes.POINTER(_sz)]),
+    "b200q_gguf_upload_tensor": (_i, [_vp, _vp, _i64, _i, _i, _pvp]),
 }
 
 _lib = None

@@ -141,6 +141,22 @@ class QuantizedWeight:
         check(backend.lib.b200q_weight_info(h, None, None, None, None, None, None, None, ctypes.byref(psz)))
         self.packed_bytes = psz.value
 
+    @classmethod
+    def from_handle(cls, backend, handle):
+        """Wrap a b200q_weight* another entry point produced (the GGUF loader's upload)."""
+        self = cls.__new__(cls)
+        self.backend = backend
+        self.handle = handle
+        q, l, o = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        nl, k, r0, nt = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        psz = ctypes.c_size_t()
+        check(backend.lib.b200q_weight_info(handle, ctypes.byref(q), ctypes.byref(l), ctypes.byref(o), ctypes.byref(nl),
+                                            ctypes.byref(k), ctypes.byref(r0), ctypes.byref(nt), ctypes.byref(psz)))
+        self.qtype, self.layout, self.orient = q.value, l.value, o.value
+        self.n_local, self.k, self.row0, self.n_total = nl.value, k.value, r0.value, nt.value
+        self.packed_bytes = psz.value
+        return self
+
     def dequantize(self, out, n_elements=None):
         n = self.n_local * self.k if n_elements is None else n_elements
         check(self.backend.lib.b200q_dequantize(self.backend.ctx, self.handle, out.as_ptr(), n))
