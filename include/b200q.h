@@ -169,6 +169,12 @@ size_t b200q_batch_weight_bytes(const b200q_batch* batch);
 /* Kernel launches one run of the batch issues (1 when every product has a grouped decode kernel). */
 int b200q_batch_launches(const b200q_batch* batch);
 
+/* ---- fused dequantise + RMSNorm: replaces fused_q4_0_rmsnorm (src/ggml/hip_backend/ops/fused_ops.rs:149-215,
+ *      kernels/fused_dequant_rmsnorm.hip:87-165). w is a packed [seq_len, hidden_size] tensor uploaded as NK
+ *      (n = seq_len, k = hidden_size; any qtype/layout, the reference has Q4_0 RF only);
+ *      out[r, j] = deq(w)[r, j] * rsqrt(mean_j(deq(w)[r, :]^2) + eps) * norm_weight[j], fp32 [seq_len, hidden_size]. */
+int b200q_fused_dequant_rmsnorm(b200q_ctx* ctx, const b200q_weight* w, const float* d_norm_weight, float* d_out, float eps);
+
 /* ---- GGUF container: replaces the parser and lazy loader in front of load_tensor_to_gpu
  *      (src/loader/gguf/header.rs:28-79 magic + version-3-only check, src/loader/gguf/metadata.rs:20-269
  *      key/value pairs, src/loader/gguf/tensor_info.rs:37-101 tensor directory -> LazyTensor,

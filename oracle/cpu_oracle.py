@@ -128,6 +128,22 @@ def dequant_q8_0_i8_variant(data, n_elements):
     return out
 
 
+def fused_dequant_rmsnorm(qtype, layout, data, seq_len, hidden, weight, eps):
+    """Row-wise RMSNorm of the dequantised [seq_len, hidden] tensor times `weight` (fused_q4_0_rmsnorm)."""
+    a = _bytes(data)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    assert w.size == hidden
+    out = np.empty((seq_len, hidden), dtype=np.float32)
+    L = lib()
+    L.orc_fused_dequant_rmsnorm.restype = ctypes.c_int
+    L.orc_fused_dequant_rmsnorm.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int,
+                                            ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p]
+    rc = L.orc_fused_dequant_rmsnorm(qtype, layout, _ptr(a), a.size, seq_len, hidden, _ptr(w), eps, _ptr(out))
+    if rc < 0:
+        raise ValueError(f"unknown qtype/layout {qtype}/{layout}")
+    return out
+
+
 def matmul_f32(a, b, nk=False, threads=1):
     """cpu_matmul_f32: fp32, ascending k, multiply then add.
 

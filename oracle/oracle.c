@@ -693,3 +693,27 @@ int orc_matmul_f32_omp(const float* a, const float* b, int m, int n, int k, floa
     }
     return threads;
 }
+
+/* ---------------------------------------------------------------- fused dequant + RMSNorm
+ * kernels/fused_dequant_rmsnorm.hip:87-165. */
+int orc_fused_dequant_rmsnorm(int qtype, int layout, const uint8_t* data, size_t nbytes, int seq_len, int hidden,
+                              const float* weight, float eps, float* out) {
+    size_t n = (size_t)seq_len * (size_t)hidden;
+    int rc = orc_dequantize(qtype, layout, data, nbytes, n, out);
+    if (rc < 0) return rc;
+    for (int r = 0; r < seq_len; r++) {
+        float* row = out + (size_t)r * hidden;
+        float part[256];
+        for (int t = 0; t < 256; t++) {
+            float s = 0.0f;
+            for (int j = t; j < hidden; j += 256) s = s + row[j] * row[j];
+            part[t] = s;
+        }
+        for (int stride = 128; stride > 0; stride >>= 1)
+            for (int t = 0; t < stride; t++) part[t] = part[t] + part[t + stride];
+        float mean_sq = part[0] / (float)hidden;
+        float rms = 1.0f / sqrtf(mean_sq + eps);
+        for (int j = 0; j < hidden; j++) row[j] = row[j] * rms * weight[j];
+    }
+    return 0;
+}

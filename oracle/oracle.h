@@ -87,6 +87,13 @@ int orc_matmul_f32_omp(const float* a, const float* b, int m, int n, int k, floa
 int orc_dequantize_omp(int qtype, int layout, const uint8_t* data, size_t nbytes, size_t n, float* out, int threads);
 int orc_max_threads(void);
 
+/* kernels/fused_dequant_rmsnorm.hip:87-165 (launched by src/ggml/hip_backend/ops/fused_ops.rs:149-215):
+ * per row of a packed [seq_len, hidden] tensor: dequantise, sum of squares accumulated the way the kernel's
+ * 256 threads do (thread t takes j = t, t+256, ...; tree reduction with halving strides), rms = 1/sqrt(mean + eps),
+ * out = val * rms * weight[j]. Parity unpinned: the reference has no test vector for this kernel. */
+int orc_fused_dequant_rmsnorm(int qtype, int layout, const uint8_t* data, size_t nbytes, int seq_len, int hidden,
+                              const float* weight, float eps, float* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -354,6 +354,18 @@ int b200q_dequantize(b200q_ctx* ctx, const b200q_weight* w, float* d_out, int64_
     return launch_dequant(ctx, w->fmt, w->view, d_out, n_elements, (int64_t)w->packed_bytes);
 }
 
+int b200q_fused_dequant_rmsnorm(b200q_ctx* ctx, const b200q_weight* w, const float* d_norm_weight, float* d_out, float eps) {
+    CTX_GUARD("fused_dequant_rmsnorm");
+    if (!w) return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: weight handle is null");
+    if (w->ctx->device != ctx->device) return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: tensor lives on device %d, ctx on %d", w->ctx->device, ctx->device);
+    if (w->orient != B200Q_ORIENT_NK) return fail(B200Q_ERR_UNSUPPORTED, "fused_dequant_rmsnorm: needs a tensor stored as rows of hidden_size values");
+    if (w->k % 8 || w->k > 0x7FFFFFF8ll) return fail(B200Q_ERR_UNSUPPORTED, "fused_dequant_rmsnorm: hidden_size %lld must be a multiple of 8", (long long)w->k);
+    if (!d_norm_weight || !d_out) return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: null device pointer");
+    if ((reinterpret_cast<uintptr_t>(d_norm_weight) & 15) || (reinterpret_cast<uintptr_t>(d_out) & 15))
+        return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: weight and output must be 16-byte aligned");
+    return launch_fused_dequant_rmsnorm(ctx, w->fmt, w->view, d_norm_weight, d_out, w->n_local, (int)w->k, eps);
+}
+
 int b200q_dequantize_bytes(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, float* d_out,
                            int64_t n_elements) {
     CTX_GUARD("dequantize_bytes");

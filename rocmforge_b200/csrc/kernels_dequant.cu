@@ -48,6 +48,59 @@ int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_
     return B200Q_OK;
 }
 
+// Fused dequantise + RMSNorm (replaces kernels/fused_dequant_rmsnorm.hip:87-165): one CTA per row of a packed
+// [rows, hidden] tensor, every thread decodes 8 consecutive weights at a time (the same decode8 as everywhere
+// else, so the normalised values start from bit-exact weights), sum of squares reduced by shuffles, then a
+// second pass over the packed bytes (served by L1/L2) writes val * rsqrt(mean + eps) * weight as 32-byte
+// sectors. The fp32 row never exists in memory; the kernel is bound by the 4 B/weight it writes.
+template <int F>
+__global__ void __launch_bounds__(256) fused_dequant_rmsnorm_kernel(WView v, const float* __restrict__ weight,
+                                                                    float* __restrict__ out, int hidden, float eps) {
+    const int64_t row = blockIdx.x;
+    const int64_t piece0 = row * (hidden >> 3);
+    float ss = 0.0f;
+    for (int p = threadIdx.x; p < (hidden >> 3); p += 256) {
+        float w[8];
+        const int64_t piece = piece0 + p;
+        decode8<F>(v, piece >> 2, (int)(piece & 3), w);
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss = fmaf(w[i], w[i], ss);
+    }
+    __shared__ float red[8];
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += red[i];
+    const float rms = 1.0f / sqrtf(__fadd_rn(__fdiv_rn(total, (float)hidden), eps));
+    for (int p = threadIdx.x; p < (hidden >> 3); p += 256) {
+        float w[8];
+        const int64_t piece = piece0 + p;
+        decode8<F>(v, piece >> 2, (int)(piece & 3), w);
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(weight) + 2 * p);
+        const float4 g1 = __ldg(reinterpret_cast<const float4*>(weight) + 2 * p + 1);
+        float4* o = reinterpret_cast<float4*>(out + row * hidden) + 2 * p;
+        o[0] = make_float4(w[0] * rms * g0.x, w[1] * rms * g0.y, w[2] * rms * g0.z, w[3] * rms * g0.w);
+        o[1] = make_float4(w[4] * rms * g1.x, w[5] * rms * g1.y, w[6] * rms * g1.z, w[7] * rms * g1.w);
+    }
+}
+
+int launch_fused_dequant_rmsnorm(b200q_ctx* ctx, int fmt, const WView& v, const float* d_weight, float* d_out, int64_t rows,
+                                 int hidden, float eps) {
+    if (rows <= 0) return B200Q_OK;
+    if (rows > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: too many rows for one launch");
+    switch (fmt) {
+#define X(F) \
+    case F: fused_dequant_rmsnorm_kernel<F><<<(unsigned)rows, 256, 0, ctx->stream>>>(v, d_weight, d_out, hidden, eps); break;
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+        default: return fail(B200Q_ERR_INVALID, "fused_dequant_rmsnorm: unknown format %d", fmt);
+    }
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
 // File blocks (header and codes interleaved) -> planes. The block sizes are not word multiples, so
 // this moves single bytes; it runs once per tensor at load time.
 struct RepackArgs {

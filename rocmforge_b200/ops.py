@@ -93,3 +93,19 @@ def matmul_mxfp6(backend, quantized_weights, input, n_rows, n_cols, output, layo
                  flags=0, e3m2=False):
     _matmul_q(backend, MXFP6_E3M2 if e3m2 else MXFP6_E2M3, quantized_weights, input, n_rows, n_cols, output, layout,
               orient, m, flags)
+
+
+def fused_q4_0_rmsnorm(backend, q4_0_input, weight, output, seq_len, hidden_size, eps, qtype=Q4_0, layout=LAYOUT_RF):
+    """fused_q4_0_rmsnorm (src/ggml/hip_backend/ops/fused_ops.rs:149-215): packed [seq_len, hidden_size] rows ->
+    RMSNorm(deq(row)) * weight, fp32, without writing the dequantised rows. q4_0_input: host bytes of the packed
+    tensor (uploaded for the call, as the reference's operators re-upload their weights) or a resident
+    QuantizedWeight; weight / output: DeviceBuffer."""
+    own = not isinstance(q4_0_input, QuantizedWeight)
+    w = QuantizedWeight(backend, q4_0_input, qtype, layout, seq_len, hidden_size) if own else q4_0_input
+    try:
+        _lib.check(backend.lib.b200q_fused_dequant_rmsnorm(backend.ctx, w.handle, weight.as_ptr(), output.as_ptr(),
+                                                            ctypes.c_float(eps)))
+        backend.synchronize()
+    finally:
+        if own:
+            w.free()
