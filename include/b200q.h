@@ -169,6 +169,12 @@ size_t b200q_batch_weight_bytes(const b200q_batch* batch);
 /* Kernel launches one run of the batch issues (1 when every product has a grouped decode kernel). */
 int b200q_batch_launches(const b200q_batch* batch);
 
+/* ---- failure-path self test (no counterpart in the reference, whose kernels have no device-side waits):
+ *      launches one thread that waits, for at most budget_cycles SM clock cycles, on a barrier nothing ever
+ *      arrives on, and gives up the way the prefill kernels do. The next b200q_synchronize returns
+ *      B200Q_ERR_TIMEOUT (recoverable); the context stays usable. Nothing faults, traps or hangs. */
+int b200q_selftest_bounded_wait(b200q_ctx* ctx, int64_t budget_cycles);
+
 /* ---- fused dequantise + RMSNorm: replaces fused_q4_0_rmsnorm (src/ggml/hip_backend/ops/fused_ops.rs:149-215,
  *      kernels/fused_dequant_rmsnorm.hip:87-165). w is a packed [seq_len, hidden_size] tensor uploaded as NK
  *      (n = seq_len, k = hidden_size; any qtype/layout, the reference has Q4_0 RF only);

@@ -74,6 +74,7 @@ SIGNATURES = {
     "b200q_batch_free": (_i, [_vp]),
     "b200q_batch_weight_bytes": (_sz, [_vp]),
     "b200q_batch_launches": (_i, [_vp]),
+    "b200q_selftest_bounded_wait": (_i, [_vp, _i64]),
     "b200q_fused_dequant_rmsnorm": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float]),
     "b200q_gguf_open": (_i, [ctypes.c_char_p, _i, _pvp]),
     "b200q_gguf_close": (None, [_vp]),

@@ -200,6 +200,15 @@ int b200q_synchronize(b200q_ctx* ctx) {
     return B200Q_OK;
 }
 
+int b200q_selftest_bounded_wait(b200q_ctx* ctx, int64_t budget_cycles) {
+    CTX_GUARD("selftest_bounded_wait");
+    if (budget_cycles < 1 || budget_cycles > (1ll << 31))
+        return fail(B200Q_ERR_INVALID, "selftest_bounded_wait: budget %lld outside 1..2^31 cycles", (long long)budget_cycles);
+    int rc = launch_bounded_wait_selftest(ctx, budget_cycles);
+    if (rc == B200Q_OK) ctx->tc_pending = true;
+    return rc;
+}
+
 void* b200q_stream(b200q_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int b200q_timer_start(b200q_ctx* ctx) {

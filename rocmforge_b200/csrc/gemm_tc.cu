@@ -68,7 +68,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for the phase with the given parity. The fast path is a bare try_wait loop; every 4096 failed tries
 // it looks at the clock and at the CTA's abort flag, gives up after WAIT_BUDGET cycles (or when another role
 // already gave up), raises the abort flag and the launch's status word and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                              long long budget) {
     long long t0 = 0;
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -76,13 +77,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag != 0) return false;
             long long now = clock64();
             if (t0 == 0) t0 = now;
-            if (now - t0 > WAIT_BUDGET) {
+            if (now - t0 > budget) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    return mbar_wait_for(bar, parity, abort_flag, status, code, WAIT_BUDGET);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int cx, int cy, uint32_t bar) {
@@ -1019,6 +1023,20 @@ int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float*
     return B200Q_OK;
 }
 
+// Exercises the give-up path of the bounded waits without touching the tensor cores: one thread waits on a
+// barrier nobody will ever arrive on, with a caller-chosen budget, raises the launch's status word exactly
+// as the GEMM kernels do, and returns. The host then sees B200Q_ERR_TIMEOUT from b200q_synchronize.
+__global__ void bounded_wait_selftest_kernel(int* status, long long budget) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status, 99, budget);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1206,6 +1224,12 @@ int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d
     int rc = launch_x_to_f16(ctx, d_x, w->k, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
     return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, w->n_local, m, "matmul_noalloc", false);
+}
+
+int launch_bounded_wait_selftest(b200q_ctx* ctx, long long budget_cycles) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, budget_cycles);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
 }
 
 // Reads and clears the status word the tensor-core kernel raises when a bounded wait expires.
