@@ -100,6 +100,15 @@ def build_step(m, seed=synth.CONFIG_SEEDS[3]):
     return ops, weights, acts
 
 
+def host_threads():
+    """Host cores this process may run on. The launcher for N > 1 exports OMP_NUM_THREADS=1, which would turn the
+    CPU legs into single-thread runs; the oracle's OpenMP loops take an explicit thread count instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_step_sample(m, threads):
     """Layer 0 of the step (7 products) on the CPU oracle: dequantise to fp32, then cpu_matmul_f32."""
     from oracle import cpu_oracle as orc
@@ -122,7 +131,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     from oracle import cpu_oracle as orc
-    threads = orc.max_threads()
+    threads = host_threads()
     step, nbytes = cpu_step_sample(args.m, threads)
     for _ in range(args.warmup):
         step()
@@ -386,7 +395,7 @@ def main():
             big.free()
             # ---- CPU baseline (oracle port of the reference path) on the host cores ---------------------------
             from oracle import cpu_oracle as orc
-            threads = orc.max_threads()
+            threads = host_threads()
             step, nb = cpu_step_sample(m, threads)
             step()
             t0 = time.perf_counter()
