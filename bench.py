@@ -242,11 +242,27 @@ def shard_leg(be, rank, world, steps):
                 kernel()
                 dist.all_gather_into_tensor(y_all.view(world * m, -1), y_slice)
 
+            # fused form: the kernels' epilogues store this rank's slice into every rank's full output through
+            # peer-mapped pointers (b200q_matmul_scatter); one 4-byte all-reduce on the same streams orders the
+            # ranks before anyone reads. Outputs live in library allocations so that they can be exported.
+            y_full = be.allocate_buffer(m * n * 4)
+            handles = [None] * world
+            dist.all_gather_object(handles, be.ipc_handle(y_full))
+            peers = [y_full.as_ptr() if r == rank else be.ipc_open(handles[r]) for r in range(world)]
+            token = torch.zeros(1, device="cuda")
+
+            def fused():
+                w.matmul_scatter(xt.data_ptr(), peers, m, n)
+                dist.all_reduce(token)
+
             for _ in range(3):
                 with_gather()
+                fused()
             t_kernel = timed(kernel, steps)
             t_total = timed(with_gather, steps)
+            t_fused = timed(fused, steps)
             case = {"qtype": qname, "m": m, "ranks": world, "ms_kernel": t_kernel, "ms_kernel_plus_allgather": t_total,
+                    "ms_fused_peer_stores_plus_sync": t_fused,
                     "gathered_bytes_per_rank": int(m * n * 4 * (world - 1) / world)}
             if rank == 0:
                 yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
@@ -263,7 +279,14 @@ def shard_leg(be, rank, world, steps):
                 # the gathered result equals the unsharded one (same kernel, same per-row arithmetic)
                 got = y_all.permute(1, 0, 2).reshape(m, n)
                 case["max_abs_diff_vs_unsharded"] = float((got - yb).abs().max().item())
+                fused_host = torch.from_numpy(y_full.to_numpy(np.float32, m * n).reshape(m, n)).cuda()
+                case["fused_max_abs_diff_vs_unsharded"] = float((fused_host - yb).abs().max().item())
             dist.barrier()
+            for r in range(world):
+                if r != rank:
+                    be.ipc_close(peers[r])
+            dist.barrier()
+            y_full.free()
             out["cases"].append(case)
         w.free()
         if full is not None:

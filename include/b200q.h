@@ -169,6 +169,21 @@ size_t b200q_batch_weight_bytes(const b200q_batch* batch);
 /* Kernel launches one run of the batch issues (1 when every product has a grouped decode kernel). */
 int b200q_batch_launches(const b200q_batch* batch);
 
+/* ---- multi-GPU (no counterpart in the reference, which is single-GPU): a tensor sharded by output feature
+ *      (shard_rank / shard_count of b200q_weight_upload) produces y[:, row0 : row0 + n_local]. matmul_scatter
+ *      fuses the gather into the product: d_y_full lists the FULL outputs [m, ldy] of every GPU that needs the
+ *      result (this GPU's own first or anywhere; the others peer-mapped through b200q_ipc_open), and the
+ *      kernels' epilogues store the slice into its column block of each of them with plain stores over NVLink.
+ *      fp32 outputs; the decode kernel's formats for m <= 8, the prefill kernels for m > 8. The caller
+ *      synchronises the GPUs (a barrier or any collective on the same streams) before reading.
+ *      ipc_*: cudaIpcGetMemHandle / OpenMemHandle / CloseMemHandle on a b200q_malloc'ed buffer; the 64 handle
+ *      bytes travel between the processes by whatever channel the host has. */
+int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* const* d_y_full,
+                         int n_outputs, int64_t ldy, int m, unsigned flags);
+int b200q_ipc_get_handle(b200q_ctx* ctx, const void* d_ptr, void* handle64);
+int b200q_ipc_open(b200q_ctx* ctx, const void* handle64, void** d_ptr_out);
+int b200q_ipc_close(b200q_ctx* ctx, void* d_ptr);
+
 /* ---- failure-path self test (no counterpart in the reference, whose kernels have no device-side waits):
  *      launches one thread that waits, for at most budget_cycles SM clock cycles, on a barrier nothing ever
  *      arrives on, and gives up the way the prefill kernels do. The next b200q_synchronize returns

@@ -74,6 +74,10 @@ SIGNATURES = {
     "b200q_batch_free": (_i, [_vp]),
     "b200q_batch_weight_bytes": (_sz, [_vp]),
     "b200q_batch_launches": (_i, [_vp]),
+    "b200q_matmul_scatter": (_i, [_vp, _vp, _vp, _i, _pvp, _i, _i64, _i, _u]),
+    "b200q_ipc_get_handle": (_i, [_vp, _vp, _vp]),
+    "b200q_ipc_open": (_i, [_vp, _vp, _pvp]),
+    "b200q_ipc_close": (_i, [_vp, _vp]),
     "b200q_selftest_bounded_wait": (_i, [_vp, _i64]),
     "b200q_fused_dequant_rmsnorm": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float]),
     "b200q_gguf_open": (_i, [ctypes.c_char_p, _i, _pvp]),

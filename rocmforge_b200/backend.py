@@ -90,6 +90,21 @@ class B200Backend:
     def allocate_buffer(self, size):
         return DeviceBuffer(self, size)
 
+    def ipc_handle(self, buf):
+        """64 opaque bytes another process on this node can turn into a pointer to `buf` (ipc_open)."""
+        h = (ctypes.c_uint8 * 64)()
+        check(self.lib.b200q_ipc_get_handle(self.ctx, buf.as_ptr(), h))
+        return bytes(h)
+
+    def ipc_open(self, handle):
+        p = ctypes.c_void_p()
+        hb = (ctypes.c_uint8 * 64).from_buffer_copy(handle)
+        check(self.lib.b200q_ipc_open(self.ctx, hb, ctypes.byref(p)))
+        return p
+
+    def ipc_close(self, ptr):
+        check(self.lib.b200q_ipc_close(self.ctx, ptr))
+
     def synchronize(self):
         check(self.lib.b200q_synchronize(self.ctx))
 
@@ -165,6 +180,14 @@ class QuantizedWeight:
         xp = x.as_ptr() if isinstance(x, DeviceBuffer) else x
         yp = y.as_ptr() if isinstance(y, DeviceBuffer) else y
         check(self.backend.lib.b200q_matmul_ex(self.backend.ctx, self.handle, xp, x_dtype, ldx, yp, y_dtype, ldy, m, flags))
+
+    def matmul_scatter(self, x, outputs, m, ldy, x_dtype=_lib.F32, flags=0):
+        """Sharded product with the gather fused in: this shard's columns are stored into every full output
+        [m, ldy] listed (DeviceBuffers or raw device pointers, own GPU's or peer-mapped)."""
+        xp = x.as_ptr() if isinstance(x, DeviceBuffer) else x
+        ptrs = [o.as_ptr() if isinstance(o, DeviceBuffer) else o for o in outputs]
+        arr = (ctypes.c_void_p * len(ptrs))(*[p.value if isinstance(p, ctypes.c_void_p) else p for p in ptrs])
+        check(self.backend.lib.b200q_matmul_scatter(self.backend.ctx, self.handle, xp, x_dtype, arr, len(ptrs), ldy, m, flags))
 
     def matmul_host(self, x, m=None, flags=0):
         x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.k)

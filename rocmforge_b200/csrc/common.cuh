@@ -28,6 +28,9 @@ struct b200q_ctx {
     void* sk_ws = nullptr;
     int sk_ctas = 0;
     int sk_epoch = 0;
+    // while b200q_matmul_scatter runs: the same output slice in the other GPUs' full outputs (peer-mapped)
+    int scatter_extra = 0;
+    float* scatter_y[7] = {};
 };
 
 struct b200q_weight {

@@ -249,6 +249,8 @@ struct GemmArgs {
     int n_rows, k, m, bn, tmem_cols;
     int a_col0;            // first TMEM column of the weight-operand slots (kernel with the A operand in TMEM)
     int* status;
+    int n_extra;           // further copies of y to write: the same slice inside other GPUs' full outputs
+    float* y_extra[7];     // (peer-mapped pointers; plain stores over NVLink, no loads)
 };
 
 // Warp roles (384 threads = 12 warps; a warp may only read the TMEM lane quarter warp_id % 4):
@@ -413,7 +415,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int tok = tok0 + c0 + j;
-                        if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                        if (tok < a.m) {
+                                const float val = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                                a.y[(int64_t)tok * a.ldy + row] = val;
+                                for (int pp = 0; pp < a.n_extra; pp++) a.y_extra[pp][(int64_t)tok * a.ldy + row] = val;
+                            }
                     }
                 }
             }
@@ -636,7 +642,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_q4k_tmem_kernel(const __grid
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int tok = tok0 + c0 + j;
-                        if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                        if (tok < a.m) {
+                                const float val = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                                a.y[(int64_t)tok * a.ldy + row] = val;
+                                for (int pp = 0; pp < a.n_extra; pp++) a.y_extra[pp][(int64_t)tok * a.ldy + row] = val;
+                            }
                     }
                 }
             }
@@ -923,7 +933,11 @@ gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
                             const int tok = tok0 + c0 + j;
-                            if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                            if (tok < a.m) {
+                                const float val = __uint_as_float(v[j]) * __ldg(a.xscale + tok);
+                                a.y[(int64_t)tok * a.ldy + row] = val;
+                                for (int pp = 0; pp < a.n_extra; pp++) a.y_extra[pp][(int64_t)tok * a.ldy + row] = val;
+                            }
                         }
                     }
                 }
@@ -1108,6 +1122,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     a.v = w->view; a.xscale = d_scale; a.y = d_y; a.ldy = ldy;
     a.n_rows = (int)w->n_local; a.k = (int)w->k; a.m = m; a.bn = bn;
     a.status = ctx->d_status;
+    a.n_extra = ctx->scatter_extra;
+    for (int p = 0; p < ctx->scatter_extra; p++) a.y_extra[p] = ctx->scatter_y[p];
     dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
     if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
         // weight operand in tensor memory

@@ -283,7 +283,11 @@ __device__ __forceinline__ void finish_tile(float (&acc)[2][MT], const GOp& op, 
                 float sacc = 0.f;
                 for (int j = 0; j < kw; j++) sacc += red[((warp + j) * 16 + r) * MT + n];
                 const int row = row_base + r;
-                if (row < sg.n_rows && n < m) op.y[(int64_t)n * op.ldy + row] = sacc * xs.fin[n];
+                if (row < sg.n_rows && n < m) {
+                    const float val = sacc * xs.fin[n];
+                    op.y[(int64_t)n * op.ldy + row] = val;
+                    for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][(int64_t)n * op.ldy + row] = val;
+                }
             }
         }
         __syncthreads();   // the reduction buffer is free again
@@ -295,7 +299,11 @@ __device__ __forceinline__ void finish_tile(float (&acc)[2][MT], const GOp& op, 
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const int row = row_base + g + 8 * i;
-                    if (row < sg.n_rows) op.y[(int64_t)n * op.ldy + row] = acc[i][n] * f;
+                    if (row < sg.n_rows) {
+                        const float val = acc[i][n] * f;
+                        op.y[(int64_t)n * op.ldy + row] = val;
+                        for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][(int64_t)n * op.ldy + row] = val;
+                    }
                 }
             }
         }

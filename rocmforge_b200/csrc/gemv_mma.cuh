@@ -16,6 +16,8 @@ struct GOp {
     int kw_log2;      // log2 of the warps that split k for one 16-row tile (8 >> kw_log2 row tiles per CTA tile)
     int tile0;        // index of this product's first CTA tile in the launch
     int ntiles;       // CTA tiles of this product
+    int n_extra;      // further copies of y to write (outputs of a sharded product gathered by peer stores)
+    float* y_extra[7];
 };
 
 bool gemv_mma_supported(const b200q_weight* w, int m);

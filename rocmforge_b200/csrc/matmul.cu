@@ -2,6 +2,8 @@
 #include <vector>
 
 #include "common.cuh"
+#include <cstring>
+
 #include "gemv_mma.cuh"
 
 using namespace b200q;
@@ -27,6 +29,8 @@ static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y
     op.v = w->view;
     op.x = x; op.y = y; op.ldx = ldx; op.ldy = ldy;
     op.n_rows = (int)w->n_local; op.k = (int)w->k; op.fmt = w->fmt;
+    op.n_extra = w->ctx->scatter_extra;
+    for (int p = 0; p < op.n_extra; p++) op.y_extra[p] = w->ctx->scatter_y[p];
     return op;
 }
 
@@ -43,19 +47,23 @@ static int check_matmul_args(b200q_ctx* ctx, const b200q_weight* w, const void* 
 // fp32 in, fp32 out; picks the kernel.
 static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy, int m,
                       unsigned flags) {
-    if ((flags & B200Q_MM_SEQUENTIAL) || !gemv_fast_supported(w)) return launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
+    const bool scatter = ctx->scatter_extra > 0;
+    if ((flags & B200Q_MM_SEQUENTIAL) || !gemv_fast_supported(w))
+        return scatter ? fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: the sequential kernel writes one output only") : launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
     bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx % 4) == 0;
-    if (!aligned) return launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
+    if (!aligned) return scatter ? fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: activations must be 16-byte aligned") : launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
     // largest activation-row chunk whose shared-memory image fits the tensor-core decode kernel
     int chunk = 8;
     while (chunk > 1 && !gemv_mma_supported(w, chunk)) chunk >>= 1;
     const bool mma = gemv_mma_supported(w, chunk);
+    if (!mma && scatter) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m <= 8 needs a format of the tensor-core decode kernel (Q4_K, Q6_K, MXFP4 in GGUF layout)");
     if (!mma) chunk = 8;
     for (int i = 0; i < m; i += chunk) {
         int mm = m - i < chunk ? m - i : chunk;
         int rc;
         if (mma) {
             GOp op = make_gop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
+            for (int p = 0; p < op.n_extra; p++) op.y_extra[p] += (int64_t)i * ldy;
             gemv_mma_plan(&op, true);
             op.tile0 = 0;
             const int ring_d = gemv_mma_ring_depth((int)w->k, mm);
@@ -115,6 +123,54 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
     }
     if (y_dtype == B200Q_BF16) rc = launch_convert_f32_to_bf16(ctx, y32, ldy32, d_y, ldy, m, w->n_local);
     return rc;
+}
+
+// Sharded product with the gather fused into the kernels' epilogues: this GPU's output slice is stored into
+// its column block of EVERY listed full output (its own and the peers', peer-mapped), so no collective copies
+// the slices afterwards. The caller synchronises the GPUs before reading (a barrier, or one tiny collective
+// on the same streams).
+int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* const* d_y_full, int n_outputs,
+                         int64_t ldy, int m, unsigned flags) {
+    if (!ctx) return fail(B200Q_ERR_INVALID, "matmul_scatter: ctx is null");
+    if (!w) return fail(B200Q_ERR_INVALID, "matmul_scatter: weight handle is null");
+    if (!d_y_full || n_outputs < 1 || n_outputs > 8) return fail(B200Q_ERR_INVALID, "matmul_scatter: %d outputs (1..8 allowed)", n_outputs);
+    if (ldy < w->row0 + w->n_local) return fail(B200Q_ERR_INVALID, "matmul_scatter: ldy=%lld is smaller than the end of this shard's columns (%lld)", (long long)ldy, (long long)(w->row0 + w->n_local));
+    for (int p = 0; p < n_outputs; p++)
+        if (!d_y_full[p] || (reinterpret_cast<uintptr_t>(d_y_full[p]) & 15)) return fail(B200Q_ERR_INVALID, "matmul_scatter: output %d is null or not 16-byte aligned", p);
+    if (flags & B200Q_MM_SEQUENTIAL) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: the sequential kernel writes one output only");
+    if (m > 8 && ((flags & B200Q_MM_NO_TENSOR) || !gemm_tc_supported(w, m)))
+        return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m > 8 needs the tensor-core prefill kernels");
+    ctx->scatter_extra = n_outputs - 1;
+    for (int p = 1; p < n_outputs; p++) ctx->scatter_y[p - 1] = static_cast<float*>(d_y_full[p]) + w->row0;
+    int rc = b200q_matmul_ex(ctx, w, d_x, x_dtype, 0, static_cast<float*>(d_y_full[0]) + w->row0, B200Q_F32, ldy, m, flags);
+    ctx->scatter_extra = 0;
+    return rc;
+}
+
+int b200q_ipc_get_handle(b200q_ctx* ctx, const void* d_ptr, void* handle64) {
+    if (!ctx || !d_ptr || !handle64) return fail(B200Q_ERR_INVALID, "ipc_get_handle: null argument");
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    cudaIpcMemHandle_t h;
+    B200Q_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(d_ptr)), B200Q_ERR_DEVICE);
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(handle64, &h, 64);
+    return B200Q_OK;
+}
+
+int b200q_ipc_open(b200q_ctx* ctx, const void* handle64, void** d_ptr_out) {
+    if (!ctx || !handle64 || !d_ptr_out) return fail(B200Q_ERR_INVALID, "ipc_open: null argument");
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    B200Q_CUDA(cudaIpcOpenMemHandle(d_ptr_out, h, cudaIpcMemLazyEnablePeerAccess), B200Q_ERR_DEVICE);
+    return B200Q_OK;
+}
+
+int b200q_ipc_close(b200q_ctx* ctx, void* d_ptr) {
+    if (!ctx || !d_ptr) return fail(B200Q_ERR_INVALID, "ipc_close: null argument");
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    B200Q_CUDA(cudaIpcCloseMemHandle(d_ptr), B200Q_ERR_DEVICE);
+    return B200Q_OK;
 }
 
 int b200q_matmul_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m) {
