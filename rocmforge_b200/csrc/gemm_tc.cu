@@ -696,8 +696,18 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// QF selects the weight format: 0 = GGUF Q4_K (raw rows of 144-byte super-blocks), 1 = GGUF MXFP4 (raw rows of
+// 8 x 16 code bytes per 256 k from the code plane; the 8 exponent bytes come by a plain load). MXFP4 codes
+// become f16 by bit placement (E2M1 s|ee|m at bits 15|11..9 is value * 2^-14) and one HMUL2 with the block
+// scale 2^(e-127) * 2^14, which has to lie in the f16 range (block exponents 2^-28 .. 2^1).
+template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, SkArgs k) {
+gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                    const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3, SkArgs k) {
+    // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
+    // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
+    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
+    constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -814,7 +824,14 @@ gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
                     const uint32_t ph = (uint32_t)(rit / RAW_STAGES) & 1;
                     if (!mbar_wait(smem_u32(&raw_empty[rs]), ph ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
                     mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), (uint32_t)RAW_STAGE_BYTES);
-                    tma_load_2d(smem_u32(sRaw + rs * RAW_STAGE_BYTES), &tmap_w, sb * RAW_ROW_BYTES, row0, smem_u32(&raw_full[rs]));
+                    if constexpr (QF == 2) {
+                        const uint32_t st = smem_u32(sRaw + rs * RAW_STAGE_BYTES), bar = smem_u32(&raw_full[rs]);
+                        tma_load_2d(st, &tmap_w, sb * 128, row0, bar);
+                        tma_load_2d(st + BM * 128, &tmap_w2, sb * 64, row0, bar);
+                        tma_load_2d(st + BM * 192, &tmap_w3, sb * 16, row0, bar);
+                    } else {
+                        tma_load_2d(smem_u32(sRaw + rs * RAW_STAGE_BYTES), &tmap_w, sb * RAW_ROW_BYTES, row0, smem_u32(&raw_full[rs]));
+                    }
                 }
                 u += sb1 - sb0;
             }
@@ -846,6 +863,7 @@ gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
                 if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
+                if constexpr (QF == 0) {
                 const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
                 const uint4 hdr = *reinterpret_cast<const uint4*>(rowp);
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
@@ -882,6 +900,95 @@ gemm_q4k_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                }
+                } else if constexpr (QF == 2) {
+                    // GGUF Q6_K: per 128-weight half, ql[64] low/high nibbles and qh[32] two-bit fields; k-block c
+                    // of the 256-k step = half c >> 1, nibble c & 1; this thread takes weights 32 nib .. 32 nib + 31.
+                    const uint8_t* stage = sRaw + rs * RAW_STAGE_BYTES;
+                    const uint8_t* qlr = stage + r * 128;
+                    const uint8_t* qhr = stage + BM * 128 + r * 64;
+                    const uint4 scv = *reinterpret_cast<const uint4*>(stage + BM * 192 + r * 16);
+                    const uint32_t scw[4] = {scv.x, scv.y, scv.z, scv.w};
+                    const int64_t grow = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
+                    const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(a.v.p[3]) + grow * k.nsb + sb)));
+                    const __half2 k1056 = __float2half2_rn(1056.0f);
+#pragma unroll
+                    for (int c = 0; c < 4; c++, it++) {
+                        const int s = it & (STAGES - 1);
+                        const uint32_t ph = (uint32_t)(it >> 2) & 1;
+                        const int half = c >> 1, hn = c & 1;
+                        // int8 scales 4c + 2 nib and + 1 (16 weights each): bytes 2 nib, 2 nib + 1 of scale word c
+                        const int sc0 = (int)(int8_t)((scw[c] >> (16 * nib)) & 0xFFu), sc1 = (int)(int8_t)((scw[c] >> (16 * nib + 8)) & 0xFFu);
+                        const __half2 ds0 = __float2half2_rn(d * (float)sc0), ds1 = __float2half2_rn(d * (float)sc1);
+                        // 128-byte and 64-byte rows are stored swizzled by the copy (bank conflicts otherwise)
+                        const int lc = 4 * half + 2 * nib, hc = 2 * half;
+                        const uint4 la = *reinterpret_cast<const uint4*>(qlr + ((lc ^ (r & 7)) << 4));
+                        const uint4 lb = *reinterpret_cast<const uint4*>(qlr + (((lc + 1) ^ (r & 7)) << 4));
+                        const uint4 ha = *reinterpret_cast<const uint4*>(qhr + ((hc ^ ((r >> 1) & 3)) << 4));
+                        const uint4 hb = *reinterpret_cast<const uint4*>(qhr + (((hc + 1) ^ ((r >> 1) & 3)) << 4));
+                        const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+                        const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+                        const int lsh = 4 * hn, hsh = 4 * hn + 2 * nib;
+                        uint32_t v[16];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const uint32_t code4 = ((lw[j] >> lsh) & 0x0F0F0F0Fu) | (((hw[j] >> hsh) & 0x03030303u) << 4);
+                            uint32_t t0 = __byte_perm(code4, 0x64646464u, 0x5140), t1 = __byte_perm(code4, 0x64646464u, 0x7362);
+                            const __half2 dsj = j < 4 ? ds0 : ds1;
+                            __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1056), dsj);   // (q - 32) exactly, then one rounding
+                            __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1056), dsj);
+                            v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                            v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                        }
+                        if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+                        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                        if (!ok) break;
+                        tc_fence_after();
+                        tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                    }
+                } else {
+                const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
+                const int64_t grow = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
+                const uint2 ex = __ldg(reinterpret_cast<const uint2*>(a.v.p[0] + grow * (a.k >> 5) + sb * 8));
+#pragma unroll
+                for (int c = 0; c < 4; c++, it++) {
+                    const int s = it & (STAGES - 1);
+                    const uint32_t ph = (uint32_t)(it >> 2) & 1;
+                    const int blk = 2 * c + nib;                      // block of 32 inside the 256-k step
+                    const uint32_t eb = ((blk < 4 ? ex.x : ex.y) >> (8 * (blk & 3))) & 0xFFu;
+                    const __half2 S = __float2half2_rn(gguf_e8m0_half((uint8_t)eb) * 32768.0f);
+                    // rows are 128 bytes: the copy swizzles the 16-byte chunks with the row number so that the
+                    // 32 rows of a warp do not all hit the same banks
+                    const uint4 q = *reinterpret_cast<const uint4*>(rowp + ((blk ^ (r & 7)) << 4));
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                    uint32_t v[16];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // low nibbles: elements 4j..4j+3 of the block (as 0,2 | 1,3), high nibbles: 16 further on
+                        const uint32_t x0 = w[j], x1 = w[j] >> 8, x2 = w[j] >> 4, x3 = w[j] >> 12;
+                        uint32_t t0 = (x0 & 0x00070007u) * 512u + (x0 & 0x00080008u) * 4096u;
+                        uint32_t t1 = (x1 & 0x00070007u) * 512u + (x1 & 0x00080008u) * 4096u;
+                        uint32_t t2 = (x2 & 0x00070007u) * 512u + (x2 & 0x00080008u) * 4096u;
+                        uint32_t t3 = (x3 & 0x00070007u) * 512u + (x3 & 0x00080008u) * 4096u;
+                        __half2 h0 = __hmul2(*reinterpret_cast<__half2*>(&t0), S), h1 = __hmul2(*reinterpret_cast<__half2*>(&t1), S);
+                        __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&t2), S), h3 = __hmul2(*reinterpret_cast<__half2*>(&t3), S);
+                        v[2 * j] = *reinterpret_cast<uint32_t*>(&h0); v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                        v[8 + 2 * j] = *reinterpret_cast<uint32_t*>(&h2); v[8 + 2 * j + 1] = *reinterpret_cast<uint32_t*>(&h3);
+                    }
+                    if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                }
                 }
                 if (!ok) break;
                 __syncwarp();
@@ -1104,6 +1211,14 @@ int ensure_sk_workspace(b200q_ctx* ctx, int ctas) {
     return B200Q_OK;
 }
 
+// MXFP4 takes the tensor-memory kernel when its 256-k steps are whole and the unit count fits an int.
+bool mx4_tmem_path(const b200q_weight* w, int m) {
+    if (w->fmt != fmt_of(MXFP4, GGUF) || (w->k % 256) != 0) return false;
+    const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+    const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
+    return tiles * (w->k / 256) < (1ll << 30);
+}
+
 int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
                      int m, const char* who, bool may_allocate) {
     EncodeTiledFn enc = get_encode_fn();
@@ -1125,6 +1240,80 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     a.n_extra = ctx->scatter_extra;
     for (int p = 0; p < ctx->scatter_extra; p++) a.y_extra[p] = ctx->scatter_y[p];
     dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
+    if (may_allocate && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
+        (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30)) {
+        // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads
+        a.a_col0 = (bn + 31) & ~31;
+        a.tmem_cols = 32;
+        while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 208 +
+                            (2 * STAGES + 2 * RAW_STAGES + 3) * 8 + 32;
+        const int nsb = (int)(w->k / 256);
+        CUtensorMap pm[3];
+        const int pbytes[3] = {128, 64, 16};
+        for (int j = 0; j < 3; j++) {
+            const cuuint64_t row_bytes = (cuuint64_t)nsb * pbytes[j];
+            cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
+            cuuint64_t wstr[1] = {row_bytes};
+            cuuint32_t wbox[2] = {(cuuint32_t)pbytes[j], (cuuint32_t)BM};
+            const CUtensorMapSwizzle sw = j == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : j == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
+            r = enc(&pm[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w->view.p[j]), wdim, wstr, wbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (Q6_K plane %d) failed with code %d", who, j, (int)r);
+        }
+        const int64_t units = (int64_t)grid.x * grid.y * nsb;
+        const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
+        int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
+        if (rc != B200Q_OK) return rc;
+        static bool configured_q6[64] = {};
+        rc = configure_once(ctx, gemm_tmem_sk_kernel<2>, configured_q6);
+        if (rc != B200Q_OK) return rc;
+        SkArgs k{};
+        k.a = a;
+        k.tiles_x = (int)grid.x; k.nsb = nsb; k.total_units = (int)units;
+        k.ws = static_cast<float*>(ctx->sk_ws);
+        k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
+        if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
+        k.epoch = ctx->sk_epoch;
+        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], k);
+        B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+        return B200Q_OK;
+    }
+    if (may_allocate && mx4_tmem_path(w, m)) {
+        // MXFP4 with the weight operand in tensor memory (persistent kernel only)
+        a.a_col0 = (bn + 31) & ~31;
+        a.tmem_cols = 32;
+        while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 128 +
+                            (2 * STAGES + 2 * RAW_STAGES + 3) * 8 + 32;
+        CUtensorMap wmap;
+        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 32) * 16;
+        cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
+        cuuint64_t wstr[1] = {row_bytes};
+        cuuint32_t wbox[2] = {128u, (cuuint32_t)BM};
+        r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w->view.p[1]), wdim, wstr, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (codes) failed with code %d", who, (int)r);
+        const int nsb = (int)(w->k / 256);
+        const int64_t units = (int64_t)grid.x * grid.y * nsb;
+        const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
+        int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
+        if (rc != B200Q_OK) return rc;
+        static bool configured_mx[64] = {};
+        rc = configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
+        if (rc != B200Q_OK) return rc;
+        SkArgs k{};
+        k.a = a;
+        k.tiles_x = (int)grid.x; k.nsb = nsb; k.total_units = (int)units;
+        k.ws = static_cast<float*>(ctx->sk_ws);
+        k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
+        if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
+        k.epoch = ctx->sk_epoch;
+        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, k);
+        B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+        return B200Q_OK;
+    }
     if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
         // weight operand in tensor memory
         a.a_col0 = (bn + 31) & ~31;
@@ -1152,7 +1341,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
             if (rc != B200Q_OK) return rc;
             static bool configured_sk[64] = {};
-            rc = configure_once(ctx, gemm_q4k_tmem_sk_kernel, configured_sk);
+            rc = configure_once(ctx, gemm_tmem_sk_kernel<0>, configured_sk);
             if (rc != B200Q_OK) return rc;
             SkArgs k{};
             k.a = a;
@@ -1161,7 +1350,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            gemm_q4k_tmem_sk_kernel<<<ctas, NTHREADS, smem + 16, ctx->stream>>>(map, wmap, k);
+            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 16, ctx->stream>>>(map, wmap, wmap, wmap, k);
             B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
@@ -1196,7 +1385,8 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     if (rc != B200Q_OK) return rc;
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
-    const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
+    // the nibble-mask producers emit weights in the order 0,2,1,3 inside every group of four
+    const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || mx4_tmem_path(w, m)) ? 1 : 0;
     if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
