@@ -730,9 +730,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const int u0 = sk_unit_begin(cta, k.total_units, nctas), u1 = sk_unit_begin(cta + 1, k.total_units, nctas);
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(&full[s]), 9);
-            mbar_init(smem_u32(&empty[s]), 1);
+        for (int s = 0; s < STAGES / 2; s++) {   // one pair of barriers per PAIR of stages
+            mbar_init(smem_u32(&full[s]), 9);    // 8 converter warps + the TMA thread's expect_tx arrival
+            mbar_init(smem_u32(&empty[s]), 1);   // tcgen05.commit
         }
         for (int s = 0; s < RAW_STAGES; s++) {
             mbar_init(smem_u32(&raw_full[s]), 1);
@@ -761,20 +761,22 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int u = u0; u < u1 && ok;) {
                 const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
                 const int tok0 = (tile / k.tiles_x) * a.bn;
-                for (int kb = 4 * sb0; kb < 4 * sb1; kb++, it++) {
-                    const int s = it & (STAGES - 1);
+                for (int kb = 4 * sb0; kb < 4 * sb1; kb += 2, it += 2) {
+                    const int s = it & (STAGES - 1);                    // first stage of the pair
                     const uint32_t ph = (it >> 2) & 1;
-                    if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
-                    mbar_arrive_expect_tx(smem_u32(&full[s]), (uint32_t)b_stage_bytes);
-                    tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, smem_u32(&full[s]));
+                    const uint32_t fb = smem_u32(&full[s >> 1]);
+                    if (!mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+                    mbar_arrive_expect_tx(fb, 2u * (uint32_t)b_stage_bytes);
+                    tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, fb);
+                    tma_load_2d(smem_u32(sB + (s + 1) * b_stage_bytes), &tmap_x, (kb + 1) * BK, tok0, fb);
                 }
                 u += sb1 - sb0;
             }
-            for (int j = max(0, it - STAGES); j < it; j++) {   // nothing stays in flight behind us
+            for (int j = max(0, it - STAGES); j < it; j += 2) {   // nothing stays in flight behind us
                 const int s = j & (STAGES - 1);
                 const uint32_t ph = (j >> 2) & 1;
                 long long t0 = clock64();
-                while (!mbar_try_wait(smem_u32(&full[s]), ph)) {
+                while (!mbar_try_wait(smem_u32(&full[s >> 1]), ph)) {
                     if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 5); break; }
                 }
             }
@@ -794,18 +796,25 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 // the previous segment's accumulator must have been read out
                 if (!mbar_wait(smem_u32(dfree), (uint32_t)(seg & 1) ^ 1, abort_flag, a.status, 10)) break;
                 tc_fence_after();
-                for (int kb = 4 * sb0; kb < 4 * sb1; kb++, it++) {
-                    const uint32_t s = (uint32_t)it & (STAGES - 1);
+                for (int kb = 4 * sb0; kb < 4 * sb1; kb += 2, it += 2) {
+                    const uint32_t s = (uint32_t)it & (STAGES - 1);     // first stage of the pair
                     const uint32_t ph = ((uint32_t)it >> 2) & 1;
-                    if (!mbar_wait(fu0 + s * 8, ph, abort_flag, a.status, 2)) { ok = false; break; }
+                    if (!mbar_wait(fu0 + (s >> 1) * 8, ph, abort_flag, a.status, 2)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t at = at0 + s * A_SLOT_COLS, bl = blo0 + s * b_step;
+                    // 16 k further: 8 TMEM columns on the A side, 32 bytes (+2 encoded) inside the swizzle atom on the B
+                    // side; the second stage of the pair is one A slot / one B stage further on
                     if (kb == 4 * sb0) umma_ts_f16_first(tmem_base, at, bl, bhi, idesc);
                     else umma_ts_f16_acc(tmem_base, at, bl, bhi, idesc);
                     umma_ts_f16_acc(tmem_base, at + 8, bl + 2, bhi, idesc);
                     umma_ts_f16_acc(tmem_base, at + 16, bl + 4, bhi, idesc);
                     umma_ts_f16_acc(tmem_base, at + 24, bl + 6, bhi, idesc);
-                    umma_commit(em0 + s * 8);
+                    const uint32_t at2 = at + A_SLOT_COLS, bl2 = bl + b_step;
+                    umma_ts_f16_acc(tmem_base, at2, bl2, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at2 + 8, bl2 + 2, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at2 + 16, bl2 + 4, bhi, idesc);
+                    umma_ts_f16_acc(tmem_base, at2 + 24, bl2 + 6, bhi, idesc);
+                    umma_commit(em0 + (s >> 1) * 8);
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(accum));
@@ -891,15 +900,20 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
                         v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                     }
-                    if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                    if (!ok) break;
-                    tc_fence_after();
+                    // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
+                    if ((c & 1) == 0) {
+                        if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
                     tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                    if (c & 1) {
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                    }
                 }
                 } else if constexpr (QF == 2) {
                     // GGUF Q6_K: per 128-weight half, ql[64] low/high nibbles and qh[32] two-bit fields; k-block c
@@ -940,15 +954,20 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
                             v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                         }
-                        if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
-                        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                        if (!ok) break;
-                        tc_fence_after();
+                        // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
+                        if ((c & 1) == 0) {
+                            if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
-                        tmem_st_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                        if (c & 1) {
+                            tmem_st_wait();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                        }
                     }
                 } else {
                 const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
@@ -979,15 +998,20 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         v[2 * j] = *reinterpret_cast<uint32_t*>(&h0); v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                         v[8 + 2 * j] = *reinterpret_cast<uint32_t*>(&h2); v[8 + 2 * j + 1] = *reinterpret_cast<uint32_t*>(&h3);
                     }
-                    if (lane == 0) ok = mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 4);
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                    if (!ok) break;
-                    tc_fence_after();
+                    // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
+                    if ((c & 1) == 0) {
+                        if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
                     tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&full[s]));
+                    if (c & 1) {
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                    }
                 }
                 }
                 if (!ok) break;
