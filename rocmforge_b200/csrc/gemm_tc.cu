@@ -1,27 +1,32 @@
-// Prefill kernel: fused dequant + GEMM on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
+// Prefill kernels: fused dequant + GEMM on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
 // Replaces what the reference does for m > 1 today: dequantise the whole tensor to fp32 and call an fp32
 // library GEMM with host-side transposes (src/kernels/matmul/quantized/q8_0.rs:69-106,
-// src/tensor/matmul.rs:153-214). Here packed weights are expanded tile by tile, to bf16, straight into shared
-// memory and never touch HBM as fp32.
-// (Shared-memory operands are f16, not bf16: see the note on operand formats below.)
+// src/tensor/matmul.rs:153-214). Here packed weights are expanded tile by tile to f16 next to the tensor
+// cores and never touch HBM as fp32.
 //
 //   y[m, n] = x[m, k] * W[n, k]^T   computed as   D[128 weight rows, BN activation rows] += A * B^T
 //
-//   A (UMMA M side) : 128 weight rows x 64 k, f16, K-major, 128-byte swizzle, written by 8 dequant warps
-//                     (decode8 gives the exact fp32 values; one round-to-nearest to f16, whose 11-bit
-//                     mantissa keeps the result well inside the 2e-3 tolerance; bf16 weights do not)
+//   A (UMMA M side) : 128 weight rows x 64 k per stage, f16. Three producers, one per kernel below:
+//                     gemm_tc_kernel<F>        every format: decode8 (exact fp32 values) + one rounding to f16,
+//                                              K-major tile with 128-byte swizzle in SHARED memory
+//                     gemm_q4k_tmem_kernel     GGUF Q4_K: raw super-blocks by TMA, converted into TENSOR memory
+//                                              (tcgen05.st), TS-form MMA; one CTA per tile
+//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K: the same in tensor memory, persistent
+//                                              CTAs with a stream-K split over all tiles
+//                     (f16, not bf16: an 11-bit mantissa keeps the result inside the 2e-3 tolerance, bf16
+//                     weights do not)
 //   B (UMMA N side) : BN <= 256 activation rows x 64 k, f16, loaded by TMA (cp.async.bulk.tensor, no
-//                     multicast) with the same swizzle. Activations (fp32 or bf16 from the caller) are first
+//                     multicast) with 128-byte swizzle. Activations (fp32 or bf16 from the caller) are first
 //                     copied to f16 with one power-of-two scale per row, so neither large nor small rows
 //                     leave the f16 range; the scale is multiplied back in the epilogue
-//   D               : fp32 in tensor memory, 128 lanes x BN columns; read back with tcgen05.ld by the four
-//                     dequant warps (one lane quarter each) and stored to y, coalesced along n
+//   D               : fp32 in tensor memory, 128 lanes x BN columns; read back with tcgen05.ld by eight
+//                     warps (two per lane quarter) and stored to y, coalesced along n
 //
 // Warp roles (384 threads): warp 0 = TMA producer + TMEM allocator, warp 1 = MMA issuer (one elected
-// thread, alone on its scheduler), 8 weight-tile producer warps, 8 epilogue warps. A 4-stage ring of {A, B}
-// tiles is handed over with mbarriers: full_a (8 warp arrivals), full_b (TMA transaction bytes), empty
-// (tcgen05.commit).
+// thread), warp 2 = raw-weight loader (tensor-memory kernels), 8 producer / converter warps that are also
+// the epilogue warps. Rings of stages are handed over with mbarriers: full (producer arrivals + TMA
+// transaction bytes), empty (tcgen05.commit).
 // Every wait is bounded by a clock budget; on expiry the kernel raises a status word, all roles leave
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
 #include <algorithm>

@@ -133,3 +133,29 @@ def test_config4_llama7b_q4k_prefill(oracle, n, k, m):
     assert float(np.max(np.abs(y[:, rows] - ref))) / scale <= TOL
     assert np.all(np.isfinite(y))
     w.free()
+
+
+@pytest.mark.parametrize("qt,m", [(synth.MXFP4, 64), (synth.MXFP4, 512), (synth.Q6_K, 300)],
+                         ids=["mxfp4-m64", "mxfp4-m512", "q6k-m300"])
+def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
+    """[28672 x 8192] (config 5; Q6_K on the same shape): MXFP4 and Q6_K take the persistent kernel whose weight
+    operand lives in tensor memory; with 448+ tiles on 148 SMs most tiles are split between CTAs. 64 sampled
+    weight rows plus the first and last against the oracle."""
+    be = backend()
+    n, k = synth.LLAMA70B_FFN_SHAPES[0]
+    rng = synth.rng_for(synth.CONFIG_SEEDS[5] + qt + m)
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    rows = np.unique(np.concatenate([rng.integers(0, n, size=64), [0, n - 1]]))
+    bb = synth.block_bytes(qt, synth.GGUF)
+    be_ = synth.block_elems(qt)
+    blocks = np.frombuffer(bytes(data), dtype=np.uint8).reshape(-1, bb)
+    sel = np.concatenate([blocks[r * k // be_:(r + 1) * k // be_] for r in rows]).reshape(-1)
+    wsel = oracle.dequantize(qt, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    ref = oracle.matmul_f32(x, wsel, nk=True, threads=8)
+    scale = float(np.max(np.abs(y)))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / scale <= TOL
+    assert np.all(np.isfinite(y))
+    w.free()
