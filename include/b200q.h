@@ -47,14 +47,19 @@ typedef enum {
     B200Q_Q6_K = 3,        /* 14 */
     B200Q_MXFP4 = 4,       /* 20 */
     B200Q_MXFP6_E2M3 = 5,  /* 21 */
-    B200Q_MXFP6_E3M2 = 6   /* 22 */
+    B200Q_MXFP6_E3M2 = 6,  /* 22 */
+    B200Q_Q2_K = 7,        /* 10 */
+    B200Q_Q3_K = 8,        /* 11 */
+    B200Q_Q5_K = 9         /* 13 */
 } b200q_qtype;
 
 /* Byte layout of the blocks.
  * RF   = what the reference's CPU dequant parses: Q4_0 20 B (f32 scale), Q8_0 36 B, Q4_K 256 B,
  *        Q6_K 256 B, MXFP4 17 B (int8 exponent, high nibble first), MXFP6 25 B
  *        (src/kernels/quant/{q4_0,q8_0,q4_k,q6_k}.rs, src/loader/dequant.rs:41-132).
- * GGUF = llama.cpp blocks: 18 / 34 / 144 / 210 / 17 / 25 bytes. */
+ * GGUF = llama.cpp blocks: 18 / 34 / 144 / 210 / 17 / 25 bytes.
+ * Q2_K / Q3_K / Q5_K: RF = 256-byte blocks of 16 sub-blocks (src/loader/dequant.rs:150-419), GGUF = 84 / 110 /
+ * 176 bytes. They have the dequantise kernel and the CUDA-core / shared-memory-operand matmul kernels. */
 typedef enum { B200Q_LAYOUT_RF = 0, B200Q_LAYOUT_GGUF = 1 } b200q_layout;
 
 /* How the flat element stream maps to the [n, k] weight matrix.
@@ -216,7 +221,7 @@ typedef struct {
     int n_dims;
     int64_t dims[4];      /* as stored in the file; unused entries are 1 */
     int ggml_type;        /* id in the file (GgufTensorType, src/loader/tensor_type.rs:16-32; 39 = ggml's MXFP4) */
-    int qtype;            /* b200q_qtype, or -1 when this library has no packed kernel for the type (F32, F16, Q2_K, Q3_K, Q5_K) */
+    int qtype;            /* b200q_qtype, or -1 when this library has no packed kernel for the type (F32, F16) */
     int layout;           /* b200q_layout the bytes are in */
     int64_t n, k;         /* rows x row length as b200q_weight_upload wants them */
     int64_t file_offset;  /* absolute */

@@ -489,6 +489,159 @@ void gguf_dequant_q6_k(const uint8_t* data, size_t nbytes, size_t n, float* out)
     }
 }
 
+/* ------------------------------------------------------------------ remaining K-quants
+ * RF layouts: src/loader/dequant.rs:150-233 (Q5_K), :243-322 (Q3_K), :326-419 (Q2_K). All three use 256-byte
+ * blocks of 16 sub-blocks with f16 scales at the block start; a block that is not completely inside the
+ * stream is skipped (":158 / :251 / :334 break"), so the per-element bounds tests inside are never taken. */
+
+void rf_dequant_q5_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        size_t bs = b * 256;
+        if (bs + 256 > nbytes) break;
+        for (int sb = 0; sb < 16; sb++) {
+            float scale = orc_f16_to_f32(le16(data + bs + (size_t)sb * 2));
+            float mn = (float)(int8_t)data[bs + 32 + (size_t)sb];
+            for (int i = 0; i < 16; i++) {
+                size_t e = b * 256 + (size_t)sb * 16 + (size_t)i;
+                if (e >= n) break;
+                int bit = i * 5, byte = bit / 8, off = bit % 8;
+                size_t qo = bs + 48 + (size_t)sb * 10 + (size_t)byte;
+                unsigned comb = ((unsigned)data[qo + 1] << 8) | (unsigned)data[qo];
+                unsigned q = (comb >> off) & 0x1F;
+                out[e] = mn + (float)q * scale;
+            }
+        }
+    }
+}
+
+void rf_dequant_q3_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        size_t bs = b * 256;
+        if (bs + 256 > nbytes) break;
+        for (int sb = 0; sb < 16; sb++) {
+            float scale = orc_f16_to_f32(le16(data + bs + (size_t)sb * 2));
+            unsigned qh = (data[bs + 32 + (size_t)(sb / 4)] >> ((sb % 4) * 2)) & 3u;
+            for (int i = 0; i < 16; i++) {
+                size_t e = b * 256 + (size_t)sb * 16 + (size_t)i;
+                if (e >= n) break;
+                int bit = i * 3, byte = bit / 8, off = bit % 8;
+                size_t qo = bs + 36 + (size_t)sb * 6 + (size_t)byte;
+                unsigned comb = ((unsigned)data[qo + 1] << 8) | (unsigned)data[qo];
+                unsigned low = (comb >> off) & 7u;
+                unsigned high = i < 8 ? ((qh >> i) & 1u) : 0u;   /* qh has two bits: only i = 0, 1 can see one */
+                float quant = (float)(int8_t)(low | (high << 3)) - 4.0f;
+                out[e] = quant * scale;
+            }
+        }
+    }
+}
+
+void rf_dequant_q2_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        size_t bs = b * 256;
+        if (bs + 256 > nbytes) break;
+        for (int sb = 0; sb < 16; sb++) {
+            float scale = orc_f16_to_f32(le16(data + bs + (size_t)sb * 2));
+            float mn = orc_f16_to_f32(le16(data + bs + 32 + (size_t)sb * 2));
+            unsigned qh = (data[bs + 64 + (size_t)(sb / 8)] >> (sb % 8)) & 1u;
+            for (int i = 0; i < 16; i++) {
+                size_t e = b * 256 + (size_t)sb * 16 + (size_t)i;
+                if (e >= n) break;
+                int bit = i * 2, byte = bit / 8, off = bit % 8;
+                size_t qo = bs + 68 + (size_t)sb * 4 + (size_t)byte;
+                unsigned comb = ((unsigned)data[qo + 1] << 8) | (unsigned)data[qo];
+                unsigned low = (comb >> off) & 3u;
+                unsigned high = i < 8 ? ((qh >> i) & 1u) : 0u;   /* qh is one bit: only i = 0 can see it */
+                float quant = (float)(int8_t)(low | (high << 2));
+                out[e] = mn + quant * scale;
+            }
+        }
+    }
+}
+
+/* GGUF layouts (llama.cpp block_q2_K 84 B, block_q3_K 110 B, block_q5_K 176 B). */
+
+void gguf_dequant_q2_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    /* scales[16] (low nibble scale, high nibble min), qs[64], f16 d, f16 dmin. Element 128h + 32j + l is
+     * (qs[32h + l] >> 2j) & 3; value = (d*sc)*q - (dmin*m) with the scale pair of its group of 16. */
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        if ((b + 1) * 84 > nbytes) break;
+        const uint8_t* p = data + b * 84;
+        float d = orc_f16_to_f32(le16(p + 80)), dmin = orc_f16_to_f32(le16(p + 82));
+        for (int i = 0; i < 256; i++) {
+            size_t e = b * 256 + (size_t)i;
+            if (e >= n) break;
+            int h = i / 128, j = (i % 128) / 32, l = i % 32;
+            unsigned q = (p[16 + 32 * h + l] >> (2 * j)) & 3u;
+            float dl = d * (float)(p[i / 16] & 0x0F);
+            float ml = dmin * (float)(p[i / 16] >> 4);
+            out[e] = dl * (float)q - ml;
+        }
+    }
+}
+
+void gguf_dequant_q3_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    /* hmask[32], qs[64], scales[12], f16 d. Sixteen 6-bit scales (minus 32): low 4 bits from the nibbles of
+     * bytes 0..7, high 2 bits from bytes 8..11. Element 128h + 32j + l has low bits (qs[32h + l] >> 2j) & 3 and
+     * subtracts 4 when bit (e / 32) of hmask[l] is CLEAR. */
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        if ((b + 1) * 110 > nbytes) break;
+        const uint8_t* p = data + b * 110;
+        const uint8_t* hm = p;
+        const uint8_t* qs = p + 32;
+        const uint8_t* sc = p + 96;
+        float d = orc_f16_to_f32(le16(p + 108));
+        for (int i = 0; i < 256; i++) {
+            size_t e = b * 256 + (size_t)i;
+            if (e >= n) break;
+            int g = i / 16;
+            unsigned lo = g < 8 ? (sc[g] & 0x0Fu) : (unsigned)(sc[g - 8] >> 4);
+            unsigned hi = (unsigned)(sc[8 + (g % 4)] >> (2 * (g / 4))) & 3u;
+            float dl = d * (float)((int)(int8_t)(lo | (hi << 4)) - 32);
+            int h = i / 128, j = (i % 128) / 32, l = i % 32;
+            int ql = (int)((qs[32 * h + l] >> (2 * j)) & 3u);
+            int bitclear = ((hm[l] >> (i / 32)) & 1u) ^ 1u;
+            out[e] = dl * (float)(ql - (bitclear << 2));
+        }
+    }
+}
+
+void gguf_dequant_q5_k(const uint8_t* data, size_t nbytes, size_t n, float* out) {
+    /* f16 d, f16 dmin, 12 bytes of 6-bit scales/mins (as Q4_K), qh[32], qs[128]. Element 64c + 32nib + l has
+     * low 4 bits (qs[32c + l] >> 4nib) & 15 and bit 4 = bit (e / 32) of qh[l]. */
+    memset(out, 0, n * sizeof(float));
+    size_t nb = (n + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        if ((b + 1) * 176 > nbytes) break;
+        const uint8_t* p = data + b * 176;
+        float d = orc_f16_to_f32(le16(p)), dmin = orc_f16_to_f32(le16(p + 2));
+        const uint8_t* qh = p + 16;
+        const uint8_t* qs = p + 48;
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            q4k_scale_min(p + 4, j, &sc, &m);
+            float d1 = d * (float)sc, dm = dmin * (float)m;
+            for (int l = 0; l < 32; l++) {
+                size_t e = b * 256 + (size_t)j * 32 + (size_t)l;
+                if (e >= n) break;
+                unsigned lo = (j & 1) ? (unsigned)(qs[(j / 2) * 32 + l] >> 4) : (qs[(j / 2) * 32 + l] & 0x0Fu);
+                unsigned hi = (qh[l] >> j) & 1u;
+                out[e] = d1 * (float)(lo | (hi << 4)) - dm;
+            }
+        }
+    }
+}
+
 static const int8_t k_e2m1_x2[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
 
 static inline float e8m0_half(uint8_t x) {
@@ -566,23 +719,25 @@ void gguf_dequant_mxfp6_e3m2(const uint8_t* data, size_t nbytes, size_t n, float
 
 /* ------------------------------------------------------------- dispatcher */
 
-size_t orc_block_elems(int qtype) { return (qtype == 2 || qtype == 3) ? 256 : 32; }
+size_t orc_block_elems(int qtype) { return (qtype == 2 || qtype == 3 || qtype >= 7) ? 256 : 32; }
 
 size_t orc_block_bytes(int qtype, int layout) {
-    static const size_t rf[7] = {20, 36, 256, 256, 17, 25, 25};
-    static const size_t gg[7] = {18, 34, 144, 210, 17, 25, 25};
-    if (qtype < 0 || qtype > 6) return 0;
+    static const size_t rf[10] = {20, 36, 256, 256, 17, 25, 25, 256, 256, 256};
+    static const size_t gg[10] = {18, 34, 144, 210, 17, 25, 25, 84, 110, 176};
+    if (qtype < 0 || qtype > 9) return 0;
     return layout == 0 ? rf[qtype] : gg[qtype];
 }
 
 typedef void (*deq_fn)(const uint8_t*, size_t, size_t, float*);
 
 static deq_fn pick(int qtype, int layout) {
-    static const deq_fn rf[7] = {rf_dequant_q4_0, rf_dequant_q8_0, rf_dequant_q4_k, rf_dequant_q6_k,
-                                 rf_dequant_mxfp4, rf_dequant_mxfp6, rf_dequant_mxfp6};
-    static const deq_fn gg[7] = {gguf_dequant_q4_0, gguf_dequant_q8_0, gguf_dequant_q4_k, gguf_dequant_q6_k,
-                                 gguf_dequant_mxfp4, gguf_dequant_mxfp6_e2m3, gguf_dequant_mxfp6_e3m2};
-    if (qtype < 0 || qtype > 6 || layout < 0 || layout > 1) return 0;
+    static const deq_fn rf[10] = {rf_dequant_q4_0, rf_dequant_q8_0, rf_dequant_q4_k, rf_dequant_q6_k,
+                                  rf_dequant_mxfp4, rf_dequant_mxfp6, rf_dequant_mxfp6,
+                                  rf_dequant_q2_k, rf_dequant_q3_k, rf_dequant_q5_k};
+    static const deq_fn gg[10] = {gguf_dequant_q4_0, gguf_dequant_q8_0, gguf_dequant_q4_k, gguf_dequant_q6_k,
+                                  gguf_dequant_mxfp4, gguf_dequant_mxfp6_e2m3, gguf_dequant_mxfp6_e3m2,
+                                  gguf_dequant_q2_k, gguf_dequant_q3_k, gguf_dequant_q5_k};
+    if (qtype < 0 || qtype > 9 || layout < 0 || layout > 1) return 0;
     return layout == 0 ? rf[qtype] : gg[qtype];
 }
 

@@ -58,6 +58,12 @@ void rf_mxfpblock_unpack_mxfp6(int8_t e, const uint8_t* elems24, float* out32); 
 /* ---- GGUF layout: what the benchmark configurations describe ---------------- */
 void gguf_dequant_q4_0(const uint8_t* data, size_t nbytes, size_t n, float* out);
 void gguf_dequant_q8_0(const uint8_t* data, size_t nbytes, size_t n, float* out);
+void rf_dequant_q5_k(const uint8_t* data, size_t nbytes, size_t n, float* out);   /* src/loader/dequant.rs:150-233 */
+void rf_dequant_q3_k(const uint8_t* data, size_t nbytes, size_t n, float* out);   /* src/loader/dequant.rs:243-322 */
+void rf_dequant_q2_k(const uint8_t* data, size_t nbytes, size_t n, float* out);   /* src/loader/dequant.rs:326-419 */
+void gguf_dequant_q2_k(const uint8_t* data, size_t nbytes, size_t n, float* out);
+void gguf_dequant_q3_k(const uint8_t* data, size_t nbytes, size_t n, float* out);
+void gguf_dequant_q5_k(const uint8_t* data, size_t nbytes, size_t n, float* out);
 void gguf_dequant_q4_k(const uint8_t* data, size_t nbytes, size_t n, float* out);
 void gguf_dequant_q6_k(const uint8_t* data, size_t nbytes, size_t n, float* out);
 void gguf_dequant_mxfp4(const uint8_t* data, size_t nbytes, size_t n, float* out);

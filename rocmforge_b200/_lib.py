@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libb200q.so")
 OK = 0
 ERR_INIT, ERR_NO_DEVICE, ERR_ALLOC, ERR_COPY, ERR_LAUNCH, ERR_DEVICE, ERR_INVALID, ERR_UNSUPPORTED, ERR_TIMEOUT = \
     -1, -2, -3, -4, -5, -6, -7, -8, -9
-Q4_0, Q8_0, Q4_K, Q6_K, MXFP4, MXFP6_E2M3, MXFP6_E3M2 = range(7)
+Q4_0, Q8_0, Q4_K, Q6_K, MXFP4, MXFP6_E2M3, MXFP6_E3M2, Q2_K, Q3_K, Q5_K = range(10)
 LAYOUT_RF, LAYOUT_GGUF = 0, 1
 ORIENT_NK, ORIENT_KN = 0, 1
 F32, BF16 = 0, 1

@@ -57,7 +57,8 @@ int ensure_scratch(b200q_ctx* ctx, size_t bytes, int which = 0);
     } while (0)
 
 // Expands `X(F)` for every format index (qtype*2+layout).
-#define B200Q_FOR_EACH_FMT(X) X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13)
+#define B200Q_FOR_EACH_FMT(X) \
+    X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14) X(15) X(16) X(17) X(18) X(19)
 
 // kernels_dequant.cu
 int launch_fused_dequant_rmsnorm(b200q_ctx* ctx, int fmt, const WView& v, const float* d_weight, float* d_out, int64_t rows,

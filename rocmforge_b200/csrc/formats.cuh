@@ -10,6 +10,8 @@
 //   Q4_K  RF   {256 raw}                          Q4_K  GGUF {144 raw}
 //   Q6_K  RF   {256 raw}                          Q6_K  GGUF {128 ql, 64 qh, 16 scales, 2 d}
 //   MXFP4 RF/GGUF {1 exponent, 16 codes}          MXFP6 RF/GGUF {1 exponent, 24 codes}
+//   Q2_K/Q3_K/Q5_K RF {256 raw}                   Q2_K GGUF {16 scales, 64 qs, 4 d+dmin}
+//   Q3_K  GGUF {32 hmask, 64 qs, 12 scales, 2 d}  Q5_K GGUF {176 raw}
 //
 // decode8<F>() returns the fp32 values of 8 consecutive weights exactly as the reference CPU code
 // computes them (ROCmForge src/kernels/quant/{q4_0,q8_0,q4_k,q6_k}.rs, src/loader/dequant.rs:41-132)
@@ -21,7 +23,7 @@
 
 namespace b200q {
 
-enum : int { Q4_0 = 0, Q8_0 = 1, Q4_K = 2, Q6_K = 3, MXFP4 = 4, MXFP6_E2M3 = 5, MXFP6_E3M2 = 6, NUM_QTYPES = 7 };
+enum : int { Q4_0 = 0, Q8_0 = 1, Q4_K = 2, Q6_K = 3, MXFP4 = 4, MXFP6_E2M3 = 5, MXFP6_E3M2 = 6, Q2_K = 7, Q3_K = 8, Q5_K = 9, NUM_QTYPES = 10 };
 enum : int { RF = 0, GGUF = 1 };
 constexpr int NUM_FMTS = NUM_QTYPES * 2;
 __host__ __device__ constexpr int fmt_of(int qtype, int layout) { return qtype * 2 + layout; }
@@ -53,6 +55,12 @@ __host__ __device__ constexpr FmtInfo fmt_info(int fmt) {
         case fmt_of(MXFP6_E2M3, GGUF):
         case fmt_of(MXFP6_E3M2, RF):
         case fmt_of(MXFP6_E3M2, GGUF): return {32, 25, 2, {1, 24, 0, 0}};
+        case fmt_of(Q2_K, RF):
+        case fmt_of(Q3_K, RF):
+        case fmt_of(Q5_K, RF): return {256, 256, 1, {256, 0, 0, 0}};
+        case fmt_of(Q2_K, GGUF): return {256, 84, 3, {16, 64, 4, 0}};
+        case fmt_of(Q3_K, GGUF): return {256, 110, 4, {32, 64, 12, 2}};
+        case fmt_of(Q5_K, GGUF): return {256, 176, 1, {176, 0, 0, 0}};
         default: return {0, 0, 0, {0, 0, 0, 0}};
     }
 }
@@ -263,6 +271,100 @@ __device__ __forceinline__ void decode8(const WView& v, int64_t g, int part, flo
         for (int i = 0; i < 8; i++) {
             uint32_t c = (uint32_t)((bits >> (6 * i)) & 63);
             out[i] = __fmul_rn(d, F == fmt_of(MXFP6_E2M3, GGUF) ? ocp_e2m3(c) : ocp_e3m2(c));
+        }
+    } else if constexpr (F == fmt_of(Q5_K, RF) || F == fmt_of(Q3_K, RF) || F == fmt_of(Q2_K, RF)) {
+        // 256-byte blocks of 16 sub-blocks x 16 weights (src/loader/dequant.rs:150-419): f16 scales @0, then
+        //   Q5_K: int8 mins @32, 5-bit codes 10 bytes per sub-block @48;            value = min + q * scale
+        //   Q3_K: 2 "high" bits per sub-block @32, 3-bit codes 6 bytes per sub-block @36; value = (q - 4) * scale
+        //   Q2_K: f16 mins @32, 1 "high" bit per sub-block @64, 2-bit codes 4 bytes @68;  value = min + q * scale
+        // The eight weights of a piece lie in one sub-block (i = 0 or 8 inside it).
+        const uint8_t* b = v.p[0] + (g >> 3) * 256;
+        const int i0 = (int)(g & 7) * 32 + part * 8, sb = i0 >> 4, i = i0 & 15;
+        const float scale = f16bits_to_f32((uint16_t)(b[2 * sb] | (b[2 * sb + 1] << 8)));
+        constexpr int BITS = F == fmt_of(Q5_K, RF) ? 5 : F == fmt_of(Q3_K, RF) ? 3 : 2;
+        constexpr int QOFF = F == fmt_of(Q5_K, RF) ? 48 : F == fmt_of(Q3_K, RF) ? 36 : 68;
+        const uint8_t* q = b + QOFF + sb * (2 * BITS) + (i * BITS) / 8;      // i * BITS is a multiple of 8
+        uint64_t bits = 0;
+#pragma unroll
+        for (int t = 0; t < BITS; t++) bits |= (uint64_t)q[t] << (8 * t);   // 8 codes = BITS bytes
+        float mn = 0.0f;
+        uint32_t qh = 0;
+        if constexpr (F == fmt_of(Q5_K, RF)) mn = (float)(int8_t)b[32 + sb];
+        if constexpr (F == fmt_of(Q2_K, RF)) {
+            mn = f16bits_to_f32((uint16_t)(b[32 + 2 * sb] | (b[33 + 2 * sb] << 8)));
+            qh = (b[64 + (sb >> 3)] >> (sb & 7)) & 1u;
+        }
+        if constexpr (F == fmt_of(Q3_K, RF)) qh = (b[32 + (sb >> 2)] >> ((sb & 3) * 2)) & 3u;
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const uint32_t low = (uint32_t)(bits >> (BITS * t)) & ((1u << BITS) - 1);
+            const int e = i + t;                                              // element inside the sub-block
+            if constexpr (F == fmt_of(Q5_K, RF)) {
+                out[t] = __fadd_rn(mn, __fmul_rn((float)low, scale));
+            } else if constexpr (F == fmt_of(Q3_K, RF)) {
+                const uint32_t high = e < 8 ? (qh >> e) & 1u : 0u;
+                out[t] = __fmul_rn(__fsub_rn((float)(int)(low | (high << 3)), 4.0f), scale);
+            } else {
+                const uint32_t high = e < 8 ? (qh >> e) & 1u : 0u;
+                out[t] = __fadd_rn(mn, __fmul_rn((float)(int)(low | (high << 2)), scale));
+            }
+        }
+    } else if constexpr (F == fmt_of(Q2_K, GGUF) || F == fmt_of(Q3_K, GGUF)) {
+        // element 128h + 32j + l of a block has its low two bits at (qs[32h + l] >> 2j) & 3
+        const int64_t blk = g >> 3;
+        const int i0 = (int)(g & 7) * 32 + part * 8;
+        const int h = i0 >> 7, j = (i0 & 127) >> 5, l0 = i0 & 31;
+        const uint8_t* qs = v.p[1] + blk * 64 + 32 * h + l0;
+        const uint32_t w0 = ld32(qs), w1 = ld32(qs + 4);
+        if constexpr (F == fmt_of(Q2_K, GGUF)) {
+            // planes scales[16] (scale | min << 4), qs[64], {f16 d, f16 dmin}; value = (d*sc)*q - dmin*m
+            const float d = f16bits_to_f32(ld16(v.p[2] + blk * 4)), dmin = f16bits_to_f32(ld16(v.p[2] + blk * 4 + 2));
+            const uint32_t sc = v.p[0][blk * 16 + (i0 >> 4)];
+            const float dl = __fmul_rn(d, (float)(sc & 15)), ml = __fmul_rn(dmin, (float)(sc >> 4));
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                out[t] = __fsub_rn(__fmul_rn(dl, (float)((w0 >> (8 * t + 2 * j)) & 3)), ml);
+                out[t + 4] = __fsub_rn(__fmul_rn(dl, (float)((w1 >> (8 * t + 2 * j)) & 3)), ml);
+            }
+        } else {
+            // planes hmask[32], qs[64], scales[12], f16 d; sixteen 6-bit scales minus 32; a CLEAR hmask bit
+            // (bit e/32 of hmask[l]) subtracts 4
+            const float d = f16bits_to_f32(ld16(v.p[3] + blk * 2));
+            const uint8_t* sc = v.p[2] + blk * 12;
+            const int g16 = i0 >> 4;
+            const uint32_t lo = g16 < 8 ? (sc[g16] & 15u) : (uint32_t)(sc[g16 - 8] >> 4);
+            const uint32_t hi = (uint32_t)(sc[8 + (g16 & 3)] >> (2 * (g16 >> 2))) & 3u;
+            const float dl = __fmul_rn(d, (float)((int)(lo | (hi << 4)) - 32));
+            const uint8_t* hm = v.p[0] + blk * 32 + l0;
+            const uint32_t m0 = ld32(hm), m1 = ld32(hm + 4);
+            const int bit = i0 >> 5;
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const int qa = (int)((w0 >> (8 * t + 2 * j)) & 3) - (int)((((m0 >> (8 * t + bit)) & 1) ^ 1) << 2);
+                const int qb = (int)((w1 >> (8 * t + 2 * j)) & 3) - (int)((((m1 >> (8 * t + bit)) & 1) ^ 1) << 2);
+                out[t] = __fmul_rn(dl, (float)qa);
+                out[t + 4] = __fmul_rn(dl, (float)qb);
+            }
+        }
+    } else if constexpr (F == fmt_of(Q5_K, GGUF)) {
+        // 176-byte block: d, dmin, 12 scale bytes (as Q4_K), qh[32], qs[128]; element 64c + 32nib + l has low
+        // bits (qs[32c + l] >> 4nib) & 15 and bit 4 = bit (e / 32) of qh[l]; value = (d*sc)*q - dmin*m
+        const uint8_t* b = v.p[0] + (g >> 3) * 176;
+        const int j = (int)(g & 7);
+        const float d = f16bits_to_f32(ld16(b)), dmin = f16bits_to_f32(ld16(b + 2));
+        uint32_t sc, m;
+        q4k_scale_min(b + 4, j, sc, m);
+        const float d1 = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)m);
+        const uint8_t* q = b + 48 + (j >> 1) * 32 + part * 8;
+        const uint8_t* qh = b + 16 + part * 8;
+        const uint32_t w0 = ld32(q), w1 = ld32(q + 4), h0 = ld32(qh), h1 = ld32(qh + 4);
+        const int sh = (j & 1) * 4;
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const uint32_t qa = ((w0 >> (8 * t + sh)) & 15) | (((h0 >> (8 * t + j)) & 1) << 4);
+            const uint32_t qb = ((w1 >> (8 * t + sh)) & 15) | (((h1 >> (8 * t + j)) & 1) << 4);
+            out[t] = __fsub_rn(__fmul_rn(d1, (float)qa), dm);
+            out[t + 4] = __fsub_rn(__fmul_rn(d1, (float)qb), dm);
         }
     }
 }

@@ -41,7 +41,7 @@ struct TensorEntry {
     uint64_t rel_offset = 0;   // as stored in the file
     uint64_t abs_offset = 0;   // file offset of the first byte
     uint64_t nbytes = 0;
-    int qtype = -1;            // b200q_qtype, or -1 for types this library has no kernel for (F32, F16, Q2/3/5_K)
+    int qtype = -1;            // b200q_qtype, or -1 for types this library has no kernel for (F32, F16)
     int64_t n = 0, k = 0;      // rows x row length as the kernels see them
 };
 
@@ -133,10 +133,10 @@ bool map_type(uint32_t id, int* qtype, int* known_block, int* plain_bytes) {
         case 1: *plain_bytes = 2; return true;    // F16
         case 2: *qtype = B200Q_Q4_0; return true;
         case 8: *qtype = B200Q_Q8_0; return true;
-        case 10: *known_block = 84; return true;   // Q2_K (no kernel here)
-        case 11: *known_block = 110; return true;  // Q3_K
+        case 10: *qtype = B200Q_Q2_K; return true;
+        case 11: *qtype = B200Q_Q3_K; return true;
         case 12: *qtype = B200Q_Q4_K; return true;
-        case 13: *known_block = 176; return true;  // Q5_K
+        case 13: *qtype = B200Q_Q5_K; return true;
         case 14: *qtype = B200Q_Q6_K; return true;
         case 20: case 39: *qtype = B200Q_MXFP4; return true;
         case 21: *qtype = B200Q_MXFP6_E2M3; return true;

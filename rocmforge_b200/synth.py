@@ -13,13 +13,13 @@ scales/mins uniform bytes; MXFP block exponents uniform integers in [-8, 0].
 """
 import numpy as np
 
-Q4_0, Q8_0, Q4_K, Q6_K, MXFP4, MXFP6_E2M3, MXFP6_E3M2 = range(7)
+Q4_0, Q8_0, Q4_K, Q6_K, MXFP4, MXFP6_E2M3, MXFP6_E3M2, Q2_K, Q3_K, Q5_K = range(10)
 RF, GGUF = 0, 1
-QNAMES = ["Q4_0", "Q8_0", "Q4_K", "Q6_K", "MXFP4", "MXFP6_E2M3", "MXFP6_E3M2"]
+QNAMES = ["Q4_0", "Q8_0", "Q4_K", "Q6_K", "MXFP4", "MXFP6_E2M3", "MXFP6_E3M2", "Q2_K", "Q3_K", "Q5_K"]
 LAYOUT_NAMES = ["RF", "GGUF"]
 
-_BLOCK_ELEMS = [32, 32, 256, 256, 32, 32, 32]
-_BLOCK_BYTES = {RF: [20, 36, 256, 256, 17, 25, 25], GGUF: [18, 34, 144, 210, 17, 25, 25]}
+_BLOCK_ELEMS = [32, 32, 256, 256, 32, 32, 32, 256, 256, 256]
+_BLOCK_BYTES = {RF: [20, 36, 256, 256, 17, 25, 25, 256, 256, 256], GGUF: [18, 34, 144, 210, 17, 25, 25, 84, 110, 176]}
 
 
 def block_elems(qtype):
@@ -102,6 +102,25 @@ def gen_packed(qtype, layout, n_elements, rng):
         e = rng.integers(-8, 1, size=nb, dtype=np.int16)
         out[:, 0] = (e.astype(np.int8).view(np.uint8) if layout == RF else (e + 127).astype(np.uint8))
         out[:, 1:25] = rng.integers(0, 256, size=(nb, 24), dtype=np.uint8)
+    elif qtype in (Q2_K, Q3_K, Q5_K):
+        if layout == RF:   # 16 f16 scales @0, then mins / high bits / packed codes: every remaining byte is data
+            out[:, 0:32] = _f16_scales(rng, (nb, 16), 0.02).view(np.uint8).reshape(nb, 32)
+            if qtype == Q2_K:   # 16 f16 mins @32
+                out[:, 32:64] = _f16_scales(rng, (nb, 16), 0.02).view(np.uint8).reshape(nb, 32)
+                out[:, 64:256] = rng.integers(0, 256, size=(nb, 192), dtype=np.uint8)
+            else:
+                out[:, 32:256] = rng.integers(0, 256, size=(nb, 224), dtype=np.uint8)
+        elif qtype == Q2_K:   # scales 16, qs 64, f16 d, f16 dmin
+            out[:, 0:80] = rng.integers(0, 256, size=(nb, 80), dtype=np.uint8)
+            out[:, 80:82] = _f16_scales(rng, nb, 0.02).view(np.uint8).reshape(nb, 2)
+            out[:, 82:84] = _f16_scales(rng, nb, 0.02).view(np.uint8).reshape(nb, 2)
+        elif qtype == Q3_K:   # hmask 32, qs 64, scales 12, f16 d
+            out[:, 0:108] = rng.integers(0, 256, size=(nb, 108), dtype=np.uint8)
+            out[:, 108:110] = _f16_scales(rng, nb, 0.02).view(np.uint8).reshape(nb, 2)
+        else:                 # Q5_K: f16 d, f16 dmin, scales 12, qh 32, qs 128
+            out[:, 0:2] = _f16_scales(rng, nb, 0.02).view(np.uint8).reshape(nb, 2)
+            out[:, 2:4] = _f16_scales(rng, nb, 0.02).view(np.uint8).reshape(nb, 2)
+            out[:, 4:176] = rng.integers(0, 256, size=(nb, 172), dtype=np.uint8)
     else:
         raise ValueError(f"unknown qtype {qtype}")
     return out.reshape(-1)

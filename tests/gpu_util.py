@@ -4,7 +4,7 @@ import numpy as np
 from rocmforge_b200 import _lib, synth
 from rocmforge_b200.backend import B200Backend, QuantizedWeight
 
-ALL_FMTS = [(qt, lay) for qt in range(7) for lay in (0, 1)]
+ALL_FMTS = [(qt, lay) for qt in range(10) for lay in (0, 1)]
 FMT_IDS = [f"{synth.QNAMES[q]}-{synth.LAYOUT_NAMES[l]}" for q, l in ALL_FMTS]
 
 _backend = None

@@ -33,13 +33,13 @@ def test_header_and_binding_agree(lib):
 
 
 def test_size_queries_match_the_format_tables(lib):
-    for qt in range(7):
+    for qt in range(10):
         assert lib.b200q_block_elems(qt) == synth.block_elems(qt)
         for lay in (0, 1):
             assert lib.b200q_block_bytes(qt, lay) == synth.block_bytes(qt, lay)
             for n in (0, 1, 31, 32, 33, 255, 256, 257, 4864 * 896):
                 assert lib.b200q_tensor_bytes(qt, lay, n) == synth.tensor_bytes(qt, lay, n)
-    assert lib.b200q_block_bytes(9, 0) == 0 and lib.b200q_block_elems(-1) == 0
+    assert lib.b200q_block_bytes(10, 0) == 0 and lib.b200q_block_elems(-1) == 0
     # the byte counts the benchmark configurations are quoted on
     assert lib.b200q_tensor_bytes(_lib.Q4_0, 1, 4864 * 896) == 2_451_456
     assert lib.b200q_tensor_bytes(_lib.Q4_0, 0, 4864 * 896) == 2_723_840

@@ -145,7 +145,7 @@ def test_full_size_lm_head_dequant_properties(be, oracle):
 def test_argument_errors_are_status_codes(be):
     out = be.allocate_buffer(1024)
     with pytest.raises(_lib.B200QError) as e:
-        ops.dequantize_gpu(be, 9, b"\0" * 20, out, 32)
+        ops.dequantize_gpu(be, 10, b"\0" * 20, out, 32)      # no such tensor type
     assert e.value.status == _lib.ERR_INVALID
     with pytest.raises(_lib.B200QError) as e:
         ops.dequantize_gpu(be, synth.Q4_0, b"\0" * 20, out, 4096)       # output buffer too small

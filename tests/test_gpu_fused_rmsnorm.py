@@ -11,7 +11,7 @@ from gpu_util import backend
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-5
-ALL = [(q, l) for q in range(7) for l in (synth.RF, synth.GGUF)]
+ALL = [(q, l) for q in range(10) for l in (synth.RF, synth.GGUF)]
 IDS = [f"{synth.QNAMES[q]}-{synth.LAYOUT_NAMES[l]}" for q, l in ALL]
 
 

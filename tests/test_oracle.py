@@ -148,7 +148,7 @@ def test_rf_mxfp_streams_follow_the_dispatcher_rules(oracle):
 def test_partial_and_truncated_streams(oracle):
     """Tail rules: n may stop inside a block; a stream that ends early leaves zeros."""
     rng = synth.rng_for(5)
-    for qt in range(7):
+    for qt in range(10):
         for lay in (synth.RF, synth.GGUF):
             be = synth.block_elems(qt)
             data = synth.gen_packed(qt, lay, 3 * be, rng)
@@ -174,7 +174,8 @@ def test_gguf_layout_against_gguf_package_live(oracle):
     from gguf import quants
     types = {synth.Q4_0: gguf.GGMLQuantizationType.Q4_0, synth.Q8_0: gguf.GGMLQuantizationType.Q8_0,
              synth.Q4_K: gguf.GGMLQuantizationType.Q4_K, synth.Q6_K: gguf.GGMLQuantizationType.Q6_K,
-             synth.MXFP4: gguf.GGMLQuantizationType.MXFP4}
+             synth.MXFP4: gguf.GGMLQuantizationType.MXFP4, synth.Q2_K: gguf.GGMLQuantizationType.Q2_K,
+             synth.Q3_K: gguf.GGMLQuantizationType.Q3_K, synth.Q5_K: gguf.GGMLQuantizationType.Q5_K}
     for qt, gt in types.items():
         rng = synth.rng_for(300 + qt)
         nblk = 100_000 if synth.block_elems(qt) == 32 else 12_500
@@ -246,3 +247,39 @@ def test_matmul_orders_and_threads(oracle):
     data = synth.gen_packed(synth.Q4_K, synth.GGUF, 256 * 50, rng)
     assert np.array_equal(oracle.dequantize(synth.Q4_K, synth.GGUF, data, 256 * 50),
                           oracle.dequantize(synth.Q4_K, synth.GGUF, data, 256 * 50, threads=3))
+
+
+def test_rf_k_quants_follow_the_reference_loops(oracle):
+    """Q5_K / Q3_K / Q2_K in the reference's 256-byte layouts (src/loader/dequant.rs:150-419), evaluated here
+    element by element in Python from the same formulas; the reference has no test vectors for them."""
+    rng = synth.rng_for(77)
+    for qt in (synth.Q5_K, synth.Q3_K, synth.Q2_K):
+        data = synth.gen_packed(qt, synth.RF, 3 * 256, rng)
+        got = oracle.dequantize(qt, synth.RF, data, 3 * 256 - 5)
+        blk = data.reshape(3, 256).astype(np.int64)
+        want = np.zeros(3 * 256, np.float32)
+        for b in range(3):
+            for sb in range(16):
+                scale = np.float32(blk[b, 2 * sb:2 * sb + 2].astype(np.uint8).view(np.float16)[0])
+                for i in range(16):
+                    bits = {synth.Q5_K: 5, synth.Q3_K: 3, synth.Q2_K: 2}[qt]
+                    qoff = {synth.Q5_K: 48, synth.Q3_K: 36, synth.Q2_K: 68}[qt] + sb * 2 * bits + (i * bits) // 8
+                    comb = int(blk[b, qoff]) | (int(blk[b, qoff + 1]) << 8)
+                    low = (comb >> ((i * bits) % 8)) & ((1 << bits) - 1)
+                    if qt == synth.Q5_K:
+                        mn = np.float32(np.int8(np.uint8(blk[b, 32 + sb])))
+                        v = mn + np.float32(low) * scale
+                    elif qt == synth.Q3_K:
+                        qh = (int(blk[b, 32 + sb // 4]) >> ((sb % 4) * 2)) & 3
+                        high = (qh >> i) & 1 if i < 8 else 0
+                        v = (np.float32(low | (high << 3)) - np.float32(4.0)) * scale
+                    else:
+                        mn = np.float32(blk[b, 32 + 2 * sb:34 + 2 * sb].astype(np.uint8).view(np.float16)[0])
+                        qh = (int(blk[b, 64 + sb // 8]) >> (sb % 8)) & 1
+                        high = (qh >> i) & 1 if i < 8 else 0
+                        v = mn + np.float32(low | (high << 2)) * scale
+                    want[b * 256 + sb * 16 + i] = v
+        assert np.array_equal(got.view(np.uint32), want[:got.size].view(np.uint32)), synth.QNAMES[qt]
+        # a block that is not completely inside the stream is skipped
+        short = oracle.dequantize(qt, synth.RF, data[:2 * 256 + 100], 3 * 256)
+        assert np.all(short[512:] == 0.0) and np.array_equal(short[:512].view(np.uint32), want[:512].view(np.uint32))
