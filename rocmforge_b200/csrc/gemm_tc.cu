@@ -101,6 +101,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Tiled store shared -> global (clipped at the tensor's edges), tracked by the thread's bulk-copy groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int cx, int cy) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(cx), "r"(cy)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -256,6 +266,7 @@ struct GemmArgs {
     int* status;
     int n_extra;           // further copies of y to write: the same slice inside other GPUs' full outputs
     float* y_extra[7];     // (peer-mapped pointers; plain stores over NVLink, no loads)
+    int staged_epilogue;   // persistent kernel: finished tiles leave through shared memory and tiled TMA stores
 };
 
 // Warp roles (384 threads = 12 warps; a warp may only read the TMEM lane quarter warp_id % 4):
@@ -708,7 +719,8 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                    const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3, SkArgs k) {
+                    const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3,
+                    const __grid_constant__ CUtensorMap tmap_y, SkArgs k) {
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
@@ -726,9 +738,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint64_t* raw_empty = raw_full + RAW_STAGES;
     uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dfree + 1);
+    uint64_t* esync = dfree + 1;                 // the eight epilogue warps meet here (staged epilogue)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(esync + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
+    // staging tile of the epilogue: 64 activation rows x 128 weight rows of fp32 (one TMA store box)
+    float* stg = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(stored + 1) + 127) & ~(uintptr_t)127);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, nctas = gridDim.x;
@@ -745,6 +760,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         mbar_init(smem_u32(accum), 1);
         mbar_init(smem_u32(dfree), 8);
+        mbar_init(smem_u32(esync), 8);
         *abort_flag = 0;
         *stored = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -868,6 +884,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const float nibscale = nib ? 0.0625f : 1.0f;
         const __half2 k1024 = __float2half2_rn(1024.0f);
         int it = 0, rit = 0, seg = 0;
+        uint32_t esync_phase = 0;
         for (int u = u0; u < u1 && ok; seg++) {
             const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
@@ -1052,6 +1069,50 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             float* myslot = k.ws + (size_t)cta * SK_SLOT_FLOATS;
+            if (head && a.staged_epilogue) {
+                // Finished tile -> shared memory -> tiled TMA stores, 64 activation rows per round: the threads
+                // only move registers to shared memory, the copy engine writes y (clipped at the edges of y)
+                // while the next round, and then the next segment's main loop, proceed.
+                auto meet = [&]() {   // all eight epilogue warps, bounded
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(smem_u32(esync));
+                        if (!mbar_wait(smem_u32(esync), esync_phase, abort_flag, a.status, 13)) ok = false;
+                    }
+                    esync_phase ^= 1;
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                };
+                const int half_off = warp >= 8 ? 32 : 0;
+                for (int rnd = 0; rnd < a.bn && ok; rnd += 64) {
+                    const int c0 = rnd + half_off;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)min(c0, 480), v);
+                    for (int p = cta + 1; p < p_end; p++) {
+                        const float* ps = k.ws + (size_t)p * SK_SLOT_FLOATS + c0 * BM + r;
+                        if (c0 < a.bn) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(ps + j * BM));
+                        }
+                    }
+                    // the previous store must have finished READING the staging tile before it is overwritten
+                    if (warp == 4 && lane == 0) bulk_wait_read0();
+                    meet();
+                    if (!ok) break;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = tok0 + c0 + j;
+                        const float sc = tok < a.m ? __ldg(a.xscale + tok) : 0.0f;
+                        stg[(half_off + j) * BM + r] = __uint_as_float(v[j]) * sc;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    meet();
+                    if (!ok) break;
+                    if (warp == 4 && lane == 0) {
+                        tma_store_2d(&tmap_y, smem_u32(stg), row0, tok0 + rnd);
+                        bulk_commit();
+                    }
+                }
+            } else
             for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
@@ -1099,6 +1160,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             u += sb1 - sb0;
         }
+        if (warp == 4 && lane == 0) bulk_wait0();   // the tile stores of this thread are complete before shared memory goes away
     }
     // ---------------------------------------------------------------- teardown (every path ends here)
     tc_fence_before();
@@ -1269,6 +1331,18 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     a.n_extra = ctx->scatter_extra;
     for (int p = 0; p < ctx->scatter_extra; p++) a.y_extra[p] = ctx->scatter_y[p];
     dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
+    // tile stores of the persistent kernel's staged epilogue: y as a [m, n_local] fp32 tensor with row pitch ldy
+    CUtensorMap ymap = map;
+    const bool y_tma_ok = ctx->scatter_extra == 0 && (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(d_y) & 15) == 0;
+    if (y_tma_ok) {
+        cuuint64_t ydim[2] = {(cuuint64_t)w->n_local, (cuuint64_t)m};
+        cuuint64_t ystr[1] = {(cuuint64_t)ldy * 4};
+        cuuint32_t ybox[2] = {(cuuint32_t)BM, 64u};
+        r = enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d_y, ydim, ystr, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output) failed with code %d", who, (int)r);
+    }
+    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128;
     if (may_allocate && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
         (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30)) {
         // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads
@@ -1276,7 +1350,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
         const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 208 +
-                            (2 * STAGES + 2 * RAW_STAGES + 3) * 8 + 32;
+                            (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + 128;
+        a.staged_epilogue = 0;   // the three raw planes leave no room for the staging tile
         const int nsb = (int)(w->k / 256);
         CUtensorMap pm[3];
         const int pbytes[3] = {128, 64, 16};
@@ -1304,7 +1379,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], k);
+        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, k);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
@@ -1314,7 +1389,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
         const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 128 +
-                            (2 * STAGES + 2 * RAW_STAGES + 3) * 8 + 32;
+                            (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + STAGE_EPI_BYTES;
+        a.staged_epilogue = y_tma_ok ? 1 : 0;
         CUtensorMap wmap;
         const cuuint64_t row_bytes = (cuuint64_t)(w->k / 32) * 16;
         cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
@@ -1339,7 +1415,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, k);
+        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, ymap, k);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
@@ -1374,12 +1450,13 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             if (rc != B200Q_OK) return rc;
             SkArgs k{};
             k.a = a;
+            k.a.staged_epilogue = y_tma_ok ? 1 : 0;
             k.tiles_x = (int)grid.x; k.nsb = nsb; k.total_units = (int)units;
             k.ws = static_cast<float*>(ctx->sk_ws);
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 16, ctx->stream>>>(map, wmap, wmap, wmap, k);
+            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 32 + STAGE_EPI_BYTES, ctx->stream>>>(map, wmap, wmap, wmap, ymap, k);
             B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
