@@ -94,6 +94,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return mbar_wait_for(bar, parity, abort_flag, status, code, WAIT_BUDGET);
 }
 
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int cx, int cy, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -282,7 +283,9 @@ __device__ __forceinline__ int producer_index(int warp) { return warp - 2 - (war
 template <int F>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
+    // address space from the compiler and turn every access below into a generic one)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int b_stage_bytes = a.bn * BK * 2;
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
@@ -472,7 +475,9 @@ constexpr int A_SLOT_COLS = BK / 2;                   // 32
 
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_q4k_tmem_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
+    // address space from the compiler and turn every access below into a generic one)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int b_stage_bytes = a.bn * BK * 2;
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * b_stage_bytes;
@@ -716,18 +721,27 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 // 8 x 16 code bytes per 256 k from the code plane; the 8 exponent bytes come by a plain load). MXFP4 codes
 // become f16 by bit placement (E2M1 s|ee|m at bits 15|11..9 is value * 2^-14) and one HMUL2 with the block
 // scale 2^(e-127) * 2^14, which has to lie in the f16 range (block exponents 2^-28 .. 2^1).
+#ifdef B200Q_SK_TRACE
+// Scratch build only: time stamps go to shared memory and are copied out at the end of the kernel.
+__device__ long long g_sk_trace[160 * 128];
+#define SKT(i) do { if (lane == 0 && warp == 4 && (i) < 128) s_trace[(i)] = clock64(); } while (0)
+#else
+#define SKT(i)
+#endif
 template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3,
-                    const __grid_constant__ CUtensorMap tmap_y, SkArgs k) {
+                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_ws, SkArgs k) {
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
+    // address space from the compiler and turn every access below into a generic one)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int b_stage_bytes = a.bn * BK * 2;
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * b_stage_bytes;
@@ -739,11 +753,16 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
     uint64_t* esync = dfree + 1;                 // the eight epilogue warps meet here (staged epilogue)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(esync + 1);
+    uint64_t* pfull = esync + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
     // staging tile of the epilogue: 64 activation rows x 128 weight rows of fp32 (one TMA store box)
-    float* stg = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(stored + 1) + 127) & ~(uintptr_t)127);
+    float* stg = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(stored + 1) + ((128u - (smem_u32(stored + 1) & 127u)) & 127u));
+#ifdef B200Q_SK_TRACE
+    long long* s_trace = reinterpret_cast<long long*>(stg + 64 * BM);
+    if (threadIdx.x < 128) s_trace[threadIdx.x] = 0;
+#endif
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, nctas = gridDim.x;
@@ -761,6 +780,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         mbar_init(smem_u32(accum), 1);
         mbar_init(smem_u32(dfree), 8);
         mbar_init(smem_u32(esync), 8);
+        for (int s = 0; s < 4; s++) mbar_init(smem_u32(&pfull[s]), 1);
         *abort_flag = 0;
         *stored = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -888,6 +908,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int u = u0; u < u1 && ok; seg++) {
             const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
+            SKT(seg * 32 + 0);
             for (int sb = sb0; sb < sb1 && ok; sb++, rit++) {
                 const int rs = rit % RAW_STAGES;
                 const uint32_t rph = (uint32_t)(rit / RAW_STAGES) & 1;
@@ -1042,12 +1063,14 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             if (!ok) break;
             // ------------------------------------------------------------ epilogue of this segment
+            SKT(seg * 32 + 1);
             if (lane == 0) ok = mbar_wait(smem_u32(accum), (uint32_t)(seg & 1), abort_flag, a.status, 6);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             const bool head = sb0 == 0, whole = head && sb1 == k.nsb;
             const int row = row0 + r;
+            SKT(seg * 32 + 2);
             // partial sums this (owning) CTA has to add: the CTAs after it, until the tile's k range is covered
             int p_end = cta + 1;
             if (head && !whole) {
@@ -1069,6 +1092,21 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             float* myslot = k.ws + (size_t)cta * SK_SLOT_FLOATS;
+            SKT(seg * 32 + 3);
+            // An owner that adds partial sums is in the LAST segment of its range (its range ends inside the
+            // tile), so the activation stages are idle once this segment's MMAs are complete: the copy engine
+            // brings the first partial tile into them, 64 activation rows per copy, while the rounds below run;
+            // the adds then read shared memory instead of waiting for L2 32 lines at a time.
+            const bool pf = head && !whole && a.staged_epilogue && (a.bn & 63) == 0 && p_end > cta + 1 && ok &&
+                            u + (sb1 - sb0) == u1;
+            if (pf && warp == 4 && lane == 0) {
+                asm volatile("fence.proxy.async;" ::: "memory");   // the flag was acquired by plain loads; the copy engine reads next
+                for (int rnd = 0; rnd < a.bn; rnd += 64) {
+                    const uint32_t pb = smem_u32(&pfull[rnd >> 6]);
+                    mbar_arrive_expect_tx(pb, 64u * BM * 4u);
+                    tma_load_2d(smem_u32(sB + (rnd >> 6) * (64 * BM * 4)), &tmap_ws, 0, (cta + 1) * 256 + rnd, pb);
+                }
+            }
             if (head && a.staged_epilogue) {
                 // Finished tile -> shared memory -> tiled TMA stores, 64 activation rows per round: the threads
                 // only move registers to shared memory, the copy engine writes y (clipped at the edges of y)
@@ -1087,7 +1125,16 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int c0 = rnd + half_off;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)min(c0, 480), v);
-                    for (int p = cta + 1; p < p_end; p++) {
+                    SKT(seg * 32 + 4 + (rnd >> 6) * 5);
+                    if (pf) {
+                        if (lane == 0) ok = mbar_wait(smem_u32(&pfull[rnd >> 6]), 0, abort_flag, a.status, 14);
+                        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                        if (!ok) break;
+                        const float* sp = reinterpret_cast<const float*>(sB + (rnd >> 6) * (64 * BM * 4)) + half_off * BM + r;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + sp[j * BM]);
+                    }
+                    for (int p = cta + 1 + (pf ? 1 : 0); p < p_end; p++) {
                         const float* ps = k.ws + (size_t)p * SK_SLOT_FLOATS + c0 * BM + r;
                         if (c0 < a.bn) {
 #pragma unroll
@@ -1095,9 +1142,11 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         }
                     }
                     // the previous store must have finished READING the staging tile before it is overwritten
+                    SKT(seg * 32 + 5 + (rnd >> 6) * 5);
                     if (warp == 4 && lane == 0) bulk_wait_read0();
                     meet();
                     if (!ok) break;
+                    SKT(seg * 32 + 6 + (rnd >> 6) * 5);
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int tok = tok0 + c0 + j;
@@ -1105,12 +1154,14 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         stg[(half_off + j) * BM + r] = __uint_as_float(v[j]) * sc;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    SKT(seg * 32 + 7 + (rnd >> 6) * 5);
                     meet();
                     if (!ok) break;
                     if (warp == 4 && lane == 0) {
                         tma_store_2d(&tmap_y, smem_u32(stg), row0, tok0 + rnd);
                         bulk_commit();
                     }
+                    SKT(seg * 32 + 8 + (rnd >> 6) * 5);
                 }
             } else
             for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
@@ -1143,6 +1194,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(dfree));
+            SKT(seg * 32 + 24);
             if (!head) {
                 // publish the partial sums: every epilogue warp fences its stores and counts itself in shared
                 // memory; one thread waits (bounded) for all eight and releases the flag
@@ -1156,6 +1208,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) { all = false; atomicCAS(a.status, 0, 12); break; }
                     }
                     if (all) st_release_gpu(k.flags + cta, k.epoch);
+                    SKT(seg * 32 + 25);
                 }
             }
             u += sb1 - sb0;
@@ -1165,6 +1218,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // ---------------------------------------------------------------- teardown (every path ends here)
     tc_fence_before();
     __syncthreads();
+#ifdef B200Q_SK_TRACE
+    if (threadIdx.x < 128) g_sk_trace[blockIdx.x * 128 + threadIdx.x] = s_trace[threadIdx.x];
+    if (threadIdx.x == 0) g_sk_trace[blockIdx.x * 128 + 127] = clock64();
+#endif
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols) : "memory");
@@ -1342,7 +1399,22 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output) failed with code %d", who, (int)r);
     }
-    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128;
+#ifdef B200Q_SK_TRACE
+    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64 + 1024;
+#else
+    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64;
+#endif
+    // the persistent kernel prefetches partial sums from its workspace: [slots * 256 activation rows, 128 weight rows] fp32
+    CUtensorMap wsmap = map;
+    auto make_wsmap = [&]() -> int {
+        cuuint64_t sdim[2] = {(cuuint64_t)BM, (cuuint64_t)ctx->sk_ctas * 256};
+        cuuint64_t sstr[1] = {(cuuint64_t)BM * 4};
+        cuuint32_t sbox[2] = {(cuuint32_t)BM, 64u};
+        CUresult e = enc(&wsmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ctx->sk_ws, sdim, sstr, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (e != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (workspace) failed with code %d", who, (int)e);
+        return B200Q_OK;
+    };
     if (may_allocate && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
         (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30)) {
         // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads
@@ -1379,7 +1451,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, k);
+        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, ymap, k);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
@@ -1405,6 +1477,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
         int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
         if (rc != B200Q_OK) return rc;
+        if ((rc = make_wsmap()) != B200Q_OK) return rc;
         static bool configured_mx[64] = {};
         rc = configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
         if (rc != B200Q_OK) return rc;
@@ -1415,7 +1488,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, ymap, k);
+        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, ymap, wsmap, k);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
@@ -1445,6 +1518,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
             rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
             if (rc != B200Q_OK) return rc;
+            if ((rc = make_wsmap()) != B200Q_OK) return rc;
             static bool configured_sk[64] = {};
             rc = configure_once(ctx, gemm_tmem_sk_kernel<0>, configured_sk);
             if (rc != B200Q_OK) return rc;
@@ -1456,7 +1530,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 32 + STAGE_EPI_BYTES, ctx->stream>>>(map, wmap, wmap, wmap, ymap, k);
+            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 32 + STAGE_EPI_BYTES, ctx->stream>>>(map, wmap, wmap, wmap, ymap, wsmap, k);
             B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
@@ -1478,6 +1552,11 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
 
 }  // namespace
 
+#ifdef B200Q_SK_TRACE
+extern "C" int b200q_debug_read_sk_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_sk_trace, sizeof(long long) * 160 * 128);
+}
+#endif
 bool gemm_tc_supported(const b200q_weight* w, int m) {
     return w->orient == B200Q_ORIENT_NK && m >= 1 && (w->k % BK) == 0 && w->n_local < 0x7FFFFF00ll && w->k < (1 << 30);
 }
