@@ -752,8 +752,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint64_t* raw_empty = raw_full + RAW_STAGES;
     uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
-    uint64_t* esync = dfree + 1;                 // the eight epilogue warps meet here (staged epilogue)
-    uint64_t* pfull = esync + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
+    uint64_t* pfull = dfree + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
@@ -779,7 +778,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         mbar_init(smem_u32(accum), 1);
         mbar_init(smem_u32(dfree), 8);
-        mbar_init(smem_u32(esync), 8);
         for (int s = 0; s < 4; s++) mbar_init(smem_u32(&pfull[s]), 1);
         *abort_flag = 0;
         *stored = 0;
@@ -904,7 +902,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const float nibscale = nib ? 0.0625f : 1.0f;
         const __half2 k1024 = __float2half2_rn(1024.0f);
         int it = 0, rit = 0, seg = 0;
-        uint32_t esync_phase = 0;
         for (int u = u0; u < u1 && ok; seg++) {
             const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
@@ -1108,24 +1105,26 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             if (head && a.staged_epilogue) {
-                // Finished tile -> shared memory -> tiled TMA stores, 64 activation rows per round: the threads
-                // only move registers to shared memory, the copy engine writes y (clipped at the edges of y)
-                // while the next round, and then the next segment's main loop, proceed.
-                auto meet = [&]() {   // all eight epilogue warps, bounded
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(smem_u32(esync));
-                        if (!mbar_wait(smem_u32(esync), esync_phase, abort_flag, a.status, 13)) ok = false;
-                    }
-                    esync_phase ^= 1;
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                };
+                // Finished tile -> shared memory -> TMA stores. Every warp owns a 32 x 32 block of the round
+                // (its 32 weight rows x 32 activation rows), stages it in a private 4 KB buffer and stores it
+                // with its own copy (clipped at the edges of y), so the eight warps never wait for one another
+                // and no thread waits for global memory; the copies drain while the next segment's main loop runs.
                 const int half_off = warp >= 8 ? 32 : 0;
+                float* wstg = stg + (warp - 4) * 1024;
+                const int last_rnd = ((a.bn + 63) >> 6) * 64 - 64;
+                bool freed = false;
                 for (int rnd = 0; rnd < a.bn && ok; rnd += 64) {
                     const int c0 = rnd + half_off;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)min(c0, 480), v);
                     SKT(seg * 32 + 4 + (rnd >> 6) * 5);
+                    if (rnd == last_rnd) {
+                        // every TMEM read of this warp is complete: the accumulator may be overwritten
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(dfree));
+                        freed = true;
+                    }
                     if (pf) {
                         if (lane == 0) ok = mbar_wait(smem_u32(&pfull[rnd >> 6]), 0, abort_flag, a.status, 14);
                         ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -1141,27 +1140,30 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(ps + j * BM));
                         }
                     }
-                    // the previous store must have finished READING the staging tile before it is overwritten
                     SKT(seg * 32 + 5 + (rnd >> 6) * 5);
-                    if (warp == 4 && lane == 0) bulk_wait_read0();
-                    meet();
-                    if (!ok) break;
+                    // this warp's previous store must have finished READING its buffer before it is overwritten
+                    if (lane == 0) bulk_wait_read0();
+                    __syncwarp();
                     SKT(seg * 32 + 6 + (rnd >> 6) * 5);
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int tok = tok0 + c0 + j;
                         const float sc = tok < a.m ? __ldg(a.xscale + tok) : 0.0f;
-                        stg[(half_off + j) * BM + r] = __uint_as_float(v[j]) * sc;
+                        wstg[j * 32 + lane] = __uint_as_float(v[j]) * sc;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
                     SKT(seg * 32 + 7 + (rnd >> 6) * 5);
-                    meet();
-                    if (!ok) break;
-                    if (warp == 4 && lane == 0) {
-                        tma_store_2d(&tmap_y, smem_u32(stg), row0, tok0 + rnd);
+                    if (lane == 0 && c0 < a.bn) {
+                        tma_store_2d(&tmap_y, smem_u32(wstg), row0 + q * 32, tok0 + c0);
                         bulk_commit();
                     }
                     SKT(seg * 32 + 8 + (rnd >> 6) * 5);
+                }
+                if (!freed) {   // a wait gave up before the last read: the MMA thread leaves through the abort flag
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(dfree));
                 }
             } else
             for (int c0 = (warp >= 8 ? 32 : 0); c0 < a.bn; c0 += 64) {
@@ -1190,10 +1192,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     }
                 }
             }
-            // every TMEM read of this warp is complete: the accumulator may be overwritten
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(dfree));
+            if (!(head && a.staged_epilogue)) {
+                // every TMEM read of this warp is complete: the accumulator may be overwritten
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(dfree));
+            }
             SKT(seg * 32 + 24);
             if (!head) {
                 // publish the partial sums: every epilogue warp fences its stores and counts itself in shared
@@ -1213,7 +1217,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             u += sb1 - sb0;
         }
-        if (warp == 4 && lane == 0) bulk_wait0();   // the tile stores of this thread are complete before shared memory goes away
+        if (lane == 0) bulk_wait0();   // the tile stores of this thread are complete before shared memory goes away
     }
     // ---------------------------------------------------------------- teardown (every path ends here)
     tc_fence_before();
@@ -1394,7 +1398,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     if (y_tma_ok) {
         cuuint64_t ydim[2] = {(cuuint64_t)w->n_local, (cuuint64_t)m};
         cuuint64_t ystr[1] = {(cuuint64_t)ldy * 4};
-        cuuint32_t ybox[2] = {(cuuint32_t)BM, 64u};
+        cuuint32_t ybox[2] = {32u, 32u};   // one epilogue warp's block: 32 weight rows x 32 activation rows
         r = enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d_y, ydim, ystr, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output) failed with code %d", who, (int)r);
