@@ -753,7 +753,8 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
     uint64_t* pfull = dfree + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull + 4);
+    uint64_t* pgo = pfull + 4;                   // MMAs of the CTA's last segment complete -> the stages are idle
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pgo + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
     // staging tile of the epilogue: 64 activation rows x 128 weight rows of fp32 (one TMA store box)
@@ -779,6 +780,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         mbar_init(smem_u32(accum), 1);
         mbar_init(smem_u32(dfree), 8);
         for (int s = 0; s < 4; s++) mbar_init(smem_u32(&pfull[s]), 1);
+        mbar_init(smem_u32(pgo), 1);
         *abort_flag = 0;
         *stored = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -857,6 +859,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(accum));
+                if (u + (sb1 - sb0) == u1) umma_commit(smem_u32(pgo));
                 u += sb1 - sb0;
             }
         }
@@ -889,6 +892,39 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&raw_full[rs]), ph)) {
                     if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 9); break; }
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- partial-tile prefetcher
+        // A range that ends inside a tile makes this CTA the tile's owner, and that segment is its last one, so
+        // the activation stages are idle once its MMAs are complete. This thread waits, beside the main loop,
+        // for the next CTA's partial tile (its flag), then for those MMAs, and lets the copy engine bring the
+        // partial tile into the stages, 64 activation rows per copy: the owner's adds read shared memory.
+        if (lane == 0 && a.staged_epilogue && (a.bn & 63) == 0 && u1 > u0 && cta + 1 < nctas) {
+            const int tl = (u1 - 1) / k.nsb;
+            const int s0 = max(u0, tl * k.nsb) - tl * k.nsb, s1 = u1 - tl * k.nsb;
+            if (s0 == 0 && s1 < k.nsb) {
+                long long t0 = clock64();
+                while (ld_acquire_gpu(k.flags + cta + 1) != k.epoch) {
+                    if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) {
+                        *abort_flag = 1;
+                        atomicCAS(a.status, 0, 11);
+                        ok = false;
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");   // the flag was acquired by a plain load; the copy engine reads next
+                if (ok && mbar_wait(smem_u32(pgo), 0, abort_flag, a.status, 15)) {
+                    for (int rnd = 0; rnd < a.bn; rnd += 64) {
+                        const uint32_t pb = smem_u32(&pfull[rnd >> 6]);
+                        mbar_arrive_expect_tx(pb, 64u * BM * 4u);
+                        tma_load_2d(smem_u32(sB + (rnd >> 6) * (64 * BM * 4)), &tmap_ws, 0, (cta + 1) * 256 + rnd, pb);
+                    }
+                    // nothing stays in flight behind this thread
+                    for (int rnd = 0; rnd < a.bn; rnd += 64)
+                        if (!mbar_wait(smem_u32(&pfull[rnd >> 6]), 0, abort_flag, a.status, 14)) break;
                 }
             }
         }
@@ -1070,10 +1106,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             SKT(seg * 32 + 2);
             // partial sums this (owning) CTA has to add: the CTAs after it, until the tile's k range is covered
             int p_end = cta + 1;
+            bool pf = false;   // the first partial tile arrives in shared memory (prefetcher warp)
             if (head && !whole) {
                 const int tile_end = (tile + 1) * k.nsb;
                 while (p_end < nctas && sk_unit_begin(p_end, k.total_units, nctas) < tile_end) p_end++;
-                for (int p = cta + 1; p < p_end && ok; p++) {
+                pf = a.staged_epilogue && (a.bn & 63) == 0 && p_end > cta + 1 && u + (sb1 - sb0) == u1;
+                for (int p = cta + 1 + (pf ? 1 : 0); p < p_end && ok; p++) {
                     if (lane == 0) {
                         long long t0 = clock64();
                         while (ld_acquire_gpu(k.flags + p) != k.epoch) {
@@ -1090,20 +1128,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             float* myslot = k.ws + (size_t)cta * SK_SLOT_FLOATS;
             SKT(seg * 32 + 3);
-            // An owner that adds partial sums is in the LAST segment of its range (its range ends inside the
-            // tile), so the activation stages are idle once this segment's MMAs are complete: the copy engine
-            // brings the first partial tile into them, 64 activation rows per copy, while the rounds below run;
-            // the adds then read shared memory instead of waiting for L2 32 lines at a time.
-            const bool pf = head && !whole && a.staged_epilogue && (a.bn & 63) == 0 && p_end > cta + 1 && ok &&
-                            u + (sb1 - sb0) == u1;
-            if (pf && warp == 4 && lane == 0) {
-                asm volatile("fence.proxy.async;" ::: "memory");   // the flag was acquired by plain loads; the copy engine reads next
-                for (int rnd = 0; rnd < a.bn; rnd += 64) {
-                    const uint32_t pb = smem_u32(&pfull[rnd >> 6]);
-                    mbar_arrive_expect_tx(pb, 64u * BM * 4u);
-                    tma_load_2d(smem_u32(sB + (rnd >> 6) * (64 * BM * 4)), &tmap_ws, 0, (cta + 1) * 256 + rnd, pb);
-                }
-            }
             if (head && a.staged_epilogue) {
                 // Finished tile -> shared memory -> TMA stores. Every warp owns a 32 x 32 block of the round
                 // (its 32 weight rows x 32 activation rows), stages it in a private 4 KB buffer and stores it
