@@ -896,11 +896,25 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
         }
     } else if (warp == 3) {
-        // ---------------------------------------------------------------- partial-tile prefetcher
+        // ---------------------------------------------------------------- publisher, then partial-tile prefetcher
         // A range that ends inside a tile makes this CTA the tile's owner, and that segment is its last one, so
         // the activation stages are idle once its MMAs are complete. This thread waits, beside the main loop,
         // for the next CTA's partial tile (its flag), then for those MMAs, and lets the copy engine bring the
         // partial tile into the stages, 64 activation rows per copy: the owner's adds read shared memory.
+        if (lane == 0 && u1 > u0 && u0 % k.nsb != 0) {
+            // publisher: this CTA's first segment starts inside a tile, so it leaves partial sums in the workspace;
+            // once the eight epilogue warps have fenced their stores the flag tells the tile's owner
+            long long t0 = clock64();
+            bool all = true;
+            while (*reinterpret_cast<volatile int*>(stored) < 8) {
+                if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) { all = false; atomicCAS(a.status, 0, 12); break; }
+                __nanosleep(100);
+            }
+            if (all) {
+                __threadfence();
+                st_release_gpu(k.flags + cta, k.epoch);
+            }
+        }
         if (lane == 0 && a.staged_epilogue && (a.bn & 63) == 0 && u1 > u0 && cta + 1 < nctas) {
             const int tl = (u1 - 1) / k.nsb;
             const int s0 = max(u0, tl * k.nsb) - tl * k.nsb, s1 = u1 - tl * k.nsb;
@@ -938,6 +952,16 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const float nibscale = nib ? 0.0625f : 1.0f;
         const __half2 k1024 = __float2half2_rn(1024.0f);
         int it = 0, rit = 0, seg = 0;
+        // Partial sums are written with plain stores; the fence that completes them costs a round trip to L2,
+        // so it waits until the next segment's first super-block is converted (the stores have landed by
+        // then), and the publisher (warp 3) releases the flag once all eight warps have fenced.
+        bool fence_due = false;
+        auto fence_and_count = [&]() {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(stored, 1);
+            fence_due = false;
+        };
         for (int u = u0; u < u1 && ok; seg++) {
             const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
@@ -1093,6 +1117,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+                if (fence_due) fence_and_count();
             }
             if (!ok) break;
             // ------------------------------------------------------------ epilogue of this segment
@@ -1223,24 +1248,11 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (lane == 0) mbar_arrive(smem_u32(dfree));
             }
             SKT(seg * 32 + 24);
-            if (!head) {
-                // publish the partial sums: every epilogue warp fences its stores and counts itself in shared
-                // memory; one thread waits (bounded) for all eight and releases the flag
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicAdd(stored, 1);
-                if (warp == 4 && lane == 0 && ok) {
-                    long long t0 = clock64();
-                    bool all = true;
-                    while (*reinterpret_cast<volatile int*>(stored) < 8) {
-                        if (*abort_flag != 0 || clock64() - t0 > WAIT_BUDGET) { all = false; atomicCAS(a.status, 0, 12); break; }
-                    }
-                    if (all) st_release_gpu(k.flags + cta, k.epoch);
-                    SKT(seg * 32 + 25);
-                }
-            }
+            if (!head) fence_due = true;   // partial sums written: fence and count later (see above)
+            SKT(seg * 32 + 25);
             u += sb1 - sb0;
         }
+        if (fence_due) fence_and_count();
         if (lane == 0) bulk_wait0();   // the tile stores of this thread are complete before shared memory goes away
     }
     // ---------------------------------------------------------------- teardown (every path ends here)
