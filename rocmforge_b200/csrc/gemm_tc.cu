@@ -737,6 +737,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
+    constexpr int RS = QF == 2 ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
@@ -745,12 +746,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const int b_stage_bytes = a.bn * BK * 2;
     uint8_t* sB = smem;
     uint8_t* sRaw = sB + STAGES * b_stage_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RAW_STAGES * RAW_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sRaw + RS * RAW_STAGE_BYTES);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* raw_full = bars + 2 * STAGES;
-    uint64_t* raw_empty = raw_full + RAW_STAGES;
-    uint64_t* accum = raw_empty + RAW_STAGES;    // MMAs of a segment complete -> epilogue
+    uint64_t* raw_empty = raw_full + RS;
+    uint64_t* accum = raw_empty + RS;    // MMAs of a segment complete -> epilogue
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
     uint64_t* pfull = dfree + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
     uint64_t* pgo = pfull + 4;                   // MMAs of the CTA's last segment complete -> the stages are idle
@@ -773,7 +774,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             mbar_init(smem_u32(&full[s]), 9);    // 8 converter warps + the TMA thread's expect_tx arrival
             mbar_init(smem_u32(&empty[s]), 1);   // tcgen05.commit
         }
-        for (int s = 0; s < RAW_STAGES; s++) {
+        for (int s = 0; s < RS; s++) {
             mbar_init(smem_u32(&raw_full[s]), 1);
             mbar_init(smem_u32(&raw_empty[s]), 8);
         }
@@ -871,8 +872,8 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
                 const int row0 = (tile % k.tiles_x) * BM;
                 for (int sb = sb0; sb < sb1; sb++, rit++) {
-                    const int rs = rit % RAW_STAGES;
-                    const uint32_t ph = (uint32_t)(rit / RAW_STAGES) & 1;
+                    const int rs = rit % RS;
+                    const uint32_t ph = (uint32_t)(rit / RS) & 1;
                     if (!mbar_wait(smem_u32(&raw_empty[rs]), ph ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
                     mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), (uint32_t)RAW_STAGE_BYTES);
                     if constexpr (QF == 2) {
@@ -886,9 +887,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
                 u += sb1 - sb0;
             }
-            for (int j = max(0, rit - RAW_STAGES); j < rit; j++) {
-                const int rs = j % RAW_STAGES;
-                const uint32_t ph = (uint32_t)(j / RAW_STAGES) & 1;
+            for (int j = max(0, rit - RS); j < rit; j++) {
+                const int rs = j % RS;
+                const uint32_t ph = (uint32_t)(j / RS) & 1;
                 long long t0 = clock64();
                 while (!mbar_try_wait(smem_u32(&raw_full[rs]), ph)) {
                     if (clock64() - t0 > WAIT_BUDGET) { atomicCAS(a.status, 0, 9); break; }
@@ -967,8 +968,8 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
             SKT(seg * 32 + 0);
             for (int sb = sb0; sb < sb1 && ok; sb++, rit++) {
-                const int rs = rit % RAW_STAGES;
-                const uint32_t rph = (uint32_t)(rit / RAW_STAGES) & 1;
+                const int rs = rit % RS;
+                const uint32_t rph = (uint32_t)(rit / RS) & 1;
                 if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
@@ -1461,9 +1462,9 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         a.a_col0 = (bn + 31) & ~31;
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
-        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 208 +
-                            (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + 128;
-        a.staged_epilogue = 0;   // the three raw planes leave no room for the staging tile
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)2 * BM * 208 +
+                            (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + STAGE_EPI_BYTES;   // raw ring of two stages
+        a.staged_epilogue = y_tma_ok ? 1 : 0;
         const int nsb = (int)(w->k / 256);
         CUtensorMap pm[3];
         const int pbytes[3] = {128, 64, 16};
@@ -1481,6 +1482,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
         int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
         if (rc != B200Q_OK) return rc;
+        if ((rc = make_wsmap()) != B200Q_OK) return rc;
         static bool configured_q6[64] = {};
         rc = configure_once(ctx, gemm_tmem_sk_kernel<2>, configured_q6);
         if (rc != B200Q_OK) return rc;
@@ -1491,7 +1493,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, ymap, k);
+        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, wsmap, k);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
