@@ -724,9 +724,14 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 #ifdef B200Q_SK_TRACE
 // Scratch build only: time stamps go to shared memory and are copied out at the end of the kernel.
 __device__ long long g_sk_trace[160 * 128];
-#define SKT(i) do { if (lane == 0 && warp == 4 && (i) < 128) s_trace[(i)] = clock64(); } while (0)
+#define SKT(i) do { if (lane == 0 && warp == 4 && (i) < 96) s_trace[(i)] = clock64(); } while (0)
+// cycle sums of one role's waits: SKA_BEGIN; <wait>; SKA_END(slot) adds the elapsed cycles to s_trace[96 + slot]
+#define SKA_BEGIN long long ska_t = clock64()
+#define SKA_END(slot) do { if (lane == 0) s_trace[96 + (slot)] += clock64() - ska_t; } while (0)
 #else
 #define SKT(i)
+#define SKA_BEGIN
+#define SKA_END(slot)
 #endif
 template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -807,7 +812,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int s = it & (STAGES - 1);                    // first stage of the pair
                     const uint32_t ph = (it >> 2) & 1;
                     const uint32_t fb = smem_u32(&full[s >> 1]);
+                    { SKA_BEGIN;
                     if (!mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+                    SKA_END(3); }
                     mbar_arrive_expect_tx(fb, 2u * (uint32_t)b_stage_bytes);
                     tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, fb);
                     tma_load_2d(smem_u32(sB + (s + 1) * b_stage_bytes), &tmap_x, (kb + 1) * BK, tok0, fb);
@@ -836,13 +843,18 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int u = u0; u < u1 && ok; seg++) {
                 const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
                 // the previous segment's accumulator must have been read out
+                { SKA_BEGIN;
                 if (!mbar_wait(smem_u32(dfree), (uint32_t)(seg & 1) ^ 1, abort_flag, a.status, 10)) break;
+                SKA_END(0); }
                 tc_fence_after();
                 for (int kb = 4 * sb0; kb < 4 * sb1; kb += 2, it += 2) {
                     const uint32_t s = (uint32_t)it & (STAGES - 1);     // first stage of the pair
                     const uint32_t ph = ((uint32_t)it >> 2) & 1;
+                    { SKA_BEGIN;
                     if (!mbar_wait(fu0 + (s >> 1) * 8, ph, abort_flag, a.status, 2)) { ok = false; break; }
+                    SKA_END(1); }
                     tc_fence_after();
+                    SKA_BEGIN;
                     const uint32_t at = at0 + s * A_SLOT_COLS, bl = blo0 + s * b_step;
                     // 16 k further: 8 TMEM columns on the A side, 32 bytes (+2 encoded) inside the swizzle atom on the B
                     // side; the second stage of the pair is one A slot / one B stage further on
@@ -857,6 +869,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     umma_ts_f16_acc(tmem_base, at2 + 16, bl2 + 4, bhi, idesc);
                     umma_ts_f16_acc(tmem_base, at2 + 24, bl2 + 6, bhi, idesc);
                     umma_commit(em0 + (s >> 1) * 8);
+                    SKA_END(2);
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(accum));
@@ -970,7 +983,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int sb = sb0; sb < sb1 && ok; sb++, rit++) {
                 const int rs = rit % RS;
                 const uint32_t rph = (uint32_t)(rit / RS) & 1;
+                { SKA_BEGIN;
                 if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
+                if (warp == 4) SKA_END(4); }
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
                 if constexpr (QF == 0) {
@@ -1003,17 +1018,21 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     }
                     // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
                     if ((c & 1) == 0) {
+                        SKA_BEGIN;
                         if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                        if (warp == 4) SKA_END(5);
                         ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                         if (!ok) break;
                         tc_fence_after();
                     }
                     tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
                     if (c & 1) {
+                        SKA_BEGIN;
                         tmem_st_wait();
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                        if (warp == 4) SKA_END(6);
                     }
                 }
                 } else if constexpr (QF == 2) {
