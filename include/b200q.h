@@ -201,6 +201,38 @@ int b200q_selftest_bounded_wait(b200q_ctx* ctx, int64_t budget_cycles);
  *      out[r, j] = deq(w)[r, j] * rsqrt(mean_j(deq(w)[r, :]^2) + eps) * norm_weight[j], fp32 [seq_len, hidden_size]. */
 int b200q_fused_dequant_rmsnorm(b200q_ctx* ctx, const b200q_weight* w, const float* d_norm_weight, float* d_out, float eps);
 
+/* ---- projection-site operators on packed weights (the callers of the fused products:
+ *      src/model/execution_plan/execute.rs:300,403,456-458,585,601).
+ *      b200q_swiglu: out[i] = gate[i] * swish(up[i]), swish(u) = u / (1 + expf(-u)) computed as
+ *        u * (1 / (1 + expf(-u))) — kernels/swiglu.hip:37-63 (the activation is on the UP projection there);
+ *        fp32 [seq_len, intermediate_size], out may alias gate.
+ *      b200q_add_row_bias: y[r, c] += bias[c] — HipBackend::add_row_bias (src/backend/hip_backend/backend.rs:924-975,
+ *        one saxpy per row); ldy = 0 means cols; rows == 0 or cols == 0 is a successful no-op as there.
+ *      b200q_mlp_*: HipBackend::mlp_swiglu (backend.rs:1153-1276) with the three weights PACKED
+ *        ([intermediate, hidden] gate and up, [hidden, intermediate] down, NK): out[m, hidden] =
+ *        (gate(x) * swish(up(x))) . down. A plan binds the buffers once (scratch for the two [m, intermediate]
+ *        projections); at m <= 8 gate and up are one grouped launch that reads x once. Errors carry the
+ *        reference's shape messages. Q, K, V projections sharing one input are the same grouped launch through
+ *        b200q_batch_create with three products. */
+typedef struct b200q_mlp b200q_mlp;
+int b200q_swiglu(b200q_ctx* ctx, const float* d_gate, const float* d_up, float* d_out, int64_t seq_len, int64_t intermediate_size);
+int b200q_add_row_bias(b200q_ctx* ctx, float* d_y, int64_t ldy, const float* d_bias, int64_t rows, int64_t cols);
+int b200q_mlp_create(b200q_ctx* ctx, const b200q_weight* w_gate, const b200q_weight* w_up, const b200q_weight* w_down,
+                     const float* d_hidden_states, float* d_output, int m, b200q_mlp** out);
+int b200q_mlp_run(b200q_ctx* ctx, b200q_mlp* plan);
+int b200q_mlp_free(b200q_mlp* plan);
+
+/* ---- quantised embedding lookup: replaces the GetRows op (execute_get_rows, src/ggml/hip_backend/op_dispatch.rs:13-102;
+ *      get_rows + validate_token_ids, src/ggml/hip_backend/ops/get_rows.rs:24-94), which copies fp32 rows of a
+ *      dequantised table. w is the packed [vocab_size, n_embd] token_embd uploaded as NK (any qtype/layout);
+ *      out[i, :] = deq(w)[ids[i], :], fp32, row pitch ldo >= n_embd floats, bit-exact against b200q_dequantize.
+ *      b200q_get_rows takes device ids and is asynchronous: an id outside [0, vocab_size) never reads the table,
+ *      its row is zero-filled and the next b200q_synchronize returns B200Q_ERR_INVALID.
+ *      b200q_get_rows_host takes host ids, validates them BEFORE any launch (the reference's order and message,
+ *      "Token ID {} exceeds vocab size {}") and returns when the rows are written. */
+int b200q_get_rows(b200q_ctx* ctx, const b200q_weight* w, const int32_t* d_ids, int64_t n_ids, float* d_out, int64_t ldo);
+int b200q_get_rows_host(b200q_ctx* ctx, const b200q_weight* w, const uint32_t* h_ids, int64_t n_ids, float* d_out, int64_t ldo);
+
 /* ---- GGUF container: replaces the parser and lazy loader in front of load_tensor_to_gpu
  *      (src/loader/gguf/header.rs:28-79 magic + version-3-only check, src/loader/gguf/metadata.rs:20-269
  *      key/value pairs, src/loader/gguf/tensor_info.rs:37-101 tensor directory -> LazyTensor,

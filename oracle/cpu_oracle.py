@@ -144,6 +144,44 @@ def fused_dequant_rmsnorm(qtype, layout, data, seq_len, hidden, weight, eps):
     return out
 
 
+def swiglu(gate, up):
+    """gate * swish(up) in fp32, the order of kernels/swiglu.hip."""
+    g = np.ascontiguousarray(gate, dtype=np.float32)
+    u = np.ascontiguousarray(up, dtype=np.float32)
+    assert g.shape == u.shape
+    out = np.empty_like(g)
+    L = lib()
+    L.orc_swiglu.restype = None
+    L.orc_swiglu.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+    L.orc_swiglu(_ptr(g), _ptr(u), _ptr(out), g.size)
+    return out
+
+
+def add_row_bias(y, bias):
+    """y[r, :] += bias (saxpy with alpha = 1 per row); returns a new array."""
+    out = np.array(y, dtype=np.float32, order="C", copy=True)
+    b = np.ascontiguousarray(bias, dtype=np.float32).reshape(-1)
+    assert out.ndim == 2 and b.size == out.shape[1]
+    L = lib()
+    L.orc_add_row_bias.restype = None
+    L.orc_add_row_bias.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
+    L.orc_add_row_bias(_ptr(out), _ptr(b), out.shape[0], out.shape[1])
+    return out
+
+
+def mlp_swiglu(qtypes, layout, gate, up, down, x, hidden, n_ff):
+    """HipBackend::mlp_swiglu on packed weights: cpu_matmul_f32 of x with the dequantised gate / up tensors
+    ([n_ff, hidden], stored as rows of hidden values), swiglu, cpu_matmul_f32 with the dequantised down tensor
+    ([hidden, n_ff]). qtypes = (gate, up, down) quantisation types."""
+    xg = np.ascontiguousarray(x, dtype=np.float32)
+    wg = dequantize(qtypes[0], layout, gate, n_ff * hidden).reshape(n_ff, hidden)
+    wu = dequantize(qtypes[1], layout, up, n_ff * hidden).reshape(n_ff, hidden)
+    wd = dequantize(qtypes[2], layout, down, hidden * n_ff).reshape(hidden, n_ff)
+    t = max_threads()
+    act = swiglu(matmul_f32(xg, wg, nk=True, threads=t), matmul_f32(xg, wu, nk=True, threads=t))
+    return matmul_f32(act, wd, nk=True, threads=t), act
+
+
 def matmul_f32(a, b, nk=False, threads=1):
     """cpu_matmul_f32: fp32, ascending k, multiply then add.
 

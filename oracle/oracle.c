@@ -872,3 +872,19 @@ int orc_fused_dequant_rmsnorm(int qtype, int layout, const uint8_t* data, size_t
     }
     return 0;
 }
+
+/* kernels/swiglu.hip:37-63 */
+void orc_swiglu(const float* gate, const float* up, float* out, size_t n) {
+    for (size_t i = 0; i < n; i++) {
+        const float u = up[i];
+        const float sigmoid_up = 1.0f / (1.0f + expf(-u));
+        const float swish_up = u * sigmoid_up;
+        out[i] = gate[i] * swish_up;
+    }
+}
+
+/* src/backend/hip_backend/backend.rs:960-972: y_row = 1.0 * bias + y_row */
+void orc_add_row_bias(float* y, const float* bias, size_t rows, size_t cols) {
+    for (size_t r = 0; r < rows; r++)
+        for (size_t j = 0; j < cols; j++) y[r * cols + j] = 1.0f * bias[j] + y[r * cols + j];
+}

@@ -100,6 +100,13 @@ int orc_max_threads(void);
 int orc_fused_dequant_rmsnorm(int qtype, int layout, const uint8_t* data, size_t nbytes, int seq_len, int hidden,
                               const float* weight, float eps, float* out);
 
+/* kernels/swiglu.hip:37-63: out[i] = gate[i] * (up[i] * (1 / (1 + expf(-up[i])))), fp32, that operation order.
+ * Parity unpinned: the reference's test for it (src/mlp/swiglu_tests.rs) compares its GPU kernel with the same
+ * formula on the CPU at 1e-4; libm's expf stands in for the device's. */
+void orc_swiglu(const float* gate, const float* up, float* out, size_t n);
+/* HipBackend::add_row_bias (src/backend/hip_backend/backend.rs:924-975): saxpy(alpha = 1) of the bias onto every row */
+void orc_add_row_bias(float* y, const float* bias, size_t rows, size_t cols);
+
 #ifdef __cplusplus
 }
 #endif

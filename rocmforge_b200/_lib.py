@@ -80,6 +80,13 @@ SIGNATURES = {
     "b200q_ipc_close": (_i, [_vp, _vp]),
     "b200q_selftest_bounded_wait": (_i, [_vp, _i64]),
     "b200q_fused_dequant_rmsnorm": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float]),
+    "b200q_swiglu": (_i, [_vp, _vp, _vp, _vp, _i64, _i64]),
+    "b200q_add_row_bias": (_i, [_vp, _vp, _i64, _vp, _i64, _i64]),
+    "b200q_mlp_create": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _pvp]),
+    "b200q_mlp_run": (_i, [_vp, _vp]),
+    "b200q_mlp_free": (_i, [_vp]),
+    "b200q_get_rows": (_i, [_vp, _vp, _vp, _i64, _vp, _i64]),
+    "b200q_get_rows_host": (_i, [_vp, _vp, _vp, _i64, _vp, _i64]),
     "b200q_gguf_open": (_i, [ctypes.c_char_p, _i, _pvp]),
     "b200q_gguf_close": (None, [_vp]),
     "b200q_gguf_tensor_count": (_i64, [_vp]),

@@ -375,6 +375,38 @@ int b200q_fused_dequant_rmsnorm(b200q_ctx* ctx, const b200q_weight* w, const flo
     return launch_fused_dequant_rmsnorm(ctx, w->fmt, w->view, d_norm_weight, d_out, w->n_local, (int)w->k, eps);
 }
 
+int b200q_get_rows(b200q_ctx* ctx, const b200q_weight* w, const int32_t* d_ids, int64_t n_ids, float* d_out, int64_t ldo) {
+    CTX_GUARD("get_rows");
+    if (!w) return fail(B200Q_ERR_INVALID, "get_rows: weight handle is null");
+    if (w->ctx->device != ctx->device) return fail(B200Q_ERR_INVALID, "get_rows: tensor lives on device %d, ctx on %d", w->ctx->device, ctx->device);
+    if (w->orient != B200Q_ORIENT_NK) return fail(B200Q_ERR_UNSUPPORTED, "get_rows: needs a table stored as rows of n_embd values");
+    if (w->k % 8 || w->k > 0x7FFFFFF8ll) return fail(B200Q_ERR_UNSUPPORTED, "get_rows: n_embd %lld must be a multiple of 8", (long long)w->k);
+    if (n_ids < 0) return fail(B200Q_ERR_INVALID, "get_rows: negative token count");
+    if (n_ids == 0) return B200Q_OK;
+    if (!d_ids || !d_out) return fail(B200Q_ERR_INVALID, "get_rows: null device pointer");
+    if (ldo < w->k || (ldo % 4) || (reinterpret_cast<uintptr_t>(d_out) & 15))
+        return fail(B200Q_ERR_INVALID, "get_rows: output rows must be 16-byte aligned and at least n_embd wide");
+    ctx->tc_pending = true;   // the next synchronize reads the status words
+    return launch_get_rows(ctx, w->fmt, w->view, d_ids, n_ids, d_out, ldo, (int)w->k, w->n_local);
+}
+
+int b200q_get_rows_host(b200q_ctx* ctx, const b200q_weight* w, const uint32_t* h_ids, int64_t n_ids, float* d_out, int64_t ldo) {
+    CTX_GUARD("get_rows_host");
+    if (!w) return fail(B200Q_ERR_INVALID, "get_rows: weight handle is null");
+    if (n_ids < 0) return fail(B200Q_ERR_INVALID, "get_rows: negative token count");
+    if (n_ids == 0) return B200Q_OK;
+    if (!h_ids) return fail(B200Q_ERR_INVALID, "get_rows: token ids are null");
+    for (int64_t i = 0; i < n_ids; i++)   // validate_token_ids: nothing is launched for a bad id
+        if ((int64_t)h_ids[i] >= w->n_local)
+            return fail(B200Q_ERR_INVALID, "Token ID %u exceeds vocab size %lld", h_ids[i], (long long)w->n_local);
+    int rc = ensure_scratch(ctx, (size_t)n_ids * sizeof(int32_t), 0);
+    if (rc != B200Q_OK) return rc;
+    B200Q_CUDA(cudaMemcpyAsync(ctx->scratch, h_ids, (size_t)n_ids * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream), B200Q_ERR_COPY);
+    rc = b200q_get_rows(ctx, w, static_cast<const int32_t*>(ctx->scratch), n_ids, d_out, ldo);
+    if (rc != B200Q_OK) return rc;
+    return b200q_synchronize(ctx);   // the ids are pageable host memory: the call returns when they have been read
+}
+
 int b200q_dequantize_bytes(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, float* d_out,
                            int64_t n_elements) {
     CTX_GUARD("dequantize_bytes");

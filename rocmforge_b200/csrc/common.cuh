@@ -64,6 +64,8 @@ int ensure_scratch(b200q_ctx* ctx, size_t bytes, int which = 0);
 int launch_fused_dequant_rmsnorm(b200q_ctx* ctx, int fmt, const WView& v, const float* d_weight, float* d_out, int64_t rows,
                                  int hidden, float eps);
 int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_t n, int64_t valid_bytes);
+int launch_get_rows(b200q_ctx* ctx, int fmt, const WView& v, const int32_t* d_ids, int64_t n_ids, float* d_out, int64_t ldo,
+                    int hidden, int64_t n_rows);
 int launch_repack(b200q_ctx* ctx, int fmt, const uint8_t* d_raw, int64_t n_blocks, const WView& v);
 // kernels_gemv.cu
 int launch_gemv(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, int64_t ldx, float* d_y, int64_t ldy, int m);

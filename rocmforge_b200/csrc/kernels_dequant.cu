@@ -101,6 +101,44 @@ int launch_fused_dequant_rmsnorm(b200q_ctx* ctx, int fmt, const WView& v, const 
     return B200Q_OK;
 }
 
+// Quantised embedding lookup (the GetRows op on a packed token_embd, replaces the per-token device copies of
+// src/ggml/hip_backend/ops/get_rows.rs:24-78 that need the table as fp32): one CTA per token id, the row is
+// decoded with the same decode8 as everywhere else (bit-exact against the dequantised table) and written as
+// 32-byte sectors. A token id outside [0, n_rows) never touches the table: its output row is zero-filled and
+// the launch's status word counts it, so the host can report it the way validate_token_ids does.
+template <int F>
+__global__ void __launch_bounds__(256) get_rows_kernel(WView v, const int32_t* __restrict__ ids, float* __restrict__ out,
+                                                       int64_t ldo, int hidden, int64_t n_rows, int* __restrict__ bad_ids) {
+    const int64_t t = blockIdx.x;
+    const int64_t id = ids[t];
+    const bool valid = id >= 0 && id < n_rows;
+    if (!valid && threadIdx.x == 0) atomicAdd(bad_ids, 1);
+    const int64_t piece0 = (valid ? id : 0) * (hidden >> 3);
+    for (int p = threadIdx.x; p < (hidden >> 3); p += 256) {
+        float w[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        const int64_t piece = piece0 + p;
+        if (valid) decode8<F>(v, piece >> 2, (int)(piece & 3), w);
+        float4* o = reinterpret_cast<float4*>(out + t * ldo) + 2 * p;
+        o[0] = make_float4(w[0], w[1], w[2], w[3]);
+        o[1] = make_float4(w[4], w[5], w[6], w[7]);
+    }
+}
+
+int launch_get_rows(b200q_ctx* ctx, int fmt, const WView& v, const int32_t* d_ids, int64_t n_ids, float* d_out, int64_t ldo,
+                    int hidden, int64_t n_rows) {
+    if (n_ids <= 0) return B200Q_OK;
+    if (n_ids > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "get_rows: too many token ids for one launch");
+    switch (fmt) {
+#define X(F) \
+    case F: get_rows_kernel<F><<<(unsigned)n_ids, 256, 0, ctx->stream>>>(v, d_ids, d_out, ldo, hidden, n_rows, ctx->d_status + 1); break;
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+        default: return fail(B200Q_ERR_INVALID, "get_rows: unknown format %d", fmt);
+    }
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
 // File blocks (header and codes interleaved) -> planes. The block sizes are not word multiples, so
 // this moves single bytes; it runs once per tensor at load time.
 struct RepackArgs {

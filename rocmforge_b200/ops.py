@@ -109,3 +109,40 @@ def fused_q4_0_rmsnorm(backend, q4_0_input, weight, output, seq_len, hidden_size
     finally:
         if own:
             w.free()
+
+
+def validate_token_ids(tokens, vocab_size):
+    """validate_token_ids (src/ggml/hip_backend/ops/get_rows.rs:84-94): the first id >= vocab_size is an error."""
+    for t in tokens:
+        if int(t) >= vocab_size:
+            raise ValueError(f"Token ID {int(t)} exceeds vocab size {vocab_size}")
+
+
+def get_rows(backend, weights, tokens, n_embd, n_vocab, output, qtype=None, layout=LAYOUT_GGUF, trim_padding=False):
+    """get_rows (src/ggml/hip_backend/ops/get_rows.rs:24-78) on a PACKED embedding table: output[i, :] =
+    deq(weights)[tokens[i], :], fp32 [len(tokens), n_embd]. weights: a resident QuantizedWeight uploaded as
+    [n_vocab, n_embd], or host bytes of the packed table with qtype/layout (uploaded for the call). tokens: host
+    integers, validated before anything is launched. trim_padding=True drops everything from the first 0 id on,
+    as execute_get_rows does with its padded token buffer (src/ggml/hip_backend/op_dispatch.rs:71-76).
+    Returns the number of rows written."""
+    import numpy as np
+    toks = np.ascontiguousarray(np.asarray(tokens, dtype=np.uint32).reshape(-1))
+    if trim_padding:
+        zeros = np.nonzero(toks == 0)[0]
+        if zeros.size:
+            toks = toks[:int(zeros[0])]
+    validate_token_ids(toks, n_vocab)
+    own = not isinstance(weights, QuantizedWeight)
+    w = QuantizedWeight(backend, weights, qtype, layout, n_vocab, n_embd) if own else weights
+    try:
+        if w.n_total != n_vocab or w.k != n_embd:
+            raise ValueError(f"table is [{w.n_total}, {w.k}], expected [{n_vocab}, {n_embd}]")
+        if output.size < toks.size * n_embd * 4:
+            raise ValueError("Output size does not match n_embd * actual_n_tokens")
+        if toks.size:
+            _lib.check(backend.lib.b200q_get_rows_host(backend.ctx, w.handle, toks.ctypes.data_as(ctypes.c_void_p),
+                                                        toks.size, output.as_ptr(), n_embd))
+    finally:
+        if own:
+            w.free()
+    return int(toks.size)
