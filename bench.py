@@ -202,6 +202,40 @@ def gemm_leg(be, peaks, steps):
             "peak_source": peaks["source"], "operands": "f16 x f16 -> fp32 (tcgen05, TMEM accumulators)", "shapes": rows}
 
 
+def mlp_leg(be, peaks, steps):
+    """The SwiGLU MLP block of a Llama-2-7B-shaped layer on packed weights (gate/up Q4_K [11008,4096], down Q6_K
+    [4096,11008]): gate+up grouped launch, activation kernel, down projection; device-resident operands."""
+    from rocmforge_b200 import projections
+    from rocmforge_b200.backend import QuantizedWeight
+    hidden, n_ff = 4096, 11008
+    rng = synth.rng_for(synth.CONFIG_SEEDS[4] + 50)
+    wg = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, n_ff * hidden, rng), synth.Q4_K, synth.GGUF, n_ff, hidden)
+    wu = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, n_ff * hidden, rng), synth.Q4_K, synth.GGUF, n_ff, hidden)
+    wd = QuantizedWeight(be, synth.gen_packed(synth.Q6_K, synth.GGUF, hidden * n_ff, rng), synth.Q6_K, synth.GGUF, hidden, n_ff)
+    packed = wg.packed_bytes + wu.packed_bytes + wd.packed_bytes
+    rows = []
+    for m in (1, 512):
+        x = synth.gen_activations(m, hidden, synth.rng_for(60 + m))
+        xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
+        ob = be.allocate_buffer(m * hidden * 4)
+        plan = projections.MlpSwiglu(be, xb, wg, wu, wd, ob, m)
+        for _ in range(3):
+            plan.run()
+        be.synchronize()
+        be.timer_start()
+        for _ in range(steps):
+            plan.run()
+        ms = be.timer_stop_ms() / steps
+        be.synchronize()
+        rows.append({"m": m, "ms": ms, "packed_GB/s": packed / (ms * 1e-3) / 1e9,
+                     "tflops": 2.0 * m * 3 * n_ff * hidden / (ms * 1e-3) / 1e12})
+        plan.free(); xb.free(); ob.free()
+    for w in (wg, wu, wd):
+        w.free()
+    return {"workload": "llama-2-7b SwiGLU MLP block, gate/up Q4_K + down Q6_K (87.7 MB packed), b200q_mlp_run",
+            "launches_per_run": {"m=1": 3, "m=512": 7}, "shapes": rows}
+
+
 def shard_leg(be, rank, world, steps):
     """Column split of the Llama-70B-shaped FFN projection [28672, 8192] over the ranks + NCCL all-gather."""
     import torch
@@ -410,6 +444,7 @@ def main():
         if world == 1:
             # ---- prefill GEMM (second half of the metric) and a single large Q4_K GEMV --------------------------
             out["gemm"] = gemm_leg(be, peaks, 10)
+            out["mlp"] = mlp_leg(be, peaks, 10)
             rng = synth.rng_for(4242)
             big = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, 65536 * 4096, rng), synth.Q4_K, synth.GGUF, 65536, 4096)
             msb = time_matmul(be, big, 1, 20, 3)
