@@ -15,6 +15,9 @@ namespace b200q {
 // activation is applied to the UP projection, and the operation order below is that kernel's)
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                      float* __restrict__ out, int64_t total) {
+    // the product that follows may start its CTAs and stream its weights while this kernel runs; it waits for
+    // this kernel's completion (griddepcontrol.wait) before it reads the activations written here
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i4 >= total) return;
     if (i4 + 4 <= total) {

@@ -315,9 +315,9 @@ __device__ __forceinline__ void finish_tile(float (&acc)[2][MT], const GOp& op, 
 // out of the 12 packed bytes (different bit positions in the first and second half of a super-block), the 64
 // codes become 16 A registers (one AND per pair of weights), 8 MMAs per activation row, and the block
 // scales are folded into the accumulator: acc += d * (scA * vA + scB * vB) - dmin * (mA * sumA + mB * sumB).
-template <int MT>
+template <int MT, class Late>
 __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
-                                        int ring_d, int m, int kw, float* red) {
+                                        int ring_d, int m, int kw, float* red, Late&& late) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
     const int depth = 2 * ring_d;
     const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * Q4K_SLOT_BYTES;
@@ -352,6 +352,7 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < depth; d++) issue_next();
+    late();   // the first product of a CTA builds its activation image only now: the weights are already on their way
     const uint8_t* cslot = ring_gen;
     const uint8_t* cend = ring_gen + depth * Q4K_SLOT_BYTES;
 
@@ -430,9 +431,9 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
 // ------------------------------------------------------------------------------------------- Q6_K (GGUF)
 // One product segment, Q6_K: acc += d * sc * (sum q x - 32 sum x) per 16-weight run (the activation image
 // stores 32 sum x).
-template <int MT>
+template <int MT, class Late>
 __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
-                                        int ring_d, int m, int kw, float* red) {
+                                        int ring_d, int m, int kw, float* red, Late&& late) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t ring = smem_addr(ring_gen), ring_end = ring + ring_d * Q6K_SLOT_BYTES;
     const int keep = ring_d - 1;
@@ -463,6 +464,7 @@ __device__ __forceinline__ void run_q6k(const GOp& op, const Seg& sg, const XImg
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < ring_d; d++) issue_next();
+    late();   // the first product of a CTA builds its activation image only now: the weights are already on their way
     const uint8_t* cslot = ring_gen;
     const uint8_t* cend = ring_gen + ring_d * Q6K_SLOT_BYTES;
 
@@ -572,9 +574,9 @@ __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t v) {
     return (v & 0x00070007u) * 512u + (v & 0x00080008u) * 4096u;
 }
 
-template <int MT>
+template <int MT, class Late>
 __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
-                                        int ring_d, int m, int kw, float* red) {
+                                        int ring_d, int m, int kw, float* red, Late&& late) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int depth = min(8, ring_d * RING_UNIT_BYTES / MX4_SLOT_BYTES) >= 8 ? 8 : 4;
     const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * MX4_SLOT_BYTES;
@@ -603,6 +605,7 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < depth; d++) issue_next();
+    late();   // the first product of a CTA builds its activation image only now: the weights are already on their way
     const uint8_t* cslot = ring_gen;
     const uint8_t* cend = ring_gen + depth * MX4_SLOT_BYTES;
 
@@ -693,6 +696,11 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         opi = lo;
     }
     if (threadIdx.x < XZERO_BYTES / 4) reinterpret_cast<uint32_t*>(xbase)[threadIdx.x] = 0u;   // published by the first barrier
+    // Programmatic dependent launch: the next kernel of the stream may start its CTAs as ours retire; like this
+    // kernel it touches nothing an earlier kernel writes (activations, outputs) before its griddepcontrol.wait,
+    // only the immutable packed weights.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    bool first = true;
 
     for (int seg_b = tb; seg_b < te;) {
         // ---- one product: tiles [seg_b, seg_e) of this CTA belong to it
@@ -705,10 +713,24 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         __syncthreads();   // everyone is done with the previous product's activations and the reduction scratch
         XImg xs = ximg_carve(xbase, op.k, m);
         const bool q4 = op.fmt == F_Q4K;
-        if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
-        else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
-        else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
-        __syncthreads();
+        auto prep = [&]() {
+            if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
+            else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
+            else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
+            __syncthreads();
+        };
+        // The CTA's first product starts streaming its weights BEFORE it waits for the kernels ahead of it in the
+        // stream (whose outputs its activations may be) and builds the activation image; later products find the
+        // dependency resolved and prepare first.
+        const bool late_prep = first;
+        first = false;
+        if (!late_prep) prep();
+        auto late = [&]() {
+            if (late_prep) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                prep();
+            }
+        };
 
         const int kw = 1 << op.kw_log2;
         const int kpart = warp & (kw - 1);
@@ -720,9 +742,9 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         sg.wrow = warp >> op.kw_log2;
         sg.tile0 = op.tile0;
         sg.n_rows = op.n_rows; sg.nh = nh;
-        if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
-        else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
-        else run_mx4<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red);
+        if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else run_mx4<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         seg_b = seg_e;
     }
 }
@@ -794,12 +816,24 @@ int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n
     }
     GOp single{};
     if (h_single) single = *h_single;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)n_ctas);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap with the tail of the kernel ahead
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le;
     switch (mi) {
-        case 0: gemv_mma_kernel<1><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        case 1: gemv_mma_kernel<2><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        case 2: gemv_mma_kernel<4><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        default: gemv_mma_kernel<8><<<n_ctas, 256, smem_bytes, ctx->stream>>>(single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        case 0: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        case 1: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<2>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        case 2: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<4>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
+        default: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<8>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
     }
+    B200Q_CUDA(le, B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
