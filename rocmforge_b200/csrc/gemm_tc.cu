@@ -800,10 +800,14 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a kernel behind this one may start its CTAs as ours retire
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (activations)
         if (lane == 0) {
+            // programmatic dependent launch: the f16 activations come from the kernel ahead of this one; the raw
+            // weight copies and their conversion into tensor memory (warps 2, 4..11) do not wait for it
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int it = 0;
             for (int u = u0; u < u1 && ok;) {
                 const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
@@ -1141,6 +1145,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             if (!ok) break;
             // ------------------------------------------------------------ epilogue of this segment
+            if (seg == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // the row scales come from the kernel ahead
             SKT(seg * 32 + 1);
             if (lane == 0) ok = mbar_wait(smem_u32(accum), (uint32_t)(seg & 1), abort_flag, a.status, 6);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -1303,6 +1308,9 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
                                                        float* __restrict__ scale, int k, int perm) {
+    // the prefill kernel behind this one may start: it streams and converts weights, and waits for this
+    // kernel's completion (griddepcontrol.wait) before it touches the f16 activations or their scales
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.x;
     const T* xr = x + (int64_t)row * ldx;
     float mx = 0.0f;
@@ -1427,6 +1435,24 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
     return tiles * (w->k / 256) < (1ll << 30);
 }
 
+// Launch of the persistent prefill kernel with programmatic stream serialisation: its CTAs may start while the
+// kernel ahead of it in the stream (the activation conversion) is still running.
+template <class K>
+cudaError_t launch_sk(b200q_ctx* ctx, K kernel, int ctas, size_t smem, const CUtensorMap& m0, const CUtensorMap& m1,
+                      const CUtensorMap& m2, const CUtensorMap& m3, const CUtensorMap& m4, const CUtensorMap& m5, const SkArgs& k) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, m0, m1, m2, m3, m4, m5, k);
+}
+
 int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
                      int m, const char* who, bool may_allocate) {
     EncodeTiledFn enc = get_encode_fn();
@@ -1512,8 +1538,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<2><<<ctas, NTHREADS, smem, ctx->stream>>>(map, pm[0], pm[1], pm[2], ymap, wsmap, k);
-        B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<2>, ctas, smem, map, pm[0], pm[1], pm[2], ymap, wsmap, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (may_allocate && mx4_tmem_path(w, m)) {
@@ -1549,8 +1574,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        gemm_tmem_sk_kernel<1><<<ctas, NTHREADS, smem, ctx->stream>>>(map, wmap, wmap, wmap, ymap, wsmap, k);
-        B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
@@ -1591,8 +1615,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            gemm_tmem_sk_kernel<0><<<ctas, NTHREADS, smem + 32 + STAGE_EPI_BYTES, ctx->stream>>>(map, wmap, wmap, wmap, ymap, wsmap, k);
-            B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+            B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, k), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
         gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
