@@ -721,6 +721,11 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 // 8 x 16 code bytes per 256 k from the code plane; the 8 exponent bytes come by a plain load). MXFP4 codes
 // become f16 by bit placement (E2M1 s|ee|m at bits 15|11..9 is value * 2^-14) and one HMUL2 with the block
 // scale 2^(e-127) * 2^14, which has to lie in the f16 range (block exponents 2^-28 .. 2^1).
+// Output tensor maps of the other GPUs' buffers for a scattered product (peer-mapped memory; TMA STORES only)
+struct PeerMaps {
+    CUtensorMap m[7];
+};
+
 #ifdef B200Q_SK_TRACE
 // Scratch build only: time stamps go to shared memory and are copied out at the end of the kernel.
 __device__ long long g_sk_trace[160 * 128];
@@ -737,7 +742,8 @@ template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3,
-                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_ws, SkArgs k) {
+                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_ws,
+                    const __grid_constant__ PeerMaps peers, SkArgs k) {
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
@@ -1230,6 +1236,8 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     SKT(seg * 32 + 7 + (rnd >> 6) * 5);
                     if (lane == 0 && c0 < a.bn) {
                         tma_store_2d(&tmap_y, smem_u32(wstg), row0 + q * 32, tok0 + c0);
+                        // scattered product: the same block into the other GPUs' outputs, over NVLink
+                        for (int pp = 0; pp < a.n_extra; pp++) tma_store_2d(&peers.m[pp], smem_u32(wstg), row0 + q * 32, tok0 + c0);
                         bulk_commit();
                     }
                     SKT(seg * 32 + 8 + (rnd >> 6) * 5);
@@ -1439,7 +1447,8 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
 // kernel ahead of it in the stream (the activation conversion) is still running.
 template <class K>
 cudaError_t launch_sk(b200q_ctx* ctx, K kernel, int ctas, size_t smem, const CUtensorMap& m0, const CUtensorMap& m1,
-                      const CUtensorMap& m2, const CUtensorMap& m3, const CUtensorMap& m4, const CUtensorMap& m5, const SkArgs& k) {
+                      const CUtensorMap& m2, const CUtensorMap& m3, const CUtensorMap& m4, const CUtensorMap& m5,
+                      const PeerMaps& peers, const SkArgs& k) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(NTHREADS);
@@ -1450,7 +1459,7 @@ cudaError_t launch_sk(b200q_ctx* ctx, K kernel, int ctas, size_t smem, const CUt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, m0, m1, m2, m3, m4, m5, k);
+    return cudaLaunchKernelEx(&cfg, kernel, m0, m1, m2, m3, m4, m5, peers, k);
 }
 
 int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
@@ -1476,14 +1485,20 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
     // tile stores of the persistent kernel's staged epilogue: y as a [m, n_local] fp32 tensor with row pitch ldy
     CUtensorMap ymap = map;
-    const bool y_tma_ok = ctx->scatter_extra == 0 && (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(d_y) & 15) == 0;
+    bool y_tma_ok = (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(d_y) & 15) == 0;
+    for (int p = 0; p < ctx->scatter_extra; p++) y_tma_ok = y_tma_ok && (reinterpret_cast<uintptr_t>(ctx->scatter_y[p]) & 15) == 0;
+    PeerMaps peers;
+    for (int p = 0; p < 7; p++) peers.m[p] = map;
     if (y_tma_ok) {
         cuuint64_t ydim[2] = {(cuuint64_t)w->n_local, (cuuint64_t)m};
         cuuint64_t ystr[1] = {(cuuint64_t)ldy * 4};
         cuuint32_t ybox[2] = {32u, 32u};   // one epilogue warp's block: 32 weight rows x 32 activation rows
-        r = enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, d_y, ydim, ystr, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output) failed with code %d", who, (int)r);
+        for (int p = -1; p < ctx->scatter_extra; p++) {   // this GPU's output, then the peers' (a scattered product)
+            r = enc(p < 0 ? &ymap : &peers.m[p], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p < 0 ? d_y : ctx->scatter_y[p], ydim, ystr, ybox,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output %d) failed with code %d", who, p + 1, (int)r);
+        }
     }
 #ifdef B200Q_SK_TRACE
     constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64 + 1024;
@@ -1538,7 +1553,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<2>, ctas, smem, map, pm[0], pm[1], pm[2], ymap, wsmap, k), B200Q_ERR_LAUNCH);
+        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<2>, ctas, smem, map, pm[0], pm[1], pm[2], ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (may_allocate && mx4_tmem_path(w, m)) {
@@ -1574,7 +1589,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, k), B200Q_ERR_LAUNCH);
+        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
@@ -1615,7 +1630,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, k), B200Q_ERR_LAUNCH);
+            B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
         gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
