@@ -178,7 +178,8 @@ int b200q_batch_launches(const b200q_batch* batch);
  *      (shard_rank / shard_count of b200q_weight_upload) produces y[:, row0 : row0 + n_local]. matmul_scatter
  *      fuses the gather into the product: d_y_full lists the FULL outputs [m, ldy] of every GPU that needs the
  *      result (this GPU's own first or anywhere; the others peer-mapped through b200q_ipc_open), and the
- *      kernels' epilogues store the slice into its column block of each of them with plain stores over NVLink.
+ *      kernels' epilogues store the slice into its column block of each of them over NVLink (plain stores in the
+ *      decode kernel, TMA stores from shared memory in the persistent prefill kernel; nothing is ever loaded from a peer).
  *      fp32 outputs; the decode kernel's formats for m <= 8, the prefill kernels for m > 8. The caller
  *      synchronises the GPUs (a barrier or any collective on the same streams) before reading.
  *      ipc_*: cudaIpcGetMemHandle / OpenMemHandle / CloseMemHandle on a b200q_malloc'ed buffer; the 64 handle

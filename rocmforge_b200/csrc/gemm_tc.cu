@@ -266,7 +266,7 @@ struct GemmArgs {
     int a_col0;            // first TMEM column of the weight-operand slots (kernel with the A operand in TMEM)
     int* status;
     int n_extra;           // further copies of y to write: the same slice inside other GPUs' full outputs
-    float* y_extra[7];     // (peer-mapped pointers; plain stores over NVLink, no loads)
+    float* y_extra[7];     // (peer-mapped pointers; stores over NVLink only, plain or TMA, never loads)
     int staged_epilogue;   // persistent kernel: finished tiles leave through shared memory and tiled TMA stores
 };
 
