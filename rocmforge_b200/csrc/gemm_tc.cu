@@ -1225,11 +1225,16 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (lane == 0) bulk_wait_read0();
                     __syncwarp();
                     SKT(seg * 32 + 6 + (rnd >> 6) * 5);
+                    // row scales of the block's 32 activation rows: 128-byte aligned, read four at a time (the
+                    // scale array is padded, and rows past m are clipped by the store)
+                    const float4* sc4 = reinterpret_cast<const float4*>(a.xscale + tok0 + c0);
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int tok = tok0 + c0 + j;
-                        const float sc = tok < a.m ? __ldg(a.xscale + tok) : 0.0f;
-                        wstg[j * 32 + lane] = __uint_as_float(v[j]) * sc;
+                    for (int j4 = 0; j4 < 8; j4++) {
+                        const float4 sc = __ldg(sc4 + j4);
+                        wstg[(4 * j4 + 0) * 32 + lane] = __uint_as_float(v[4 * j4 + 0]) * sc.x;
+                        wstg[(4 * j4 + 1) * 32 + lane] = __uint_as_float(v[4 * j4 + 1]) * sc.y;
+                        wstg[(4 * j4 + 2) * 32 + lane] = __uint_as_float(v[4 * j4 + 2]) * sc.z;
+                        wstg[(4 * j4 + 3) * 32 + lane] = __uint_as_float(v[4 * j4 + 3]) * sc.w;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
@@ -1665,7 +1670,8 @@ bool gemm_tc_supported(const b200q_weight* w, int m) {
 int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m) {
     if (!gemm_tc_supported(w, m)) return fail(B200Q_ERR_UNSUPPORTED, "gemm: needs an NK tensor with k %% 64 == 0");
     const size_t x16_bytes = ((size_t)m * w->k * 2 + 255) & ~(size_t)255;
-    int rc = ensure_scratch(ctx, x16_bytes + (size_t)m * sizeof(float), 2);
+    // + 2 KB: the staged epilogue reads the scales of whole 32-row blocks, up to one tile past row m
+    int rc = ensure_scratch(ctx, x16_bytes + (size_t)m * sizeof(float) + 2048, 2);
     if (rc != B200Q_OK) return rc;
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
