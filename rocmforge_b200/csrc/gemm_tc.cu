@@ -21,11 +21,15 @@
 //                     copied to f16 with one power-of-two scale per row, so neither large nor small rows
 //                     leave the f16 range; the scale is multiplied back in the epilogue
 //   D               : fp32 in tensor memory, 128 lanes x BN columns; read back with tcgen05.ld by eight
-//                     warps (two per lane quarter) and stored to y, coalesced along n
+//                     warps (two per lane quarter). The persistent kernel scales each warp's 32 x 32 block into
+//                     a private shared-memory buffer and writes it with one TMA store per warp (and per rank
+//                     of a scattered product); the other kernels store from registers, coalesced along n
 //
 // Warp roles (384 threads): warp 0 = TMA producer + TMEM allocator, warp 1 = MMA issuer (one elected
-// thread), warp 2 = raw-weight loader (tensor-memory kernels), 8 producer / converter warps that are also
-// the epilogue warps. Rings of stages are handed over with mbarriers: full (producer arrivals + TMA
+// thread), warp 2 = raw-weight loader (tensor-memory kernels), warp 3 = partial-sum publisher and prefetcher
+// (persistent kernel), 8 producer / converter warps that are also the epilogue warps. The persistent kernel
+// is launched with programmatic stream serialisation: weight copies and conversion start while the
+// activation conversion kernel ahead of it still runs (griddepcontrol.wait before the first activation copy). Rings of stages are handed over with mbarriers: full (producer arrivals + TMA
 // transaction bytes), empty (tcgen05.commit).
 // Every wait is bounded by a clock budget; on expiry the kernel raises a status word, all roles leave
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
