@@ -440,7 +440,7 @@ def main():
             dt = float(t.item())
         out["e2e"] = {"value": world * STEP_BYTES / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(hx.numel() * 4),
                       "d2h_bytes_per_step": int(hy.numel() * 4), "ms_per_step": dt * 1e3,
-                      "api": "b200q_batch_run_host: pinned host activations in, host outputs out, weights resident (uploaded once)"}
+                      "api": "b200q_batch_run_host: pinned host activations in (one H2D copy), outputs stored by the kernel straight into the pinned host buffer, weights resident (uploaded once)"}
         if world == 1:
             # ---- prefill GEMM (second half of the metric) and a single large Q4_K GEMV --------------------------
             out["gemm"] = gemm_leg(be, peaks, 10)

@@ -165,7 +165,10 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out);
 /* Host activations in, host results out for the whole batch: h_x_all is the [m, k_i] inputs of the products
  * back to back in batch order, h_y_all receives the [m, n_i] outputs the same way. Copies ride the context's
  * stream (one copy each way when the batch's device buffers are contiguous) and the call returns after the
- * results have landed. The reference's process_batch takes a device input and returns device buffers
+ * results have landed. When h_y_all is page-locked host memory the device can address (cudaHostAlloc /
+ * cudaHostRegister, a pinned torch tensor) and the batch is one grouped launch, the kernel stores its results
+ * straight into h_y_all — posted writes that overlap the launch — and the batch's device output buffers are
+ * left untouched by that call. The reference's process_batch takes a device input and returns device buffers
  * (batch_quantized.rs:147-161); this is the same call for a caller whose tensors live on the host. */
 int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_all, float* h_y_all);
 int b200q_batch_free(b200q_batch* batch);

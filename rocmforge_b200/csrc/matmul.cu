@@ -22,6 +22,12 @@ struct b200q_batch {
     int n_ctas = 0, total_tiles = 0, ring_d = 4;
     size_t smem = 0;
     GOp single{};
+    // host-output variant of the plan (b200q_batch_run_host with pinned, device-mapped outputs): the same
+    // products with y pointing into the caller's host buffer
+    std::vector<GOp> h_ops;
+    GOp* d_ops_hosty = nullptr;
+    const float* hosty_base = nullptr;
+    GOp single_hosty{};
 };
 
 static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
@@ -274,6 +280,7 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
             return cuda_fail(B200Q_ERR_ALLOC, e, "batch_create");
         }
         b->grouped = true;
+        b->h_ops = ops;
         b->n_ctas = n_ctas;
         b->total_tiles = total;
         b->smem = smem;
@@ -331,6 +338,36 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
             off += xb;
         }
     }
+    // Outputs in pinned host memory the device can address: the grouped kernel stores its results straight into
+    // them (posted writes over PCIe, overlapped with the rest of the launch) instead of a device buffer + a copy.
+    if (batch->grouped && batch->w[0]->ctx->scatter_extra == 0) {
+        cudaPointerAttributes pa{};
+        if (cudaPointerGetAttributes(&pa, h_y_all) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer) {
+            float* dy = static_cast<float*>(pa.devicePointer);
+            if (batch->hosty_base != h_y_all) {
+                std::vector<GOp> ops = batch->h_ops;
+                size_t off = 0;
+                for (size_t i = 0; i < cnt; i++) {
+                    ops[i].y = dy + off;
+                    off += (size_t)batch->m * batch->w[i]->n_local;
+                }
+                cudaError_t e = cudaSuccess;
+                if (!batch->d_ops_hosty) e = cudaMalloc(&batch->d_ops_hosty, sizeof(GOp) * cnt);
+                if (e == cudaSuccess) e = cudaMemcpyAsync(batch->d_ops_hosty, ops.data(), sizeof(GOp) * cnt, cudaMemcpyHostToDevice, ctx->stream);
+                if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // `ops` is pageable and local
+                if (e != cudaSuccess) return cuda_fail(B200Q_ERR_ALLOC, e, "batch_run_host");
+                batch->single_hosty = ops[0];
+                batch->hosty_base = h_y_all;
+            }
+            int n = (int)cnt;
+            int rc = launch_gemv_mma(ctx, &batch->single_hosty, batch->d_ops_hosty, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
+                                     batch->total_tiles, batch->m, batch->smem, batch->ring_d);
+            if (rc != B200Q_OK) return rc;
+            B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
+            return B200Q_OK;
+        }
+        cudaGetLastError();   // pageable host memory: not an error, take the copy path
+    }
     int rc = b200q_batch_run(ctx, batch, nullptr);
     if (rc != B200Q_OK) return rc;
     if (yc) {
@@ -354,6 +391,7 @@ int b200q_batch_free(b200q_batch* batch) {
         cudaStreamSynchronize(batch->ctx->stream);
         if (batch->d_ops) cudaFree(batch->d_ops);
         if (batch->d_ranges) cudaFree(batch->d_ranges);
+        if (batch->d_ops_hosty) cudaFree(batch->d_ops_hosty);
         cudaGetLastError();
     }
     delete batch;

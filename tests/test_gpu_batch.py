@@ -96,3 +96,31 @@ def test_batch_argument_errors():
     assert be.lib.b200q_batch_run(be.ctx, b, None) == 0
     assert be.lib.b200q_batch_free(b) == 0
     assert be.lib.b200q_batch_run(be.ctx, None, None) == _lib.ERR_INVALID
+
+
+def test_run_host_pinned_outputs_equal_pageable_outputs():
+    """b200q_batch_run_host: with page-locked, device-addressable outputs the grouped kernel stores straight into
+    host memory; the bits must equal the device-buffer + copy path taken for pageable memory."""
+    torch = pytest.importorskip("torch")
+    from rocmforge_b200.batch import DeviceBatch
+    be = backend()
+    m = 2
+    rng = synth.rng_for(8101)
+    shapes = [(synth.Q4_K, 896, 896), (synth.Q4_K, 128, 896), (synth.Q6_K, 896, 4864), (synth.MXFP4, 512, 1024)]
+    ws = [QuantizedWeight(be, synth.gen_packed(q, synth.GGUF, n * k, rng), q, synth.GGUF, n, k) for q, n, k in shapes]
+    batch = DeviceBatch(be, ws, m)
+    assert batch.launches == 1
+    xtot, ytot = sum(batch.xsizes), sum(batch.ysizes)
+    hx = torch.from_numpy(rng.standard_normal(xtot, dtype=np.float32)).pin_memory()
+    hy_pinned = torch.full((ytot + 16,), float("nan"), dtype=torch.float32).pin_memory()
+    hy_paged = np.full(ytot, np.nan, dtype=np.float32)
+    batch.run_host(hx.data_ptr(), hy_paged.ctypes.data)
+    batch.run_host(hx.data_ptr(), hy_pinned.data_ptr())
+    batch.run_host(hx.data_ptr(), hy_pinned.data_ptr())          # the host-output plan is cached and reused
+    got = hy_pinned.numpy()
+    assert np.all(np.isfinite(hy_paged))
+    assert np.array_equal(got[:ytot].view(np.uint32), hy_paged.view(np.uint32))
+    assert np.all(np.isnan(got[ytot:]))                          # nothing written past the outputs
+    batch.free()
+    for w in ws:
+        w.free()
