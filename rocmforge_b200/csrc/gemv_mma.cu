@@ -39,6 +39,7 @@ namespace {
 constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
+constexpr int F_Q40 = fmt_of(Q4_0, GGUF);
 constexpr int RED_FLOATS = 8 * 16 * 8;   // 8 warps x 16 rows x up to 8 activation rows
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -157,6 +158,7 @@ constexpr int Q6K_DATA_BYTES = 2 * 2 * 32 * 16, Q6K_SLOT_BYTES = Q6K_DATA_BYTES 
 constexpr int Q4K_DATA_BYTES = 2 * 32 * 16, Q4K_SLOT_BYTES = Q4K_DATA_BYTES + RING_HDR_BYTES;       // 1280
 constexpr int RING_UNIT_BYTES = 2 * Q4K_SLOT_BYTES;                                                // 2560 >= 2304
 constexpr int MX4_DATA_BYTES = 2 * 32 * 16, MX4_SLOT_BYTES = MX4_DATA_BYTES + 2 * 8 * 4;           // 1088
+constexpr int Q40_SLOT_BYTES = MX4_DATA_BYTES + 2 * 8 * 8;                                          // 1152: four f16 scales per row
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -549,24 +551,34 @@ struct MX4Cursor {
     int64_t dq, de;         // byte distances to row g+8 (0 when that row is past the end)
 };
 
+// Q40 = GGUF Q4_0 on the same path: the same 16 code bytes per block (byte i = elements i and i+16), and an
+// f16 scale d per block (2 bytes) where MXFP4 has its exponent byte.
+template <bool Q40>
 __device__ __forceinline__ void mx4_seek(MX4Cursor& c, const GOp& op, const Seg& sg, int tile, int g, int t) {
+    constexpr int SB = Q40 ? 8 : 4;   // scale bytes of one row's half (four blocks)
     const int rb = seg_row_base(sg, tile) + g;
     const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
     const int64_t hs = r0 * sg.nh + sg.hb;
     c.q = op.v.p[1] + hs * 64 + t * 16;
-    c.e = op.v.p[0] + hs * 4;
+    c.e = op.v.p[0] + hs * SB;
     const bool two = rb + 8 <= sg.n_rows - 1;
     c.dq = two ? (int64_t)sg.nh * 8 * 64 : 0;
-    c.de = two ? (int64_t)sg.nh * 8 * 4 : 0;
+    c.de = two ? (int64_t)sg.nh * 8 * SB : 0;
 }
+template <bool Q40>
 __device__ __forceinline__ void mx4_issue(MX4Cursor& c, uint32_t slot, int lane) {
     cp_async16(slot + lane * 16, c.q);
     cp_async16(slot + 512 + lane * 16, c.q + c.dq);
     if ((lane & 3) == 0) {
-        cp_async4(slot + MX4_DATA_BYTES + (lane >> 2) * 4, c.e);
-        cp_async4(slot + MX4_DATA_BYTES + 32 + (lane >> 2) * 4, c.e + c.de);
+        if constexpr (Q40) {
+            cp_async8(slot + MX4_DATA_BYTES + (lane >> 2) * 8, c.e);
+            cp_async8(slot + MX4_DATA_BYTES + 64 + (lane >> 2) * 8, c.e + c.de);
+        } else {
+            cp_async4(slot + MX4_DATA_BYTES + (lane >> 2) * 4, c.e);
+            cp_async4(slot + MX4_DATA_BYTES + 32 + (lane >> 2) * 4, c.e + c.de);
+        }
     }
-    c.q += 64; c.e += 4;
+    c.q += 64; c.e += Q40 ? 8 : 4;
 }
 
 // two E2M1 codes (bits 0..3 and 16..19 of v) -> f16x2 holding value * 2^-14
@@ -574,12 +586,13 @@ __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t v) {
     return (v & 0x00070007u) * 512u + (v & 0x00080008u) * 4096u;
 }
 
-template <int MT, class Late>
+template <int MT, bool Q40, class Late>
 __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
                                         int ring_d, int m, int kw, float* red, Late&& late) {
+    constexpr int SLOT_BYTES = Q40 ? Q40_SLOT_BYTES : MX4_SLOT_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int depth = min(8, ring_d * RING_UNIT_BYTES / MX4_SLOT_BYTES) >= 8 ? 8 : 4;
-    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * MX4_SLOT_BYTES;
+    const int depth = min(8, ring_d * RING_UNIT_BYTES / SLOT_BYTES) >= 8 ? 8 : 4;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * SLOT_BYTES;
     const int keep = depth - 1;
     const bool has_items = sg.hb < sg.he;
     const bool active = (g >> 1) == t;
@@ -591,51 +604,66 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
     MX4Cursor cur{};
     int pt = sg.seg_b, ph = sg.hb;
     uint32_t pslot = ring;
-    if (has_items && pt < sg.seg_e) mx4_seek(cur, op, sg, pt, g, t);
+    if (has_items && pt < sg.seg_e) mx4_seek<Q40>(cur, op, sg, pt, g, t);
     auto issue_next = [&]() {
         if (has_items && pt < sg.seg_e) {
-            mx4_issue(cur, pslot, lane);
+            mx4_issue<Q40>(cur, pslot, lane);
             if (++ph == sg.he) {
                 ph = sg.hb;
-                if (++pt < sg.seg_e) mx4_seek(cur, op, sg, pt, g, t);
+                if (++pt < sg.seg_e) mx4_seek<Q40>(cur, op, sg, pt, g, t);
             }
         }
         cp_commit();
-        pslot += MX4_SLOT_BYTES;
+        pslot += SLOT_BYTES;
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < depth; d++) issue_next();
     late();   // the first product of a CTA builds its activation image only now: the weights are already on their way
     const uint8_t* cslot = ring_gen;
-    const uint8_t* cend = ring_gen + depth * MX4_SLOT_BYTES;
+    const uint8_t* cend = ring_gen + depth * SLOT_BYTES;
 
     for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
         float acc[2][MT];
 #pragma unroll
         for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
         const uint4* bp = bbase + sg.hb * bstep;
+        const float* sp = xs.sum + ((size_t)sg.hb * 8 + 2 * t) * m;   // Q4_0: 8 * sum(x) of the block's two 16-weight runs
         for (int h = sg.hb; h < sg.he; h++) {
             cp_wait_keep(keep);
             __syncwarp();
             const uint4* sd = reinterpret_cast<const uint4*>(cslot);
-            const uint32_t* se = reinterpret_cast<const uint32_t*>(cslot + MX4_DATA_BYTES);
             const uint4 wa = sd[lane], wb = sd[32 + lane];
             float S[2];
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const uint32_t eb = (se[i * 8 + g] >> (8 * t)) & 0xFFu;
-                // 2^(e-127) * 2^14, over the 2^24 every product's final factor carries for the integer-coded formats
-                S[i] = gguf_e8m0_half((uint8_t)eb) * (1.0f / 512.0f);
-            }
             const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
             const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
             uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][bytes (0,2) | (1,3)]
+            if constexpr (Q40) {
+                const uint16_t* sdh = reinterpret_cast<const uint16_t*>(cslot + MX4_DATA_BYTES);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                aL[0][j][0] = e2m1x2_to_f16x2(w0[j]);       aL[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 8);
-                aH[0][j][0] = e2m1x2_to_f16x2(w0[j] >> 4);  aH[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 12);
-                aL[1][j][0] = e2m1x2_to_f16x2(w1[j]);       aL[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 8);
-                aH[1][j][0] = e2m1x2_to_f16x2(w1[j] >> 4);  aH[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 12);
+                for (int i = 0; i < 2; i++) S[i] = __half2float(__ushort_as_half(sdh[(i * 8 + g) * 4 + t]));   // d of block t
+                const uint32_t ML = 0x000F000Fu;   // an integer code in the low bits of an f16 lane is code * 2^-24
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    aL[0][j][0] = w0[j] & ML;          aL[0][j][1] = (w0[j] >> 8) & ML;
+                    aH[0][j][0] = (w0[j] >> 4) & ML;   aH[0][j][1] = (w0[j] >> 12) & ML;
+                    aL[1][j][0] = w1[j] & ML;          aL[1][j][1] = (w1[j] >> 8) & ML;
+                    aH[1][j][0] = (w1[j] >> 4) & ML;   aH[1][j][1] = (w1[j] >> 12) & ML;
+                }
+            } else {
+                const uint32_t* se = reinterpret_cast<const uint32_t*>(cslot + MX4_DATA_BYTES);
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const uint32_t eb = (se[i * 8 + g] >> (8 * t)) & 0xFFu;
+                    // 2^(e-127) * 2^14, over the 2^24 every product's final factor carries for the integer-coded formats
+                    S[i] = gguf_e8m0_half((uint8_t)eb) * (1.0f / 512.0f);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    aL[0][j][0] = e2m1x2_to_f16x2(w0[j]);       aL[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 8);
+                    aH[0][j][0] = e2m1x2_to_f16x2(w0[j] >> 4);  aH[0][j][1] = e2m1x2_to_f16x2(w0[j] >> 12);
+                    aL[1][j][0] = e2m1x2_to_f16x2(w1[j]);       aL[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 8);
+                    aH[1][j][0] = e2m1x2_to_f16x2(w1[j] >> 4);  aH[1][j][1] = e2m1x2_to_f16x2(w1[j] >> 12);
+                }
             }
 #pragma unroll
             for (int n = 0; n < MT; n++) {
@@ -652,15 +680,18 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
                     mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
                     mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
                     mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
+                    // Q4_0: d * (sum q x - 8 sum x) over the block
+                    const float off = Q40 ? sp[n] + sp[m + n] : 0.0f;
 #pragma unroll
                     for (int i = 0; i < 2; i++)
-                        acc[i][n] = fmaf(S[i], (cL[2 * i] + cL[2 * i + 1]) + (cH[2 * i] + cH[2 * i + 1]), acc[i][n]);
+                        acc[i][n] = fmaf(S[i], (cL[2 * i] + cL[2 * i + 1]) + (cH[2 * i] + cH[2 * i + 1]) - off, acc[i][n]);
                 }
             }
             bp += bstep;
+            sp += 8 * m;
             __syncwarp();
             issue_next();
-            cslot += MX4_SLOT_BYTES;
+            cslot += SLOT_BYTES;
             if (cslot == cend) cslot = ring_gen;
         }
         finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
@@ -669,7 +700,9 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
 }
 
 // ---------------------------------------------------------------------------------------------- kernel
-template <int MT>
+// Q40K: the instantiation that also carries the GGUF Q4_0 path. Launches without a Q4_0 product use the other
+// one, whose code (and register allocation) is exactly that of the three-format kernel.
+template <int MT, bool Q40K>
 __global__ void __launch_bounds__(256, 2)
 gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_tiles, int m,
                 int ring_d) {
@@ -716,7 +749,7 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         auto prep = [&]() {
             if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
             else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
-            else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
+            else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, (Q40K && op.fmt == F_Q40) ? 8.0f : 1.0f);
             __syncthreads();
         };
         // The CTA's first product starts streaming its weights BEFORE it waits for the kernels ahead of it in the
@@ -744,7 +777,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         sg.n_rows = op.n_rows; sg.nh = nh;
         if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
-        else run_mx4<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else if (Q40K && op.fmt == F_Q40) run_mx4<MT, Q40K>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else run_mx4<MT, false>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         seg_b = seg_e;
     }
 }
@@ -766,10 +800,12 @@ size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
            (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
+bool gemv_mma_is_q4_0(int fmt) { return fmt == F_Q40; }
+
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
-    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4) return false;
+    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4 && w->fmt != F_Q40) return false;
     if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 220 * 1024;
 }
@@ -798,21 +834,20 @@ size_t gemv_mma_smem_for(int ring_d, int kmax, int m) {
 }
 
 int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
-                    int total_tiles, int m, size_t smem_bytes, int ring_d) {
+                    int total_tiles, int m, size_t smem_bytes, int ring_d, bool has_q4_0) {
     if (total_tiles <= 0) return B200Q_OK;
-    static bool configured[64][4] = {};
+    static bool configured[64][4][2] = {};
     const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
+    const int qi = has_q4_0 ? 1 : 0;
     const int smem_cap = 226 * 1024;
-    if (!configured[ctx->device & 63][mi]) {
-        cudaError_t e = cudaSuccess;
-        switch (mi) {
-            case 0: e = cudaFuncSetAttribute(gemv_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
-            case 1: e = cudaFuncSetAttribute(gemv_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
-            case 2: e = cudaFuncSetAttribute(gemv_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
-            default: e = cudaFuncSetAttribute(gemv_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap); break;
-        }
-        B200Q_CUDA(e, B200Q_ERR_LAUNCH);
-        configured[ctx->device & 63][mi] = true;
+    const void* kernels[4][2] = {
+        {(const void*)gemv_mma_kernel<1, false>, (const void*)gemv_mma_kernel<1, true>},
+        {(const void*)gemv_mma_kernel<2, false>, (const void*)gemv_mma_kernel<2, true>},
+        {(const void*)gemv_mma_kernel<4, false>, (const void*)gemv_mma_kernel<4, true>},
+        {(const void*)gemv_mma_kernel<8, false>, (const void*)gemv_mma_kernel<8, true>}};
+    if (!configured[ctx->device & 63][mi][qi]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kernels[mi][qi], cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap), B200Q_ERR_LAUNCH);
+        configured[ctx->device & 63][mi][qi] = true;
     }
     GOp single{};
     if (h_single) single = *h_single;
@@ -826,13 +861,8 @@ int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t le;
-    switch (mi) {
-        case 0: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        case 1: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<2>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        case 2: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<4>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-        default: le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<8>, single, d_ops, n_ops, d_ranges, total_tiles, m, ring_d); break;
-    }
+    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &total_tiles, &m, &ring_d};
+    cudaError_t le = cudaLaunchKernelExC(&cfg, kernels[mi][qi], args);
     B200Q_CUDA(le, B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;

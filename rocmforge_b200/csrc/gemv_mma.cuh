@@ -30,6 +30,8 @@ void gemv_mma_plan(GOp* op, bool few_tiles);
 int gemv_mma_ring_depth(int k, int m);
 size_t gemv_mma_smem_for(int ring_d, int kmax, int m);
 int launch_gemv_mma(b200q_ctx* ctx, const GOp* h_single, const GOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
-                    int total_tiles, int m, size_t smem_bytes, int ring_d);
+                    int total_tiles, int m, size_t smem_bytes, int ring_d, bool has_q4_0);
+// true when the product needs the kernel instantiation that carries the GGUF Q4_0 path
+bool gemv_mma_is_q4_0(int fmt);
 
 }  // namespace b200q

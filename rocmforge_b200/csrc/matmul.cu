@@ -28,6 +28,7 @@ struct b200q_batch {
     GOp* d_ops_hosty = nullptr;
     const float* hosty_base = nullptr;
     GOp single_hosty{};
+    bool has_q4_0 = false;   // some product is GGUF Q4_0: the launch uses the kernel instantiation that carries it
 };
 
 static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
@@ -76,7 +77,7 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
             size_t smem = gemv_mma_smem_for(ring_d, (int)w->k, mm);
             int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
             if (n_ctas > op.ntiles) n_ctas = op.ntiles;
-            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem, ring_d);
+            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem, ring_d, gemv_mma_is_q4_0(op.fmt));
         } else {
             rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
         }
@@ -241,6 +242,7 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
         size_t smem = 0;
         for (int i = 0; i < count; i++) {
             ops[i] = make_gop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
+            b->has_q4_0 = b->has_q4_0 || gemv_mma_is_q4_0(w[i]->fmt);
             gemv_mma_plan(&ops[i], count == 1);
             ops[i].tile0 = total;
             total += ops[i].ntiles;
@@ -297,7 +299,7 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (batch->grouped) {
         int n = (int)batch->w.size();
         int rc = launch_gemv_mma(ctx, &batch->single, batch->d_ops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
-                                 batch->total_tiles, batch->m, batch->smem, batch->ring_d);
+                                 batch->total_tiles, batch->m, batch->smem, batch->ring_d, batch->has_q4_0);
         if (rc != B200Q_OK) return rc;
     } else {
         for (size_t i = 0; i < batch->w.size(); i++) {
@@ -361,7 +363,7 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
             }
             int n = (int)cnt;
             int rc = launch_gemv_mma(ctx, &batch->single_hosty, batch->d_ops_hosty, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
-                                     batch->total_tiles, batch->m, batch->smem, batch->ring_d);
+                                     batch->total_tiles, batch->m, batch->smem, batch->ring_d, batch->has_q4_0);
             if (rc != B200Q_OK) return rc;
             B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
             return B200Q_OK;

@@ -59,7 +59,7 @@ def test_grouped_launch_of_mixed_products(oracle, m):
 def test_batch_of_other_formats_falls_back_to_per_product_launches(oracle):
     be = backend()
     rng = synth.rng_for(600)
-    ops = [(synth.Q4_0, 256, 512), (synth.MXFP4, 300, 1024), (synth.Q4_K, 128, 256)]
+    ops = [(synth.Q8_0, 256, 512), (synth.MXFP4, 300, 1024), (synth.Q4_K, 128, 256)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(2, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, 2)
@@ -67,6 +67,23 @@ def test_batch_of_other_formats_falls_back_to_per_product_launches(oracle):
     for (qt, n, k), d, x, y in zip(ops, datas, xs, outs):
         w = oracle.dequantize(qt, synth.GGUF, d, n * k).reshape(n, k)
         assert rel_err(y, oracle.matmul_f32(x, w, nk=True)) <= 1e-4
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_q4_0_gguf_rides_the_grouped_tensor_core_launch(oracle, m):
+    """GGUF Q4_0 (config 1's format: [4864, 896]) shares the grouped decode launch with the K-quants and MXFP4;
+    odd row counts exercise the clamped last tile."""
+    be = backend()
+    rng = synth.rng_for(601 + m)
+    ops = [(synth.Q4_0, 4864, 896), (synth.Q4_0, 300, 1024), (synth.Q4_K, 128, 256), (synth.Q4_0, 17, 128)]
+    datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
+    xs = [synth.gen_activations(m, k, rng) for _, _, k in ops]
+    outs, ms, nb, nl = run_batch(be, ops, datas, xs, m)
+    assert nl == 1
+    for (qt, n, k), d, x, y in zip(ops, datas, xs, outs):
+        w = oracle.dequantize(qt, synth.GGUF, d, n * k).reshape(n, k)
+        assert rel_err(y, oracle.matmul_f32(x, w, nk=True)) <= 1e-4, (qt, n, k)
+        assert rel_err(y, oracle.matmul_f64(x, w, nk=True)) <= 1e-4, (qt, n, k)
 
 
 def test_large_activation_magnitudes_and_zeros(oracle):
