@@ -12,7 +12,7 @@
 //                                              K-major tile with 128-byte swizzle in SHARED memory
 //                     gemm_q4k_tmem_kernel     GGUF Q4_K: raw super-blocks by TMA, converted into TENSOR memory
 //                                              (tcgen05.st), TS-form MMA; one CTA per tile
-//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K: the same in tensor memory, persistent
+//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K / Q4_0: the same in tensor memory, persistent
 //                                              CTAs with a stream-K split over all tiles
 //                     (f16, not bf16: an 11-bit mantissa keeps the result inside the 2e-3 tolerance, bf16
 //                     weights do not)
@@ -750,7 +750,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const __grid_constant__ PeerMaps peers, SkArgs k) {
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
-    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 1 ? 128 : 208;
+    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : (QF == 1 || QF == 3) ? 128 : 208;   // QF 3 = GGUF Q4_0: MXFP4's code rows
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
     constexpr int RS = QF == 2 ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
     const GemmArgs& a = k.a;
@@ -1106,14 +1106,27 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 } else {
                 const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
                 const int64_t grow = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
-                const uint2 ex = __ldg(reinterpret_cast<const uint2*>(a.v.p[0] + grow * (a.k >> 5) + sb * 8));
+                // block scales of the 256-k step: eight exponent bytes (MXFP4) or eight f16 d (Q4_0)
+                uint4 ex = make_uint4(0u, 0u, 0u, 0u);
+                if constexpr (QF == 3) ex = __ldg(reinterpret_cast<const uint4*>(a.v.p[0] + (grow * (a.k >> 5) + sb * 8) * 2));
+                else {
+                    const uint2 e2 = __ldg(reinterpret_cast<const uint2*>(a.v.p[0] + grow * (a.k >> 5) + sb * 8));
+                    ex.x = e2.x; ex.y = e2.y;
+                }
+                const __half2 k1032 = __float2half2_rn(1032.0f);
 #pragma unroll
                 for (int c = 0; c < 4; c++, it++) {
                     const int s = it & (STAGES - 1);
                     const uint32_t ph = (uint32_t)(it >> 2) & 1;
                     const int blk = 2 * c + nib;                      // block of 32 inside the 256-k step
-                    const uint32_t eb = ((blk < 4 ? ex.x : ex.y) >> (8 * (blk & 3))) & 0xFFu;
-                    const __half2 S = __float2half2_rn(gguf_e8m0_half((uint8_t)eb) * 32768.0f);
+                    __half2 S;
+                    if constexpr (QF == 3) {
+                        const uint32_t dw = blk < 2 ? ex.x : blk < 4 ? ex.y : blk < 6 ? ex.z : ex.w;
+                        S = __half2half2(__ushort_as_half((unsigned short)((blk & 1) ? (dw >> 16) : (dw & 0xFFFFu))));
+                    } else {
+                        const uint32_t eb = ((blk < 4 ? ex.x : ex.y) >> (8 * (blk & 3))) & 0xFFu;
+                        S = __float2half2_rn(gguf_e8m0_half((uint8_t)eb) * 32768.0f);
+                    }
                     // rows are 128 bytes: the copy swizzles the 16-byte chunks with the row number so that the
                     // 32 rows of a warp do not all hit the same banks
                     const uint4 q = *reinterpret_cast<const uint4*>(rowp + ((blk ^ (r & 7)) << 4));
@@ -1123,12 +1136,24 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     for (int j = 0; j < 4; j++) {
                         // low nibbles: elements 4j..4j+3 of the block (as 0,2 | 1,3), high nibbles: 16 further on
                         const uint32_t x0 = w[j], x1 = w[j] >> 8, x2 = w[j] >> 4, x3 = w[j] >> 12;
-                        uint32_t t0 = (x0 & 0x00070007u) * 512u + (x0 & 0x00080008u) * 4096u;
-                        uint32_t t1 = (x1 & 0x00070007u) * 512u + (x1 & 0x00080008u) * 4096u;
-                        uint32_t t2 = (x2 & 0x00070007u) * 512u + (x2 & 0x00080008u) * 4096u;
-                        uint32_t t3 = (x3 & 0x00070007u) * 512u + (x3 & 0x00080008u) * 4096u;
-                        __half2 h0 = __hmul2(*reinterpret_cast<__half2*>(&t0), S), h1 = __hmul2(*reinterpret_cast<__half2*>(&t1), S);
-                        __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&t2), S), h3 = __hmul2(*reinterpret_cast<__half2*>(&t3), S);
+                        uint32_t t0, t1, t2, t3;
+                        __half2 h0, h1, h2, h3;
+                        if constexpr (QF == 3) {
+                            // Q4_0: (1024 + q) - 1032 = q - 8 exactly, then one rounding in the multiply by d
+                            t0 = (x0 & 0x000F000Fu) | 0x64006400u; t1 = (x1 & 0x000F000Fu) | 0x64006400u;
+                            t2 = (x2 & 0x000F000Fu) | 0x64006400u; t3 = (x3 & 0x000F000Fu) | 0x64006400u;
+                            h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1032), S);
+                            h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1032), S);
+                            h2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1032), S);
+                            h3 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1032), S);
+                        } else {
+                            t0 = (x0 & 0x00070007u) * 512u + (x0 & 0x00080008u) * 4096u;
+                            t1 = (x1 & 0x00070007u) * 512u + (x1 & 0x00080008u) * 4096u;
+                            t2 = (x2 & 0x00070007u) * 512u + (x2 & 0x00080008u) * 4096u;
+                            t3 = (x3 & 0x00070007u) * 512u + (x3 & 0x00080008u) * 4096u;
+                            h0 = __hmul2(*reinterpret_cast<__half2*>(&t0), S); h1 = __hmul2(*reinterpret_cast<__half2*>(&t1), S);
+                            h2 = __hmul2(*reinterpret_cast<__half2*>(&t2), S); h3 = __hmul2(*reinterpret_cast<__half2*>(&t3), S);
+                        }
                         v[2 * j] = *reinterpret_cast<uint32_t*>(&h0); v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                         v[8 + 2 * j] = *reinterpret_cast<uint32_t*>(&h2); v[8 + 2 * j + 1] = *reinterpret_cast<uint32_t*>(&h3);
                     }
@@ -1446,7 +1471,8 @@ int ensure_sk_workspace(b200q_ctx* ctx, int ctas) {
 
 // MXFP4 takes the tensor-memory kernel when its 256-k steps are whole and the unit count fits an int.
 bool mx4_tmem_path(const b200q_weight* w, int m) {
-    if (w->fmt != fmt_of(MXFP4, GGUF) || (w->k % 256) != 0) return false;
+    // GGUF Q4_0 shares the path: the same 16 code bytes per block, an f16 d per block where MXFP4 has an exponent byte
+    if ((w->fmt != fmt_of(MXFP4, GGUF) && w->fmt != fmt_of(Q4_0, GGUF)) || (w->k % 256) != 0) return false;
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
     return tiles * (w->k / 256) < (1ll << 30);
@@ -1588,8 +1614,9 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
         if (rc != B200Q_OK) return rc;
         if ((rc = make_wsmap()) != B200Q_OK) return rc;
-        static bool configured_mx[64] = {};
-        rc = configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
+        const bool q40 = w->fmt == fmt_of(Q4_0, GGUF);
+        static bool configured_mx[64] = {}, configured_q40[64] = {};
+        rc = q40 ? configure_once(ctx, gemm_tmem_sk_kernel<3>, configured_q40) : configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
         if (rc != B200Q_OK) return rc;
         SkArgs k{};
         k.a = a;
@@ -1598,7 +1625,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+        if (q40) B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<3>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+        else B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {

@@ -135,10 +135,10 @@ def test_config4_llama7b_q4k_prefill(oracle, n, k, m):
     w.free()
 
 
-@pytest.mark.parametrize("qt,m", [(synth.MXFP4, 64), (synth.MXFP4, 512), (synth.Q6_K, 300)],
-                         ids=["mxfp4-m64", "mxfp4-m512", "q6k-m300"])
+@pytest.mark.parametrize("qt,m", [(synth.MXFP4, 64), (synth.MXFP4, 512), (synth.Q6_K, 300), (synth.Q4_0, 512)],
+                         ids=["mxfp4-m64", "mxfp4-m512", "q6k-m300", "q4_0-m512"])
 def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
-    """[28672 x 8192] (config 5; Q6_K on the same shape): MXFP4 and Q6_K take the persistent kernel whose weight
+    """[28672 x 8192] (config 5; Q6_K and Q4_0 on the same shape): MXFP4, Q6_K and Q4_0 take the persistent kernel whose weight
     operand lives in tensor memory; with 448+ tiles on 148 SMs most tiles are split between CTAs. 64 sampled
     weight rows plus the first and last against the oracle."""
     be = backend()
