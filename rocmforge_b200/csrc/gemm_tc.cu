@@ -12,7 +12,7 @@
 //                                              K-major tile with 128-byte swizzle in SHARED memory
 //                     gemm_q4k_tmem_kernel     GGUF Q4_K: raw super-blocks by TMA, converted into TENSOR memory
 //                                              (tcgen05.st), TS-form MMA; one CTA per tile
-//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K / Q4_0: the same in tensor memory, persistent
+//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K / Q4_0 / Q8_0: the same in tensor memory, persistent
 //                                              CTAs with a stream-K split over all tiles
 //                     (f16, not bf16: an 11-bit mantissa keeps the result inside the 2e-3 tolerance, bf16
 //                     weights do not)
@@ -750,9 +750,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const __grid_constant__ PeerMaps peers, SkArgs k) {
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
-    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : (QF == 1 || QF == 3) ? 128 : 208;   // QF 3 = GGUF Q4_0: MXFP4's code rows
+    // QF 3 = GGUF Q4_0: MXFP4's code rows; QF 4 = GGUF Q8_0: 256 code bytes per row and step, two 128-byte boxes
+    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : (QF == 1 || QF == 3) ? 128 : QF == 4 ? 256 : 208;
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
-    constexpr int RS = QF == 2 ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
+    constexpr int RS = (QF == 2 || QF == 4) ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
@@ -908,6 +909,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         tma_load_2d(st, &tmap_w, sb * 128, row0, bar);
                         tma_load_2d(st + BM * 128, &tmap_w2, sb * 64, row0, bar);
                         tma_load_2d(st + BM * 192, &tmap_w3, sb * 16, row0, bar);
+                    } else if constexpr (QF == 4) {
+                        const uint32_t st = smem_u32(sRaw + rs * RAW_STAGE_BYTES), bar = smem_u32(&raw_full[rs]);
+                        tma_load_2d(st, &tmap_w, sb * 256, row0, bar);                 // blocks 0..3 of the step
+                        tma_load_2d(st + BM * 128, &tmap_w, sb * 256 + 128, row0, bar);   // blocks 4..7
                     } else {
                         tma_load_2d(smem_u32(sRaw + rs * RAW_STAGE_BYTES), &tmap_w, sb * RAW_ROW_BYTES, row0, smem_u32(&raw_full[rs]));
                     }
@@ -1089,6 +1094,51 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                         }
                         // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
+                        if ((c & 1) == 0) {
+                            if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                        if (c & 1) {
+                            tmem_st_wait();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                        }
+                    }
+                } else if constexpr (QF == 4) {
+                    // GGUF Q8_0: block = f16 d + 32 int8 codes. The step's 256 code bytes of a row arrive as two
+                    // swizzled 128-byte rows (blocks 0..3 and 4..7); this thread takes block 2c + nib of k-block c:
+                    // byte ^ 0x80 = q + 128, widened with one PRMT per pair to 1024 + 128 + q, minus 1152 = q exactly,
+                    // one rounding in the multiply by d. Natural weight order (activations are not permuted).
+                    const uint8_t* stage = sRaw + rs * RAW_STAGE_BYTES;
+                    const int64_t grow = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
+                    const uint4 dv = __ldg(reinterpret_cast<const uint4*>(a.v.p[0] + (grow * (a.k >> 5) + sb * 8) * 2));
+                    const __half2 k1152 = __float2half2_rn(1152.0f);
+#pragma unroll
+                    for (int c = 0; c < 4; c++, it++) {
+                        const int s = it & (STAGES - 1);
+                        const uint32_t ph = (uint32_t)(it >> 2) & 1;
+                        const int blk = 2 * c + nib;
+                        const uint32_t dw = blk < 2 ? dv.x : blk < 4 ? dv.y : blk < 6 ? dv.z : dv.w;
+                        const __half2 S = __half2half2(__ushort_as_half((unsigned short)((blk & 1) ? (dw >> 16) : (dw & 0xFFFFu))));
+                        const uint8_t* rowp = stage + (blk >> 2) * (BM * 128) + r * 128;
+                        const int ch = (blk & 3) * 2;
+                        const uint4 qa = *reinterpret_cast<const uint4*>(rowp + ((ch ^ (r & 7)) << 4));
+                        const uint4 qb = *reinterpret_cast<const uint4*>(rowp + (((ch + 1) ^ (r & 7)) << 4));
+                        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                        uint32_t v[16];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const uint32_t u4 = w[j] ^ 0x80808080u;
+                            uint32_t t0 = __byte_perm(u4, 0x64646464u, 0x5140), t1 = __byte_perm(u4, 0x64646464u, 0x7362);
+                            __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1152), S);
+                            __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1152), S);
+                            v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                            v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                        }
                         if ((c & 1) == 0) {
                             if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
                             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -1469,10 +1519,10 @@ int ensure_sk_workspace(b200q_ctx* ctx, int ctas) {
     return B200Q_OK;
 }
 
-// MXFP4 takes the tensor-memory kernel when its 256-k steps are whole and the unit count fits an int.
+// MXFP4, Q4_0 and Q8_0 (GGUF) take the tensor-memory kernel when their 256-k steps are whole and the unit count fits an int.
 bool mx4_tmem_path(const b200q_weight* w, int m) {
     // GGUF Q4_0 shares the path: the same 16 code bytes per block, an f16 d per block where MXFP4 has an exponent byte
-    if ((w->fmt != fmt_of(MXFP4, GGUF) && w->fmt != fmt_of(Q4_0, GGUF)) || (w->k % 256) != 0) return false;
+    if ((w->fmt != fmt_of(MXFP4, GGUF) && w->fmt != fmt_of(Q4_0, GGUF) && w->fmt != fmt_of(Q8_0, GGUF)) || (w->k % 256) != 0) return false;
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
     return tiles * (w->k / 256) < (1ll << 30);
@@ -1596,11 +1646,12 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         a.a_col0 = (bn + 31) & ~31;
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
-        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * BM * 128 +
+        const bool q80 = w->fmt == fmt_of(Q8_0, GGUF);   // 32 code bytes per block, raw ring of two 32 KB stages
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (q80 ? (size_t)2 * BM * 256 : (size_t)RAW_STAGES * BM * 128) +
                             (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + STAGE_EPI_BYTES;
         a.staged_epilogue = y_tma_ok ? 1 : 0;
         CUtensorMap wmap;
-        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 32) * 16;
+        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 32) * (q80 ? 32 : 16);
         cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
         cuuint64_t wstr[1] = {row_bytes};
         cuuint32_t wbox[2] = {128u, (cuuint32_t)BM};
@@ -1616,7 +1667,9 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         if ((rc = make_wsmap()) != B200Q_OK) return rc;
         const bool q40 = w->fmt == fmt_of(Q4_0, GGUF);
         static bool configured_mx[64] = {}, configured_q40[64] = {};
-        rc = q40 ? configure_once(ctx, gemm_tmem_sk_kernel<3>, configured_q40) : configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
+        static bool configured_q80[64] = {};
+        rc = q80 ? configure_once(ctx, gemm_tmem_sk_kernel<4>, configured_q80)
+                 : q40 ? configure_once(ctx, gemm_tmem_sk_kernel<3>, configured_q40) : configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
         if (rc != B200Q_OK) return rc;
         SkArgs k{};
         k.a = a;
@@ -1625,7 +1678,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        if (q40) B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<3>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+        if (q80) B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<4>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+        else if (q40) B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<3>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         else B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
@@ -1708,7 +1762,7 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
     // the nibble-mask producers emit weights in the order 0,2,1,3 inside every group of four
-    const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || mx4_tmem_path(w, m)) ? 1 : 0;
+    const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || (mx4_tmem_path(w, m) && w->fmt != fmt_of(Q8_0, GGUF))) ? 1 : 0;
     if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
