@@ -40,6 +40,7 @@ constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 constexpr int F_Q40 = fmt_of(Q4_0, GGUF);
+constexpr int F_Q80 = fmt_of(Q8_0, GGUF);
 constexpr int RED_FLOATS = 8 * 16 * 8;   // 8 warps x 16 rows x up to 8 activation rows
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -159,6 +160,7 @@ constexpr int Q4K_DATA_BYTES = 2 * 32 * 16, Q4K_SLOT_BYTES = Q4K_DATA_BYTES + RI
 constexpr int RING_UNIT_BYTES = 2 * Q4K_SLOT_BYTES;                                                // 2560 >= 2304
 constexpr int MX4_DATA_BYTES = 2 * 32 * 16, MX4_SLOT_BYTES = MX4_DATA_BYTES + 2 * 8 * 4;           // 1088
 constexpr int Q40_SLOT_BYTES = MX4_DATA_BYTES + 2 * 8 * 8;                                          // 1152: four f16 scales per row
+constexpr int Q80_DATA_BYTES = 2 * 2 * 32 * 16, Q80_SLOT_BYTES = Q80_DATA_BYTES + 2 * 8 * 8;        // 2176: 32 code bytes per block
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -551,34 +553,44 @@ struct MX4Cursor {
     int64_t dq, de;         // byte distances to row g+8 (0 when that row is past the end)
 };
 
-// Q40 = GGUF Q4_0 on the same path: the same 16 code bytes per block (byte i = elements i and i+16), and an
-// f16 scale d per block (2 bytes) where MXFP4 has its exponent byte.
-template <bool Q40>
+// KIND 1 = GGUF Q4_0 on the same path: the same 16 code bytes per block (byte i = elements i and i+16), and an
+// f16 scale d per block (2 bytes) where MXFP4 (KIND 0) has its exponent byte. KIND 2 = GGUF Q8_0: f16 d and 32
+// int8 codes per block, two 16-byte pieces per thread and row (elements 0..15 = run 2t, 16..31 = run 2t+1).
+template <int KIND>
 __device__ __forceinline__ void mx4_seek(MX4Cursor& c, const GOp& op, const Seg& sg, int tile, int g, int t) {
-    constexpr int SB = Q40 ? 8 : 4;   // scale bytes of one row's half (four blocks)
+    constexpr int SB = KIND ? 8 : 4;          // scale bytes of one row's half (four blocks)
+    constexpr int CB = KIND == 2 ? 32 : 16;   // code bytes of one block
     const int rb = seg_row_base(sg, tile) + g;
     const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
     const int64_t hs = r0 * sg.nh + sg.hb;
-    c.q = op.v.p[1] + hs * 64 + t * 16;
+    c.q = op.v.p[1] + hs * (4 * CB) + t * CB;
     c.e = op.v.p[0] + hs * SB;
     const bool two = rb + 8 <= sg.n_rows - 1;
-    c.dq = two ? (int64_t)sg.nh * 8 * 64 : 0;
+    c.dq = two ? (int64_t)sg.nh * 8 * (4 * CB) : 0;
     c.de = two ? (int64_t)sg.nh * 8 * SB : 0;
 }
-template <bool Q40>
+template <int KIND>
 __device__ __forceinline__ void mx4_issue(MX4Cursor& c, uint32_t slot, int lane) {
-    cp_async16(slot + lane * 16, c.q);
-    cp_async16(slot + 512 + lane * 16, c.q + c.dq);
+    constexpr int DATA = KIND == 2 ? Q80_DATA_BYTES : MX4_DATA_BYTES;
+    if constexpr (KIND == 2) {   // [row g | g+8][piece 0 | 1][lane]
+        cp_async16(slot + lane * 16, c.q);
+        cp_async16(slot + 512 + lane * 16, c.q + 16);
+        cp_async16(slot + 1024 + lane * 16, c.q + c.dq);
+        cp_async16(slot + 1536 + lane * 16, c.q + c.dq + 16);
+    } else {
+        cp_async16(slot + lane * 16, c.q);
+        cp_async16(slot + 512 + lane * 16, c.q + c.dq);
+    }
     if ((lane & 3) == 0) {
-        if constexpr (Q40) {
-            cp_async8(slot + MX4_DATA_BYTES + (lane >> 2) * 8, c.e);
-            cp_async8(slot + MX4_DATA_BYTES + 64 + (lane >> 2) * 8, c.e + c.de);
+        if constexpr (KIND != 0) {
+            cp_async8(slot + DATA + (lane >> 2) * 8, c.e);
+            cp_async8(slot + DATA + 64 + (lane >> 2) * 8, c.e + c.de);
         } else {
-            cp_async4(slot + MX4_DATA_BYTES + (lane >> 2) * 4, c.e);
-            cp_async4(slot + MX4_DATA_BYTES + 32 + (lane >> 2) * 4, c.e + c.de);
+            cp_async4(slot + DATA + (lane >> 2) * 4, c.e);
+            cp_async4(slot + DATA + 32 + (lane >> 2) * 4, c.e + c.de);
         }
     }
-    c.q += 64; c.e += Q40 ? 8 : 4;
+    c.q += KIND == 2 ? 128 : 64; c.e += KIND ? 8 : 4;
 }
 
 // two E2M1 codes (bits 0..3 and 16..19 of v) -> f16x2 holding value * 2^-14
@@ -586,12 +598,15 @@ __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t v) {
     return (v & 0x00070007u) * 512u + (v & 0x00080008u) * 4096u;
 }
 
-template <int MT, bool Q40, class Late>
+template <int MT, int KIND, class Late>
 __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
                                         int ring_d, int m, int kw, float* red, Late&& late) {
-    constexpr int SLOT_BYTES = Q40 ? Q40_SLOT_BYTES : MX4_SLOT_BYTES;
+    constexpr bool Q40 = KIND == 1, Q80 = KIND == 2;
+    constexpr int SLOT_BYTES = Q80 ? Q80_SLOT_BYTES : Q40 ? Q40_SLOT_BYTES : MX4_SLOT_BYTES;
+    constexpr int DATA_BYTES = Q80 ? Q80_DATA_BYTES : MX4_DATA_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int depth = min(8, ring_d * RING_UNIT_BYTES / SLOT_BYTES) >= 8 ? 8 : 4;
+    // slots the warp's ring holds: 8 or 4 of the small slots, ring_d (4 or 2) of the 2176-byte Q8_0 slots
+    const int depth = Q80 ? ring_d : (min(8, ring_d * RING_UNIT_BYTES / SLOT_BYTES) >= 8 ? 8 : 4);
     const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * SLOT_BYTES;
     const int keep = depth - 1;
     const bool has_items = sg.hb < sg.he;
@@ -604,13 +619,13 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
     MX4Cursor cur{};
     int pt = sg.seg_b, ph = sg.hb;
     uint32_t pslot = ring;
-    if (has_items && pt < sg.seg_e) mx4_seek<Q40>(cur, op, sg, pt, g, t);
+    if (has_items && pt < sg.seg_e) mx4_seek<KIND>(cur, op, sg, pt, g, t);
     auto issue_next = [&]() {
         if (has_items && pt < sg.seg_e) {
-            mx4_issue<Q40>(cur, pslot, lane);
+            mx4_issue<KIND>(cur, pslot, lane);
             if (++ph == sg.he) {
                 ph = sg.hb;
-                if (++pt < sg.seg_e) mx4_seek<Q40>(cur, op, sg, pt, g, t);
+                if (++pt < sg.seg_e) mx4_seek<KIND>(cur, op, sg, pt, g, t);
             }
         }
         cp_commit();
@@ -632,13 +647,29 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
             cp_wait_keep(keep);
             __syncwarp();
             const uint4* sd = reinterpret_cast<const uint4*>(cslot);
-            const uint4 wa = sd[lane], wb = sd[32 + lane];
+            const uint4 wa = sd[lane], wb = sd[(Q80 ? 64 : 32) + lane];
             float S[2];
             const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
             const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
             uint32_t aL[2][4][2], aH[2][4][2];   // [row][word][bytes (0,2) | (1,3)]
-            if constexpr (Q40) {
-                const uint16_t* sdh = reinterpret_cast<const uint16_t*>(cslot + MX4_DATA_BYTES);
+            if constexpr (Q80) {
+                const uint16_t* sdh = reinterpret_cast<const uint16_t*>(cslot + DATA_BYTES);
+#pragma unroll
+                for (int i = 0; i < 2; i++) S[i] = __half2float(__ushort_as_half(sdh[(i * 8 + g) * 4 + t]));   // d of block t
+                const uint4 wc = sd[32 + lane], wd = sd[96 + lane];   // second pieces: elements 16..31 of the block
+                const uint32_t h0[4] = {wc.x, wc.y, wc.z, wc.w};
+                const uint32_t h1[4] = {wd.x, wd.y, wd.z, wd.w};
+                // int8 code ^ 0x80 = q + 128 in 0..255: in the low byte of an f16 lane that is (q + 128) * 2^-24
+                const uint32_t MB = 0x00FF00FFu, SX = 0x80808080u;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    aL[0][j][0] = (w0[j] ^ SX) & MB;   aL[0][j][1] = ((w0[j] ^ SX) >> 8) & MB;
+                    aH[0][j][0] = (h0[j] ^ SX) & MB;   aH[0][j][1] = ((h0[j] ^ SX) >> 8) & MB;
+                    aL[1][j][0] = (w1[j] ^ SX) & MB;   aL[1][j][1] = ((w1[j] ^ SX) >> 8) & MB;
+                    aH[1][j][0] = (h1[j] ^ SX) & MB;   aH[1][j][1] = ((h1[j] ^ SX) >> 8) & MB;
+                }
+            } else if constexpr (Q40) {
+                const uint16_t* sdh = reinterpret_cast<const uint16_t*>(cslot + DATA_BYTES);
 #pragma unroll
                 for (int i = 0; i < 2; i++) S[i] = __half2float(__ushort_as_half(sdh[(i * 8 + g) * 4 + t]));   // d of block t
                 const uint32_t ML = 0x000F000Fu;   // an integer code in the low bits of an f16 lane is code * 2^-24
@@ -650,7 +681,7 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
                     aH[1][j][0] = (w1[j] >> 4) & ML;   aH[1][j][1] = (w1[j] >> 12) & ML;
                 }
             } else {
-                const uint32_t* se = reinterpret_cast<const uint32_t*>(cslot + MX4_DATA_BYTES);
+                const uint32_t* se = reinterpret_cast<const uint32_t*>(cslot + DATA_BYTES);
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const uint32_t eb = (se[i * 8 + g] >> (8 * t)) & 0xFFu;
@@ -680,8 +711,8 @@ __device__ __forceinline__ void run_mx4(const GOp& op, const Seg& sg, const XImg
                     mma16816(cH, aH[0][1][0], aH[1][1][0], aH[0][1][1], aH[1][1][1], b01.z, b01.w);
                     mma16816(cH, aH[0][2][0], aH[1][2][0], aH[0][2][1], aH[1][2][1], b23.x, b23.y);
                     mma16816(cH, aH[0][3][0], aH[1][3][0], aH[0][3][1], aH[1][3][1], b23.z, b23.w);
-                    // Q4_0: d * (sum q x - 8 sum x) over the block
-                    const float off = Q40 ? sp[n] + sp[m + n] : 0.0f;
+                    // Q4_0: d * (sum q x - 8 sum x) over the block; Q8_0: d * (sum (q + 128) x - 128 sum x)
+                    const float off = KIND ? sp[n] + sp[m + n] : 0.0f;
 #pragma unroll
                     for (int i = 0; i < 2; i++)
                         acc[i][n] = fmaf(S[i], (cL[2 * i] + cL[2 * i + 1]) + (cH[2 * i] + cH[2 * i + 1]) - off, acc[i][n]);
@@ -749,7 +780,7 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         auto prep = [&]() {
             if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
             else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
-            else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, (Q40K && op.fmt == F_Q40) ? 8.0f : 1.0f);
+            else prep_x<2>(op.x, op.ldx, op.k, m, xs, red, !Q40K ? 1.0f : op.fmt == F_Q40 ? 8.0f : op.fmt == F_Q80 ? 128.0f : 1.0f);
             __syncthreads();
         };
         // The CTA's first product starts streaming its weights BEFORE it waits for the kernels ahead of it in the
@@ -777,8 +808,9 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         sg.n_rows = op.n_rows; sg.nh = nh;
         if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
-        else if (Q40K && op.fmt == F_Q40) run_mx4<MT, Q40K>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
-        else run_mx4<MT, false>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else if (Q40K && op.fmt == F_Q40) run_mx4<MT, Q40K ? 1 : 0>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else if (Q40K && op.fmt == F_Q80) run_mx4<MT, Q40K ? 2 : 0>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else run_mx4<MT, 0>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         seg_b = seg_e;
     }
 }
@@ -800,12 +832,12 @@ size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
            (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
-bool gemv_mma_is_q4_0(int fmt) { return fmt == F_Q40; }
+bool gemv_mma_is_q4_0(int fmt) { return fmt == F_Q40 || fmt == F_Q80; }
 
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
-    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4 && w->fmt != F_Q40) return false;
+    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4 && w->fmt != F_Q40 && w->fmt != F_Q80) return false;
     if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 220 * 1024;
 }
