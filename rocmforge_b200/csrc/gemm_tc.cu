@@ -12,7 +12,7 @@
 //                                              K-major tile with 128-byte swizzle in SHARED memory
 //                     gemm_q4k_tmem_kernel     GGUF Q4_K: raw super-blocks by TMA, converted into TENSOR memory
 //                                              (tcgen05.st), TS-form MMA; one CTA per tile
-//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / MXFP4 / Q6_K / Q4_0 / Q8_0: the same in tensor memory, persistent
+//                     gemm_tmem_sk_kernel<QF>  GGUF Q4_K / Q5_K / Q6_K / MXFP4 / Q4_0 / Q8_0: the same in tensor memory, persistent
 //                                              CTAs with a stream-K split over all tiles
 //                     (f16, not bf16: an 11-bit mantissa keeps the result inside the 2e-3 tolerance, bf16
 //                     weights do not)
@@ -751,9 +751,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // bytes of one weight row per 256-k step in the raw ring; Q6_K keeps its three planes one after the other
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     // QF 3 = GGUF Q4_0: MXFP4's code rows; QF 4 = GGUF Q8_0: 256 code bytes per row and step, two 128-byte boxes
-    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : (QF == 1 || QF == 3) ? 128 : QF == 4 ? 256 : 208;
+    // QF 5 = GGUF Q5_K: Q4_K's block with 32 bytes of fifth bits (qh) between the scales and the nibbles
+    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 5 ? 176 : (QF == 1 || QF == 3) ? 128 : QF == 4 ? 256 : 208;
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
-    constexpr int RS = (QF == 2 || QF == 4) ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
+    constexpr int RS = (QF == 2 || QF == 4 || QF == 5) ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
@@ -1007,9 +1008,19 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (warp == 4) SKA_END(4); }
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
-                if constexpr (QF == 0) {
+                if constexpr (QF == 0 || QF == 5) {
                 const uint8_t* rowp = sRaw + rs * RAW_STAGE_BYTES + r * RAW_ROW_BYTES;
                 const uint4 hdr = *reinterpret_cast<const uint4*>(rowp);
+                // Q5_K: the fifth bit of weight l of sub-block j is bit j of qh[l]; it lands on bit 4 of the code
+                // (bit 8 where the high nibble stays in place and the scale carries 1/16)
+                uint32_t qhw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                if constexpr (QF == 5) {
+                    const uint4 ha = *reinterpret_cast<const uint4*>(rowp + 16), hb = *reinterpret_cast<const uint4*>(rowp + 32);
+                    qhw[0] = ha.x; qhw[1] = ha.y; qhw[2] = ha.z; qhw[3] = ha.w;
+                    qhw[4] = hb.x; qhw[5] = hb.y; qhw[6] = hb.z; qhw[7] = hb.w;
+                }
+                constexpr int QS0 = QF == 5 ? 48 : 16;   // first nibble byte of the block
+                const int hs = nib ? 8 : 4;
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
                 const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, m_lo = hdr.z & 0x3F3F3F3Fu;
@@ -1023,13 +1034,18 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const uint32_t sc = ((c < 2 ? sc_lo : sc_hi) >> sh) & 0xFFu, mn = ((c < 2 ? m_lo : m_hi) >> sh) & 0xFFu;
                     const __half2 ds = __float2half2_rn(d * (float)sc * nibscale);
                     const __half2 nd = __float2half2_rn(-dmin * (float)mn);
-                    const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + c * 32);
-                    const uint4 qb = *reinterpret_cast<const uint4*>(rowp + 32 + c * 32);
+                    const uint4 qa = *reinterpret_cast<const uint4*>(rowp + QS0 + c * 32);
+                    const uint4 qb = *reinterpret_cast<const uint4*>(rowp + QS0 + 16 + c * 32);
                     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                     uint32_t v[16];
+                    const int jb = 2 * c + nib;   // sub-block of this thread's 32 weights
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         uint32_t t0 = (w[j] & mask) | 0x64006400u, t1 = ((w[j] >> 8) & mask) | 0x64006400u;
+                        if constexpr (QF == 5) {
+                            t0 |= ((qhw[j] >> jb) & 0x00010001u) << hs;
+                            t1 |= ((qhw[j] >> (jb + 8)) & 0x00010001u) << hs;
+                        }
                         __half2 h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), ds, nd);
                         __half2 h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), ds, nd);
                         v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
@@ -1528,6 +1544,14 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
     return tiles * (w->k / 256) < (1ll << 30);
 }
 
+// GGUF Q5_K takes the tensor-memory kernel under the same conditions (persistent kernel only).
+bool q5k_tmem_path(const b200q_weight* w, int m) {
+    if (w->fmt != fmt_of(Q5_K, GGUF) || (w->k % 256) != 0) return false;
+    const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+    const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
+    return tiles * (w->k / 256) < (1ll << 30);
+}
+
 // Launch of the persistent prefill kernel with programmatic stream serialisation: its CTAs may start while the
 // kernel ahead of it in the stream (the activation conversion) is still running.
 template <class K>
@@ -1683,21 +1707,24 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         else B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<1>, ctas, smem, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
-    if (w->fmt == fmt_of(Q4_K, GGUF) && (w->k % 256) == 0) {
+    const bool q5k = w->fmt == fmt_of(Q5_K, GGUF);   // persistent kernel only (no one-CTA-per-tile variant)
+    if ((w->fmt == fmt_of(Q4_K, GGUF) || (q5k && may_allocate && (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30))) && (w->k % 256) == 0) {
         // weight operand in tensor memory
         a.a_col0 = (bn + 31) & ~31;
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
-        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)RAW_STAGES * RAW_STAGE_BYTES +
+        const int raw_row = q5k ? 176 : RAW_ROW_BYTES;   // bytes of one super-block
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 +
+                            (q5k ? (size_t)2 * BM * 176 : (size_t)RAW_STAGES * RAW_STAGE_BYTES) +   // Q5_K: raw ring of two stages
                             (2 * STAGES + 2 * RAW_STAGES + 1) * 8 + 16;
         static bool configured[64] = {};
-        int rc = configure_once(ctx, gemm_q4k_tmem_kernel, configured);
+        int rc = q5k ? B200Q_OK : configure_once(ctx, gemm_q4k_tmem_kernel, configured);
         if (rc != B200Q_OK) return rc;
         CUtensorMap wmap;
-        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 256) * RAW_ROW_BYTES;
+        const cuuint64_t row_bytes = (cuuint64_t)(w->k / 256) * raw_row;
         cuuint64_t wdim[2] = {row_bytes, (cuuint64_t)w->n_local};
         cuuint64_t wstr[1] = {row_bytes};
-        cuuint32_t wbox[2] = {(cuuint32_t)RAW_ROW_BYTES, (cuuint32_t)BM};
+        cuuint32_t wbox[2] = {(cuuint32_t)raw_row, (cuuint32_t)BM};
         r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w->view.p[0]), wdim, wstr, wbox, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1710,8 +1737,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
             if (rc != B200Q_OK) return rc;
             if ((rc = make_wsmap()) != B200Q_OK) return rc;
-            static bool configured_sk[64] = {};
-            rc = configure_once(ctx, gemm_tmem_sk_kernel<0>, configured_sk);
+            static bool configured_sk[64] = {}, configured_q5k[64] = {};
+            rc = q5k ? configure_once(ctx, gemm_tmem_sk_kernel<5>, configured_q5k) : configure_once(ctx, gemm_tmem_sk_kernel<0>, configured_sk);
             if (rc != B200Q_OK) return rc;
             SkArgs k{};
             k.a = a;
@@ -1721,7 +1748,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
             if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
             k.epoch = ctx->sk_epoch;
-            B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+            if (q5k) B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<5>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+            else B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
         gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
@@ -1762,7 +1790,7 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     __half* d_x16 = static_cast<__half*>(ctx->scratch3);
     float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
     // the nibble-mask producers emit weights in the order 0,2,1,3 inside every group of four
-    const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || (mx4_tmem_path(w, m) && w->fmt != fmt_of(Q8_0, GGUF))) ? 1 : 0;
+    const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || q5k_tmem_path(w, m) || (mx4_tmem_path(w, m) && w->fmt != fmt_of(Q8_0, GGUF))) ? 1 : 0;
     if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
     if (rc != B200Q_OK) return rc;
