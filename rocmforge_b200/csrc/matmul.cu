@@ -63,7 +63,7 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
     int chunk = 8;
     while (chunk > 1 && !gemv_mma_supported(w, chunk)) chunk >>= 1;
     const bool mma = gemv_mma_supported(w, chunk);
-    if (!mma && scatter) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m <= 8 needs a format of the tensor-core decode kernel (Q4_K, Q6_K, MXFP4 in GGUF layout)");
+    if (!mma && scatter) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m <= 8 needs a format of the tensor-core decode kernel (Q4_K, Q6_K, MXFP4, Q4_0, Q8_0 in GGUF layout)");
     if (!mma) chunk = 8;
     for (int i = 0; i < m; i += chunk) {
         int mm = m - i < chunk ? m - i : chunk;
