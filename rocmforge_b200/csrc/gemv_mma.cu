@@ -41,6 +41,7 @@ constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 constexpr int F_Q40 = fmt_of(Q4_0, GGUF);
 constexpr int F_Q80 = fmt_of(Q8_0, GGUF);
+constexpr int F_Q5K = fmt_of(Q5_K, GGUF);
 constexpr int RED_FLOATS = 8 * 16 * 8;   // 8 warps x 16 rows x up to 8 activation rows
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -199,25 +200,35 @@ struct Q4KCursor {
     int sec;            // 1 when the half is the second half of its super-block
 };
 
+// Q5 = GGUF Q5_K: the same block with 32 bytes of fifth bits (qh) between the 16 header bytes and the nibbles.
+template <bool Q5>
 __device__ __forceinline__ void q4k_seek(Q4KCursor& c, const uint8_t* base, const Seg& sg, int tile, int g, int qo) {
+    constexpr int BB = Q5 ? 176 : 144, NO = Q5 ? 48 : 16;   // block bytes, offset of the nibbles
     const int rb = seg_row_base(sg, tile) + g;
     const int64_t r0 = min((int64_t)rb, (int64_t)sg.n_rows - 1);
     const int64_t hs = r0 * sg.nh + sg.hb;
     c.sec = (int)(hs & 1);
-    c.p = base + (hs >> 1) * 144 + 16 + c.sec * 64 + qo;
-    c.d1 = (rb + 8 <= sg.n_rows - 1) ? (int64_t)sg.nh * (4 * 144) : 0;
+    c.p = base + (hs >> 1) * BB + NO + c.sec * 64 + qo;
+    c.d1 = (rb + 8 <= sg.n_rows - 1) ? (int64_t)sg.nh * (4 * BB) : 0;
 }
 // Copies the cursor's half of both rows (and, by the quad's first lane, the two super-block headers) into
 // the ring slot and steps to the next half.
+template <bool Q5>
 __device__ __forceinline__ void q4k_issue(Q4KCursor& c, uint32_t slot, int lane) {
+    constexpr int BB = Q5 ? 176 : 144, NO = Q5 ? 48 : 16, DATA = Q5 ? 2 * Q4K_DATA_BYTES : Q4K_DATA_BYTES;
     cp_async16(slot + lane * 16, c.p);
     cp_async16(slot + 512 + lane * 16, c.p + c.d1);
-    if ((lane & 3) == 0) {
-        const uint8_t* h = c.p - 16 - c.sec * 64;
-        cp_async16(slot + Q4K_DATA_BYTES + (lane >> 2) * 16, h);
-        cp_async16(slot + Q4K_DATA_BYTES + 128 + (lane >> 2) * 16, h + c.d1);
+    const int t = lane & 3;
+    const uint8_t* blk = c.p - NO - c.sec * 64 - ((t >> 1) * 32 + (t & 1) * 16);   // start of the super-block
+    if constexpr (Q5) {   // the 16 fifth-bit bytes that go with this thread's 16 nibble bytes
+        cp_async16(slot + 1024 + lane * 16, blk + 16 + (t & 1) * 16);
+        cp_async16(slot + 1536 + lane * 16, blk + 16 + (t & 1) * 16 + c.d1);
     }
-    c.p += 64 + c.sec * 16;
+    if (t == 0) {
+        cp_async16(slot + DATA + (lane >> 2) * 16, blk);
+        cp_async16(slot + DATA + 128 + (lane >> 2) * 16, blk + c.d1);
+    }
+    c.p += 64 + c.sec * (BB - 128);
     c.sec ^= 1;
 }
 
@@ -319,12 +330,14 @@ __device__ __forceinline__ void finish_tile(float (&acc)[2][MT], const GOp& op, 
 // out of the 12 packed bytes (different bit positions in the first and second half of a super-block), the 64
 // codes become 16 A registers (one AND per pair of weights), 8 MMAs per activation row, and the block
 // scales are folded into the accumulator: acc += d * (scA * vA + scB * vB) - dmin * (mA * sumA + mB * sumB).
-template <int MT, class Late>
+template <int MT, bool Q5, class Late>
 __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg& xs, const uint8_t* xzero, uint8_t* ring_gen,
                                         int ring_d, int m, int kw, float* red, Late&& late) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, tp = t >> 1;
-    const int depth = 2 * ring_d;
-    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * Q4K_SLOT_BYTES;
+    constexpr int SLOT_BYTES = Q5 ? Q6K_SLOT_BYTES : Q4K_SLOT_BYTES;   // Q5_K: two more 512-byte pieces (the fifth bits)
+    constexpr int DATA_BYTES = Q5 ? 2 * Q4K_DATA_BYTES : Q4K_DATA_BYTES;
+    const int depth = Q5 ? ring_d : 2 * ring_d;
+    const uint32_t ring = smem_addr(ring_gen), ring_end = ring + depth * SLOT_BYTES;
     const int keep = depth - 1;
     const int qo = tp * 32 + (t & 1) * 16;
     const int sh16 = tp * 16;
@@ -342,23 +355,23 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
     Q4KCursor cur{};
     int pt = sg.seg_b, ph = sg.hb;
     uint32_t pslot = ring;
-    if (has_items && pt < sg.seg_e) q4k_seek(cur, op.v.p[0], sg, pt, g, qo);
+    if (has_items && pt < sg.seg_e) q4k_seek<Q5>(cur, op.v.p[0], sg, pt, g, qo);
     auto issue_next = [&]() {
         if (has_items && pt < sg.seg_e) {
-            q4k_issue(cur, pslot, lane);
+            q4k_issue<Q5>(cur, pslot, lane);
             if (++ph == sg.he) {
                 ph = sg.hb;
-                if (++pt < sg.seg_e) q4k_seek(cur, op.v.p[0], sg, pt, g, qo);
+                if (++pt < sg.seg_e) q4k_seek<Q5>(cur, op.v.p[0], sg, pt, g, qo);
             }
         }
         cp_commit();
-        pslot += Q4K_SLOT_BYTES;
+        pslot += SLOT_BYTES;
         if (pslot == ring_end) pslot = ring;
     };
     for (int d = 0; d < depth; d++) issue_next();
     late();   // the first product of a CTA builds its activation image only now: the weights are already on their way
     const uint8_t* cslot = ring_gen;
-    const uint8_t* cend = ring_gen + depth * Q4K_SLOT_BYTES;
+    const uint8_t* cend = ring_gen + depth * SLOT_BYTES;
 
     for (int tile = sg.seg_b; tile < sg.seg_e; tile++) {
         float acc[2][MT];
@@ -372,7 +385,7 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             cp_wait_keep(keep);
             __syncwarp();   // the quad leader's header copies are visible to its quad
             const uint4* sd = reinterpret_cast<const uint4*>(cslot);
-            const uint4* sh = reinterpret_cast<const uint4*>(cslot + Q4K_DATA_BYTES);
+            const uint4* sh = reinterpret_cast<const uint4*>(cslot + DATA_BYTES);
             const uint4 wa = sd[lane], wb = sd[32 + lane];
             const uint4 hd[2] = {sh[g], sh[8 + g]};
             const uint32_t MA = csec ? 0x0F0Fu : 0x3F3Fu, MB = csec ? 0x3030u : 0u;
@@ -393,21 +406,51 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             uint32_t s0[4], s1[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) { s0[j] = w0[j] >> 8; s1[j] = w1[j] >> 8; }
+            // Q5_K: bit (4 sec + 2 tp) of a qh byte is the fifth bit of its low-nibble weight, the next bit that of
+            // its high-nibble weight; it joins the code at bit 4 (bit 8 where the nibble stays in bits 4..7). The
+            // operands are completed once per item: [row g bytes 0,2 | row g+8 bytes 0,2 | row g bytes 1,3 | row g+8 bytes 1,3]
+            uint32_t qL[4][4], qH[4][4];
+            if constexpr (Q5) {
+                const uint4 qa = sd[64 + lane], qb = sd[96 + lane];
+                const uint32_t q0[4] = {qa.x, qa.y, qa.z, qa.w};
+                const uint32_t q1[4] = {qb.x, qb.y, qb.z, qb.w};
+                const int jl = 4 * csec + 2 * tp;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t a0 = q0[j] >> jl, a1 = q1[j] >> jl;
+                    qL[0][j] = (w0[j] & ML) | ((a0 & 0x00010001u) << 4);
+                    qL[1][j] = (w1[j] & ML) | ((a1 & 0x00010001u) << 4);
+                    qL[2][j] = (s0[j] & ML) | (((a0 >> 8) & 0x00010001u) << 4);
+                    qL[3][j] = (s1[j] & ML) | (((a1 >> 8) & 0x00010001u) << 4);
+                    qH[0][j] = (w0[j] & MH) | (((a0 >> 1) & 0x00010001u) << 8);
+                    qH[1][j] = (w1[j] & MH) | (((a1 >> 1) & 0x00010001u) << 8);
+                    qH[2][j] = (s0[j] & MH) | (((a0 >> 9) & 0x00010001u) << 8);
+                    qH[3][j] = (s1[j] & MH) | (((a1 >> 9) & 0x00010001u) << 8);
+                }
+            }
+            auto AL = [&](int which, int j) -> uint32_t {
+                if constexpr (Q5) return qL[which][j];
+                else return (which == 0 ? w0[j] : which == 1 ? w1[j] : which == 2 ? s0[j] : s1[j]) & ML;
+            };
+            auto AH = [&](int which, int j) -> uint32_t {
+                if constexpr (Q5) return qH[which][j];
+                else return (which == 0 ? w0[j] : which == 1 ? w1[j] : which == 2 ? s0[j] : s1[j]) & MH;
+            };
 #pragma unroll
             for (int n = 0; n < MT; n++) {
                 if (n < m) {
                     float cA[4], cB[4];
                     const uint4* bq = bp + n * bn;
                     uint4 b01 = bq[0], b23 = bq[1];
-                    mma16816_z(cA, w0[0] & ML, w1[0] & ML, s0[0] & ML, s1[0] & ML, b01.x, b01.y);
-                    mma16816(cA, w0[1] & ML, w1[1] & ML, s0[1] & ML, s1[1] & ML, b01.z, b01.w);
-                    mma16816(cA, w0[2] & ML, w1[2] & ML, s0[2] & ML, s1[2] & ML, b23.x, b23.y);
-                    mma16816(cA, w0[3] & ML, w1[3] & ML, s0[3] & ML, s1[3] & ML, b23.z, b23.w);
+                    mma16816_z(cA, AL(0, 0), AL(1, 0), AL(2, 0), AL(3, 0), b01.x, b01.y);
+                    mma16816(cA, AL(0, 1), AL(1, 1), AL(2, 1), AL(3, 1), b01.z, b01.w);
+                    mma16816(cA, AL(0, 2), AL(1, 2), AL(2, 2), AL(3, 2), b23.x, b23.y);
+                    mma16816(cA, AL(0, 3), AL(1, 3), AL(2, 3), AL(3, 3), b23.z, b23.w);
                     b01 = bq[bhigh]; b23 = bq[bhigh + 1];
-                    mma16816_z(cB, w0[0] & MH, w1[0] & MH, s0[0] & MH, s1[0] & MH, b01.x, b01.y);
-                    mma16816(cB, w0[1] & MH, w1[1] & MH, s0[1] & MH, s1[1] & MH, b01.z, b01.w);
-                    mma16816(cB, w0[2] & MH, w1[2] & MH, s0[2] & MH, s1[2] & MH, b23.x, b23.y);
-                    mma16816(cB, w0[3] & MH, w1[3] & MH, s0[3] & MH, s1[3] & MH, b23.z, b23.w);
+                    mma16816_z(cB, AH(0, 0), AH(1, 0), AH(2, 0), AH(3, 0), b01.x, b01.y);
+                    mma16816(cB, AH(0, 1), AH(1, 1), AH(2, 1), AH(3, 1), b01.z, b01.w);
+                    mma16816(cB, AH(0, 2), AH(1, 2), AH(2, 2), AH(3, 2), b23.x, b23.y);
+                    mma16816(cB, AH(0, 3), AH(1, 3), AH(2, 3), AH(3, 3), b23.z, b23.w);
                     const float sa = sp[n], sb = sp[2 * m + n];
 #pragma unroll
                     for (int i = 0; i < 2; i++) {
@@ -423,7 +466,7 @@ __device__ __forceinline__ void run_q4k(const GOp& op, const Seg& sg, const XImg
             sp += 8 * m;
             __syncwarp();   // every lane has read the slot before it is refilled
             issue_next();
-            cslot += Q4K_SLOT_BYTES;
+            cslot += SLOT_BYTES;
             if (cslot == cend) cslot = ring_gen;
         }
         finish_tile<MT>(acc, op, sg, xs, tile, m, kw, red, warp, lane);
@@ -776,7 +819,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         const int seg_e = min(te, op.tile0 + op.ntiles);
         __syncthreads();   // everyone is done with the previous product's activations and the reduction scratch
         XImg xs = ximg_carve(xbase, op.k, m);
-        const bool q4 = op.fmt == F_Q4K;
+        const bool q5 = Q40K && op.fmt == F_Q5K;
+        const bool q4 = op.fmt == F_Q4K || q5;
         auto prep = [&]() {
             if (q4) prep_x<1>(op.x, op.ldx, op.k, m, xs, red, 1.0f);
             else if (op.fmt == F_Q6K) prep_x<0>(op.x, op.ldx, op.k, m, xs, red, 32.0f);
@@ -806,7 +850,8 @@ gemv_mma_kernel(GOp single, const GOp* __restrict__ ops, int n_ops, const int2* 
         sg.wrow = warp >> op.kw_log2;
         sg.tile0 = op.tile0;
         sg.n_rows = op.n_rows; sg.nh = nh;
-        if (q4) run_q4k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        if (q5) run_q4k<MT, Q40K>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
+        else if (q4) run_q4k<MT, false>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         else if (op.fmt == F_Q6K) run_q6k<MT>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         else if (Q40K && op.fmt == F_Q40) run_mx4<MT, Q40K ? 1 : 0>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
         else if (Q40K && op.fmt == F_Q80) run_mx4<MT, Q40K ? 2 : 0>(op, sg, xs, xbase, ring_gen, ring_d, m, kw, red, late);
@@ -832,12 +877,12 @@ size_t gemv_mma_smem_bytes(int fmt, int k, int m) {
            (size_t)(k >> 4) * m * (64 + sizeof(float2)) + 16;
 }
 
-bool gemv_mma_is_q4_0(int fmt) { return fmt == F_Q40 || fmt == F_Q80; }
+bool gemv_mma_is_q4_0(int fmt) { return fmt == F_Q40 || fmt == F_Q80 || fmt == F_Q5K; }
 
 bool gemv_mma_supported(const b200q_weight* w, int m) {
     if (w->orient != B200Q_ORIENT_NK || m < 1 || m > 8) return false;
     if (w->n_local > 0x7FFFFFF0ll || w->k > (1 << 24) || w->n_elements >= (1ll << 37)) return false;
-    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4 && w->fmt != F_Q40 && w->fmt != F_Q80) return false;
+    if (w->fmt != F_Q4K && w->fmt != F_Q6K && w->fmt != F_MX4 && w->fmt != F_Q40 && w->fmt != F_Q80 && w->fmt != F_Q5K) return false;
     if (w->k % 128) return false;
     return gemv_mma_smem_bytes(w->fmt, (int)w->k, m) <= 220 * 1024;
 }

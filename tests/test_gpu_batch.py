@@ -70,13 +70,13 @@ def test_batch_of_other_formats_falls_back_to_per_product_launches(oracle):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8])
-def test_q4_0_and_q8_0_gguf_ride_the_grouped_tensor_core_launch(oracle, m):
-    """GGUF Q4_0 (config 1's format: [4864, 896]) and Q8_0 share the grouped decode launch with the K-quants and MXFP4;
+def test_q4_0_q8_0_and_q5_k_gguf_ride_the_grouped_tensor_core_launch(oracle, m):
+    """GGUF Q4_0 (config 1's format: [4864, 896]), Q8_0 and Q5_K share the grouped decode launch with the K-quants and MXFP4;
     odd row counts exercise the clamped last tile."""
     be = backend()
     rng = synth.rng_for(601 + m)
     ops = [(synth.Q4_0, 4864, 896), (synth.Q8_0, 4864, 896), (synth.Q4_0, 300, 1024), (synth.Q4_K, 128, 256), (synth.Q4_0, 17, 128),
-           (synth.Q8_0, 301, 1152), (synth.Q8_0, 9, 128)]
+           (synth.Q8_0, 301, 1152), (synth.Q8_0, 9, 128), (synth.Q5_K, 4864, 1024), (synth.Q5_K, 33, 256), (synth.Q5_K, 300, 2304)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(m, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, m)
