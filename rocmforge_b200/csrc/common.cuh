@@ -78,6 +78,8 @@ bool gemm_tc_supported(const b200q_weight* w, int m);
 int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m);
 int gemm_tc_check_status(b200q_ctx* ctx);
 int launch_bounded_wait_selftest(b200q_ctx* ctx, long long budget_cycles);
+int launch_gemm_tc_pair(b200q_ctx* ctx, const b200q_weight* w0, const b200q_weight* w1, const float* d_x, int64_t ldx,
+                        float* d_y0, float* d_y1, int m);
 int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m);
 
 }  // namespace b200q

@@ -134,6 +134,12 @@ int b200q_mlp_run(b200q_ctx* ctx, b200q_mlp* p) {
     if (p->gate_up) {
         rc = b200q_batch_run(ctx, p->gate_up, nullptr);
         if (rc != B200Q_OK) return rc;
+    } else if (p->m > 8 && gemm_tc_supported(p->gate, p->m) && gemm_tc_supported(p->up, p->m)) {
+        // prefill: one f16 copy of the activations serves both tensor-core products
+        B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+        rc = launch_gemm_tc_pair(ctx, p->gate, p->up, p->x, p->gate->k, p->d_gate, p->d_up, p->m);
+        if (rc != B200Q_OK) return rc;
+        ctx->tc_pending = true;
     } else {
         rc = b200q_matmul(ctx, p->gate, p->x, B200Q_F32, p->d_gate, B200Q_F32, p->m, 0);
         if (rc != B200Q_OK) return rc;

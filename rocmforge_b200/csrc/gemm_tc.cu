@@ -1797,6 +1797,32 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, ldy, m, "gemm", true);
 }
 
+// Two prefill products of ONE activation tensor (gate and up, or any pair with the same inner dimension and the
+// same activation order): the f16 copy of the activations is made once and both tensor-core kernels read it.
+int launch_gemm_tc_pair(b200q_ctx* ctx, const b200q_weight* w0, const b200q_weight* w1, const float* d_x, int64_t ldx,
+                        float* d_y0, float* d_y1, int m) {
+    auto perm_of = [&](const b200q_weight* w) {
+        return (w->fmt == fmt_of(Q4_K, GGUF) || q5k_tmem_path(w, m) || (mx4_tmem_path(w, m) && w->fmt != fmt_of(Q8_0, GGUF))) ? 1 : 0;
+    };
+    if (!gemm_tc_supported(w0, m) || !gemm_tc_supported(w1, m) || w0->k != w1->k || perm_of(w0) != perm_of(w1)) {
+        int rc = launch_gemm_tc(ctx, w0, d_x, 0, ldx, d_y0, w0->n_local, m);
+        if (rc != B200Q_OK) return rc;
+        return launch_gemm_tc(ctx, w1, d_x, 0, ldx, d_y1, w1->n_local, m);
+    }
+    const size_t x16_bytes = ((size_t)m * w0->k * 2 + 255) & ~(size_t)255;
+    int rc = ensure_scratch(ctx, x16_bytes + (size_t)m * sizeof(float) + 2048, 2);
+    if (rc != B200Q_OK) return rc;
+    __half* d_x16 = static_cast<__half*>(ctx->scratch3);
+    float* d_scale = reinterpret_cast<float*>(static_cast<uint8_t*>(ctx->scratch3) + x16_bytes);
+    rc = launch_x_to_f16(ctx, d_x, ldx, d_x16, d_scale, m, (int)w0->k, perm_of(w0));
+    if (rc != B200Q_OK) return rc;
+    rc = launch_gemm_core(ctx, w0, d_x16, d_scale, d_y0, w0->n_local, m, "gemm", true);
+    if (rc != B200Q_OK) return rc;
+    // the second kernel's weight copies and conversion overlap the first kernel's tail; it reads the same f16
+    // activations only after the first kernel has completed (griddepcontrol.wait), and both only read them
+    return launch_gemm_core(ctx, w1, d_x16, d_scale, d_y1, w1->n_local, m, "gemm", true);
+}
+
 // ---------------------------------------------------------------------------------------------------
 // Prefill product for callers that must not allocate device memory.
 //
