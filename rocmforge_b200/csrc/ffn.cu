@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     // the product that follows may start its CTAs and stream its weights while this kernel runs; it waits for
     // this kernel's completion (griddepcontrol.wait) before it reads the activations written here
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // launched with programmatic stream serialisation itself: gate and up come from the kernel ahead of it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i4 >= total) return;
     if (i4 + 4 <= total) {
@@ -73,8 +75,16 @@ int b200q_swiglu(b200q_ctx* ctx, const float* d_gate, const float* d_up, float* 
         return fail(B200Q_ERR_INVALID, "swiglu: buffers must be 16-byte aligned");
     const int64_t grid = (total + 1023) / 1024;
     if (grid > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "swiglu: tensor too large for one launch");
-    swiglu_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(d_gate, d_up, d_out, total);
-    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA(cudaLaunchKernelEx(&cfg, swiglu_kernel, d_gate, d_up, d_out, total), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
 

@@ -1419,6 +1419,10 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     // the prefill kernel behind this one may start: it streams and converts weights, and waits for this
     // kernel's completion (griddepcontrol.wait) before it touches the f16 activations or their scales
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // this kernel itself is launched with programmatic stream serialisation: its CTAs may be resident while the
+    // kernel ahead of it still runs (it may produce x, or still read the f16 copy this kernel overwrites), so
+    // nothing is read or written before that kernel has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.x;
     const T* xr = x + (int64_t)row * ldx;
     float mx = 0.0f;
@@ -1462,9 +1466,17 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
 template <typename T>
 int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float* scale, int m, int k, int perm) {
     const bool vec = (k % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0;
-    if (vec) x_to_f16_kernel<T, 4><<<m, 256, 0, ctx->stream>>>(x, ldx, out, scale, k, perm);
-    else x_to_f16_kernel<T, 1><<<m, 256, 0, ctx->stream>>>(x, ldx, out, scale, k, perm);
-    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)m);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (vec) B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 4>, x, ldx, out, scale, k, perm), B200Q_ERR_LAUNCH);
+    else B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 1>, x, ldx, out, scale, k, perm), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
 
