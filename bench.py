@@ -236,6 +236,25 @@ def mlp_leg(be, peaks, steps):
             "launches_per_run": {"m=1": 3, "m=512": 6}, "shapes": rows}
 
 
+def formats_leg(be, peaks, steps):
+    """Every GGUF format with a tensor-core decode kernel and a tensor-memory prefill kernel on one [8192, 8192]
+    tensor: decode (m = 1) in packed GB/s and prefill (m = 512) in TFLOP/s, device-resident operands."""
+    from rocmforge_b200.backend import QuantizedWeight
+    n = k = 8192
+    rows = []
+    for qname in ("Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "MXFP4"):
+        qt = synth.QNAMES.index(qname)
+        w = QuantizedWeight(be, synth.gen_packed(qt, synth.GGUF, n * k, synth.rng_for(9000 + qt)), qt, synth.GGUF, n, k)
+        ms1 = time_matmul(be, w, 1, steps * 2, 3)
+        ms512 = time_matmul(be, w, 512, steps, 3)
+        rows.append({"qtype": qname, "decode_GB/s": w.packed_bytes / (ms1 * 1e-3) / 1e9,
+                     "decode_frac_of_hbm": w.packed_bytes / (ms1 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "prefill_tflops": 2.0 * 512 * n * k / (ms512 * 1e-3) / 1e12,
+                     "prefill_frac_of_peak": 2.0 * 512 * n * k / (ms512 * 1e-3) / 1e12 / peaks["bf16_tflops"]})
+        w.free()
+    return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)", "rows": rows}
+
+
 def shard_leg(be, rank, world, steps):
     """Column split of the Llama-70B-shaped FFN projection [28672, 8192] over the ranks + NCCL all-gather."""
     import torch
@@ -445,6 +464,7 @@ def main():
             # ---- prefill GEMM (second half of the metric) and a single large Q4_K GEMV --------------------------
             out["gemm"] = gemm_leg(be, peaks, 10)
             out["mlp"] = mlp_leg(be, peaks, 10)
+            out["formats"] = formats_leg(be, peaks, 10)
             rng = synth.rng_for(4242)
             big = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, 65536 * 4096, rng), synth.Q4_K, synth.GGUF, 65536, 4096)
             msb = time_matmul(be, big, 1, 20, 3)
