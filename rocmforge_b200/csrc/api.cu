@@ -2,10 +2,12 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 #include <vector>
 
 #include "common.cuh"
+#include "gemv_i8.cuh"
 
 namespace b200q {
 
@@ -323,6 +325,12 @@ int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int 
     w->packed_bytes = (size_t)n_blocks * I.block_bytes;
     int rc = make_planes(ctx, fmt, src, w->packed_bytes, n_blocks, &w->base, &w->view);
     if (rc != B200Q_OK) { delete w; return rc; }
+    // second, decode-ordered copy for the m <= 8 kernel (B200Q_NO_DECODE_IMAGE=1 keeps only the stream layout)
+    const char* no_img = getenv("B200Q_NO_DECODE_IMAGE");
+    if (!(no_img && no_img[0] == '1') && decode_image_wanted(fmt, orient, n_local, k)) {
+        rc = build_decode_image(ctx, w, &w->dimg);
+        if (rc != B200Q_OK) { cudaFree(w->base); delete w; return rc; }
+    }
     *out = w;
     return B200Q_OK;
 }
@@ -333,6 +341,7 @@ int b200q_weight_free(b200q_weight* w) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     cudaFree(w->base);
+    if (w->dimg.base) cudaFree(w->dimg.base);
     cudaGetLastError();
     delete w;
     return B200Q_OK;

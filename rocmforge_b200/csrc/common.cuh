@@ -33,6 +33,22 @@ struct b200q_ctx {
     float* scatter_y[7] = {};
 };
 
+namespace b200q {
+// Decode image of one NK tensor (built at upload, streamed by the integer tensor-core decode kernel): the
+// packed weights re-arranged into the order that kernel's threads consume them. An ITEM is 16 weight rows x
+// 128 weights (half a super-block per row) stored contiguously; item (row tile T, half h) sits at
+// (T * nh + h) * item_bytes with nh = k / 128, so any run of row tiles is one contiguous byte range. Rows
+// past the tensor's last row are zero items.
+struct DImage {
+    uint8_t* base = nullptr;   // device allocation (nullptr: the tensor has no decode image)
+    int kind = -1;
+    int item_bytes = 0;
+    int nh = 0;                // items per row tile
+    int nrt = 0;               // row tiles
+    size_t bytes = 0;
+};
+}  // namespace b200q
+
 struct b200q_weight {
     b200q_ctx* ctx = nullptr;
     int qtype = 0, layout = 0, orient = 0, fmt = 0;
@@ -42,6 +58,7 @@ struct b200q_weight {
     size_t packed_bytes = 0;  // bytes of the file blocks this handle holds
     void* base = nullptr;     // one allocation holding every plane
     b200q::WView view{};
+    b200q::DImage dimg{};     // second, decode-ordered copy for m <= 8 (formats of the integer decode kernel)
 };
 
 namespace b200q {

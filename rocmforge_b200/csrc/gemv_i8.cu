@@ -1,0 +1,812 @@
+// Integer tensor-core decode kernel: fused dequant + matmul for 1..8 activation rows, HBM-bound.
+//
+// Replaces the per-row-block scalar kernels of the reference (kernels/q4_k_matmul.hip:216, q6_k_matmul.hip:216:
+// one thread block per ACTIVATION row, one 4-bit code per inner iteration) and the serial per-op loop of
+// BatchQuantizedMatmul::process_batch (src/ggml/hip_backend/ops/batch_quantized.rs:147-161).
+//
+// Arithmetic. The integer codes go to the tensor cores AS INTEGERS (mma.sync.m16n8k32, u8 x s8 -> s32): a
+// nibble masked in place is a u8 (the high nibble of a byte is 16 q, a Q6_K code kept as 4 q), so extraction is
+// one logic operation per FOUR weights. Activations are quantised per scale group of the format (32 weights for
+// Q4_K, 16 for Q6_K) to a 15-bit integer round(x * 16256 / max|x|) held as two s8 limbs (value = 128 hi + lo),
+// so the integer dot product of a group is exact and the only error is the activation rounding: about 4e-5 of
+// the result's magnitude for normally distributed activations, inside the 1e-4 bound of this path. The
+// group's factor max|x| / 16256, the block scales (d * sc, exact in fp32) and the offsets (- dmin * m * sum x,
+// - 32 * sum x) are applied in fp32 once per group and weight row.
+//
+// Block-diagonal B operand. Thread (g, t) of a warp streams its OWN group of 32 weights of rows g and g+8.
+// The 8 columns of the MMA are 4 threads x {hi limb, lo limb}: column 2t holds the hi limbs of the
+// activations that meet thread t's k-slots and zeros elsewhere, column 2t+1 the lo limbs. The accumulator
+// fragment thread t receives (columns 2t, 2t+1) is then the dot product of ITS group, so block scales are
+// applied by the thread that owns the group: no redundant work across the quad. More activation rows repeat
+// the MMAs on the same extracted codes.
+//
+// Data movement. Weights are read from the tensor's DECODE IMAGE (built at upload): items of 16 rows x 128
+// weights laid out in the order the lanes consume them, scales already widened to bytes, consecutive items of
+// a row tile and consecutive row tiles contiguous. Every warp owns a contiguous byte range of the image and
+// pulls it through a private ring in shared memory with one bulk copy (cp.async.bulk, completion on an
+// mbarrier) per chunk of items issued by one lane; the other lanes spend no instruction on addressing. A
+// launch covers any number of products (a whole decode step): persistent CTAs own contiguous ranges of row
+// tiles balanced by bytes; inside a CTA the items of a product segment are split evenly over the 8 warps, at
+// any item boundary, and the (at most one per warp) row tile a warp did not start is handed to the warp that
+// did through shared memory, added in warp order.
+#include <cuda_fp16.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "gemv_i8.cuh"
+
+namespace b200q {
+
+namespace {
+
+constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
+constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
+
+// ---- item layouts (bytes inside one item; L = lane = 4 g + t, rows g and g+8 of the row tile) ---------------
+// Q4_K:   [0,512)      16 code bytes of row g per lane: byte b = weight b (low nibble) | weight 16+b (high nibble)
+//                      of sub-block t of the half
+//         [512,1024)   the same for row g+8
+//         [1024,1152)  per lane: scale(g), min(g), scale(g+8), min(g+8) of that sub-block, one byte each
+//         [1152,1216)  per g: f16 d(g), dmin(g), d(g+8), dmin(g+8) of the super-block the half lies in
+// Q6_K:   [0,512) / [512,1024) as above with nibble byte b = low 4 bits of weight b | (weight 16+b >> 2) << 4
+//         [1024,1536)  per lane 16 bytes: two words of 2-bit fields for row g, two for row g+8. Word u, byte z:
+//                      bits 4-5 = weight 8u+z >> 4, bits 2-3 = weight 16+8u+z & 3,
+//                      bits 6-7 = weight 8u+4+z >> 4, bits 0-1 = weight 16+8u+4+z & 3
+//         [1536,1664)  per lane: int8 scale of weights 0..15 and of weights 16..31 for row g, then for row g+8
+//         [1664,1696)  per g: f16 d(g), d(g+8)
+constexpr int Q4K_ITEM = 1216;
+constexpr int Q6K_ITEM = 1696;
+
+constexpr int MAX_DEPTH = 8;
+constexpr int BAR_BYTES = 8 * MAX_DEPTH * 8;          // 8 warps x MAX_DEPTH mbarriers
+constexpr int RED_BYTES = 8 * 16 * 8 * 4;             // 8 warps x 16 rows x up to 8 activation rows
+constexpr int ZERO_BYTES = 32;                        // lanes that supply the zero columns of B read these
+constexpr int FIXED_BYTES = BAR_BYTES + RED_BYTES + ZERO_BYTES;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// first MMA of a group: the accumulator input is the constant zero
+__device__ __forceinline__ void mma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// global -> this CTA's shared memory, completion counted in bytes on the mbarrier (no multicast)
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// explicit shared-space loads (the addresses are 32-bit shared-window offsets)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+
+// Shared-memory image of one product's activations (m rows of k values), per block of 32 values:
+//   limbs[((n * nb + b) * 2 + L) * 32 + i]  s8 limb L (0 = hi, 1 = lo) of value 32 b + i of row n
+//   fs: per scale group of G values {factor max|x| / 16256, sum of the group's x times `sum_mul`}
+//       G = 32: float2 fs[n * nb + b];  G = 16: float4 fs[n * nb + b] = {f, s} of values 0..15, {f, s} of 16..31
+struct ActImg {
+    const uint8_t* limbs;
+    const float* fs;
+    int nb;   // blocks of 32 per row
+};
+
+// x[m, k] (fp32, global) -> image. 8 consecutive values per thread; the G / 8 lanes of a group agree on the
+// group's maximum and sum by shuffles.
+template <int G>
+__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, uint8_t* limbs, float* fs,
+                                       float sum_mul) {
+    const int units = k >> 3;
+    const int nb = k >> 5;
+    const int total = units * m;
+    for (int u0 = 0; u0 < total; u0 += 256) {
+        const int u = u0 + threadIdx.x;
+        const bool valid = u < total;
+        const int n = valid ? u / units : 0;
+        const int p = valid ? u - n * units : 0;
+        float v[8];
+        if (valid) {
+            const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)p * 8);
+            const float4 a = __ldg(xp), b = __ldg(xp + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = 0.0f;
+        }
+        float mx = 0.0f, sm = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) { mx = fmaxf(mx, fabsf(v[i])); sm += v[i]; }
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
+        if (G == 32) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
+        }
+        const float s = mx > 0.0f ? 16256.0f / mx : 0.0f;
+        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int q = __float2int_rn(v[i] * s);   // |q| <= 16256 = 127 * 128
+            const int h = (q + 64) >> 7;              // -127 .. 127
+            const int l = q - (h << 7);               // -64 .. 63
+            hi[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
+            lo[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
+        }
+        if (valid) {
+            const int b = p >> 2, j = p & 3;
+            uint8_t* dst = limbs + ((size_t)(n * nb + b) * 2) * 32 + j * 8;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2*>(dst + 32) = make_uint2(lo[0], lo[1]);
+            const float f = mx * (1.0f / 16256.0f);
+            if (G == 32) {
+                if (j == 0) *reinterpret_cast<float2*>(fs + (size_t)(n * nb + b) * 2) = make_float2(f, sm * sum_mul);
+            } else {
+                if ((j & 1) == 0) *reinterpret_cast<float2*>(fs + (size_t)(n * nb + b) * 4 + (j >> 1) * 2) = make_float2(f, sm * sum_mul);
+            }
+        }
+    }
+}
+
+// Per-lane addressing of the B operand and of the group factors. Lanes g == 2t (hi limbs) and g == 2t+1 (lo limbs)
+// read the limbs of thread t's block; all other lanes read the zero region with stride 0, so no load is predicated.
+struct LaneB {
+    uint32_t b0;         // shared address of the limbs of block (h = 0, this lane's t), or of the zero region
+    int bh, bn;          // byte steps per item (4 blocks) and per activation row
+    uint32_t f0;         // shared address of the factors of block (h = 0, t)
+    int fh, fn;          // byte steps per item and per activation row
+};
+
+template <int G>
+__device__ __forceinline__ LaneB lane_b(const ActImg& a, const uint8_t* zero, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const bool active = (g >> 1) == t;
+    LaneB r;
+    r.b0 = active ? smem_addr(a.limbs) + t * 64 + (g & 1) * 32 : smem_addr(zero);
+    r.bh = active ? 256 : 0;
+    r.bn = active ? a.nb * 64 : 0;
+    constexpr int FPB = G == 32 ? 8 : 16;   // bytes of factors per block
+    r.f0 = smem_addr(a.fs) + t * FPB;
+    r.fh = 4 * FPB;
+    r.fn = a.nb * FPB;
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------- Q4_K (GGUF)
+// acc += d * sc * (factor * sum q x_int) - dmin * m * (sum x) for the lane's sub-block of rows g and g+8.
+template <int MT>
+__device__ __forceinline__ void item_q4k(uint32_t it, const LaneB& lb, int h, int m, float (&acc)[2][MT], int lane) {
+    const int g = lane >> 2;
+    const uint4 wa = lds128(it + lane * 16);
+    const uint4 wb = lds128(it + 512 + lane * 16);
+    const uint32_t hs = lds32(it + 1024 + lane * 4);
+    const uint2 dd = lds64(it + 1152 + g * 8);
+    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
+    const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
+    const float A0 = d0.x * (float)(hs & 0xFFu), B0 = -d0.y * (float)((hs >> 8) & 0xFFu);
+    const float A1 = d1.x * (float)((hs >> 16) & 0xFFu), B1 = -d1.y * (float)(hs >> 24);
+    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
+    const uint32_t bp = lb.b0 + h * lb.bh;
+    const uint32_t fp = lb.f0 + h * lb.fh;
+#pragma unroll
+    for (int n = 0; n < MT; n++) {
+        if (n < m) {
+            const uint4 q0 = lds128(bp + n * lb.bn);
+            const uint4 q1 = lds128(bp + n * lb.bn + 16);
+            const uint2 fSb = lds64(fp + n * lb.fn);
+            const float2 fS = make_float2(__uint_as_float(fSb.x), __uint_as_float(fSb.y));
+            int cl[4], ch[4];
+            mma_u8s8_z(cl, wa.x & ML, wb.x & ML, wa.y & ML, wb.y & ML, q0.x, q0.y);
+            mma_u8s8(cl, wa.z & ML, wb.z & ML, wa.w & ML, wb.w & ML, q0.z, q0.w);
+            mma_u8s8_z(ch, wa.x & MH, wb.x & MH, wa.y & MH, wb.y & MH, q1.x, q1.y);
+            mma_u8s8(ch, wa.z & MH, wb.z & MH, wa.w & MH, wb.w & MH, q1.z, q1.w);
+            // columns (hi limb, lo limb): value = 128 hi + lo; the high-nibble sums carry a factor 16
+            const int v0 = cl[0] * 128 + cl[1] + ((ch[0] * 128 + ch[1]) >> 4);
+            const int v1 = cl[2] * 128 + cl[3] + ((ch[2] * 128 + ch[3]) >> 4);
+            acc[0][n] = fmaf(A0, (float)v0 * fS.x, fmaf(B0, fS.y, acc[0][n]));
+            acc[1][n] = fmaf(A1, (float)v1 * fS.x, fmaf(B1, fS.y, acc[1][n]));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------- Q6_K (GGUF)
+// acc += d * sc * (factor * sum q x_int - 32 sum x) per 16 weights (the image stores 32 sum x).
+template <int MT>
+__device__ __forceinline__ void item_q6k(uint32_t it, const LaneB& lb, int h, int m, float (&acc)[2][MT], int lane) {
+    const int g = lane >> 2;
+    const uint4 wa = lds128(it + lane * 16);
+    const uint4 wb = lds128(it + 512 + lane * 16);
+    const uint4 hq = lds128(it + 1024 + lane * 16);
+    const uint32_t hs = lds32(it + 1536 + lane * 4);
+    const uint32_t dd = lds32(it + 1664 + g * 4);
+    const float2 d01 = __half22float2(*reinterpret_cast<const __half2*>(&dd));
+    // scale of the low group, and a quarter of the scale of the high group (its codes are kept as 4 q)
+    const float D00 = d01.x * (float)(int)(int8_t)(hs & 0xFFu), D01 = d01.x * 0.25f * (float)(int)(int8_t)((hs >> 8) & 0xFFu);
+    const float D10 = d01.y * (float)(int)(int8_t)((hs >> 16) & 0xFFu), D11 = d01.y * 0.25f * (float)(int)(int8_t)(hs >> 24);
+    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u, M45 = 0x30303030u, M23 = 0x0C0C0C0Cu;
+    uint32_t A[2][4], B[2][4];   // [row][nibble word]
+    {
+        const uint32_t w[2][4] = {{wa.x, wa.y, wa.z, wa.w}, {wb.x, wb.y, wb.z, wb.w}};
+        const uint32_t q[2][2] = {{hq.x, hq.y}, {hq.z, hq.w}};
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint32_t hh = q[r][u];
+                A[r][2 * u] = (w[r][2 * u] & ML) | (hh & M45);
+                B[r][2 * u] = (w[r][2 * u] & MH) | (hh & M23);
+                A[r][2 * u + 1] = (w[r][2 * u + 1] & ML) | ((hh >> 2) & M45);
+                B[r][2 * u + 1] = (w[r][2 * u + 1] & MH) | ((hh << 2) & M23);
+            }
+        }
+    }
+    const uint32_t bp = lb.b0 + h * lb.bh;
+    const uint32_t fp = lb.f0 + h * lb.fh;
+#pragma unroll
+    for (int n = 0; n < MT; n++) {
+        if (n < m) {
+            const uint4 q0 = lds128(bp + n * lb.bn);
+            const uint4 q1 = lds128(bp + n * lb.bn + 16);
+            const uint4 fSb = lds128(fp + n * lb.fn);
+            const float4 fS = make_float4(__uint_as_float(fSb.x), __uint_as_float(fSb.y), __uint_as_float(fSb.z), __uint_as_float(fSb.w));
+            int cl[4], ch[4];
+            mma_u8s8_z(cl, A[0][0], A[1][0], A[0][1], A[1][1], q0.x, q0.y);
+            mma_u8s8(cl, A[0][2], A[1][2], A[0][3], A[1][3], q0.z, q0.w);
+            mma_u8s8_z(ch, B[0][0], B[1][0], B[0][1], B[1][1], q1.x, q1.y);
+            mma_u8s8(ch, B[0][2], B[1][2], B[0][3], B[1][3], q1.z, q1.w);
+            const float l0 = (float)(cl[0] * 128 + cl[1]), l1 = (float)(cl[2] * 128 + cl[3]);
+            const float h0 = (float)(ch[0] * 128 + ch[1]), h1 = (float)(ch[2] * 128 + ch[3]);
+            // high group: 4 q in the codes and a quarter scale, so its offset is 4 * 32 sum x
+            acc[0][n] = fmaf(D00, fmaf(l0, fS.x, -fS.y), fmaf(D01, fmaf(h0, fS.z, -4.0f * fS.w), acc[0][n]));
+            acc[1][n] = fmaf(D10, fmaf(l1, fS.x, -fS.y), fmaf(D11, fmaf(h1, fS.z, -4.0f * fS.w), acc[1][n]));
+        }
+    }
+}
+
+// What a warp streams for one product segment.
+struct Stream {
+    const uint8_t* src;   // next byte to copy
+    int to_issue;         // items not yet requested
+    int item_bytes;
+};
+
+// Per-warp ring bookkeeping (uniform across the lanes of a warp).
+struct Ring {
+    uint32_t bar0;        // shared address of the warp's first mbarrier
+    uint32_t slot0;       // shared address of the warp's first slot
+    int depth, slot_bytes, chunk;
+    int pslot, cslot;     // next slot to fill / to consume
+    uint32_t parity;      // bit s: parity the next wait on slot s uses
+    int inflight;         // chunks requested and not yet consumed
+};
+
+__device__ __forceinline__ void ring_issue(Ring& r, Stream& s, int lane) {
+    const int cnt = min(r.chunk, s.to_issue);
+    const uint32_t bytes = (uint32_t)cnt * (uint32_t)s.item_bytes;
+    if (lane == 0) {
+        const uint32_t bar = r.bar0 + r.pslot * 8;
+        // the slot's previous contents were read through the generic proxy; order those reads before the
+        // asynchronous write
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(r.slot0 + r.pslot * r.slot_bytes, s.src, bytes, bar);
+    }
+    s.src += bytes;
+    s.to_issue -= cnt;
+    r.pslot = r.pslot + 1 == r.depth ? 0 : r.pslot + 1;
+    r.inflight++;
+}
+
+__device__ __forceinline__ void ring_fill(Ring& r, Stream& s, int lane) {
+    while (r.inflight < r.depth && s.to_issue > 0) ring_issue(r, s, lane);
+}
+
+// Waits (bounded) for the chunk in the consumer slot; false when the wait gave up.
+__device__ __forceinline__ bool ring_wait(const Ring& r, long long budget) {
+    const uint32_t bar = r.bar0 + r.cslot * 8;
+    const uint32_t par = (r.parity >> r.cslot) & 1u;
+    if (mbar_try_wait(bar, par)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, par)) return true;
+        if (clock64() - t0 > budget) return false;
+    }
+}
+
+__device__ __forceinline__ void ring_release(Ring& r) {
+    r.parity ^= 1u << r.cslot;
+    r.cslot = r.cslot + 1 == r.depth ? 0 : r.cslot + 1;
+    r.inflight--;
+}
+
+template <int MT>
+__device__ __forceinline__ void quad_reduce(float (&acc)[2][MT]) {
+#pragma unroll
+    for (int n = 0; n < MT; n++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float s = acc[i][n];
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+            acc[i][n] = s;
+        }
+    }
+}
+
+template <int MT>
+__device__ __forceinline__ void store_tile(const DOp& op, int prt, const float (&acc)[2][MT], int m, int lane) {
+    if ((lane & 3) != 0) return;
+    const int g = lane >> 2;
+#pragma unroll
+    for (int n = 0; n < MT; n++) {
+        if (n < m) {
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int row = prt * 16 + g + 8 * i;
+                if (row < op.n_rows) {
+                    const float val = acc[i][n];
+                    op.y[(int64_t)n * op.ldy + row] = val;
+                    for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][(int64_t)n * op.ldy + row] = val;
+                }
+            }
+        }
+    }
+}
+
+constexpr long long WAIT_BUDGET = 2000000000ll;   // SM clock cycles (about a second)
+
+// One product segment: row tiles [rtb, rte) of `op` (product-local indices), consumed by the CTA's 8 warps.
+// Returns false when a bounded wait expired.
+template <int KIND, int MT>
+__device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int i1, Ring& ring, Stream& st, const LaneB& lb, int m,
+                                            float* red, float (&pend)[2][MT], int& pend_rt, int lane, int warp) {
+    const int nh = op.nh;
+    int prt = rtb + i0 / nh;
+    int h = i0 - (i0 / nh) * nh;
+    bool mine = h == 0;
+    float acc[2][MT];
+#pragma unroll
+    for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+    int remaining = i1 - i0;
+    pend_rt = -1;
+    while (remaining > 0) {
+        const int cnt = min(ring.chunk, remaining);
+        bool ok = ring_wait(ring, WAIT_BUDGET);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) return false;
+        uint32_t it = ring.slot0 + ring.cslot * ring.slot_bytes;
+        for (int c = 0; c < cnt; c++, it += op.item_bytes) {
+            if (KIND == DK_Q4K) item_q4k<MT>(it, lb, h, m, acc, lane);
+            else item_q6k<MT>(it, lb, h, m, acc, lane);
+            if (++h == nh) {   // the row tile is complete as far as this warp is concerned
+                quad_reduce<MT>(acc);
+                if (mine) {
+                    store_tile<MT>(op, prt, acc, m, lane);
+                } else if ((lane & 3) == 0) {
+#pragma unroll
+                    for (int n = 0; n < MT; n++) {
+                        red[(warp * 16 + (lane >> 2)) * MT + n] = acc[0][n];
+                        red[(warp * 16 + (lane >> 2) + 8) * MT + n] = acc[1][n];
+                    }
+                }
+                h = 0; prt++; mine = true;
+#pragma unroll
+                for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+            }
+        }
+        remaining -= cnt;
+        __syncwarp();   // every lane has read the slot before it is refilled
+        ring_release(ring);
+        if (st.to_issue > 0) ring_issue(ring, st, lane);
+    }
+    if (h != 0) {   // the range ends inside a row tile
+        quad_reduce<MT>(acc);
+        if (mine) {   // this warp started it: it collects the other parts after the CTA has met
+            pend_rt = prt;
+#pragma unroll
+            for (int n = 0; n < MT; n++) { pend[0][n] = acc[0][n]; pend[1][n] = acc[1][n]; }
+        } else if ((lane & 3) == 0) {
+#pragma unroll
+            for (int n = 0; n < MT; n++) {
+                red[(warp * 16 + (lane >> 2)) * MT + n] = acc[0][n];
+                red[(warp * 16 + (lane >> 2) + 8) * MT + n] = acc[1][n];
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void warp_range(int items, int warp, int& i0, int& i1) {
+    i0 = (int)(((int64_t)items * warp) >> 3);
+    i1 = (int)(((int64_t)items * (warp + 1)) >> 3);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(256, 2)
+gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_rt, int m,
+               int* status, int chunk, int depth, int slot_bytes) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* red = reinterpret_cast<float*>(smem + BAR_BYTES);
+    uint8_t* zero = smem + BAR_BYTES + RED_BYTES;
+    uint8_t* ring_base = smem + FIXED_BYTES;
+    uint8_t* ximg = ring_base + (size_t)8 * depth * slot_bytes;
+
+    Ring ring;
+    ring.bar0 = smem_addr(smem) + warp * MAX_DEPTH * 8;
+    ring.slot0 = smem_addr(ring_base + (size_t)warp * depth * slot_bytes);
+    ring.depth = depth; ring.slot_bytes = slot_bytes; ring.chunk = chunk;
+    ring.pslot = 0; ring.cslot = 0; ring.parity = 0u; ring.inflight = 0;
+    if (lane == 0)
+        for (int s = 0; s < depth; s++) mbar_init(ring.bar0 + s * 8, 1);
+    if (threadIdx.x < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(zero)[threadIdx.x] = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+
+    int tb, te;
+    if (ranges) {
+        const int2 rg = ranges[blockIdx.x];
+        tb = rg.x; te = rg.y;
+    } else {
+        tb = (int)(((int64_t)blockIdx.x * total_rt) / gridDim.x);
+        te = (int)(((int64_t)(blockIdx.x + 1) * total_rt) / gridDim.x);
+    }
+    int opi = 0;
+    if (n_ops > 1) {   // first product whose row tiles reach tb
+        int lo = 0, hi = n_ops - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (ops[mid].rt0 + ops[mid].nrt <= tb) lo = mid + 1; else hi = mid;
+        }
+        opi = lo;
+    }
+    // Programmatic dependent launch: the next kernel of the stream may start its CTAs as ours retire; like this
+    // kernel it touches nothing an earlier kernel writes (activations, outputs) before its griddepcontrol.wait,
+    // only the immutable packed weights.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    bool alive = true;
+    bool first = true;
+    // segment state: the product, its row tiles owned by this CTA, this warp's items and stream
+    DOp op = single;
+    int seg_b = tb, seg_e = tb, i0 = 0, i1 = 0;
+    Stream st{nullptr, 0, 0};
+    auto open_segment = [&](int sb, bool issue) {
+        if (n_ops > 1) {
+            while (opi < n_ops - 1 && sb >= ops[opi].rt0 + ops[opi].nrt) opi++;
+            op = ops[opi];
+        }
+        seg_b = sb;
+        seg_e = min(te, op.rt0 + op.nrt);
+        warp_range((seg_e - seg_b) * op.nh, warp, i0, i1);
+        st.src = op.img + ((int64_t)(seg_b - op.rt0) * op.nh + i0) * op.item_bytes;
+        st.to_issue = i1 - i0;
+        st.item_bytes = op.item_bytes;
+        if (issue) ring_fill(ring, st, lane);   // the weights are immutable: start them before anything else
+    };
+    if (tb < te) open_segment(tb, true);
+
+    while (seg_b < te) {
+        if (first) {
+            // only now wait for the kernels ahead in the stream, whose outputs the activations may be
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            first = false;
+        }
+        __syncthreads();   // the previous segment's activations and hand-over slots are no longer read
+        ActImg ai;
+        ai.nb = op.k >> 5;
+        ai.limbs = ximg;
+        float* fs = reinterpret_cast<float*>(ximg + (size_t)m * ai.nb * 64);
+        ai.fs = fs;
+        LaneB lb;
+        if (op.kind == DK_Q4K) {
+            prep_x<32>(op.x, op.ldx, op.k, m, ximg, fs, 1.0f);
+            lb = lane_b<32>(ai, zero, lane);
+        } else {
+            prep_x<16>(op.x, op.ldx, op.k, m, ximg, fs, 32.0f);
+            lb = lane_b<16>(ai, zero, lane);
+        }
+        __syncthreads();
+
+        float pend[2][MT];
+        int pend_rt = -1;
+        const DOp cur = op;
+        const int cur_b = seg_b - op.rt0, cur_items = (seg_e - seg_b) * op.nh, cur_i1 = i1;
+        if (alive) {
+            bool ok;
+            if (cur.kind == DK_Q4K) ok = run_segment<DK_Q4K, MT>(cur, cur_b, i0, i1, ring, st, lb, m, red, pend, pend_rt, lane, warp);
+            else ok = run_segment<DK_Q6K, MT>(cur, cur_b, i0, i1, ring, st, lb, m, red, pend, pend_rt, lane, warp);
+            if (!ok) {
+                alive = false;
+                if (lane == 0) atomicExch(status, 100 + warp);
+            }
+        }
+        // next segment: its first chunks are requested before the CTA meets for the hand-over
+        const int next_b = seg_e;
+        if (next_b < te) open_segment(next_b, alive);   // a warp that gave up still follows the CTA's segments
+        else seg_b = next_b;
+        __syncthreads();   // hand-over slots are written
+        if (alive && pend_rt >= 0) {
+            // parts of the pending row tile lie with the following warps, in order, until one reaches its end
+            const int tile_end = (pend_rt - cur_b + 1) * cur.nh;
+            int pos = cur_i1;
+            for (int w2 = warp + 1; w2 < 8 && pos < tile_end; w2++) {
+                int j0, j1;
+                warp_range(cur_items, w2, j0, j1);
+                if (j0 == j1) continue;
+                if ((lane & 3) == 0) {
+#pragma unroll
+                    for (int n = 0; n < MT; n++) {
+                        pend[0][n] += red[(w2 * 16 + (lane >> 2)) * MT + n];
+                        pend[1][n] += red[(w2 * 16 + (lane >> 2) + 8) * MT + n];
+                    }
+                }
+                pos = j1;
+            }
+            store_tile<MT>(cur, pend_rt, pend, m, lane);
+        }
+    }
+    // a wait that gave up leaves copies in flight: they must land before the CTA's shared memory is released
+    if (!alive) {
+        while (ring.inflight > 0) {
+            ring_wait(ring, WAIT_BUDGET);
+            ring_release(ring);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- image build
+// One thread per (item, lane): gathers the lane's bytes of rows g and g+8 from the stream-layout planes.
+__global__ void __launch_bounds__(256) build_image_q4k_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ img, int n_rows, int nh,
+                                                               int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * Q4K_ITEM;
+    uint32_t hs = 0;
+    uint32_t dd[2] = {0u, 0u};
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) {
+            const int64_t hsi = row * nh + h;
+            const uint8_t* blk = raw + (hsi >> 1) * 144;
+            const int j = 4 * (int)(hsi & 1) + t;   // sub-block of the super-block
+            const uint8_t* qs = blk + 16 + 32 * (j >> 1);
+            uint8_t o[16];
+            for (int b = 0; b < 16; b++)
+                o[b] = (j & 1) ? (uint8_t)((qs[b] >> 4) | (qs[16 + b] & 0xF0)) : (uint8_t)((qs[b] & 0x0F) | ((qs[16 + b] & 0x0F) << 4));
+            out = *reinterpret_cast<uint4*>(o);
+            uint32_t sc, mn;
+            q4k_scale_min(blk + 4, j, sc, mn);
+            hs |= (sc | (mn << 8)) << (16 * i);
+            dd[i] = ld32(blk);
+        }
+        *reinterpret_cast<uint4*>(it + 512 * i + lane * 16) = out;
+    }
+    *reinterpret_cast<uint32_t*>(it + 1024 + lane * 4) = hs;
+    if (t == 0) *reinterpret_cast<uint2*>(it + 1152 + g * 8) = make_uint2(dd[0], dd[1]);
+}
+
+__global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * Q6K_ITEM;
+    uint32_t hs = 0, dd = 0;
+    uint32_t hq[4] = {0u, 0u, 0u, 0u};
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) {
+            const int64_t hsi = row * nh + h;
+            const int64_t blk = hsi >> 1;
+            const int sec = (int)(hsi & 1);
+            const uint8_t* ql = v.p[0] + blk * 128 + sec * 64 + 32 * (t & 1);
+            const uint8_t* qh = v.p[1] + blk * 64 + sec * 32;
+            uint8_t q[32];   // the lane's 32 codes: weights 32 t + e of the half
+            for (int e = 0; e < 32; e++) {
+                const uint32_t lo4 = (t < 2) ? (ql[e] & 0x0Fu) : (uint32_t)(ql[e] >> 4);
+                const uint32_t hi2 = (qh[e] >> (2 * t)) & 3u;
+                q[e] = (uint8_t)(lo4 | (hi2 << 4));
+            }
+            uint8_t o[16];
+            for (int b = 0; b < 16; b++) o[b] = (uint8_t)((q[b] & 0x0F) | ((q[16 + b] >> 2) << 4));
+            out = *reinterpret_cast<uint4*>(o);
+            for (int u = 0; u < 2; u++) {
+                uint32_t word = 0;
+                for (int z = 0; z < 4; z++) {
+                    const uint32_t byte = ((uint32_t)(q[8 * u + z] >> 4) << 4) | ((uint32_t)(q[16 + 8 * u + z] & 3) << 2) |
+                                          ((uint32_t)(q[8 * u + 4 + z] >> 4) << 6) | (uint32_t)(q[16 + 8 * u + 4 + z] & 3);
+                    word |= byte << (8 * z);
+                }
+                hq[2 * i + u] = word;
+            }
+            const uint8_t* sc = v.p[2] + blk * 16 + sec * 8 + 2 * t;
+            hs |= ((uint32_t)sc[0] | ((uint32_t)sc[1] << 8)) << (16 * i);
+            dd |= (uint32_t)ld16(v.p[3] + blk * 2) << (16 * i);
+        }
+        *reinterpret_cast<uint4*>(it + 512 * i + lane * 16) = out;
+    }
+    *reinterpret_cast<uint4*>(it + 1024 + lane * 16) = make_uint4(hq[0], hq[1], hq[2], hq[3]);
+    *reinterpret_cast<uint32_t*>(it + 1536 + lane * 4) = hs;
+    if (t == 0) *reinterpret_cast<uint32_t*>(it + 1664 + g * 4) = dd;
+}
+
+}  // namespace
+
+int decode_kind_of(int fmt) {
+    if (fmt == F_Q4K) return DK_Q4K;
+    if (fmt == F_Q6K) return DK_Q6K;
+    return DK_NONE;
+}
+
+int decode_item_bytes(int kind) { return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : 0; }
+
+bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k) {
+    if (decode_kind_of(fmt) == DK_NONE || orient != B200Q_ORIENT_NK) return false;
+    if (k % 128 || k > (1 << 24) || n_rows > 0x7FFFFFF0ll) return false;
+    const int64_t items = ((n_rows + 15) / 16) * (k / 128);
+    return items < (1ll << 31) / 8;   // item counts of a CTA's segment stay inside 32-bit arithmetic
+}
+
+int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
+    *out = DImage{};
+    const int kind = decode_kind_of(w->fmt);
+    if (kind == DK_NONE) return B200Q_OK;
+    DImage d;
+    d.kind = kind;
+    d.item_bytes = decode_item_bytes(kind);
+    d.nh = (int)(w->k / 128);
+    d.nrt = (int)((w->n_local + 15) / 16);
+    const int64_t n_items = (int64_t)d.nrt * d.nh;
+    d.bytes = (size_t)n_items * d.item_bytes;
+    void* p = nullptr;
+    B200Q_CUDA(cudaMalloc(&p, d.bytes + 256), B200Q_ERR_ALLOC);
+    d.base = static_cast<uint8_t*>(p);
+    const int64_t threads = n_items * 32;
+    const int64_t grid = (threads + 255) / 256;
+    if (grid > 0x7FFFFFFF) {
+        cudaFree(p);
+        return fail(B200Q_ERR_INVALID, "upload: tensor too large for one image-build launch");
+    }
+    if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
+    else build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(B200Q_ERR_LAUNCH, e, "upload: decode image");
+    }
+    *out = d;
+    return B200Q_OK;
+}
+
+size_t gemv_i8_image_smem(int kind, int k, int m) {
+    // limbs: 2 bytes per value; factors: 8 bytes per group of 32 (Q4_K) or 16 (Q6_K)
+    const size_t nb = (size_t)(k >> 5);
+    return (size_t)m * nb * 64 + (size_t)m * nb * (kind == DK_Q6K ? 16 : 8) + 16;
+}
+
+bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaunch* out) {
+    size_t image = 0;
+    for (int kd = 0; kd < DK_COUNT; kd++)
+        if (kind_mask & (1 << kd)) image = max(image, gemv_i8_image_smem(kd, kmax, m));
+    // tuning knob (like the reference's ROCFORGE_TILE_* variables, src/ggml/hip_backend/tuning.rs:237-275):
+    // B200Q_DECODE_RING="items per copy,slots per warp"
+    int chunk = 2, depth = 4;
+    if (const char* e = getenv("B200Q_DECODE_RING")) {
+        int c = 0, d = 0;
+        if (sscanf(e, "%d,%d", &c, &d) == 2 && c >= 1 && c <= 8 && d >= 2 && d <= MAX_DEPTH) { chunk = c; depth = d; }
+    }
+    const size_t cap2 = 113 * 1024, cap1 = 226 * 1024;
+    for (;;) {
+        const int slot = ((chunk * max_item_bytes + 127) / 128) * 128;
+        const size_t total = FIXED_BYTES + (size_t)8 * depth * slot + image;
+        if (total <= cap2 || (total <= cap1 && depth <= 3)) {
+            out->chunk_items = chunk; out->depth = depth; out->slot_bytes = slot;
+            out->smem_bytes = total;
+            out->ctas_per_sm = total <= cap2 ? 2 : 1;
+            return true;
+        }
+        if (total <= cap1 && FIXED_BYTES + (size_t)8 * 2 * slot + image > cap2) {
+            // two CTAs per SM are out of reach: keep the deep ring on one CTA
+            out->chunk_items = chunk; out->depth = depth; out->slot_bytes = slot;
+            out->smem_bytes = total;
+            out->ctas_per_sm = 1;
+            return true;
+        }
+        if (depth > 2) depth--;
+        else if (chunk > 1) chunk--;
+        else return false;
+    }
+}
+
+bool gemv_i8_supported(const b200q_weight* w, int m) {
+    if (!w->dimg.base || m < 1 || m > 8) return false;
+    DecodeLaunch L;
+    return gemv_i8_plan(w->dimg.item_bytes, (int)w->k, 1 << w->dimg.kind, m, &L);
+}
+
+int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
+                   int total_rt, int m, const DecodeLaunch& L) {
+    if (total_rt <= 0) return B200Q_OK;
+    static bool configured[64][4] = {};
+    const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
+    const void* kernels[4] = {(const void*)gemv_i8_kernel<1>, (const void*)gemv_i8_kernel<2>, (const void*)gemv_i8_kernel<4>,
+                              (const void*)gemv_i8_kernel<8>};
+    if (!configured[ctx->device & 63][mi]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kernels[mi], cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024), B200Q_ERR_LAUNCH);
+        configured[ctx->device & 63][mi] = true;
+    }
+    DOp single{};
+    if (h_single) single = *h_single;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)n_ctas);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = L.smem_bytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap with the tail of the kernel ahead
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int* status = ctx->d_status;
+    int chunk = L.chunk_items, depth = L.depth, slot = L.slot_bytes;
+    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &total_rt, &m, &status, &chunk, &depth, &slot};
+    B200Q_CUDA(cudaLaunchKernelExC(&cfg, kernels[mi], args), B200Q_ERR_LAUNCH);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    ctx->tc_pending = true;   // the next synchronise reads the status word
+    return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include <cstring>
 
+#include "gemv_i8.cuh"
 #include "gemv_mma.cuh"
 
 using namespace b200q;
@@ -29,7 +30,27 @@ struct b200q_batch {
     const float* hosty_base = nullptr;
     GOp single_hosty{};
     bool has_q4_0 = false;   // some product is GGUF Q4_0: the launch uses the kernel instantiation that carries it
+    // grouped launch of the integer decode kernel (every product has a decode image)
+    bool grouped_i8 = false;
+    DOp* d_dops = nullptr;
+    DOp* d_dops_hosty = nullptr;
+    std::vector<DOp> h_dops;
+    DOp dsingle{}, dsingle_hosty{};
+    DecodeLaunch dl{};
+    int total_rt = 0;
 };
+
+static DOp make_dop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
+    DOp op{};
+    op.img = w->dimg.base;
+    op.x = x; op.y = y; op.ldx = ldx; op.ldy = ldy;
+    op.n_rows = (int)w->n_local; op.k = (int)w->k;
+    op.kind = w->dimg.kind; op.item_bytes = w->dimg.item_bytes; op.nh = w->dimg.nh;
+    op.rt0 = 0; op.nrt = w->dimg.nrt;
+    op.n_extra = w->ctx->scatter_extra;
+    for (int p = 0; p < op.n_extra; p++) op.y_extra[p] = w->ctx->scatter_y[p];
+    return op;
+}
 
 static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
     GOp op{};
@@ -59,6 +80,25 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
         return scatter ? fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: the sequential kernel writes one output only") : launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
     bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx % 4) == 0;
     if (!aligned) return scatter ? fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: activations must be 16-byte aligned") : launch_matmul_seq(ctx, w, x, ldx, y, ldy, m);
+    // integer decode kernel on the tensor's decode image: largest activation-row chunk whose image fits
+    {
+        int chunk = 8;
+        while (chunk > 1 && !gemv_i8_supported(w, chunk)) chunk >>= 1;
+        if (gemv_i8_supported(w, chunk)) {
+            for (int i = 0; i < m; i += chunk) {
+                const int mm = m - i < chunk ? m - i : chunk;
+                DOp op = make_dop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
+                for (int p = 0; p < op.n_extra; p++) op.y_extra[p] += (int64_t)i * ldy;
+                DecodeLaunch L;
+                gemv_i8_plan(op.item_bytes, op.k, 1 << op.kind, mm, &L);
+                int n_ctas = ctx->info.sm_count * L.ctas_per_sm;
+                if (n_ctas > op.nrt) n_ctas = op.nrt;
+                int rc = launch_gemv_i8(ctx, &op, nullptr, 1, nullptr, n_ctas, op.nrt, mm, L);
+                if (rc != B200Q_OK) return rc;
+            }
+            return B200Q_OK;
+        }
+    }
     // largest activation-row chunk whose shared-memory image fits the tensor-core decode kernel
     int chunk = 8;
     while (chunk > 1 && !gemv_mma_supported(w, chunk)) chunk >>= 1;
@@ -232,6 +272,63 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
         b->y.push_back(d_y[i]);
         b->weight_bytes += w[i]->packed_bytes;
     }
+    // one grouped launch of the integer decode kernel when every product has a decode image
+    bool all_i8 = count > 0;
+    for (int i = 0; i < count; i++) all_i8 = all_i8 && gemv_i8_supported(w[i], m);
+    if (all_i8) {
+        int max_item = 0, kmax = 0, mask = 0;
+        for (int i = 0; i < count; i++) {
+            if (w[i]->dimg.item_bytes > max_item) max_item = w[i]->dimg.item_bytes;
+            if (w[i]->k > kmax) kmax = (int)w[i]->k;
+            mask |= 1 << w[i]->dimg.kind;
+        }
+        all_i8 = gemv_i8_plan(max_item, kmax, mask, m, &b->dl);
+    }
+    if (all_i8) {
+        std::vector<DOp> ops(count);
+        std::vector<double> tile_cost;
+        int total = 0;
+        for (int i = 0; i < count; i++) {
+            ops[i] = make_dop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
+            ops[i].rt0 = total;
+            total += ops[i].nrt;
+            const double c = (double)ops[i].nh * ops[i].item_bytes;
+            for (int t = 0; t < ops[i].nrt; t++) tile_cost.push_back(c);
+        }
+        int n_ctas = ctx->info.sm_count * b->dl.ctas_per_sm;
+        if (n_ctas > total) n_ctas = total;
+        double sum = 0;
+        for (double c : tile_cost) sum += c;
+        std::vector<int2> ranges(n_ctas);
+        double acc = 0;
+        int t = 0;
+        for (int c = 0; c < n_ctas; c++) {
+            ranges[c].x = t;
+            const double limit = sum * (c + 1) / n_ctas;
+            while (t < total && (acc + tile_cost[t] * 0.5 <= limit || c == n_ctas - 1)) acc += tile_cost[t++];
+            ranges[c].y = t;
+        }
+        cudaError_t e = cudaSetDevice(ctx->device);
+        if (e == cudaSuccess) e = cudaMalloc(&b->d_dops, sizeof(DOp) * count);
+        if (e == cudaSuccess) e = cudaMalloc(&b->d_ranges, sizeof(int2) * n_ctas);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_dops, ops.data(), sizeof(DOp) * count, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ranges, ranges.data(), sizeof(int2) * n_ctas, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            if (b->d_dops) cudaFree(b->d_dops);
+            if (b->d_ranges) cudaFree(b->d_ranges);
+            delete b;
+            return cuda_fail(B200Q_ERR_ALLOC, e, "batch_create");
+        }
+        b->grouped = true;
+        b->grouped_i8 = true;
+        b->h_dops = ops;
+        b->n_ctas = n_ctas;
+        b->total_rt = total;
+        b->dsingle = ops[0];
+        *out = b;
+        return B200Q_OK;
+    }
     // plan one grouped launch when every product has a tensor-core decode kernel
     bool all = count > 0;
     for (int i = 0; i < count; i++) all = all && gemv_mma_supported(w[i], m);
@@ -296,7 +393,12 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (!ctx || !batch) return fail(B200Q_ERR_INVALID, "batch_run: null argument");
     B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
     if (ms_out) B200Q_CUDA(cudaEventRecord(ctx->ev0, ctx->stream), B200Q_ERR_DEVICE);
-    if (batch->grouped) {
+    if (batch->grouped_i8) {
+        int n = (int)batch->w.size();
+        int rc = launch_gemv_i8(ctx, &batch->dsingle, batch->d_dops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
+                                batch->total_rt, batch->m, batch->dl);
+        if (rc != B200Q_OK) return rc;
+    } else if (batch->grouped) {
         int n = (int)batch->w.size();
         int rc = launch_gemv_mma(ctx, &batch->single, batch->d_ops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
                                  batch->total_tiles, batch->m, batch->smem, batch->ring_d, batch->has_q4_0);
@@ -346,6 +448,28 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
         cudaPointerAttributes pa{};
         if (cudaPointerGetAttributes(&pa, h_y_all) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer) {
             float* dy = static_cast<float*>(pa.devicePointer);
+            if (batch->grouped_i8) {
+                if (batch->hosty_base != h_y_all) {
+                    std::vector<DOp> ops = batch->h_dops;
+                    size_t off = 0;
+                    for (size_t i = 0; i < cnt; i++) {
+                        ops[i].y = dy + off;
+                        off += (size_t)batch->m * batch->w[i]->n_local;
+                    }
+                    cudaError_t e = cudaSuccess;
+                    if (!batch->d_dops_hosty) e = cudaMalloc(&batch->d_dops_hosty, sizeof(DOp) * cnt);
+                    if (e == cudaSuccess) e = cudaMemcpyAsync(batch->d_dops_hosty, ops.data(), sizeof(DOp) * cnt, cudaMemcpyHostToDevice, ctx->stream);
+                    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // `ops` is pageable and local
+                    if (e != cudaSuccess) return cuda_fail(B200Q_ERR_ALLOC, e, "batch_run_host");
+                    batch->dsingle_hosty = ops[0];
+                    batch->hosty_base = h_y_all;
+                }
+                int n = (int)cnt;
+                int rc = launch_gemv_i8(ctx, &batch->dsingle_hosty, batch->d_dops_hosty, n, n > 1 ? batch->d_ranges : nullptr,
+                                        batch->n_ctas, batch->total_rt, batch->m, batch->dl);
+                if (rc != B200Q_OK) return rc;
+                return b200q_synchronize(ctx);
+            }
             if (batch->hosty_base != h_y_all) {
                 std::vector<GOp> ops = batch->h_ops;
                 size_t off = 0;
@@ -388,12 +512,14 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
 
 int b200q_batch_free(b200q_batch* batch) {
     if (!batch) return B200Q_OK;
-    if (batch->d_ops || batch->d_ranges) {
+    if (batch->d_ops || batch->d_ranges || batch->d_dops) {
         cudaSetDevice(batch->ctx->device);
         cudaStreamSynchronize(batch->ctx->stream);
         if (batch->d_ops) cudaFree(batch->d_ops);
+        if (batch->d_dops) cudaFree(batch->d_dops);
         if (batch->d_ranges) cudaFree(batch->d_ranges);
         if (batch->d_ops_hosty) cudaFree(batch->d_ops_hosty);
+        if (batch->d_dops_hosty) cudaFree(batch->d_dops_hosty);
         cudaGetLastError();
     }
     delete batch;

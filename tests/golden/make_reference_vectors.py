@@ -117,6 +117,36 @@ for i in range(8):
 d[32:256] = b"\x88" * 224
 add("q4_k_gpu_test_input", "tests/q_dequant_tests.rs:257-273", "rf_q4_k", d, 256, q4k_expect(d, 256), 1e-3)
 
+# ---- Q5_K / Q3_K / Q2_K in the reference's 256-byte layouts: src/loader/dequant.rs:439-665 -------------------
+# (the tests set only the first sub-block's f16 scale; every other scale, min and code byte is zero)
+def kblock(scale=1.0):
+    b = bytearray(256); b[0:2] = f16le(scale)
+    return b
+
+d = kblock()
+add("q5_k_zeros", "src/loader/dequant.rs:440-461", "rf_q5_k", d, 256, {"all": 0.0}, 1e-6)
+d = kblock(); d[48] = 0x01
+e = {0: 1.0}; e.update({i: 0.0 for i in range(1, 16)})
+add("q5_k_positive", "src/loader/dequant.rs:464-495", "rf_q5_k", d, 256, e, 0.1)
+d = kblock()
+add("q5_k_partial_block", "src/loader/dequant.rs:498-515", "rf_q5_k", d, 100, {"all": 0.0}, 1e-6)
+d = kblock() + kblock(2.0); d[256 + 48] = 0xFF; d[256 + 49] = 0x80
+add("q5_k_multiple_blocks_first", "src/loader/dequant.rs:518-546", "rf_q5_k", d, 512, {i: 0.0 for i in range(256)}, 1e-5)
+add("q5_k_multiple_blocks_second", "src/loader/dequant.rs:518-546", "rf_q5_k", d, 512, {256: 62.0}, 1.0)
+d = kblock()
+add("q3_k_zeros", "src/loader/dequant.rs:549-566", "rf_q3_k", d, 256, {i: -4.0 for i in range(16)}, 0.1)
+d = kblock(); d[36] = 0x01
+e = {0: -3.0}; e.update({i: -4.0 for i in range(1, 16)})
+add("q3_k_positive", "src/loader/dequant.rs:569-592", "rf_q3_k", d, 256, e, 0.1)
+d = kblock()
+add("q3_k_partial_block", "src/loader/dequant.rs:595-613", "rf_q3_k", d, 100, {i: -4.0 for i in range(16)}, 0.1)
+d = kblock()
+add("q2_k_zeros", "src/loader/dequant.rs:616-635", "rf_q2_k", d, 256, {i: 0.0 for i in range(16)}, 1e-5)
+d = kblock(); d[68] = 0x01
+add("q2_k_positive", "src/loader/dequant.rs:638-657", "rf_q2_k", d, 256, {0: 1.0}, 0.1)
+d = kblock()
+add("q2_k_partial_block", "src/loader/dequant.rs:660-678", "rf_q2_k", d, 100, {i: 0.0 for i in range(16)}, 1e-5)
+
 json_cases = dict(dequant=cases)
 
 # ---- scalar codecs, src/loader/mxfp_tests.rs ------------------------------------

@@ -99,13 +99,17 @@ def test_reference_known_answer_vectors_on_gpu(be):
     gold = json.load(open(os.path.join(HERE, "golden", "reference_vectors.json")))
     fn = {"rf_q4_0": ops.dequantize_q4_0_kernel_cached, "rf_q8_0": ops.dequantize_q8_0_gpu_kernel,
           "rf_q4_k": ops.dequantize_q4_k_gpu_kernel, "rf_q6_k": ops.dequantize_q6_k_gpu_kernel}
+    generic = {"rf_q5_k": synth.Q5_K, "rf_q3_k": synth.Q3_K, "rf_q2_k": synth.Q2_K}   # src/loader/dequant.rs:439-665
     for case in gold["dequant"]:
-        if case["fn"] not in fn:
+        if case["fn"] not in fn and case["fn"] not in generic:
             continue
         data, n = bytes.fromhex(case["data"]), case["n"]
         out = be.allocate_buffer(n * 4)
-        fn[case["fn"]](be, data, out, n)
-        got = out.to_numpy(np.float32, n)
+        if case["fn"] in generic:   # the reference has no GPU wrapper for these: host bytes -> device fp32
+            got = gpu_dequant_bytes(be, generic[case["fn"]], synth.RF, np.frombuffer(data, dtype=np.uint8), n)
+        else:
+            fn[case["fn"]](be, data, out, n)
+            got = out.to_numpy(np.float32, n)
         if case.get("finite"):
             assert np.all(np.isfinite(got))
         for k, v in case["expect"].items():

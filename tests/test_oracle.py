@@ -16,7 +16,8 @@ with open(os.path.join(HERE, "golden", "reference_vectors.json")) as f:
     GOLD = json.load(f)
 
 FN = {"rf_q4_0": (synth.Q4_0, synth.RF), "rf_q8_0": (synth.Q8_0, synth.RF), "rf_q4_k": (synth.Q4_K, synth.RF),
-      "rf_q6_k": (synth.Q6_K, synth.RF)}
+      "rf_q6_k": (synth.Q6_K, synth.RF), "rf_q5_k": (synth.Q5_K, synth.RF), "rf_q3_k": (synth.Q3_K, synth.RF),
+      "rf_q2_k": (synth.Q2_K, synth.RF)}
 
 
 @pytest.mark.parametrize("case", GOLD["dequant"], ids=[c["name"] for c in GOLD["dequant"]])
@@ -251,7 +252,9 @@ def test_matmul_orders_and_threads(oracle):
 
 def test_rf_k_quants_follow_the_reference_loops(oracle):
     """Q5_K / Q3_K / Q2_K in the reference's 256-byte layouts (src/loader/dequant.rs:150-419), evaluated here
-    element by element in Python from the same formulas; the reference has no test vectors for them."""
+    element by element in Python from the same formulas on random bytes. The reference's own known-answer
+    vectors for these formats (src/loader/dequant.rs:439-665) are checked in test_reference_dequant_vectors;
+    this test widens them to non-trivial scales, minima and high bits."""
     rng = synth.rng_for(77)
     for qt in (synth.Q5_K, synth.Q3_K, synth.Q2_K):
         data = synth.gen_packed(qt, synth.RF, 3 * 256, rng)
