@@ -42,26 +42,28 @@ namespace {
 constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 
-// ---- item layouts (bytes inside one item; L = lane = 4 g + t, rows g and g+8 of the row tile) ---------------
-// Q4_K:   [0,512)      16 code bytes of row g per lane: byte b = weight b (low nibble) | weight 16+b (high nibble)
-//                      of sub-block t of the half
+// ---- item layouts (bytes inside one item; lane = 4 g + t; rows g and g+8 of the row tile; s = sub-block of 32
+// weights inside the item's 128). A "chunk" (g, s) is 16 bytes placed at chunk_pos(g, s) * 16 of its 512-byte area,
+// so that both kernels read it without bank conflicts.
+// Q4_K:   [0,512)      chunk (g, s): codes of sub-block s of row g: byte b = weight b (low nibble) | weight 16+b (high)
 //         [512,1024)   the same for row g+8
-//         [1024,1152)  per lane: scale(g), min(g), scale(g+8), min(g+8) of that sub-block, one byte each
+//         [1024,1152)  per g 16 bytes: for s = 0..3 {scale(g), min(g), scale(g+8), min(g+8)}, one byte each
 //         [1152,1216)  per g: f16 d(g), dmin(g), d(g+8), dmin(g+8) of the super-block the half lies in
 // Q6_K:   [0,512) / [512,1024) as above with nibble byte b = low 4 bits of weight b | (weight 16+b >> 2) << 4
-//         [1024,1536)  per lane 16 bytes: two words of 2-bit fields for row g, two for row g+8. Word u, byte z:
+//         [1024,1536)  chunk (g, s): two words of 2-bit fields for row g, two for row g+8. Word u, byte z:
 //                      bits 4-5 = weight 8u+z >> 4, bits 2-3 = weight 16+8u+z & 3,
 //                      bits 6-7 = weight 8u+4+z >> 4, bits 0-1 = weight 16+8u+4+z & 3
-//         [1536,1664)  per lane: int8 scale of weights 0..15 and of weights 16..31 for row g, then for row g+8
+//         [1536,1664)  per g 16 bytes: for s = 0..3 the int8 scales of weights 0..15 and 16..31 of sub-block s for row
+//                      g, then for row g+8
 //         [1664,1696)  per g: f16 d(g), d(g+8)
 constexpr int Q4K_ITEM = 1216;
 constexpr int Q6K_ITEM = 1696;
 
 constexpr int MAX_DEPTH = 8;
-constexpr int BAR_BYTES = 8 * MAX_DEPTH * 8;          // 8 warps x MAX_DEPTH mbarriers
-constexpr int RED_BYTES = 8 * 16 * 8 * 4;             // 8 warps x 16 rows x up to 8 activation rows
-constexpr int ZERO_BYTES = 32;                        // lanes that supply the zero columns of B read these
-constexpr int FIXED_BYTES = BAR_BYTES + RED_BYTES + ZERO_BYTES;
+constexpr int ZERO_BYTES = 128;                       // lanes that supply the zero columns of B read these
+__host__ __device__ constexpr int bar_bytes(int nw) { return nw * MAX_DEPTH * 8; }   // warps x MAX_DEPTH mbarriers
+__host__ __device__ constexpr int red_bytes(int nw) { return nw * 16 * 8 * 4; }      // warps x 16 rows x up to 8 activation rows
+__host__ __device__ constexpr int fixed_bytes(int nw) { return bar_bytes(nw) + red_bytes(nw) + ZERO_BYTES; }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -122,25 +124,44 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     return v;
 }
 
-// Shared-memory image of one product's activations (m rows of k values), per block of 32 values:
-//   limbs[((n * nb + b) * 2 + L) * 32 + i]  s8 limb L (0 = hi, 1 = lo) of value 32 b + i of row n
-//   fs: per scale group of G values {factor max|x| / 16256, sum of the group's x times `sum_mul`}
-//       G = 32: float2 fs[n * nb + b];  G = 16: float4 fs[n * nb + b] = {f, s} of values 0..15, {f, s} of 16..31
+// ---- activation images ------------------------------------------------------------------------------------
+// Activations are quantised per scale group of the format (G = 32 values for Q4_K, 16 for Q6_K) to the integer
+// q = round(x * 16256 * 128 / max|x|), |q| < 2^21, held as three s8 limbs: q = (l0 * 128 + l1) * 128 + l2 with
+// l0 in [-127, 127] and l1, l2 in [-64, 63]. Per group the image keeps the factor max|x| / (16256 * 128) and the
+// sum of the group's x (times `sum_mul`).
+//
+// One-row layout (m = 1, block-diagonal kernel), per block b of 32 values:
+//   limbs[(b * 3 + L) * 32 + i]   limb L of value 32 b + i
+//   fs: G = 32: float2 {f, s} per block; G = 16: float4 {f, s} of values 0..15, {f, s} of values 16..31
+// Many-row layout (m = 2..8, activation rows on the MMA's N side), per item h (128 values) and row n < m:
+//   lane (n, t) of a warp owns 96 bytes at ((h * m + n) * 4 + t) * 96: for sub-block s and limb L the 8 bytes at
+//   (s * 3 + L) * 8 = values 32 s + 4 t .. + 3 and 32 s + 16 + 4 t .. + 3 (the k-slots of that lane's B fragment)
+//   fs: G = 32: float2 {f, s} at [(b * mp) + n]; G = 16: [(b * 2 + group) * mp + n]; mp = m rounded up to even
 struct ActImg {
-    const uint8_t* limbs;
-    const float* fs;
-    int nb;   // blocks of 32 per row
+    uint8_t* limbs;
+    float* fs;
 };
 
+__device__ __forceinline__ void split_limbs(int q, int& l0, int& l1, int& l2) {
+    l2 = ((q + 64) & 127) - 64;
+    const int q1 = (q - l2) >> 7;
+    l1 = ((q1 + 64) & 127) - 64;
+    l0 = (q1 - l1) >> 7;
+}
+
 // x[m, k] (fp32, global) -> image. 8 consecutive values per thread; the G / 8 lanes of a group agree on the
-// group's maximum and sum by shuffles.
-template <int G>
-__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, uint8_t* limbs, float* fs,
-                                       float sum_mul) {
+// group's maximum and sum by shuffles. MANY selects the many-row layout.
+template <int G, bool MANY, int NT>
+__device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const ActImg& img, float sum_mul) {
     const int units = k >> 3;
     const int nb = k >> 5;
+    const int mp = (m + 1) & ~1;
     const int total = units * m;
-    for (int u0 = 0; u0 < total; u0 += 256) {
+    if (MANY && (m & 1)) {   // the factors of the padding row read as zero
+        const int groups = nb * (G == 32 ? 1 : 2);
+        for (int i = threadIdx.x; i < groups; i += NT) *reinterpret_cast<float2*>(img.fs + ((size_t)i * mp + m) * 2) = make_float2(0.f, 0.f);
+    }
+    for (int u0 = 0; u0 < total; u0 += NT) {
         const int u = u0 + threadIdx.x;
         const bool valid = u < total;
         const int n = valid ? u / units : 0;
@@ -163,108 +184,201 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
             sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
         }
-        const float s = mx > 0.0f ? 16256.0f / mx : 0.0f;
-        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+        const float s = mx > 0.0f ? 2080768.0f / mx : 0.0f;   // 16256 * 128
+        uint32_t w[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const int q = __float2int_rn(v[i] * s);   // |q| <= 16256 = 127 * 128
-            const int h = (q + 64) >> 7;              // -127 .. 127
-            const int l = q - (h << 7);               // -64 .. 63
-            hi[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
-            lo[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
+            int l0, l1, l2;
+            split_limbs(__float2int_rn(v[i] * s), l0, l1, l2);
+            w[0][i >> 2] |= (uint32_t)(l0 & 0xFF) << (8 * (i & 3));
+            w[1][i >> 2] |= (uint32_t)(l1 & 0xFF) << (8 * (i & 3));
+            w[2][i >> 2] |= (uint32_t)(l2 & 0xFF) << (8 * (i & 3));
         }
         if (valid) {
             const int b = p >> 2, j = p & 3;
-            uint8_t* dst = limbs + ((size_t)(n * nb + b) * 2) * 32 + j * 8;
-            *reinterpret_cast<uint2*>(dst) = make_uint2(hi[0], hi[1]);
-            *reinterpret_cast<uint2*>(dst + 32) = make_uint2(lo[0], lo[1]);
-            const float f = mx * (1.0f / 16256.0f);
-            if (G == 32) {
-                if (j == 0) *reinterpret_cast<float2*>(fs + (size_t)(n * nb + b) * 2) = make_float2(f, sm * sum_mul);
+            const float f = mx * (1.0f / 2080768.0f);
+            if (!MANY) {
+                uint8_t* dst = img.limbs + (size_t)b * 96 + j * 8;
+#pragma unroll
+                for (int L = 0; L < 3; L++) *reinterpret_cast<uint2*>(dst + L * 32) = make_uint2(w[L][0], w[L][1]);
+                if (G == 32) {
+                    if (j == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 2) = make_float2(f, sm * sum_mul);
+                } else {
+                    if ((j & 1) == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 4 + (j >> 1) * 2) = make_float2(f, sm * sum_mul);
+                }
             } else {
-                if ((j & 1) == 0) *reinterpret_cast<float2*>(fs + (size_t)(n * nb + b) * 4 + (j >> 1) * 2) = make_float2(f, sm * sum_mul);
+                const int h = b >> 2, sb = b & 3;
+                // values 8 j .. 8 j + 3 belong to lane t = (2 j) & 3, values 8 j + 4 .. to lane t + 1; j < 2: first
+                // half of the sub-block (b0 of the fragment), else second half (b1)
+                const int t0 = (2 * j) & 3, half = j >> 1;
+                uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + t0) * 96 + sb * 24 + half * 4;
+#pragma unroll
+                for (int L = 0; L < 3; L++) {
+                    *reinterpret_cast<uint32_t*>(dst + L * 8) = w[L][0];
+                    *reinterpret_cast<uint32_t*>(dst + 96 + L * 8) = w[L][1];
+                }
+                if (G == 32) {
+                    if (j == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)b * mp + n) * 2) = make_float2(f, sm * sum_mul);
+                } else {
+                    if ((j & 1) == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)(b * 2 + (j >> 1)) * mp + n) * 2) = make_float2(f, sm * sum_mul);
+                }
             }
         }
     }
 }
 
-// Per-lane addressing of the B operand and of the group factors. Lanes g == 2t (hi limbs) and g == 2t+1 (lo limbs)
-// read the limbs of thread t's block; all other lanes read the zero region with stride 0, so no load is predicated.
-struct LaneB {
-    uint32_t b0;         // shared address of the limbs of block (h = 0, this lane's t), or of the zero region
-    int bh, bn;          // byte steps per item (4 blocks) and per activation row
-    uint32_t f0;         // shared address of the factors of block (h = 0, t)
-    int fh, fn;          // byte steps per item and per activation row
+// bytes of the image of a product with inner dimension k and m rows (limbs, then factors)
+__host__ __device__ inline size_t act_limb_bytes(int k, int m) { return (size_t)(k >> 5) * 96 * m; }
+__host__ __device__ inline size_t act_image_bytes(int kind, int k, int m) {
+    const int mp = m == 1 ? 1 : (m + 1) & ~1;
+    return act_limb_bytes(k, m) + (size_t)(k >> 5) * mp * (kind == DK_Q6K ? 16 : 8) + 16;
+}
+
+// chunk (g, s) of a 512-byte code area: 16 bytes of row g (or g + 8), sub-block s. Both access patterns -- one
+// lane per chunk (16-byte loads) and four lanes per chunk (4-byte loads, fixed s) -- hit every bank once.
+__device__ __forceinline__ int chunk_pos(int g, int s) { return 8 * s + ((g + 2 * s) & 7); }
+
+// Per-lane addressing of the one-row B operand. Lanes g == 2t (limb 0) and g == 2t+1 (limb 1) read the limbs of
+// thread t's block for the first pass, lane g == 2t limb 2 for the second; all other lanes read the zero region
+// with stride 0, so no load is predicated.
+struct LaneB1 {
+    uint32_t p1, p2;     // shared addresses for item 0 (first / second pass)
+    int s1, s2;          // byte steps per item
+    uint32_t f0;         // factors of block t of item 0
+    int fh;              // byte step per item
 };
 
 template <int G>
-__device__ __forceinline__ LaneB lane_b(const ActImg& a, const uint8_t* zero, int lane) {
+__device__ __forceinline__ LaneB1 lane_b1(const ActImg& a, const uint8_t* zero, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    const bool active = (g >> 1) == t;
-    LaneB r;
-    r.b0 = active ? smem_addr(a.limbs) + t * 64 + (g & 1) * 32 : smem_addr(zero);
-    r.bh = active ? 256 : 0;
-    r.bn = active ? a.nb * 64 : 0;
-    constexpr int FPB = G == 32 ? 8 : 16;   // bytes of factors per block
+    const bool a1 = (g >> 1) == t, a2 = g == 2 * t;
+    LaneB1 r;
+    const uint32_t base = smem_addr(a.limbs) + t * 96;
+    r.p1 = a1 ? base + (g & 1) * 32 : smem_addr(zero);
+    r.p2 = a2 ? base + 64 : smem_addr(zero);
+    r.s1 = a1 ? 384 : 0;
+    r.s2 = a2 ? 384 : 0;
+    constexpr int FPB = G == 32 ? 8 : 16;
     r.f0 = smem_addr(a.fs) + t * FPB;
     r.fh = 4 * FPB;
-    r.fn = a.nb * FPB;
     return r;
 }
 
+// Many-row kernel: lane (g, t) supplies column g = activation row g of the B fragment.
+struct LaneBM {
+    uint32_t p;          // shared address of the lane's 96 bytes of item 0, or of the zero region
+    int sh;              // byte step per item
+    uint32_t f0;         // factors {f, s} of rows 2t, 2t+1 for block 0
+    int fb;              // byte step per block (G = 32) or per group (G = 16)
+};
+
+__device__ __forceinline__ LaneBM lane_bm(const ActImg& a, const uint8_t* zero, int lane, int m) {
+    const int g = lane >> 2, t = lane & 3;
+    const int mp = (m + 1) & ~1;
+    LaneBM r;
+    const bool act = g < m;
+    r.p = act ? smem_addr(a.limbs) + (g * 4 + t) * 96 : smem_addr(zero);
+    r.sh = act ? m * 384 : 0;
+    // rows 2t, 2t+1 past the padded row count read the zero region too (their outputs are never stored)
+    const bool fact = 2 * t < mp;
+    r.f0 = fact ? smem_addr(a.fs) + 2 * t * 8 : smem_addr(zero);
+    r.fb = fact ? mp * 8 : 0;
+    return r;
+}
+
+__device__ __forceinline__ void mma_k16_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};\n"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
 // ------------------------------------------------------------------------------------------- Q4_K (GGUF)
-// acc += d * sc * (factor * sum q x_int) - dmin * m * (sum x) for the lane's sub-block of rows g and g+8.
-template <int MT>
-__device__ __forceinline__ void item_q4k(uint32_t it, const LaneB& lb, int h, int m, float (&acc)[2][MT], int lane) {
-    const int g = lane >> 2;
-    const uint4 wa = lds128(it + lane * 16);
-    const uint4 wb = lds128(it + 512 + lane * 16);
+// One row: acc += d * sc * (factor * sum q x_int) - dmin * m * (sum x) for the lane's sub-block of rows g, g+8.
+__device__ __forceinline__ void item_q4k_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int cp = chunk_pos(g, t) * 16;
+    const uint4 wa = lds128(it + cp);
+    const uint4 wb = lds128(it + 512 + cp);
     const uint32_t hs = lds32(it + 1024 + lane * 4);
+    const uint2 dd = lds64(it + 1152 + g * 8);
+    const uint4 q0 = lds128(lb.p1 + h * lb.s1), q1 = lds128(lb.p1 + h * lb.s1 + 16);
+    const uint4 r0 = lds128(lb.p2 + h * lb.s2), r1 = lds128(lb.p2 + h * lb.s2 + 16);
+    const uint2 fSb = lds64(lb.f0 + h * lb.fh);
+    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
+    const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
+    constexpr uint32_t ML = 0x0F0F0F0Fu;
+    const uint32_t a[2][4] = {{wa.x & ML, wa.y & ML, wa.z & ML, wa.w & ML}, {wb.x & ML, wb.y & ML, wb.z & ML, wb.w & ML}};
+    const uint32_t b[2][4] = {{(wa.x >> 4) & ML, (wa.y >> 4) & ML, (wa.z >> 4) & ML, (wa.w >> 4) & ML},
+                              {(wb.x >> 4) & ML, (wb.y >> 4) & ML, (wb.z >> 4) & ML, (wb.w >> 4) & ML}};
+    int c[4], e[4];   // c: columns (limb 0, limb 1); e: columns (limb 2, zero)
+    mma_u8s8_z(c, a[0][0], a[1][0], a[0][1], a[1][1], q0.x, q0.y);
+    mma_u8s8_z(e, a[0][0], a[1][0], a[0][1], a[1][1], r0.x, r0.y);
+    mma_u8s8(c, a[0][2], a[1][2], a[0][3], a[1][3], q0.z, q0.w);
+    mma_u8s8(e, a[0][2], a[1][2], a[0][3], a[1][3], r0.z, r0.w);
+    mma_u8s8(c, b[0][0], b[1][0], b[0][1], b[1][1], q1.x, q1.y);
+    mma_u8s8(e, b[0][0], b[1][0], b[0][1], b[1][1], r1.x, r1.y);
+    mma_u8s8(c, b[0][2], b[1][2], b[0][3], b[1][3], q1.z, q1.w);
+    mma_u8s8(e, b[0][2], b[1][2], b[0][3], b[1][3], r1.z, r1.w);
+    const int v0 = (c[0] * 128 + c[1]) * 128 + e[0];
+    const int v1 = (c[2] * 128 + c[3]) * 128 + e[2];
+    const float f = __uint_as_float(fSb.x), S = __uint_as_float(fSb.y);
+    const float A0 = d0.x * (float)(hs & 0xFFu), B0 = -d0.y * (float)((hs >> 8) & 0xFFu);
+    const float A1 = d1.x * (float)((hs >> 16) & 0xFFu), B1 = -d1.y * (float)(hs >> 24);
+    acc[0] = fmaf(A0, (float)v0 * f, fmaf(B0, S, acc[0]));
+    acc[1] = fmaf(A1, (float)v1 * f, fmaf(B1, S, acc[1]));
+}
+
+// Many rows: one MMA per sub-block and limb, the activation rows are the MMA's columns; lane (g, t) ends up with
+// rows g, g+8 x activation rows 2t, 2t+1.  acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}
+__device__ __forceinline__ void item_q4k_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint4 hdr = lds128(it + 1024 + g * 16);
     const uint2 dd = lds64(it + 1152 + g * 8);
     const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
     const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
-    const float A0 = d0.x * (float)(hs & 0xFFu), B0 = -d0.y * (float)((hs >> 8) & 0xFFu);
-    const float A1 = d1.x * (float)((hs >> 16) & 0xFFu), B1 = -d1.y * (float)(hs >> 24);
-    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
-    const uint32_t bp = lb.b0 + h * lb.bh;
-    const uint32_t fp = lb.f0 + h * lb.fh;
+    const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
+    const uint32_t bp = lb.p + h * lb.sh;
+    constexpr uint32_t ML = 0x0F0F0F0Fu;
 #pragma unroll
-    for (int n = 0; n < MT; n++) {
-        if (n < m) {
-            const uint4 q0 = lds128(bp + n * lb.bn);
-            const uint4 q1 = lds128(bp + n * lb.bn + 16);
-            const uint2 fSb = lds64(fp + n * lb.fn);
-            const float2 fS = make_float2(__uint_as_float(fSb.x), __uint_as_float(fSb.y));
-            int cl[4], ch[4];
-            mma_u8s8_z(cl, wa.x & ML, wb.x & ML, wa.y & ML, wb.y & ML, q0.x, q0.y);
-            mma_u8s8(cl, wa.z & ML, wb.z & ML, wa.w & ML, wb.w & ML, q0.z, q0.w);
-            mma_u8s8_z(ch, wa.x & MH, wb.x & MH, wa.y & MH, wb.y & MH, q1.x, q1.y);
-            mma_u8s8(ch, wa.z & MH, wb.z & MH, wa.w & MH, wb.w & MH, q1.z, q1.w);
-            // columns (hi limb, lo limb): value = 128 hi + lo; the high-nibble sums carry a factor 16
-            const int v0 = cl[0] * 128 + cl[1] + ((ch[0] * 128 + ch[1]) >> 4);
-            const int v1 = cl[2] * 128 + cl[3] + ((ch[2] * 128 + ch[3]) >> 4);
-            acc[0][n] = fmaf(A0, (float)v0 * fS.x, fmaf(B0, fS.y, acc[0][n]));
-            acc[1][n] = fmaf(A1, (float)v1 * fS.x, fmaf(B1, fS.y, acc[1][n]));
-        }
+    for (int s = 0; s < 4; s++) {
+        const int cp = chunk_pos(g, s) * 16 + 4 * t;
+        const uint32_t w0 = lds32(it + cp), w1 = lds32(it + 512 + cp);
+        const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
+        const uint4 fSb = lds128(lb.f0 + (4 * h + s) * lb.fb);
+        const uint32_t a0 = w0 & ML, a1 = w1 & ML, a2 = (w0 >> 4) & ML, a3 = (w1 >> 4) & ML;
+        int c0[4], c1[4], c2[4];
+        mma_u8s8_z(c0, a0, a1, a2, a3, b0.x, b0.y);
+        mma_u8s8_z(c1, a0, a1, a2, a3, b1.x, b1.y);
+        mma_u8s8_z(c2, a0, a1, a2, a3, b2.x, b2.y);
+        const float A0 = d0.x * (float)(hw[s] & 0xFFu), B0 = -d0.y * (float)((hw[s] >> 8) & 0xFFu);
+        const float A1 = d1.x * (float)((hw[s] >> 16) & 0xFFu), B1 = -d1.y * (float)(hw[s] >> 24);
+        const float fa = __uint_as_float(fSb.x), Sa = __uint_as_float(fSb.y), fb = __uint_as_float(fSb.z), Sb = __uint_as_float(fSb.w);
+        const float v0 = (float)((c0[0] * 128 + c1[0]) * 128 + c2[0]), v1 = (float)((c0[1] * 128 + c1[1]) * 128 + c2[1]);
+        const float v2 = (float)((c0[2] * 128 + c1[2]) * 128 + c2[2]), v3 = (float)((c0[3] * 128 + c1[3]) * 128 + c2[3]);
+        acc[0] = fmaf(A0, v0 * fa, fmaf(B0, Sa, acc[0]));
+        acc[1] = fmaf(A0, v1 * fb, fmaf(B0, Sb, acc[1]));
+        acc[2] = fmaf(A1, v2 * fa, fmaf(B1, Sa, acc[2]));
+        acc[3] = fmaf(A1, v3 * fb, fmaf(B1, Sb, acc[3]));
     }
 }
 
 // ------------------------------------------------------------------------------------------- Q6_K (GGUF)
-// acc += d * sc * (factor * sum q x_int - 32 sum x) per 16 weights (the image stores 32 sum x).
-template <int MT>
-__device__ __forceinline__ void item_q6k(uint32_t it, const LaneB& lb, int h, int m, float (&acc)[2][MT], int lane) {
-    const int g = lane >> 2;
-    const uint4 wa = lds128(it + lane * 16);
-    const uint4 wb = lds128(it + 512 + lane * 16);
-    const uint4 hq = lds128(it + 1024 + lane * 16);
+// One row: acc += d * sc * (factor * sum q x_int - 32 sum x) per 16 weights (the image stores 32 sum x).
+__device__ __forceinline__ void item_q6k_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int cp = chunk_pos(g, t) * 16;
+    const uint4 wa = lds128(it + cp);
+    const uint4 wb = lds128(it + 512 + cp);
+    const uint4 hq = lds128(it + 1024 + cp);
     const uint32_t hs = lds32(it + 1536 + lane * 4);
     const uint32_t dd = lds32(it + 1664 + g * 4);
+    const uint4 q0 = lds128(lb.p1 + h * lb.s1), q1 = lds128(lb.p1 + h * lb.s1 + 16);
+    const uint4 r0 = lds128(lb.p2 + h * lb.s2), r1 = lds128(lb.p2 + h * lb.s2 + 16);
+    const uint4 fSb = lds128(lb.f0 + h * lb.fh);
     const float2 d01 = __half22float2(*reinterpret_cast<const __half2*>(&dd));
-    // scale of the low group, and a quarter of the scale of the high group (its codes are kept as 4 q)
-    const float D00 = d01.x * (float)(int)(int8_t)(hs & 0xFFu), D01 = d01.x * 0.25f * (float)(int)(int8_t)((hs >> 8) & 0xFFu);
-    const float D10 = d01.y * (float)(int)(int8_t)((hs >> 16) & 0xFFu), D11 = d01.y * 0.25f * (float)(int)(int8_t)(hs >> 24);
     constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u, M45 = 0x30303030u, M23 = 0x0C0C0C0Cu;
-    uint32_t A[2][4], B[2][4];   // [row][nibble word]
+    uint32_t A[2][4], B[2][4];   // [row][nibble word]; B holds 4 q
     {
         const uint32_t w[2][4] = {{wa.x, wa.y, wa.z, wa.w}, {wb.x, wb.y, wb.z, wb.w}};
         const uint32_t q[2][2] = {{hq.x, hq.y}, {hq.z, hq.w}};
@@ -280,26 +394,67 @@ __device__ __forceinline__ void item_q6k(uint32_t it, const LaneB& lb, int h, in
             }
         }
     }
-    const uint32_t bp = lb.b0 + h * lb.bh;
-    const uint32_t fp = lb.f0 + h * lb.fh;
+    int cl[4], el[4], ch[4], eh[4];
+    mma_u8s8_z(cl, A[0][0], A[1][0], A[0][1], A[1][1], q0.x, q0.y);
+    mma_u8s8_z(el, A[0][0], A[1][0], A[0][1], A[1][1], r0.x, r0.y);
+    mma_u8s8_z(ch, B[0][0], B[1][0], B[0][1], B[1][1], q1.x, q1.y);
+    mma_u8s8_z(eh, B[0][0], B[1][0], B[0][1], B[1][1], r1.x, r1.y);
+    mma_u8s8(cl, A[0][2], A[1][2], A[0][3], A[1][3], q0.z, q0.w);
+    mma_u8s8(el, A[0][2], A[1][2], A[0][3], A[1][3], r0.z, r0.w);
+    mma_u8s8(ch, B[0][2], B[1][2], B[0][3], B[1][3], q1.z, q1.w);
+    mma_u8s8(eh, B[0][2], B[1][2], B[0][3], B[1][3], r1.z, r1.w);
+    // the high group's sums carry the factor 4 of its codes: exact shifts before the limbs are combined
+    const float l0 = (float)((cl[0] * 128 + cl[1]) * 128 + el[0]), l1 = (float)((cl[2] * 128 + cl[3]) * 128 + el[2]);
+    const float h0 = (float)(((ch[0] >> 2) * 128 + (ch[1] >> 2)) * 128 + (eh[0] >> 2));
+    const float h1 = (float)(((ch[2] >> 2) * 128 + (ch[3] >> 2)) * 128 + (eh[2] >> 2));
+    const float D00 = d01.x * (float)(int)(int8_t)(hs & 0xFFu), D01 = d01.x * (float)(int)(int8_t)((hs >> 8) & 0xFFu);
+    const float D10 = d01.y * (float)(int)(int8_t)((hs >> 16) & 0xFFu), D11 = d01.y * (float)(int)(int8_t)(hs >> 24);
+    const float fl = __uint_as_float(fSb.x), Sl = __uint_as_float(fSb.y), fh = __uint_as_float(fSb.z), Sh = __uint_as_float(fSb.w);
+    acc[0] = fmaf(D00, fmaf(l0, fl, -Sl), fmaf(D01, fmaf(h0, fh, -Sh), acc[0]));
+    acc[1] = fmaf(D10, fmaf(l1, fl, -Sl), fmaf(D11, fmaf(h1, fh, -Sh), acc[1]));
+}
+
+// Many rows: per sub-block the low group (k-slots 0..15 of the lane's fragment words) and the high group are
+// separate k16 MMAs, one per limb.
+__device__ __forceinline__ void item_q6k_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint4 hdr = lds128(it + 1536 + g * 16);
+    const uint32_t dd = lds32(it + 1664 + g * 4);
+    const float2 d01 = __half22float2(*reinterpret_cast<const __half2*>(&dd));
+    const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
+    const uint32_t bp = lb.p + h * lb.sh;
+    const int sh = (t & 1) * 2;   // odd nibble words keep their high bits two positions further out
+    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u, M45 = 0x30303030u, M23 = 0x0C0C0C0Cu;
 #pragma unroll
-    for (int n = 0; n < MT; n++) {
-        if (n < m) {
-            const uint4 q0 = lds128(bp + n * lb.bn);
-            const uint4 q1 = lds128(bp + n * lb.bn + 16);
-            const uint4 fSb = lds128(fp + n * lb.fn);
-            const float4 fS = make_float4(__uint_as_float(fSb.x), __uint_as_float(fSb.y), __uint_as_float(fSb.z), __uint_as_float(fSb.w));
-            int cl[4], ch[4];
-            mma_u8s8_z(cl, A[0][0], A[1][0], A[0][1], A[1][1], q0.x, q0.y);
-            mma_u8s8(cl, A[0][2], A[1][2], A[0][3], A[1][3], q0.z, q0.w);
-            mma_u8s8_z(ch, B[0][0], B[1][0], B[0][1], B[1][1], q1.x, q1.y);
-            mma_u8s8(ch, B[0][2], B[1][2], B[0][3], B[1][3], q1.z, q1.w);
-            const float l0 = (float)(cl[0] * 128 + cl[1]), l1 = (float)(cl[2] * 128 + cl[3]);
-            const float h0 = (float)(ch[0] * 128 + ch[1]), h1 = (float)(ch[2] * 128 + ch[3]);
-            // high group: 4 q in the codes and a quarter scale, so its offset is 4 * 32 sum x
-            acc[0][n] = fmaf(D00, fmaf(l0, fS.x, -fS.y), fmaf(D01, fmaf(h0, fS.z, -4.0f * fS.w), acc[0][n]));
-            acc[1][n] = fmaf(D10, fmaf(l1, fS.x, -fS.y), fmaf(D11, fmaf(h1, fS.z, -4.0f * fS.w), acc[1][n]));
+    for (int s = 0; s < 4; s++) {
+        const int cpos = chunk_pos(g, s) * 16;
+        const uint32_t w0 = lds32(it + cpos + 4 * t), w1 = lds32(it + 512 + cpos + 4 * t);
+        const uint32_t h0 = lds32(it + 1024 + cpos + 4 * (t >> 1)), h1 = lds32(it + 1024 + cpos + 8 + 4 * (t >> 1));
+        const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
+        const uint4 fL = lds128(lb.f0 + (2 * (4 * h + s)) * lb.fb), fH = lds128(lb.f0 + (2 * (4 * h + s) + 1) * lb.fb);
+        const uint32_t aL0 = (w0 & ML) | ((h0 >> sh) & M45), aL1 = (w1 & ML) | ((h1 >> sh) & M45);
+        const uint32_t aH0 = (w0 & MH) | ((h0 << sh) & M23), aH1 = (w1 & MH) | ((h1 << sh) & M23);
+        int l0[4], l1[4], l2[4], g0[4], g1[4], g2[4];
+        mma_k16_u8s8_z(l0, aL0, aL1, b0.x);
+        mma_k16_u8s8_z(l1, aL0, aL1, b1.x);
+        mma_k16_u8s8_z(l2, aL0, aL1, b2.x);
+        mma_k16_u8s8_z(g0, aH0, aH1, b0.y);
+        mma_k16_u8s8_z(g1, aH0, aH1, b1.y);
+        mma_k16_u8s8_z(g2, aH0, aH1, b2.y);
+        const float DL0 = d01.x * (float)(int)(int8_t)(hw[s] & 0xFFu), DH0 = d01.x * (float)(int)(int8_t)((hw[s] >> 8) & 0xFFu);
+        const float DL1 = d01.y * (float)(int)(int8_t)((hw[s] >> 16) & 0xFFu), DH1 = d01.y * (float)(int)(int8_t)(hw[s] >> 24);
+        const float fLa = __uint_as_float(fL.x), SLa = __uint_as_float(fL.y), fLb = __uint_as_float(fL.z), SLb = __uint_as_float(fL.w);
+        const float fHa = __uint_as_float(fH.x), SHa = __uint_as_float(fH.y), fHb = __uint_as_float(fH.z), SHb = __uint_as_float(fH.w);
+        float vl[4], vh[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            vl[j] = (float)((l0[j] * 128 + l1[j]) * 128 + l2[j]);
+            vh[j] = (float)(((g0[j] >> 2) * 128 + (g1[j] >> 2)) * 128 + (g2[j] >> 2));
         }
+        acc[0] = fmaf(DL0, fmaf(vl[0], fLa, -SLa), fmaf(DH0, fmaf(vh[0], fHa, -SHa), acc[0]));
+        acc[1] = fmaf(DL0, fmaf(vl[1], fLb, -SLb), fmaf(DH0, fmaf(vh[1], fHb, -SHb), acc[1]));
+        acc[2] = fmaf(DL1, fmaf(vl[2], fLa, -SLa), fmaf(DH1, fmaf(vh[2], fHa, -SHa), acc[2]));
+        acc[3] = fmaf(DL1, fmaf(vl[3], fLb, -SLb), fmaf(DH1, fmaf(vh[3], fHb, -SHb), acc[3]));
     }
 }
 
@@ -361,54 +516,83 @@ __device__ __forceinline__ void ring_release(Ring& r) {
     r.inflight--;
 }
 
-template <int MT>
-__device__ __forceinline__ void quad_reduce(float (&acc)[2][MT]) {
-#pragma unroll
-    for (int n = 0; n < MT; n++) {
+// The four values a lane accumulates. One-row kernel: acc[0], acc[1] = its share of rows g, g+8 (the quad's four
+// shares are added at the end of a row tile). Many-row kernel: complete sums of (g, 2t), (g, 2t+1), (g+8, 2t),
+// (g+8, 2t+1).
+template <bool MANY>
+__device__ __forceinline__ void finish_acc(float (&acc)[4]) {
+    if (!MANY) {
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            float s = acc[i][n];
+            float s = acc[i];
             s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
             s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-            acc[i][n] = s;
+            acc[i] = s;
         }
     }
 }
 
-template <int MT>
-__device__ __forceinline__ void store_tile(const DOp& op, int prt, const float (&acc)[2][MT], int m, int lane) {
-    if ((lane & 3) != 0) return;
-    const int g = lane >> 2;
+template <bool MANY>
+__device__ __forceinline__ void store_tile(const DOp& op, int prt, const float (&acc)[4], int m, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    if (!MANY) {
+        if (t != 0) return;
 #pragma unroll
-    for (int n = 0; n < MT; n++) {
-        if (n < m) {
+        for (int i = 0; i < 2; i++) {
+            const int row = prt * 16 + g + 8 * i;
+            if (row < op.n_rows) {
+                op.y[row] = acc[i];
+                for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][row] = acc[i];
+            }
+        }
+    } else {
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int row = prt * 16 + g + 8 * i;
-                if (row < op.n_rows) {
-                    const float val = acc[i][n];
-                    op.y[(int64_t)n * op.ldy + row] = val;
-                    for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][(int64_t)n * op.ldy + row] = val;
-                }
+        for (int j = 0; j < 4; j++) {
+            const int row = prt * 16 + g + 8 * (j >> 1), n = 2 * t + (j & 1);
+            if (row < op.n_rows && n < m) {
+                op.y[(int64_t)n * op.ldy + row] = acc[j];
+                for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][(int64_t)n * op.ldy + row] = acc[j];
             }
         }
     }
 }
 
+// hand-over slot of a warp: 16 rows x 8 activation rows
+template <bool MANY>
+__device__ __forceinline__ void slot_write(float* red, int warp, const float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    float* s = red + warp * 128;
+    if (!MANY) {
+        if (t == 0) { s[g * 8] = acc[0]; s[(g + 8) * 8] = acc[1]; }
+    } else {
+        s[g * 8 + 2 * t] = acc[0]; s[g * 8 + 2 * t + 1] = acc[1];
+        s[(g + 8) * 8 + 2 * t] = acc[2]; s[(g + 8) * 8 + 2 * t + 1] = acc[3];
+    }
+}
+template <bool MANY>
+__device__ __forceinline__ void slot_add(const float* red, int warp, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const float* s = red + warp * 128;
+    if (!MANY) {
+        if (t == 0) { acc[0] += s[g * 8]; acc[1] += s[(g + 8) * 8]; }
+    } else {
+        acc[0] += s[g * 8 + 2 * t]; acc[1] += s[g * 8 + 2 * t + 1];
+        acc[2] += s[(g + 8) * 8 + 2 * t]; acc[3] += s[(g + 8) * 8 + 2 * t + 1];
+    }
+}
+
 constexpr long long WAIT_BUDGET = 2000000000ll;   // SM clock cycles (about a second)
 
-// One product segment: row tiles [rtb, rte) of `op` (product-local indices), consumed by the CTA's 8 warps.
+// One product segment: this warp's items [i0, i1) of the segment that starts at product row tile rtb.
 // Returns false when a bounded wait expired.
-template <int KIND, int MT>
-__device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int i1, Ring& ring, Stream& st, const LaneB& lb, int m,
-                                            float* red, float (&pend)[2][MT], int& pend_rt, int lane, int warp) {
+template <int KIND, bool MANY>
+__device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int i1, Ring& ring, Stream& st, const LaneB1& lb1,
+                                            const LaneBM& lbm, int m, float* red, float (&pend)[4], int& pend_rt, int lane, int warp) {
     const int nh = op.nh;
     int prt = rtb + i0 / nh;
     int h = i0 - (i0 / nh) * nh;
     bool mine = h == 0;
-    float acc[2][MT];
-#pragma unroll
-    for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int remaining = i1 - i0;
     pend_rt = -1;
     while (remaining > 0) {
@@ -418,22 +602,17 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
         if (!ok) return false;
         uint32_t it = ring.slot0 + ring.cslot * ring.slot_bytes;
         for (int c = 0; c < cnt; c++, it += op.item_bytes) {
-            if (KIND == DK_Q4K) item_q4k<MT>(it, lb, h, m, acc, lane);
-            else item_q6k<MT>(it, lb, h, m, acc, lane);
+            if (KIND == DK_Q4K) {
+                if (MANY) item_q4k_many(it, lbm, h, acc, lane); else item_q4k_one(it, lb1, h, acc, lane);
+            } else {
+                if (MANY) item_q6k_many(it, lbm, h, acc, lane); else item_q6k_one(it, lb1, h, acc, lane);
+            }
             if (++h == nh) {   // the row tile is complete as far as this warp is concerned
-                quad_reduce<MT>(acc);
-                if (mine) {
-                    store_tile<MT>(op, prt, acc, m, lane);
-                } else if ((lane & 3) == 0) {
-#pragma unroll
-                    for (int n = 0; n < MT; n++) {
-                        red[(warp * 16 + (lane >> 2)) * MT + n] = acc[0][n];
-                        red[(warp * 16 + (lane >> 2) + 8) * MT + n] = acc[1][n];
-                    }
-                }
+                finish_acc<MANY>(acc);
+                if (mine) store_tile<MANY>(op, prt, acc, m, lane);
+                else slot_write<MANY>(red, warp, acc, lane);
                 h = 0; prt++; mine = true;
-#pragma unroll
-                for (int n = 0; n < MT; n++) { acc[0][n] = 0.f; acc[1][n] = 0.f; }
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
             }
         }
         remaining -= cnt;
@@ -442,37 +621,34 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
         if (st.to_issue > 0) ring_issue(ring, st, lane);
     }
     if (h != 0) {   // the range ends inside a row tile
-        quad_reduce<MT>(acc);
+        finish_acc<MANY>(acc);
         if (mine) {   // this warp started it: it collects the other parts after the CTA has met
             pend_rt = prt;
-#pragma unroll
-            for (int n = 0; n < MT; n++) { pend[0][n] = acc[0][n]; pend[1][n] = acc[1][n]; }
-        } else if ((lane & 3) == 0) {
-#pragma unroll
-            for (int n = 0; n < MT; n++) {
-                red[(warp * 16 + (lane >> 2)) * MT + n] = acc[0][n];
-                red[(warp * 16 + (lane >> 2) + 8) * MT + n] = acc[1][n];
-            }
+            pend[0] = acc[0]; pend[1] = acc[1]; pend[2] = acc[2]; pend[3] = acc[3];
+        } else {
+            slot_write<MANY>(red, warp, acc, lane);
         }
     }
     return true;
 }
 
+template <int NW>
 __device__ __forceinline__ void warp_range(int items, int warp, int& i0, int& i1) {
-    i0 = (int)(((int64_t)items * warp) >> 3);
-    i1 = (int)(((int64_t)items * (warp + 1)) >> 3);
+    i0 = (int)(((int64_t)items * warp) / NW);
+    i1 = (int)(((int64_t)items * (warp + 1)) / NW);
 }
 
-template <int MT>
-__global__ void __launch_bounds__(256, 2)
+// NW warps per CTA; MANY = activation rows on the MMA's N side (m = 2..8), else the one-row block-diagonal form.
+template <int NW, bool MANY>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
 gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_rt, int m,
                int* status, int chunk, int depth, int slot_bytes) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* red = reinterpret_cast<float*>(smem + BAR_BYTES);
-    uint8_t* zero = smem + BAR_BYTES + RED_BYTES;
-    uint8_t* ring_base = smem + FIXED_BYTES;
-    uint8_t* ximg = ring_base + (size_t)8 * depth * slot_bytes;
+    float* red = reinterpret_cast<float*>(smem + bar_bytes(NW));
+    uint8_t* zero = smem + bar_bytes(NW) + red_bytes(NW);
+    uint8_t* ring_base = smem + fixed_bytes(NW);
+    uint8_t* ximg = ring_base + (size_t)NW * depth * slot_bytes;
 
     Ring ring;
     ring.bar0 = smem_addr(smem) + warp * MAX_DEPTH * 8;
@@ -521,7 +697,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         }
         seg_b = sb;
         seg_e = min(te, op.rt0 + op.nrt);
-        warp_range((seg_e - seg_b) * op.nh, warp, i0, i1);
+        warp_range<NW>((seg_e - seg_b) * op.nh, warp, i0, i1);
         st.src = op.img + ((int64_t)(seg_b - op.rt0) * op.nh + i0) * op.item_bytes;
         st.to_issue = i1 - i0;
         st.item_bytes = op.item_bytes;
@@ -537,28 +713,27 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         }
         __syncthreads();   // the previous segment's activations and hand-over slots are no longer read
         ActImg ai;
-        ai.nb = op.k >> 5;
         ai.limbs = ximg;
-        float* fs = reinterpret_cast<float*>(ximg + (size_t)m * ai.nb * 64);
-        ai.fs = fs;
-        LaneB lb;
+        ai.fs = reinterpret_cast<float*>(ximg + act_limb_bytes(op.k, m));
+        LaneB1 lb1{};
+        LaneBM lbm{};
         if (op.kind == DK_Q4K) {
-            prep_x<32>(op.x, op.ldx, op.k, m, ximg, fs, 1.0f);
-            lb = lane_b<32>(ai, zero, lane);
+            prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 1.0f);
+            if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
         } else {
-            prep_x<16>(op.x, op.ldx, op.k, m, ximg, fs, 32.0f);
-            lb = lane_b<16>(ai, zero, lane);
+            prep_x<16, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 32.0f);
+            if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<16>(ai, zero, lane);
         }
         __syncthreads();
 
-        float pend[2][MT];
+        float pend[4];
         int pend_rt = -1;
         const DOp cur = op;
         const int cur_b = seg_b - op.rt0, cur_items = (seg_e - seg_b) * op.nh, cur_i1 = i1;
         if (alive) {
             bool ok;
-            if (cur.kind == DK_Q4K) ok = run_segment<DK_Q4K, MT>(cur, cur_b, i0, i1, ring, st, lb, m, red, pend, pend_rt, lane, warp);
-            else ok = run_segment<DK_Q6K, MT>(cur, cur_b, i0, i1, ring, st, lb, m, red, pend, pend_rt, lane, warp);
+            if (cur.kind == DK_Q4K) ok = run_segment<DK_Q4K, MANY>(cur, cur_b, i0, i1, ring, st, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else ok = run_segment<DK_Q6K, MANY>(cur, cur_b, i0, i1, ring, st, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             if (!ok) {
                 alive = false;
                 if (lane == 0) atomicExch(status, 100 + warp);
@@ -573,20 +748,14 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             // parts of the pending row tile lie with the following warps, in order, until one reaches its end
             const int tile_end = (pend_rt - cur_b + 1) * cur.nh;
             int pos = cur_i1;
-            for (int w2 = warp + 1; w2 < 8 && pos < tile_end; w2++) {
+            for (int w2 = warp + 1; w2 < NW && pos < tile_end; w2++) {
                 int j0, j1;
-                warp_range(cur_items, w2, j0, j1);
+                warp_range<NW>(cur_items, w2, j0, j1);
                 if (j0 == j1) continue;
-                if ((lane & 3) == 0) {
-#pragma unroll
-                    for (int n = 0; n < MT; n++) {
-                        pend[0][n] += red[(w2 * 16 + (lane >> 2)) * MT + n];
-                        pend[1][n] += red[(w2 * 16 + (lane >> 2) + 8) * MT + n];
-                    }
-                }
+                slot_add<MANY>(red, w2, pend, lane);
                 pos = j1;
             }
-            store_tile<MT>(cur, pend_rt, pend, m, lane);
+            store_tile<MANY>(cur, pend_rt, pend, m, lane);
         }
     }
     // a wait that gave up leaves copies in flight: they must land before the CTA's shared memory is released
@@ -628,7 +797,7 @@ __global__ void __launch_bounds__(256) build_image_q4k_kernel(const uint8_t* __r
             hs |= (sc | (mn << 8)) << (16 * i);
             dd[i] = ld32(blk);
         }
-        *reinterpret_cast<uint4*>(it + 512 * i + lane * 16) = out;
+        *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = out;
     }
     *reinterpret_cast<uint32_t*>(it + 1024 + lane * 4) = hs;
     if (t == 0) *reinterpret_cast<uint2*>(it + 1152 + g * 8) = make_uint2(dd[0], dd[1]);
@@ -675,9 +844,9 @@ __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* 
             hs |= ((uint32_t)sc[0] | ((uint32_t)sc[1] << 8)) << (16 * i);
             dd |= (uint32_t)ld16(v.p[3] + blk * 2) << (16 * i);
         }
-        *reinterpret_cast<uint4*>(it + 512 * i + lane * 16) = out;
+        *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = out;
     }
-    *reinterpret_cast<uint4*>(it + 1024 + lane * 16) = make_uint4(hq[0], hq[1], hq[2], hq[3]);
+    *reinterpret_cast<uint4*>(it + 1024 + chunk_pos(g, t) * 16) = make_uint4(hq[0], hq[1], hq[2], hq[3]);
     *reinterpret_cast<uint32_t*>(it + 1536 + lane * 4) = hs;
     if (t == 0) *reinterpret_cast<uint32_t*>(it + 1664 + g * 4) = dd;
 }
@@ -731,16 +900,14 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
     return B200Q_OK;
 }
 
-size_t gemv_i8_image_smem(int kind, int k, int m) {
-    // limbs: 2 bytes per value; factors: 8 bytes per group of 32 (Q4_K) or 16 (Q6_K)
-    const size_t nb = (size_t)(k >> 5);
-    return (size_t)m * nb * 64 + (size_t)m * nb * (kind == DK_Q6K ? 16 : 8) + 16;
-}
+size_t gemv_i8_image_smem(int kind, int k, int m) { return act_image_bytes(kind, k, m); }
 
 bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaunch* out) {
     size_t image = 0;
     for (int kd = 0; kd < DK_COUNT; kd++)
-        if (kind_mask & (1 << kd)) image = max(image, gemv_i8_image_smem(kd, kmax, m));
+        if (kind_mask & (1 << kd)) image = max(image, act_image_bytes(kd, kmax, m));
+    // one activation row: 8 warps per CTA, two CTAs per SM; more rows: 16 warps, one CTA per SM (one image per SM)
+    const int nw = m == 1 ? 8 : 16;
     // tuning knob (like the reference's ROCFORGE_TILE_* variables, src/ggml/hip_backend/tuning.rs:237-275):
     // B200Q_DECODE_RING="items per copy,slots per warp"
     int chunk = 2, depth = 4;
@@ -748,27 +915,27 @@ bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaun
         int c = 0, d = 0;
         if (sscanf(e, "%d,%d", &c, &d) == 2 && c >= 1 && c <= 8 && d >= 2 && d <= MAX_DEPTH) { chunk = c; depth = d; }
     }
-    const size_t cap2 = 113 * 1024, cap1 = 226 * 1024;
-    for (;;) {
-        const int slot = ((chunk * max_item_bytes + 127) / 128) * 128;
-        const size_t total = FIXED_BYTES + (size_t)8 * depth * slot + image;
-        if (total <= cap2 || (total <= cap1 && depth <= 3)) {
-            out->chunk_items = chunk; out->depth = depth; out->slot_bytes = slot;
-            out->smem_bytes = total;
-            out->ctas_per_sm = total <= cap2 ? 2 : 1;
-            return true;
+    const size_t cap = nw == 8 ? 113 * 1024 : 226 * 1024, cap1 = 226 * 1024;
+    const size_t fixed = fixed_bytes(nw);
+    for (int pass = 0; pass < 2; pass++) {
+        // first pass: the preferred occupancy; second pass (8-warp form only): one CTA per SM
+        const size_t limit = pass == 0 ? cap : cap1;
+        int c = chunk, d = depth;
+        for (;;) {
+            const int slot = ((c * max_item_bytes + 127) / 128) * 128;
+            const size_t total = fixed + (size_t)nw * d * slot + image;
+            if (total <= limit) {
+                out->chunk_items = c; out->depth = d; out->slot_bytes = slot; out->smem_bytes = total;
+                out->ctas_per_sm = (nw == 8 && total <= 113 * 1024) ? 2 : 1;
+                out->nw = nw; out->many = m > 1;
+                return true;
+            }
+            if (d > 2) d--;
+            else if (c > 1) c--;
+            else break;
         }
-        if (total <= cap1 && FIXED_BYTES + (size_t)8 * 2 * slot + image > cap2) {
-            // two CTAs per SM are out of reach: keep the deep ring on one CTA
-            out->chunk_items = chunk; out->depth = depth; out->slot_bytes = slot;
-            out->smem_bytes = total;
-            out->ctas_per_sm = 1;
-            return true;
-        }
-        if (depth > 2) depth--;
-        else if (chunk > 1) chunk--;
-        else return false;
     }
+    return false;
 }
 
 bool gemv_i8_supported(const b200q_weight* w, int m) {
@@ -780,19 +947,18 @@ bool gemv_i8_supported(const b200q_weight* w, int m) {
 int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
                    int total_rt, int m, const DecodeLaunch& L) {
     if (total_rt <= 0) return B200Q_OK;
-    static bool configured[64][4] = {};
-    const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
-    const void* kernels[4] = {(const void*)gemv_i8_kernel<1>, (const void*)gemv_i8_kernel<2>, (const void*)gemv_i8_kernel<4>,
-                              (const void*)gemv_i8_kernel<8>};
-    if (!configured[ctx->device & 63][mi]) {
-        B200Q_CUDA(cudaFuncSetAttribute(kernels[mi], cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024), B200Q_ERR_LAUNCH);
-        configured[ctx->device & 63][mi] = true;
+    static bool configured[64][2] = {};
+    const int ki = L.many ? 1 : 0;
+    const void* kernels[2] = {(const void*)gemv_i8_kernel<8, false>, (const void*)gemv_i8_kernel<16, true>};
+    if (!configured[ctx->device & 63][ki]) {
+        B200Q_CUDA(cudaFuncSetAttribute(kernels[ki], cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024), B200Q_ERR_LAUNCH);
+        configured[ctx->device & 63][ki] = true;
     }
     DOp single{};
     if (h_single) single = *h_single;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)n_ctas);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(L.nw * 32);
     cfg.dynamicSmemBytes = L.smem_bytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -803,7 +969,7 @@ int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_
     int* status = ctx->d_status;
     int chunk = L.chunk_items, depth = L.depth, slot = L.slot_bytes;
     void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &total_rt, &m, &status, &chunk, &depth, &slot};
-    B200Q_CUDA(cudaLaunchKernelExC(&cfg, kernels[mi], args), B200Q_ERR_LAUNCH);
+    B200Q_CUDA(cudaLaunchKernelExC(&cfg, kernels[ki], args), B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     ctx->tc_pending = true;   // the next synchronise reads the status word
     return B200Q_OK;

@@ -38,6 +38,8 @@ struct DecodeLaunch {
     int slot_bytes;
     size_t smem_bytes;
     int ctas_per_sm;
+    int nw;            // warps per CTA
+    bool many;         // activation rows on the MMA's N side (m >= 2)
 };
 
 bool gemv_i8_supported(const b200q_weight* w, int m);
