@@ -112,6 +112,8 @@ int b200q_init_on_stream(int device, void* cuda_stream, b200q_ctx** out) {
     e = cudaMalloc(&ctx->d_status, sizeof(int) * 4);
     if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaMalloc(status)"); }
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int) * 4, ctx->stream);
+    e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_status), sizeof(int) * 4, cudaHostAllocDefault);
+    if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaHostAlloc(status)"); }
     *out = ctx;
     return B200Q_OK;
 }
@@ -127,6 +129,7 @@ void b200q_destroy(b200q_ctx* ctx) {
     if (ctx->scratch3) cudaFree(ctx->scratch3);
     if (ctx->sk_ws) cudaFree(ctx->sk_ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -180,6 +183,10 @@ int b200q_memcpy_d2h(b200q_ctx* ctx, void* h_dst, const void* d_src, size_t byte
     if (bytes == 0) return B200Q_OK;
     if (!h_dst || !d_src) return fail(B200Q_ERR_INVALID, "memcpy_d2h: null pointer");
     B200Q_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
+    if (ctx->tc_pending) {   // a caller that fetches results this way must still learn of an expired device-side wait
+        ctx->tc_pending = false;
+        return gemm_tc_check_status(ctx);
+    }
     B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_COPY);
     return B200Q_OK;
 }
@@ -194,11 +201,11 @@ int b200q_memset(b200q_ctx* ctx, void* d_dst, int value, size_t bytes) {
 
 int b200q_synchronize(b200q_ctx* ctx) {
     CTX_GUARD("synchronize");
-    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
-    if (ctx->tc_pending) {
+    if (ctx->tc_pending) {   // kernels that can report through the status words ran: read them behind the work
         ctx->tc_pending = false;
         return gemm_tc_check_status(ctx);
     }
+    B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
     return B200Q_OK;
 }
 

@@ -19,7 +19,8 @@ struct b200q_ctx {
     size_t scratch_bytes = 0;
     void* scratch2 = nullptr;
     size_t scratch2_bytes = 0;
-    int* d_status = nullptr;  // device word the tensor-core kernel reports bounded-wait failures in
+    int* d_status = nullptr;  // device words: [0] bounded-wait failures, [1] bad token ids, [2..3] work-unit counters of the decode kernel
+    int* h_status = nullptr;  // page-locked landing place of [0..1] when a synchronise reads them
     bool tc_pending = false;  // a tensor-core launch has not had its status word read yet
     void* scratch3 = nullptr; // f16 copy of the activations + row scales for the tensor-core path
     size_t scratch3_bytes = 0;

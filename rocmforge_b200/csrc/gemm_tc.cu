@@ -1883,14 +1883,16 @@ int launch_bounded_wait_selftest(b200q_ctx* ctx, long long budget_cycles) {
 // Reads and clears the launch status words: [0] a bounded wait of a tensor-core kernel expired (site code),
 // [1] token ids the embedding lookup found out of range.
 int gemm_tc_check_status(b200q_ctx* ctx) {
-    int h[2] = {0, 0};
-    B200Q_CUDA(cudaMemcpyAsync(h, ctx->d_status, sizeof(h), cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
+    // one small copy into page-locked memory and ONE synchronise: the copy rides the stream behind the kernels
+    int* h = ctx->h_status;
+    B200Q_CUDA(cudaMemcpyAsync(h, ctx->d_status, 2 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
     B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
-    if (h[0] != 0 || h[1] != 0) cudaMemsetAsync(ctx->d_status, 0, sizeof(h), ctx->stream);
-    if (h[0] != 0)
-        return fail(B200Q_ERR_TIMEOUT, "gemm: a bounded device-side wait expired (site %d); results of that launch are invalid", h[0]);
-    if (h[1] != 0)
-        return fail(B200Q_ERR_INVALID, "get_rows: %d token id(s) exceed the vocabulary size; their output rows were zero-filled", h[1]);
+    const int h0 = h[0], h1 = h[1];
+    if (h0 != 0 || h1 != 0) cudaMemsetAsync(ctx->d_status, 0, 2 * sizeof(int), ctx->stream);
+    if (h0 != 0)
+        return fail(B200Q_ERR_TIMEOUT, "a bounded device-side wait expired (site %d); results of that launch are invalid", h0);
+    if (h1 != 0)
+        return fail(B200Q_ERR_INVALID, "get_rows: %d token id(s) exceed the vocabulary size; their output rows were zero-filled", h1);
     return B200Q_OK;
 }
 

@@ -149,8 +149,9 @@ __device__ __forceinline__ void split_limbs(int q, int& l0, int& l1, int& l2) {
     l0 = (q1 - l1) >> 7;
 }
 
-// x[m, k] (fp32, global) -> image. 8 consecutive values per thread; the G / 8 lanes of a group agree on the
-// group's maximum and sum by shuffles. MANY selects the many-row layout.
+// x[m, k] (fp32, global) -> image. 8 consecutive values per thread and step, four steps' loads in flight at a time
+// (the activations usually come from HBM: the packed weights have pushed them out of L2); the G / 8 lanes of a
+// group agree on the group's maximum and sum by shuffles. MANY selects the many-row layout.
 template <int G, bool MANY, int NT>
 __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const ActImg& img, float sum_mul) {
     const int units = k >> 3;
@@ -161,66 +162,76 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
         const int groups = nb * (G == 32 ? 1 : 2);
         for (int i = threadIdx.x; i < groups; i += NT) *reinterpret_cast<float2*>(img.fs + ((size_t)i * mp + m) * 2) = make_float2(0.f, 0.f);
     }
-    for (int u0 = 0; u0 < total; u0 += NT) {
-        const int u = u0 + threadIdx.x;
-        const bool valid = u < total;
-        const int n = valid ? u / units : 0;
-        const int p = valid ? u - n * units : 0;
-        float v[8];
-        if (valid) {
-            const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)p * 8);
-            const float4 a = __ldg(xp), b = __ldg(xp + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        } else {
+    constexpr int B = 4;
+    for (int u0 = 0; u0 < total; u0 += B * NT) {
+        float4 xa[B], xb[B];
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = 0.0f;
+        for (int j = 0; j < B; j++) {
+            const int u = u0 + j * NT + threadIdx.x;
+            xa[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            xb[j] = xa[j];
+            if (u < total) {
+                const int n = u / units, p = u - n * units;
+                const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)n * ldx + (int64_t)p * 8);
+                xa[j] = __ldg(xp);
+                xb[j] = __ldg(xp + 1);
+            }
         }
-        float mx = 0.0f, sm = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) { mx = fmaxf(mx, fabsf(v[i])); sm += v[i]; }
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-        sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
-        if (G == 32) {
-            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-            sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
-        }
-        const float s = mx > 0.0f ? 2080768.0f / mx : 0.0f;   // 16256 * 128
-        uint32_t w[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+        for (int j = 0; j < B; j++) {
+            if (u0 + j * NT >= total) break;   // uniform: the whole step is past the end
+            const int u = u0 + j * NT + threadIdx.x;
+            const bool valid = u < total;
+            const int n = valid ? u / units : 0;
+            const int p = valid ? u - n * units : 0;
+            const float v[8] = {xa[j].x, xa[j].y, xa[j].z, xa[j].w, xb[j].x, xb[j].y, xb[j].z, xb[j].w};
+            float mx = 0.0f, sm = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            int l0, l1, l2;
-            split_limbs(__float2int_rn(v[i] * s), l0, l1, l2);
-            w[0][i >> 2] |= (uint32_t)(l0 & 0xFF) << (8 * (i & 3));
-            w[1][i >> 2] |= (uint32_t)(l1 & 0xFF) << (8 * (i & 3));
-            w[2][i >> 2] |= (uint32_t)(l2 & 0xFF) << (8 * (i & 3));
-        }
-        if (valid) {
-            const int b = p >> 2, j = p & 3;
-            const float f = mx * (1.0f / 2080768.0f);
-            if (!MANY) {
-                uint8_t* dst = img.limbs + (size_t)b * 96 + j * 8;
+            for (int i = 0; i < 8; i++) { mx = fmaxf(mx, fabsf(v[i])); sm += v[i]; }
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
+            if (G == 32) {
+                mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+                sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
+            }
+            const float s = mx > 0.0f ? 2080768.0f / mx : 0.0f;   // 16256 * 128
+            uint32_t w[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
 #pragma unroll
-                for (int L = 0; L < 3; L++) *reinterpret_cast<uint2*>(dst + L * 32) = make_uint2(w[L][0], w[L][1]);
-                if (G == 32) {
-                    if (j == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 2) = make_float2(f, sm * sum_mul);
+            for (int i = 0; i < 8; i++) {
+                int l0, l1, l2;
+                split_limbs(__float2int_rn(v[i] * s), l0, l1, l2);
+                w[0][i >> 2] |= (uint32_t)(l0 & 0xFF) << (8 * (i & 3));
+                w[1][i >> 2] |= (uint32_t)(l1 & 0xFF) << (8 * (i & 3));
+                w[2][i >> 2] |= (uint32_t)(l2 & 0xFF) << (8 * (i & 3));
+            }
+            if (valid) {
+                const int b = p >> 2, jj = p & 3;
+                const float f = mx * (1.0f / 2080768.0f);
+                if (!MANY) {
+                    uint8_t* dst = img.limbs + (size_t)b * 96 + jj * 8;
+#pragma unroll
+                    for (int L = 0; L < 3; L++) *reinterpret_cast<uint2*>(dst + L * 32) = make_uint2(w[L][0], w[L][1]);
+                    if (G == 32) {
+                        if (jj == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 2) = make_float2(f, sm * sum_mul);
+                    } else {
+                        if ((jj & 1) == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 4 + (jj >> 1) * 2) = make_float2(f, sm * sum_mul);
+                    }
                 } else {
-                    if ((j & 1) == 0) *reinterpret_cast<float2*>(img.fs + (size_t)b * 4 + (j >> 1) * 2) = make_float2(f, sm * sum_mul);
-                }
-            } else {
-                const int h = b >> 2, sb = b & 3;
-                // values 8 j .. 8 j + 3 belong to lane t = (2 j) & 3, values 8 j + 4 .. to lane t + 1; j < 2: first
-                // half of the sub-block (b0 of the fragment), else second half (b1)
-                const int t0 = (2 * j) & 3, half = j >> 1;
-                uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + t0) * 96 + sb * 24 + half * 4;
+                    const int h = b >> 2, sb = b & 3;
+                    // values 8 jj .. 8 jj + 3 belong to lane t = (2 jj) & 3, values 8 jj + 4 .. to lane t + 1; jj < 2:
+                    // first half of the sub-block (b0 of the fragment), else second half (b1)
+                    const int t0 = (2 * jj) & 3, half = jj >> 1;
+                    uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + t0) * 96 + sb * 24 + half * 4;
 #pragma unroll
-                for (int L = 0; L < 3; L++) {
-                    *reinterpret_cast<uint32_t*>(dst + L * 8) = w[L][0];
-                    *reinterpret_cast<uint32_t*>(dst + 96 + L * 8) = w[L][1];
-                }
-                if (G == 32) {
-                    if (j == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)b * mp + n) * 2) = make_float2(f, sm * sum_mul);
-                } else {
-                    if ((j & 1) == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)(b * 2 + (j >> 1)) * mp + n) * 2) = make_float2(f, sm * sum_mul);
+                    for (int L = 0; L < 3; L++) {
+                        *reinterpret_cast<uint32_t*>(dst + L * 8) = w[L][0];
+                        *reinterpret_cast<uint32_t*>(dst + 96 + L * 8) = w[L][1];
+                    }
+                    if (G == 32) {
+                        if (jj == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)b * mp + n) * 2) = make_float2(f, sm * sum_mul);
+                    } else {
+                        if ((jj & 1) == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)(b * 2 + (jj >> 1)) * mp + n) * 2) = make_float2(f, sm * sum_mul);
+                    }
                 }
             }
         }
@@ -424,7 +435,7 @@ __device__ __forceinline__ void item_q6k_many(uint32_t it, const LaneBM& lb, int
     const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
     const uint32_t bp = lb.p + h * lb.sh;
     const int sh = (t & 1) * 2;   // odd nibble words keep their high bits two positions further out
-    constexpr uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u, M45 = 0x30303030u, M23 = 0x0C0C0C0Cu;
+    constexpr uint32_t ML = 0x0F0F0F0Fu, M45 = 0x30303030u, M2345 = 0x3C3C3C3Cu, M01 = 0x03030303u;
 #pragma unroll
     for (int s = 0; s < 4; s++) {
         const int cpos = chunk_pos(g, s) * 16;
@@ -433,7 +444,8 @@ __device__ __forceinline__ void item_q6k_many(uint32_t it, const LaneBM& lb, int
         const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
         const uint4 fL = lds128(lb.f0 + (2 * (4 * h + s)) * lb.fb), fH = lds128(lb.f0 + (2 * (4 * h + s) + 1) * lb.fb);
         const uint32_t aL0 = (w0 & ML) | ((h0 >> sh) & M45), aL1 = (w1 & ML) | ((h1 >> sh) & M45);
-        const uint32_t aH0 = (w0 & MH) | ((h0 << sh) & M23), aH1 = (w1 & MH) | ((h1 << sh) & M23);
+        // high group as plain codes: the nibble holds q >> 2, the 2-bit field q & 3
+        const uint32_t aH0 = ((w0 >> 2) & M2345) | ((h0 >> (2 - sh)) & M01), aH1 = ((w1 >> 2) & M2345) | ((h1 >> (2 - sh)) & M01);
         int l0[4], l1[4], l2[4], g0[4], g1[4], g2[4];
         mma_k16_u8s8_z(l0, aL0, aL1, b0.x);
         mma_k16_u8s8_z(l1, aL0, aL1, b1.x);
@@ -449,7 +461,7 @@ __device__ __forceinline__ void item_q6k_many(uint32_t it, const LaneBM& lb, int
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             vl[j] = (float)((l0[j] * 128 + l1[j]) * 128 + l2[j]);
-            vh[j] = (float)(((g0[j] >> 2) * 128 + (g1[j] >> 2)) * 128 + (g2[j] >> 2));
+            vh[j] = (float)((g0[j] * 128 + g1[j]) * 128 + g2[j]);
         }
         acc[0] = fmaf(DL0, fmaf(vl[0], fLa, -SLa), fmaf(DH0, fmaf(vh[0], fHa, -SHa), acc[0]));
         acc[1] = fmaf(DL0, fmaf(vl[1], fLb, -SLb), fmaf(DH0, fmaf(vh[1], fHb, -SHb), acc[1]));
@@ -583,10 +595,11 @@ __device__ __forceinline__ void slot_add(const float* red, int warp, float (&acc
 
 constexpr long long WAIT_BUDGET = 2000000000ll;   // SM clock cycles (about a second)
 
-// One product segment: this warp's items [i0, i1) of the segment that starts at product row tile rtb.
-// Returns false when a bounded wait expired.
+// One product segment: this warp's items [i0, i1) of the segment that starts at product row tile rtb. When the
+// warp's own stream is exhausted the ring goes on with `nx`, the warp's share of the NEXT segment, so the copies
+// never pause at a segment boundary. Returns false when a bounded wait expired.
 template <int KIND, bool MANY>
-__device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int i1, Ring& ring, Stream& st, const LaneB1& lb1,
+__device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int i1, Ring& ring, Stream& st, Stream& nx, const LaneB1& lb1,
                                             const LaneBM& lbm, int m, float* red, float (&pend)[4], int& pend_rt, int lane, int warp) {
     const int nh = op.nh;
     int prt = rtb + i0 / nh;
@@ -595,13 +608,15 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int remaining = i1 - i0;
     pend_rt = -1;
+    const int item_bytes = op.item_bytes;
+    while (ring.inflight < ring.depth && st.to_issue == 0 && nx.to_issue > 0) ring_issue(ring, nx, lane);
     while (remaining > 0) {
         const int cnt = min(ring.chunk, remaining);
         bool ok = ring_wait(ring, WAIT_BUDGET);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) return false;
         uint32_t it = ring.slot0 + ring.cslot * ring.slot_bytes;
-        for (int c = 0; c < cnt; c++, it += op.item_bytes) {
+        for (int c = 0; c < cnt; c++, it += item_bytes) {
             if (KIND == DK_Q4K) {
                 if (MANY) item_q4k_many(it, lbm, h, acc, lane); else item_q4k_one(it, lb1, h, acc, lane);
             } else {
@@ -619,6 +634,7 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
         __syncwarp();   // every lane has read the slot before it is refilled
         ring_release(ring);
         if (st.to_issue > 0) ring_issue(ring, st, lane);
+        else if (nx.to_issue > 0) ring_issue(ring, nx, lane);
     }
     if (h != 0) {   // the range ends inside a row tile
         finish_acc<MANY>(acc);
@@ -638,12 +654,21 @@ __device__ __forceinline__ void warp_range(int items, int warp, int& i0, int& i1
     i1 = (int)(((int64_t)items * (warp + 1)) / NW);
 }
 
+// A segment: row tiles [b, e) (launch-wide indices) of the product in `slot` of the descriptor cache.
+struct Seg {
+    int b, e;     // launch-wide row tiles
+    int opi;      // index of the product
+    int ub, ue;   // the work unit the segment belongs to
+};
+
 // NW warps per CTA; MANY = activation rows on the MMA's N side (m = 2..8), else the one-row block-diagonal form.
 template <int NW, bool MANY>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
-gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int total_rt, int m,
-               int* status, int chunk, int depth, int slot_bytes) {
+gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int n_units, int total_rt, int m,
+               int* status, int* sched, int chunk, int depth, int slot_bytes) {
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ DOp s_op[3];    // descriptors of the previous, the current and the next segment's product
+    __shared__ int s_next;     // next work unit of the CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* red = reinterpret_cast<float*>(smem + bar_bytes(NW));
     uint8_t* zero = smem + bar_bytes(NW) + red_bytes(NW);
@@ -660,58 +685,107 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
     if (threadIdx.x < ZERO_BYTES / 4) reinterpret_cast<uint32_t*>(zero)[threadIdx.x] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
 
-    int tb, te;
-    if (ranges) {
-        const int2 rg = ranges[blockIdx.x];
-        tb = rg.x; te = rg.y;
-    } else {
-        tb = (int)(((int64_t)blockIdx.x * total_rt) / gridDim.x);
-        te = (int)(((int64_t)(blockIdx.x + 1) * total_rt) / gridDim.x);
-    }
-    int opi = 0;
-    if (n_ops > 1) {   // first product whose row tiles reach tb
+    // Work units are contiguous ranges of row tiles (of one or several products). Unit blockIdx.x is this CTA's
+    // first; further units are handed out by an atomic counter. Every fetch happens after griddepcontrol.wait,
+    // i.e. after the launch ahead in the stream (which uses the same counter) has completed and reset it.
+    auto unit_range = [&](int u, int& b, int& e) {
+        if (ranges) {
+            const int2 rg = ranges[u];
+            b = rg.x; e = rg.y;
+        } else {
+            b = (int)(((int64_t)u * total_rt) / n_units);
+            e = (int)(((int64_t)(u + 1) * total_rt) / n_units);
+        }
+    };
+    auto find_op = [&](int rt) {   // product whose row tiles contain rt
         int lo = 0, hi = n_ops - 1;
         while (lo < hi) {
             const int mid = (lo + hi) >> 1;
-            if (ops[mid].rt0 + ops[mid].nrt <= tb) lo = mid + 1; else hi = mid;
+            if (ops[mid].rt0 + ops[mid].nrt <= rt) lo = mid + 1; else hi = mid;
         }
-        opi = lo;
-    }
+        return lo;
+    };
+    // a warp copies one 128-byte descriptor into the cache
+    static_assert(sizeof(DOp) == 128, "one word per lane");
+    auto cache_op = [&](int slot, int opi) {
+        const uint32_t* src = n_ops > 1 ? reinterpret_cast<const uint32_t*>(ops + opi) : nullptr;
+        reinterpret_cast<uint32_t*>(&s_op[slot])[lane] = src ? __ldg(src + lane) : reinterpret_cast<const uint32_t*>(&single)[lane];
+    };
+
+    Seg cur;
+    unit_range(blockIdx.x, cur.ub, cur.ue);
+    cur.b = cur.ub;
+    cur.opi = n_ops > 1 ? find_op(cur.b) : 0;
+    if (warp == 0) cache_op(0, cur.opi);
+    __syncthreads();
+    cur.e = min(cur.ue, s_op[0].rt0 + s_op[0].nrt);
     // Programmatic dependent launch: the next kernel of the stream may start its CTAs as ours retire; like this
     // kernel it touches nothing an earlier kernel writes (activations, outputs) before its griddepcontrol.wait,
     // only the immutable packed weights.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    bool alive = true;
-    bool first = true;
-    // segment state: the product, its row tiles owned by this CTA, this warp's items and stream
-    DOp op = single;
-    int seg_b = tb, seg_e = tb, i0 = 0, i1 = 0;
-    Stream st{nullptr, 0, 0};
-    auto open_segment = [&](int sb, bool issue) {
-        if (n_ops > 1) {
-            while (opi < n_ops - 1 && sb >= ops[opi].rt0 + ops[opi].nrt) opi++;
-            op = ops[opi];
-        }
-        seg_b = sb;
-        seg_e = min(te, op.rt0 + op.nrt);
-        warp_range<NW>((seg_e - seg_b) * op.nh, warp, i0, i1);
-        st.src = op.img + ((int64_t)(seg_b - op.rt0) * op.nh + i0) * op.item_bytes;
+    // this warp's share of a segment as a stream of items
+    auto stream_of = [&](const DOp& o, const Seg& sg, int& i0, int& i1) {
+        warp_range<NW>((sg.e - sg.b) * o.nh, warp, i0, i1);
+        Stream st;
+        st.src = o.img + ((int64_t)(sg.b - o.rt0) * o.nh + i0) * o.item_bytes;
         st.to_issue = i1 - i0;
-        st.item_bytes = op.item_bytes;
-        if (issue) ring_fill(ring, st, lane);   // the weights are immutable: start them before anything else
+        st.item_bytes = o.item_bytes;
+        return st;
     };
-    if (tb < te) open_segment(tb, true);
+    int i0, i1;
+    Stream st = stream_of(s_op[0], cur, i0, i1);
+    ring_fill(ring, st, lane);   // the weights are immutable: start them before anything else
 
-    while (seg_b < te) {
-        if (first) {
-            // only now wait for the kernels ahead in the stream, whose outputs the activations may be
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            first = false;
+    // only now wait for the kernels ahead in the stream, whose outputs the activations may be
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    int fetched = 0;   // thread 0: the unit after the current one (asked for at the start of the current unit)
+    if (threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);
+
+    bool alive = true;
+    int si = 0;   // descriptor slot of the current segment; the previous one is (si + 2) % 3, the next (si + 1) % 3
+    // hand-over of the previous segment, completed after the CTA has met
+    float pend[4];
+    int pend_rt = -1, prev_b = 0, prev_items = 0, prev_i1 = 0;
+    for (;;) {
+        const DOp& op = s_op[si];
+        const int sp = si == 0 ? 2 : si - 1, sn = si == 2 ? 0 : si + 1;
+        const bool last_seg = cur.e >= cur.ue;   // the unit ends with this segment
+        if (last_seg && threadIdx.x == 0) s_next = fetched;
+        __syncthreads();   // the previous segment is done: its hand-over slots are written, its activations free
+        if (alive && pend_rt >= 0) {
+            // parts of the pending row tile lie with the following warps, in order, until one reaches its end
+            const DOp& po = s_op[sp];
+            const int tile_end = (pend_rt - prev_b + 1) * po.nh;
+            int pos = prev_i1;
+            for (int w2 = warp + 1; w2 < NW && pos < tile_end; w2++) {
+                int j0, j1;
+                warp_range<NW>(prev_items, w2, j0, j1);
+                if (j0 == j1) continue;
+                slot_add<MANY>(red, w2, pend, lane);
+                pos = j1;
+            }
+            store_tile<MANY>(po, pend_rt, pend, m, lane);
         }
-        __syncthreads();   // the previous segment's activations and hand-over slots are no longer read
+        // the segment after this one; its descriptor goes into the slot nobody reads any more
+        Seg nxt;
+        bool have_next = true;
+        if (!last_seg) {
+            nxt.ub = cur.ub; nxt.ue = cur.ue; nxt.b = cur.e; nxt.opi = cur.opi + 1;   // products are consecutive in row tiles
+        } else {
+            const int nu = s_next;
+            if (nu < n_units) {
+                unit_range(nu, nxt.ub, nxt.ue);
+                nxt.b = nxt.ub;
+                nxt.opi = n_ops > 1 ? find_op(nxt.b) : 0;
+                if (threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);
+            } else {
+                have_next = false;
+            }
+        }
+        if (have_next && warp == NW - 1) cache_op(sn, nxt.opi);
+        // activation image of this segment
         ActImg ai;
         ai.limbs = ximg;
         ai.fs = reinterpret_cast<float*>(ximg + act_limb_bytes(op.k, m));
@@ -724,39 +798,51 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             prep_x<16, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 32.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<16>(ai, zero, lane);
         }
-        __syncthreads();
+        __syncthreads();   // the image is complete and the next descriptor is cached
+        Stream nx{nullptr, 0, 0};
+        int n0 = 0, n1 = 0;
+        if (have_next) {
+            const DOp& no = s_op[sn];
+            nxt.e = min(nxt.ue, no.rt0 + no.nrt);
+            nx = stream_of(no, nxt, n0, n1);
+            if (!alive) nx.to_issue = 0;
+        }
 
-        float pend[4];
-        int pend_rt = -1;
-        const DOp cur = op;
-        const int cur_b = seg_b - op.rt0, cur_items = (seg_e - seg_b) * op.nh, cur_i1 = i1;
+        prev_b = cur.b - op.rt0; prev_items = (cur.e - cur.b) * op.nh; prev_i1 = i1;
+        pend_rt = -1;
         if (alive) {
             bool ok;
-            if (cur.kind == DK_Q4K) ok = run_segment<DK_Q4K, MANY>(cur, cur_b, i0, i1, ring, st, lb1, lbm, m, red, pend, pend_rt, lane, warp);
-            else ok = run_segment<DK_Q6K, MANY>(cur, cur_b, i0, i1, ring, st, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            if (op.kind == DK_Q4K) ok = run_segment<DK_Q4K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else ok = run_segment<DK_Q6K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             if (!ok) {
                 alive = false;
+                pend_rt = -1;
                 if (lane == 0) atomicExch(status, 100 + warp);
             }
         }
-        // next segment: its first chunks are requested before the CTA meets for the hand-over
-        const int next_b = seg_e;
-        if (next_b < te) open_segment(next_b, alive);   // a warp that gave up still follows the CTA's segments
-        else seg_b = next_b;
-        __syncthreads();   // hand-over slots are written
-        if (alive && pend_rt >= 0) {
-            // parts of the pending row tile lie with the following warps, in order, until one reaches its end
-            const int tile_end = (pend_rt - cur_b + 1) * cur.nh;
-            int pos = cur_i1;
-            for (int w2 = warp + 1; w2 < NW && pos < tile_end; w2++) {
-                int j0, j1;
-                warp_range<NW>(cur_items, w2, j0, j1);
-                if (j0 == j1) continue;
-                slot_add<MANY>(red, w2, pend, lane);
-                pos = j1;
-            }
-            store_tile<MANY>(cur, pend_rt, pend, m, lane);
+        if (!have_next) break;
+        cur = nxt; st = nx; i0 = n0; i1 = n1;
+        si = sn;
+    }
+    __syncthreads();   // hand-over slots of the last segment are written
+    if (alive && pend_rt >= 0) {
+        const DOp& po = s_op[si];
+        const int tile_end = (pend_rt - prev_b + 1) * po.nh;
+        int pos = prev_i1;
+        for (int w2 = warp + 1; w2 < NW && pos < tile_end; w2++) {
+            int j0, j1;
+            warp_range<NW>(prev_items, w2, j0, j1);
+            if (j0 == j1) continue;
+            slot_add<MANY>(red, w2, pend, lane);
+            pos = j1;
         }
+        store_tile<MANY>(po, pend_rt, pend, m, lane);
+    }
+    // the last CTA to run out of units resets the counters for the next launch
+    if (threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) {
+        sched[0] = 0;
+        sched[1] = 0;
+        __threadfence();
     }
     // a wait that gave up leaves copies in flight: they must land before the CTA's shared memory is released
     if (!alive) {
@@ -910,12 +996,12 @@ bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaun
     const int nw = m == 1 ? 8 : 16;
     // tuning knob (like the reference's ROCFORGE_TILE_* variables, src/ggml/hip_backend/tuning.rs:237-275):
     // B200Q_DECODE_RING="items per copy,slots per warp"
-    int chunk = 2, depth = 4;
+    int chunk = 4, depth = 2;
     if (const char* e = getenv("B200Q_DECODE_RING")) {
         int c = 0, d = 0;
         if (sscanf(e, "%d,%d", &c, &d) == 2 && c >= 1 && c <= 8 && d >= 2 && d <= MAX_DEPTH) { chunk = c; depth = d; }
     }
-    const size_t cap = nw == 8 ? 113 * 1024 : 226 * 1024, cap1 = 226 * 1024;
+    const size_t cap = nw == 8 ? 112 * 1024 : 225 * 1024, cap1 = 225 * 1024;
     const size_t fixed = fixed_bytes(nw);
     for (int pass = 0; pass < 2; pass++) {
         // first pass: the preferred occupancy; second pass (8-warp form only): one CTA per SM
@@ -926,7 +1012,7 @@ bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaun
             const size_t total = fixed + (size_t)nw * d * slot + image;
             if (total <= limit) {
                 out->chunk_items = c; out->depth = d; out->slot_bytes = slot; out->smem_bytes = total;
-                out->ctas_per_sm = (nw == 8 && total <= 113 * 1024) ? 2 : 1;
+                out->ctas_per_sm = (nw == 8 && total <= 112 * 1024) ? 2 : 1;
                 out->nw = nw; out->many = m > 1;
                 return true;
             }
@@ -938,15 +1024,67 @@ bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaun
     return false;
 }
 
+void gemv_i8_make_units(const std::vector<double>& tile_cost, const std::vector<int>& tile_op, int n_ctas, std::vector<int2>* units) {
+    // Contiguous ranges of (nearly) equal cost. A range that starts a new product pays for the barrier, the
+    // activation image and the hand-over of a segment: `seg_cost` bytes' worth of time.
+    // tuning knobs: B200Q_DECODE_UNITS="static share in percent,tail units per CTA,segment cost in KiB": the first
+    // n_ctas units split that share of the work evenly, the rest is cut into smaller units handed out dynamically
+    double share = 100.0, seg_cost = 96.0 * 1024;
+    int tail = 0;
+    if (const char* e = getenv("B200Q_DECODE_UNITS")) {
+        double a = 0, c = 0;
+        int t = 0;
+        if (sscanf(e, "%lf,%d,%lf", &a, &t, &c) == 3 && a >= 10 && a <= 100 && t >= 0 && t <= 16 && c >= 0) { share = a; tail = t; seg_cost = c * 1024; }
+    }
+    const int total = (int)tile_cost.size();
+    std::vector<double> cost(total);
+    double sum = 0;
+    for (int t = 0; t < total; t++) {
+        cost[t] = tile_cost[t] + ((t == 0 || tile_op[t] != tile_op[t - 1]) ? seg_cost : 0.0);
+        sum += cost[t];
+    }
+    units->clear();
+    if (tail == 0) share = 100.0;
+    const double first_part = sum * share / 100.0;
+    double acc = 0;
+    int t = 0;
+    for (int c = 0; c < n_ctas && t < total; c++) {
+        int2 u;
+        u.x = t;
+        const double limit = first_part * (c + 1) / n_ctas;
+        const bool last = share >= 100.0 && c == n_ctas - 1;
+        // a range that does not start a product pays for its segment all the same
+        double own = (tile_op[t] == (t ? tile_op[t - 1] : -1)) ? seg_cost : 0.0;
+        while (t < total && (last || acc + own + cost[t] * 0.5 <= limit || t == u.x)) acc += cost[t++];
+        u.y = t;
+        units->push_back(u);
+    }
+    if (t < total) {
+        const int n_tail = n_ctas * tail;
+        const double rest = sum - acc;
+        double acc2 = 0;
+        for (int c = 0; c < n_tail && t < total; c++) {
+            int2 u;
+            u.x = t;
+            const double limit = rest * (c + 1) / n_tail;
+            while (t < total && (c == n_tail - 1 || acc2 + cost[t] * 0.5 <= limit || t == u.x)) acc2 += cost[t++];
+            u.y = t;
+            units->push_back(u);
+        }
+    }
+}
+
 bool gemv_i8_supported(const b200q_weight* w, int m) {
     if (!w->dimg.base || m < 1 || m > 8) return false;
     DecodeLaunch L;
     return gemv_i8_plan(w->dimg.item_bytes, (int)w->k, 1 << w->dimg.kind, m, &L);
 }
 
-int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
+int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_units, int n_ctas,
                    int total_rt, int m, const DecodeLaunch& L) {
     if (total_rt <= 0) return B200Q_OK;
+    if (n_units > total_rt) n_units = total_rt;
+    if (n_ctas > n_units) n_ctas = n_units;
     static bool configured[64][2] = {};
     const int ki = L.many ? 1 : 0;
     const void* kernels[2] = {(const void*)gemv_i8_kernel<8, false>, (const void*)gemv_i8_kernel<16, true>};
@@ -967,8 +1105,9 @@ int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int* status = ctx->d_status;
+    int* sched = ctx->d_status + 2;   // {next unit, CTAs done}: zero between launches
     int chunk = L.chunk_items, depth = L.depth, slot = L.slot_bytes;
-    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &total_rt, &m, &status, &chunk, &depth, &slot};
+    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &n_units, &total_rt, &m, &status, &sched, &chunk, &depth, &slot};
     B200Q_CUDA(cudaLaunchKernelExC(&cfg, kernels[ki], args), B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     ctx->tc_pending = true;   // the next synchronise reads the status word

@@ -1,5 +1,7 @@
 // Declarations of the integer tensor-core decode kernel and of the decode image it streams (gemv_i8.cu).
 #pragma once
+#include <vector>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -47,9 +49,13 @@ bool gemv_i8_supported(const b200q_weight* w, int m);
 // dimension at most kmax and kinds in `kind_mask`; returns false when the activation image does not fit.
 bool gemv_i8_plan(int max_item_bytes, int kmax, int kind_mask, int m, DecodeLaunch* out);
 size_t gemv_i8_image_smem(int kind, int k, int m);
-// ops/ranges are device pointers when n_ops > 1; for n_ops == 1 the product travels as a kernel argument and the
-// row tiles are split evenly over the CTAs.
-int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_ctas,
+// Work units: d_ranges lists n_units contiguous row-tile ranges (device array), or is null and the total_rt row
+// tiles are cut into n_units equal ranges. The first n_ctas units start on their own CTA, the rest are handed out
+// as CTAs finish. d_ops is a device array when n_ops > 1; a single product travels as a kernel argument.
+int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_units, int n_ctas,
                    int total_rt, int m, const DecodeLaunch& L);
+// Cuts the row tiles of a launch (byte cost and product index per tile) into work units: n_ctas ranges of equal
+// cost, optionally followed by smaller units that are handed out as CTAs finish.
+void gemv_i8_make_units(const std::vector<double>& tile_cost, const std::vector<int>& tile_op, int n_ctas, std::vector<int2>* units);
 
 }  // namespace b200q

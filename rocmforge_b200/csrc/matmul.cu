@@ -37,7 +37,7 @@ struct b200q_batch {
     std::vector<DOp> h_dops;
     DOp dsingle{}, dsingle_hosty{};
     DecodeLaunch dl{};
-    int total_rt = 0;
+    int total_rt = 0, n_units = 0;
 };
 
 static DOp make_dop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
@@ -91,9 +91,8 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
                 for (int p = 0; p < op.n_extra; p++) op.y_extra[p] += (int64_t)i * ldy;
                 DecodeLaunch L;
                 gemv_i8_plan(op.item_bytes, op.k, 1 << op.kind, mm, &L);
-                int n_ctas = ctx->info.sm_count * L.ctas_per_sm;
-                if (n_ctas > op.nrt) n_ctas = op.nrt;
-                int rc = launch_gemv_i8(ctx, &op, nullptr, 1, nullptr, n_ctas, op.nrt, mm, L);
+                const int n_ctas = ctx->info.sm_count * L.ctas_per_sm;
+                int rc = launch_gemv_i8(ctx, &op, nullptr, 1, nullptr, n_ctas, n_ctas, op.nrt, mm, L);
                 if (rc != B200Q_OK) return rc;
             }
             return B200Q_OK;
@@ -287,32 +286,25 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
     if (all_i8) {
         std::vector<DOp> ops(count);
         std::vector<double> tile_cost;
+        std::vector<int> tile_op;
         int total = 0;
         for (int i = 0; i < count; i++) {
             ops[i] = make_dop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
             ops[i].rt0 = total;
             total += ops[i].nrt;
             const double c = (double)ops[i].nh * ops[i].item_bytes;
-            for (int t = 0; t < ops[i].nrt; t++) tile_cost.push_back(c);
+            for (int t = 0; t < ops[i].nrt; t++) { tile_cost.push_back(c); tile_op.push_back(i); }
         }
         int n_ctas = ctx->info.sm_count * b->dl.ctas_per_sm;
-        if (n_ctas > total) n_ctas = total;
-        double sum = 0;
-        for (double c : tile_cost) sum += c;
-        std::vector<int2> ranges(n_ctas);
-        double acc = 0;
-        int t = 0;
-        for (int c = 0; c < n_ctas; c++) {
-            ranges[c].x = t;
-            const double limit = sum * (c + 1) / n_ctas;
-            while (t < total && (acc + tile_cost[t] * 0.5 <= limit || c == n_ctas - 1)) acc += tile_cost[t++];
-            ranges[c].y = t;
-        }
+        std::vector<int2> ranges;
+        gemv_i8_make_units(tile_cost, tile_op, n_ctas, &ranges);
+        b->n_units = (int)ranges.size();
+        if (n_ctas > b->n_units) n_ctas = b->n_units;
         cudaError_t e = cudaSetDevice(ctx->device);
         if (e == cudaSuccess) e = cudaMalloc(&b->d_dops, sizeof(DOp) * count);
-        if (e == cudaSuccess) e = cudaMalloc(&b->d_ranges, sizeof(int2) * n_ctas);
+        if (e == cudaSuccess) e = cudaMalloc(&b->d_ranges, sizeof(int2) * ranges.size());
         if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_dops, ops.data(), sizeof(DOp) * count, cudaMemcpyHostToDevice, ctx->stream);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ranges, ranges.data(), sizeof(int2) * n_ctas, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ranges, ranges.data(), sizeof(int2) * ranges.size(), cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) {
             if (b->d_dops) cudaFree(b->d_dops);
@@ -395,7 +387,7 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (ms_out) B200Q_CUDA(cudaEventRecord(ctx->ev0, ctx->stream), B200Q_ERR_DEVICE);
     if (batch->grouped_i8) {
         int n = (int)batch->w.size();
-        int rc = launch_gemv_i8(ctx, &batch->dsingle, batch->d_dops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
+        int rc = launch_gemv_i8(ctx, &batch->dsingle, batch->d_dops, n, batch->d_ranges, batch->n_units, batch->n_ctas,
                                 batch->total_rt, batch->m, batch->dl);
         if (rc != B200Q_OK) return rc;
     } else if (batch->grouped) {
@@ -465,7 +457,7 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
                     batch->hosty_base = h_y_all;
                 }
                 int n = (int)cnt;
-                int rc = launch_gemv_i8(ctx, &batch->dsingle_hosty, batch->d_dops_hosty, n, n > 1 ? batch->d_ranges : nullptr,
+                int rc = launch_gemv_i8(ctx, &batch->dsingle_hosty, batch->d_dops_hosty, n, batch->d_ranges, batch->n_units,
                                         batch->n_ctas, batch->total_rt, batch->m, batch->dl);
                 if (rc != B200Q_OK) return rc;
                 return b200q_synchronize(ctx);
