@@ -41,6 +41,8 @@ namespace {
 
 constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
+constexpr int F_Q80 = fmt_of(Q8_0, GGUF);
+constexpr int F_MX6 = fmt_of(MXFP6_E2M3, GGUF);
 
 // ---- item layouts (bytes inside one item; lane = 4 g + t; rows g and g+8 of the row tile; s = sub-block of 32
 // weights inside the item's 128). A "chunk" (g, s) is 16 bytes placed at chunk_pos(g, s) * 16 of its 512-byte area,
@@ -56,8 +58,17 @@ constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 //         [1536,1664)  per g 16 bytes: for s = 0..3 the int8 scales of weights 0..15 and 16..31 of sub-block s for row
 //                      g, then for row g+8
 //         [1664,1696)  per g: f16 d(g), d(g+8)
+// Q8_0:   [0,512) / [512,1024)      chunk (g, s): int8 codes 0..15 / 16..31 of sub-block s of row g
+//         [1024,1536) / [1536,2048) the same for row g+8
+//         [2048,2176)  per lane (g, s): f16 d(g), d(g+8) of the sub-block
+// MXFP6 (E2M3 element type, GGUF): the 6-bit codes are widened at upload to the int8 value 8 * e2m3(code) (|.| <= 60),
+//         so the item is Q8_0's with a one-byte header: [2048,2112) per lane (g, s): E8M0 exponent of row g, of row g+8.
+//         The image is 8.25 bits per weight against the format's 6.25: this kernel trades HBM bytes for not
+//         decoding a 6-bit float per weight on the integer pipes.
 constexpr int Q4K_ITEM = 1216;
 constexpr int Q6K_ITEM = 1696;
+constexpr int Q80_ITEM = 2176;
+constexpr int MX6_ITEM = 2112;
 
 constexpr int MAX_DEPTH = 8;
 constexpr int ZERO_BYTES = 128;                       // lanes that supply the zero columns of B read these
@@ -79,6 +90,21 @@ __device__ __forceinline__ void mma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1
                                            uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
@@ -470,6 +496,79 @@ __device__ __forceinline__ void item_q6k_many(uint32_t it, const LaneBM& lb, int
     }
 }
 
+// ---------------------------------------------------------------------------------- Q8_0 and MXFP6 as int8
+// Block scale of the lane's sub-block for rows g and g+8.
+template <int KIND>
+__device__ __forceinline__ void s8_scales_lane(uint32_t it, int lane, float& s0, float& s1) {
+    if (KIND == DK_Q80) {
+        const uint32_t dd = lds32(it + 2048 + lane * 4);
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dd));
+        s0 = d.x; s1 = d.y;
+    } else {
+        const uint32_t w = lds32(it + 2048 + (lane >> 1) * 4) >> ((lane & 1) * 16);
+        s0 = ocp_e8m0((uint8_t)(w & 0xFFu)) * 0.125f;   // codes are 8 * value
+        s1 = ocp_e8m0((uint8_t)((w >> 8) & 0xFFu)) * 0.125f;
+    }
+}
+
+// One row: acc += scale * (factor * sum q x_int) for the lane's block of rows g and g+8.
+template <int KIND>
+__device__ __forceinline__ void item_s8_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int cp = chunk_pos(g, t) * 16;
+    const uint4 a0 = lds128(it + cp), a1 = lds128(it + 512 + cp);
+    const uint4 b0 = lds128(it + 1024 + cp), b1 = lds128(it + 1536 + cp);
+    const uint4 q0 = lds128(lb.p1 + h * lb.s1), q1 = lds128(lb.p1 + h * lb.s1 + 16);
+    const uint4 r0 = lds128(lb.p2 + h * lb.s2), r1 = lds128(lb.p2 + h * lb.s2 + 16);
+    const uint2 fSb = lds64(lb.f0 + h * lb.fh);
+    float s0, s1;
+    s8_scales_lane<KIND>(it, lane, s0, s1);
+    int c[4], e[4];   // c: columns (limb 0, limb 1); e: columns (limb 2, zero)
+    mma_s8s8_z(c, a0.x, b0.x, a0.y, b0.y, q0.x, q0.y);
+    mma_s8s8_z(e, a0.x, b0.x, a0.y, b0.y, r0.x, r0.y);
+    mma_s8s8(c, a0.z, b0.z, a0.w, b0.w, q0.z, q0.w);
+    mma_s8s8(e, a0.z, b0.z, a0.w, b0.w, r0.z, r0.w);
+    mma_s8s8(c, a1.x, b1.x, a1.y, b1.y, q1.x, q1.y);
+    mma_s8s8(e, a1.x, b1.x, a1.y, b1.y, r1.x, r1.y);
+    mma_s8s8(c, a1.z, b1.z, a1.w, b1.w, q1.z, q1.w);
+    mma_s8s8(e, a1.z, b1.z, a1.w, b1.w, r1.z, r1.w);
+    // 32 codes of up to 7 bits times 21-bit activations leave 32 bits: the last limb joins in floating point
+    const float v0 = fmaf((float)(c[0] * 128 + c[1]), 128.0f, (float)e[0]);
+    const float v1 = fmaf((float)(c[2] * 128 + c[3]), 128.0f, (float)e[2]);
+    const float f = __uint_as_float(fSb.x);
+    acc[0] = fmaf(s0, v0 * f, acc[0]);
+    acc[1] = fmaf(s1, v1 * f, acc[1]);
+}
+
+// Many rows: the lane's fragment words are the code bytes as stored, no extraction at all.
+template <int KIND>
+__device__ __forceinline__ void item_s8_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t bp = lb.p + h * lb.sh;
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        const int cp = chunk_pos(g, s) * 16 + 4 * t;
+        const uint32_t a0 = lds32(it + cp), a2 = lds32(it + 512 + cp);
+        const uint32_t a1 = lds32(it + 1024 + cp), a3 = lds32(it + 1536 + cp);
+        const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
+        const uint4 fSb = lds128(lb.f0 + (4 * h + s) * lb.fb);
+        float s0, s1;
+        s8_scales_lane<KIND>(it, 4 * g + s, s0, s1);
+        int c0[4], c1[4], c2[4];
+        mma_s8s8_z(c0, a0, a1, a2, a3, b0.x, b0.y);
+        mma_s8s8_z(c1, a0, a1, a2, a3, b1.x, b1.y);
+        mma_s8s8_z(c2, a0, a1, a2, a3, b2.x, b2.y);
+        const float fa = __uint_as_float(fSb.x), fb = __uint_as_float(fSb.z);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = fmaf((float)(c0[j] * 128 + c1[j]), 128.0f, (float)c2[j]);
+        acc[0] = fmaf(s0, v[0] * fa, acc[0]);
+        acc[1] = fmaf(s0, v[1] * fb, acc[1]);
+        acc[2] = fmaf(s1, v[2] * fa, acc[2]);
+        acc[3] = fmaf(s1, v[3] * fb, acc[3]);
+    }
+}
+
 // What a warp streams for one product segment.
 struct Stream {
     const uint8_t* src;   // next byte to copy
@@ -619,8 +718,10 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
         for (int c = 0; c < cnt; c++, it += item_bytes) {
             if (KIND == DK_Q4K) {
                 if (MANY) item_q4k_many(it, lbm, h, acc, lane); else item_q4k_one(it, lb1, h, acc, lane);
-            } else {
+            } else if (KIND == DK_Q6K) {
                 if (MANY) item_q6k_many(it, lbm, h, acc, lane); else item_q6k_one(it, lb1, h, acc, lane);
+            } else {
+                if (MANY) item_s8_many<KIND>(it, lbm, h, acc, lane); else item_s8_one<KIND>(it, lb1, h, acc, lane);
             }
             if (++h == nh) {   // the row tile is complete as far as this warp is concerned
                 finish_acc<MANY>(acc);
@@ -791,7 +892,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         ai.fs = reinterpret_cast<float*>(ximg + act_limb_bytes(op.k, m));
         LaneB1 lb1{};
         LaneBM lbm{};
-        if (op.kind == DK_Q4K) {
+        if (op.kind != DK_Q6K) {   // scale groups of 32; only Q4_K uses the sums
             prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 1.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
         } else {
@@ -813,7 +914,9 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         if (alive) {
             bool ok;
             if (op.kind == DK_Q4K) ok = run_segment<DK_Q4K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
-            else ok = run_segment<DK_Q6K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else if (op.kind == DK_Q6K) ok = run_segment<DK_Q6K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else if (op.kind == DK_Q80) ok = run_segment<DK_Q80, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else ok = run_segment<DK_MX6, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             if (!ok) {
                 alive = false;
                 pend_rt = -1;
@@ -937,15 +1040,58 @@ __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* 
     if (t == 0) *reinterpret_cast<uint32_t*>(it + 1664 + g * 4) = dd;
 }
 
+// Q8_0 (codes as stored) and MXFP6 E2M3 (codes widened to 8 * value): one thread per (item, lane).
+template <int KIND>
+__global__ void __launch_bounds__(256) build_image_s8_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * (KIND == DK_Q80 ? Q80_ITEM : MX6_ITEM);
+    uint16_t sc[2] = {0, 0};
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint8_t o[32];
+        for (int b = 0; b < 32; b++) o[b] = 0;
+        if (row < n_rows) {
+            const int64_t blk = (row * nh + h) * 4 + t;   // 32-weight block in the flat stream
+            if (KIND == DK_Q80) {
+                const uint8_t* q = v.p[1] + blk * 32;
+                for (int b = 0; b < 32; b++) o[b] = q[b];
+                sc[i] = ld16(v.p[0] + blk * 2);
+            } else {
+                const uint8_t* q = v.p[1] + blk * 24;
+                for (int b = 0; b < 32; b++) {
+                    const int bit = 6 * b;
+                    const uint32_t comb = (uint32_t)q[bit >> 3] | ((bit >> 3) + 1 < 24 ? (uint32_t)q[(bit >> 3) + 1] << 8 : 0u);
+                    o[b] = (uint8_t)(int8_t)__float2int_rn(ocp_e2m3((comb >> (bit & 7)) & 63u) * 8.0f);
+                }
+                sc[i] = v.p[0][blk];
+            }
+        }
+        const int cp = chunk_pos(g, t) * 16;
+        *reinterpret_cast<uint4*>(it + 1024 * i + cp) = *reinterpret_cast<uint4*>(o);
+        *reinterpret_cast<uint4*>(it + 1024 * i + 512 + cp) = *reinterpret_cast<uint4*>(o + 16);
+    }
+    if (KIND == DK_Q80) *reinterpret_cast<uint32_t*>(it + 2048 + lane * 4) = (uint32_t)sc[0] | ((uint32_t)sc[1] << 16);
+    else *reinterpret_cast<uint16_t*>(it + 2048 + lane * 2) = (uint16_t)((sc[0] & 0xFF) | ((sc[1] & 0xFF) << 8));
+}
+
 }  // namespace
 
 int decode_kind_of(int fmt) {
     if (fmt == F_Q4K) return DK_Q4K;
     if (fmt == F_Q6K) return DK_Q6K;
+    if (fmt == F_Q80) return DK_Q80;
+    if (fmt == F_MX6) return DK_MX6;
     return DK_NONE;
 }
 
-int decode_item_bytes(int kind) { return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : 0; }
+int decode_item_bytes(int kind) {
+    return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : kind == DK_Q80 ? Q80_ITEM : kind == DK_MX6 ? MX6_ITEM : 0;
+}
 
 bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k) {
     if (decode_kind_of(fmt) == DK_NONE || orient != B200Q_ORIENT_NK) return false;
@@ -975,7 +1121,9 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
         return fail(B200Q_ERR_INVALID, "upload: tensor too large for one image-build launch");
     }
     if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
-    else build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q6K) build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q80) build_image_s8_kernel<DK_Q80><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else build_image_s8_kernel<DK_MX6><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
