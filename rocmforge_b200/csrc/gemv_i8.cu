@@ -43,6 +43,7 @@ constexpr int F_Q4K = fmt_of(Q4_K, GGUF);
 constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 constexpr int F_Q80 = fmt_of(Q8_0, GGUF);
 constexpr int F_MX6 = fmt_of(MXFP6_E2M3, GGUF);
+constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 
 // ---- item layouts (bytes inside one item; lane = 4 g + t; rows g and g+8 of the row tile; s = sub-block of 32
 // weights inside the item's 128). A "chunk" (g, s) is 16 bytes placed at chunk_pos(g, s) * 16 of its 512-byte area,
@@ -65,6 +66,12 @@ constexpr int F_MX6 = fmt_of(MXFP6_E2M3, GGUF);
 //         so the item is Q8_0's with a one-byte header: [2048,2112) per lane (g, s): E8M0 exponent of row g, of row g+8.
 //         The image is 8.25 bits per weight against the format's 6.25: this kernel trades HBM bytes for not
 //         decoding a 6-bit float per weight on the integer pipes.
+// MXFP4 (GGUF): [0,512)  chunk (g, s): the 32 E2M1 codes of sub-block s of row g in order, nibble k of word j = weight 8j+k
+//         [512,1024)   the same for row g+8
+//         [1024,1088)  per lane (g, s): E8M0 exponent of row g, of row g+8
+//         A code becomes the magnitude 2 * |e2m1(code)| through one byte-permute table look-up; positive and negative
+//         codes go through separate MMAs whose sums are subtracted.
+constexpr int MX4_ITEM = 1088;
 constexpr int Q4K_ITEM = 1216;
 constexpr int Q6K_ITEM = 1696;
 constexpr int Q80_ITEM = 2176;
@@ -178,7 +185,9 @@ __device__ __forceinline__ void split_limbs(int q, int& l0, int& l1, int& l2) {
 // x[m, k] (fp32, global) -> image. 8 consecutive values per thread and step, four steps' loads in flight at a time
 // (the activations usually come from HBM: the packed weights have pushed them out of L2); the G / 8 lanes of a
 // group agree on the group's maximum and sum by shuffles. MANY selects the many-row layout.
-template <int G, bool MANY, int NT>
+// PERM (many-row layout only): the lane t of the fragment owns values 8t..8t+7 of a sub-block (MXFP4's code order)
+// instead of 4t..4t+3 and 16+4t..16+4t+3.
+template <int G, bool MANY, int NT, bool PERM = false>
 __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx, int k, int m, const ActImg& img, float sum_mul) {
     const int units = k >> 3;
     const int nb = k >> 5;
@@ -246,12 +255,18 @@ __device__ __forceinline__ void prep_x(const float* __restrict__ x, int64_t ldx,
                     const int h = b >> 2, sb = b & 3;
                     // values 8 jj .. 8 jj + 3 belong to lane t = (2 jj) & 3, values 8 jj + 4 .. to lane t + 1; jj < 2:
                     // first half of the sub-block (b0 of the fragment), else second half (b1)
-                    const int t0 = (2 * jj) & 3, half = jj >> 1;
-                    uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + t0) * 96 + sb * 24 + half * 4;
+                    if (PERM) {
+                        uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + jj) * 96 + sb * 24;
 #pragma unroll
-                    for (int L = 0; L < 3; L++) {
-                        *reinterpret_cast<uint32_t*>(dst + L * 8) = w[L][0];
-                        *reinterpret_cast<uint32_t*>(dst + 96 + L * 8) = w[L][1];
+                        for (int L = 0; L < 3; L++) *reinterpret_cast<uint2*>(dst + L * 8) = make_uint2(w[L][0], w[L][1]);
+                    } else {
+                        const int t0 = (2 * jj) & 3, half = jj >> 1;
+                        uint8_t* dst = img.limbs + ((size_t)(h * m + n) * 4 + t0) * 96 + sb * 24 + half * 4;
+#pragma unroll
+                        for (int L = 0; L < 3; L++) {
+                            *reinterpret_cast<uint32_t*>(dst + L * 8) = w[L][0];
+                            *reinterpret_cast<uint32_t*>(dst + 96 + L * 8) = w[L][1];
+                        }
                     }
                     if (G == 32) {
                         if (jj == 0) *reinterpret_cast<float2*>(img.fs + ((size_t)b * mp + n) * 2) = make_float2(f, sm * sum_mul);
@@ -569,6 +584,88 @@ __device__ __forceinline__ void item_s8_many(uint32_t it, const LaneBM& lb, int 
     }
 }
 
+// ------------------------------------------------------------------------------------------ MXFP4 (GGUF)
+// Eight E2M1 codes (one word) -> four byte words: the magnitudes 2 * |e2m1(code)| of the non-negative codes
+// 0..3 and 4..7 (zero where the code is negative), and the same for the negative codes. A byte permute with the raw
+// nibbles as selector returns the table byte where the sign bit is clear and 0x00 where it is set (its
+// sign-replicate mode on a table of bytes below 0x80), so each half costs one instruction; the product with the
+// negative part is subtracted after the MMAs.
+__device__ __forceinline__ void e2m1x8_split(uint32_t w, uint32_t& p_lo, uint32_t& p_hi, uint32_t& n_lo, uint32_t& n_hi) {
+    const uint32_t wn = w ^ 0x88888888u;
+    p_lo = __byte_perm(0x03020100u, 0x0C080604u, w);
+    p_hi = __byte_perm(0x03020100u, 0x0C080604u, w >> 16);
+    n_lo = __byte_perm(0x03020100u, 0x0C080604u, wn);
+    n_hi = __byte_perm(0x03020100u, 0x0C080604u, wn >> 16);
+}
+
+__device__ __forceinline__ void mx4_scales_lane(uint32_t it, int lane, float& s0, float& s1) {
+    const uint32_t w = lds32(it + 1024 + (lane >> 1) * 4) >> ((lane & 1) * 16);
+    s0 = gguf_e8m0_half((uint8_t)(w & 0xFFu));   // codes are 2 * value
+    s1 = gguf_e8m0_half((uint8_t)((w >> 8) & 0xFFu));
+}
+
+__device__ __forceinline__ void item_mx4_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int cp = chunk_pos(g, t) * 16;
+    const uint4 wa = lds128(it + cp), wb = lds128(it + 512 + cp);
+    const uint4 q0 = lds128(lb.p1 + h * lb.s1), q1 = lds128(lb.p1 + h * lb.s1 + 16);
+    const uint4 r0 = lds128(lb.p2 + h * lb.s2), r1 = lds128(lb.p2 + h * lb.s2 + 16);
+    const uint2 fSb = lds64(lb.f0 + h * lb.fh);
+    float s0, s1;
+    mx4_scales_lane(it, lane, s0, s1);
+    const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w}, w1[4] = {wb.x, wb.y, wb.z, wb.w};
+    const uint32_t bq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t br[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    int cp_[4] = {0, 0, 0, 0}, ep[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0}, en[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t p0, p2, n0, n2, p1, p3, n1, n3;
+        e2m1x8_split(w0[j], p0, p2, n0, n2);
+        e2m1x8_split(w1[j], p1, p3, n1, n3);
+        mma_u8s8(cp_, p0, p1, p2, p3, bq[2 * j], bq[2 * j + 1]);
+        mma_u8s8(ep, p0, p1, p2, p3, br[2 * j], br[2 * j + 1]);
+        mma_u8s8(cn, n0, n1, n2, n3, bq[2 * j], bq[2 * j + 1]);
+        mma_u8s8(en, n0, n1, n2, n3, br[2 * j], br[2 * j + 1]);
+    }
+    const int v0 = ((cp_[0] - cn[0]) * 128 + (cp_[1] - cn[1])) * 128 + (ep[0] - en[0]);
+    const int v1 = ((cp_[2] - cn[2]) * 128 + (cp_[3] - cn[3])) * 128 + (ep[2] - en[2]);
+    const float f = __uint_as_float(fSb.x);
+    acc[0] = fmaf(s0, (float)v0 * f, acc[0]);
+    acc[1] = fmaf(s1, (float)v1 * f, acc[1]);
+}
+
+__device__ __forceinline__ void item_mx4_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t bp = lb.p + h * lb.sh;
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        const int cp = chunk_pos(g, s) * 16 + 4 * t;
+        const uint32_t w0 = lds32(it + cp), w1 = lds32(it + 512 + cp);
+        const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
+        const uint4 fSb = lds128(lb.f0 + (4 * h + s) * lb.fb);
+        float s0, s1;
+        mx4_scales_lane(it, 4 * g + s, s0, s1);
+        uint32_t p0, p1, p2, p3, n0, n1, n2, n3;
+        e2m1x8_split(w0, p0, p2, n0, n2);
+        e2m1x8_split(w1, p1, p3, n1, n3);
+        int c0[4], c1[4], c2[4], d0[4], d1[4], d2[4];
+        mma_u8s8_z(c0, p0, p1, p2, p3, b0.x, b0.y);
+        mma_u8s8_z(c1, p0, p1, p2, p3, b1.x, b1.y);
+        mma_u8s8_z(c2, p0, p1, p2, p3, b2.x, b2.y);
+        mma_u8s8_z(d0, n0, n1, n2, n3, b0.x, b0.y);
+        mma_u8s8_z(d1, n0, n1, n2, n3, b1.x, b1.y);
+        mma_u8s8_z(d2, n0, n1, n2, n3, b2.x, b2.y);
+        const float fa = __uint_as_float(fSb.x), fb = __uint_as_float(fSb.z);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = (float)(((c0[j] - d0[j]) * 128 + (c1[j] - d1[j])) * 128 + (c2[j] - d2[j]));
+        acc[0] = fmaf(s0, v[0] * fa, acc[0]);
+        acc[1] = fmaf(s0, v[1] * fb, acc[1]);
+        acc[2] = fmaf(s1, v[2] * fa, acc[2]);
+        acc[3] = fmaf(s1, v[3] * fb, acc[3]);
+    }
+}
+
 // What a warp streams for one product segment.
 struct Stream {
     const uint8_t* src;   // next byte to copy
@@ -720,6 +817,8 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
                 if (MANY) item_q4k_many(it, lbm, h, acc, lane); else item_q4k_one(it, lb1, h, acc, lane);
             } else if (KIND == DK_Q6K) {
                 if (MANY) item_q6k_many(it, lbm, h, acc, lane); else item_q6k_one(it, lb1, h, acc, lane);
+            } else if (KIND == DK_MX4) {
+                if (MANY) item_mx4_many(it, lbm, h, acc, lane); else item_mx4_one(it, lb1, h, acc, lane);
             } else {
                 if (MANY) item_s8_many<KIND>(it, lbm, h, acc, lane); else item_s8_one<KIND>(it, lb1, h, acc, lane);
             }
@@ -892,7 +991,10 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         ai.fs = reinterpret_cast<float*>(ximg + act_limb_bytes(op.k, m));
         LaneB1 lb1{};
         LaneBM lbm{};
-        if (op.kind != DK_Q6K) {   // scale groups of 32; only Q4_K uses the sums
+        if (op.kind == DK_MX4) {
+            prep_x<32, MANY, NW * 32, true>(op.x, op.ldx, op.k, m, ai, 1.0f);
+            if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
+        } else if (op.kind != DK_Q6K) {   // scale groups of 32; only Q4_K uses the sums
             prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 1.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
         } else {
@@ -916,6 +1018,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             if (op.kind == DK_Q4K) ok = run_segment<DK_Q4K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else if (op.kind == DK_Q6K) ok = run_segment<DK_Q6K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else if (op.kind == DK_Q80) ok = run_segment<DK_Q80, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else if (op.kind == DK_MX4) ok = run_segment<DK_MX4, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else ok = run_segment<DK_MX6, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             if (!ok) {
                 alive = false;
@@ -1079,6 +1182,32 @@ __global__ void __launch_bounds__(256) build_image_s8_kernel(WView v, uint8_t* _
     else *reinterpret_cast<uint16_t*>(it + 2048 + lane * 2) = (uint16_t)((sc[0] & 0xFF) | ((sc[1] & 0xFF) << 8));
 }
 
+__global__ void __launch_bounds__(256) build_image_mx4_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * MX4_ITEM;
+    uint32_t sc = 0;
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint32_t o[4] = {0u, 0u, 0u, 0u};
+        if (row < n_rows) {
+            const int64_t blk = (row * nh + h) * 4 + t;
+            const uint8_t* q = v.p[1] + blk * 16;   // byte i: element i (low nibble), element i + 16 (high nibble)
+            for (int e = 0; e < 32; e++) {
+                const uint32_t code = e < 16 ? (q[e] & 0x0Fu) : (uint32_t)(q[e - 16] >> 4);
+                o[e >> 3] |= code << (4 * (e & 7));
+            }
+            sc |= (uint32_t)v.p[0][blk] << (8 * i);
+        }
+        *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    *reinterpret_cast<uint16_t*>(it + 1024 + lane * 2) = (uint16_t)sc;
+}
+
 }  // namespace
 
 int decode_kind_of(int fmt) {
@@ -1086,11 +1215,12 @@ int decode_kind_of(int fmt) {
     if (fmt == F_Q6K) return DK_Q6K;
     if (fmt == F_Q80) return DK_Q80;
     if (fmt == F_MX6) return DK_MX6;
+    if (fmt == F_MX4) return DK_MX4;
     return DK_NONE;
 }
 
 int decode_item_bytes(int kind) {
-    return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : kind == DK_Q80 ? Q80_ITEM : kind == DK_MX6 ? MX6_ITEM : 0;
+    return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : kind == DK_Q80 ? Q80_ITEM : kind == DK_MX6 ? MX6_ITEM : kind == DK_MX4 ? MX4_ITEM : 0;
 }
 
 bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k) {
@@ -1123,6 +1253,7 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
     if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q6K) build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q80) build_image_s8_kernel<DK_Q80><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_MX4) build_image_mx4_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else build_image_s8_kernel<DK_MX6><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);

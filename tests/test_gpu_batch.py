@@ -59,7 +59,7 @@ def test_grouped_launch_of_mixed_products(oracle, m):
 def test_batch_of_other_formats_falls_back_to_per_product_launches(oracle):
     be = backend()
     rng = synth.rng_for(600)
-    ops = [(synth.MXFP6_E2M3, 256, 512), (synth.MXFP4, 300, 1024), (synth.Q4_K, 128, 256)]
+    ops = [(synth.MXFP6_E3M2, 256, 512), (synth.Q3_K, 300, 1024), (synth.Q4_K, 128, 256)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(2, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, 2)
