@@ -590,12 +590,17 @@ __device__ __forceinline__ void item_s8_many(uint32_t it, const LaneBM& lb, int 
 // nibbles as selector returns the table byte where the sign bit is clear and 0x00 where it is set (its
 // sign-replicate mode on a table of bytes below 0x80), so each half costs one instruction; the product with the
 // negative part is subtracted after the MMAs.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {   // bit 3 of a selector nibble: replicate the sign
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
 __device__ __forceinline__ void e2m1x8_split(uint32_t w, uint32_t& p_lo, uint32_t& p_hi, uint32_t& n_lo, uint32_t& n_hi) {
     const uint32_t wn = w ^ 0x88888888u;
-    p_lo = __byte_perm(0x03020100u, 0x0C080604u, w);
-    p_hi = __byte_perm(0x03020100u, 0x0C080604u, w >> 16);
-    n_lo = __byte_perm(0x03020100u, 0x0C080604u, wn);
-    n_hi = __byte_perm(0x03020100u, 0x0C080604u, wn >> 16);
+    p_lo = prmt(0x03020100u, 0x0C080604u, w);
+    p_hi = prmt(0x03020100u, 0x0C080604u, w >> 16);
+    n_lo = prmt(0x03020100u, 0x0C080604u, wn);
+    n_hi = prmt(0x03020100u, 0x0C080604u, wn >> 16);
 }
 
 __device__ __forceinline__ void mx4_scales_lane(uint32_t it, int lane, float& s0, float& s1) {
@@ -940,8 +945,11 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
 
     // only now wait for the kernels ahead in the stream, whose outputs the activations may be
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    int fetched = 0;   // thread 0: the unit after the current one (asked for at the start of the current unit)
-    if (threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);
+    // thread 0: the unit after the current one (asked for at the start of the current unit); launches whose units
+    // all start on a CTA of their own never touch the counter
+    const bool dynamic = n_units > (int)gridDim.x;
+    int fetched = n_units;
+    if (dynamic && threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);
 
     bool alive = true;
     int si = 0;   // descriptor slot of the current segment; the previous one is (si + 2) % 3, the next (si + 1) % 3
@@ -979,7 +987,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
                 unit_range(nu, nxt.ub, nxt.ue);
                 nxt.b = nxt.ub;
                 nxt.opi = n_ops > 1 ? find_op(nxt.b) : 0;
-                if (threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);
+                if (threadIdx.x == 0) fetched = (int)gridDim.x + atomicAdd(&sched[0], 1);   // only reached when dynamic
             } else {
                 have_next = false;
             }
@@ -1045,7 +1053,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         store_tile<MANY>(po, pend_rt, pend, m, lane);
     }
     // the last CTA to run out of units resets the counters for the next launch
-    if (threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) {
+    if (dynamic && threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) {
         sched[0] = 0;
         sched[1] = 0;
         __threadfence();
