@@ -2,6 +2,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <math.h>
 #include <stdlib.h>
 
 #include <vector>
@@ -248,6 +249,67 @@ size_t b200q_tensor_bytes(int qtype, int layout, int64_t n_elements) {
     return (size_t)((n_elements + I.block_elems - 1) / I.block_elems) * I.block_bytes;
 }
 
+static float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 31u, man = h & 1023u;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) bits = sign;
+        else {
+            int e = -1;
+            uint32_t mm = man;
+            do { mm <<= 1; e++; } while (!(mm & 1024u));
+            bits = sign | ((uint32_t)(112 - e) << 23) | ((mm & 1023u) << 13);
+        }
+    } else if (exp == 31) bits = sign | 0x7F800000u | (man << 13);
+    else bits = sign | ((exp + 112u) << 23) | (man << 13);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+// Scan of the block scales in the file bytes (GGUF layouts with a tensor-core prefill kernel). The prefill kernels
+// hold weights as f16: `weights_ok` says every weight fits the f16 range (and the largest block is not lost to
+// underflow), `scales_ok` the same for the products "scale x sub-scale" the tensor-memory kernels' converters form
+// in f16. A tensor that fails takes the next more careful kernel; one that fails both is multiplied by the fp32
+// decode kernels, eight activation rows at a time.
+static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bool* scales_ok, bool* weights_ok) {
+    *scales_ok = *weights_ok = true;
+    auto ld16h = [](const uint8_t* p) { return half_bits_to_float((uint16_t)(p[0] | (p[1] << 8))); };
+    auto mag = [](float d) { return d != d ? INFINITY : (d < 0 ? -d : d); };
+    FmtInfo I = fmt_info(fmt);
+    // per block: s = the f16 (or power-of-two) scale; the format's largest "s x sub-scale" and largest weight follow
+    float sub = 0.f, top = 0.f;   // multipliers of s
+    switch (fmt) {
+        case fmt_of(MXFP4, GGUF): sub = 1.f; top = 12.f; break;        // s = 2^(E-127) / 2, codes are 2 x value
+        case fmt_of(MXFP6_E2M3, GGUF): sub = 1.f; top = 7.5f; break;
+        case fmt_of(MXFP6_E3M2, GGUF): sub = 1.f; top = 28.f; break;
+        case fmt_of(Q4_K, GGUF): sub = 63.f; top = 63.f * 16.f; break; // d sc q - dmin m
+        case fmt_of(Q5_K, GGUF): sub = 63.f; top = 63.f * 32.f; break;
+        case fmt_of(Q6_K, GGUF): sub = 128.f; top = 128.f * 32.f; break;
+        case fmt_of(Q8_0, GGUF): sub = 128.f; top = 128.f; break;
+        case fmt_of(Q4_0, GGUF): sub = 8.f; top = 8.f; break;
+        default: return;
+    }
+    float smax = 0.f;
+    for (int64_t b = 0; b < n_blocks; b++) {
+        const uint8_t* p = blocks + b * I.block_bytes;
+        float s;
+        switch (fmt) {
+            case fmt_of(MXFP4, GGUF): s = p[0] == 255 ? INFINITY : ldexpf(0.5f, (int)p[0] - 127); break;
+            case fmt_of(MXFP6_E2M3, GGUF):
+            case fmt_of(MXFP6_E3M2, GGUF): s = p[0] == 255 ? INFINITY : ldexpf(1.0f, (int)p[0] - 127); break;
+            case fmt_of(Q4_K, GGUF):
+            case fmt_of(Q5_K, GGUF): s = fmaxf(mag(ld16h(p)), mag(ld16h(p + 2))); break;
+            case fmt_of(Q6_K, GGUF): s = mag(ld16h(p + 208)); break;
+            default: s = mag(ld16h(p)); break;
+        }
+        if (s > smax) smax = s;
+    }
+    if (!(smax * sub <= 60000.f) || smax * sub < 6.2e-5f) *scales_ok = false;
+    if (!(smax * top <= 60000.f) || smax < 6.2e-5f) *weights_ok = false;
+    if (smax == 0.f) *scales_ok = *weights_ok = true;   // an all-zero tensor is exact on every path
+}
+
 // Allocates the planes for n_blocks blocks, copies `avail` bytes of file blocks from the host (zero
 // filling the rest) and splits them into planes. Used by upload and by dequantize_bytes.
 static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t avail, int64_t n_blocks, void** base_out,
@@ -330,6 +392,7 @@ int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int 
     w->n_local = n_local; w->k = k; w->row0 = row0; w->n_total = n;
     w->n_elements = n_el; w->n_blocks = n_blocks;
     w->packed_bytes = (size_t)n_blocks * I.block_bytes;
+    if (layout == GGUF) scan_f16_ranges(fmt, src, n_blocks, &w->f16_scales_ok, &w->f16_weights_ok);
     int rc = make_planes(ctx, fmt, src, w->packed_bytes, n_blocks, &w->base, &w->view);
     if (rc != B200Q_OK) { delete w; return rc; }
     // second, decode-ordered copy for the m <= 8 kernel (B200Q_NO_DECODE_IMAGE=1 keeps only the stream layout)

@@ -59,6 +59,10 @@ struct b200q_weight {
     size_t packed_bytes = 0;  // bytes of the file blocks this handle holds
     void* base = nullptr;     // one allocation holding every plane
     b200q::WView view{};
+    // From a scan of the scale bytes at upload. f16_scales_ok: the products "scale x sub-scale" the tensor-memory
+    // prefill kernels form in f16 stay in range; f16_weights_ok: every weight does (the kernel that decodes in fp32
+    // and rounds each weight once to f16). A tensor that fails both is multiplied by the fp32 decode kernels.
+    bool f16_scales_ok = true, f16_weights_ok = true;
     b200q::DImage dimg{};     // second, decode-ordered copy for m <= 8 (formats of the integer decode kernel)
 };
 

@@ -1551,6 +1551,7 @@ int ensure_sk_workspace(b200q_ctx* ctx, int ctas) {
 bool mx4_tmem_path(const b200q_weight* w, int m) {
     // GGUF Q4_0 shares the path: the same 16 code bytes per block, an f16 d per block where MXFP4 has an exponent byte
     if ((w->fmt != fmt_of(MXFP4, GGUF) && w->fmt != fmt_of(Q4_0, GGUF) && w->fmt != fmt_of(Q8_0, GGUF)) || (w->k % 256) != 0) return false;
+    if (!w->f16_scales_ok) return false;   // a block scale outside the f16 converters' range: shared-memory-operand kernel
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
     return tiles * (w->k / 256) < (1ll << 30);
@@ -1558,7 +1559,7 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
 
 // GGUF Q5_K takes the tensor-memory kernel under the same conditions (persistent kernel only).
 bool q5k_tmem_path(const b200q_weight* w, int m) {
-    if (w->fmt != fmt_of(Q5_K, GGUF) || (w->k % 256) != 0) return false;
+    if (w->fmt != fmt_of(Q5_K, GGUF) || (w->k % 256) != 0 || !w->f16_scales_ok) return false;
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
     return tiles * (w->k / 256) < (1ll << 30);
@@ -1637,7 +1638,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         if (e != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (workspace) failed with code %d", who, (int)e);
         return B200Q_OK;
     };
-    if (may_allocate && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
+    if (may_allocate && w->f16_scales_ok && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
         (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30)) {
         // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads
         a.a_col0 = (bn + 31) & ~31;
@@ -1720,7 +1721,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         return B200Q_OK;
     }
     const bool q5k = w->fmt == fmt_of(Q5_K, GGUF);   // persistent kernel only (no one-CTA-per-tile variant)
-    if ((w->fmt == fmt_of(Q4_K, GGUF) || (q5k && may_allocate && (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30))) && (w->k % 256) == 0) {
+    if (w->f16_scales_ok && (w->fmt == fmt_of(Q4_K, GGUF) || (q5k && may_allocate && (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30))) && (w->k % 256) == 0) {
         // weight operand in tensor memory
         a.a_col0 = (bn + 31) & ~31;
         a.tmem_cols = 32;
@@ -1788,7 +1789,9 @@ extern "C" int b200q_debug_read_sk_trace(long long* out) {
 }
 #endif
 bool gemm_tc_supported(const b200q_weight* w, int m) {
-    return w->orient == B200Q_ORIENT_NK && m >= 1 && (w->k % BK) == 0 && w->n_local < 0x7FFFFF00ll && w->k < (1 << 30);
+    // weights beyond the f16 range (seen by the upload's scan of the block scales) stay on the fp32 decode kernels
+    return w->orient == B200Q_ORIENT_NK && m >= 1 && (w->k % BK) == 0 && w->n_local < 0x7FFFFF00ll && w->k < (1 << 30) &&
+           w->f16_weights_ok;
 }
 
 // x: fp32 or bf16 [m, ldx] on the device. y: fp32 [m, ldy]. Uses the context's third scratch buffer for the

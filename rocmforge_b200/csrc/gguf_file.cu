@@ -125,8 +125,10 @@ std::string scalar_text(Reader& r, uint32_t t) {
 }
 
 // GGUF type id -> (b200q qtype or -1, known). Ids follow GgufTensorType (src/loader/tensor_type.rs:16-61):
-// 3, 6, 7 (Q4_1, Q5_0, Q5_1) and unknown ids are errors there and here; 39 is ggml's own id of MXFP4.
-bool map_type(uint32_t id, int* qtype, int* known_block, int* plain_bytes) {
+// 3, 6, 7 (Q4_1, Q5_0, Q5_1) and unknown ids are errors there and here. Ids 20, 21, 22 mean MXFP4 / MXFP6 only in
+// the reference's own enum (tensor_type.rs:31-33), i.e. in files read in its dialect; files written by ggml use
+// them for IQ4_NL / IQ3_S / IQ2_S, whose blocks this library has no kernel for, and carry MXFP4 as id 39.
+bool map_type(uint32_t id, bool ref_style, int* qtype, int* known_block, int* plain_bytes) {
     *qtype = -1; *known_block = 0; *plain_bytes = 0;
     switch (id) {
         case 0: *plain_bytes = 4; return true;    // F32
@@ -138,9 +140,10 @@ bool map_type(uint32_t id, int* qtype, int* known_block, int* plain_bytes) {
         case 12: *qtype = B200Q_Q4_K; return true;
         case 13: *qtype = B200Q_Q5_K; return true;
         case 14: *qtype = B200Q_Q6_K; return true;
-        case 20: case 39: *qtype = B200Q_MXFP4; return true;
-        case 21: *qtype = B200Q_MXFP6_E2M3; return true;
-        case 22: *qtype = B200Q_MXFP6_E3M2; return true;
+        case 39: if (ref_style) return false; *qtype = B200Q_MXFP4; return true;
+        case 20: if (!ref_style) return false; *qtype = B200Q_MXFP4; return true;
+        case 21: if (!ref_style) return false; *qtype = B200Q_MXFP6_E2M3; return true;
+        case 22: if (!ref_style) return false; *qtype = B200Q_MXFP6_E3M2; return true;
         default: return false;
     }
 }
@@ -235,7 +238,7 @@ int b200q_gguf_open(const char* path, int flags, b200q_gguf** out) {
         t.rel_offset = r.get<uint64_t>();
         if (!r.ok) return bail(B200Q_ERR_INVALID, "file ends inside the tensor directory");
         int block = 0, plain = 0;
-        if (!map_type(t.ggml_type, &t.qtype, &block, &plain))
+        if (!map_type(t.ggml_type, ref_style, &t.qtype, &block, &plain))
             return bail(B200Q_ERR_UNSUPPORTED, "tensor '" + t.name + "' has unsupported GGUF tensor type " + std::to_string(t.ggml_type));
         unsigned __int128 elems = 1;
         for (uint32_t d = 0; d < t.n_dims; d++) {

@@ -167,3 +167,37 @@ def test_metadata_key_table():
     assert md.vocab_size == 32000 and md.rms_norm_eps == 1e-5 and md.embedded_tokenizer_json == "{}"
     names = layer_tensor_names(3)
     assert names["attn_qkv"] == "blk.3.attn_qkv.weight" and names["ffn_down"] == "blk.3.ffn_down.weight"
+
+
+def test_type_ids_20_to_22_mean_mxfp_only_in_the_reference_dialect(tmp_path):
+    """The reference's enum gives ids 20/21/22 to MXFP4 / MXFP6 (src/loader/tensor_type.rs:31-33); ggml gives them to
+    IQ4_NL / IQ3_S / IQ2_S and writes MXFP4 as 39. A file read in the ggml dialect must not decode an IQ tensor
+    as MXFP: the open fails with the reference's 'unsupported tensor type' class of error."""
+    n, k = 4, 64
+    name = "blk.0.ffn_up.weight"
+    for type_id in (20, 21, 22):
+        head = b"GGUF" + struct.pack("<IQQ", 3, 1, 0)
+        blob = head + _tinfo(name, [k, n], type_id, 0) + b"\0" * 64 + b"\0" * (n * k)
+        path = tmp_path / f"ggml_{type_id}.gguf"
+        path.write_bytes(blob)
+        with pytest.raises(B200QError) as e:
+            GgufLoader(path)
+        assert e.value.status == _lib.ERR_UNSUPPORTED and str(type_id) in str(e.value)
+    # the same ids in the reference's dialect: its own byte layouts
+    rng = synth.rng_for(12)
+    data = synth.gen_packed(synth.MXFP4, synth.RF, n * k, rng)
+    head = b"GGUF" + struct.pack("<IQQ", 3, 1, 0)
+    info_len = 8 + len(name) + 4 + 16 + 4 + 8
+    offset = len(head) + info_len
+    path = tmp_path / "ref_20.gguf"
+    path.write_bytes(head + _tinfo(name, [n, k], 20, offset) + bytes(data))
+    L = GgufLoader(path, reference_fixture=True)
+    lt = L.lazy_tensors[name]
+    assert (lt.n, lt.k, lt.qtype, lt.size) == (n, k, synth.MXFP4, n * k // 32 * 17)
+    L.close()
+    # and ggml's MXFP4 id is not part of the reference's enum
+    path = tmp_path / "ref_39.gguf"
+    path.write_bytes(head + _tinfo(name, [n, k], 39, offset) + bytes(data))
+    with pytest.raises(B200QError) as e:
+        GgufLoader(path, reference_fixture=True)
+    assert e.value.status == _lib.ERR_UNSUPPORTED

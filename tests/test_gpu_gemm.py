@@ -159,3 +159,41 @@ def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
     assert float(np.max(np.abs(y[:, rows] - ref))) / scale <= TOL
     assert np.all(np.isfinite(y))
     w.free()
+
+
+@pytest.mark.parametrize("case", ["mxfp4-huge", "mxfp4-tiny", "mxfp4-nan-free-mix", "q4k-big-d", "q8_0-big-d"])
+def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
+    """The tensor-memory prefill kernels form block scales in f16. The upload scans the scale bytes: a tensor whose
+    scales (or weights) leave the f16 range takes the next more careful kernel, down to the fp32 decode kernels, so
+    that m > 8 gives what m <= 8 gives. Exponent bytes 0x00, 0x40, 0x90 and 0xF0; f16 d of 2000 and 30000."""
+    be = backend()
+    n, k, m = 256, 512, 64
+    rng = synth.rng_for(8800 + len(case))
+    if case.startswith("mxfp4"):
+        qt = synth.MXFP4
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+        blocks = data.reshape(-1, 17)
+        if case == "mxfp4-huge":
+            blocks[:, 0] = 0x90          # 2^17: weights up to 7.9e5, beyond f16
+        elif case == "mxfp4-tiny":
+            blocks[:, 0] = 0x40          # 2^-63: every weight below the smallest f16
+        else:
+            blocks[::7, 0] = 0x00        # a few vanishing blocks among ordinary ones
+            blocks[3::11, 0] = 0x40
+    elif case == "q4k-big-d":
+        qt = synth.Q4_K
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+        blocks = data.reshape(-1, 144)
+        blocks[:, 0:2] = np.frombuffer(np.float16(2000.0).tobytes(), dtype=np.uint8)      # d * 63 overflows f16
+    else:
+        qt = synth.Q8_0
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+        blocks = data.reshape(-1, 34)
+        blocks[:, 0:2] = np.frombuffer(np.float16(30000.0).tobytes(), dtype=np.uint8)     # weights up to 3.8e6
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    ref = reference(oracle, qt, synth.GGUF, data, n, k, x)
+    assert np.all(np.isfinite(ref)) and np.all(np.isfinite(y))
+    assert rel_err(y, ref) <= TOL
+    w.free()

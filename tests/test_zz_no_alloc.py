@@ -52,6 +52,39 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(oracle):
     w.free()
 
 
+@pytest.mark.parametrize("qt,n,k,m", [(synth.Q8_0, 256, 1024, 96), (synth.MXFP4, 192, 2048, 40), (synth.Q6_K, 128, 512, 130),
+                                      (synth.Q4_K, 256, 320, 64), (synth.Q4_K, 128, 8192, 1024)],
+                         ids=["q8_0", "mxfp4", "q6_k", "q4_k-k320", "q4_k-at-the-limit"])
+def test_noalloc_other_formats_and_the_size_limit(oracle, qt, n, k, m):
+    """Formats other than Q4_K (and Q4_K rows that are not whole super-blocks) take the kernel whose weight tile is
+    staged in shared memory; the last case sits exactly on m * k = 8,388,608. Free device memory must not move
+    across a call: nothing is allocated, not even on the first use of a format."""
+    from gpu_util import QuantizedWeight, backend, rel_err
+    be = backend()
+    rng = synth.rng_for(9200 + qt + k)
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    x = synth.gen_activations(m, k, rng)
+    wf = oracle.dequantize(qt, synth.GGUF, data, n * k, threads=8).reshape(n, k)
+    ref = oracle.matmul_f32(x, wf, nk=True, threads=8)
+    y0 = _run(be, w, x, m, noalloc=True)          # warm-up: kernel attributes, the array's address
+    info = _lib.DeviceInfo()
+    _lib.check(be.lib.b200q_get_device_info(be.ctx, ctypes.byref(info)))
+    free_before = info.free_mem
+    xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
+    yb = be.allocate_buffer(m * n * 4)
+    _lib.check(be.lib.b200q_get_device_info(be.ctx, ctypes.byref(info)))
+    free_before = info.free_mem
+    _lib.check(be.lib.b200q_matmul_noalloc(be.ctx, w.handle, xb.ptr, yb.ptr, m))
+    be.synchronize()
+    _lib.check(be.lib.b200q_get_device_info(be.ctx, ctypes.byref(info)))
+    assert info.free_mem == free_before
+    y1 = yb.to_numpy(np.float32, m * n).reshape(m, n)
+    assert rel_err(y0, ref) <= TOL and rel_err(y1, ref) <= TOL
+    assert rel_err(y1, _run(be, w, x, m, noalloc=False)) <= TOL
+    xb.free(); yb.free(); w.free()
+
+
 def test_noalloc_refuses_what_does_not_fit():
     from gpu_util import QuantizedWeight, backend
     be = backend()
