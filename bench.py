@@ -109,10 +109,20 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
-def cpu_step_sample(m, threads):
-    """Layer 0 of the step (7 products) on the CPU oracle: dequantise to fp32, then cpu_matmul_f32."""
+def step_config(m, gpus):
+    """The `config` object, identical in both arms (this library and --impl reference)."""
+    return {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "products": 169, "m": m, "layout": "GGUF",
+            "packed_bytes_per_step": STEP_BYTES, "parallelism": "replicas" if gpus > 1 else "single",
+            "l2": "inputs larger than L2 (340 MB streamed per step)"}
+
+
+def cpu_step(m, threads, products=None):
+    """The step (or its first `products` products) on the CPU oracle, the composition the reference's own bench
+    times (benches/matmul_bench.rs:360-365): dequantise the tensor to fp32, then cpu_matmul_f32."""
     from oracle import cpu_oracle as orc
-    ops = synth.qwen2_0p5b_step()[:7]
+    ops = synth.qwen2_0p5b_step()
+    if products:
+        ops = ops[:products]
     rng = synth.rng_for(synth.CONFIG_SEEDS[3])
     ws = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for _, qt, n, k in ops]
     xs = [synth.gen_activations(m, k, rng) for _, _, _, k in ops]
@@ -127,29 +137,45 @@ def cpu_step_sample(m, threads):
 
 
 def run_reference(args, rank, world):
-    """The reference's CPU path (oracle port of its dequant + cpu_matmul_f32 composition) on all host threads."""
+    """The reference's CPU path (oracle port of its dequant + cpu_matmul_f32 composition) on all host threads, one whole
+    step (all 169 products) per timed step."""
     if rank != 0:
         return
-    from oracle import cpu_oracle as orc
     threads = host_threads()
-    step, nbytes = cpu_step_sample(args.m, threads)
-    for _ in range(args.warmup):
+    step, nbytes = cpu_step(args.m, threads)
+    assert nbytes == STEP_BYTES
+    for _ in range(max(args.warmup, 1)):      # also warms the OpenMP pool and the page cache of the temporaries
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     gbs = nbytes / dt / 1e9
-    sample = f"layer 0 of the step (7 products, {nbytes} packed bytes) per step, all {threads} host threads"
+    sample = f"the whole step (169 products, {nbytes} packed bytes) per timed step, all {threads} host threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC % args.m, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "m": args.m, "layout": "GGUF",
-                   "l2": "n/a (CPU)"},
+        "config": step_config(args.m, args.gpus),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
+
+
+def step_traffic(m):
+    """DRAM bytes one launch of the step kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture
+    summarised under profiles/), or None when the kernel source has changed since that capture was taken."""
+    import hashlib
+    tp = os.path.join(ROOT, "profiles", "gemv_i8_kernel_qwen2_decode_step.md")
+    src = os.path.join(ROOT, "rocmforge_b200", "csrc", "gemv_i8.cu")
+    if not (os.path.exists(tp) and os.path.exists(src)):
+        return None
+    text = open(tp).read()
+    want = re.search(r"source_sha256\(gemv_i8\.cu\)\s*=\s*([0-9a-f]{64})", text)
+    hit = re.search(r"dram_bytes_per_launch\(m=%d\)\s*=\s*([0-9]+)" % m, text)
+    if not want or not hit or hashlib.sha256(open(src, "rb").read()).hexdigest() != want.group(1):
+        return None
+    return int(hit.group(1))
 
 
 def time_matmul(be, w, m, steps, warmup, x_dtype=0):
@@ -192,11 +218,11 @@ def gemm_leg(be, peaks, steps):
     for n, k in synth.LLAMA7B_SHAPES:
         data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
         w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
-        for m in (512, 2048):
+        for m in (256, 512, 2048):
             ms = time_matmul(be, w, m, steps, 3)
             rows.append({"n": n, "k": k, "m": m, "ms": ms, "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12})
         w.free()
-    head = rows[0]
+    head = rows[1]
     return {"metric": "Q4_K prefill GEMM TFLOP/s at M=512", "workload": "llama-2-7b ffn_up Q4_K [11008,4096], M=512",
             "value": head["tflops"], "unit": "TFLOP/s", "peak": peaks["bf16_tflops"], "frac": head["tflops"] / peaks["bf16_tflops"],
             "peak_source": peaks["source"], "operands": "f16 x f16 -> fp32 (tcgen05, TMEM accumulators)", "shapes": rows}
@@ -242,7 +268,7 @@ def formats_leg(be, peaks, steps):
     from rocmforge_b200.backend import QuantizedWeight
     n = k = 8192
     rows = []
-    for qname in ("Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "MXFP4"):
+    for qname in ("Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "MXFP4", "MXFP6_E2M3", "MXFP6_E3M2", "Q2_K", "Q3_K"):
         qt = synth.QNAMES.index(qname)
         w = QuantizedWeight(be, synth.gen_packed(qt, synth.GGUF, n * k, synth.rng_for(9000 + qt)), qt, synth.GGUF, n, k)
         ms1 = time_matmul(be, w, 1, steps * 2, 3)
@@ -252,7 +278,48 @@ def formats_leg(be, peaks, steps):
                      "prefill_tflops": 2.0 * 512 * n * k / (ms512 * 1e-3) / 1e12,
                      "prefill_frac_of_peak": 2.0 * 512 * n * k / (ms512 * 1e-3) / 1e12 / peaks["bf16_tflops"]})
         w.free()
-    return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)", "rows": rows}
+    return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)",
+            "note": "MXFP6_E3M2, Q2_K and Q3_K have no tensor-core decode kernel (CUDA-core kernel at m = 1); MXFP6, Q2_K and Q3_K "
+                    "prefill on the shared-memory-operand tensor-core kernel", "rows": rows}
+
+
+def config5_leg(be, peaks, steps):
+    """BASELINE config 5: MXFP4 and MXFP6 at the Llama-70B FFN shape [28672, 8192], m = 1 (packed GB/s) and m = 64, 512
+    (TFLOP/s), single launches, device-resident operands. Fractions use the FORMAT's bytes (17 / 25 bytes per 32
+    weights), not the bytes of the decode image."""
+    from rocmforge_b200.backend import QuantizedWeight
+    n, k = synth.LLAMA70B_FFN_SHAPES[0]
+    rows = []
+    for qname in ("MXFP4", "MXFP6_E2M3"):
+        qt = synth.QNAMES.index(qname)
+        w = QuantizedWeight(be, synth.gen_packed(qt, synth.GGUF, n * k, synth.rng_for(synth.CONFIG_SEEDS[5] + qt)), qt, synth.GGUF, n, k)
+        ms1 = time_matmul(be, w, 1, steps * 2, 3)
+        row = {"qtype": qname, "m1_ms": ms1, "m1_GB/s": w.packed_bytes / (ms1 * 1e-3) / 1e9,
+               "m1_frac_of_hbm": w.packed_bytes / (ms1 * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        for m in (64, 512):
+            ms = time_matmul(be, w, m, steps, 3)
+            row[f"m{m}_ms"] = ms
+            row[f"m{m}_tflops"] = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            row[f"m{m}_frac_of_peak"] = row[f"m{m}_tflops"] / peaks["bf16_tflops"]
+        rows.append(row)
+        w.free()
+    return {"workload": "llama-70b ffn [28672, 8192], MXFP4 and MXFP6 (E2M3), single launches", "rows": rows}
+
+
+def config2_leg(be, steps):
+    """BASELINE config 2: Q8_0 [896, 896] and [4864, 896], m = 1, 16, 128, 512. These products are launch-bound (0.85 and
+    4.6 MB of weights): the figure is the time of one launch in a back-to-back series."""
+    from rocmforge_b200.backend import QuantizedWeight
+    rows = []
+    for n in (896, 4864):
+        w = QuantizedWeight(be, synth.gen_packed(synth.Q8_0, synth.GGUF, n * 896, synth.rng_for(synth.CONFIG_SEEDS[2] + n)),
+                            synth.Q8_0, synth.GGUF, n, 896)
+        for m in (1, 16, 128, 512):
+            ms = time_matmul(be, w, m, steps * 2, 3)
+            rows.append({"n": n, "k": 896, "m": m, "us": ms * 1e3, "packed_GB/s": w.packed_bytes / (ms * 1e-3) / 1e9,
+                         "tflops": 2.0 * m * n * 896 / (ms * 1e-3) / 1e12})
+        w.free()
+    return {"workload": "Q8_0 [896, 896] and [4864, 896] (qwen2-0.5b attention / FFN shapes), single launches", "rows": rows}
 
 
 def shard_leg(be, rank, world, steps):
@@ -420,24 +487,17 @@ def main():
     ms_step = ms / args.steps
     per_gpu = STEP_BYTES / (ms_step * 1e-3) / 1e9
     value = world * per_gpu
-    traffic = None
-    # DRAM bytes per algorithmic byte of the step kernel, from the committed ncu capture of this workload
-    tp = os.path.join(ROOT, "profiles", "gemv_mma_kernel_qwen2_decode_step.md")
-    if os.path.exists(tp):
-        hit = re.search(r"dram_bytes_per_algorithmic_byte\s*=\s*([0-9.]+)", open(tp).read())
-        if hit:
-            traffic = int(float(hit.group(1)) * STEP_BYTES)
+    traffic = step_traffic(m)
 
     out = {
         "metric": METRIC % m, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "qwen2-0.5b-q4_k_m-decode-step-matmul-only", "products": len(W), "m": m, "layout": "GGUF",
-                   "packed_bytes_per_step": STEP_BYTES, "parallelism": "replicas" if world > 1 else "single",
-                   "l2": "inputs larger than L2 (340 MB streamed per step)"},
+        "config": step_config(m, world),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": per_gpu / peaks["hbm_gbs"], "traffic": traffic, "peak_source": peaks["source"],
-                     "kernel": "gemv_mma_kernel<1> (one grouped launch = one step)", "launches_per_step": batch.launches},
+                     "kernel": "gemv_i8_kernel (one grouped launch = one step; back-to-back launches overlap their prologues through programmatic dependent launch)",
+                     "launches_per_step": batch.launches},
         "clocks": clocks, "gpu_launches": batch.launches * args.steps,
     }
 
@@ -461,10 +521,27 @@ def main():
                       "d2h_bytes_per_step": int(hy.numel() * 4), "ms_per_step": dt * 1e3,
                       "api": "b200q_batch_run_host: pinned host activations in (one H2D copy), outputs stored by the kernel straight into the pinned host buffer, weights resident (uploaded once)"}
         if world == 1:
+            # ---- the same step with 8 activation rows (config 3 is m = 1 and m = 8) --------------------------------
+            rng8 = synth.rng_for(synth.CONFIG_SEEDS[3] + 8)
+            batch8 = DeviceBatch(be, W, 8)
+            batch8.set_inputs([synth.gen_activations(8, k, rng8) for _, _, _, k in ops])
+            for _ in range(3):
+                batch8.run()
+            be.synchronize()
+            be.timer_start()
+            for _ in range(args.steps):
+                batch8.run()
+            ms8 = be.timer_stop_ms() / args.steps
+            out["decode_m8"] = {"workload": "the same 169-product step with m = 8", "ms_per_step": ms8,
+                                "GB/s": STEP_BYTES / (ms8 * 1e-3) / 1e9, "frac": STEP_BYTES / (ms8 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                "traffic": step_traffic(8), "launches_per_step": batch8.launches}
+            batch8.free()
             # ---- prefill GEMM (second half of the metric) and a single large Q4_K GEMV --------------------------
             out["gemm"] = gemm_leg(be, peaks, 10)
             out["mlp"] = mlp_leg(be, peaks, 10)
             out["formats"] = formats_leg(be, peaks, 10)
+            out["config5"] = config5_leg(be, peaks, 10)
+            out["config2"] = config2_leg(be, 10)
             rng = synth.rng_for(4242)
             big = QuantizedWeight(be, synth.gen_packed(synth.Q4_K, synth.GGUF, 65536 * 4096, rng), synth.Q4_K, synth.GGUF, 65536, 4096)
             msb = time_matmul(be, big, 1, 20, 3)
@@ -472,18 +549,28 @@ def main():
                                   "frac_of_hbm": big.packed_bytes / (msb * 1e-3) / 1e9 / peaks["hbm_gbs"]}
             big.free()
             # ---- CPU baseline (oracle port of the reference path) on the host cores ---------------------------
-            from oracle import cpu_oracle as orc
             threads = host_threads()
-            step, nb = cpu_step_sample(m, threads)
-            step()
+            step, nb = cpu_step(m, threads)
+            step()                              # warms the OpenMP pool
             t0 = time.perf_counter()
             reps = 0
-            while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 500):
+            while reps < 3 or (time.perf_counter() - t0 < 12.0 and reps < 200):
                 step()
                 reps += 1
             dtc = (time.perf_counter() - t0) / reps
+            # the "faithful" figure: the reference's matmul is single-threaded (src/tensor/matmul.rs:219-233)
+            step1, nb1 = cpu_step(m, 1, products=7)
+            step1()
+            t0 = time.perf_counter()
+            reps1 = 0
+            while reps1 < 2 or (time.perf_counter() - t0 < 6.0 and reps1 < 50):
+                step1()
+                reps1 += 1
+            dt1 = (time.perf_counter() - t0) / reps1
             out["cpu_baseline"] = {"value": nb / dtc / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-                                   "sample": f"layer 0 of the step (7 products, {nb} packed bytes), {reps} repetitions"}
+                                   "sample": f"the whole step (169 products, {nb} packed bytes), {reps} repetitions",
+                                   "single_thread": {"value": nb1 / dt1 / 1e9, "unit": "GB/s", "cores": 1,
+                                                     "sample": f"layer 0 of the step (7 products, {nb1} packed bytes), {reps1} repetitions"}}
         else:
             out["shard"] = shard_leg(be, rank, world, 10)
     if rank == 0:

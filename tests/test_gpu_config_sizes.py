@@ -20,10 +20,16 @@ TOL_PREFILL = 2e-3
 
 
 def sampled_reference(oracle, qt, data, n, k, x, rows):
+    """x . W[rows]^T on the CPU. A row of k weights may start inside a block (k = 896 is 3.5 super-blocks): the blocks
+    that cover the row are dequantised and the row cut out of them."""
     bb, be_ = synth.block_bytes(qt, synth.GGUF), synth.block_elems(qt)
     blocks = np.frombuffer(bytes(data), dtype=np.uint8).reshape(-1, bb)
-    sel = np.concatenate([blocks[r * k // be_:(r + 1) * k // be_] for r in rows]).reshape(-1)
-    wsel = oracle.dequantize(qt, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    wsel = np.empty((rows.size, k), dtype=np.float32)
+    for i, r in enumerate(rows):
+        e0 = int(r) * k
+        b0, b1 = e0 // be_, -(-(e0 + k) // be_)
+        part = oracle.dequantize(qt, synth.GGUF, blocks[b0:b1].reshape(-1), (b1 - b0) * be_)
+        wsel[i] = part[e0 - b0 * be_: e0 - b0 * be_ + k]
     return oracle.matmul_f32(x, wsel, nk=True, threads=8)
 
 

@@ -120,7 +120,8 @@ def test_config3_qwen_step_matrices(be, oracle, name, qt, n, k, m):
 
 
 def test_shards_concatenate_to_the_whole(be, oracle):
-    """Output-feature shards of one tensor give, side by side, exactly the unsharded result."""
+    """Output-feature shards of one tensor give, side by side, the unsharded result: to rounding, not bit for bit,
+    because a launch cuts a row's k-range where its work split falls, and the pieces are added in that order."""
     rng = synth.rng_for(77)
     n, k, m = 1024, 2048, 4
     for qt in (synth.Q4_K, synth.MXFP4, synth.MXFP6_E2M3):
@@ -135,7 +136,7 @@ def test_shards_concatenate_to_the_whole(be, oracle):
                 assert w.n_local == n // g and w.row0 == r * n // g
                 parts.append(gpu_matmul(be, w, x, m))
                 w.free()
-            assert np.array_equal(np.concatenate(parts, axis=1).view(np.uint32), y.view(np.uint32))
+            assert rel_err(np.concatenate(parts, axis=1), y) <= 2e-6
         whole.free()
 
 

@@ -49,12 +49,12 @@ def test_scatter_argument_errors():
     be = backend()
     rng = synth.rng_for(6200)
     n, k = 256, 512
-    data = synth.gen_packed(synth.MXFP6_E2M3, synth.GGUF, n * k, rng)
-    w = QuantizedWeight(be, data, synth.MXFP6_E2M3, synth.GGUF, n, k, shard_rank=1, shard_count=2)
+    data = synth.gen_packed(synth.MXFP6_E3M2, synth.GGUF, n * k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP6_E3M2, synth.GGUF, n, k, shard_rank=1, shard_count=2)
     x = be.allocate_buffer(k * 4)
     y = be.allocate_buffer(n * 4)
     with pytest.raises(B200QError) as e:
-        w.matmul_scatter(x, [y, y], 1, n)            # MXFP6 has no tensor-core decode kernel
+        w.matmul_scatter(x, [y, y], 1, n)            # MXFP6 E3M2 has no tensor-core decode kernel
     assert e.value.status == _lib.ERR_UNSUPPORTED
     with pytest.raises(B200QError) as e:
         w.matmul_scatter(x, [y], 1, n // 2)          # ldy ends before this shard's columns
