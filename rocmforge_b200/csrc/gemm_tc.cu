@@ -730,18 +730,6 @@ struct PeerMaps {
     CUtensorMap m[7];
 };
 
-#ifdef B200Q_SK_TRACE
-// Scratch build only: time stamps go to shared memory and are copied out at the end of the kernel.
-__device__ long long g_sk_trace[160 * 128];
-#define SKT(i) do { if (lane == 0 && warp == 4 && (i) < 96) s_trace[(i)] = clock64(); } while (0)
-// cycle sums of one role's waits: SKA_BEGIN; <wait>; SKA_END(slot) adds the elapsed cycles to s_trace[96 + slot]
-#define SKA_BEGIN long long ska_t = clock64()
-#define SKA_END(slot) do { if (lane == 0) s_trace[96 + (slot)] += clock64() - ska_t; } while (0)
-#else
-#define SKT(i)
-#define SKA_BEGIN
-#define SKA_END(slot)
-#endif
 template <int QF>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -777,10 +765,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
     // staging tile of the epilogue: 64 activation rows x 128 weight rows of fp32 (one TMA store box)
     float* stg = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(stored + 1) + ((128u - (smem_u32(stored + 1) & 127u)) & 127u));
-#ifdef B200Q_SK_TRACE
-    long long* s_trace = reinterpret_cast<long long*>(stg + 64 * BM);
-    if (threadIdx.x < 128) s_trace[threadIdx.x] = 0;
-#endif
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, nctas = gridDim.x;
@@ -828,9 +812,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int s = it & (STAGES - 1);                    // first stage of the pair
                     const uint32_t ph = (it >> 2) & 1;
                     const uint32_t fb = smem_u32(&full[s >> 1]);
-                    { SKA_BEGIN;
+                    {
                     if (!mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
-                    SKA_END(3); }
+ }
                     mbar_arrive_expect_tx(fb, 2u * (uint32_t)b_stage_bytes);
                     tma_load_2d(smem_u32(sB + s * b_stage_bytes), &tmap_x, kb * BK, tok0, fb);
                     tma_load_2d(smem_u32(sB + (s + 1) * b_stage_bytes), &tmap_x, (kb + 1) * BK, tok0, fb);
@@ -859,18 +843,15 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int u = u0; u < u1 && ok; seg++) {
                 const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
                 // the previous segment's accumulator must have been read out
-                { SKA_BEGIN;
                 if (!mbar_wait(smem_u32(dfree), (uint32_t)(seg & 1) ^ 1, abort_flag, a.status, 10)) break;
-                SKA_END(0); }
                 tc_fence_after();
                 for (int kb = 4 * sb0; kb < 4 * sb1; kb += 2, it += 2) {
                     const uint32_t s = (uint32_t)it & (STAGES - 1);     // first stage of the pair
                     const uint32_t ph = ((uint32_t)it >> 2) & 1;
-                    { SKA_BEGIN;
+                    {
                     if (!mbar_wait(fu0 + (s >> 1) * 8, ph, abort_flag, a.status, 2)) { ok = false; break; }
-                    SKA_END(1); }
+ }
                     tc_fence_after();
-                    SKA_BEGIN;
                     const uint32_t at = at0 + s * A_SLOT_COLS, bl = blo0 + s * b_step;
                     // 16 k further: 8 TMEM columns on the A side, 32 bytes (+2 encoded) inside the swizzle atom on the B
                     // side; the second stage of the pair is one A slot / one B stage further on
@@ -885,7 +866,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     umma_ts_f16_acc(tmem_base, at2 + 16, bl2 + 4, bhi, idesc);
                     umma_ts_f16_acc(tmem_base, at2 + 24, bl2 + 6, bhi, idesc);
                     umma_commit(em0 + (s >> 1) * 8);
-                    SKA_END(2);
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(accum));
@@ -999,13 +979,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int u = u0; u < u1 && ok; seg++) {
             const int tile = u / k.nsb, sb0 = u - tile * k.nsb, sb1 = min(k.nsb, sb0 + (u1 - u));
             const int row0 = (tile % k.tiles_x) * BM, tok0 = (tile / k.tiles_x) * a.bn;
-            SKT(seg * 32 + 0);
             for (int sb = sb0; sb < sb1 && ok; sb++, rit++) {
                 const int rs = rit % RS;
                 const uint32_t rph = (uint32_t)(rit / RS) & 1;
-                { SKA_BEGIN;
                 if (lane == 0) ok = mbar_wait(smem_u32(&raw_full[rs]), rph, abort_flag, a.status, 8);
-                if (warp == 4) SKA_END(4); }
                 ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
                 if constexpr (QF == 0 || QF == 5) {
@@ -1053,21 +1030,17 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     }
                     // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
                     if ((c & 1) == 0) {
-                        SKA_BEGIN;
                         if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
-                        if (warp == 4) SKA_END(5);
                         ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                         if (!ok) break;
                         tc_fence_after();
                     }
                     tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
                     if (c & 1) {
-                        SKA_BEGIN;
                         tmem_st_wait();
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
-                        if (warp == 4) SKA_END(6);
                     }
                 }
                 } else if constexpr (QF == 2) {
@@ -1247,14 +1220,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             if (!ok) break;
             // ------------------------------------------------------------ epilogue of this segment
             if (seg == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // the row scales come from the kernel ahead
-            SKT(seg * 32 + 1);
             if (lane == 0) ok = mbar_wait(smem_u32(accum), (uint32_t)(seg & 1), abort_flag, a.status, 6);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             const bool head = sb0 == 0, whole = head && sb1 == k.nsb;
             const int row = row0 + r;
-            SKT(seg * 32 + 2);
             // partial sums this (owning) CTA has to add: the CTAs after it, until the tile's k range is covered
             int p_end = cta + 1;
             bool pf = false;   // the first partial tile arrives in shared memory (prefetcher warp)
@@ -1278,7 +1249,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             float* myslot = k.ws + (size_t)cta * SK_SLOT_FLOATS;
-            SKT(seg * 32 + 3);
             if (head && a.staged_epilogue) {
                 // Finished tile -> shared memory -> TMA stores. Every warp owns a 32 x 32 block of the round
                 // (its 32 weight rows x 32 activation rows), stages it in a private 4 KB buffer and stores it
@@ -1292,7 +1262,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int c0 = rnd + half_off;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)min(c0, 480), v);
-                    SKT(seg * 32 + 4 + (rnd >> 6) * 5);
                     if (rnd == last_rnd) {
                         // every TMEM read of this warp is complete: the accumulator may be overwritten
                         tc_fence_before();
@@ -1315,11 +1284,9 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(ps + j * BM));
                         }
                     }
-                    SKT(seg * 32 + 5 + (rnd >> 6) * 5);
                     // this warp's previous store must have finished READING its buffer before it is overwritten
                     if (lane == 0) bulk_wait_read0();
                     __syncwarp();
-                    SKT(seg * 32 + 6 + (rnd >> 6) * 5);
                     // row scales of the block's 32 activation rows: 128-byte aligned, read four at a time (the
                     // scale array is padded, and rows past m are clipped by the store)
                     const float4* sc4 = reinterpret_cast<const float4*>(a.xscale + tok0 + c0);
@@ -1333,14 +1300,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
-                    SKT(seg * 32 + 7 + (rnd >> 6) * 5);
                     if (lane == 0 && c0 < a.bn) {
                         tma_store_2d(&tmap_y, smem_u32(wstg), row0 + q * 32, tok0 + c0);
                         // scattered product: the same block into the other GPUs' outputs, over NVLink
                         for (int pp = 0; pp < a.n_extra; pp++) tma_store_2d(&peers.m[pp], smem_u32(wstg), row0 + q * 32, tok0 + c0);
                         bulk_commit();
                     }
-                    SKT(seg * 32 + 8 + (rnd >> 6) * 5);
                 }
                 if (!freed) {   // a wait gave up before the last read: the MMA thread leaves through the abort flag
                     tc_fence_before();
@@ -1380,9 +1345,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(dfree));
             }
-            SKT(seg * 32 + 24);
             if (!head) fence_due = true;   // partial sums written: fence and count later (see above)
-            SKT(seg * 32 + 25);
             u += sb1 - sb0;
         }
         if (fence_due) fence_and_count();
@@ -1391,10 +1354,6 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // ---------------------------------------------------------------- teardown (every path ends here)
     tc_fence_before();
     __syncthreads();
-#ifdef B200Q_SK_TRACE
-    if (threadIdx.x < 128) g_sk_trace[blockIdx.x * 128 + threadIdx.x] = s_trace[threadIdx.x];
-    if (threadIdx.x == 0) g_sk_trace[blockIdx.x * 128 + 127] = clock64();
-#endif
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols) : "memory");
@@ -1622,11 +1581,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output %d) failed with code %d", who, p + 1, (int)r);
         }
     }
-#ifdef B200Q_SK_TRACE
-    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64 + 1024;
-#else
     constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64;
-#endif
     // the persistent kernel prefetches partial sums from its workspace: [slots * 256 activation rows, 128 weight rows] fp32
     CUtensorMap wsmap = map;
     auto make_wsmap = [&]() -> int {
@@ -1783,11 +1738,6 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
 
 }  // namespace
 
-#ifdef B200Q_SK_TRACE
-extern "C" int b200q_debug_read_sk_trace(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_sk_trace, sizeof(long long) * 160 * 128);
-}
-#endif
 bool gemm_tc_supported(const b200q_weight* w, int m) {
     // weights beyond the f16 range (seen by the upload's scan of the block scales) stay on the fp32 decode kernels
     return w->orient == B200Q_ORIENT_NK && m >= 1 && (w->k % BK) == 0 && w->n_local < 0x7FFFFF00ll && w->k < (1 << 30) &&
