@@ -44,6 +44,8 @@ constexpr int F_Q6K = fmt_of(Q6_K, GGUF);
 constexpr int F_Q80 = fmt_of(Q8_0, GGUF);
 constexpr int F_MX6 = fmt_of(MXFP6_E2M3, GGUF);
 constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
+constexpr int F_Q40 = fmt_of(Q4_0, GGUF);
+constexpr int F_Q5K = fmt_of(Q5_K, GGUF);
 
 // ---- item layouts (bytes inside one item; lane = 4 g + t; rows g and g+8 of the row tile; s = sub-block of 32
 // weights inside the item's 128). A "chunk" (g, s) is 16 bytes placed at chunk_pos(g, s) * 16 of its 512-byte area,
@@ -71,6 +73,11 @@ constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 //         [1024,1088)  per lane (g, s): E8M0 exponent of row g, of row g+8
 //         A code becomes the magnitude 2 * |e2m1(code)| through one byte-permute table look-up; positive and negative
 //         codes go through separate MMAs whose sums are subtracted.
+// Q4_0:   codes as Q4_K's (a block's 16 bytes are stored as they are); [1024,1152) per lane (g, s): f16 d(g), d(g+8)
+// Q5_K:   Q4_K's item followed by [1216,1472): per lane (g, s) the fifth bits of sub-block s of row g, then of row
+//         g+8, one word each: bit 8z+j = weight 4j+z, bit 8z+4+j = weight 16+4j+z (j, z = 0..3)
+constexpr int Q40_ITEM = 1152;
+constexpr int Q5K_ITEM = 1472;
 constexpr int MX4_ITEM = 1088;
 constexpr int Q4K_ITEM = 1216;
 constexpr int Q6K_ITEM = 1696;
@@ -347,6 +354,8 @@ __device__ __forceinline__ void mma_k16_u8s8_z(int (&c)[4], uint32_t a0, uint32_
 
 // ------------------------------------------------------------------------------------------- Q4_K (GGUF)
 // One row: acc += d * sc * (factor * sum q x_int) - dmin * m * (sum x) for the lane's sub-block of rows g, g+8.
+// Q5: the fifth bit of every code joins at bit 4 of its byte.
+template <bool Q5>
 __device__ __forceinline__ void item_q4k_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
     const int g = lane >> 2, t = lane & 3;
     const int cp = chunk_pos(g, t) * 16;
@@ -359,11 +368,102 @@ __device__ __forceinline__ void item_q4k_one(uint32_t it, const LaneB1& lb, int 
     const uint2 fSb = lds64(lb.f0 + h * lb.fh);
     const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
     const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
+    constexpr uint32_t ML = 0x0F0F0F0Fu, M4 = 0x10101010u;
+    uint32_t a[2][4] = {{wa.x & ML, wa.y & ML, wa.z & ML, wa.w & ML}, {wb.x & ML, wb.y & ML, wb.z & ML, wb.w & ML}};
+    uint32_t b[2][4] = {{(wa.x >> 4) & ML, (wa.y >> 4) & ML, (wa.z >> 4) & ML, (wa.w >> 4) & ML},
+                        {(wb.x >> 4) & ML, (wb.y >> 4) & ML, (wb.z >> 4) & ML, (wb.w >> 4) & ML}};
+    if constexpr (Q5) {
+        const uint2 hb = lds64(it + 1216 + lane * 8);
+        const uint32_t H[2] = {hb.x, hb.y};
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                a[r][j] |= (H[r] << (4 - j)) & M4;
+                b[r][j] |= (H[r] >> j) & M4;
+            }
+        }
+    }
+    int c[4], e[4];   // c: columns (limb 0, limb 1); e: columns (limb 2, zero)
+    mma_u8s8_z(c, a[0][0], a[1][0], a[0][1], a[1][1], q0.x, q0.y);
+    mma_u8s8_z(e, a[0][0], a[1][0], a[0][1], a[1][1], r0.x, r0.y);
+    mma_u8s8(c, a[0][2], a[1][2], a[0][3], a[1][3], q0.z, q0.w);
+    mma_u8s8(e, a[0][2], a[1][2], a[0][3], a[1][3], r0.z, r0.w);
+    mma_u8s8(c, b[0][0], b[1][0], b[0][1], b[1][1], q1.x, q1.y);
+    mma_u8s8(e, b[0][0], b[1][0], b[0][1], b[1][1], r1.x, r1.y);
+    mma_u8s8(c, b[0][2], b[1][2], b[0][3], b[1][3], q1.z, q1.w);
+    mma_u8s8(e, b[0][2], b[1][2], b[0][3], b[1][3], r1.z, r1.w);
+    // Q5_K: 32 five-bit codes times 21-bit activations can leave 32 bits, so its last limb joins in floating point
+    const float v0 = Q5 ? fmaf((float)(c[0] * 128 + c[1]), 128.0f, (float)e[0]) : (float)((c[0] * 128 + c[1]) * 128 + e[0]);
+    const float v1 = Q5 ? fmaf((float)(c[2] * 128 + c[3]), 128.0f, (float)e[2]) : (float)((c[2] * 128 + c[3]) * 128 + e[2]);
+    const float f = __uint_as_float(fSb.x), S = __uint_as_float(fSb.y);
+    const float A0 = d0.x * (float)(hs & 0xFFu), B0 = -d0.y * (float)((hs >> 8) & 0xFFu);
+    const float A1 = d1.x * (float)((hs >> 16) & 0xFFu), B1 = -d1.y * (float)(hs >> 24);
+    acc[0] = fmaf(A0, v0 * f, fmaf(B0, S, acc[0]));
+    acc[1] = fmaf(A1, v1 * f, fmaf(B1, S, acc[1]));
+}
+
+// Many rows: one MMA per sub-block and limb, the activation rows are the MMA's columns; lane (g, t) ends up with
+// rows g, g+8 x activation rows 2t, 2t+1.  acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}
+template <bool Q5>
+__device__ __forceinline__ void item_q4k_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint4 hdr = lds128(it + 1024 + g * 16);
+    const uint2 dd = lds64(it + 1152 + g * 8);
+    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
+    const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
+    const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
+    const uint32_t bp = lb.p + h * lb.sh;
+    constexpr uint32_t ML = 0x0F0F0F0Fu, M4 = 0x10101010u;
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        const int cp = chunk_pos(g, s) * 16 + 4 * t;
+        const uint32_t w0 = lds32(it + cp), w1 = lds32(it + 512 + cp);
+        const uint2 b0 = lds64(bp + s * 24), b1 = lds64(bp + s * 24 + 8), b2 = lds64(bp + s * 24 + 16);
+        const uint4 fSb = lds128(lb.f0 + (4 * h + s) * lb.fb);
+        uint32_t a0 = w0 & ML, a1 = w1 & ML, a2 = (w0 >> 4) & ML, a3 = (w1 >> 4) & ML;
+        if constexpr (Q5) {
+            const uint2 hb = lds64(it + 1216 + (4 * g + s) * 8);
+            a0 |= (hb.x << (4 - t)) & M4; a2 |= (hb.x >> t) & M4;
+            a1 |= (hb.y << (4 - t)) & M4; a3 |= (hb.y >> t) & M4;
+        }
+        int c0[4], c1[4], c2[4];
+        mma_u8s8_z(c0, a0, a1, a2, a3, b0.x, b0.y);
+        mma_u8s8_z(c1, a0, a1, a2, a3, b1.x, b1.y);
+        mma_u8s8_z(c2, a0, a1, a2, a3, b2.x, b2.y);
+        const float A0 = d0.x * (float)(hw[s] & 0xFFu), B0 = -d0.y * (float)((hw[s] >> 8) & 0xFFu);
+        const float A1 = d1.x * (float)((hw[s] >> 16) & 0xFFu), B1 = -d1.y * (float)(hw[s] >> 24);
+        const float fa = __uint_as_float(fSb.x), Sa = __uint_as_float(fSb.y), fb = __uint_as_float(fSb.z), Sb = __uint_as_float(fSb.w);
+        // 32 five-bit codes times 21-bit activations can leave 32 bits: the last limb joins in floating point
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            v[j] = Q5 ? fmaf((float)(c0[j] * 128 + c1[j]), 128.0f, (float)c2[j]) : (float)((c0[j] * 128 + c1[j]) * 128 + c2[j]);
+        const float v0 = v[0], v1 = v[1], v2 = v[2], v3 = v[3];
+        acc[0] = fmaf(A0, v0 * fa, fmaf(B0, Sa, acc[0]));
+        acc[1] = fmaf(A0, v1 * fb, fmaf(B0, Sb, acc[1]));
+        acc[2] = fmaf(A1, v2 * fa, fmaf(B1, Sa, acc[2]));
+        acc[3] = fmaf(A1, v3 * fb, fmaf(B1, Sb, acc[3]));
+    }
+}
+
+// ------------------------------------------------------------------------------------------- Q4_0 (GGUF)
+// acc += d * (factor * sum q x_int - 8 sum x) per block of 32 (the image stores 8 sum x).
+__device__ __forceinline__ void item_q40_one(uint32_t it, const LaneB1& lb, int h, float (&acc)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int cp = chunk_pos(g, t) * 16;
+    const uint4 wa = lds128(it + cp);
+    const uint4 wb = lds128(it + 512 + cp);
+    const uint32_t dd = lds32(it + 1024 + lane * 4);
+    const uint4 q0 = lds128(lb.p1 + h * lb.s1), q1 = lds128(lb.p1 + h * lb.s1 + 16);
+    const uint4 r0 = lds128(lb.p2 + h * lb.s2), r1 = lds128(lb.p2 + h * lb.s2 + 16);
+    const uint2 fSb = lds64(lb.f0 + h * lb.fh);
+    const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dd));
     constexpr uint32_t ML = 0x0F0F0F0Fu;
     const uint32_t a[2][4] = {{wa.x & ML, wa.y & ML, wa.z & ML, wa.w & ML}, {wb.x & ML, wb.y & ML, wb.z & ML, wb.w & ML}};
     const uint32_t b[2][4] = {{(wa.x >> 4) & ML, (wa.y >> 4) & ML, (wa.z >> 4) & ML, (wa.w >> 4) & ML},
                               {(wb.x >> 4) & ML, (wb.y >> 4) & ML, (wb.z >> 4) & ML, (wb.w >> 4) & ML}};
-    int c[4], e[4];   // c: columns (limb 0, limb 1); e: columns (limb 2, zero)
+    int c[4], e[4];
     mma_u8s8_z(c, a[0][0], a[1][0], a[0][1], a[1][1], q0.x, q0.y);
     mma_u8s8_z(e, a[0][0], a[1][0], a[0][1], a[1][1], r0.x, r0.y);
     mma_u8s8(c, a[0][2], a[1][2], a[0][3], a[1][3], q0.z, q0.w);
@@ -374,21 +474,14 @@ __device__ __forceinline__ void item_q4k_one(uint32_t it, const LaneB1& lb, int 
     mma_u8s8(e, b[0][2], b[1][2], b[0][3], b[1][3], r1.z, r1.w);
     const int v0 = (c[0] * 128 + c[1]) * 128 + e[0];
     const int v1 = (c[2] * 128 + c[3]) * 128 + e[2];
-    const float f = __uint_as_float(fSb.x), S = __uint_as_float(fSb.y);
-    const float A0 = d0.x * (float)(hs & 0xFFu), B0 = -d0.y * (float)((hs >> 8) & 0xFFu);
-    const float A1 = d1.x * (float)((hs >> 16) & 0xFFu), B1 = -d1.y * (float)(hs >> 24);
-    acc[0] = fmaf(A0, (float)v0 * f, fmaf(B0, S, acc[0]));
-    acc[1] = fmaf(A1, (float)v1 * f, fmaf(B1, S, acc[1]));
+    const float f = __uint_as_float(fSb.x), S8 = __uint_as_float(fSb.y);
+    acc[0] = fmaf(d.x, fmaf((float)v0, f, -S8), acc[0]);
+    acc[1] = fmaf(d.y, fmaf((float)v1, f, -S8), acc[1]);
 }
 
-// Many rows: one MMA per sub-block and limb, the activation rows are the MMA's columns; lane (g, t) ends up with
-// rows g, g+8 x activation rows 2t, 2t+1.  acc = {(g, 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)}
-__device__ __forceinline__ void item_q4k_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
+__device__ __forceinline__ void item_q40_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
     const int g = lane >> 2, t = lane & 3;
     const uint4 hdr = lds128(it + 1024 + g * 16);
-    const uint2 dd = lds64(it + 1152 + g * 8);
-    const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&dd.x));
-    const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&dd.y));
     const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
     const uint32_t bp = lb.p + h * lb.sh;
     constexpr uint32_t ML = 0x0F0F0F0Fu;
@@ -403,15 +496,12 @@ __device__ __forceinline__ void item_q4k_many(uint32_t it, const LaneBM& lb, int
         mma_u8s8_z(c0, a0, a1, a2, a3, b0.x, b0.y);
         mma_u8s8_z(c1, a0, a1, a2, a3, b1.x, b1.y);
         mma_u8s8_z(c2, a0, a1, a2, a3, b2.x, b2.y);
-        const float A0 = d0.x * (float)(hw[s] & 0xFFu), B0 = -d0.y * (float)((hw[s] >> 8) & 0xFFu);
-        const float A1 = d1.x * (float)((hw[s] >> 16) & 0xFFu), B1 = -d1.y * (float)(hw[s] >> 24);
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&hw[s]));
         const float fa = __uint_as_float(fSb.x), Sa = __uint_as_float(fSb.y), fb = __uint_as_float(fSb.z), Sb = __uint_as_float(fSb.w);
-        const float v0 = (float)((c0[0] * 128 + c1[0]) * 128 + c2[0]), v1 = (float)((c0[1] * 128 + c1[1]) * 128 + c2[1]);
-        const float v2 = (float)((c0[2] * 128 + c1[2]) * 128 + c2[2]), v3 = (float)((c0[3] * 128 + c1[3]) * 128 + c2[3]);
-        acc[0] = fmaf(A0, v0 * fa, fmaf(B0, Sa, acc[0]));
-        acc[1] = fmaf(A0, v1 * fb, fmaf(B0, Sb, acc[1]));
-        acc[2] = fmaf(A1, v2 * fa, fmaf(B1, Sa, acc[2]));
-        acc[3] = fmaf(A1, v3 * fb, fmaf(B1, Sb, acc[3]));
+        acc[0] = fmaf(d.x, fmaf((float)((c0[0] * 128 + c1[0]) * 128 + c2[0]), fa, -Sa), acc[0]);
+        acc[1] = fmaf(d.x, fmaf((float)((c0[1] * 128 + c1[1]) * 128 + c2[1]), fb, -Sb), acc[1]);
+        acc[2] = fmaf(d.y, fmaf((float)((c0[2] * 128 + c1[2]) * 128 + c2[2]), fa, -Sa), acc[2]);
+        acc[3] = fmaf(d.y, fmaf((float)((c0[3] * 128 + c1[3]) * 128 + c2[3]), fb, -Sb), acc[3]);
     }
 }
 
@@ -818,8 +908,10 @@ __device__ __forceinline__ bool run_segment(const DOp& op, int rtb, int i0, int 
         if (!ok) return false;
         uint32_t it = ring.slot0 + ring.cslot * ring.slot_bytes;
         for (int c = 0; c < cnt; c++, it += item_bytes) {
-            if (KIND == DK_Q4K) {
-                if (MANY) item_q4k_many(it, lbm, h, acc, lane); else item_q4k_one(it, lb1, h, acc, lane);
+            if (KIND == DK_Q4K || KIND == DK_Q5K) {
+                if (MANY) item_q4k_many<KIND == DK_Q5K>(it, lbm, h, acc, lane); else item_q4k_one<KIND == DK_Q5K>(it, lb1, h, acc, lane);
+            } else if (KIND == DK_Q40) {
+                if (MANY) item_q40_many(it, lbm, h, acc, lane); else item_q40_one(it, lb1, h, acc, lane);
             } else if (KIND == DK_Q6K) {
                 if (MANY) item_q6k_many(it, lbm, h, acc, lane); else item_q6k_one(it, lb1, h, acc, lane);
             } else if (KIND == DK_MX4) {
@@ -1002,7 +1094,10 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         if (op.kind == DK_MX4) {
             prep_x<32, MANY, NW * 32, true>(op.x, op.ldx, op.k, m, ai, 1.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
-        } else if (op.kind != DK_Q6K) {   // scale groups of 32; only Q4_K uses the sums
+        } else if (op.kind == DK_Q40) {   // the image keeps 8 sum x
+            prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 8.0f);
+            if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
+        } else if (op.kind != DK_Q6K) {   // scale groups of 32; only Q4_K and Q5_K use the sums
             prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 1.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
         } else {
@@ -1027,6 +1122,8 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             else if (op.kind == DK_Q6K) ok = run_segment<DK_Q6K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else if (op.kind == DK_Q80) ok = run_segment<DK_Q80, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else if (op.kind == DK_MX4) ok = run_segment<DK_MX4, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else if (op.kind == DK_Q40) ok = run_segment<DK_Q40, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
+            else if (op.kind == DK_Q5K) ok = run_segment<DK_Q5K, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             else ok = run_segment<DK_MX6, MANY>(op, prev_b, i0, i1, ring, st, nx, lb1, lbm, m, red, pend, pend_rt, lane, warp);
             if (!ok) {
                 alive = false;
@@ -1216,6 +1313,76 @@ __global__ void __launch_bounds__(256) build_image_mx4_kernel(WView v, uint8_t* 
     *reinterpret_cast<uint16_t*>(it + 1024 + lane * 2) = (uint16_t)sc;
 }
 
+// Q4_0: the block's 16 code bytes as they are, f16 d per block.
+__global__ void __launch_bounds__(256) build_image_q40_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * Q40_ITEM;
+    uint32_t dd = 0;
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) {
+            const int64_t blk = (row * nh + h) * 4 + t;
+            const uint8_t* q = v.p[1] + blk * 16;
+            uint8_t o[16];
+            for (int b = 0; b < 16; b++) o[b] = q[b];
+            out = *reinterpret_cast<uint4*>(o);
+            dd |= (uint32_t)ld16(v.p[0] + blk * 2) << (16 * i);
+        }
+        *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = out;
+    }
+    *reinterpret_cast<uint32_t*>(it + 1024 + lane * 4) = dd;
+}
+
+// Q5_K: Q4_K's item plus the fifth bits.
+__global__ void __launch_bounds__(256) build_image_q5k_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ img, int n_rows, int nh,
+                                                               int64_t n_items) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t item = idx >> 5;
+    if (item >= n_items) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, t = lane & 3;
+    const int64_t T = item / nh;
+    const int h = (int)(item - T * nh);
+    uint8_t* it = img + item * Q5K_ITEM;
+    uint32_t hs = 0;
+    uint32_t dd[2] = {0u, 0u}, hb[2] = {0u, 0u};
+    for (int i = 0; i < 2; i++) {
+        const int64_t row = T * 16 + g + 8 * i;
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows) {
+            const int64_t hsi = row * nh + h;
+            const uint8_t* blk = raw + (hsi >> 1) * 176;   // d, dmin, scales[12], qh[32], qs[128]
+            const int j = 4 * (int)(hsi & 1) + t;           // sub-block of the super-block
+            const uint8_t* qh = blk + 16;
+            const uint8_t* qs = blk + 48 + 32 * (j >> 1);
+            uint8_t o[16];
+            for (int b = 0; b < 16; b++)
+                o[b] = (j & 1) ? (uint8_t)((qs[b] >> 4) | (qs[16 + b] & 0xF0)) : (uint8_t)((qs[b] & 0x0F) | ((qs[16 + b] & 0x0F) << 4));
+            out = *reinterpret_cast<uint4*>(o);
+            uint32_t H = 0;
+            for (int e = 0; e < 32; e++) {   // weight e of the sub-block: fifth bit = bit j of qh[e]
+                const uint32_t bit = (qh[e] >> j) & 1u;
+                const int z = e & 3, jj = (e & 15) >> 2;
+                H |= bit << (8 * z + (e < 16 ? jj : 4 + jj));
+            }
+            hb[i] = H;
+            uint32_t sc, mn;
+            q4k_scale_min(blk + 4, j, sc, mn);
+            hs |= (sc | (mn << 8)) << (16 * i);
+            dd[i] = ld32(blk);
+        }
+        *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = out;
+    }
+    *reinterpret_cast<uint32_t*>(it + 1024 + lane * 4) = hs;
+    if (t == 0) *reinterpret_cast<uint2*>(it + 1152 + g * 8) = make_uint2(dd[0], dd[1]);
+    *reinterpret_cast<uint2*>(it + 1216 + lane * 8) = make_uint2(hb[0], hb[1]);
+}
+
 }  // namespace
 
 int decode_kind_of(int fmt) {
@@ -1224,11 +1391,13 @@ int decode_kind_of(int fmt) {
     if (fmt == F_Q80) return DK_Q80;
     if (fmt == F_MX6) return DK_MX6;
     if (fmt == F_MX4) return DK_MX4;
+    if (fmt == F_Q40) return DK_Q40;
+    if (fmt == F_Q5K) return DK_Q5K;
     return DK_NONE;
 }
 
 int decode_item_bytes(int kind) {
-    return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : kind == DK_Q80 ? Q80_ITEM : kind == DK_MX6 ? MX6_ITEM : kind == DK_MX4 ? MX4_ITEM : 0;
+    return kind == DK_Q4K ? Q4K_ITEM : kind == DK_Q6K ? Q6K_ITEM : kind == DK_Q80 ? Q80_ITEM : kind == DK_MX6 ? MX6_ITEM : kind == DK_MX4 ? MX4_ITEM : kind == DK_Q40 ? Q40_ITEM : kind == DK_Q5K ? Q5K_ITEM : 0;
 }
 
 bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k) {
@@ -1261,6 +1430,8 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
     if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q6K) build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q80) build_image_s8_kernel<DK_Q80><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q40) build_image_q40_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q5K) build_image_q5k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_MX4) build_image_mx4_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else build_image_s8_kernel<DK_MX6><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     cudaError_t e = cudaGetLastError();

@@ -7,7 +7,7 @@
 namespace b200q {
 
 // Formats the kernel has an item layout for.
-enum : int { DK_NONE = -1, DK_Q4K = 0, DK_Q6K = 1, DK_Q80 = 2, DK_MX6 = 3, DK_MX4 = 4, DK_COUNT = 5 };
+enum : int { DK_NONE = -1, DK_Q4K = 0, DK_Q6K = 1, DK_Q80 = 2, DK_MX6 = 3, DK_MX4 = 4, DK_Q40 = 5, DK_Q5K = 6, DK_COUNT = 7 };
 
 // kind for a format index (fmt_of(qtype, layout)), or DK_NONE
 int decode_kind_of(int fmt);

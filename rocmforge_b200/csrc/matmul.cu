@@ -5,7 +5,6 @@
 #include <cstring>
 
 #include "gemv_i8.cuh"
-#include "gemv_mma.cuh"
 
 using namespace b200q;
 
@@ -16,28 +15,19 @@ struct b200q_batch {
     std::vector<const float*> x;
     std::vector<float*> y;
     size_t weight_bytes = 0;
-    // grouped launch (every product has a tensor-core decode kernel): device copies of the plan
+    // grouped launch of the decode kernel (every product has a decode image): device copies of the plan
     bool grouped = false;
-    GOp* d_ops = nullptr;
+    DOp* d_dops = nullptr;
     int2* d_ranges = nullptr;
-    int n_ctas = 0, total_tiles = 0, ring_d = 4;
-    size_t smem = 0;
-    GOp single{};
+    int n_ctas = 0, total_rt = 0, n_units = 0;
+    DOp dsingle{};
+    DecodeLaunch dl{};
     // host-output variant of the plan (b200q_batch_run_host with pinned, device-mapped outputs): the same
     // products with y pointing into the caller's host buffer
-    std::vector<GOp> h_ops;
-    GOp* d_ops_hosty = nullptr;
-    const float* hosty_base = nullptr;
-    GOp single_hosty{};
-    bool has_q4_0 = false;   // some product is GGUF Q4_0: the launch uses the kernel instantiation that carries it
-    // grouped launch of the integer decode kernel (every product has a decode image)
-    bool grouped_i8 = false;
-    DOp* d_dops = nullptr;
-    DOp* d_dops_hosty = nullptr;
     std::vector<DOp> h_dops;
-    DOp dsingle{}, dsingle_hosty{};
-    DecodeLaunch dl{};
-    int total_rt = 0, n_units = 0;
+    DOp* d_dops_hosty = nullptr;
+    const float* hosty_base = nullptr;
+    DOp dsingle_hosty{};
 };
 
 static DOp make_dop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
@@ -52,17 +42,6 @@ static DOp make_dop(const b200q_weight* w, const float* x, int64_t ldx, float* y
     return op;
 }
 
-static GOp make_gop(const b200q_weight* w, const float* x, int64_t ldx, float* y, int64_t ldy) {
-    GOp op{};
-    op.v = w->view;
-    op.x = x; op.y = y; op.ldx = ldx; op.ldy = ldy;
-    op.n_rows = (int)w->n_local; op.k = (int)w->k; op.fmt = w->fmt;
-    op.n_extra = w->ctx->scatter_extra;
-    for (int p = 0; p < op.n_extra; p++) op.y_extra[p] = w->ctx->scatter_y[p];
-    return op;
-}
-
-static int ctas_per_sm(size_t smem) { return smem <= 112 * 1024 ? 2 : 1; }
 
 static int check_matmul_args(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, const void* d_y, int m) {
     if (!w) return fail(B200Q_ERR_INVALID, "matmul: weight handle is null");
@@ -98,28 +77,11 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
             return B200Q_OK;
         }
     }
-    // largest activation-row chunk whose shared-memory image fits the tensor-core decode kernel
-    int chunk = 8;
-    while (chunk > 1 && !gemv_mma_supported(w, chunk)) chunk >>= 1;
-    const bool mma = gemv_mma_supported(w, chunk);
-    if (!mma && scatter) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m <= 8 needs a format of the tensor-core decode kernel (Q4_K, Q6_K, MXFP4, Q4_0, Q8_0 in GGUF layout)");
-    if (!mma) chunk = 8;
-    for (int i = 0; i < m; i += chunk) {
-        int mm = m - i < chunk ? m - i : chunk;
-        int rc;
-        if (mma) {
-            GOp op = make_gop(w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy);
-            for (int p = 0; p < op.n_extra; p++) op.y_extra[p] += (int64_t)i * ldy;
-            gemv_mma_plan(&op, true);
-            op.tile0 = 0;
-            const int ring_d = gemv_mma_ring_depth((int)w->k, mm);
-            size_t smem = gemv_mma_smem_for(ring_d, (int)w->k, mm);
-            int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
-            if (n_ctas > op.ntiles) n_ctas = op.ntiles;
-            rc = launch_gemv_mma(ctx, &op, nullptr, 1, nullptr, n_ctas, op.ntiles, mm, smem, ring_d, gemv_mma_is_q4_0(op.fmt));
-        } else {
-            rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
-        }
+    // no decode image (a format, orientation or k the decode kernel does not take): the CUDA-core kernel
+    if (scatter) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m <= 8 needs a tensor with a decode image (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, MXFP4, MXFP6 E2M3 in GGUF layout, NK, k %% 128 == 0)");
+    for (int i = 0; i < m; i += 8) {
+        const int mm = m - i < 8 ? m - i : 8;
+        int rc = launch_gemv(ctx, w, x + (int64_t)i * ldx, ldx, y + (int64_t)i * ldy, ldy, mm);
         if (rc != B200Q_OK) return rc;
     }
     return B200Q_OK;
@@ -313,69 +275,12 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
             return cuda_fail(B200Q_ERR_ALLOC, e, "batch_create");
         }
         b->grouped = true;
-        b->grouped_i8 = true;
         b->h_dops = ops;
         b->n_ctas = n_ctas;
         b->total_rt = total;
         b->dsingle = ops[0];
         *out = b;
         return B200Q_OK;
-    }
-    // plan one grouped launch when every product has a tensor-core decode kernel
-    bool all = count > 0;
-    for (int i = 0; i < count; i++) all = all && gemv_mma_supported(w[i], m);
-    if (all) {
-        std::vector<GOp> ops(count);
-        std::vector<double> tile_cost;
-        int total = 0, kmax = 0, ring_d = 4;
-        size_t smem = 0;
-        for (int i = 0; i < count; i++) {
-            ops[i] = make_gop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
-            b->has_q4_0 = b->has_q4_0 || gemv_mma_is_q4_0(w[i]->fmt);
-            gemv_mma_plan(&ops[i], count == 1);
-            ops[i].tile0 = total;
-            total += ops[i].ntiles;
-            FmtInfo I = fmt_info(w[i]->fmt);
-            double c = (double)(8 >> ops[i].kw_log2) * 16 * w[i]->k * I.block_bytes / I.block_elems + 2048.0;
-            for (int t = 0; t < ops[i].ntiles; t++) tile_cost.push_back(c);
-            if (w[i]->k > kmax) kmax = (int)w[i]->k;
-            int rd = gemv_mma_ring_depth((int)w[i]->k, m);
-            if (rd < ring_d) ring_d = rd;
-        }
-        smem = gemv_mma_smem_for(ring_d, kmax, m);
-        b->ring_d = ring_d;
-        int n_ctas = ctx->info.sm_count * ctas_per_sm(smem);
-        if (n_ctas > total) n_ctas = total;
-        // contiguous tile ranges of (nearly) equal cost
-        double sum = 0;
-        for (double c : tile_cost) sum += c;
-        std::vector<int2> ranges(n_ctas);
-        double acc = 0;
-        int t = 0;
-        for (int c = 0; c < n_ctas; c++) {
-            ranges[c].x = t;
-            double limit = sum * (c + 1) / n_ctas;
-            while (t < total && (acc + tile_cost[t] * 0.5 <= limit || c == n_ctas - 1)) acc += tile_cost[t++];
-            ranges[c].y = t;
-        }
-        cudaError_t e = cudaSetDevice(ctx->device);
-        if (e == cudaSuccess) e = cudaMalloc(&b->d_ops, sizeof(GOp) * count);
-        if (e == cudaSuccess) e = cudaMalloc(&b->d_ranges, sizeof(int2) * n_ctas);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ops, ops.data(), sizeof(GOp) * count, cudaMemcpyHostToDevice, ctx->stream);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(b->d_ranges, ranges.data(), sizeof(int2) * n_ctas, cudaMemcpyHostToDevice, ctx->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-        if (e != cudaSuccess) {
-            if (b->d_ops) cudaFree(b->d_ops);
-            if (b->d_ranges) cudaFree(b->d_ranges);
-            delete b;
-            return cuda_fail(B200Q_ERR_ALLOC, e, "batch_create");
-        }
-        b->grouped = true;
-        b->h_ops = ops;
-        b->n_ctas = n_ctas;
-        b->total_tiles = total;
-        b->smem = smem;
-        b->single = ops[0];
     }
     *out = b;
     return B200Q_OK;
@@ -385,15 +290,10 @@ int b200q_batch_run(b200q_ctx* ctx, b200q_batch* batch, float* ms_out) {
     if (!ctx || !batch) return fail(B200Q_ERR_INVALID, "batch_run: null argument");
     B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
     if (ms_out) B200Q_CUDA(cudaEventRecord(ctx->ev0, ctx->stream), B200Q_ERR_DEVICE);
-    if (batch->grouped_i8) {
+    if (batch->grouped) {
         int n = (int)batch->w.size();
         int rc = launch_gemv_i8(ctx, &batch->dsingle, batch->d_dops, n, batch->d_ranges, batch->n_units, batch->n_ctas,
                                 batch->total_rt, batch->m, batch->dl);
-        if (rc != B200Q_OK) return rc;
-    } else if (batch->grouped) {
-        int n = (int)batch->w.size();
-        int rc = launch_gemv_mma(ctx, &batch->single, batch->d_ops, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
-                                 batch->total_tiles, batch->m, batch->smem, batch->ring_d, batch->has_q4_0);
         if (rc != B200Q_OK) return rc;
     } else {
         for (size_t i = 0; i < batch->w.size(); i++) {
@@ -440,7 +340,7 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
         cudaPointerAttributes pa{};
         if (cudaPointerGetAttributes(&pa, h_y_all) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer) {
             float* dy = static_cast<float*>(pa.devicePointer);
-            if (batch->grouped_i8) {
+            {
                 if (batch->hosty_base != h_y_all) {
                     std::vector<DOp> ops = batch->h_dops;
                     size_t off = 0;
@@ -462,27 +362,6 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
                 if (rc != B200Q_OK) return rc;
                 return b200q_synchronize(ctx);
             }
-            if (batch->hosty_base != h_y_all) {
-                std::vector<GOp> ops = batch->h_ops;
-                size_t off = 0;
-                for (size_t i = 0; i < cnt; i++) {
-                    ops[i].y = dy + off;
-                    off += (size_t)batch->m * batch->w[i]->n_local;
-                }
-                cudaError_t e = cudaSuccess;
-                if (!batch->d_ops_hosty) e = cudaMalloc(&batch->d_ops_hosty, sizeof(GOp) * cnt);
-                if (e == cudaSuccess) e = cudaMemcpyAsync(batch->d_ops_hosty, ops.data(), sizeof(GOp) * cnt, cudaMemcpyHostToDevice, ctx->stream);
-                if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // `ops` is pageable and local
-                if (e != cudaSuccess) return cuda_fail(B200Q_ERR_ALLOC, e, "batch_run_host");
-                batch->single_hosty = ops[0];
-                batch->hosty_base = h_y_all;
-            }
-            int n = (int)cnt;
-            int rc = launch_gemv_mma(ctx, &batch->single_hosty, batch->d_ops_hosty, n, n > 1 ? batch->d_ranges : nullptr, batch->n_ctas,
-                                     batch->total_tiles, batch->m, batch->smem, batch->ring_d, batch->has_q4_0);
-            if (rc != B200Q_OK) return rc;
-            B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
-            return B200Q_OK;
         }
         cudaGetLastError();   // pageable host memory: not an error, take the copy path
     }
@@ -504,13 +383,11 @@ int b200q_batch_run_host(b200q_ctx* ctx, b200q_batch* batch, const float* h_x_al
 
 int b200q_batch_free(b200q_batch* batch) {
     if (!batch) return B200Q_OK;
-    if (batch->d_ops || batch->d_ranges || batch->d_dops) {
+    if (batch->d_ranges || batch->d_dops) {
         cudaSetDevice(batch->ctx->device);
         cudaStreamSynchronize(batch->ctx->stream);
-        if (batch->d_ops) cudaFree(batch->d_ops);
         if (batch->d_dops) cudaFree(batch->d_dops);
         if (batch->d_ranges) cudaFree(batch->d_ranges);
-        if (batch->d_ops_hosty) cudaFree(batch->d_ops_hosty);
         if (batch->d_dops_hosty) cudaFree(batch->d_dops_hosty);
         cudaGetLastError();
     }
