@@ -363,17 +363,22 @@ def shard_leg(be, rank, world, steps):
                 dist.all_gather_into_tensor(y_all.view(world * m, -1), y_slice)
 
             # fused form: the kernels' epilogues store this rank's slice into every rank's full output through
-            # peer-mapped pointers (b200q_matmul_scatter); one 4-byte all-reduce on the same streams orders the
-            # ranks before anyone reads. Outputs live in library allocations so that they can be exported.
+            # peer-mapped pointers (b200q_matmul_scatter); then every rank raises a flag in every other rank's
+            # memory (b200q_peer_signal) and holds its stream until the others' flags are in (b200q_peer_wait,
+            # bounded). Outputs and flags live in library allocations so that they can be exported.
             y_full = be.allocate_buffer(m * n * 4)
+            flags = be.allocate_buffer(64); flags.fill(0)
             handles = [None] * world
-            dist.all_gather_object(handles, be.ipc_handle(y_full))
-            peers = [y_full.as_ptr() if r == rank else be.ipc_open(handles[r]) for r in range(world)]
-            token = torch.zeros(1, device="cuda")
+            dist.all_gather_object(handles, (be.ipc_handle(y_full), be.ipc_handle(flags)))
+            peers = [y_full.as_ptr() if r == rank else be.ipc_open(handles[r][0]) for r in range(world)]
+            peer_flags = [flags.as_ptr() if r == rank else be.ipc_open(handles[r][1]) for r in range(world)]
+            epoch = [0]
 
             def fused():
+                epoch[0] += 1
                 w.matmul_scatter(xt.data_ptr(), peers, m, n)
-                dist.all_reduce(token)
+                be.peer_signal(peer_flags, rank, epoch[0])
+                be.peer_wait(flags, world, rank, epoch[0])
 
             for _ in range(3):
                 with_gather()
@@ -381,9 +386,12 @@ def shard_leg(be, rank, world, steps):
             t_kernel = timed(kernel, steps)
             t_total = timed(with_gather, steps)
             t_fused = timed(fused, steps)
+            gathered = int(m * n * 4 * (world - 1) / world)
             case = {"qtype": qname, "m": m, "ranks": world, "ms_kernel": t_kernel, "ms_kernel_plus_allgather": t_total,
-                    "ms_fused_peer_stores_plus_sync": t_fused,
-                    "gathered_bytes_per_rank": int(m * n * 4 * (world - 1) / world)}
+                    "ms_fused_peer_stores_plus_flags": t_fused,
+                    "gathered_bytes_per_rank": gathered,
+                    # what the bytes every rank must receive cost at the measured peer-copy rate of this pool
+                    "nvlink_floor_ms": gathered / 770e9 * 1e3, "nvlink_GBps_assumed": 770}
             if rank == 0:
                 yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
                 for _ in range(3):
@@ -395,7 +403,12 @@ def shard_leg(be, rank, world, steps):
                     full.matmul(xt.data_ptr(), yb.data_ptr(), m)
                 e1.record(cur)
                 torch.cuda.synchronize()
-                case["ms_one_gpu_unsharded"] = e0.elapsed_time(e1) / steps
+                t1 = e0.elapsed_time(e1) / steps
+                case["ms_one_gpu_unsharded"] = t1
+                # strong scaling on the fixed problem: t(1 GPU) / (ranks x t(ranks))
+                case["efficiency_kernel"] = t1 / (world * t_kernel)
+                case["efficiency_with_allgather"] = t1 / (world * t_total)
+                case["efficiency_fused"] = t1 / (world * t_fused)
                 # the gathered result equals the unsharded one (same kernel, same per-row arithmetic)
                 got = y_all.permute(1, 0, 2).reshape(m, n)
                 case["max_abs_diff_vs_unsharded"] = float((got - yb).abs().max().item())
@@ -405,8 +418,10 @@ def shard_leg(be, rank, world, steps):
             for r in range(world):
                 if r != rank:
                     be.ipc_close(peers[r])
+                    be.ipc_close(peer_flags[r])
             dist.barrier()
             y_full.free()
+            flags.free()
             out["cases"].append(case)
         w.free()
         if full is not None:

@@ -189,6 +189,15 @@ int b200q_batch_launches(const b200q_batch* batch);
  *      bytes travel between the processes by whatever channel the host has. */
 int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* const* d_y_full,
                          int n_outputs, int64_t ldy, int m, unsigned flags);
+/* Ordering the GPUs after a scattered product without a collective: every rank owns a flag array of n_ranks ints
+ * (b200q_malloc + b200q_memset to 0, exported like the outputs). b200q_peer_signal, enqueued behind the product,
+ * stores `epoch` into slot my_rank of every other rank's array (release stores over NVLink; the product's own peer
+ * stores are complete by then because the kernel has ended). b200q_peer_wait, enqueued on the same stream, holds the
+ * stream until every other slot of THIS rank's array holds `epoch`; whatever follows it on the stream may read the
+ * full output. The wait is bounded (about a second of SM clock): on expiry the next b200q_synchronize returns
+ * B200Q_ERR_TIMEOUT and the context stays usable. Use a new epoch value for every product (a counter). */
+int b200q_peer_signal(b200q_ctx* ctx, void* const* d_flags_of_ranks, int n_ranks, int my_rank, int epoch);
+int b200q_peer_wait(b200q_ctx* ctx, const void* d_flags_own, int n_ranks, int my_rank, int epoch);
 int b200q_ipc_get_handle(b200q_ctx* ctx, const void* d_ptr, void* handle64);
 int b200q_ipc_open(b200q_ctx* ctx, const void* handle64, void** d_ptr_out);
 int b200q_ipc_close(b200q_ctx* ctx, void* d_ptr);

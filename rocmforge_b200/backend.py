@@ -105,6 +105,18 @@ class B200Backend:
     def ipc_close(self, ptr):
         check(self.lib.b200q_ipc_close(self.ctx, ptr))
 
+    def peer_signal(self, flag_arrays, my_rank, epoch):
+        """Behind a scattered product: store `epoch` into slot my_rank of every other rank's flag array
+        (DeviceBuffers or raw, peer-mapped pointers, one per rank)."""
+        ptrs = [f.as_ptr() if isinstance(f, DeviceBuffer) else f for f in flag_arrays]
+        arr = (ctypes.c_void_p * len(ptrs))(*[p.value if isinstance(p, ctypes.c_void_p) else p for p in ptrs])
+        check(self.lib.b200q_peer_signal(self.ctx, arr, len(ptrs), my_rank, epoch))
+
+    def peer_wait(self, own_flags, n_ranks, my_rank, epoch):
+        """Hold the stream (bounded) until every other rank has signalled `epoch` into this rank's flag array."""
+        p = own_flags.as_ptr() if isinstance(own_flags, DeviceBuffer) else own_flags
+        check(self.lib.b200q_peer_wait(self.ctx, p, n_ranks, my_rank, epoch))
+
     def synchronize(self):
         check(self.lib.b200q_synchronize(self.ctx))
 

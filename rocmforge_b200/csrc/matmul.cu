@@ -87,7 +87,68 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
     return B200Q_OK;
 }
 
+namespace {
+
+struct PeerFlags {
+    int* p[8];
+};
+
+// one lane per rank: the slice this GPU stored into rank p's output is complete (the kernel that stored it has ended)
+__global__ void peer_signal_kernel(PeerFlags f, int n_ranks, int my_rank, int epoch) {
+    const int p = threadIdx.x;
+    if (p >= n_ranks || p == my_rank) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[p] + my_rank), "r"(epoch) : "memory");
+}
+
+// one lane per rank: bounded wait until rank p has signalled this round
+__global__ void peer_wait_kernel(const int* flags, int n_ranks, int my_rank, int epoch, long long budget, int* status) {
+    const int p = threadIdx.x;
+    if (p >= n_ranks || p == my_rank) return;
+    const long long t0 = clock64();
+    for (;;) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+        if (v == epoch) return;
+        if (clock64() - t0 > budget) {
+            atomicExch(status, 300 + p);
+            return;
+        }
+        __nanosleep(100);
+    }
+}
+
+}  // namespace
+
 extern "C" {
+
+int b200q_peer_signal(b200q_ctx* ctx, void* const* d_flags_of_ranks, int n_ranks, int my_rank, int epoch) {
+    if (!ctx) return fail(B200Q_ERR_INVALID, "peer_signal: ctx is null");
+    if (!d_flags_of_ranks || n_ranks < 1 || n_ranks > 8 || my_rank < 0 || my_rank >= n_ranks)
+        return fail(B200Q_ERR_INVALID, "peer_signal: rank %d of %d (1..8 ranks)", my_rank, n_ranks);
+    PeerFlags f{};
+    for (int p = 0; p < n_ranks; p++) {
+        if (!d_flags_of_ranks[p]) return fail(B200Q_ERR_INVALID, "peer_signal: flag array of rank %d is null", p);
+        f.p[p] = static_cast<int*>(d_flags_of_ranks[p]);
+    }
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    if (n_ranks == 1) return B200Q_OK;
+    peer_signal_kernel<<<1, 32, 0, ctx->stream>>>(f, n_ranks, my_rank, epoch);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
+int b200q_peer_wait(b200q_ctx* ctx, const void* d_flags_own, int n_ranks, int my_rank, int epoch) {
+    if (!ctx) return fail(B200Q_ERR_INVALID, "peer_wait: ctx is null");
+    if (!d_flags_own || n_ranks < 1 || n_ranks > 8 || my_rank < 0 || my_rank >= n_ranks)
+        return fail(B200Q_ERR_INVALID, "peer_wait: rank %d of %d (1..8 ranks)", my_rank, n_ranks);
+    B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+    if (n_ranks == 1) return B200Q_OK;
+    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(static_cast<const int*>(d_flags_own), n_ranks, my_rank, epoch, 2000000000ll, ctx->d_status);
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    ctx->tc_pending = true;   // the next synchronise reads the status word
+    return B200Q_OK;
+}
 
 int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, int64_t ldx, void* d_y,
                     int y_dtype, int64_t ldy, int m, unsigned flags) {

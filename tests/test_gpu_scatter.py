@@ -84,14 +84,19 @@ for qt, m in ((synth.Q4_K, 1), (synth.Q4_K, 256)):
     x = synth.gen_activations(m, k, rng)
     xt = torch.from_numpy(x).cuda()
     y_full = be.allocate_buffer(m * n * 4); y_full.fill(0xFF)
+    flags = be.allocate_buffer(64); flags.fill(0)
     handles = [None] * world
-    dist.all_gather_object(handles, be.ipc_handle(y_full))
-    peers = [y_full.as_ptr() if r == rank else be.ipc_open(handles[r]) for r in range(world)]
+    dist.all_gather_object(handles, (be.ipc_handle(y_full), be.ipc_handle(flags)))
+    peers = [y_full.as_ptr() if r == rank else be.ipc_open(handles[r][0]) for r in range(world)]
+    peer_flags = [flags.as_ptr() if r == rank else be.ipc_open(handles[r][1]) for r in range(world)]
     w = QuantizedWeight(be, data, qt, synth.GGUF, n, k, shard_rank=rank, shard_count=world)
     full = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
-    w.matmul_scatter(xt.data_ptr(), peers, m, n)
-    dist.all_reduce(torch.zeros(1, device="cuda"))
-    torch.cuda.synchronize()
+    dist.barrier()                                   # every rank has mapped the others' buffers
+    for epoch in (1, 2):                             # no collective between the product and the read: flags only
+        w.matmul_scatter(xt.data_ptr(), peers, m, n)
+        be.peer_signal(peer_flags, rank, epoch)
+        be.peer_wait(flags, world, rank, epoch)
+    be.synchronize()
     yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
     full.matmul(xt.data_ptr(), yb.data_ptr(), m)
     be.synchronize()
@@ -103,12 +108,35 @@ for qt, m in ((synth.Q4_K, 1), (synth.Q4_K, 256)):
     for r in range(world):
         if r != rank:
             be.ipc_close(peers[r])
+            be.ipc_close(peer_flags[r])
     dist.barrier()
 t = torch.tensor([1.0 if ok else 0.0], device="cuda")
 dist.all_reduce(t, op=dist.ReduceOp.MIN)
 dist.destroy_process_group()
 sys.exit(0 if t.item() == 1.0 else 3)
 """
+
+
+def test_peer_wait_gives_up_when_no_peer_signals():
+    """A rank that never hears from a peer (it died between steps) must not hang its GPU: the wait is bounded, the
+    next synchronise reports a recoverable time-out, and the context goes on working. The failure is made on the
+    host: nothing ever writes the flag."""
+    be = backend()
+    flags = be.allocate_buffer(64)
+    flags.fill(0)
+    be.peer_wait(flags, 2, 0, 7)                     # slot 1 never becomes 7
+    with pytest.raises(B200QError) as e:
+        be.synchronize()
+    assert e.value.status == _lib.ERR_TIMEOUT and e.value.recoverable
+    be.synchronize()                                 # the status was consumed; the context is usable
+    import numpy as np
+    one = np.array([0, 7] + [0] * 14, dtype=np.int32)
+    flags.copy_from_host(one)
+    be.peer_wait(flags, 2, 0, 7)                     # the flag is there: returns at once
+    be.synchronize()
+    with pytest.raises(B200QError):
+        be.peer_wait(flags, 9, 0, 1)
+    flags.free()
 
 
 def test_two_processes_write_into_each_others_outputs(tmp_path):
