@@ -376,8 +376,7 @@ def shard_leg(be, rank, world, steps):
 
             def fused():
                 epoch[0] += 1
-                w.matmul_scatter(xt.data_ptr(), peers, m, n)
-                be.peer_signal(peer_flags, rank, epoch[0])
+                w.matmul_scatter_signal(xt.data_ptr(), peers, m, n, peer_flags, rank, epoch[0])
                 be.peer_wait(flags, world, rank, epoch[0])
 
             for _ in range(3):

@@ -197,6 +197,12 @@ int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x,
  * full output. The wait is bounded (about a second of SM clock): on expiry the next b200q_synchronize returns
  * B200Q_ERR_TIMEOUT and the context stays usable. Use a new epoch value for every product (a counter). */
 int b200q_peer_signal(b200q_ctx* ctx, void* const* d_flags_of_ranks, int n_ranks, int my_rank, int epoch);
+/* b200q_matmul_scatter followed by b200q_peer_signal in one call (d_y_full[p] and d_flags_of_ranks[p] belong to rank p,
+ * n_outputs ranks). The decode kernel raises the flags itself when its last CTA has stored its rows, so m <= 8 costs
+ * no extra launch. */
+int b200q_matmul_scatter_signal(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* const* d_y_full,
+                                int n_outputs, int64_t ldy, int m, unsigned flags, void* const* d_flags_of_ranks, int my_rank,
+                                int epoch);
 int b200q_peer_wait(b200q_ctx* ctx, const void* d_flags_own, int n_ranks, int my_rank, int epoch);
 int b200q_ipc_get_handle(b200q_ctx* ctx, const void* d_ptr, void* handle64);
 int b200q_ipc_open(b200q_ctx* ctx, const void* handle64, void** d_ptr_out);

@@ -77,6 +77,7 @@ SIGNATURES = {
     "b200q_matmul_scatter": (_i, [_vp, _vp, _vp, _i, _pvp, _i, _i64, _i, _u]),
     "b200q_peer_signal": (_i, [_vp, _pvp, _i, _i, _i]),
     "b200q_peer_wait": (_i, [_vp, _vp, _i, _i, _i]),
+    "b200q_matmul_scatter_signal": (_i, [_vp, _vp, _vp, _i, _pvp, _i, _i64, _i, _u, _pvp, _i, _i]),
     "b200q_ipc_get_handle": (_i, [_vp, _vp, _vp]),
     "b200q_ipc_open": (_i, [_vp, _vp, _pvp]),
     "b200q_ipc_close": (_i, [_vp, _vp]),

@@ -201,6 +201,14 @@ class QuantizedWeight:
         arr = (ctypes.c_void_p * len(ptrs))(*[p.value if isinstance(p, ctypes.c_void_p) else p for p in ptrs])
         check(self.backend.lib.b200q_matmul_scatter(self.backend.ctx, self.handle, xp, x_dtype, arr, len(ptrs), ldy, m, flags))
 
+    def matmul_scatter_signal(self, x, outputs, m, ldy, flag_arrays, my_rank, epoch, x_dtype=_lib.F32, flags=0):
+        """matmul_scatter, then `epoch` into slot my_rank of every other rank's flag array (raised by the decode kernel's
+        last CTA itself at m <= 8). outputs[p] and flag_arrays[p] belong to rank p."""
+        xp = x.as_ptr() if isinstance(x, DeviceBuffer) else x
+        conv = lambda seq: (ctypes.c_void_p * len(seq))(*[(q.as_ptr() if isinstance(q, DeviceBuffer) else q) if not isinstance(q, ctypes.c_void_p) else q.value for q in seq])
+        check(self.backend.lib.b200q_matmul_scatter_signal(self.backend.ctx, self.handle, xp, x_dtype, conv(outputs), len(outputs), ldy,
+                                                           m, flags, conv(flag_arrays), my_rank, epoch))
+
     def matmul_host(self, x, m=None, flags=0):
         x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.k)
         m = x.shape[0] if m is None else m

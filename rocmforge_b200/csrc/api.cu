@@ -110,9 +110,9 @@ int b200q_init_on_stream(int device, void* cuda_stream, b200q_ctx** out) {
         b200q_destroy(ctx);
         return fail(B200Q_ERR_INIT, "init: device is sm_%d%d; this library is built for sm_100a only", maj, min);
     }
-    e = cudaMalloc(&ctx->d_status, sizeof(int) * 4);
+    e = cudaMalloc(&ctx->d_status, sizeof(int) * 8);
     if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaMalloc(status)"); }
-    cudaMemsetAsync(ctx->d_status, 0, sizeof(int) * 4, ctx->stream);
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int) * 8, ctx->stream);
     e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_status), sizeof(int) * 4, cudaHostAllocDefault);
     if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaHostAlloc(status)"); }
     *out = ctx;

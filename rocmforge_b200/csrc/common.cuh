@@ -19,7 +19,7 @@ struct b200q_ctx {
     size_t scratch_bytes = 0;
     void* scratch2 = nullptr;
     size_t scratch2_bytes = 0;
-    int* d_status = nullptr;  // device words: [0] bounded-wait failures, [1] bad token ids, [2..3] work-unit counters of the decode kernel
+    int* d_status = nullptr;  // device words: [0] bounded-wait failures, [1] bad token ids, [2..4] counters of the decode kernel
     int* h_status = nullptr;  // page-locked landing place of [0..1] when a synchronise reads them
     bool tc_pending = false;  // a tensor-core launch has not had its status word read yet
     void* scratch3 = nullptr; // f16 copy of the activations + row scales for the tensor-core path
@@ -32,6 +32,10 @@ struct b200q_ctx {
     // while b200q_matmul_scatter runs: the same output slice in the other GPUs' full outputs (peer-mapped)
     int scatter_extra = 0;
     float* scatter_y[7] = {};
+    // ... and the peers' flag arrays when the product's last CTA is to signal them (scatter_sig_n == 0: no signal)
+    int* scatter_flag[8] = {};
+    int scatter_sig_n = 0, scatter_sig_my = 0, scatter_sig_epoch = 0;
+    bool scatter_signalled = false;   // the kernel that ran took care of the signal
 };
 
 namespace b200q {

@@ -1841,7 +1841,7 @@ int gemm_tc_check_status(b200q_ctx* ctx) {
     B200Q_CUDA(cudaMemcpyAsync(h, ctx->d_status, 2 * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream), B200Q_ERR_COPY);
     B200Q_CUDA(cudaStreamSynchronize(ctx->stream), B200Q_ERR_DEVICE);
     const int h0 = h[0], h1 = h[1];
-    if (h0 != 0 || h1 != 0) cudaMemsetAsync(ctx->d_status, 0, 2 * sizeof(int), ctx->stream);
+    if (h0 != 0 || h1 != 0) cudaMemsetAsync(ctx->d_status, 0, 8 * sizeof(int), ctx->stream);   // the decode kernel's counters too
     if (h0 != 0)
         return fail(B200Q_ERR_TIMEOUT, "a bounded device-side wait expired (site %d); results of that launch are invalid", h0);
     if (h1 != 0)

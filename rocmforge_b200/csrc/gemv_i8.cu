@@ -962,7 +962,7 @@ struct Seg {
 template <int NW, bool MANY>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
 gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int n_units, int total_rt, int m,
-               int* status, int* sched, int chunk, int depth, int slot_bytes) {
+               int* status, int* sched, int chunk, int depth, int slot_bytes, PeerSignal sig) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ DOp s_op[3];    // descriptors of the previous, the current and the next segment's product
     __shared__ int s_next;     // next work unit of the CTA
@@ -1148,6 +1148,17 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             pos = j1;
         }
         store_tile<MANY>(po, pend_rt, pend, m, lane);
+    }
+    // scattered products: when every CTA's stores to the peers are out, the last CTA tells the peers
+    if (sig.n > 0) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(&sched[2], 1) == (int)gridDim.x - 1) {
+            sched[2] = 0;
+            __threadfence_system();
+            for (int p = 0; p < sig.n; p++)
+                if (p != sig.my) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sig.flag[p] + sig.my), "r"(sig.epoch) : "memory");
+        }
     }
     // the last CTA to run out of units resets the counters for the next launch
     if (dynamic && threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) {
@@ -1539,7 +1550,7 @@ bool gemv_i8_supported(const b200q_weight* w, int m) {
 }
 
 int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_units, int n_ctas,
-                   int total_rt, int m, const DecodeLaunch& L) {
+                   int total_rt, int m, const DecodeLaunch& L, const PeerSignal* sig_in) {
     if (total_rt <= 0) return B200Q_OK;
     if (n_units > total_rt) n_units = total_rt;
     if (n_ctas > n_units) n_ctas = n_units;
@@ -1563,9 +1574,11 @@ int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int* status = ctx->d_status;
-    int* sched = ctx->d_status + 2;   // {next unit, CTAs done}: zero between launches
+    int* sched = ctx->d_status + 2;   // {next unit, CTAs done, CTAs done storing to peers}: zero between launches
+    PeerSignal sig{};
+    if (sig_in) sig = *sig_in;
     int chunk = L.chunk_items, depth = L.depth, slot = L.slot_bytes;
-    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &n_units, &total_rt, &m, &status, &sched, &chunk, &depth, &slot};
+    void* args[] = {&single, &d_ops, &n_ops, &d_ranges, &n_units, &total_rt, &m, &status, &sched, &chunk, &depth, &slot, &sig};
     B200Q_CUDA(cudaLaunchKernelExC(&cfg, kernels[ki], args), B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     ctx->tc_pending = true;   // the next synchronise reads the status word

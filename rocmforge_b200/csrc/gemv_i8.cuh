@@ -34,6 +34,13 @@ struct DOp {
     float* y_extra[7];
 };
 
+// Signal raised at the end of a launch whose products were scattered to peer GPUs: the last CTA stores `epoch` into
+// slot `my` of every other rank's flag array (n == 0: no signal).
+struct PeerSignal {
+    int* flag[8];
+    int n, my, epoch;
+};
+
 struct DecodeLaunch {
     int chunk_items;   // items per bulk copy
     int depth;         // ring slots per warp
@@ -53,7 +60,7 @@ size_t gemv_i8_image_smem(int kind, int k, int m);
 // tiles are cut into n_units equal ranges. The first n_ctas units start on their own CTA, the rest are handed out
 // as CTAs finish. d_ops is a device array when n_ops > 1; a single product travels as a kernel argument.
 int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_ops, const int2* d_ranges, int n_units, int n_ctas,
-                   int total_rt, int m, const DecodeLaunch& L);
+                   int total_rt, int m, const DecodeLaunch& L, const PeerSignal* sig = nullptr);
 // Cuts the row tiles of a launch (byte cost and product index per tile) into work units: n_ctas ranges of equal
 // cost, optionally followed by smaller units that are handed out as CTAs finish.
 void gemv_i8_make_units(const std::vector<double>& tile_cost, const std::vector<int>& tile_op, int n_ctas, std::vector<int2>* units);

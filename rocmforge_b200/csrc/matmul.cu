@@ -71,7 +71,15 @@ static int matmul_f32(b200q_ctx* ctx, const b200q_weight* w, const float* x, int
                 DecodeLaunch L;
                 gemv_i8_plan(op.item_bytes, op.k, 1 << op.kind, mm, &L);
                 const int n_ctas = ctx->info.sm_count * L.ctas_per_sm;
-                int rc = launch_gemv_i8(ctx, &op, nullptr, 1, nullptr, n_ctas, n_ctas, op.nrt, mm, L);
+                // the launch that stores the last rows raises the peers' flags itself
+                PeerSignal sig{};
+                const bool last = i + chunk >= m;
+                if (last && ctx->scatter_sig_n > 0) {
+                    sig.n = ctx->scatter_sig_n; sig.my = ctx->scatter_sig_my; sig.epoch = ctx->scatter_sig_epoch;
+                    for (int p = 0; p < sig.n; p++) sig.flag[p] = ctx->scatter_flag[p];
+                    ctx->scatter_signalled = true;
+                }
+                int rc = launch_gemv_i8(ctx, &op, nullptr, 1, nullptr, n_ctas, n_ctas, op.nrt, mm, L, &sig);
                 if (rc != B200Q_OK) return rc;
             }
             return B200Q_OK;
@@ -101,21 +109,27 @@ __global__ void peer_signal_kernel(PeerFlags f, int n_ranks, int my_rank, int ep
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[p] + my_rank), "r"(epoch) : "memory");
 }
 
-// one lane per rank: bounded wait until rank p has signalled this round
+// One lane per rank: bounded wait until rank p has signalled this round. Launched programmatically behind the product
+// whose stores it orders: it lets the kernel behind it become resident at once, polls while the product still runs,
+// and completes only after the product has (griddepcontrol.wait), so that completion of this kernel still implies
+// completion of everything ahead of it on the stream.
 __global__ void peer_wait_kernel(const int* flags, int n_ranks, int my_rank, int epoch, long long budget, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int p = threadIdx.x;
-    if (p >= n_ranks || p == my_rank) return;
-    const long long t0 = clock64();
-    for (;;) {
-        int v;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
-        if (v == epoch) return;
-        if (clock64() - t0 > budget) {
-            atomicExch(status, 300 + p);
-            return;
+    if (p < n_ranks && p != my_rank) {
+        const long long t0 = clock64();
+        for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+            if (v == epoch) break;
+            if (clock64() - t0 > budget) {
+                atomicExch(status, 300 + p);
+                break;
+            }
+            __nanosleep(100);
         }
-        __nanosleep(100);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace
@@ -144,7 +158,19 @@ int b200q_peer_wait(b200q_ctx* ctx, const void* d_flags_own, int n_ranks, int my
         return fail(B200Q_ERR_INVALID, "peer_wait: rank %d of %d (1..8 ranks)", my_rank, n_ranks);
     B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
     if (n_ranks == 1) return B200Q_OK;
-    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(static_cast<const int*>(d_flags_own), n_ranks, my_rank, epoch, 2000000000ll, ctx->d_status);
+    // programmatic launch: the one-warp kernel may become resident while the product ahead of it still runs (it reads
+    // nothing that kernel writes); what follows it on the stream still waits for its completion
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA(cudaLaunchKernelEx(&cfg, peer_wait_kernel, static_cast<const int*>(d_flags_own), n_ranks, my_rank, epoch, 2000000000ll, ctx->d_status),
+               B200Q_ERR_LAUNCH);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     ctx->tc_pending = true;   // the next synchronise reads the status word
     return B200Q_OK;
@@ -214,6 +240,26 @@ int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x,
     int rc = b200q_matmul_ex(ctx, w, d_x, x_dtype, 0, static_cast<float*>(d_y_full[0]) + w->row0, B200Q_F32, ldy, m, flags);
     ctx->scatter_extra = 0;
     return rc;
+}
+
+int b200q_matmul_scatter_signal(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_dtype, void* const* d_y_full, int n_outputs,
+                                int64_t ldy, int m, unsigned flags, void* const* d_flags_of_ranks, int my_rank, int epoch) {
+    if (!ctx) return fail(B200Q_ERR_INVALID, "matmul_scatter_signal: ctx is null");
+    if (!d_flags_of_ranks || n_outputs < 1 || n_outputs > 8 || my_rank < 0 || my_rank >= n_outputs)
+        return fail(B200Q_ERR_INVALID, "matmul_scatter_signal: rank %d of %d outputs", my_rank, n_outputs);
+    for (int p = 0; p < n_outputs; p++) {
+        if (!d_flags_of_ranks[p]) return fail(B200Q_ERR_INVALID, "matmul_scatter_signal: flag array of rank %d is null", p);
+        ctx->scatter_flag[p] = static_cast<int*>(d_flags_of_ranks[p]);
+    }
+    ctx->scatter_sig_n = n_outputs; ctx->scatter_sig_my = my_rank; ctx->scatter_sig_epoch = epoch;
+    ctx->scatter_signalled = false;
+    int rc = b200q_matmul_scatter(ctx, w, d_x, x_dtype, d_y_full, n_outputs, ldy, m, flags);
+    const bool done = ctx->scatter_signalled;
+    ctx->scatter_sig_n = 0;
+    ctx->scatter_signalled = false;
+    if (rc != B200Q_OK) return rc;
+    // kernels that do not raise the flags themselves (the prefill kernels): a one-warp kernel behind them does
+    return done ? B200Q_OK : b200q_peer_signal(ctx, d_flags_of_ranks, n_outputs, my_rank, epoch);
 }
 
 int b200q_ipc_get_handle(b200q_ctx* ctx, const void* d_ptr, void* handle64) {

@@ -93,8 +93,11 @@ for qt, m in ((synth.Q4_K, 1), (synth.Q4_K, 256)):
     full = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
     dist.barrier()                                   # every rank has mapped the others' buffers
     for epoch in (1, 2):                             # no collective between the product and the read: flags only
-        w.matmul_scatter(xt.data_ptr(), peers, m, n)
-        be.peer_signal(peer_flags, rank, epoch)
+        if epoch == 1:
+            w.matmul_scatter(xt.data_ptr(), peers, m, n)
+            be.peer_signal(peer_flags, rank, epoch)
+        else:
+            w.matmul_scatter_signal(xt.data_ptr(), peers, m, n, peer_flags, rank, epoch)
         be.peer_wait(flags, world, rank, epoch)
     be.synchronize()
     yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
