@@ -281,7 +281,7 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
     float sub = 0.f, top = 0.f;   // multipliers of s
     switch (fmt) {
         case fmt_of(MXFP4, GGUF): sub = 1.f; top = 12.f; break;        // s = 2^(E-127) / 2, codes are 2 x value
-        case fmt_of(MXFP6_E2M3, GGUF): sub = 1.f; top = 7.5f; break;
+        case fmt_of(MXFP6_E2M3, GGUF): sub = 8.f; top = 7.5f; break;    // the prefill converter forms (8 x value) x (s / 8)
         case fmt_of(MXFP6_E3M2, GGUF): sub = 1.f; top = 28.f; break;
         case fmt_of(Q4_K, GGUF): sub = 63.f; top = 63.f * 16.f; break; // d sc q - dmin m
         case fmt_of(Q5_K, GGUF): sub = 63.f; top = 63.f * 32.f; break;
@@ -291,9 +291,13 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
         default: return;
     }
     float smax = 0.f;
+    bool small_block = false;   // MXFP6 E2M3: a block with codes and a scale below 2^-21 (its int8 x f16 products would round)
     for (int64_t b = 0; b < n_blocks; b++) {
         const uint8_t* p = blocks + b * I.block_bytes;
         float s;
+        if (fmt == fmt_of(MXFP6_E2M3, GGUF) && p[0] < 106) {
+            for (int j = 1; j < 25 && !small_block; j++) small_block = p[j] != 0;
+        }
         switch (fmt) {
             case fmt_of(MXFP4, GGUF): s = p[0] == 255 ? INFINITY : ldexpf(0.5f, (int)p[0] - 127); break;
             case fmt_of(MXFP6_E2M3, GGUF):
@@ -307,6 +311,7 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
     }
     if (!(smax * sub <= 60000.f) || smax * sub < 6.2e-5f) *scales_ok = false;
     if (!(smax * top <= 60000.f) || smax < 6.2e-5f) *weights_ok = false;
+    if (small_block) *scales_ok = false;
     if (smax == 0.f) *scales_ok = *weights_ok = true;   // an all-zero tensor is exact on every path
 }
 

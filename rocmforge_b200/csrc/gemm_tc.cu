@@ -40,6 +40,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "gemv_i8.cuh"
 
 namespace b200q {
 
@@ -104,6 +105,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(cx), "r"(cy)
         : "memory");
+}
+
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 
 // Tiled store shared -> global (clipped at the tensor's edges), tracked by the thread's bulk-copy groups.
@@ -706,6 +714,10 @@ struct SkArgs {
     float* ws;           // [gridDim.x][bn][128] partial accumulators
     int* flags;          // [gridDim.x]
     int epoch;
+    // MXFP6 (QF 6): the tensor's decode image (items of 16 rows x 128 k, 2048 code bytes + 64 exponent bytes each)
+    const uint8_t* img;
+    int img_nh;          // items per row tile
+    int img_nrt;         // row tiles of 16 rows
 };
 
 constexpr int SK_SLOT_FLOATS = BM * 256;
@@ -740,9 +752,11 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // inside a stage: [128 rows x 128 B ql][128 rows x 64 B qh][128 rows x 16 B scales]
     // QF 3 = GGUF Q4_0: MXFP4's code rows; QF 4 = GGUF Q8_0: 256 code bytes per row and step, two 128-byte boxes
     // QF 5 = GGUF Q5_K: Q4_K's block with 32 bytes of fifth bits (qh) between the scales and the nibbles
-    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 5 ? 176 : (QF == 1 || QF == 3) ? 128 : QF == 4 ? 256 : 208;
+    // QF 6 = GGUF MXFP6 E2M3 from the decode image: codes widened to int8 (8 x value) at upload, 256 bytes per row and step,
+    //        fetched as the 2048 code bytes of 16 items (8 row tiles x 2 k-halves) by untiled bulk copies
+    constexpr int RAW_ROW_BYTES = QF == 0 ? 144 : QF == 5 ? 176 : (QF == 1 || QF == 3) ? 128 : (QF == 4 || QF == 6) ? 256 : 208;
     constexpr int RAW_STAGE_BYTES = BM * RAW_ROW_BYTES;
-    constexpr int RS = (QF == 2 || QF == 4 || QF == 5) ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
+    constexpr int RS = (QF == 2 || QF == 4 || QF == 5 || QF == 6) ? 2 : RAW_STAGES;   // raw ring depth; Q6_K's 26 KB stages leave room for two beside the staging tile
     const GemmArgs& a = k.a;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte aligned by an OFFSET on the shared array (a round trip through an integer would hide the
@@ -884,6 +898,18 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int rs = rit % RS;
                     const uint32_t ph = (uint32_t)(rit / RS) & 1;
                     if (!mbar_wait(smem_u32(&raw_empty[rs]), ph ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
+                    if constexpr (QF == 6) {
+                        // row tiles past the tensor's last one are not copied (their rows are never stored)
+                        const int T0 = row0 >> 4, nT = min(8, k.img_nrt - T0);
+                        const uint32_t st = smem_u32(sRaw + rs * RAW_STAGE_BYTES), bar = smem_u32(&raw_full[rs]);
+                        mbar_arrive_expect_tx(bar, (uint32_t)nT * 4096u);
+                        for (int j = 0; j < nT; j++) {
+                            const uint8_t* src = k.img + ((int64_t)(T0 + j) * k.img_nh + 2 * sb) * 2112;
+                            bulk_load(st + (uint32_t)j * 4096u, src, 2048u, bar);
+                            bulk_load(st + (uint32_t)j * 4096u + 2048u, src + 2112, 2048u, bar);
+                        }
+                        continue;
+                    }
                     mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), (uint32_t)RAW_STAGE_BYTES);
                     if constexpr (QF == 2) {
                         const uint32_t st = smem_u32(sRaw + rs * RAW_STAGE_BYTES), bar = smem_u32(&raw_full[rs]);
@@ -1083,6 +1109,53 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
                         }
                         // stages are handed over in pairs (128 k): one wait before the first store, one arrival after the second
+                        if ((c & 1) == 0) {
+                            if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
+                            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        tmem_st16(slot0 + (uint32_t)s * A_SLOT_COLS, v);
+                        if (c & 1) {
+                            tmem_st_wait();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&full[s >> 1]));
+                        }
+                    }
+                } else if constexpr (QF == 6) {
+                    // MXFP6 E2M3 from the decode image: int8 codes = 8 x value (exact). A stage holds, per row tile j of
+                    // 16 rows and k-half hh, 2048 bytes: [rows g | rows g + 8] x [first | second 16 codes of a block],
+                    // 16-byte chunk (g, t) of block t at 8 t + ((g + 2 t) & 7). This thread takes block 2c + nib of
+                    // k-block c; byte ^ 0x80 widened by one PRMT per pair to 1152 + q, minus 1152, times 2^(e-127) / 8:
+                    // exact in f16 for block exponents 106..140. Natural weight order.
+                    const uint8_t* stage = sRaw + rs * RAW_STAGE_BYTES + (r >> 4) * 4096 + ((r >> 3) & 1) * 1024;
+                    const int g8 = r & 7;
+                    const int64_t grow = min((int64_t)row0 + r, (int64_t)a.n_rows - 1);
+                    const uint2 ex = __ldg(reinterpret_cast<const uint2*>(a.v.p[0] + grow * (a.k >> 5) + sb * 8));
+                    const __half2 k1152 = __float2half2_rn(1152.0f);
+#pragma unroll
+                    for (int c = 0; c < 4; c++, it++) {
+                        const int s = it & (STAGES - 1);
+                        const uint32_t ph = (uint32_t)(it >> 2) & 1;
+                        const int blk = 2 * c + nib, t4 = blk & 3;
+                        const uint32_t eb = ((blk < 4 ? ex.x : ex.y) >> (8 * t4)) & 0xFFu;
+                        // 2^(eb - 130) built from bits: eb <= 116 lands in the f16 subnormals, still exact down to 2^-24
+                        const __half2 S = __float2half2_rn(__uint_as_float(eb >= 4u ? (eb - 3u) << 23 : 0u));
+                        const uint8_t* cp = stage + (blk >> 2) * 2048 + ((8 * t4 + ((g8 + 2 * t4) & 7)) << 4);
+                        const uint4 qa = *reinterpret_cast<const uint4*>(cp);
+                        const uint4 qb = *reinterpret_cast<const uint4*>(cp + 512);
+                        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                        uint32_t v[16];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const uint32_t u4 = w[j] ^ 0x80808080u;
+                            uint32_t t0 = __byte_perm(u4, 0x64646464u, 0x5140), t1 = __byte_perm(u4, 0x64646464u, 0x7362);
+                            __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1152), S);
+                            __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1152), S);
+                            v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                            v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                        }
                         if ((c & 1) == 0) {
                             if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
                             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
@@ -1516,6 +1589,14 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
     return tiles * (w->k / 256) < (1ll << 30);
 }
 
+// GGUF MXFP6 E2M3 takes the tensor-memory kernel through its decode image (int8 codes), when the tensor has one.
+bool mx6_tmem_path(const b200q_weight* w, int m) {
+    if (w->fmt != fmt_of(MXFP6_E2M3, GGUF) || (w->k % 256) != 0 || !w->f16_scales_ok || !w->dimg.base || w->dimg.kind != DK_MX6) return false;
+    const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+    const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
+    return tiles * (w->k / 256) < (1ll << 30);
+}
+
 // GGUF Q5_K takes the tensor-memory kernel under the same conditions (persistent kernel only).
 bool q5k_tmem_path(const b200q_weight* w, int m) {
     if (w->fmt != fmt_of(Q5_K, GGUF) || (w->k % 256) != 0 || !w->f16_scales_ok) return false;
@@ -1631,6 +1712,33 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
         B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<2>, ctas, smem, map, pm[0], pm[1], pm[2], ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
+        return B200Q_OK;
+    }
+    if (may_allocate && mx6_tmem_path(w, m)) {
+        // MXFP6 E2M3 with the weight operand in tensor memory, read from the decode image (persistent kernel only)
+        a.a_col0 = (bn + 31) & ~31;
+        a.tmem_cols = 32;
+        while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
+        const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 + (size_t)2 * BM * 256 + (2 * STAGES + 2 * RAW_STAGES + 4) * 8 + 32 + STAGE_EPI_BYTES;
+        a.staged_epilogue = y_tma_ok ? 1 : 0;
+        const int nsb = (int)(w->k / 256);
+        const int64_t units = (int64_t)grid.x * grid.y * nsb;
+        const int ctas = (int)std::min<int64_t>(ctx->info.sm_count, units);
+        int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
+        if (rc != B200Q_OK) return rc;
+        if ((rc = make_wsmap()) != B200Q_OK) return rc;
+        static bool configured_mx6[64] = {};
+        rc = configure_once(ctx, gemm_tmem_sk_kernel<6>, configured_mx6);
+        if (rc != B200Q_OK) return rc;
+        SkArgs k{};
+        k.a = a;
+        k.tiles_x = (int)grid.x; k.nsb = nsb; k.total_units = (int)units;
+        k.ws = static_cast<float*>(ctx->sk_ws);
+        k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
+        if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
+        k.epoch = ctx->sk_epoch;
+        k.img = w->dimg.base; k.img_nh = w->dimg.nh; k.img_nrt = w->dimg.nrt;
+        B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<6>, ctas, smem, map, map, map, map, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
     if (may_allocate && mx4_tmem_path(w, m)) {

@@ -1149,15 +1149,20 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         }
         store_tile<MANY>(po, pend_rt, pend, m, lane);
     }
-    // scattered products: when every CTA's stores to the peers are out, the last CTA tells the peers
+    // scattered products: when every CTA's stores to the peers are out, the last CTA tells the peers. One system-scope
+    // fence per CTA (after the barrier it covers the whole CTA's stores), one more in the last CTA between its
+    // observation of the counter and the flag stores, which are then plain system-scope stores issued back to back
+    // (a release store per peer would wait for a round trip over NVLink each).
     if (sig.n > 0) {
-        __threadfence_system();
         __syncthreads();
-        if (threadIdx.x == 0 && atomicAdd(&sched[2], 1) == (int)gridDim.x - 1) {
-            sched[2] = 0;
+        if (threadIdx.x == 0) {
             __threadfence_system();
-            for (int p = 0; p < sig.n; p++)
-                if (p != sig.my) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sig.flag[p] + sig.my), "r"(sig.epoch) : "memory");
+            if (atomicAdd(&sched[2], 1) == (int)gridDim.x - 1) {
+                sched[2] = 0;
+                __threadfence_system();
+                for (int p = 0; p < sig.n; p++)
+                    if (p != sig.my) asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(sig.flag[p] + sig.my), "r"(sig.epoch) : "memory");
+            }
         }
     }
     // the last CTA to run out of units resets the counters for the next launch

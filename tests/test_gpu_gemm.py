@@ -161,7 +161,8 @@ def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
     w.free()
 
 
-@pytest.mark.parametrize("case", ["mxfp4-huge", "mxfp4-tiny", "mxfp4-nan-free-mix", "q4k-big-d", "q8_0-big-d"])
+@pytest.mark.parametrize("case", ["mxfp4-huge", "mxfp4-tiny", "mxfp4-nan-free-mix", "q4k-big-d", "q8_0-big-d",
+                                  "mxfp6-huge", "mxfp6-tiny", "mxfp6-mixed-exponents", "mxfp6-ordinary"])
 def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
     """The tensor-memory prefill kernels form block scales in f16. The upload scans the scale bytes: a tensor whose
     scales (or weights) leave the f16 range takes the next more careful kernel, down to the fp32 decode kernels, so
@@ -180,6 +181,19 @@ def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
         else:
             blocks[::7, 0] = 0x00        # a few vanishing blocks among ordinary ones
             blocks[3::11, 0] = 0x40
+    elif case.startswith("mxfp6"):
+        # E2M3 reaches the tensor-memory kernel as int8 codes times 2^(e-130) in f16: exact for e in 106..140
+        qt = synth.MXFP6_E2M3
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+        blocks = data.reshape(-1, 25)
+        if case == "mxfp6-huge":
+            blocks[:, 0] = 0x90
+        elif case == "mxfp6-tiny":
+            blocks[:, 0] = 0x40
+        elif case == "mxfp6-mixed-exponents":
+            blocks[::5, 0] = 0x00        # vanishing blocks with codes among ordinary ones: not the f16 path
+            blocks[1::9, 0] = 106
+            blocks[2::9, 0] = 139
     elif case == "q4k-big-d":
         qt = synth.Q4_K
         data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
