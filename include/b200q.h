@@ -296,6 +296,30 @@ int b200q_gguf_tensor_data(const b200q_gguf* file, int64_t index, const void** h
 int b200q_gguf_upload_tensor(b200q_ctx* ctx, const b200q_gguf* file, int64_t index, int shard_rank, int shard_count,
                              b200q_weight** out);
 
+/* ---- bulk upload into one allocation --------------------------------------------------------------------
+ * Replaces GgufLoader::load_to_gpu_async / arena_upload_phase (src/loader/gguf/types.rs:326,
+ * src/loader/gguf/gpu_upload.rs:413-594) and ModelWeightArena (src/memory/arena.rs:82,206): ONE device allocation
+ * for all tensors of a model, bump-allocated in 256-byte aligned pieces. Unlike the reference's arena the tensors
+ * stay packed (their planes, plus the decode image where the format has one). Uploads into an arena are queued on
+ * the context's stream without waiting for one another (file bytes -> staging buffer -> plane split -> image
+ * build); b200q_synchronize, or any product on the same context, orders behind them. Handles are freed with
+ * b200q_weight_free as usual (their memory returns with the arena); b200q_arena_free refuses while handles live. */
+typedef struct b200q_arena b200q_arena;
+/* bytes one tensor (or one rank's shard of n_local rows) takes in an arena */
+int b200q_arena_tensor_bytes(int qtype, int layout, int orient, int64_t n_local, int64_t k, size_t* bytes);
+int b200q_arena_create(b200q_ctx* ctx, size_t capacity, b200q_arena** out);
+/* b200q_weight_upload into the arena; B200Q_ERR_ALLOC when the arena is full */
+int b200q_arena_upload(b200q_ctx* ctx, b200q_arena* arena, const void* h_packed, size_t nbytes, int qtype, int layout,
+                       int orient, int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out);
+int b200q_arena_info(const b200q_arena* arena, size_t* capacity, size_t* used, int64_t* tensors, int64_t* live);
+int b200q_arena_free(b200q_arena* arena);
+/* Every tensor of the file this library has packed kernels for, into a new arena sized for exactly them.
+ * handles[i] (i < n_handles = b200q_gguf_tensor_count) receives tensor i's handle, or NULL for a tensor type
+ * without packed kernels (F32/F16 norms and the like stay with the caller). A tensor whose row count does not
+ * divide by shard_count is uploaded whole on every rank. Returns after the last copy is queued. */
+int b200q_gguf_upload_all(b200q_ctx* ctx, const b200q_gguf* file, int shard_rank, int shard_count, b200q_arena** arena_out,
+                          b200q_weight** handles, int64_t n_handles);
+
 #ifdef __cplusplus
 }
 #endif

@@ -77,6 +77,12 @@ SIGNATURES = {
     "b200q_matmul_scatter": (_i, [_vp, _vp, _vp, _i, _pvp, _i, _i64, _i, _u]),
     "b200q_peer_signal": (_i, [_vp, _pvp, _i, _i, _i]),
     "b200q_peer_wait": (_i, [_vp, _vp, _i, _i, _i]),
+    "b200q_arena_tensor_bytes": (_i, [_i, _i, _i, _i64, _i64, ctypes.POINTER(ctypes.c_size_t)]),
+    "b200q_arena_create": (_i, [_vp, ctypes.c_size_t, _pvp]),
+    "b200q_arena_upload": (_i, [_vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i, _i64, _i64, _i, _i, _pvp]),
+    "b200q_arena_info": (_i, [_vp, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "b200q_arena_free": (_i, [_vp]),
+    "b200q_gguf_upload_all": (_i, [_vp, _vp, _i, _i, _pvp, _pvp, _i64]),
     "b200q_matmul_scatter_signal": (_i, [_vp, _vp, _vp, _i, _pvp, _i, _i64, _i, _u, _pvp, _i, _i]),
     "b200q_ipc_get_handle": (_i, [_vp, _vp, _vp]),
     "b200q_ipc_open": (_i, [_vp, _vp, _pvp]),

@@ -150,6 +150,43 @@ class B200Backend:
         self.close()
 
 
+class WeightArena:
+    """ModelWeightArena (src/memory/arena.rs:82,206) for packed tensors: one device allocation, 256-byte aligned
+    bump allocation. Uploads are queued on the backend's stream without waiting for one another."""
+
+    def __init__(self, backend, capacity=None, handle=None):
+        self.backend = backend
+        if handle is None:
+            handle = ctypes.c_void_p()
+            check(backend.lib.b200q_arena_create(backend.ctx, int(capacity), ctypes.byref(handle)))
+        self.handle = handle
+
+    @staticmethod
+    def tensor_bytes(backend, qtype, layout, n_local, k, orient=_lib.ORIENT_NK) -> int:
+        b = ctypes.c_size_t()
+        check(backend.lib.b200q_arena_tensor_bytes(qtype, layout, orient, n_local, k, ctypes.byref(b)))
+        return b.value
+
+    def upload(self, data, qtype, layout, n, k, orient=_lib.ORIENT_NK, shard_rank=0, shard_count=1) -> "QuantizedWeight":
+        a = as_u8(data)
+        h = ctypes.c_void_p()
+        check(self.backend.lib.b200q_arena_upload(self.backend.ctx, self.handle, _host_ptr(a), a.size, qtype, layout, orient, n, k,
+                                                  shard_rank, shard_count, ctypes.byref(h)))
+        return QuantizedWeight.from_handle(self.backend, h)
+
+    def info(self) -> dict:
+        cap, used = ctypes.c_size_t(), ctypes.c_size_t()
+        t, live = ctypes.c_int64(), ctypes.c_int64()
+        check(self.backend.lib.b200q_arena_info(self.handle, ctypes.byref(cap), ctypes.byref(used), ctypes.byref(t), ctypes.byref(live)))
+        return {"capacity": cap.value, "used": used.value, "tensors": t.value, "live": live.value}
+
+    def free(self):
+        """Refused (B200Error) while weight handles of the arena are alive."""
+        if self.handle:
+            check(self.backend.lib.b200q_arena_free(self.handle))
+            self.handle = None
+
+
 class QuantizedWeight:
     """A packed tensor resident on the device (what load_tensor_to_gpu hands out for a quantized weight)."""
 

@@ -317,13 +317,15 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
 
 // Allocates the planes for n_blocks blocks, copies `avail` bytes of file blocks from the host (zero
 // filling the rest) and splits them into planes. Used by upload and by dequantize_bytes.
+// With `place` (plane_layout() bytes inside an arena) and `stage_buf` (room for the file blocks) nothing is allocated
+// and the stream is not synchronised: copies and kernels of consecutive tensors queue up behind one another.
 static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t avail, int64_t n_blocks, void** base_out,
-                       WView* view_out) {
+                       WView* view_out, uint8_t* place = nullptr, void* stage_buf = nullptr) {
     FmtInfo I = fmt_info(fmt);
     size_t off[4] = {0, 0, 0, 0};
     size_t total = plane_layout(fmt, n_blocks, off);
-    void* base = nullptr;
-    B200Q_CUDA(cudaMalloc(&base, total), B200Q_ERR_ALLOC);
+    void* base = place;
+    if (!place) B200Q_CUDA(cudaMalloc(&base, total), B200Q_ERR_ALLOC);
     WView v{};
     for (int j = 0; j < I.nplanes; j++) v.p[j] = static_cast<uint8_t*>(base) + off[j];
     size_t raw_bytes = (size_t)n_blocks * I.block_bytes;
@@ -334,13 +336,13 @@ static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t a
         // the file layout is the device layout
         e = cudaMemsetAsync(static_cast<uint8_t*>(base) + avail, 0, total - avail, ctx->stream);
         if (e == cudaSuccess && avail) e = cudaMemcpyAsync(base, h_bytes, avail, cudaMemcpyHostToDevice, ctx->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess && !place) e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(B200Q_ERR_COPY, e, "upload copy");
     } else {
-        void* stage = nullptr;
-        e = cudaMalloc(&stage, raw_bytes ? raw_bytes : 1);
+        void* stage = stage_buf;
+        if (!stage) e = cudaMalloc(&stage, raw_bytes ? raw_bytes : 1);
         if (e != cudaSuccess) {
-            cudaFree(base);
+            if (!place) cudaFree(base);
             return cuda_fail(B200Q_ERR_ALLOC, e, "upload staging");
         }
         e = cudaMemsetAsync(base, 0, total, ctx->stream);
@@ -349,12 +351,14 @@ static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t a
         if (e == cudaSuccess && avail) e = cudaMemcpyAsync(stage, h_bytes, avail, cudaMemcpyHostToDevice, ctx->stream);
         if (e != cudaSuccess) rc = cuda_fail(B200Q_ERR_COPY, e, "upload copy");
         if (rc == B200Q_OK) rc = launch_repack(ctx, fmt, static_cast<const uint8_t*>(stage), n_blocks, v);
-        e = cudaStreamSynchronize(ctx->stream);
-        if (rc == B200Q_OK && e != cudaSuccess) rc = cuda_fail(B200Q_ERR_DEVICE, e, "upload repack");
-        cudaFree(stage);
+        if (!stage_buf) {
+            e = cudaStreamSynchronize(ctx->stream);
+            if (rc == B200Q_OK && e != cudaSuccess) rc = cuda_fail(B200Q_ERR_DEVICE, e, "upload repack");
+            cudaFree(stage);
+        }
     }
     if (rc != B200Q_OK) {
-        cudaFree(base);
+        if (!place) cudaFree(base);
         return rc;
     }
     *base_out = base;
@@ -362,8 +366,15 @@ static int make_planes(b200q_ctx* ctx, int fmt, const uint8_t* h_bytes, size_t a
     return B200Q_OK;
 }
 
-int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
-                        int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out) {
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static bool image_enabled() {
+    const char* no_img = getenv("B200Q_NO_DECODE_IMAGE");
+    return !(no_img && no_img[0] == '1');
+}
+
+static int weight_upload_impl(b200q_ctx* ctx, b200q_arena* arena, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
+                              int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out) {
     CTX_GUARD("weight_upload");
     if (!out) return fail(B200Q_ERR_INVALID, "weight_upload: out is null");
     *out = nullptr;
@@ -398,15 +409,111 @@ int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int 
     w->n_elements = n_el; w->n_blocks = n_blocks;
     w->packed_bytes = (size_t)n_blocks * I.block_bytes;
     if (layout == GGUF) scan_f16_ranges(fmt, src, n_blocks, &w->f16_scales_ok, &w->f16_weights_ok);
-    int rc = make_planes(ctx, fmt, src, w->packed_bytes, n_blocks, &w->base, &w->view);
+    const bool image = image_enabled() && decode_image_wanted(fmt, orient, n_local, k);
+    uint8_t *place = nullptr, *img_place = nullptr;
+    if (arena) {
+        // bump allocation, 256-byte aligned (ModelWeightArena, src/memory/arena.rs:82,206); the staging buffer grows to
+        // the largest tensor seen (a growth waits for the copies queued on the old one)
+        size_t off[4];
+        const size_t planes = align256(plane_layout(fmt, n_blocks, off));
+        const size_t img = image ? align256(decode_image_bytes(fmt, n_local, k)) : 0;
+        if (arena->used + planes + img > arena->capacity) {
+            delete w;
+            return fail(B200Q_ERR_ALLOC, "arena_upload: tensor needs %zu bytes, arena has %zu of %zu left", planes + img,
+                        arena->capacity - arena->used, arena->capacity);
+        }
+        if (I.nplanes > 1 && arena->stage_bytes < w->packed_bytes) {
+            cudaStreamSynchronize(ctx->stream);
+            if (arena->stage) cudaFree(arena->stage);
+            arena->stage = nullptr;
+            arena->stage_bytes = 0;
+            cudaError_t e = cudaMalloc(&arena->stage, w->packed_bytes);
+            if (e != cudaSuccess) { delete w; return cuda_fail(B200Q_ERR_ALLOC, e, "arena staging"); }
+            arena->stage_bytes = w->packed_bytes;
+        }
+        place = arena->base + arena->used;
+        img_place = image ? place + planes : nullptr;
+        arena->used += planes + img;
+    }
+    int rc = make_planes(ctx, fmt, src, w->packed_bytes, n_blocks, &w->base, &w->view, place, arena ? arena->stage : nullptr);
     if (rc != B200Q_OK) { delete w; return rc; }
     // second, decode-ordered copy for the m <= 8 kernel (B200Q_NO_DECODE_IMAGE=1 keeps only the stream layout)
-    const char* no_img = getenv("B200Q_NO_DECODE_IMAGE");
-    if (!(no_img && no_img[0] == '1') && decode_image_wanted(fmt, orient, n_local, k)) {
-        rc = build_decode_image(ctx, w, &w->dimg);
-        if (rc != B200Q_OK) { cudaFree(w->base); delete w; return rc; }
+    if (image) {
+        rc = build_decode_image(ctx, w, &w->dimg, img_place);
+        if (rc != B200Q_OK) { if (!arena) cudaFree(w->base); delete w; return rc; }
+    }
+    if (arena) {
+        w->arena = arena;
+        arena->tensors++;
+        arena->live++;
     }
     *out = w;
+    return B200Q_OK;
+}
+
+int b200q_weight_upload(b200q_ctx* ctx, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
+                        int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out) {
+    return weight_upload_impl(ctx, nullptr, h_bytes, nbytes, qtype, layout, orient, n, k, shard_rank, shard_count, out);
+}
+
+int b200q_arena_tensor_bytes(int qtype, int layout, int orient, int64_t n_local, int64_t k, size_t* bytes) {
+    if (!bytes) return fail(B200Q_ERR_INVALID, "arena_tensor_bytes: bytes is null");
+    if (!valid_qtype(qtype) || !valid_layout(layout) || n_local <= 0 || k <= 0)
+        return fail(B200Q_ERR_INVALID, "arena_tensor_bytes: qtype %d / layout %d / %lld x %lld", qtype, layout, (long long)n_local, (long long)k);
+    const int fmt = fmt_of(qtype, layout);
+    FmtInfo I = fmt_info(fmt);
+    const int64_t n_blocks = (n_local * k + I.block_elems - 1) / I.block_elems;
+    size_t off[4];
+    size_t total = align256(plane_layout(fmt, n_blocks, off));
+    if (image_enabled() && decode_image_wanted(fmt, orient, n_local, k)) total += align256(decode_image_bytes(fmt, n_local, k));
+    *bytes = total;
+    return B200Q_OK;
+}
+
+int b200q_arena_create(b200q_ctx* ctx, size_t capacity, b200q_arena** out) {
+    CTX_GUARD("arena_create");
+    if (!out) return fail(B200Q_ERR_INVALID, "arena_create: out is null");
+    *out = nullptr;
+    if (capacity == 0) return fail(B200Q_ERR_INVALID, "arena_create: capacity is 0");
+    b200q_arena* a = new b200q_arena();
+    a->ctx = ctx;
+    a->capacity = align256(capacity);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, a->capacity);
+    if (e != cudaSuccess) {
+        delete a;
+        return cuda_fail(B200Q_ERR_ALLOC, e, "arena_create");
+    }
+    a->base = static_cast<uint8_t*>(p);
+    *out = a;
+    return B200Q_OK;
+}
+
+int b200q_arena_upload(b200q_ctx* ctx, b200q_arena* arena, const void* h_bytes, size_t nbytes, int qtype, int layout, int orient,
+                       int64_t n, int64_t k, int shard_rank, int shard_count, b200q_weight** out) {
+    if (!arena) return fail(B200Q_ERR_INVALID, "arena_upload: arena is null");
+    if (ctx && arena->ctx != ctx) return fail(B200Q_ERR_INVALID, "arena_upload: the arena belongs to another context");
+    return weight_upload_impl(ctx, arena, h_bytes, nbytes, qtype, layout, orient, n, k, shard_rank, shard_count, out);
+}
+
+int b200q_arena_info(const b200q_arena* arena, size_t* capacity, size_t* used, int64_t* tensors, int64_t* live) {
+    if (!arena) return fail(B200Q_ERR_INVALID, "arena_info: arena is null");
+    if (capacity) *capacity = arena->capacity;
+    if (used) *used = arena->used;
+    if (tensors) *tensors = arena->tensors;
+    if (live) *live = arena->live;
+    return B200Q_OK;
+}
+
+int b200q_arena_free(b200q_arena* arena) {
+    if (!arena) return B200Q_OK;
+    if (arena->live != 0) return fail(B200Q_ERR_INVALID, "arena_free: %lld weight handles of this arena are still alive", (long long)arena->live);
+    cudaSetDevice(arena->ctx->device);
+    cudaStreamSynchronize(arena->ctx->stream);
+    if (arena->stage) cudaFree(arena->stage);
+    cudaFree(arena->base);
+    cudaGetLastError();
+    delete arena;
     return B200Q_OK;
 }
 
@@ -415,8 +522,12 @@ int b200q_weight_free(b200q_weight* w) {
     b200q_ctx* ctx = w->ctx;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    cudaFree(w->base);
-    if (w->dimg.base) cudaFree(w->dimg.base);
+    if (w->arena) {
+        w->arena->live--;   // the memory goes back with the arena
+    } else {
+        cudaFree(w->base);
+        if (w->dimg.base) cudaFree(w->dimg.base);
+    }
     cudaGetLastError();
     delete w;
     return B200Q_OK;

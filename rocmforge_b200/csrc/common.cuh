@@ -54,8 +54,21 @@ struct DImage {
 };
 }  // namespace b200q
 
+// One device allocation that holds the planes and decode images of many tensors (256-byte aligned sub-allocations),
+// plus the staging buffer their file bytes pass through.
+struct b200q_arena {
+    b200q_ctx* ctx = nullptr;
+    uint8_t* base = nullptr;
+    size_t capacity = 0, used = 0;
+    void* stage = nullptr;
+    size_t stage_bytes = 0;
+    int64_t tensors = 0;   // handles handed out
+    int64_t live = 0;      // ... and not yet freed
+};
+
 struct b200q_weight {
     b200q_ctx* ctx = nullptr;
+    b200q_arena* arena = nullptr;   // set when base and dimg.base are sub-allocations of an arena
     int qtype = 0, layout = 0, orient = 0, fmt = 0;
     int64_t n_local = 0, k = 0, row0 = 0, n_total = 0;
     int64_t n_elements = 0;  // n_local * k

@@ -1423,7 +1423,13 @@ bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k) {
     return items < (1ll << 31) / 8;   // item counts of a CTA's segment stay inside 32-bit arithmetic
 }
 
-int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
+size_t decode_image_bytes(int fmt, int64_t n_rows, int64_t k) {
+    const int kind = decode_kind_of(fmt);
+    if (kind == DK_NONE) return 0;
+    return (size_t)((n_rows + 15) / 16) * (size_t)(k / 128) * decode_item_bytes(kind) + 256;
+}
+
+int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out, uint8_t* place) {
     *out = DImage{};
     const int kind = decode_kind_of(w->fmt);
     if (kind == DK_NONE) return B200Q_OK;
@@ -1434,13 +1440,13 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
     d.nrt = (int)((w->n_local + 15) / 16);
     const int64_t n_items = (int64_t)d.nrt * d.nh;
     d.bytes = (size_t)n_items * d.item_bytes;
-    void* p = nullptr;
-    B200Q_CUDA(cudaMalloc(&p, d.bytes + 256), B200Q_ERR_ALLOC);
+    void* p = place;
+    if (!place) B200Q_CUDA(cudaMalloc(&p, d.bytes + 256), B200Q_ERR_ALLOC);
     d.base = static_cast<uint8_t*>(p);
     const int64_t threads = n_items * 32;
     const int64_t grid = (threads + 255) / 256;
     if (grid > 0x7FFFFFFF) {
-        cudaFree(p);
+        if (!place) cudaFree(p);
         return fail(B200Q_ERR_INVALID, "upload: tensor too large for one image-build launch");
     }
     if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
@@ -1451,9 +1457,9 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
     else if (kind == DK_MX4) build_image_mx4_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else build_image_s8_kernel<DK_MX6><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && !place) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
-        cudaFree(p);
+        if (!place) cudaFree(p);
         return cuda_fail(B200Q_ERR_LAUNCH, e, "upload: decode image");
     }
     *out = d;

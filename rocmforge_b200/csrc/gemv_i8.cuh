@@ -14,8 +14,10 @@ int decode_kind_of(int fmt);
 int decode_item_bytes(int kind);
 // true when the tensor can carry a decode image (NK, a format of the kernel, k a multiple of 128)
 bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k);
-// Builds the image of `w` (its stream-layout planes are already on the device) into a new allocation.
-int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out);
+// Builds the image of `w` (its stream-layout planes are already on the device) into a new allocation, or at `place`
+// (decode_image_bytes() bytes, 256-byte aligned) without synchronising the stream.
+int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out, uint8_t* place = nullptr);
+size_t decode_image_bytes(int fmt, int64_t n_rows, int64_t k);
 
 // One fused dequant + matmul product inside a grouped launch of the integer decode kernel.
 struct DOp {

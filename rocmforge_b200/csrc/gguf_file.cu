@@ -344,4 +344,47 @@ int b200q_gguf_upload_tensor(b200q_ctx* ctx, const b200q_gguf* g, int64_t index,
                                shard_count, out);
 }
 
+int b200q_gguf_upload_all(b200q_ctx* ctx, const b200q_gguf* g, int shard_rank, int shard_count, b200q_arena** arena_out,
+                          b200q_weight** handles, int64_t n_handles) {
+    if (!ctx || !g || !arena_out || !handles) return fail(B200Q_ERR_INVALID, "gguf_upload_all: null argument");
+    *arena_out = nullptr;
+    if (n_handles != (int64_t)g->tensors.size())
+        return fail(B200Q_ERR_INVALID, "gguf_upload_all: %lld handle slots for %zu tensors", (long long)n_handles, g->tensors.size());
+    if (shard_count < 1 || shard_rank < 0 || shard_rank >= shard_count) return fail(B200Q_ERR_INVALID, "gguf_upload_all: shard %d of %d", shard_rank, shard_count);
+    const int layout = (g->flags & B200Q_GGUF_REFERENCE_FIXTURE) ? B200Q_LAYOUT_RF : B200Q_LAYOUT_GGUF;
+    for (int64_t i = 0; i < n_handles; i++) handles[i] = nullptr;
+    // pass 1: what the arena has to hold (MemoryCalculator's role, src/memory/)
+    size_t total = 0;
+    for (const TensorEntry& t : g->tensors) {
+        if (t.qtype < 0) continue;
+        const int64_t n_local = (shard_count > 1 && t.n % shard_count == 0) ? t.n / shard_count : t.n;
+        size_t b = 0;
+        int rc = b200q_arena_tensor_bytes(t.qtype, layout, B200Q_ORIENT_NK, n_local, t.k, &b);
+        if (rc != B200Q_OK) return rc;
+        total += b;
+    }
+    if (total == 0) return fail(B200Q_ERR_UNSUPPORTED, "gguf_upload_all: the file holds no tensor type this library has packed kernels for");
+    b200q_arena* arena = nullptr;
+    int rc = b200q_arena_create(ctx, total, &arena);
+    if (rc != B200Q_OK) return rc;
+    // pass 2: queue the uploads
+    for (size_t i = 0; i < g->tensors.size() && rc == B200Q_OK; i++) {
+        const TensorEntry& t = g->tensors[i];
+        if (t.qtype < 0) continue;
+        const bool split = shard_count > 1 && t.n % shard_count == 0;
+        rc = b200q_arena_upload(ctx, arena, g->map + t.abs_offset, (size_t)t.nbytes, t.qtype, layout, B200Q_ORIENT_NK, t.n, t.k,
+                                split ? shard_rank : 0, split ? shard_count : 1, &handles[i]);
+    }
+    if (rc != B200Q_OK) {
+        for (int64_t i = 0; i < n_handles; i++) {
+            if (handles[i]) b200q_weight_free(handles[i]);
+            handles[i] = nullptr;
+        }
+        b200q_arena_free(arena);
+        return rc;
+    }
+    *arena_out = arena;
+    return B200Q_OK;
+}
+
 }  // extern "C"

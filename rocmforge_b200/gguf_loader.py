@@ -146,6 +146,7 @@ class GgufLoader:
             self.lazy_tensors[name] = LazyTensor(name, t.file_offset, t.nbytes, tuple(t.dims[:t.n_dims]),
                                                  TYPE_NAMES.get(t.ggml_type, str(t.ggml_type)), i, t.qtype, t.n, t.k)
         self.gpu_cache: Dict[Tuple[str, int, int], QuantizedWeight] = {}
+        self.arenas = []
 
     def tensor_names(self):
         return list(self.lazy_tensors)
@@ -187,10 +188,37 @@ class GgufLoader:
             out[name] = self.load_tensor_to_gpu(name, backend, shard_rank, shard_count)
         return out
 
+    def load_to_gpu_async(self, backend, shard_rank=0, shard_count=1) -> Dict[str, QuantizedWeight]:
+        """GgufLoader::load_to_gpu_async (src/loader/gguf/types.rs:326): every tensor with packed kernels goes into ONE
+        arena sized for exactly them (arena_upload_phase, gpu_upload.rs:413-594); copies and layout kernels are queued
+        on the backend's stream and this returns without waiting for them. The weights enter the cache under their
+        names, so load_tensor_to_gpu serves them afterwards."""
+        from .backend import WeightArena
+        n = len(self.lazy_tensors)
+        handles = (ctypes.c_void_p * n)()
+        arena = ctypes.c_void_p()
+        check(self.lib.b200q_gguf_upload_all(backend.ctx, self.handle, shard_rank, shard_count, ctypes.byref(arena), handles, n))
+        self.arenas.append(WeightArena(backend, handle=arena))
+        out = {}
+        for name, lt in self.lazy_tensors.items():
+            h = handles[lt.index]
+            if not h:
+                continue
+            w = QuantizedWeight.from_handle(backend, ctypes.c_void_p(h))
+            old = self.gpu_cache.pop((name, shard_rank, shard_count), None)
+            if old is not None:
+                old.free()
+            self.gpu_cache[(name, shard_rank, shard_count)] = w
+            out[name] = w
+        return out
+
     def close(self):
         for w in self.gpu_cache.values():
             w.free()
         self.gpu_cache.clear()
+        for a in getattr(self, "arenas", []):
+            a.free()
+        self.arenas = []
         if self.handle:
             self.lib.b200q_gguf_close(self.handle)
             self.handle = None

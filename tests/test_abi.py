@@ -72,3 +72,24 @@ def test_no_device_is_a_status_not_a_crash(lib):
         from rocmforge_b200.backend import B200Backend
         B200Backend(0)
     assert e.value.status == _lib.ERR_NO_DEVICE and not e.value.recoverable
+
+
+def test_arena_tensor_bytes_is_host_arithmetic():
+    """Planes plus the decode image (NK tensors of the decode kernel's formats with k % 128 == 0), each rounded up to
+    256 bytes: computed without touching a device."""
+    import ctypes
+    from rocmforge_b200 import _lib, synth
+    lib = _lib.load()
+    def nbytes(qt, orient, n, k):
+        b = ctypes.c_size_t()
+        assert lib.b200q_arena_tensor_bytes(qt, synth.GGUF, orient, n, k, ctypes.byref(b)) == 0
+        return b.value
+    n, k = 64, 512
+    packed = n * k // 256 * 144
+    nk, kn = nbytes(synth.Q4_K, _lib.ORIENT_NK, n, k), nbytes(synth.Q4_K, _lib.ORIENT_KN, n, k)
+    assert packed <= kn <= packed + 512 and kn % 256 == 0       # the planes (with their tail padding); no image for KN
+    items = (n // 16) * (k // 128)
+    assert nk == kn + (items * 1216 + 256 + 255) // 256 * 256
+    assert nbytes(synth.Q2_K, _lib.ORIENT_NK, n, k) % 256 == 0  # a format without an image
+    b = ctypes.c_size_t()
+    assert lib.b200q_arena_tensor_bytes(99, synth.GGUF, _lib.ORIENT_NK, n, k, ctypes.byref(b)) != 0

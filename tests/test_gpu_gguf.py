@@ -59,3 +59,61 @@ def test_reference_fixture_style_dequantises_bit_exactly(oracle, tmp_path):
     got = out.to_numpy(np.float32, 8 * 64)
     assert np.array_equal(got.view(np.uint32), oracle.dequantize(synth.Q4_0, synth.RF, bytes(data), 8 * 64).view(np.uint32))
     L.close()
+
+
+def test_bulk_upload_into_one_arena_equals_per_tensor_uploads(oracle, tmp_path):
+    """load_to_gpu_async: every packed tensor of the file in ONE allocation, uploads queued without waiting for one
+    another. Products and dequantised values equal those of tensors uploaded one by one, bit for bit."""
+    from rocmforge_b200._lib import B200QError as B200Error
+    from rocmforge_b200.backend import WeightArena
+    tensors = make_tensors(31)
+    path = tmp_path / "bulk.gguf"
+    write_model(path, tensors)
+    be = backend()
+    L = GgufLoader(path)
+    weights = L.load_to_gpu_async(be)
+    assert set(weights) == {t[0] for t in tensors}
+    arena = L.arenas[0]
+    info = arena.info()
+    want = sum(WeightArena.tensor_bytes(be, qt, synth.GGUF, n, k) for _, qt, n, k, _ in tensors)
+    assert info["tensors"] == info["live"] == len(tensors)
+    assert info["used"] == want == info["capacity"] and want % 256 == 0
+    assert L.load_tensor_to_gpu(tensors[0][0], be) is weights[tensors[0][0]]        # served from the cache afterwards
+    with pytest.raises(B200Error):
+        arena.free()                                                                # handles are alive
+    L2 = GgufLoader(path)
+    rng = synth.rng_for(32)
+    for name, qt, n, k, data in tensors:
+        single = L2.load_tensor_to_gpu(name, be)
+        for m in (1, 8, 64):
+            x = synth.gen_activations(m, k, rng)
+            assert np.array_equal(weights[name].matmul_host(x), single.matmul_host(x)), (name, m)
+        a, b = be.allocate_buffer(n * k * 4), be.allocate_buffer(n * k * 4)
+        weights[name].dequantize(a)
+        single.dequantize(b)
+        be.synchronize()
+        assert np.array_equal(a.to_numpy(np.uint32, n * k), b.to_numpy(np.uint32, n * k))
+        assert np.array_equal(a.to_numpy(np.float32, n * k).view(np.uint32), oracle.dequantize(qt, synth.GGUF, bytes(data), n * k).view(np.uint32))
+        a.free(); b.free()
+    L2.close()
+    L.close()                                                                       # frees the handles, then the arena
+    assert L.arenas == []
+
+
+def test_arena_refuses_what_does_not_fit(tmp_path):
+    from rocmforge_b200._lib import B200QError as B200Error
+    from rocmforge_b200.backend import WeightArena
+    be = backend()
+    qt, n, k = synth.Q4_K, 64, 256
+    data = synth.gen_packed(qt, synth.GGUF, n * k, synth.rng_for(33))
+    need = WeightArena.tensor_bytes(be, qt, synth.GGUF, n, k)
+    arena = WeightArena(be, need + 256)
+    w = arena.upload(data, qt, synth.GGUF, n, k)
+    with pytest.raises(B200Error) as e:
+        arena.upload(data, qt, synth.GGUF, n, k)
+    assert "arena" in str(e.value)
+    x = synth.gen_activations(1, k, synth.rng_for(34))
+    y = w.matmul_host(x)
+    assert np.all(np.isfinite(y))
+    w.free()
+    arena.free()
