@@ -32,7 +32,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from rocmforge_b200 import synth  # noqa: E402
+from rocmforge_b200 import _lib, synth  # noqa: E402
 
 STEP_BYTES = 339_916_416
 METRIC = "Q4_K-model decode GEMV packed-weight GB/s at M=%d"
@@ -379,18 +379,38 @@ def shard_leg(be, rank, world, steps):
                 w.matmul_scatter_signal(xt.data_ptr(), peers, m, n, peer_flags, rank, epoch[0])
                 be.peer_wait(flags, world, rank, epoch[0])
 
+            # the same with bf16 outputs (B200Q_MM_SCATTER_BF16, prefill only): half the bytes over NVLink
+            t_fused16 = None
+            if m > 8:
+                y16 = be.allocate_buffer(m * n * 2)
+                h16 = [None] * world
+                dist.all_gather_object(h16, be.ipc_handle(y16))
+                peers16 = [y16.as_ptr() if r == rank else be.ipc_open(h16[r]) for r in range(world)]
+
+                def fused16():
+                    epoch[0] += 1
+                    w.matmul_scatter_signal(xt.data_ptr(), peers16, m, n, peer_flags, rank, epoch[0], flags=_lib.MM_SCATTER_BF16)
+                    be.peer_wait(flags, world, rank, epoch[0])
+
             for _ in range(3):
                 with_gather()
                 fused()
+                if m > 8:
+                    fused16()
             t_kernel = timed(kernel, steps)
             t_total = timed(with_gather, steps)
             t_fused = timed(fused, steps)
+            if m > 8:
+                t_fused16 = timed(fused16, steps)
             gathered = int(m * n * 4 * (world - 1) / world)
             case = {"qtype": qname, "m": m, "ranks": world, "ms_kernel": t_kernel, "ms_kernel_plus_allgather": t_total,
                     "ms_fused_peer_stores_plus_flags": t_fused,
                     "gathered_bytes_per_rank": gathered,
                     # what the bytes every rank must receive cost at the measured peer-copy rate of this pool
                     "nvlink_floor_ms": gathered / 770e9 * 1e3, "nvlink_GBps_assumed": 770}
+            if t_fused16 is not None:
+                case["ms_fused_bf16_outputs"] = t_fused16
+                case["nvlink_floor_ms_bf16"] = gathered / 2 / 770e9 * 1e3
             if rank == 0:
                 yb = torch.empty((m, n), dtype=torch.float32, device="cuda")
                 for _ in range(3):
@@ -408,6 +428,8 @@ def shard_leg(be, rank, world, steps):
                 case["efficiency_kernel"] = t1 / (world * t_kernel)
                 case["efficiency_with_allgather"] = t1 / (world * t_total)
                 case["efficiency_fused"] = t1 / (world * t_fused)
+                if t_fused16 is not None:
+                    case["efficiency_fused_bf16"] = t1 / (world * t_fused16)
                 # the gathered result equals the unsharded one (same kernel, same per-row arithmetic)
                 got = y_all.permute(1, 0, 2).reshape(m, n)
                 case["max_abs_diff_vs_unsharded"] = float((got - yb).abs().max().item())
@@ -418,7 +440,11 @@ def shard_leg(be, rank, world, steps):
                 if r != rank:
                     be.ipc_close(peers[r])
                     be.ipc_close(peer_flags[r])
+                    if m > 8:
+                        be.ipc_close(peers16[r])
             dist.barrier()
+            if m > 8:
+                y16.free()
             y_full.free()
             flags.free()
             out["cases"].append(case)

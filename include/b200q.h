@@ -75,6 +75,8 @@ typedef enum { B200Q_F32 = 0, B200Q_BF16 = 1 } b200q_dtype;
 #define B200Q_MM_DEFAULT 0u
 #define B200Q_MM_SEQUENTIAL 1u /* one thread per output, ascending k, multiply then add: bit-identical to cpu_matmul_f32 */
 #define B200Q_MM_NO_TENSOR 2u  /* never take the tcgen05 path (CUDA-core kernels only) */
+#define B200Q_MM_SCATTER_BF16 4u /* b200q_matmul_scatter[_signal] only, m > 8: every output is bf16 [m, ldy] (half the
+                                  * bytes over NVLink), rounded once from the fp32 accumulators */
 
 typedef struct {
     char name[128];

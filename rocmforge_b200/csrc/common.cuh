@@ -31,6 +31,7 @@ struct b200q_ctx {
     int sk_epoch = 0;
     // while b200q_matmul_scatter runs: the same output slice in the other GPUs' full outputs (peer-mapped)
     int scatter_extra = 0;
+    bool scatter_bf16 = false;   // the outputs of the scattered product are bf16
     float* scatter_y[7] = {};
     // ... and the peers' flag arrays when the product's last CTA is to signal them (scatter_sig_n == 0: no signal)
     int* scatter_flag[8] = {};

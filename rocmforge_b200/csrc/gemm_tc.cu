@@ -34,6 +34,7 @@
 // Every wait is bounded by a clock budget; on expiry the kernel raises a status word, all roles leave
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
 #include <algorithm>
+#include <atomic>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -280,6 +281,7 @@ struct GemmArgs {
     int n_extra;           // further copies of y to write: the same slice inside other GPUs' full outputs
     float* y_extra[7];     // (peer-mapped pointers; stores over NVLink only, plain or TMA, never loads)
     int staged_epilogue;   // persistent kernel: finished tiles leave through shared memory and tiled TMA stores
+    int y_bf16;            // staged epilogue only: y (and its copies on other GPUs) are bf16, rounded once from fp32
 };
 
 // Warp roles (384 threads = 12 warps; a warp may only read the TMEM lane quarter warp_id % 4):
@@ -1363,6 +1365,18 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     // row scales of the block's 32 activation rows: 128-byte aligned, read four at a time (the
                     // scale array is padded, and rows past m are clipped by the store)
                     const float4* sc4 = reinterpret_cast<const float4*>(a.xscale + tok0 + c0);
+                    if (a.y_bf16) {
+                        // bf16 outputs: the block is staged as [32 activation rows][32 weight rows] of 2 bytes
+                        __nv_bfloat16* w16 = reinterpret_cast<__nv_bfloat16*>(wstg);
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; j4++) {
+                            const float4 sc = __ldg(sc4 + j4);
+                            w16[(4 * j4 + 0) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 0]) * sc.x);
+                            w16[(4 * j4 + 1) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 1]) * sc.y);
+                            w16[(4 * j4 + 2) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 2]) * sc.z);
+                            w16[(4 * j4 + 3) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 3]) * sc.w);
+                        }
+                    } else {
 #pragma unroll
                     for (int j4 = 0; j4 < 8; j4++) {
                         const float4 sc = __ldg(sc4 + j4);
@@ -1370,6 +1384,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         wstg[(4 * j4 + 1) * 32 + lane] = __uint_as_float(v[4 * j4 + 1]) * sc.y;
                         wstg[(4 * j4 + 2) * 32 + lane] = __uint_as_float(v[4 * j4 + 2]) * sc.z;
                         wstg[(4 * j4 + 3) * 32 + lane] = __uint_as_float(v[4 * j4 + 3]) * sc.w;
+                    }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
@@ -1543,7 +1558,8 @@ EncodeTiledFn get_encode_fn() {
 }
 
 template <typename K>
-int configure_once(b200q_ctx* ctx, K kernel, bool* configured) {
+// The flags are atomics: contexts of one device may be driven from different threads (setting the attribute twice is harmless).
+int configure_once(b200q_ctx* ctx, K kernel, std::atomic<bool>* configured) {
     if (!configured[ctx->device & 63]) {
         B200Q_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
         configured[ctx->device & 63] = true;
@@ -1553,7 +1569,7 @@ int configure_once(b200q_ctx* ctx, K kernel, bool* configured) {
 
 template <int F>
 int launch_fmt(b200q_ctx* ctx, const CUtensorMap& map, const GemmArgs& a, dim3 grid, size_t smem) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     int rc = configure_once(ctx, gemm_tc_kernel<F>, configured);
     if (rc != B200Q_OK) return rc;
     gemm_tc_kernel<F><<<grid, NTHREADS, smem, ctx->stream>>>(map, a);
@@ -1647,16 +1663,20 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     dim3 grid((unsigned)((w->n_local + BM - 1) / BM), (unsigned)((m + bn - 1) / bn));
     // tile stores of the persistent kernel's staged epilogue: y as a [m, n_local] fp32 tensor with row pitch ldy
     CUtensorMap ymap = map;
-    bool y_tma_ok = (ldy % 4) == 0 && (reinterpret_cast<uintptr_t>(d_y) & 15) == 0;
+    const bool y16 = ctx->scatter_bf16;   // outputs are bf16 (a scattered product with B200Q_MM_SCATTER_BF16)
+    a.y_bf16 = y16 ? 1 : 0;
+    bool y_tma_ok = (ldy % (y16 ? 8 : 4)) == 0 && (reinterpret_cast<uintptr_t>(d_y) & 15) == 0;
+    if (y16 && !may_allocate) return fail(B200Q_ERR_UNSUPPORTED, "%s: bf16 outputs need the persistent kernel", who);
     for (int p = 0; p < ctx->scatter_extra; p++) y_tma_ok = y_tma_ok && (reinterpret_cast<uintptr_t>(ctx->scatter_y[p]) & 15) == 0;
+    if (y16 && !y_tma_ok) return fail(B200Q_ERR_UNSUPPORTED, "%s: bf16 outputs must be 16-byte aligned with ldy %% 8 == 0", who);
     PeerMaps peers;
     for (int p = 0; p < 7; p++) peers.m[p] = map;
     if (y_tma_ok) {
         cuuint64_t ydim[2] = {(cuuint64_t)w->n_local, (cuuint64_t)m};
-        cuuint64_t ystr[1] = {(cuuint64_t)ldy * 4};
+        cuuint64_t ystr[1] = {(cuuint64_t)ldy * (y16 ? 2 : 4)};
         cuuint32_t ybox[2] = {32u, 32u};   // one epilogue warp's block: 32 weight rows x 32 activation rows
         for (int p = -1; p < ctx->scatter_extra; p++) {   // this GPU's output, then the peers' (a scattered product)
-            r = enc(p < 0 ? &ymap : &peers.m[p], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p < 0 ? d_y : ctx->scatter_y[p], ydim, ystr, ybox,
+            r = enc(p < 0 ? &ymap : &peers.m[p], y16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p < 0 ? d_y : ctx->scatter_y[p], ydim, ystr, ybox,
                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output %d) failed with code %d", who, p + 1, (int)r);
@@ -1701,7 +1721,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
         if (rc != B200Q_OK) return rc;
         if ((rc = make_wsmap()) != B200Q_OK) return rc;
-        static bool configured_q6[64] = {};
+        static std::atomic<bool> configured_q6[64] = {};
         rc = configure_once(ctx, gemm_tmem_sk_kernel<2>, configured_q6);
         if (rc != B200Q_OK) return rc;
         SkArgs k{};
@@ -1727,7 +1747,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         int rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
         if (rc != B200Q_OK) return rc;
         if ((rc = make_wsmap()) != B200Q_OK) return rc;
-        static bool configured_mx6[64] = {};
+        static std::atomic<bool> configured_mx6[64] = {};
         rc = configure_once(ctx, gemm_tmem_sk_kernel<6>, configured_mx6);
         if (rc != B200Q_OK) return rc;
         SkArgs k{};
@@ -1766,8 +1786,8 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         if (rc != B200Q_OK) return rc;
         if ((rc = make_wsmap()) != B200Q_OK) return rc;
         const bool q40 = w->fmt == fmt_of(Q4_0, GGUF);
-        static bool configured_mx[64] = {}, configured_q40[64] = {};
-        static bool configured_q80[64] = {};
+        static std::atomic<bool> configured_mx[64] = {}, configured_q40[64] = {};
+        static std::atomic<bool> configured_q80[64] = {};
         rc = q80 ? configure_once(ctx, gemm_tmem_sk_kernel<4>, configured_q80)
                  : q40 ? configure_once(ctx, gemm_tmem_sk_kernel<3>, configured_q40) : configure_once(ctx, gemm_tmem_sk_kernel<1>, configured_mx);
         if (rc != B200Q_OK) return rc;
@@ -1793,7 +1813,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         const size_t smem = 1024 + (size_t)STAGES * bn * BK * 2 +
                             (q5k ? (size_t)2 * BM * 176 : (size_t)RAW_STAGES * RAW_STAGE_BYTES) +   // Q5_K: raw ring of two stages
                             (2 * STAGES + 2 * RAW_STAGES + 1) * 8 + 16;
-        static bool configured[64] = {};
+        static std::atomic<bool> configured[64] = {};
         int rc = q5k ? B200Q_OK : configure_once(ctx, gemm_q4k_tmem_kernel, configured);
         if (rc != B200Q_OK) return rc;
         CUtensorMap wmap;
@@ -1813,7 +1833,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             rc = ensure_sk_workspace(ctx, ctx->info.sm_count);
             if (rc != B200Q_OK) return rc;
             if ((rc = make_wsmap()) != B200Q_OK) return rc;
-            static bool configured_sk[64] = {}, configured_q5k[64] = {};
+            static std::atomic<bool> configured_sk[64] = {}, configured_q5k[64] = {};
             rc = q5k ? configure_once(ctx, gemm_tmem_sk_kernel<5>, configured_q5k) : configure_once(ctx, gemm_tmem_sk_kernel<0>, configured_sk);
             if (rc != B200Q_OK) return rc;
             SkArgs k{};
@@ -1828,10 +1848,12 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             else B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<0>, ctas, smem + 32 + STAGE_EPI_BYTES, map, wmap, wmap, wmap, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
             return B200Q_OK;
         }
+        if (y16) return fail(B200Q_ERR_UNSUPPORTED, "%s: bf16 outputs need the persistent kernel", who);
         gemm_q4k_tmem_kernel<<<grid, NTHREADS, smem, ctx->stream>>>(map, wmap, a);
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }
+    if (y16) return fail(B200Q_ERR_UNSUPPORTED, "%s: bf16 outputs need a format of the tensor-memory kernel with k %% 256 == 0 and block scales in the f16 range", who);
     a.tmem_cols = 32;
     while (a.tmem_cols < bn) a.tmem_cols <<= 1;
     const size_t smem = 1024 + (size_t)STAGES * (A_STAGE_BYTES + (size_t)bn * BK * 2) + (3 * STAGES + 1) * 8 + 16;
@@ -1911,7 +1933,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_X16_BYT
 
 // In host code the array's name is only a stand-in; the device address has to be asked for, once per
 // device, with that device current.
-static void* g_noalloc_dev_ptr[64] = {};
+static std::atomic<void*> g_noalloc_dev_ptr[64] = {};
 
 int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, float* d_y, int m) {
     if (!gemm_tc_supported(w, m)) return fail(B200Q_ERR_UNSUPPORTED, "matmul_noalloc: needs an NK tensor with k %% 64 == 0");
@@ -1920,14 +1942,14 @@ int launch_gemm_tc_noalloc(b200q_ctx* ctx, const b200q_weight* w, const float* d
         return fail(B200Q_ERR_INVALID,
                     "matmul_noalloc: m=%d x k=%lld needs %zu bytes of scratch; the built-in scratch holds m*k <= %zu elements and m <= %zu rows",
                     m, (long long)w->k, (size_t)m * (size_t)w->k * 2, NOALLOC_X16_BYTES / 2, NOALLOC_SCALE_BYTES / sizeof(float));
-    if (!g_noalloc_dev_ptr[ctx->device]) {
+    if (!g_noalloc_dev_ptr[ctx->device].load()) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || !p) return cuda_fail(B200Q_ERR_INIT, e, "cudaGetSymbolAddress(built-in scratch)");
         g_noalloc_dev_ptr[ctx->device] = p;
     }
-    __half* d_x16 = static_cast<__half*>(g_noalloc_dev_ptr[ctx->device]);
-    float* d_scale = reinterpret_cast<float*>(static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device]) + NOALLOC_X16_BYTES);
+    __half* d_x16 = static_cast<__half*>(g_noalloc_dev_ptr[ctx->device].load());
+    float* d_scale = reinterpret_cast<float*>(static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device].load()) + NOALLOC_X16_BYTES);
     // nothing in the scratch has to start at zero: the conversion below rewrites every element the GEMM reads
     const int perm = w->fmt == fmt_of(Q4_K, GGUF) ? 1 : 0;
     int rc = launch_x_to_f16(ctx, d_x, w->k, d_x16, d_scale, m, (int)w->k, perm);

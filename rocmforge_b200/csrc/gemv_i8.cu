@@ -32,6 +32,7 @@
 #include <cuda_fp16.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <atomic>
 
 #include "gemv_i8.cuh"
 
@@ -1565,7 +1566,7 @@ int launch_gemv_i8(b200q_ctx* ctx, const DOp* h_single, const DOp* d_ops, int n_
     if (total_rt <= 0) return B200Q_OK;
     if (n_units > total_rt) n_units = total_rt;
     if (n_ctas > n_units) n_ctas = n_units;
-    static bool configured[64][2] = {};
+    static std::atomic<bool> configured[64][2] = {};
     const int ki = L.many ? 1 : 0;
     const void* kernels[2] = {(const void*)gemv_i8_kernel<8, false>, (const void*)gemv_i8_kernel<16, true>};
     if (!configured[ctx->device & 63][ki]) {

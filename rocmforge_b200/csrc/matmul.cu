@@ -1,4 +1,5 @@
 // b200q_matmul*: argument checks and the choice of kernel for one fused dequant + matmul.
+#include <cuda_bf16.h>
 #include <vector>
 
 #include "common.cuh"
@@ -235,6 +236,24 @@ int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x,
     if (flags & B200Q_MM_SEQUENTIAL) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: the sequential kernel writes one output only");
     if (m > 8 && ((flags & B200Q_MM_NO_TENSOR) || !gemm_tc_supported(w, m)))
         return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: m > 8 needs the tensor-core prefill kernels");
+    if (flags & B200Q_MM_SCATTER_BF16) {
+        // bf16 outputs: the prefill kernels' staged epilogue only
+        if (m <= 8) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: bf16 outputs are for m > 8 (the decode kernel writes fp32)");
+        if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return fail(B200Q_ERR_INVALID, "matmul_scatter: unknown activation dtype %d", x_dtype);
+        if (w->ctx->device != ctx->device) return fail(B200Q_ERR_INVALID, "matmul_scatter: weight lives on device %d, ctx on %d", w->ctx->device, ctx->device);
+        if (!d_x) return fail(B200Q_ERR_INVALID, "matmul_scatter: null activation pointer");
+        B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+        ctx->scatter_extra = n_outputs - 1;
+        ctx->scatter_bf16 = true;
+        for (int p = 1; p < n_outputs; p++)
+            ctx->scatter_y[p - 1] = reinterpret_cast<float*>(static_cast<__nv_bfloat16*>(d_y_full[p]) + w->row0);
+        int rc = launch_gemm_tc(ctx, w, d_x, x_dtype == B200Q_BF16 ? 1 : 0, w->k,
+                                reinterpret_cast<float*>(static_cast<__nv_bfloat16*>(d_y_full[0]) + w->row0), ldy, m);
+        ctx->scatter_extra = 0;
+        ctx->scatter_bf16 = false;
+        if (rc == B200Q_OK) ctx->tc_pending = true;
+        return rc;
+    }
     ctx->scatter_extra = n_outputs - 1;
     for (int p = 1; p < n_outputs; p++) ctx->scatter_y[p - 1] = static_cast<float*>(d_y_full[p]) + w->row0;
     int rc = b200q_matmul_ex(ctx, w, d_x, x_dtype, 0, static_cast<float*>(d_y_full[0]) + w->row0, B200Q_F32, ldy, m, flags);

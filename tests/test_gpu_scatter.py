@@ -45,6 +45,41 @@ def test_every_shard_lands_in_every_output(oracle, qt, m, tol):
         w.free()
 
 
+def _bf16_bits(a):
+    """fp32 -> bf16 with round-to-nearest-even, as 16-bit patterns (finite inputs)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+@pytest.mark.parametrize("qt", [synth.Q4_K, synth.MXFP4, synth.Q8_0, synth.MXFP6_E2M3], ids=["q4k", "mxfp4", "q8_0", "mxfp6"])
+def test_bf16_outputs_are_the_fp32_ones_rounded_once(qt):
+    """B200Q_MM_SCATTER_BF16: the same accumulators, rounded to bf16 in the epilogue, in every copy."""
+    be = backend()
+    rng = synth.rng_for(6300 + qt)
+    n, k, m, shards, copies = 512, 1024, 200, 2, 3
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    xb = be.allocate_buffer(x.nbytes)
+    xb.copy_from_host(x)
+    o32 = [be.allocate_buffer(m * n * 4) for _ in range(copies)]
+    o16 = [be.allocate_buffer(m * n * 2) for _ in range(copies)]
+    for o in o32 + o16:
+        o.fill(0xFF)
+    ws = [QuantizedWeight(be, data, qt, synth.GGUF, n, k, shard_rank=r, shard_count=shards) for r in range(shards)]
+    for w in ws:
+        w.matmul_scatter(xb, o32, m, n)
+        w.matmul_scatter(xb, o16, m, n, flags=_lib.MM_SCATTER_BF16)
+    be.synchronize()
+    want = _bf16_bits(o32[0].to_numpy(np.float32, m * n))
+    for o in o16:
+        assert np.array_equal(o.to_numpy(np.uint16, m * n), want)
+    with pytest.raises(B200QError) as e:
+        ws[0].matmul_scatter(xb, o16, 4, n, flags=_lib.MM_SCATTER_BF16)     # the decode kernel writes fp32
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    for w in ws:
+        w.free()
+
+
 def test_scatter_argument_errors():
     be = backend()
     rng = synth.rng_for(6200)
