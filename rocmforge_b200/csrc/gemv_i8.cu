@@ -676,22 +676,21 @@ __device__ __forceinline__ void item_s8_many(uint32_t it, const LaneBM& lb, int 
 }
 
 // ------------------------------------------------------------------------------------------ MXFP4 (GGUF)
-// Eight E2M1 codes (one word) -> four byte words: the magnitudes 2 * |e2m1(code)| of the non-negative codes
-// 0..3 and 4..7 (zero where the code is negative), and the same for the negative codes. A byte permute with the raw
-// nibbles as selector returns the table byte where the sign bit is clear and 0x00 where it is set (its
-// sign-replicate mode on a table of bytes below 0x80), so each half costs one instruction; the product with the
-// negative part is subtracted after the MMAs.
+// Eight E2M1 codes (one word) -> two byte words of OFFSET codes u = 12 + 2 * e2m1(code) in 0..24, so that one unsigned
+// operand carries the signed weights and the -12 is taken back through the group sums (12 * sum x, as Q4_0 does with
+// its 8). A byte permute with the raw nibbles as selector returns the table byte where the sign bit is clear and 0x00
+// where it is set (its sign-replicate mode on a table of bytes below 0x80); the same on the sign-flipped word with
+// the table of the negative codes; the two are disjoint and OR-ed. Five instructions per eight codes.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {   // bit 3 of a selector nibble: replicate the sign
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-__device__ __forceinline__ void e2m1x8_split(uint32_t w, uint32_t& p_lo, uint32_t& p_hi, uint32_t& n_lo, uint32_t& n_hi) {
+__device__ __forceinline__ void e2m1x8_offset(uint32_t w, uint32_t& u_lo, uint32_t& u_hi) {
+    // 12 + {0,1,2,3,4,6,8,12} and 12 - {0,1,2,3,4,6,8,12}
     const uint32_t wn = w ^ 0x88888888u;
-    p_lo = prmt(0x03020100u, 0x0C080604u, w);
-    p_hi = prmt(0x03020100u, 0x0C080604u, w >> 16);
-    n_lo = prmt(0x03020100u, 0x0C080604u, wn);
-    n_hi = prmt(0x03020100u, 0x0C080604u, wn >> 16);
+    u_lo = prmt(0x0F0E0D0Cu, 0x18141210u, w) | prmt(0x090A0B0Cu, 0x00040608u, wn);
+    u_hi = prmt(0x0F0E0D0Cu, 0x18141210u, w >> 16) | prmt(0x090A0B0Cu, 0x00040608u, wn >> 16);
 }
 
 __device__ __forceinline__ void mx4_scales_lane(uint32_t it, int lane, float& s0, float& s1) {
@@ -712,22 +711,20 @@ __device__ __forceinline__ void item_mx4_one(uint32_t it, const LaneB1& lb, int 
     const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w}, w1[4] = {wb.x, wb.y, wb.z, wb.w};
     const uint32_t bq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     const uint32_t br[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    int cp_[4] = {0, 0, 0, 0}, ep[4] = {0, 0, 0, 0}, cn[4] = {0, 0, 0, 0}, en[4] = {0, 0, 0, 0};
+    int c[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        uint32_t p0, p2, n0, n2, p1, p3, n1, n3;
-        e2m1x8_split(w0[j], p0, p2, n0, n2);
-        e2m1x8_split(w1[j], p1, p3, n1, n3);
-        mma_u8s8(cp_, p0, p1, p2, p3, bq[2 * j], bq[2 * j + 1]);
-        mma_u8s8(ep, p0, p1, p2, p3, br[2 * j], br[2 * j + 1]);
-        mma_u8s8(cn, n0, n1, n2, n3, bq[2 * j], bq[2 * j + 1]);
-        mma_u8s8(en, n0, n1, n2, n3, br[2 * j], br[2 * j + 1]);
+        uint32_t u0, u2, u1, u3;
+        e2m1x8_offset(w0[j], u0, u2);
+        e2m1x8_offset(w1[j], u1, u3);
+        mma_u8s8(c, u0, u1, u2, u3, bq[2 * j], bq[2 * j + 1]);
+        mma_u8s8(e, u0, u1, u2, u3, br[2 * j], br[2 * j + 1]);
     }
-    const int v0 = ((cp_[0] - cn[0]) * 128 + (cp_[1] - cn[1])) * 128 + (ep[0] - en[0]);
-    const int v1 = ((cp_[2] - cn[2]) * 128 + (cp_[3] - cn[3])) * 128 + (ep[2] - en[2]);
-    const float f = __uint_as_float(fSb.x);
-    acc[0] = fmaf(s0, (float)v0 * f, acc[0]);
-    acc[1] = fmaf(s1, (float)v1 * f, acc[1]);
+    const int v0 = (c[0] * 128 + c[1]) * 128 + e[0];
+    const int v1 = (c[2] * 128 + c[3]) * 128 + e[2];
+    const float f = __uint_as_float(fSb.x), S12 = __uint_as_float(fSb.y);
+    acc[0] = fmaf(s0, fmaf((float)v0, f, -S12), acc[0]);
+    acc[1] = fmaf(s1, fmaf((float)v1, f, -S12), acc[1]);
 }
 
 __device__ __forceinline__ void item_mx4_many(uint32_t it, const LaneBM& lb, int h, float (&acc)[4], int lane) {
@@ -741,24 +738,18 @@ __device__ __forceinline__ void item_mx4_many(uint32_t it, const LaneBM& lb, int
         const uint4 fSb = lds128(lb.f0 + (4 * h + s) * lb.fb);
         float s0, s1;
         mx4_scales_lane(it, 4 * g + s, s0, s1);
-        uint32_t p0, p1, p2, p3, n0, n1, n2, n3;
-        e2m1x8_split(w0, p0, p2, n0, n2);
-        e2m1x8_split(w1, p1, p3, n1, n3);
-        int c0[4], c1[4], c2[4], d0[4], d1[4], d2[4];
-        mma_u8s8_z(c0, p0, p1, p2, p3, b0.x, b0.y);
-        mma_u8s8_z(c1, p0, p1, p2, p3, b1.x, b1.y);
-        mma_u8s8_z(c2, p0, p1, p2, p3, b2.x, b2.y);
-        mma_u8s8_z(d0, n0, n1, n2, n3, b0.x, b0.y);
-        mma_u8s8_z(d1, n0, n1, n2, n3, b1.x, b1.y);
-        mma_u8s8_z(d2, n0, n1, n2, n3, b2.x, b2.y);
-        const float fa = __uint_as_float(fSb.x), fb = __uint_as_float(fSb.z);
-        float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) v[j] = (float)(((c0[j] - d0[j]) * 128 + (c1[j] - d1[j])) * 128 + (c2[j] - d2[j]));
-        acc[0] = fmaf(s0, v[0] * fa, acc[0]);
-        acc[1] = fmaf(s0, v[1] * fb, acc[1]);
-        acc[2] = fmaf(s1, v[2] * fa, acc[2]);
-        acc[3] = fmaf(s1, v[3] * fb, acc[3]);
+        uint32_t u0, u1, u2, u3;
+        e2m1x8_offset(w0, u0, u2);
+        e2m1x8_offset(w1, u1, u3);
+        int c0[4], c1[4], c2[4];
+        mma_u8s8_z(c0, u0, u1, u2, u3, b0.x, b0.y);
+        mma_u8s8_z(c1, u0, u1, u2, u3, b1.x, b1.y);
+        mma_u8s8_z(c2, u0, u1, u2, u3, b2.x, b2.y);
+        const float fa = __uint_as_float(fSb.x), Sa = __uint_as_float(fSb.y), fb = __uint_as_float(fSb.z), Sb = __uint_as_float(fSb.w);
+        acc[0] = fmaf(s0, fmaf((float)((c0[0] * 128 + c1[0]) * 128 + c2[0]), fa, -Sa), acc[0]);
+        acc[1] = fmaf(s0, fmaf((float)((c0[1] * 128 + c1[1]) * 128 + c2[1]), fb, -Sb), acc[1]);
+        acc[2] = fmaf(s1, fmaf((float)((c0[2] * 128 + c1[2]) * 128 + c2[2]), fa, -Sa), acc[2]);
+        acc[3] = fmaf(s1, fmaf((float)((c0[3] * 128 + c1[3]) * 128 + c2[3]), fb, -Sb), acc[3]);
     }
 }
 
@@ -1093,7 +1084,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
         LaneB1 lb1{};
         LaneBM lbm{};
         if (op.kind == DK_MX4) {
-            prep_x<32, MANY, NW * 32, true>(op.x, op.ldx, op.k, m, ai, 1.0f);
+            prep_x<32, MANY, NW * 32, true>(op.x, op.ldx, op.k, m, ai, 12.0f);
             if (MANY) lbm = lane_bm(ai, zero, lane, m); else lb1 = lane_b1<32>(ai, zero, lane);
         } else if (op.kind == DK_Q40) {   // the image keeps 8 sum x
             prep_x<32, MANY, NW * 32>(op.x, op.ldx, op.k, m, ai, 8.0f);
