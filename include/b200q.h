@@ -195,9 +195,12 @@ int b200q_matmul_scatter(b200q_ctx* ctx, const b200q_weight* w, const void* d_x,
  * (b200q_malloc + b200q_memset to 0, exported like the outputs). b200q_peer_signal, enqueued behind the product,
  * stores `epoch` into slot my_rank of every other rank's array (release stores over NVLink; the product's own peer
  * stores are complete by then because the kernel has ended). b200q_peer_wait, enqueued on the same stream, holds the
- * stream until every other slot of THIS rank's array holds `epoch`; whatever follows it on the stream may read the
- * full output. The wait is bounded (about a second of SM clock): on expiry the next b200q_synchronize returns
- * B200Q_ERR_TIMEOUT and the context stays usable. Use a new epoch value for every product (a counter). */
+ * stream until every other slot of THIS rank's array holds `epoch` or a later value (a peer that runs ahead may
+ * already have signalled its next product); whatever follows it on the stream may read the full output. The wait
+ * is bounded (about a second of SM clock): on expiry the next b200q_synchronize returns B200Q_ERR_TIMEOUT and the
+ * context stays usable. Epochs must grow by one per product (a counter). A peer that runs ahead also stores its
+ * NEXT product's rows while this rank may still read the current ones: alternate two output buffers when both
+ * products write the same one. */
 int b200q_peer_signal(b200q_ctx* ctx, void* const* d_flags_of_ranks, int n_ranks, int my_rank, int epoch);
 /* b200q_matmul_scatter followed by b200q_peer_signal in one call (d_y_full[p] and d_flags_of_ranks[p] belong to rank p,
  * n_outputs ranks). The decode kernel raises the flags itself when its last CTA has stored its rows, so m <= 8 costs

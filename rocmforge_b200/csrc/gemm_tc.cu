@@ -776,10 +776,12 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint64_t* dfree = accum + 1;                 // epilogue has read the accumulator -> next segment's MMAs
     uint64_t* pfull = dfree + 1;                 // [4] rounds of a partial tile prefetched into the idle activation stages
     uint64_t* pgo = pfull + 4;                   // MMAs of the CTA's last segment complete -> the stages are idle
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pgo + 1);
+    uint64_t* gfree = pgo + 1;                   // [2] staging tile of an epilogue group may be overwritten (its stores have read it)
+    uint64_t* gready = gfree + 2;                // [2] the four warps of a group have written their blocks
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gready + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* stored = const_cast<int*>(abort_flag) + 1;   // epilogue warps whose partial-sum stores are fenced
-    // staging tile of the epilogue: 64 activation rows x 128 weight rows of fp32 (one TMA store box)
+    // staging tiles of the epilogue: per group of four warps 32 activation rows x 128 weight rows of fp32 (one TMA store box)
     float* stg = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(stored + 1) + ((128u - (smem_u32(stored + 1) & 127u)) & 127u));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -799,6 +801,10 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         mbar_init(smem_u32(dfree), 8);
         for (int s = 0; s < 4; s++) mbar_init(smem_u32(&pfull[s]), 1);
         mbar_init(smem_u32(pgo), 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(smem_u32(&gfree[s]), 1);
+            mbar_init(smem_u32(&gready[s]), 4);
+        }
         *abort_flag = 0;
         *stored = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -997,6 +1003,7 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // Partial sums are written with plain stores; the fence that completes them costs a round trip to L2,
         // so it waits until the next segment's first super-block is converted (the stores have landed by
         // then), and the publisher (warp 3) releases the flag once all eight warps have fenced.
+        int ep_round = 0;   // rounds of the staged epilogue so far (phase of the group's hand-over barriers)
         bool fence_due = false;
         auto fence_and_count = [&]() {
             __threadfence();
@@ -1329,8 +1336,21 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 // (its 32 weight rows x 32 activation rows), stages it in a private 4 KB buffer and stores it
                 // with its own copy (clipped at the edges of y), so the eight warps never wait for one another
                 // and no thread waits for global memory; the copies drain while the next segment's main loop runs.
+                // Scattered product (one store per GPU): the four warps that share a 32-row half of the round (warps 4..7:
+                // activation rows 0..31, warps 8..11: 32..63) write their 32 x 32 blocks side by side into ONE tile of [32 activation rows][128 weight
+                // rows], and the group's first warp stores it with one copy whose rows are 512 contiguous bytes (256
+                // in bf16): the copy engine spends its time per row, so four times fewer rows per byte. The hand-over
+                // inside a group goes through two mbarriers with bounded waits.
+                // A product stored to one output keeps a private 4 KB buffer and a store of its own per warp (no
+                // hand-over at all; measured faster there).
                 const int half_off = warp >= 8 ? 32 : 0;
-                float* wstg = stg + (warp - 4) * 1024;
+                const int grp = warp >= 8 ? 1 : 0;
+                const bool coop = a.n_extra > 0;
+                float* wstg = coop ? stg + grp * 4096 : stg + (warp - 4) * 1024;
+                const int wpitch = coop ? 128 : 32;            // elements per activation row of the staging tile
+                const int wcol = coop ? q * 32 + lane : lane;
+                const bool leader = (warp & 3) == 0;
+                const uint32_t gfree_b = smem_u32(&gfree[grp]), gready_b = smem_u32(&gready[grp]);
                 const int last_rnd = ((a.bn + 63) >> 6) * 64 - 64;
                 bool freed = false;
                 for (int rnd = 0; rnd < a.bn && ok; rnd += 64) {
@@ -1359,41 +1379,68 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(ps + j * BM));
                         }
                     }
-                    // this warp's previous store must have finished READING its buffer before it is overwritten
-                    if (lane == 0) bulk_wait_read0();
-                    __syncwarp();
+                    // the group's previous store must have finished READING the tile before it is overwritten
+                    if (lane == 0) {
+                        if (!coop) {
+                            bulk_wait_read0();
+                        } else {
+                            if (leader) {
+                                bulk_wait_read0();
+                                mbar_arrive(gfree_b);
+                            }
+                            ok = mbar_wait(gfree_b, (uint32_t)(ep_round & 1), abort_flag, a.status, 16);
+                        }
+                    }
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
                     // row scales of the block's 32 activation rows: 128-byte aligned, read four at a time (the
                     // scale array is padded, and rows past m are clipped by the store)
                     const float4* sc4 = reinterpret_cast<const float4*>(a.xscale + tok0 + c0);
                     if (a.y_bf16) {
                         // bf16 outputs: the block is staged as [32 activation rows][32 weight rows] of 2 bytes
-                        __nv_bfloat16* w16 = reinterpret_cast<__nv_bfloat16*>(wstg);
+                        __nv_bfloat16* w16 = reinterpret_cast<__nv_bfloat16*>(wstg) + wcol;
 #pragma unroll
                         for (int j4 = 0; j4 < 8; j4++) {
                             const float4 sc = __ldg(sc4 + j4);
-                            w16[(4 * j4 + 0) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 0]) * sc.x);
-                            w16[(4 * j4 + 1) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 1]) * sc.y);
-                            w16[(4 * j4 + 2) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 2]) * sc.z);
-                            w16[(4 * j4 + 3) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 3]) * sc.w);
+                            w16[(4 * j4 + 0) * wpitch] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 0]) * sc.x);
+                            w16[(4 * j4 + 1) * wpitch] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 1]) * sc.y);
+                            w16[(4 * j4 + 2) * wpitch] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 2]) * sc.z);
+                            w16[(4 * j4 + 3) * wpitch] = __float2bfloat16_rn(__uint_as_float(v[4 * j4 + 3]) * sc.w);
                         }
                     } else {
+                        float* w32 = wstg + wcol;
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; j4++) {
-                        const float4 sc = __ldg(sc4 + j4);
-                        wstg[(4 * j4 + 0) * 32 + lane] = __uint_as_float(v[4 * j4 + 0]) * sc.x;
-                        wstg[(4 * j4 + 1) * 32 + lane] = __uint_as_float(v[4 * j4 + 1]) * sc.y;
-                        wstg[(4 * j4 + 2) * 32 + lane] = __uint_as_float(v[4 * j4 + 2]) * sc.z;
-                        wstg[(4 * j4 + 3) * 32 + lane] = __uint_as_float(v[4 * j4 + 3]) * sc.w;
-                    }
+                        for (int j4 = 0; j4 < 8; j4++) {
+                            const float4 sc = __ldg(sc4 + j4);
+                            w32[(4 * j4 + 0) * wpitch] = __uint_as_float(v[4 * j4 + 0]) * sc.x;
+                            w32[(4 * j4 + 1) * wpitch] = __uint_as_float(v[4 * j4 + 1]) * sc.y;
+                            w32[(4 * j4 + 2) * wpitch] = __uint_as_float(v[4 * j4 + 2]) * sc.z;
+                            w32[(4 * j4 + 3) * wpitch] = __uint_as_float(v[4 * j4 + 3]) * sc.w;
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0 && c0 < a.bn) {
-                        tma_store_2d(&tmap_y, smem_u32(wstg), row0 + q * 32, tok0 + c0);
-                        // scattered product: the same block into the other GPUs' outputs, over NVLink
-                        for (int pp = 0; pp < a.n_extra; pp++) tma_store_2d(&peers.m[pp], smem_u32(wstg), row0 + q * 32, tok0 + c0);
-                        bulk_commit();
+                    if (lane == 0) {
+                        if (!coop) {
+                            if (c0 < a.bn) {
+                                tma_store_2d(&tmap_y, smem_u32(wstg), row0 + q * 32, tok0 + c0);
+                                bulk_commit();
+                            }
+                        } else {
+                            mbar_arrive(gready_b);
+                            if (leader) {
+                                ok = mbar_wait(gready_b, (uint32_t)(ep_round & 1), abort_flag, a.status, 17);
+                                if (ok && c0 < a.bn) {
+                                    tma_store_2d(&tmap_y, smem_u32(wstg), row0, tok0 + c0);
+                                    // the same tile into the other GPUs' outputs, over NVLink
+                                    for (int pp = 0; pp < a.n_extra; pp++) tma_store_2d(&peers.m[pp], smem_u32(wstg), row0, tok0 + c0);
+                                    bulk_commit();
+                                }
+                            }
+                        }
                     }
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    ep_round++;
                 }
                 if (!freed) {   // a wait gave up before the last read: the MMA thread leaves through the abort flag
                     tc_fence_before();
@@ -1674,7 +1721,9 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
     if (y_tma_ok) {
         cuuint64_t ydim[2] = {(cuuint64_t)w->n_local, (cuuint64_t)m};
         cuuint64_t ystr[1] = {(cuuint64_t)ldy * (y16 ? 2 : 4)};
-        cuuint32_t ybox[2] = {32u, 32u};   // one epilogue warp's block: 32 weight rows x 32 activation rows
+        // one epilogue warp's block (32 weight rows x 32 activation rows), or, for a scattered product, the tile of a
+        // group of four warps (128 weight rows)
+        cuuint32_t ybox[2] = {ctx->scatter_extra > 0 ? 128u : 32u, 32u};
         for (int p = -1; p < ctx->scatter_extra; p++) {   // this GPU's output, then the peers' (a scattered product)
             r = enc(p < 0 ? &ymap : &peers.m[p], y16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p < 0 ? d_y : ctx->scatter_y[p], ydim, ystr, ybox,
                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -1682,7 +1731,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (output %d) failed with code %d", who, p + 1, (int)r);
         }
     }
-    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 64;
+    constexpr size_t STAGE_EPI_BYTES = 64 * BM * sizeof(float) + 128 + 128;
     // the persistent kernel prefetches partial sums from its workspace: [slots * 256 activation rows, 128 weight rows] fp32
     CUtensorMap wsmap = map;
     auto make_wsmap = [&]() -> int {

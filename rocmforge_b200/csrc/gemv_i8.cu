@@ -47,6 +47,7 @@ constexpr int F_MX6 = fmt_of(MXFP6_E2M3, GGUF);
 constexpr int F_MX4 = fmt_of(MXFP4, GGUF);
 constexpr int F_Q40 = fmt_of(Q4_0, GGUF);
 constexpr int F_Q5K = fmt_of(Q5_K, GGUF);
+constexpr int F_Q3K = fmt_of(Q3_K, GGUF);
 
 // ---- item layouts (bytes inside one item; lane = 4 g + t; rows g and g+8 of the row tile; s = sub-block of 32
 // weights inside the item's 128). A "chunk" (g, s) is 16 bytes placed at chunk_pos(g, s) * 16 of its 512-byte area,
@@ -1208,6 +1209,10 @@ __global__ void __launch_bounds__(256) build_image_q4k_kernel(const uint8_t* __r
     if (t == 0) *reinterpret_cast<uint2*>(it + 1152 + g * 8) = make_uint2(dd[0], dd[1]);
 }
 
+// Q3K = true: a GGUF Q3_K tensor re-encoded, exactly, in Q6_K's item form. value = d (sc6 - 32) (q3 - 4) with q3 - 4 in
+// -4..3 is d * sc * (q6 - 32) with the int8 scale sc = sc6 - 32 and q6 = q3 + 28: the decode kernel then runs its Q6_K
+// code on the image (which holds 6.6 bit per weight where the file has 3.4).
+template <bool Q3K>
 __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t item = idx >> 5;
@@ -1225,13 +1230,32 @@ __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* 
             const int64_t hsi = row * nh + h;
             const int64_t blk = hsi >> 1;
             const int sec = (int)(hsi & 1);
-            const uint8_t* ql = v.p[0] + blk * 128 + sec * 64 + 32 * (t & 1);
-            const uint8_t* qh = v.p[1] + blk * 64 + sec * 32;
             uint8_t q[32];   // the lane's 32 codes: weights 32 t + e of the half
-            for (int e = 0; e < 32; e++) {
-                const uint32_t lo4 = (t < 2) ? (ql[e] & 0x0Fu) : (uint32_t)(ql[e] >> 4);
-                const uint32_t hi2 = (qh[e] >> (2 * t)) & 3u;
-                q[e] = (uint8_t)(lo4 | (hi2 << 4));
+            uint32_t sc2 = 0;  // the two int8 scales of those weights (16 each)
+            if (Q3K) {
+                // planes hmask[32], qs[64], scales[12], d: element 128 sec + 32 t + e has its low two bits at
+                // (qs[32 sec + e] >> 2 t) & 3 and its third bit at bit 4 sec + t of hmask[e]
+                const uint8_t* hm = v.p[0] + blk * 32;
+                const uint8_t* qs = v.p[1] + blk * 64 + sec * 32;
+                for (int e = 0; e < 32; e++)
+                    q[e] = (uint8_t)(((qs[e] >> (2 * t)) & 3u) + (((hm[e] >> (4 * sec + t)) & 1u) << 2) + 28u);
+                const uint8_t* sc = v.p[2] + blk * 12;
+                for (int u = 0; u < 2; u++) {
+                    const int g16 = 8 * sec + 2 * t + u;
+                    const uint32_t lo = g16 < 8 ? (sc[g16] & 15u) : (uint32_t)(sc[g16 - 8] >> 4);
+                    const uint32_t hi = (uint32_t)(sc[8 + (g16 & 3)] >> (2 * (g16 >> 2))) & 3u;
+                    sc2 |= (uint32_t)(uint8_t)(int8_t)((int)(lo | (hi << 4)) - 32) << (8 * u);
+                }
+            } else {
+                const uint8_t* ql = v.p[0] + blk * 128 + sec * 64 + 32 * (t & 1);
+                const uint8_t* qh = v.p[1] + blk * 64 + sec * 32;
+                for (int e = 0; e < 32; e++) {
+                    const uint32_t lo4 = (t < 2) ? (ql[e] & 0x0Fu) : (uint32_t)(ql[e] >> 4);
+                    const uint32_t hi2 = (qh[e] >> (2 * t)) & 3u;
+                    q[e] = (uint8_t)(lo4 | (hi2 << 4));
+                }
+                const uint8_t* sc = v.p[2] + blk * 16 + sec * 8 + 2 * t;
+                sc2 = (uint32_t)sc[0] | ((uint32_t)sc[1] << 8);
             }
             uint8_t o[16];
             for (int b = 0; b < 16; b++) o[b] = (uint8_t)((q[b] & 0x0F) | ((q[16 + b] >> 2) << 4));
@@ -1245,8 +1269,7 @@ __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* 
                 }
                 hq[2 * i + u] = word;
             }
-            const uint8_t* sc = v.p[2] + blk * 16 + sec * 8 + 2 * t;
-            hs |= ((uint32_t)sc[0] | ((uint32_t)sc[1] << 8)) << (16 * i);
+            hs |= sc2 << (16 * i);
             dd |= (uint32_t)ld16(v.p[3] + blk * 2) << (16 * i);
         }
         *reinterpret_cast<uint4*>(it + 512 * i + chunk_pos(g, t) * 16) = out;
@@ -1401,6 +1424,7 @@ int decode_kind_of(int fmt) {
     if (fmt == F_MX4) return DK_MX4;
     if (fmt == F_Q40) return DK_Q40;
     if (fmt == F_Q5K) return DK_Q5K;
+    if (fmt == F_Q3K) return DK_Q6K;   // re-encoded in Q6_K's item form when the image is built
     return DK_NONE;
 }
 
@@ -1442,7 +1466,8 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out, uint8
         return fail(B200Q_ERR_INVALID, "upload: tensor too large for one image-build launch");
     }
     if (kind == DK_Q4K) build_image_q4k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);
-    else if (kind == DK_Q6K) build_image_q6k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q6K && w->fmt == F_Q3K) build_image_q6k_kernel<true><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
+    else if (kind == DK_Q6K) build_image_q6k_kernel<false><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q80) build_image_s8_kernel<DK_Q80><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q40) build_image_q40_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items);
     else if (kind == DK_Q5K) build_image_q5k_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view.p[0], d.base, (int)w->n_local, d.nh, n_items);

@@ -122,7 +122,7 @@ __global__ void peer_wait_kernel(const int* flags, int n_ranks, int my_rank, int
         for (;;) {
             int v;
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
-            if (v == epoch) break;
+            if (v - epoch >= 0) break;   // epochs only grow: a fast peer may already have signalled a later one
             if (clock64() - t0 > budget) {
                 atomicExch(status, 300 + p);
                 break;

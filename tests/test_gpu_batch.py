@@ -59,7 +59,7 @@ def test_grouped_launch_of_mixed_products(oracle, m):
 def test_batch_of_other_formats_falls_back_to_per_product_launches(oracle):
     be = backend()
     rng = synth.rng_for(600)
-    ops = [(synth.MXFP6_E3M2, 256, 512), (synth.Q3_K, 300, 1024), (synth.Q4_K, 128, 256)]
+    ops = [(synth.MXFP6_E3M2, 256, 512), (synth.Q2_K, 300, 1024), (synth.Q4_K, 128, 256)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(2, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, 2)
@@ -76,7 +76,9 @@ def test_q4_0_q8_0_and_q5_k_gguf_ride_the_grouped_tensor_core_launch(oracle, m):
     be = backend()
     rng = synth.rng_for(601 + m)
     ops = [(synth.Q4_0, 4864, 896), (synth.Q8_0, 4864, 896), (synth.Q4_0, 300, 1024), (synth.Q4_K, 128, 256), (synth.Q4_0, 17, 128),
-           (synth.Q8_0, 301, 1152), (synth.Q8_0, 9, 128), (synth.Q5_K, 4864, 1024), (synth.Q5_K, 33, 256), (synth.Q5_K, 300, 2304)]
+           (synth.Q8_0, 301, 1152), (synth.Q8_0, 9, 128), (synth.Q5_K, 4864, 1024), (synth.Q5_K, 33, 256), (synth.Q5_K, 300, 2304),
+           # Q3_K rides the launch re-encoded in Q6_K's item form (an exact integer re-encoding made at upload)
+           (synth.Q3_K, 4864, 1024), (synth.Q3_K, 33, 256), (synth.Q3_K, 300, 2304)]
     datas = [synth.gen_packed(qt, synth.GGUF, n * k, rng) for qt, n, k in ops]
     xs = [synth.gen_activations(m, k, rng) for _, _, k in ops]
     outs, ms, nb, nl = run_batch(be, ops, datas, xs, m)
