@@ -279,8 +279,9 @@ def formats_leg(be, peaks, steps):
                      "prefill_frac_of_peak": 2.0 * 512 * n * k / (ms512 * 1e-3) / 1e12 / peaks["bf16_tflops"]})
         w.free()
     return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)",
-            "note": "MXFP6_E3M2, Q2_K and Q3_K have no tensor-core decode kernel (CUDA-core kernel at m = 1); MXFP6, Q2_K and Q3_K "
-                    "prefill on the shared-memory-operand tensor-core kernel", "rows": rows}
+            "note": "MXFP6_E3M2 and Q2_K have no tensor-core decode kernel (CUDA-core kernel at m = 1); Q3_K decodes re-encoded in "
+                    "Q6_K's item form (6.6 bit per weight streamed for 3.4 in the file); MXFP6_E3M2, Q2_K and Q3_K prefill on the "
+                    "shared-memory-operand tensor-core kernel", "rows": rows}
 
 
 def config5_leg(be, peaks, steps):
