@@ -18,8 +18,9 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("qt,m,tol", [(synth.Q4_K, 1, 1e-4), (synth.Q6_K, 3, 1e-4), (synth.MXFP4, 8, 1e-4),
-                                       (synth.Q4_K, 200, 2e-3), (synth.Q8_0, 64, 2e-3)],
-                         ids=["decode-q4k", "decode-q6k", "decode-mxfp4", "prefill-q4k-streamk", "prefill-q8_0"])
+                                       (synth.Q4_K, 200, 2e-3), (synth.Q8_0, 64, 2e-3), (synth.Q4_K, 600, 2e-3), (synth.Q6_K, 1030, 2e-3)],
+                         ids=["decode-q4k", "decode-q6k", "decode-mxfp4", "prefill-q4k-streamk", "prefill-q8_0",
+                              "prefill-q4k-three-token-tiles", "prefill-q6k-five-token-tiles"])
 def test_every_shard_lands_in_every_output(oracle, qt, m, tol):
     be = backend()
     rng = synth.rng_for(6100 + qt + m)
@@ -51,12 +52,14 @@ def _bf16_bits(a):
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
+@pytest.mark.parametrize("m", [200, 520])
 @pytest.mark.parametrize("qt", [synth.Q4_K, synth.MXFP4, synth.Q8_0, synth.MXFP6_E2M3], ids=["q4k", "mxfp4", "q8_0", "mxfp6"])
-def test_bf16_outputs_are_the_fp32_ones_rounded_once(qt):
-    """B200Q_MM_SCATTER_BF16: the same accumulators, rounded to bf16 in the epilogue, in every copy."""
+def test_bf16_outputs_are_the_fp32_ones_rounded_once(qt, m):
+    """B200Q_MM_SCATTER_BF16: the same accumulators, rounded to bf16 in the epilogue, in every copy (m = 520: three
+    token tiles, the last one ragged)."""
     be = backend()
     rng = synth.rng_for(6300 + qt)
-    n, k, m, shards, copies = 512, 1024, 200, 2, 3
+    n, k, shards, copies = 512, 1024, 2, 3
     data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
     x = synth.gen_activations(m, k, rng)
     xb = be.allocate_buffer(x.nbytes)
