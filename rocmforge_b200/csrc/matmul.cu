@@ -197,7 +197,20 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
         y32 = static_cast<float*>(ctx->scratch2);
         ldy32 = w->n_local;
     }
-    const bool tensor = m > 8 && !(flags & (B200Q_MM_SEQUENTIAL | B200Q_MM_NO_TENSOR)) && gemm_tc_supported(w, m);
+    // A few activation rows on a small tensor: the decode kernel, 8 rows at a time, beats the prefill kernels, whose
+    // launch pair, pipeline fill and partial-tile hand-over cost about 20 us whatever the size. Estimates from the
+    // measured rates: decode 5 us + image bytes at 2.5 TB/s per 8 rows; prefill 20 us + the larger of flops at
+    // 1.2 PFLOP/s and bytes at 5 TB/s.
+    bool decode_rows = false;
+    if (m > 8 && m <= 32 && x_dtype == B200Q_F32 && w->dimg.base && gemv_fast_supported(w) && gemv_i8_supported(w, 8) &&
+        (reinterpret_cast<uintptr_t>(d_x) & 15) == 0 && (ldx % 4) == 0) {
+        const double bytes = (double)w->dimg.bytes;
+        const double t_dec = ((m + 7) / 8) * (5e-6 + bytes / 2.5e12);
+        const double flops = 2.0 * m * (double)w->n_local * (double)w->k;
+        const double t_pre = 20e-6 + (flops / 1.2e15 > bytes / 5e12 ? flops / 1.2e15 : bytes / 5e12);
+        decode_rows = t_dec < t_pre;
+    }
+    const bool tensor = m > 8 && !decode_rows && !(flags & (B200Q_MM_SEQUENTIAL | B200Q_MM_NO_TENSOR)) && gemm_tc_supported(w, m);
     if (tensor) {
         // tcgen05 path: activations are copied to f16 (row-scaled) and fetched by TMA
         rc = launch_gemm_tc(ctx, w, d_x, x_dtype == B200Q_BF16, ldx, y32, ldy32, m);
