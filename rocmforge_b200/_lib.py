@@ -15,7 +15,7 @@ Q4_0, Q8_0, Q4_K, Q6_K, MXFP4, MXFP6_E2M3, MXFP6_E3M2, Q2_K, Q3_K, Q5_K = range(
 LAYOUT_RF, LAYOUT_GGUF = 0, 1
 ORIENT_NK, ORIENT_KN = 0, 1
 F32, BF16 = 0, 1
-MM_DEFAULT, MM_SEQUENTIAL, MM_NO_TENSOR, MM_SCATTER_BF16 = 0, 1, 2, 4
+MM_DEFAULT, MM_SEQUENTIAL, MM_NO_TENSOR, MM_SCATTER_BF16, MM_MX_NATIVE = 0, 1, 2, 4, 8
 
 
 class DeviceInfo(ctypes.Structure):

@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "matmul.cu", "kernels_dequant.cu", "kernels_gemv.cu", "gemv_i8.cu", "gemm_tc.cu", "gguf_file.cu", "ffn.cu"]
+SOURCES = ["api.cu", "matmul.cu", "kernels_dequant.cu", "kernels_gemv.cu", "gemv_i8.cu", "gemm_tc.cu", "gemm_mx.cu", "gguf_file.cu", "ffn.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-ccbin", "/usr/bin/g++"]

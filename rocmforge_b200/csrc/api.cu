@@ -522,6 +522,7 @@ int b200q_weight_free(b200q_weight* w) {
     b200q_ctx* ctx = w->ctx;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (w->mx_sfa) cudaFree(w->mx_sfa);
     if (w->arena) {
         w->arena->live--;   // the memory goes back with the arena
     } else {

@@ -82,6 +82,7 @@ struct b200q_weight {
     // and rounds each weight once to f16). A tensor that fails both is multiplied by the fp32 decode kernels.
     bool f16_scales_ok = true, f16_weights_ok = true;
     b200q::DImage dimg{};     // second, decode-ordered copy for m <= 8 (formats of the integer decode kernel)
+    void* mx_sfa = nullptr;   // MXFP4: block scales in the chunk order of the block-scaled MMA (built on first use, own allocation)
 };
 
 namespace b200q {
@@ -113,6 +114,9 @@ int launch_matmul_seq(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, i
 int launch_convert_bf16_to_f32(b200q_ctx* ctx, const void* d_in, int64_t ld_in, float* d_out, int64_t ld_out, int rows, int64_t cols);
 int launch_convert_f32_to_bf16(b200q_ctx* ctx, const float* d_in, int64_t ld_in, void* d_out, int64_t ld_out, int rows, int64_t cols);
 bool gemv_fast_supported(const b200q_weight* w);
+// gemm_mx.cu
+bool gemm_mx_native_supported(const b200q_weight* w, int m);
+int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m);
 // gemm_tc.cu
 bool gemm_tc_supported(const b200q_weight* w, int m);
 int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m);

@@ -210,6 +210,16 @@ int b200q_matmul_ex(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int 
         const double t_pre = 20e-6 + (flops / 1.2e15 > bytes / 5e12 ? flops / 1.2e15 : bytes / 5e12);
         decode_rows = t_dec < t_pre;
     }
+    if ((flags & B200Q_MM_MX_NATIVE) && m > 8) {
+        // opt-in: 4-bit codes and their block scales straight into the block-scaled tensor-core MMA, activations as MXFP8
+        if (flags & (B200Q_MM_SEQUENTIAL | B200Q_MM_NO_TENSOR)) return fail(B200Q_ERR_INVALID, "matmul: B200Q_MM_MX_NATIVE contradicts the other flags");
+        if (ctx->scatter_extra > 0) return fail(B200Q_ERR_UNSUPPORTED, "matmul_scatter: the native MX kernel writes one output");
+        rc = launch_gemm_mx_native(ctx, w, d_x, x_dtype == B200Q_BF16, ldx, y32, ldy32, m);
+        if (rc != B200Q_OK) return rc;
+        ctx->tc_pending = true;
+        if (y_dtype == B200Q_BF16) rc = launch_convert_f32_to_bf16(ctx, y32, ldy32, d_y, ldy, m, w->n_local);
+        return rc;
+    }
     const bool tensor = m > 8 && !decode_rows && !(flags & (B200Q_MM_SEQUENTIAL | B200Q_MM_NO_TENSOR)) && gemm_tc_supported(w, m);
     if (tensor) {
         // tcgen05 path: activations are copied to f16 (row-scaled) and fetched by TMA

@@ -1,0 +1,104 @@
+"""B200Q_MM_MX_NATIVE: GGUF MXFP4 codes and their E8M0 block scales straight into the block-scaled tensor-core MMA
+(tcgen05.mma.kind::mxf8f6f4.block_scale), activations quantised to MXFP8 on the way in.
+
+Two kinds of check against the CPU oracle. (1) Activations that MXFP8 represents exactly (integers of at most four
+significant bits times a power of two per block of 32): every product is then exact and only the fp32 summation
+order differs from the oracle's, so the tolerance is 2e-5 — this pins the operand layouts, the element order of a
+block, both scale planes and the accumulation. (2) Random activations: the result carries the rounding of E4M3's
+3-bit mantissa; tolerance 5e-2 of the largest output, stated here because it is far from the 2e-3 of the default
+path, which is why the mode is opt-in.
+"""
+import numpy as np
+import pytest
+
+from rocmforge_b200 import _lib, synth
+from rocmforge_b200._lib import B200QError
+
+from gpu_util import QuantizedWeight, backend, gpu_matmul, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def exact_activations(m, k, rng):
+    ints = rng.integers(-15, 16, size=(m, k)).astype(np.float32)
+    ints[:, ::32] = 15.0                                   # every block reaches the largest magnitude: the scale is fixed by it
+    scale = np.exp2(rng.integers(-6, 7, size=(m, k // 32))).astype(np.float32)
+    return (ints.reshape(m, k // 32, 32) * scale[:, :, None]).reshape(m, k)
+
+
+def reference(oracle, data, n, k, x):
+    w = oracle.dequantize(synth.MXFP4, synth.GGUF, data, n * k, threads=8).reshape(n, k)
+    return oracle.matmul_f64(x, w, nk=True)
+
+
+@pytest.mark.parametrize("n,k,m", [(128, 128, 16), (128, 512, 64), (300, 1024, 100), (256, 1024, 300), (1024, 2048, 512), (384, 8192, 520)],
+                         ids=["one-stage", "four-stages", "ragged", "two-token-tiles", "m512", "k8192-ragged-m"])
+def test_exactly_representable_activations_give_the_fp32_result(oracle, n, k, m):
+    be = backend()
+    rng = synth.rng_for(9100 + n + k + m)
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    assert rel_err(y, reference(oracle, data, n, k, x)) <= 2e-5
+    y2 = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)      # second call: the weight's scale plane comes from its cache
+    assert np.array_equal(y, y2)
+    w.free()
+
+
+def test_every_block_exponent_and_code(oracle):
+    """All 16 codes in every position of a block, block exponents from 2^-40 to 2^40 (the scales stay E8M0 end to end,
+    nothing passes through f16)."""
+    be = backend()
+    n, k, m = 128, 1024, 32
+    rng = synth.rng_for(9200)
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng).copy()
+    blocks = data.reshape(-1, 17)
+    blocks[:, 0] = rng.integers(87, 168, size=blocks.shape[0]).astype(np.uint8)
+    blocks[:, 1:] = rng.integers(0, 256, size=(blocks.shape[0], 16)).astype(np.uint8)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    ref = reference(oracle, data, n, k, x)
+    assert np.all(np.isfinite(y))
+    # rows differ by many orders of magnitude: compare row by row
+    err = np.abs(y - ref).max(axis=0) / np.maximum(np.abs(ref).max(axis=0), 1e-30)
+    assert float(err.max()) <= 2e-5
+    w.free()
+
+
+@pytest.mark.parametrize("m", [64, 512])
+def test_random_activations_within_the_mxfp8_tolerance(oracle, m):
+    be = backend()
+    n, k = 512, 4096
+    rng = synth.rng_for(9300 + m)
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    ref = reference(oracle, data, n, k, x)
+    e = rel_err(y, ref)
+    assert e <= 5e-2, e
+    assert e > 1e-4          # it IS the lower-precision path (the default one meets 2e-3 on the same input)
+    assert rel_err(gpu_matmul(be, w, x, m), ref) <= 2e-3
+    w.free()
+
+
+def test_other_formats_and_small_m(oracle):
+    be = backend()
+    n, k = 128, 256
+    rng = synth.rng_for(9400)
+    data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+    w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+    x = synth.gen_activations(16, k, rng)
+    with pytest.raises(B200QError) as e:
+        gpu_matmul(be, w, x, 16, flags=_lib.MM_MX_NATIVE)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    w.free()
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    x = synth.gen_activations(4, k, rng)
+    y = gpu_matmul(be, w, x, 4, flags=_lib.MM_MX_NATIVE)        # m <= 8: the flag is ignored, the decode kernel runs
+    wf = oracle.dequantize(synth.MXFP4, synth.GGUF, data, n * k).reshape(n, k)
+    assert rel_err(y, oracle.matmul_f32(x, wf, nk=True)) <= 1e-4
+    w.free()
