@@ -178,18 +178,18 @@ def step_traffic(m):
     return int(hit.group(1))
 
 
-def time_matmul(be, w, m, steps, warmup, x_dtype=0):
+def time_matmul(be, w, m, steps, warmup, x_dtype=0, flags=0):
     """Device time per launch of one fused dequant+matmul (CUDA events on the library's stream)."""
     rng = synth.rng_for(4243)
     x = synth.gen_activations(m, w.k, rng)
     xb = be.allocate_buffer(x.nbytes); xb.copy_from_host(x)
     yb = be.allocate_buffer(m * w.n_local * 4)
     for _ in range(max(warmup, 1)):
-        w.matmul(xb, yb, m)
+        w.matmul(xb, yb, m, flags=flags)
     be.synchronize()
     be.timer_start()
     for _ in range(steps):
-        w.matmul(xb, yb, m)
+        w.matmul(xb, yb, m, flags=flags)
     ms = be.timer_stop_ms() / steps
     be.synchronize()
     xb.free(); yb.free()
@@ -302,6 +302,14 @@ def config5_leg(be, peaks, steps):
             row[f"m{m}_ms"] = ms
             row[f"m{m}_tflops"] = 2.0 * m * n * k / (ms * 1e-3) / 1e12
             row[f"m{m}_frac_of_peak"] = row[f"m{m}_tflops"] / peaks["bf16_tflops"]
+        if qname == "MXFP4":
+            # opt-in: 4-bit codes and E8M0 scales straight into the block-scaled MMA, activations quantised to MXFP8 (a
+            # lower-precision mode: a few 1e-2 against 2e-3); the fraction is still taken of the measured bf16 peak
+            for m in (512, 2048):
+                ms = time_matmul(be, w, m, steps, 3, flags=_lib.MM_MX_NATIVE)
+                row[f"m{m}_native_mx_ms"] = ms
+                row[f"m{m}_native_mx_tflops"] = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+                row[f"m{m}_native_mx_vs_bf16_peak"] = row[f"m{m}_native_mx_tflops"] / peaks["bf16_tflops"]
         rows.append(row)
         w.free()
     return {"workload": "llama-70b ffn [28672, 8192], MXFP4 and MXFP6 (E2M3), single launches", "rows": rows}

@@ -75,7 +75,7 @@ typedef enum { B200Q_F32 = 0, B200Q_BF16 = 1 } b200q_dtype;
 #define B200Q_MM_DEFAULT 0u
 #define B200Q_MM_SEQUENTIAL 1u /* one thread per output, ascending k, multiply then add: bit-identical to cpu_matmul_f32 */
 #define B200Q_MM_NO_TENSOR 2u  /* never take the tcgen05 path (CUDA-core kernels only) */
-#define B200Q_MM_MX_NATIVE 8u  /* m > 8, GGUF MXFP4 NK tensors with k % 128 == 0 only (B200Q_ERR_UNSUPPORTED otherwise): the 4-bit codes
+#define B200Q_MM_MX_NATIVE 8u  /* m > 8, GGUF MXFP4 / MXFP6 NK tensors with k % 128 == 0 only (B200Q_ERR_UNSUPPORTED otherwise): the 4- or 6-bit codes
                                   * and their E8M0 block scales go to tcgen05.mma.kind::mxf8f6f4.block_scale as they are, the
                                   * activations are quantised to MXFP8 (E4M3, one E8M0 scale per 32) on the way in. About twice
                                   * the throughput of the default path; the result carries the activations' 4-bit mantissa

@@ -1,6 +1,6 @@
-// Native block-scaled prefill product for GGUF MXFP4 (opt-in, B200Q_MM_MX_NATIVE): the 4-bit E2M1 codes go to the
-// tensor cores AS THEY ARE, with their E8M0 block scales, through tcgen05.mma.kind::mxf8f6f4.block_scale; nothing
-// is dequantised. The activations are quantised to MXFP8 (E4M3 codes, one E8M0 scale per 32 values) by a small
+// Native block-scaled prefill product for GGUF MXFP4 and MXFP6 (opt-in, B200Q_MM_MX_NATIVE): the 4-bit E2M1 (6-bit
+// E2M3 / E3M2) codes go to the tensor cores AS THEY ARE, with their E8M0 block scales, through
+// tcgen05.mma.kind::mxf8f6f4.block_scale; nothing is dequantised. The activations are quantised to MXFP8 (E4M3 codes, one E8M0 scale per 32 values) by a small
 // kernel ahead of the product, so the result carries the rounding of a 4-bit mantissa per activation (relative
 // error of a few 1e-2 on random data, against 2e-3 for the default f16 path): it is a throughput mode for callers
 // that accept MX activations, never the default. Reference side: the tensors of src/loader/dequant.rs:85-132 /
@@ -11,7 +11,9 @@
 //      (CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B: 8 code bytes followed by 8 bytes of padding), the layout the MMA reads
 //      4-bit operands in. The hardware takes byte j of a block as elements (2j, 2j+1); a GGUF block keeps elements
 //      (j, j+16) there, so hardware position h of a block holds element 8 (h/16) + (h%16)/2 + 16 (h%2). The
-//      activation codes are written in the same order, so the products pair up.
+//      activation codes are written in the same order, so the products pair up. MXFP6: the code plane [n, 3k/4]
+//      bytes as 16 x U6 -> 16-byte containers (12 code bytes + 4 of padding); its 6-bit fields are already in the
+//      hardware's order (element i at bit 6 i), so the activations keep theirs.
 //   B  activations: E4M3 bytes [m, k] in that order, plain tiled TMA.
 //   Scales: one byte per row and 32 k, in tensor memory. The MMA wants them as 512-byte chunks of 128 rows x 4
 //      k-blocks, byte (row % 32) * 16 + (row / 32) * 4 + kblock; both scale planes are kept in that order in global
@@ -144,6 +146,8 @@ struct MxArgs {
     float* y;
     int64_t ldy;
     int n_rows, m, k, bn;
+    int a_format;         // operand format of the weights in the MMA: 5 = E2M1, 3 = E2M3, 4 = E3M2
+    int a_tx;             // bytes a stage's code tile counts for on its barrier: the PACKED bytes (64 or 96 per row)
     int* status;
 };
 
@@ -166,7 +170,7 @@ __global__ void __launch_bounds__(256) mx_build_sfa_kernel(const uint8_t* __rest
 // Activations -> MXFP8: one thread per (row, block of 32). E8M0 scale = the smallest power of two that brings the
 // block's largest magnitude inside E4M3's range (448), codes by round-to-nearest with saturation, written at the
 // hardware positions of the weights' code order; the scale byte goes to its place in the chunk order.
-template <typename T>
+template <typename T, bool PERM>
 __global__ void __launch_bounds__(256) mx_quantize_x_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q, uint8_t* __restrict__ sfb,
                                                             int m, int k, int m_pad) {
     const int nb = k >> 5;
@@ -202,7 +206,7 @@ __global__ void __launch_bounds__(256) mx_quantize_x_kernel(const T* __restrict_
 #pragma unroll
         for (int p = 0; p < 4; p += 2) {
             const int h = 4 * g + p;
-            const float2 pr = make_float2(v[mx_elem_of_pos(h)] * inv, v[mx_elem_of_pos(h + 1)] * inv);
+            const float2 pr = PERM ? make_float2(v[mx_elem_of_pos(h)] * inv, v[mx_elem_of_pos(h + 1)] * inv) : make_float2(v[h] * inv, v[h + 1] * inv);
             word |= (uint32_t)__nv_cvt_float2_to_fp8x2(pr, __NV_SATFINITE, __NV_E4M3) << (8 * p);
         }
         w[g] = word;
@@ -257,8 +261,8 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     if (warp == 0) {
         // ---------------------------------------------------------------- copies: codes, activation codes, scales
         if (lane == 0) {
-            // the code tile counts with its PACKED bytes (64 per row), although it fills 128 bytes per row of shared memory
-            const uint32_t stage_tx = (uint32_t)(MX_BM * MX_BK / 2 + b_stage + 512 + 512 * nsfb);
+            // the code tile counts with its PACKED bytes (64 or 96 per row), although it fills 128 bytes per row of shared memory
+            const uint32_t stage_tx = (uint32_t)(a.a_tx + b_stage + 512 + 512 * nsfb);
             const uint8_t* sfa_row = a.sfa + (int64_t)blockIdx.x * nkb * 512;
             int issued = 0;
             for (int kb = 0; kb < nkb; kb++, issued++) {
@@ -285,10 +289,10 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     } else if (warp == 1) {
         // ---------------------------------------------------------------- scales to tensor memory, then the MMAs
         if (lane == 0) {
-            // instruction descriptor (block-scaled form): A = E2M1 (5) at bits 7..9, B = E4M3 (0) at 10..12, both K-major,
+            // instruction descriptor (block-scaled form): A = E2M1 (5), E2M3 (3) or E3M2 (4) at bits 7..9, B = E4M3 (0) at 10..12, both K-major,
             // N / 8 at bits 17..22, scales E8M0 at bit 23, M / 16 at bits 24..28; the scale byte of an MMA's k-block
             // inside its 32-bit column goes to bits 4..5 (B) and 29..30 (A)
-            const uint32_t idesc0 = (5u << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | (1u << 23) | ((uint32_t)(MX_BM >> 4) << 24);
+            const uint32_t idesc0 = ((uint32_t)a.a_format << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | (1u << 23) | ((uint32_t)(MX_BM >> 4) << 24);
             const uint64_t adesc0 = mx_desc_sw128(mx_smem_u32(sA)), bdesc0 = mx_desc_sw128(mx_smem_u32(sB));
             bool ok = true;
             for (int kb = 0; kb < nkb; kb++) {
@@ -357,17 +361,18 @@ MxEncodeFn mx_encode_fn() {
 }  // namespace
 
 bool gemm_mx_native_supported(const b200q_weight* w, int m) {
-    return w->fmt == fmt_of(MXFP4, GGUF) && w->orient == B200Q_ORIENT_NK && m > 8 && (w->k % 128) == 0 && w->k < (1 << 30) &&
+    return (w->fmt == fmt_of(MXFP4, GGUF) || w->fmt == fmt_of(MXFP6_E2M3, GGUF) || w->fmt == fmt_of(MXFP6_E3M2, GGUF)) && w->orient == B200Q_ORIENT_NK && m > 8 && (w->k % 128) == 0 && w->k < (1 << 30) &&
            w->n_local < 0x7FFFFF00ll;
 }
 
 // x: fp32 or bf16 [m, ldx] on the device; y: fp32 [m, ldy]. Uses the context's third scratch buffer for the activation
 // codes and their scales; the weights' scale plane in chunk order is built on first use and kept with the tensor.
 int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x_is_bf16, int64_t ldx, float* d_y, int64_t ldy, int m) {
-    if (!gemm_mx_native_supported(w, m)) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): needs a GGUF MXFP4 NK tensor with k %% 128 == 0 and m > 8");
+    if (!gemm_mx_native_supported(w, m)) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): needs a GGUF MXFP4 or MXFP6 NK tensor with k %% 128 == 0 and m > 8");
     MxEncodeFn enc = mx_encode_fn();
     if (!enc) return fail(B200Q_ERR_INIT, "matmul (native MX): cuTensorMapEncodeTiled is not available from this driver");
     const int k = (int)w->k, nkb = k / MX_BK;
+    const bool fp4 = w->fmt == fmt_of(MXFP4, GGUF);
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int m_tiles = (m + bn - 1) / bn;
     const int m_pad = ((m_tiles * bn + 127) / 128) * 128;   // whole chunks of 128 rows of scales; rows the copies may touch exist
@@ -394,18 +399,23 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     {
         const int64_t threads = (int64_t)m_pad * (k / 32);
         const unsigned grid = (unsigned)((threads + 255) / 256);
-        if (x_is_bf16) mx_quantize_x_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
-        else mx_quantize_x_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
+        if (fp4) {
+            if (x_is_bf16) mx_quantize_x_kernel<__nv_bfloat16, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
+            else mx_quantize_x_kernel<float, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
+        } else {
+            if (x_is_bf16) mx_quantize_x_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
+            else mx_quantize_x_kernel<float, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(d_x), ldx, d_q, d_sfb, m, k, m_pad);
+        }
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     }
     CUtensorMap wmap, xmap;
     cuuint32_t estr[2] = {1, 1};
     {
-        // code plane as [n, k] 4-bit elements: 16 x U4 per 8 bytes, unpacked to 16-byte containers in shared memory
+        // code plane as [n, k] 4-bit (6-bit) elements: 16 per 8 (12) bytes, unpacked to 16-byte containers in shared memory
         cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)w->n_local};
-        cuuint64_t gstr[1] = {(cuuint64_t)k / 2};
+        cuuint64_t gstr[1] = {fp4 ? (cuuint64_t)k / 2 : (cuuint64_t)k / 4 * 3};
         cuuint32_t box[2] = {128u, (cuuint32_t)MX_BM};
-        CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<uint8_t*>(w->view.p[1]), gdim, gstr, box, estr,
+        CUresult r = enc(&wmap, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, 2, const_cast<uint8_t*>(w->view.p[1]), gdim, gstr, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (codes) failed with code %d", (int)r);
         cuuint64_t xdim[2] = {(cuuint64_t)k, (cuuint64_t)m_pad};
@@ -420,6 +430,8 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     a.sfb = d_sfb;
     a.y = d_y; a.ldy = ldy;
     a.n_rows = (int)w->n_local; a.m = m; a.k = k; a.bn = bn;
+    a.a_format = fp4 ? 5 : w->fmt == fmt_of(MXFP6_E2M3, GGUF) ? 3 : 4;
+    a.a_tx = MX_BM * (fp4 ? 64 : 96);
     a.status = ctx->d_status;
     const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (2 * MX_STAGES + 1) * 8 + 16;
     static std::atomic<bool> configured[64] = {};

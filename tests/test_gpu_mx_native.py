@@ -26,9 +26,27 @@ def exact_activations(m, k, rng):
     return (ints.reshape(m, k // 32, 32) * scale[:, :, None]).reshape(m, k)
 
 
-def reference(oracle, data, n, k, x):
-    w = oracle.dequantize(synth.MXFP4, synth.GGUF, data, n * k, threads=8).reshape(n, k)
+def reference(oracle, data, n, k, x, qt=synth.MXFP4):
+    w = oracle.dequantize(qt, synth.GGUF, data, n * k, threads=8).reshape(n, k)
     return oracle.matmul_f64(x, w, nk=True)
+
+
+@pytest.mark.parametrize("qt", [synth.MXFP6_E2M3, synth.MXFP6_E3M2], ids=["e2m3", "e3m2"])
+@pytest.mark.parametrize("n,k,m", [(128, 128, 16), (300, 1024, 100), (256, 2048, 300), (512, 8192, 520)],
+                         ids=["one-stage", "ragged", "two-token-tiles", "k8192-ragged-m"])
+def test_mxfp6_codes_go_in_as_they_are(oracle, qt, n, k, m):
+    """The 6-bit code plane by TMA as 16 x U6 -> 16-byte containers; E3M2 has no other tensor-core path that keeps
+    its codes exact (its values are not 8-bit integers times a power of two)."""
+    be = backend()
+    rng = synth.rng_for(9150 + qt + n + k + m)
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+    blocks = data.reshape(-1, 25)
+    blocks[:, 1:] = rng.integers(0, 256, size=(blocks.shape[0], 24)).astype(np.uint8)     # every code in every position
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    assert rel_err(y, reference(oracle, data, n, k, x, qt)) <= 2e-5
+    w.free()
 
 
 @pytest.mark.parametrize("n,k,m", [(128, 128, 16), (128, 512, 64), (300, 1024, 100), (256, 1024, 300), (1024, 2048, 512), (384, 8192, 520)],
