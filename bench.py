@@ -291,7 +291,7 @@ def config5_leg(be, peaks, steps):
     from rocmforge_b200.backend import QuantizedWeight
     n, k = synth.LLAMA70B_FFN_SHAPES[0]
     rows = []
-    for qname in ("MXFP4", "MXFP6_E2M3"):
+    for qname in ("MXFP4", "MXFP6_E2M3", "MXFP6_E3M2"):
         qt = synth.QNAMES.index(qname)
         w = QuantizedWeight(be, synth.gen_packed(qt, synth.GGUF, n * k, synth.rng_for(synth.CONFIG_SEEDS[5] + qt)), qt, synth.GGUF, n, k)
         ms1 = time_matmul(be, w, 1, steps * 2, 3)
@@ -302,9 +302,9 @@ def config5_leg(be, peaks, steps):
             row[f"m{m}_ms"] = ms
             row[f"m{m}_tflops"] = 2.0 * m * n * k / (ms * 1e-3) / 1e12
             row[f"m{m}_frac_of_peak"] = row[f"m{m}_tflops"] / peaks["bf16_tflops"]
-        if qname == "MXFP4":
-            # opt-in: 4-bit codes and E8M0 scales straight into the block-scaled MMA, activations quantised to MXFP8 (a
-            # lower-precision mode: a few 1e-2 against 2e-3); the fraction is still taken of the measured bf16 peak
+        if True:
+            # opt-in: the 4- or 6-bit codes and E8M0 scales straight into the block-scaled MMA, activations quantised to
+            # MXFP8 (a lower-precision mode: a few 1e-2 against 2e-3); the fraction is still taken of the measured bf16 peak
             for m in (512, 2048):
                 ms = time_matmul(be, w, m, steps, 3, flags=_lib.MM_MX_NATIVE)
                 row[f"m{m}_native_mx_ms"] = ms
@@ -312,7 +312,8 @@ def config5_leg(be, peaks, steps):
                 row[f"m{m}_native_mx_vs_bf16_peak"] = row[f"m{m}_native_mx_tflops"] / peaks["bf16_tflops"]
         rows.append(row)
         w.free()
-    return {"workload": "llama-70b ffn [28672, 8192], MXFP4 and MXFP6 (E2M3), single launches", "rows": rows}
+    return {"workload": "llama-70b ffn [28672, 8192], MXFP4 and MXFP6 (E2M3, E3M2), single launches; native_mx = B200Q_MM_MX_NATIVE "
+                        "(tcgen05.mma.kind::mxf8f6f4.block_scale on the packed codes, MXFP8 activations)", "rows": rows}
 
 
 def config2_leg(be, steps):

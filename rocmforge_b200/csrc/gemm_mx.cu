@@ -181,11 +181,19 @@ __global__ void __launch_bounds__(256) mx_quantize_x_kernel(const T* __restrict_
     float amax = 0.f;
     if (tok < m) {
         const T* xp = x + (int64_t)tok * ldx + (int64_t)blk * 32;
+        if (sizeof(T) == 4 && (ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            const float4* x4 = reinterpret_cast<const float4*>(xp);
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-            v[j] = (float)xp[j];
-            amax = fmaxf(amax, fabsf(v[j]));
+            for (int j = 0; j < 8; j++) {
+                const float4 t = __ldg(x4 + j);
+                v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = (float)xp[j];
         }
+#pragma unroll
+        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(v[j]));
     } else {
 #pragma unroll
         for (int j = 0; j < 32; j++) v[j] = 0.f;
