@@ -20,13 +20,15 @@
 //      memory (the weights' plane is built once per tensor from its exponent plane, the activations' by the
 //      quantising kernel), a stage fetches its chunks with untiled bulk copies and the MMA thread moves them to
 //      tensor memory with tcgen05.cp (32 x 128 bit, replicated to the four lane quarters).
-// One CTA per 128 x BN output tile (whole tiles, no partial sums): warp 0 issues the copies, warp 1 the tensor-memory
-// copies and MMAs, warps 2..5 read the accumulator and store fp32. Every wait is bounded.
+// Persistent CTAs, one per SM, over whole 128 x BN output tiles (no partial sums): warp 0 issues the copies and runs
+// ahead across tile boundaries, warp 1 the tensor-memory copies and MMAs, warps 2..5 read the accumulator and store
+// fp32 while the ring refills for the next tile. Every wait is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 
 #include "common.cuh"
@@ -148,6 +150,7 @@ struct MxArgs {
     int n_rows, m, k, bn;
     int a_format;         // operand format of the weights in the MMA: 5 = E2M1, 3 = E2M3, 4 = E3M2
     int a_tx;             // bytes a stage's code tile counts for on its barrier: the PACKED bytes (64 or 96 per row)
+    int m_tiles, row_tiles;
     int* status;
 };
 
@@ -241,19 +244,23 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSFB + MX_STAGES * 1024);
     uint64_t* full = bars;
     uint64_t* empty = bars + MX_STAGES;
-    uint64_t* accum = empty + MX_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    uint64_t* accum = empty + MX_STAGES;     // the MMAs of a tile are complete -> epilogue
+    uint64_t* afree = accum + 1;             // the four epilogue warps have read the accumulator -> next tile's MMAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(afree + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row0 = blockIdx.x * MX_BM, tok0 = blockIdx.y * a.bn;
     const int nkb = a.k / MX_BK;
+    // Persistent: CTA c takes tiles c, c + grid, ...; token tiles vary fastest, so the CTAs that run together share
+    // the weight tiles (read from HBM once) and the activation tiles of all token tiles stay in L2.
+    const int total_tiles = a.m_tiles * a.row_tiles;
     if (tid == 0) {
         for (int s = 0; s < MX_STAGES; s++) {
             mx_bar_init(mx_smem_u32(&full[s]), 1);
             mx_bar_init(mx_smem_u32(&empty[s]), 1);
         }
         mx_bar_init(mx_smem_u32(accum), 1);
+        mx_bar_init(mx_smem_u32(afree), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -268,24 +275,30 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
     if (warp == 0) {
         // ---------------------------------------------------------------- copies: codes, activation codes, scales
+        // (runs ahead of the MMAs by the depth of the ring, across tile boundaries: the ring is full again when the
+        // accumulator of the previous tile has been read out)
         if (lane == 0) {
             // the code tile counts with its PACKED bytes (64 or 96 per row), although it fills 128 bytes per row of shared memory
             const uint32_t stage_tx = (uint32_t)(a.a_tx + b_stage + 512 + 512 * nsfb);
-            const uint8_t* sfa_row = a.sfa + (int64_t)blockIdx.x * nkb * 512;
-            int issued = 0;
-            for (int kb = 0; kb < nkb; kb++, issued++) {
-                const int s = kb & (MX_STAGES - 1);
-                const uint32_t ph = (uint32_t)(kb / MX_STAGES) & 1;
-                if (!mx_bar_wait(mx_smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 21)) break;
-                const uint32_t fb = mx_smem_u32(&full[s]);
-                mx_bar_expect_tx(fb, stage_tx);
-                mx_tma_2d(mx_smem_u32(sA + s * MX_BM * MX_BK), &tmap_w, kb * MX_BK, row0, fb);
-                mx_tma_2d(mx_smem_u32(sB + s * b_stage), &tmap_x, kb * MX_BK, tok0, fb);
-                mx_bulk(mx_smem_u32(sSFA + s * 512), sfa_row + (int64_t)kb * 512, 512u, fb);
-                for (int c = 0; c < nsfb; c++)
-                    mx_bulk(mx_smem_u32(sSFB + s * 1024 + c * 512), a.sfb + ((int64_t)((tok0 >> 7) + c) * nkb + kb) * 512, 512u, fb);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int row_tile = tile / a.m_tiles, row0 = row_tile * MX_BM, tok0 = (tile - row_tile * a.m_tiles) * a.bn;
+                const uint8_t* sfa_row = a.sfa + (int64_t)row_tile * nkb * 512;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it & (MX_STAGES - 1);
+                    const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
+                    if (!mx_bar_wait(mx_smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 21)) { ok = false; break; }
+                    const uint32_t fb = mx_smem_u32(&full[s]);
+                    mx_bar_expect_tx(fb, stage_tx);
+                    mx_tma_2d(mx_smem_u32(sA + s * MX_BM * MX_BK), &tmap_w, kb * MX_BK, row0, fb);
+                    mx_tma_2d(mx_smem_u32(sB + s * b_stage), &tmap_x, kb * MX_BK, tok0, fb);
+                    mx_bulk(mx_smem_u32(sSFA + s * 512), sfa_row + (int64_t)kb * 512, 512u, fb);
+                    for (int c = 0; c < nsfb; c++)
+                        mx_bulk(mx_smem_u32(sSFB + s * 1024 + c * 512), a.sfb + ((int64_t)((tok0 >> 7) + c) * nkb + kb) * 512, 512u, fb);
+                }
             }
-            for (int j = max(0, issued - MX_STAGES); j < issued; j++) {   // nothing stays in flight behind this thread
+            for (int j = max(0, it - MX_STAGES); j < it; j++) {   // nothing stays in flight behind this thread
                 const int s = j & (MX_STAGES - 1);
                 const uint32_t ph = (uint32_t)(j / MX_STAGES) & 1;
                 const long long t0 = clock64();
@@ -303,37 +316,52 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             const uint32_t idesc0 = ((uint32_t)a.a_format << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | (1u << 23) | ((uint32_t)(MX_BM >> 4) << 24);
             const uint64_t adesc0 = mx_desc_sw128(mx_smem_u32(sA)), bdesc0 = mx_desc_sw128(mx_smem_u32(sB));
             bool ok = true;
-            for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb & (MX_STAGES - 1);
-                const uint32_t ph = (uint32_t)(kb / MX_STAGES) & 1;
-                if (!mx_bar_wait(mx_smem_u32(&full[s]), ph, abort_flag, a.status, 23)) { ok = false; break; }
+            int it = 0, n = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, n++) {
+                // the previous tile's accumulator must have been read out
+                if (!mx_bar_wait(mx_smem_u32(afree), (uint32_t)(n & 1) ^ 1, abort_flag, a.status, 25)) break;
                 mx_fence_after();
-                const uint32_t sfa_col = tmem_base + MX_SFA_COL + 4 * s, sfb_col = tmem_base + MX_SFB_COL + 8 * s;
-                mx_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
-                for (int c = 0; c < nsfb; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
-                const uint64_t ad = adesc0 + (uint64_t)((s * MX_BM * MX_BK) >> 4), bd = bdesc0 + (uint64_t)((s * b_stage) >> 4);
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it & (MX_STAGES - 1);
+                    const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
+                    if (!mx_bar_wait(mx_smem_u32(&full[s]), ph, abort_flag, a.status, 23)) { ok = false; break; }
+                    mx_fence_after();
+                    const uint32_t sfa_col = tmem_base + MX_SFA_COL + 4 * s, sfb_col = tmem_base + MX_SFB_COL + 8 * s;
+                    mx_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
+                    for (int c = 0; c < nsfb; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
+                    const uint64_t ad = adesc0 + (uint64_t)((s * MX_BM * MX_BK) >> 4), bd = bdesc0 + (uint64_t)((s * b_stage) >> 4);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    // 32 k further: 32 bytes inside the swizzle row (+2 in the encoded address), next scale byte
-                    const uint32_t idesc = idesc0 | ((uint32_t)j << 4) | ((uint32_t)j << 29);
-                    mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col);
+                    for (int j = 0; j < 4; j++) {
+                        // 32 k further: 32 bytes inside the swizzle row (+2 in the encoded address), next scale byte
+                        const uint32_t idesc = idesc0 | ((uint32_t)j << 4) | ((uint32_t)j << 29);
+                        mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col);
+                    }
+                    mx_commit(mx_smem_u32(&empty[s]));
                 }
-                mx_commit(mx_smem_u32(&empty[s]));
+                if (ok) mx_commit(mx_smem_u32(accum));
             }
-            if (ok) mx_commit(mx_smem_u32(accum));
         }
     } else {
         // ---------------------------------------------------------------- epilogue: lane quarter warp % 4
         const int q = warp & 3;
         bool ok = true;
-        if (lane == 0) ok = mx_bar_wait(mx_smem_u32(accum), 0, abort_flag, a.status, 24);
-        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-        if (ok) {
+        int n = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, n++) {
+            const int row_tile = tile / a.m_tiles, row0 = row_tile * MX_BM, tok0 = (tile - row_tile * a.m_tiles) * a.bn;
+            if (lane == 0) ok = mx_bar_wait(mx_smem_u32(accum), (uint32_t)(n & 1), abort_flag, a.status, 24);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
             mx_fence_after();
             const int row = row0 + q * 32 + lane;
             for (int c0 = 0; c0 < a.bn; c0 += 32) {
                 uint32_t v[32];
                 mx_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (c0 + 32 >= a.bn) {
+                    // the last read of this warp: the accumulator may be overwritten once all four warps are here
+                    mx_fence_before();
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mx_smem_u32(afree)) : "memory");
+                }
                 if (row < a.n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -440,14 +468,17 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     a.n_rows = (int)w->n_local; a.m = m; a.k = k; a.bn = bn;
     a.a_format = fp4 ? 5 : w->fmt == fmt_of(MXFP6_E2M3, GGUF) ? 3 : 4;
     a.a_tx = MX_BM * (fp4 ? 64 : 96);
+    a.m_tiles = m_tiles; a.row_tiles = (int)row_tiles;
     a.status = ctx->d_status;
-    const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (2 * MX_STAGES + 1) * 8 + 16;
+    const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (2 * MX_STAGES + 2) * 8 + 16;
     static std::atomic<bool> configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200Q_CUDA(cudaFuncSetAttribute(gemm_mxf4_native_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
         configured[ctx->device & 63] = true;
     }
-    dim3 grid((unsigned)row_tiles, (unsigned)m_tiles);
+    const int64_t total_tiles = row_tiles * m_tiles;
+    if (total_tiles > 0x7FFFFFF0ll) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): too many tiles for one launch");
+    dim3 grid((unsigned)std::min<int64_t>(total_tiles, ctx->info.sm_count));
     gemm_mxf4_native_kernel<<<grid, MX_THREADS, smem, ctx->stream>>>(wmap, xmap, a);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
