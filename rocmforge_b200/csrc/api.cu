@@ -113,6 +113,20 @@ int b200q_init_on_stream(int device, void* cuda_stream, b200q_ctx** out) {
     e = cudaMalloc(&ctx->d_status, sizeof(int) * 8);
     if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaMalloc(status)"); }
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int) * 8, ctx->stream);
+    {
+        void* hd = nullptr;
+        if (cudaHostAlloc(&hd, sizeof(int) * 4, cudaHostAllocMapped) == cudaSuccess) {
+            void* dd = nullptr;
+            if (cudaHostGetDevicePointer(&dd, hd, 0) == cudaSuccess) {
+                memset(hd, 0, sizeof(int) * 4);
+                ctx->h_done = static_cast<volatile int*>(hd);
+                ctx->d_done = static_cast<int*>(dd);
+            } else {
+                cudaFreeHost(hd);
+            }
+        }
+        cudaGetLastError();   // without the word the host-buffer path synchronises the stream as before
+    }
     e = cudaHostAlloc(reinterpret_cast<void**>(&ctx->h_status), sizeof(int) * 4, cudaHostAllocDefault);
     if (e != cudaSuccess) { b200q_destroy(ctx); return cuda_fail(B200Q_ERR_ALLOC, e, "cudaHostAlloc(status)"); }
     *out = ctx;
@@ -131,6 +145,7 @@ void b200q_destroy(b200q_ctx* ctx) {
     if (ctx->sk_ws) cudaFree(ctx->sk_ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->h_done) cudaFreeHost(const_cast<int*>(ctx->h_done));
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);

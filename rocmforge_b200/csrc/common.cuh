@@ -21,6 +21,11 @@ struct b200q_ctx {
     size_t scratch2_bytes = 0;
     int* d_status = nullptr;  // device words: [0] bounded-wait failures, [1] bad token ids, [2..4] counters of the decode kernel
     int* h_status = nullptr;  // page-locked landing place of [0..1] when a synchronise reads them
+    // Completion word of launches whose results go straight to host memory: [0] the sequence number the kernel's
+    // last CTA stores when every CTA's results are out, [1] the launch's status word (page-locked, device-mapped)
+    volatile int* h_done = nullptr;
+    int* d_done = nullptr;    // the same words as the device sees them
+    int done_seq = 0;
     bool tc_pending = false;  // a tensor-core launch has not had its status word read yet
     void* scratch3 = nullptr; // f16 copy of the activations + row scales for the tensor-core path
     size_t scratch3_bytes = 0;

@@ -1152,6 +1152,7 @@ gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* _
             __threadfence_system();
             if (atomicAdd(&sched[2], 1) == (int)gridDim.x - 1) {
                 sched[2] = 0;
+                if (sig.status_out) *reinterpret_cast<volatile int*>(sig.status_out) = *reinterpret_cast<volatile int*>(status);
                 __threadfence_system();
                 for (int p = 0; p < sig.n; p++)
                     if (p != sig.my) asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(sig.flag[p] + sig.my), "r"(sig.epoch) : "memory");

@@ -41,6 +41,7 @@ struct DOp {
 struct PeerSignal {
     int* flag[8];
     int n, my, epoch;
+    int* status_out;   // when set: the launch's status word is copied there ahead of the flags (a host-visible word)
 };
 
 struct DecodeLaunch {
