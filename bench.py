@@ -203,9 +203,9 @@ def run_matrix(args, be, peaks):
     rng = synth.rng_for(4242)
     data = synth.gen_packed(qt, synth.GGUF, args.n * args.k, rng)
     w = QuantizedWeight(be, data, qt, synth.GGUF, args.n, args.k)
-    ms = time_matmul(be, w, args.m, args.steps, args.warmup)
+    ms = time_matmul(be, w, args.m, args.steps, args.warmup, flags=_lib.MM_MX_NATIVE if args.native_mx else 0)
     gbs = w.packed_bytes / (ms * 1e-3) / 1e9
-    print(json.dumps({"workload": "matrix", "qtype": args.qtype, "n": args.n, "k": args.k, "m": args.m,
+    print(json.dumps({"workload": "matrix", "qtype": args.qtype, "n": args.n, "k": args.k, "m": args.m, "native_mx": bool(args.native_mx),
                       "packed_bytes": w.packed_bytes, "ms_per_launch": ms, "GB/s": gbs, "frac_of_hbm": gbs / peaks["hbm_gbs"],
                       "tflops": 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12}))
 
@@ -475,6 +475,7 @@ def main():
     ap.add_argument("--workload", default="step", choices=["step", "matrix"],
                     help="step: the decode step (headline); matrix: one [--n, --k] tensor of --qtype (profiling aid)")
     ap.add_argument("--qtype", default="Q4_K")
+    ap.add_argument("--native-mx", action="store_true", help="matrix workload: B200Q_MM_MX_NATIVE (MXFP4 / MXFP6, m > 8)")
     ap.add_argument("--n", type=int, default=65536)
     ap.add_argument("--k", type=int, default=4096)
     args = ap.parse_args()
