@@ -120,3 +120,39 @@ def test_other_formats_and_small_m(oracle):
     wf = oracle.dequantize(synth.MXFP4, synth.GGUF, data, n * k).reshape(n, k)
     assert rel_err(y, oracle.matmul_f32(x, wf, nk=True)) <= 1e-4
     w.free()
+
+
+def test_bf16_activations_a_row_pitch_and_bf16_outputs(oracle):
+    """The exactly representable activations are bf16 values too, so the bf16 entry gives the same fp32 result; a
+    row pitch larger than k and a bf16 output go through the same kernel."""
+    import torch
+    be = backend()
+    n, k, m, ldx = 256, 1024, 72, 1024 + 64
+    rng = synth.rng_for(9500)
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    ref = reference(oracle, data, n, k, x)
+    xp = np.zeros((m, ldx), dtype=np.float32)
+    xp[:, :k] = x
+    xp[:, k:] = 1e30                                            # never read
+    xb = be.allocate_buffer(xp.nbytes); xb.copy_from_host(xp)
+    yb = be.allocate_buffer(m * n * 4)
+    w.matmul(xb, yb, m, flags=_lib.MM_MX_NATIVE, ldx=ldx)
+    be.synchronize()
+    assert rel_err(yb.to_numpy(np.float32, m * n).reshape(m, n), ref) <= 2e-5
+    x16 = torch.from_numpy(x).to(torch.bfloat16)
+    assert np.array_equal(x16.float().numpy(), x)               # nothing is lost on the way in
+    xb16 = be.allocate_buffer(m * k * 2); xb16.copy_from_host(x16.view(torch.int16).numpy())
+    w.matmul(xb16, yb, m, x_dtype=_lib.BF16, flags=_lib.MM_MX_NATIVE)
+    be.synchronize()
+    y = yb.to_numpy(np.float32, m * n).reshape(m, n)
+    assert rel_err(y, ref) <= 2e-5
+    y16 = be.allocate_buffer(m * n * 2)
+    w.matmul(xb16, y16, m, x_dtype=_lib.BF16, y_dtype=_lib.BF16, flags=_lib.MM_MX_NATIVE)
+    be.synchronize()
+    got = torch.from_numpy(y16.to_numpy(np.int16, m * n)).view(torch.bfloat16).float().numpy().reshape(m, n)
+    assert np.array_equal(got, torch.from_numpy(y).to(torch.bfloat16).float().numpy())
+    for b in (xb, xb16, yb, y16):
+        b.free()
+    w.free()
