@@ -151,6 +151,9 @@ struct MxArgs {
     int a_format;         // operand format of the weights in the MMA: 5 = E2M1, 3 = E2M3, 4 = E3M2
     int a_tx;             // bytes a stage's code tile counts for on its barrier: the PACKED bytes (64 or 96 per row)
     int m_tiles, row_tiles;
+    // The tiles of the last, partly filled wave are cut along the activation rows into `split` (1 or 2) pieces of
+    // `sub_bn` rows each (work items >= full_tiles), so that the wave costs half a tile time instead of a whole one.
+    int full_tiles, split, sub_bn, n_work;
     int* status;
 };
 
@@ -231,8 +234,27 @@ __global__ void __launch_bounds__(256) mx_quantize_x_kernel(const T* __restrict_
     sfb[chunk * 512 + (r & 31) * 16 + (r >> 5) * 4 + (blk & 3)] = (uint8_t)e;
 }
 
+struct MxWork {
+    int row0, tok0, nb, row_tile;
+};
+__device__ __forceinline__ MxWork mx_work(const MxArgs& a, int w) {
+    MxWork r;
+    int tile = w, sub = 0;
+    r.nb = a.bn;
+    if (w >= a.full_tiles) {
+        tile = a.full_tiles + (w - a.full_tiles) / a.split;
+        sub = (w - a.full_tiles) % a.split;
+        r.nb = a.sub_bn;
+    }
+    r.row_tile = tile / a.m_tiles;
+    r.row0 = r.row_tile * MX_BM;
+    r.tok0 = (tile - r.row_tile * a.m_tiles) * a.bn + sub * a.sub_bn;
+    return r;
+}
+
 __global__ void __launch_bounds__(MX_THREADS, 1)
-gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, MxArgs a) {
+gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_xs, MxArgs a) {
     extern __shared__ uint8_t mx_smem_raw[];
     uint8_t* smem = mx_smem_raw + ((1024u - (mx_smem_u32(mx_smem_raw) & 1023u)) & 1023u);
     const int b_stage = a.bn * MX_BK;                 // bytes
@@ -253,7 +275,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int nkb = a.k / MX_BK;
     // Persistent: CTA c takes tiles c, c + grid, ...; token tiles vary fastest, so the CTAs that run together share
     // the weight tiles (read from HBM once) and the activation tiles of all token tiles stay in L2.
-    const int total_tiles = a.m_tiles * a.row_tiles;
+    const int total_tiles = a.n_work;
     if (tid == 0) {
         for (int s = 0; s < MX_STAGES; s++) {
             mx_bar_init(mx_smem_u32(&full[s]), 1);
@@ -279,12 +301,15 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         // accumulator of the previous tile has been read out)
         if (lane == 0) {
             // the code tile counts with its PACKED bytes (64 or 96 per row), although it fills 128 bytes per row of shared memory
-            const uint32_t stage_tx = (uint32_t)(a.a_tx + b_stage + 512 + 512 * nsfb);
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int row_tile = tile / a.m_tiles, row0 = row_tile * MX_BM, tok0 = (tile - row_tile * a.m_tiles) * a.bn;
-                const uint8_t* sfa_row = a.sfa + (int64_t)row_tile * nkb * 512;
+                const MxWork wk = mx_work(a, tile);
+                const int row0 = wk.row0, tok0 = wk.tok0;
+                const bool piece = wk.nb != a.bn;            // a piece of a tile of the last wave: its own, smaller copy box
+                const int nsf = piece ? 1 : nsfb;            // pieces are at most 128 rows inside one chunk of scales
+                const uint32_t stage_tx = (uint32_t)(a.a_tx + wk.nb * MX_BK + 512 + 512 * nsf);
+                const uint8_t* sfa_row = a.sfa + (int64_t)wk.row_tile * nkb * 512;
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it & (MX_STAGES - 1);
                     const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
@@ -292,9 +317,9 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     const uint32_t fb = mx_smem_u32(&full[s]);
                     mx_bar_expect_tx(fb, stage_tx);
                     mx_tma_2d(mx_smem_u32(sA + s * MX_BM * MX_BK), &tmap_w, kb * MX_BK, row0, fb);
-                    mx_tma_2d(mx_smem_u32(sB + s * b_stage), &tmap_x, kb * MX_BK, tok0, fb);
+                    mx_tma_2d(mx_smem_u32(sB + s * b_stage), piece ? &tmap_xs : &tmap_x, kb * MX_BK, tok0, fb);
                     mx_bulk(mx_smem_u32(sSFA + s * 512), sfa_row + (int64_t)kb * 512, 512u, fb);
-                    for (int c = 0; c < nsfb; c++)
+                    for (int c = 0; c < nsf; c++)
                         mx_bulk(mx_smem_u32(sSFB + s * 1024 + c * 512), a.sfb + ((int64_t)((tok0 >> 7) + c) * nkb + kb) * 512, 512u, fb);
                 }
             }
@@ -313,7 +338,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             // instruction descriptor (block-scaled form): A = E2M1 (5), E2M3 (3) or E3M2 (4) at bits 7..9, B = E4M3 (0) at 10..12, both K-major,
             // N / 8 at bits 17..22, scales E8M0 at bit 23, M / 16 at bits 24..28; the scale byte of an MMA's k-block
             // inside its 32-bit column goes to bits 4..5 (B) and 29..30 (A)
-            const uint32_t idesc0 = ((uint32_t)a.a_format << 7) | (0u << 10) | ((uint32_t)(a.bn >> 3) << 17) | (1u << 23) | ((uint32_t)(MX_BM >> 4) << 24);
+            const uint32_t idesc_base = ((uint32_t)a.a_format << 7) | (0u << 10) | (1u << 23) | ((uint32_t)(MX_BM >> 4) << 24);
             const uint64_t adesc0 = mx_desc_sw128(mx_smem_u32(sA)), bdesc0 = mx_desc_sw128(mx_smem_u32(sB));
             bool ok = true;
             int it = 0, n = 0;
@@ -321,6 +346,11 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 // the previous tile's accumulator must have been read out
                 if (!mx_bar_wait(mx_smem_u32(afree), (uint32_t)(n & 1) ^ 1, abort_flag, a.status, 25)) break;
                 mx_fence_after();
+                const MxWork wk = mx_work(a, tile);
+                const bool piece = wk.nb != a.bn;
+                const int nsf = piece ? 1 : nsfb;
+                const uint32_t idesc0 = idesc_base | ((uint32_t)(wk.nb >> 3) << 17);
+                const uint32_t sfb_off = 0u;   // pieces start on a chunk of activation scales (see the host side)
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it & (MX_STAGES - 1);
                     const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
@@ -328,13 +358,13 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     mx_fence_after();
                     const uint32_t sfa_col = tmem_base + MX_SFA_COL + 4 * s, sfb_col = tmem_base + MX_SFB_COL + 8 * s;
                     mx_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
-                    for (int c = 0; c < nsfb; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
+                    for (int c = 0; c < nsf; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
                     const uint64_t ad = adesc0 + (uint64_t)((s * MX_BM * MX_BK) >> 4), bd = bdesc0 + (uint64_t)((s * b_stage) >> 4);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         // 32 k further: 32 bytes inside the swizzle row (+2 in the encoded address), next scale byte
                         const uint32_t idesc = idesc0 | ((uint32_t)j << 4) | ((uint32_t)j << 29);
-                        mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col);
+                        mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col + sfb_off);
                     }
                     mx_commit(mx_smem_u32(&empty[s]));
                 }
@@ -347,16 +377,17 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         bool ok = true;
         int n = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, n++) {
-            const int row_tile = tile / a.m_tiles, row0 = row_tile * MX_BM, tok0 = (tile - row_tile * a.m_tiles) * a.bn;
+            const MxWork wk = mx_work(a, tile);
+            const int row0 = wk.row0, tok0 = wk.tok0, nb = wk.nb;
             if (lane == 0) ok = mx_bar_wait(mx_smem_u32(accum), (uint32_t)(n & 1), abort_flag, a.status, 24);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             mx_fence_after();
             const int row = row0 + q * 32 + lane;
-            for (int c0 = 0; c0 < a.bn; c0 += 32) {
+            for (int c0 = 0; c0 < nb; c0 += 32) {
                 uint32_t v[32];
                 mx_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-                if (c0 + 32 >= a.bn) {
+                if (c0 + 32 >= nb) {
                     // the last read of this warp: the accumulator may be overwritten once all four warps are here
                     mx_fence_before();
                     __syncwarp();
@@ -366,7 +397,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int tok = tok0 + c0 + j;
-                        if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]);
+                        if (tok < a.m && c0 + j < nb) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -444,7 +475,7 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
         }
         B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     }
-    CUtensorMap wmap, xmap;
+    CUtensorMap wmap, xmap, xsmap;
     cuuint32_t estr[2] = {1, 1};
     {
         // code plane as [n, k] 4-bit (6-bit) elements: 16 per 8 (12) bytes, unpacked to 16-byte containers in shared memory
@@ -461,6 +492,8 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (activations) failed with code %d", (int)r);
     }
+    const int64_t total_tiles = row_tiles * m_tiles;
+    if (total_tiles > 0x3FFFFFF0ll) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): too many tiles for one launch");
     MxArgs a{};
     a.sfa = static_cast<const uint8_t*>(wm->mx_sfa);
     a.sfb = d_sfb;
@@ -469,6 +502,29 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     a.a_format = fp4 ? 5 : w->fmt == fmt_of(MXFP6_E2M3, GGUF) ? 3 : 4;
     a.a_tx = MX_BM * (fp4 ? 64 : 96);
     a.m_tiles = m_tiles; a.row_tiles = (int)row_tiles;
+    a.full_tiles = (int)total_tiles; a.split = 1; a.sub_bn = bn; a.n_work = (int)total_tiles;
+    {
+        const int ctas = ctx->info.sm_count;
+        const int rem = (int)(total_tiles % ctas);
+        // Two pieces of 128 rows only: a piece must start on a whole 128-row chunk of activation scales, because the
+        // scale address the MMA takes in tensor memory has to stay on the chunk's first column (an address 1..3
+        // columns into a chunk raised a misaligned-address fault).
+        if (total_tiles > ctas && bn == 256 && rem > 0 && rem * 2 <= ctas) {
+            a.full_tiles = (int)(total_tiles - rem);
+            a.split = 2;
+            a.sub_bn = 128;
+            a.n_work = a.full_tiles + rem * 2;
+        }
+    }
+    xsmap = xmap;
+    if (a.split > 1) {
+        cuuint64_t xdim[2] = {(cuuint64_t)k, (cuuint64_t)m_pad};
+        cuuint64_t xstr[1] = {(cuuint64_t)k};
+        cuuint32_t xbox[2] = {128u, (cuuint32_t)a.sub_bn};
+        CUresult r = enc(&xsmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, d_q, xdim, xstr, xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (activation pieces) failed with code %d", (int)r);
+    }
     a.status = ctx->d_status;
     const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (2 * MX_STAGES + 2) * 8 + 16;
     static std::atomic<bool> configured[64] = {};
@@ -476,10 +532,8 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
         B200Q_CUDA(cudaFuncSetAttribute(gemm_mxf4_native_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
         configured[ctx->device & 63] = true;
     }
-    const int64_t total_tiles = row_tiles * m_tiles;
-    if (total_tiles > 0x7FFFFFF0ll) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): too many tiles for one launch");
-    dim3 grid((unsigned)std::min<int64_t>(total_tiles, ctx->info.sm_count));
-    gemm_mxf4_native_kernel<<<grid, MX_THREADS, smem, ctx->stream>>>(wmap, xmap, a);
+    dim3 grid((unsigned)std::min<int64_t>(a.n_work, ctx->info.sm_count));
+    gemm_mxf4_native_kernel<<<grid, MX_THREADS, smem, ctx->stream>>>(wmap, xmap, xsmap, a);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }

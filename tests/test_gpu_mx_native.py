@@ -156,3 +156,26 @@ def test_bf16_activations_a_row_pitch_and_bf16_outputs(oracle):
     for b in (xb, xb16, yb, y16):
         b.free()
     w.free()
+
+
+@pytest.mark.parametrize("row_tiles,m", [(94, 512), (75, 512), (84, 500), (75, 300)],
+                         ids=["40-of-188-tiles", "2-of-150-tiles", "20-of-168-tiles-ragged-m", "2-of-150-tiles-ragged-m"])
+def test_last_wave_cut_into_pieces(oracle, row_tiles, m):
+    """More tiles than SMs with a small remainder: the tiles of the last wave are cut along the activation rows into
+    two pieces of 128 (188 tiles on 148 SMs -> 40 tiles in 80 pieces). Checked on sampled weight rows: the first and
+    last tiles and the cut ones."""
+    be = backend()
+    n, k = 128 * row_tiles, 512
+    rng = synth.rng_for(9600 + row_tiles + m)
+    data = synth.gen_packed(synth.MXFP4, synth.GGUF, n * k, rng)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.MXFP4, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    rows = np.unique(np.concatenate([np.arange(0, 256), np.arange(n - 6 * 128, n), rng.integers(0, n, size=256)]))
+    blocks = np.frombuffer(bytes(data), dtype=np.uint8).reshape(-1, 17)
+    sel = np.concatenate([blocks[r * k // 32:(r + 1) * k // 32] for r in rows]).reshape(-1)
+    wsel = oracle.dequantize(synth.MXFP4, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    ref = oracle.matmul_f64(x, wsel, nk=True)
+    assert np.all(np.isfinite(y))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / float(np.max(np.abs(ref))) <= 2e-5
+    w.free()
