@@ -179,3 +179,26 @@ def test_last_wave_cut_into_pieces(oracle, row_tiles, m):
     assert np.all(np.isfinite(y))
     assert float(np.max(np.abs(y[:, rows] - ref))) / float(np.max(np.abs(ref))) <= 2e-5
     w.free()
+
+
+@pytest.mark.parametrize("qt", [synth.MXFP4, synth.MXFP6_E2M3], ids=["mxfp4", "mxfp6"])
+@pytest.mark.parametrize("n,k", [(28672, 8192), (8192, 28672)], ids=["28672x8192", "8192x28672"])
+def test_config5_full_size(oracle, qt, n, k):
+    """BASELINE config 5's shapes at full size, M = 512: 448 (128) tiles on 148 SMs, the last wave cut in two.
+    Sampled weight rows against the oracle on exactly representable activations."""
+    be = backend()
+    m = 512
+    rng = synth.rng_for(9700 + qt + n)
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    rows = np.unique(np.concatenate([rng.integers(0, n, size=96), np.arange(n - 130, n), [0, 127, 128]]))
+    bb = synth.block_bytes(qt, synth.GGUF)
+    blocks = np.frombuffer(bytes(data), dtype=np.uint8).reshape(-1, bb)
+    sel = np.concatenate([blocks[r * k // 32:(r + 1) * k // 32] for r in rows]).reshape(-1)
+    wsel = oracle.dequantize(qt, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    ref = oracle.matmul_f64(x, wsel, nk=True)
+    assert np.all(np.isfinite(y))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / float(np.max(np.abs(ref))) <= 2e-5
+    w.free()
