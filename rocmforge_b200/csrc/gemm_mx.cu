@@ -28,6 +28,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 #include <atomic>
 
@@ -411,6 +413,214 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The same product on CTA PAIRS (tcgen05 cta_group::2): two CTAs of a cluster, one per SM, share a 256 x 256 output tile.
+// Each CTA holds 128 of the tile's weight rows (its A operand and their scales) and HALF of the activation tile (128 of
+// the 256 activation rows); one MMA issued by the pair's first CTA reads both halves, so every SM fetches and stages
+// half the activation bytes per flop -- the shared-memory traffic that bounds the single-CTA form. All copies are
+// tiled TMA loads in their pair form (their bytes count on the FIRST CTA's barrier); stages are handed back with one
+// commit per CTA; the accumulator hand-over of the second CTA's epilogue warps arrives on the first CTA's barrier
+// through its cluster address. Every wait is bounded; every thread of both CTAs reaches the cluster barrier at the end.
+constexpr int PX_STAGES = 6;
+constexpr int PX_SFA_COL = 256;   // 4 columns per stage
+constexpr int PX_SFB_COL = 288;   // 8 columns per stage
+constexpr int PX_STAGE_BYTES = MX_BM * MX_BK + 128 * MX_BK + 512 + 1024;
+
+__device__ __forceinline__ uint32_t px_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t px_mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void px_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// pair form of the tiled load: executed by both CTAs, the bytes count on the barrier of the pair's first CTA
+__device__ __forceinline__ void px_tma_2d(uint32_t dst, const CUtensorMap* map, int cx, int cy, uint32_t bar_of_first) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_of_first), "r"(cx), "r"(cy)
+        : "memory");
+}
+__device__ __forceinline__ void px_commit(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void px_cp_sf(uint32_t tmem_col, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void px_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate, uint32_t sfa,
+                                       uint32_t sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+__device__ __forceinline__ void px_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+struct PxArgs {
+    float* y;
+    int64_t ldy;
+    int n_rows, m, k;
+    int a_format, a_tx;
+    int m_tiles, pair_tiles;   // 256-row activation tiles, 256-row weight tiles
+    int* status;
+};
+
+__global__ void __launch_bounds__(MX_THREADS, 1)
+gemm_mxf4_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, PxArgs a) {
+    extern __shared__ uint8_t mx_smem_raw[];
+    uint8_t* smem = mx_smem_raw + ((1024u - (mx_smem_u32(mx_smem_raw) & 1023u)) & 1023u);
+    uint8_t* sA = smem;                                 // [stages][128 rows][128 B]
+    uint8_t* sB = sA + PX_STAGES * MX_BM * MX_BK;       // [stages][128 activation rows][128 B]
+    uint8_t* sSFA = sB + PX_STAGES * 128 * MX_BK;       // [stages][512]
+    uint8_t* sSFB = sSFA + PX_STAGES * 512;             // [stages][2][512]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSFB + PX_STAGES * 1024);
+    uint64_t* full = bars;                  // used in the pair's first CTA: the stage's bytes of BOTH CTAs have landed
+    uint64_t* empty = bars + PX_STAGES;     // per CTA: the MMAs that read the stage are complete
+    uint64_t* accum = empty + PX_STAGES;    // per CTA: the tile's MMAs are complete
+    uint64_t* afree = accum + 1;            // first CTA: the eight epilogue warps of the pair have read their accumulators
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(afree + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = px_cta_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int nkb = a.k / MX_BK;
+    const int total = a.m_tiles * a.pair_tiles;
+    if (tid == 0) {
+        for (int s = 0; s < PX_STAGES; s++) {
+            mx_bar_init(mx_smem_u32(&full[s]), 1);
+            mx_bar_init(mx_smem_u32(&empty[s]), 1);
+        }
+        mx_bar_init(mx_smem_u32(accum), 1);
+        mx_bar_init(mx_smem_u32(afree), 8);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(mx_smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    mx_fence_before();
+    __syncthreads();
+    px_cluster_sync();     // both CTAs' barriers exist before anything arrives on them from the other CTA
+    mx_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- copies (both CTAs: their own halves)
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int w = pair; w < total && ok; w += n_pairs) {
+                const int pt = w / a.m_tiles, tt = w - pt * a.m_tiles;
+                const int row_tile = 2 * pt + (int)rank, row0 = row_tile * MX_BM, tok0 = tt * 256;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % PX_STAGES;
+                    const uint32_t ph = (uint32_t)(it / PX_STAGES) & 1;
+                    if (!mx_bar_wait(mx_smem_u32(&empty[s]), ph ^ 1, abort_flag, a.status, 31)) { ok = false; break; }
+                    const uint32_t fb = mx_smem_u32(&full[s]) & 0xFEFFFFFFu;   // the first CTA's barrier
+                    if (rank == 0) mx_bar_expect_tx(mx_smem_u32(&full[s]), 2u * (uint32_t)(a.a_tx + 128 * MX_BK + 512 + 1024));
+                    px_tma_2d(mx_smem_u32(sA + s * MX_BM * MX_BK), &tmap_w, kb * MX_BK, row0, fb);
+                    px_tma_2d(mx_smem_u32(sB + s * 128 * MX_BK), &tmap_x, kb * MX_BK, tok0 + (int)rank * 128, fb);
+                    px_tma_2d(mx_smem_u32(sSFA + s * 512), &tmap_sfa, 0, row_tile * nkb + kb, fb);
+                    px_tma_2d(mx_smem_u32(sSFB + s * 1024), &tmap_sfb, 0, (tok0 >> 7) * nkb + kb, fb);
+                    px_tma_2d(mx_smem_u32(sSFB + s * 1024 + 512), &tmap_sfb, 0, ((tok0 >> 7) + 1) * nkb + kb, fb);
+                }
+            }
+            if (!ok) {   // gave up: let copies that may still be in flight land before this CTA's shared memory goes away
+                const long long t0 = clock64();
+                while (clock64() - t0 < 400000) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- the pair's MMAs (first CTA only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc0 = ((uint32_t)a.a_format << 7) | (0u << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24);
+            const uint64_t adesc0 = mx_desc_sw128(mx_smem_u32(sA)), bdesc0 = mx_desc_sw128(mx_smem_u32(sB));
+            bool ok = true;
+            int it = 0, n = 0;
+            for (int w = pair; w < total && ok; w += n_pairs, n++) {
+                if (!mx_bar_wait(mx_smem_u32(afree), (uint32_t)(n & 1) ^ 1, abort_flag, a.status, 35)) break;
+                mx_fence_after();
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % PX_STAGES;
+                    const uint32_t ph = (uint32_t)(it / PX_STAGES) & 1;
+                    if (!mx_bar_wait(mx_smem_u32(&full[s]), ph, abort_flag, a.status, 33)) { ok = false; break; }
+                    mx_fence_after();
+                    const uint32_t sfa_col = tmem_base + PX_SFA_COL + 4 * s, sfb_col = tmem_base + PX_SFB_COL + 8 * s;
+                    px_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
+                    px_cp_sf(sfb_col, mx_desc_sf(mx_smem_u32(sSFB + s * 1024)));
+                    px_cp_sf(sfb_col + 4, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + 512)));
+                    const uint64_t ad = adesc0 + (uint64_t)((s * MX_BM * MX_BK) >> 4), bd = bdesc0 + (uint64_t)((s * 128 * MX_BK) >> 4);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t idesc = idesc0 | ((uint32_t)j << 4) | ((uint32_t)j << 29);
+                        px_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col);
+                    }
+                    // hand the stage back to the copy threads of both CTAs
+                    const uint32_t eb = mx_smem_u32(&empty[s]);
+                    px_commit(px_mapa(eb, 0));
+                    px_commit(px_mapa(eb, 1));
+                }
+                if (ok) {
+                    const uint32_t ab = mx_smem_u32(accum);
+                    px_commit(px_mapa(ab, 0));
+                    px_commit(px_mapa(ab, 1));
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs): lane quarter warp % 4
+        const int q = warp & 3;
+        bool ok = true;
+        int n = 0;
+        const uint32_t afree_first = px_mapa(mx_smem_u32(afree), 0);
+        for (int w = pair; w < total && ok; w += n_pairs, n++) {
+            const int pt = w / a.m_tiles, tt = w - pt * a.m_tiles;
+            const int row0 = (2 * pt + (int)rank) * MX_BM, tok0 = tt * 256;
+            if (lane == 0) ok = mx_bar_wait(mx_smem_u32(accum), (uint32_t)(n & 1), abort_flag, a.status, 34);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            mx_fence_after();
+            const int row = row0 + q * 32 + lane;
+            for (int c0 = 0; c0 < 256; c0 += 32) {
+                uint32_t v[32];
+                mx_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (c0 == 224) {
+                    mx_fence_before();
+                    __syncwarp();
+                    if (lane == 0) px_arrive_cluster(afree_first);
+                }
+                if (row < a.n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = tok0 + c0 + j;
+                        if (tok < a.m) a.y[(int64_t)tok * a.ldy + row] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    mx_fence_before();
+    __syncthreads();
+    px_cluster_sync();     // the first CTA's MMAs read this CTA's shared memory: neither leaves before both are done
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 typedef CUresult (*MxEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -445,8 +655,9 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     const int m_pad = ((m_tiles * bn + 127) / 128) * 128;   // whole chunks of 128 rows of scales; rows the copies may touch exist
     const int64_t row_tiles = (w->n_local + MX_BM - 1) / MX_BM;
     b200q_weight* wm = const_cast<b200q_weight*>(w);
+    const int64_t sfa_row_tiles = (row_tiles + 1) & ~(int64_t)1;   // the pair kernel's second CTA may stand on a row tile past the end
     if (!wm->mx_sfa) {
-        const int64_t total = row_tiles * nkb * 512;
+        const int64_t total = sfa_row_tiles * nkb * 512;
         void* p = nullptr;
         B200Q_CUDA(cudaMalloc(&p, (size_t)total), B200Q_ERR_ALLOC);
         mx_build_sfa_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(w->view.p[0], static_cast<uint8_t*>(p), (int)w->n_local, nkb, total);
@@ -494,6 +705,61 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
     }
     const int64_t total_tiles = row_tiles * m_tiles;
     if (total_tiles > 0x3FFFFFF0ll) return fail(B200Q_ERR_UNSUPPORTED, "matmul (native MX): too many tiles for one launch");
+    {
+        // CTA pairs (cta_group::2) for whole 256-row activation tiles: B200Q_MX_PAIR=1 (a tuning knob like
+        // B200Q_DECODE_RING). Off by default: it measured the same as the single-CTA kernel on the shapes tried
+        // ([28672 x 8192], M = 512 and 2048), so halving the activation bytes per SM is not what bounds this path.
+        const char* pe = getenv("B200Q_MX_PAIR");
+        const bool want_pair = pe && pe[0] == '1';
+        if (want_pair && bn == 256 && (m % 256) == 0 && row_tiles >= 2) {
+            const int64_t pair_tiles = (row_tiles + 1) / 2;
+            CUtensorMap xh, sfam, sfbm;
+            cuuint64_t xdim[2] = {(cuuint64_t)k, (cuuint64_t)m_pad};
+            cuuint64_t xstr[1] = {(cuuint64_t)k};
+            cuuint32_t xbox[2] = {128u, 128u};
+            CUresult r = enc(&xh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, d_q, xdim, xstr, xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (activation halves) failed with code %d", (int)r);
+            // scale planes as [chunks, 128 words]: one 512-byte chunk per copy; the weights' plane holds an even number of row tiles
+            cuuint64_t sdim[2] = {128u, (cuuint64_t)(sfa_row_tiles * nkb)};
+            cuuint64_t sstr[1] = {512u};
+            cuuint32_t sbox[2] = {128u, 1u};
+            r = enc(&sfam, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, wm->mx_sfa, sdim, sstr, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (weight scales) failed with code %d", (int)r);
+            cuuint64_t bdim[2] = {128u, (cuuint64_t)((m_pad / 128) * nkb)};
+            r = enc(&sfbm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, d_sfb, bdim, sstr, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (activation scales) failed with code %d", (int)r);
+            PxArgs pa{};
+            pa.y = d_y; pa.ldy = ldy;
+            pa.n_rows = (int)w->n_local; pa.m = m; pa.k = k;
+            pa.a_format = fp4 ? 5 : w->fmt == fmt_of(MXFP6_E2M3, GGUF) ? 3 : 4;
+            pa.a_tx = MX_BM * (fp4 ? 64 : 96);
+            pa.m_tiles = m / 256; pa.pair_tiles = (int)pair_tiles;
+            pa.status = ctx->d_status;
+            const size_t psmem = 1024 + (size_t)PX_STAGES * PX_STAGE_BYTES + (2 * PX_STAGES + 2) * 8 + 16;
+            static std::atomic<bool> pconfigured[64] = {};
+            if (!pconfigured[ctx->device & 63]) {
+                B200Q_CUDA(cudaFuncSetAttribute(gemm_mxf4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
+                pconfigured[ctx->device & 63] = true;
+            }
+            const int64_t items = pair_tiles * pa.m_tiles;
+            const int pairs = (int)std::min<int64_t>(items, ctx->info.sm_count / 2);
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)(2 * pairs));
+            cfg.blockDim = dim3(MX_THREADS);
+            cfg.dynamicSmemBytes = psmem;
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            B200Q_CUDA(cudaLaunchKernelEx(&cfg, gemm_mxf4_pair_kernel, wmap, xh, sfam, sfbm, pa), B200Q_ERR_LAUNCH);
+            return B200Q_OK;
+        }
+    }
     MxArgs a{};
     a.sfa = static_cast<const uint8_t*>(wm->mx_sfa);
     a.sfb = d_sfb;

@@ -202,3 +202,28 @@ def test_config5_full_size(oracle, qt, n, k):
     assert np.all(np.isfinite(y))
     assert float(np.max(np.abs(y[:, rows] - ref))) / float(np.max(np.abs(ref))) <= 2e-5
     w.free()
+
+
+@pytest.mark.parametrize("qt", [synth.MXFP4, synth.MXFP6_E3M2], ids=["mxfp4", "e3m2"])
+@pytest.mark.parametrize("n,k,m", [(1024, 2048, 512), (384, 1024, 256), (128 * 151, 512, 512)],
+                         ids=["four-pair-tiles", "odd-row-tiles", "more-items-than-pairs"])
+def test_cta_pairs(oracle, qt, n, k, m, monkeypatch):
+    """B200Q_MX_PAIR=1: two CTAs of a cluster share a 256 x 256 tile (tcgen05 cta_group::2), each holding 128 weight
+    rows and half of the activation tile. Same exact result; an odd number of row tiles leaves the last pair's second
+    CTA on rows past the end."""
+    monkeypatch.setenv("B200Q_MX_PAIR", "1")
+    be = backend()
+    rng = synth.rng_for(9800 + qt + n + m)
+    data = synth.gen_packed(qt, synth.GGUF, n * k, rng)
+    x = exact_activations(m, k, rng)
+    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m, flags=_lib.MM_MX_NATIVE)
+    rows = np.unique(np.concatenate([np.arange(0, min(n, 300)), np.arange(max(0, n - 300), n), rng.integers(0, n, size=128)]))
+    bb = synth.block_bytes(qt, synth.GGUF)
+    blocks = np.frombuffer(bytes(data), dtype=np.uint8).reshape(-1, bb)
+    sel = np.concatenate([blocks[r * k // 32:(r + 1) * k // 32] for r in rows]).reshape(-1)
+    wsel = oracle.dequantize(qt, synth.GGUF, sel, rows.size * k, threads=8).reshape(rows.size, k)
+    ref = oracle.matmul_f64(x, wsel, nk=True)
+    assert np.all(np.isfinite(y))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / float(np.max(np.abs(ref))) <= 2e-5
+    w.free()
