@@ -117,3 +117,32 @@ def test_arena_refuses_what_does_not_fit(tmp_path):
     assert np.all(np.isfinite(y))
     w.free()
     arena.free()
+
+
+def test_bulk_upload_of_a_rank_s_shards(oracle, tmp_path):
+    """load_to_gpu_async with shard_rank / shard_count: every tensor whose rows divide is cut like a per-tensor sharded
+    upload; the arena is sized for the shards, not for the whole tensors."""
+    from rocmforge_b200.backend import WeightArena
+    tensors = make_tensors(41)
+    path = tmp_path / "bulk_shards.gguf"
+    write_model(path, tensors)
+    be = backend()
+    rng = synth.rng_for(42)
+    loaders = [GgufLoader(path) for _ in range(2)]
+    parts = [L.load_to_gpu_async(be, shard_rank=r, shard_count=2) for r, L in enumerate(loaders)]
+    whole = GgufLoader(path)
+    for name, qt, n, k, data in tensors:
+        x = synth.gen_activations(2, k, rng)
+        full = whole.load_tensor_to_gpu(name, be).matmul_host(x)
+        if n % 2 == 0:
+            assert parts[0][name].n_local == n // 2 and parts[1][name].row0 == n // 2
+            got = np.concatenate([p[name].matmul_host(x) for p in parts], axis=1)
+        else:
+            assert parts[0][name].n_local == n
+            got = parts[1][name].matmul_host(x)
+        assert rel_err(got, full) <= 2e-6, name
+    used = loaders[0].arenas[0].info()["used"]
+    want = sum(WeightArena.tensor_bytes(be, qt, synth.GGUF, n // 2 if n % 2 == 0 else n, k) for _, qt, n, k, _ in tensors)
+    assert used == want
+    for L in loaders + [whole]:
+        L.close()
