@@ -43,7 +43,8 @@ namespace {
 constexpr int MX_BM = 128;
 constexpr int MX_BK = 128;          // k per stage = one 128-byte swizzle row of 8-bit containers
 constexpr int MX_STAGES = 4;
-constexpr int MX_THREADS = 192;
+constexpr int MX_THREADS = 192;          // pair kernel: copies / MMA / 4 epilogue warps
+constexpr int MX1_THREADS = 224;         // single-CTA kernel: one more warp moves the scales to tensor memory
 constexpr long long MX_WAIT_BUDGET = 1ll << 31;
 constexpr int MX_SFA_COL = 256;     // tensor-memory columns: accumulator 0..255, weight scales 4 per stage, activation scales 8 per stage
 constexpr int MX_SFB_COL = 272;
@@ -254,7 +255,7 @@ __device__ __forceinline__ MxWork mx_work(const MxArgs& a, int w) {
     return r;
 }
 
-__global__ void __launch_bounds__(MX_THREADS, 1)
+__global__ void __launch_bounds__(MX1_THREADS, 1)
 gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_xs, MxArgs a) {
     extern __shared__ uint8_t mx_smem_raw[];
@@ -270,7 +271,8 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t* empty = bars + MX_STAGES;
     uint64_t* accum = empty + MX_STAGES;     // the MMAs of a tile are complete -> epilogue
     uint64_t* afree = accum + 1;             // the four epilogue warps have read the accumulator -> next tile's MMAs
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(afree + 1);
+    uint64_t* sfrdy = afree + 1;             // [stages] the stage's scales are in tensor memory -> its MMAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sfrdy + MX_STAGES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -282,6 +284,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         for (int s = 0; s < MX_STAGES; s++) {
             mx_bar_init(mx_smem_u32(&full[s]), 1);
             mx_bar_init(mx_smem_u32(&empty[s]), 1);
+            mx_bar_init(mx_smem_u32(&sfrdy[s]), 1);
         }
         mx_bar_init(mx_smem_u32(accum), 1);
         mx_bar_init(mx_smem_u32(afree), 4);
@@ -356,11 +359,10 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it & (MX_STAGES - 1);
                     const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
-                    if (!mx_bar_wait(mx_smem_u32(&full[s]), ph, abort_flag, a.status, 23)) { ok = false; break; }
+                    // the scale warp has seen the stage's bytes land and has moved its scales to tensor memory
+                    if (!mx_bar_wait(mx_smem_u32(&sfrdy[s]), ph, abort_flag, a.status, 23)) { ok = false; break; }
                     mx_fence_after();
                     const uint32_t sfa_col = tmem_base + MX_SFA_COL + 4 * s, sfb_col = tmem_base + MX_SFB_COL + 8 * s;
-                    mx_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
-                    for (int c = 0; c < nsf; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
                     const uint64_t ad = adesc0 + (uint64_t)((s * MX_BM * MX_BK) >> 4), bd = bdesc0 + (uint64_t)((s * b_stage) >> 4);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -371,6 +373,27 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     mx_commit(mx_smem_u32(&empty[s]));
                 }
                 if (ok) mx_commit(mx_smem_u32(accum));
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------------------------------------------------------- scales to tensor memory, a stage ahead of the MMAs
+        // (its own thread: the three copies per stage cost the MMA thread a fifth of its time when it issued them itself)
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const MxWork wk = mx_work(a, tile);
+                const int nsf = wk.nb != a.bn ? 1 : nsfb;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it & (MX_STAGES - 1);
+                    const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
+                    if (!mx_bar_wait(mx_smem_u32(&full[s]), ph, abort_flag, a.status, 26)) { ok = false; break; }
+                    mx_fence_after();
+                    const uint32_t sfa_col = tmem_base + MX_SFA_COL + 4 * s, sfb_col = tmem_base + MX_SFB_COL + 8 * s;
+                    mx_cp_sf(sfa_col, mx_desc_sf(mx_smem_u32(sSFA + s * 512)));
+                    for (int c = 0; c < nsf; c++) mx_cp_sf(sfb_col + 4 * c, mx_desc_sf(mx_smem_u32(sSFB + s * 1024 + c * 512)));
+                    mx_commit(mx_smem_u32(&sfrdy[s]));
+                }
             }
         }
     } else {
@@ -792,14 +815,14 @@ int launch_gemm_mx_native(b200q_ctx* ctx, const b200q_weight* w, const void* d_x
         if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "matmul (native MX): cuTensorMapEncodeTiled (activation pieces) failed with code %d", (int)r);
     }
     a.status = ctx->d_status;
-    const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (2 * MX_STAGES + 2) * 8 + 16;
+    const size_t smem = 1024 + (size_t)MX_STAGES * (MX_BM * MX_BK + (size_t)bn * MX_BK + 512 + 1024) + (3 * MX_STAGES + 2) * 8 + 16;
     static std::atomic<bool> configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200Q_CUDA(cudaFuncSetAttribute(gemm_mxf4_native_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), B200Q_ERR_LAUNCH);
         configured[ctx->device & 63] = true;
     }
     dim3 grid((unsigned)std::min<int64_t>(a.n_work, ctx->info.sm_count));
-    gemm_mxf4_native_kernel<<<grid, MX_THREADS, smem, ctx->stream>>>(wmap, xmap, xsmap, a);
+    gemm_mxf4_native_kernel<<<grid, MX1_THREADS, smem, ctx->stream>>>(wmap, xmap, xsmap, a);
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
