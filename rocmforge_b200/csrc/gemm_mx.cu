@@ -352,10 +352,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 if (!mx_bar_wait(mx_smem_u32(afree), (uint32_t)(n & 1) ^ 1, abort_flag, a.status, 25)) break;
                 mx_fence_after();
                 const MxWork wk = mx_work(a, tile);
-                const bool piece = wk.nb != a.bn;
-                const int nsf = piece ? 1 : nsfb;
                 const uint32_t idesc0 = idesc_base | ((uint32_t)(wk.nb >> 3) << 17);
-                const uint32_t sfb_off = 0u;   // pieces start on a chunk of activation scales (see the host side)
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it & (MX_STAGES - 1);
                     const uint32_t ph = (uint32_t)(it / MX_STAGES) & 1;
@@ -368,7 +365,7 @@ gemm_mxf4_native_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     for (int j = 0; j < 4; j++) {
                         // 32 k further: 32 bytes inside the swizzle row (+2 in the encoded address), next scale byte
                         const uint32_t idesc = idesc0 | ((uint32_t)j << 4) | ((uint32_t)j << 29);
-                        mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col + sfb_off);
+                        mx_mma(tmem_base, ad + 2 * j, bd + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u, sfa_col, sfb_col);   // a piece starts on a chunk of activation scales: same address
                     }
                     mx_commit(mx_smem_u32(&empty[s]));
                 }
