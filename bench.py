@@ -259,7 +259,7 @@ def mlp_leg(be, peaks, steps):
     for w in (wg, wu, wd):
         w.free()
     return {"workload": "llama-2-7b SwiGLU MLP block, gate/up Q4_K + down Q6_K (87.7 MB packed), b200q_mlp_run",
-            "launches_per_run": {"m=1": 3, "m=512": 6}, "shapes": rows}
+            "launches_per_run": {"m=1": 3, "m=512": 5}, "shapes": rows}
 
 
 def formats_leg(be, peaks, steps):

@@ -156,6 +156,16 @@ int b200q_mlp_run(b200q_ctx* ctx, b200q_mlp* p) {
         rc = b200q_matmul(ctx, p->up, p->x, B200Q_F32, p->d_up, B200Q_F32, p->m, 0);
         if (rc != B200Q_OK) return rc;
     }
+    // prefill: gate * swish(up) is formed by the down projection's activation conversion, the pass that reads those
+    // rows anyway (five launches for the block instead of six, one pass over [m, intermediate] less)
+    if (p->m > 32 && gemm_tc_supported(p->down, p->m)) {
+        B200Q_CUDA(cudaSetDevice(ctx->device), B200Q_ERR_DEVICE);
+        ctx->act_mul = p->d_up;
+        rc = launch_gemm_tc(ctx, p->down, p->d_gate, 0, p->down->k, p->out, p->down->n_local, p->m);
+        ctx->act_mul = nullptr;
+        if (rc == B200Q_OK) ctx->tc_pending = true;
+        return rc;
+    }
     rc = b200q_swiglu(ctx, p->d_gate, p->d_up, p->d_gate, p->m, p->gate->n_local);
     if (rc != B200Q_OK) return rc;
     return b200q_matmul(ctx, p->down, p->d_gate, B200Q_F32, p->out, B200Q_F32, p->m, 0);

@@ -1507,9 +1507,21 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
                        __uint_as_float(u.y & 0xFFFF0000u));
 }
 
+// With `up` set (fp32 rows of the same shape and pitch) the row converted is x * swish(up), swish(u) = u * 1 / (1 + expf(-u)),
+// in the operation order of the stand-alone SwiGLU kernel (kernels/swiglu.hip:55-62): the activation of an MLP
+// block's down projection is formed here, in the pass that reads it anyway.
+__device__ __forceinline__ float4 swiglu4(float4 g, float4 u) {
+    float4 o;
+    o.x = g.x * (u.x * (1.0f / (1.0f + expf(-u.x))));
+    o.y = g.y * (u.y * (1.0f / (1.0f + expf(-u.y))));
+    o.z = g.z * (u.z * (1.0f / (1.0f + expf(-u.z))));
+    o.w = g.w * (u.w * (1.0f / (1.0f + expf(-u.w))));
+    return o;
+}
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
-                                                       float* __restrict__ scale, int k, int perm) {
+                                                       float* __restrict__ scale, int k, int perm, const float* __restrict__ up) {
     // the prefill kernel behind this one may start: it streams and converts weights, and waits for this
     // kernel's completion (griddepcontrol.wait) before it touches the f16 activations or their scales
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -1519,14 +1531,20 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.x;
     const T* xr = x + (int64_t)row * ldx;
+    const float* ur = up ? up + (int64_t)row * ldx : nullptr;
     float mx = 0.0f;
     if constexpr (VEC == 4) {
         for (int i = threadIdx.x * 4; i < k; i += 1024) {
-            const float4 v = load4(xr + i);
+            float4 v = load4(xr + i);
+            if (ur) v = swiglu4(v, load4(ur + i));
             mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
     } else {
-        for (int i = threadIdx.x; i < k; i += 256) mx = fmaxf(mx, fabsf((float)xr[i]));
+        for (int i = threadIdx.x; i < k; i += 256) {
+            float v = (float)xr[i];
+            if (ur) { const float u = ur[i]; v = v * (u * (1.0f / (1.0f + expf(-u)))); }
+            mx = fmaxf(mx, fabsf(v));
+        }
     }
     __shared__ float red[8];
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
@@ -1540,7 +1558,8 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     __half* orow = out + (int64_t)row * k;
     if constexpr (VEC == 4) {
         for (int i = threadIdx.x * 4; i < k; i += 1024) {
-            const float4 v = load4(xr + i);
+            float4 v = load4(xr + i);
+            if (ur) v = swiglu4(v, load4(ur + i));
             const __half2 a = perm ? __floats2half2_rn(v.x * sdown, v.z * sdown) : __floats2half2_rn(v.x * sdown, v.y * sdown);
             const __half2 b = perm ? __floats2half2_rn(v.y * sdown, v.w * sdown) : __floats2half2_rn(v.z * sdown, v.w * sdown);
             uint2 pk;
@@ -1551,15 +1570,132 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const T* __restrict__ x, 
     } else {
         for (int i = threadIdx.x; i < k; i += 256) {
             const int src = perm ? ((i & ~3) | ((i & 1) << 1) | ((i & 2) >> 1)) : i;
-            orow[i] = __float2half_rn((float)xr[src] * sdown);
+            float v = (float)xr[src];
+            if (ur) { const float u = ur[src]; v = v * (u * (1.0f / (1.0f + expf(-u)))); }
+            orow[i] = __float2half_rn(v * sdown);
         }
     }
     if (threadIdx.x == 0) scale[row] = __uint_as_float((uint32_t)e << 23);
 }
 
+// The same conversion for short rows of up to 1024 * NC elements (k % 4 == 0, aligned rows): every thread keeps its NC
+// groups of four values in registers between the row maximum and the conversion, so the row is read once and all of a
+// thread's loads are in flight together. Same arithmetic, element for element, as the two-pass kernel above.
+template <typename T, int NC>
+__global__ void __launch_bounds__(256) x_to_f16_regs_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
+                                                            float* __restrict__ scale, int k, int perm, const float* __restrict__ up) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // see x_to_f16_kernel
+    const int row = blockIdx.x;
+    const T* xr = x + (int64_t)row * ldx;
+    float4 v[NC];
+#pragma unroll
+    for (int j = 0; j < NC; j++) {
+        const int i = (threadIdx.x + j * 256) * 4;
+        v[j] = i < k ? load4(xr + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (up) {
+        const float* ur = up + (int64_t)row * ldx;
+        float4 u[NC];
+#pragma unroll
+        for (int j = 0; j < NC; j++) {
+            const int i = (threadIdx.x + j * 256) * 4;
+            u[j] = i < k ? load4(ur + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < NC; j++) v[j] = swiglu4(v[j], u[j]);
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NC; j++) mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[j].x), fabsf(v[j].y))), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+    __shared__ float red[8];
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    int e = (int)((__float_as_uint(mx) >> 23) & 255u);
+    e = (mx == 0.0f || !(mx <= 3.0e38f)) ? 127 : min(max(e, 1), 253);
+    const float sdown = __uint_as_float((uint32_t)(254 - e) << 23);
+    __half* orow = out + (int64_t)row * k;
+#pragma unroll
+    for (int j = 0; j < NC; j++) {
+        const int i = (threadIdx.x + j * 256) * 4;
+        if (i < k) {
+            const float4 w = v[j];
+            const __half2 a = perm ? __floats2half2_rn(w.x * sdown, w.z * sdown) : __floats2half2_rn(w.x * sdown, w.y * sdown);
+            const __half2 b = perm ? __floats2half2_rn(w.y * sdown, w.w * sdown) : __floats2half2_rn(w.z * sdown, w.w * sdown);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&a);
+            pk.y = *reinterpret_cast<const uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(orow + i) = pk;
+        }
+    }
+    if (threadIdx.x == 0) scale[row] = __uint_as_float((uint32_t)e << 23);
+}
+
+// Longer rows (up to 47 KB of fp32, k % 4 == 0, aligned rows): the values wait in shared memory instead, written and
+// read back by the same thread, so several rows per SM stay in flight at a small register count.
 template <typename T>
-int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float* scale, int m, int k, int perm) {
-    const bool vec = (k % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0;
+__global__ void __launch_bounds__(256) x_to_f16_smem_kernel(const T* __restrict__ x, int64_t ldx, __half* __restrict__ out,
+                                                            float* __restrict__ scale, int k, int perm, const float* __restrict__ up) {
+    extern __shared__ float4 srow[];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // see x_to_f16_kernel
+    const int row = blockIdx.x;
+    const T* xr = x + (int64_t)row * ldx;
+    const float* ur = up ? up + (int64_t)row * ldx : nullptr;
+    const int k4 = k >> 2;
+    float mx = 0.0f;
+    for (int i0 = threadIdx.x; i0 < k4; i0 += 1024) {
+        float4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int i = i0 + q * 256;
+            v[q] = i < k4 ? load4(xr + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        if (ur) {
+            float4 u[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int i = i0 + q * 256;
+                u[q] = i < k4 ? load4(ur + 4 * i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[q] = swiglu4(v[q], u[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int i = i0 + q * 256;
+            if (i < k4) srow[i] = v[q];
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[q].x), fabsf(v[q].y))), fmaxf(fabsf(v[q].z), fabsf(v[q].w)));
+        }
+    }
+    __shared__ float red[8];
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, red[i]);
+    int e = (int)((__float_as_uint(mx) >> 23) & 255u);
+    e = (mx == 0.0f || !(mx <= 3.0e38f)) ? 127 : min(max(e, 1), 253);
+    const float sdown = __uint_as_float((uint32_t)(254 - e) << 23);
+    __half* orow = out + (int64_t)row * k;
+    for (int i = threadIdx.x; i < k4; i += 256) {
+        const float4 w = srow[i];
+        const __half2 a = perm ? __floats2half2_rn(w.x * sdown, w.z * sdown) : __floats2half2_rn(w.x * sdown, w.y * sdown);
+        const __half2 b = perm ? __floats2half2_rn(w.y * sdown, w.w * sdown) : __floats2half2_rn(w.z * sdown, w.w * sdown);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&a);
+        pk.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(orow + 4 * i) = pk;
+    }
+    if (threadIdx.x == 0) scale[row] = __uint_as_float((uint32_t)e << 23);
+}
+
+template <typename T>
+int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float* scale, int m, int k, int perm, const float* up = nullptr) {
+    const bool vec = (k % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(up) % 16) == 0;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)m);
     cfg.blockDim = dim3(256);
@@ -1569,8 +1705,13 @@ int launch_x_to_f16(b200q_ctx* ctx, const T* x, int64_t ldx, __half* out, float*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (vec) B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 4>, x, ldx, out, scale, k, perm), B200Q_ERR_LAUNCH);
-    else B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 1>, x, ldx, out, scale, k, perm), B200Q_ERR_LAUNCH);
+    if (vec && k <= 4096) B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_regs_kernel<T, 4>, x, ldx, out, scale, k, perm, up), B200Q_ERR_LAUNCH);
+    else if (vec && k <= 12032) {   // the row and the eight partial maxima within the 48 KB a launch may ask for unconfigured
+        cfg.dynamicSmemBytes = (size_t)k * sizeof(float);
+        B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_smem_kernel<T>, x, ldx, out, scale, k, perm, up), B200Q_ERR_LAUNCH);
+    }
+    else if (vec) B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 4>, x, ldx, out, scale, k, perm, up), B200Q_ERR_LAUNCH);
+    else B200Q_CUDA(cudaLaunchKernelEx(&cfg, x_to_f16_kernel<T, 1>, x, ldx, out, scale, k, perm, up), B200Q_ERR_LAUNCH);
     return B200Q_OK;
 }
 
@@ -1936,7 +2077,7 @@ int launch_gemm_tc(b200q_ctx* ctx, const b200q_weight* w, const void* d_x, int x
     // the nibble-mask producers emit weights in the order 0,2,1,3 inside every group of four
     const int perm = (w->fmt == fmt_of(Q4_K, GGUF) || q5k_tmem_path(w, m) || (mx4_tmem_path(w, m) && w->fmt != fmt_of(Q8_0, GGUF))) ? 1 : 0;
     if (x_is_bf16) rc = launch_x_to_f16(ctx, static_cast<const __nv_bfloat16*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
-    else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm);
+    else rc = launch_x_to_f16(ctx, static_cast<const float*>(d_x), ldx, d_x16, d_scale, m, (int)w->k, perm, ctx->act_mul);
     if (rc != B200Q_OK) return rc;
     return launch_gemm_core(ctx, w, d_x16, d_scale, d_y, ldy, m, "gemm", true);
 }

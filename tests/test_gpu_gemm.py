@@ -89,6 +89,44 @@ def test_token_counts_around_the_tile_edges(oracle, m, k):
     w.free()
 
 
+@pytest.mark.parametrize("k,bf16,pitch", [(4096, False, 0), (4096, True, 0), (8192, False, 0), (8192, True, 0),
+                                          (12032, False, 0), (12288, False, 0), (14336, True, 0),
+                                          (2048, False, 2049), (8192, False, 8195)],
+                         ids=["regs", "regs-bf16", "smem", "smem-bf16", "smem-max", "two-pass", "two-pass-bf16",
+                              "scalar-odd-pitch", "scalar-odd-pitch-long"])
+def test_every_form_of_the_activation_conversion(oracle, k, bf16, pitch):
+    """The f16 copy of the activations is made by one of four kernels, chosen by row length and alignment: rows kept
+    in registers (k <= 4096), in shared memory (k <= 12032), the two-pass form beyond, and the scalar form for a row
+    pitch that is not a multiple of four elements. One row carries a single large value, one is all zero."""
+    be = backend()
+    rng = synth.rng_for(3450 + k + (1 if bf16 else 0) + pitch)
+    n, m = 128, 40
+    data = synth.gen_packed(synth.Q4_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    x[3, :] = 0.0
+    x[5, k - 1] = 3.0e4
+    if bf16:
+        x = bf16_round(x)
+    ld = pitch or k
+    xp = np.zeros((m, ld), dtype=np.float32)
+    xp[:, :k] = x
+    w = QuantizedWeight(be, data, synth.Q4_K, synth.GGUF, n, k)
+    if bf16:
+        xb = be.allocate_buffer(m * ld * 2)
+        xb.copy_from_host(torch.from_numpy(xp).to(torch.bfloat16).view(torch.int16).numpy())
+    else:
+        xb = be.allocate_buffer(m * ld * 4); xb.copy_from_host(xp)
+    yb = be.allocate_buffer(m * n * 4)
+    w.matmul(xb, yb, m, x_dtype=_lib.BF16 if bf16 else _lib.F32, ldx=pitch)
+    be.synchronize()
+    y = yb.to_numpy(np.float32, m * n).reshape(m, n)
+    ref = reference(oracle, synth.Q4_K, synth.GGUF, data, n, k, x)
+    for r in range(m):                      # per row: the large value of row 5 must not hide the others
+        scale = np.max(np.abs(ref[r]))
+        assert np.max(np.abs(y[r] - ref[r])) <= TOL * scale if scale > 0 else np.all(y[r] == 0), r
+    xb.free(); yb.free(); w.free()
+
+
 def test_bf16_activations_and_outputs(oracle):
     be = backend()
     rng = synth.rng_for(3400)
