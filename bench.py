@@ -280,7 +280,7 @@ def formats_leg(be, peaks, steps):
         w.free()
     return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)",
             "note": "MXFP6_E3M2 and Q2_K have no tensor-core decode kernel (CUDA-core kernel at m = 1); Q3_K decodes re-encoded in "
-                    "Q6_K's item form (6.6 bit per weight streamed for 3.4 in the file); MXFP6_E3M2, Q2_K and Q3_K prefill on the "
+                    "Q6_K's item form (6.6 bit per weight streamed for 3.4 in the file) and prefills on Q6_K planes; MXFP6_E3M2 and Q2_K prefill on the "
                     "shared-memory-operand tensor-core kernel", "rows": rows}
 
 
@@ -305,7 +305,7 @@ def config5_leg(be, peaks, steps):
         if True:
             # opt-in: the 4- or 6-bit codes and E8M0 scales straight into the block-scaled MMA, activations quantised to
             # MXFP8 (a lower-precision mode: a few 1e-2 against 2e-3); the fraction is still taken of the measured bf16 peak
-            for m in (512, 2048):
+            for m in (64, 512, 2048):
                 ms = time_matmul(be, w, m, steps, 3, flags=_lib.MM_MX_NATIVE)
                 row[f"m{m}_native_mx_ms"] = ms
                 row[f"m{m}_native_mx_tflops"] = 2.0 * m * n * k / (ms * 1e-3) / 1e12

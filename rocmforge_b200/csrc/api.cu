@@ -303,6 +303,8 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
         case fmt_of(Q6_K, GGUF): sub = 128.f; top = 128.f * 32.f; break;
         case fmt_of(Q8_0, GGUF): sub = 128.f; top = 128.f; break;
         case fmt_of(Q4_0, GGUF): sub = 8.f; top = 8.f; break;
+        case fmt_of(Q3_K, GGUF): sub = 32.f; top = 32.f * 4.f; break;  // d (sc - 32) (q - 4)
+        case fmt_of(Q2_K, GGUF): sub = 15.f; top = 15.f * 4.f; break;  // d sc q - dmin m, q <= 3
         default: return;
     }
     float smax = 0.f;
@@ -320,6 +322,8 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
             case fmt_of(Q4_K, GGUF):
             case fmt_of(Q5_K, GGUF): s = fmaxf(mag(ld16h(p)), mag(ld16h(p + 2))); break;
             case fmt_of(Q6_K, GGUF): s = mag(ld16h(p + 208)); break;
+            case fmt_of(Q3_K, GGUF): s = mag(ld16h(p + 108)); break;
+            case fmt_of(Q2_K, GGUF): s = fmaxf(mag(ld16h(p + 80)), mag(ld16h(p + 82))); break;
             default: s = mag(ld16h(p)); break;
         }
         if (s > smax) smax = s;
@@ -424,6 +428,7 @@ static int weight_upload_impl(b200q_ctx* ctx, b200q_arena* arena, const void* h_
     w->n_elements = n_el; w->n_blocks = n_blocks;
     w->packed_bytes = (size_t)n_blocks * I.block_bytes;
     if (layout == GGUF) scan_f16_ranges(fmt, src, n_blocks, &w->f16_scales_ok, &w->f16_weights_ok);
+    else w->range_scanned = false;   // f32 and per-sub-block scales: the weights themselves are scanned, on the device, on first use
     const bool image = image_enabled() && decode_image_wanted(fmt, orient, n_local, k);
     uint8_t *place = nullptr, *img_place = nullptr;
     if (arena) {
@@ -538,6 +543,7 @@ int b200q_weight_free(b200q_weight* w) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (w->mx_sfa) cudaFree(w->mx_sfa);
+    if (w->q6_planes) cudaFree(w->q6_planes);
     if (w->arena) {
         w->arena->live--;   // the memory goes back with the arena
     } else {

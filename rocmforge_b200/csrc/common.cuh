@@ -91,6 +91,13 @@ struct b200q_weight {
     bool f16_scales_ok = true, f16_weights_ok = true;
     b200q::DImage dimg{};     // second, decode-ordered copy for m <= 8 (formats of the integer decode kernel)
     void* mx_sfa = nullptr;   // MXFP4: block scales in the chunk order of the block-scaled MMA (built on first use, own allocation)
+    // GGUF Q3_K: the same weights re-encoded, exactly, as Q6_K planes for the tensor-memory prefill kernel (built on
+    // first use, own allocation)
+    void* q6_planes = nullptr;
+    b200q::WView q6_view{};
+    // false for the layouts whose scales the upload does not scan on the host: f16_weights_ok is then settled by a
+    // device scan of the weights on first use
+    bool range_scanned = true;
 };
 
 namespace b200q {
@@ -116,6 +123,7 @@ int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_
 int launch_get_rows(b200q_ctx* ctx, int fmt, const WView& v, const int32_t* d_ids, int64_t n_ids, float* d_out, int64_t ldo,
                     int hidden, int64_t n_rows);
 int launch_repack(b200q_ctx* ctx, int fmt, const uint8_t* d_raw, int64_t n_blocks, const WView& v);
+int launch_absmax(b200q_ctx* ctx, int fmt, const WView& v, int64_t n, unsigned int* d_out);
 // kernels_gemv.cu
 int launch_gemv(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, int64_t ldx, float* d_y, int64_t ldy, int m);
 int launch_matmul_seq(b200q_ctx* ctx, const b200q_weight* w, const float* d_x, int64_t ldx, float* d_y, int64_t ldy, int m);

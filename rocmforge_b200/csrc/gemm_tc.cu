@@ -35,6 +35,7 @@
 // their loops, outstanding copies are waited for (again bounded), TMEM is freed and the kernel returns.
 #include <algorithm>
 #include <atomic>
+#include <mutex>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -1828,6 +1829,62 @@ cudaError_t launch_sk(b200q_ctx* ctx, K kernel, int ctas, size_t smem, const CUt
     return cudaLaunchKernelEx(&cfg, kernel, m0, m1, m2, m3, m4, m5, peers, k);
 }
 
+// GGUF Q3_K planes -> GGUF Q6_K planes holding the same weights exactly: d (sc6 - 32) (q3 - 4) is d * sc * (q6 - 32) with the
+// int8 scale sc = sc6 - 32 and q6 = q3 + 28 in 28..35. One thread per (block, half of 128, position e of 32): its four
+// weights 32 t + e of the half share one byte of each Q6_K code plane.
+__global__ void __launch_bounds__(256) q3k_to_q6k_planes_kernel(WView q3, WView q6, int64_t n_blocks) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t blk = idx >> 6;
+    if (blk >= n_blocks) return;
+    const int sec = (int)(idx >> 5) & 1, e = (int)idx & 31;
+    const uint32_t hm = q3.p[0][blk * 32 + e];
+    const uint32_t qs = q3.p[1][blk * 64 + sec * 32 + e];
+    uint32_t q[4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) q[t] = ((qs >> (2 * t)) & 3u) + (((hm >> (4 * sec + t)) & 1u) << 2) + 28u;
+    const_cast<uint8_t*>(q6.p[0])[blk * 128 + sec * 64 + e] = (uint8_t)((q[0] & 15u) | ((q[2] & 15u) << 4));
+    const_cast<uint8_t*>(q6.p[0])[blk * 128 + sec * 64 + 32 + e] = (uint8_t)((q[1] & 15u) | ((q[3] & 15u) << 4));
+    const_cast<uint8_t*>(q6.p[1])[blk * 64 + sec * 32 + e] = (uint8_t)((q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6));
+    if (e < 8) {
+        const uint8_t* sc = q3.p[2] + blk * 12;
+        const int g16 = 8 * sec + e;
+        const uint32_t lo = g16 < 8 ? (sc[g16] & 15u) : (uint32_t)(sc[g16 - 8] >> 4);
+        const uint32_t hi = (uint32_t)(sc[8 + (g16 & 3)] >> (2 * (g16 >> 2))) & 3u;
+        const_cast<uint8_t*>(q6.p[2])[blk * 16 + g16] = (uint8_t)(int8_t)((int)(lo | (hi << 4)) - 32);
+    } else if (e == 8 && sec == 0) {
+        const_cast<uint8_t*>(q6.p[3])[blk * 2] = q3.p[3][blk * 2];
+        const_cast<uint8_t*>(q6.p[3])[blk * 2 + 1] = q3.p[3][blk * 2 + 1];
+    }
+}
+
+int ensure_q6_planes(b200q_ctx* ctx, const b200q_weight* cw) {
+    b200q_weight* w = const_cast<b200q_weight*>(cw);
+    if (w->q6_planes) return B200Q_OK;
+    const int pbytes[4] = {128, 64, 16, 2};
+    size_t off[4], total = 0;
+    for (int j = 0; j < 4; j++) {
+        off[j] = total;
+        total += ((size_t)w->n_blocks * pbytes[j] + 64 + 255) & ~(size_t)255;   // slack: vector loads may over-read a tail
+    }
+    void* p = nullptr;
+    B200Q_CUDA(cudaMalloc(&p, total), B200Q_ERR_ALLOC);
+    WView v{};
+    for (int j = 0; j < 4; j++) v.p[j] = static_cast<uint8_t*>(p) + off[j];
+    cudaError_t e = cudaMemsetAsync(p, 0, total, ctx->stream);
+    if (e == cudaSuccess) {
+        const int64_t threads = w->n_blocks * 64;
+        q3k_to_q6k_planes_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(w->view, v, w->n_blocks);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(B200Q_ERR_LAUNCH, e, "gemm: Q6_K planes of a Q3_K tensor");
+    }
+    w->q6_planes = p;
+    w->q6_view = v;
+    return B200Q_OK;
+}
+
 int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16, const float* d_scale, float* d_y, int64_t ldy,
                      int m, const char* who, bool may_allocate) {
     EncodeTiledFn enc = get_encode_fn();
@@ -1884,9 +1941,15 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         if (e != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (workspace) failed with code %d", who, (int)e);
         return B200Q_OK;
     };
-    if (may_allocate && w->f16_scales_ok && w->fmt == fmt_of(Q6_K, GGUF) && (w->k % 256) == 0 &&
+    if (may_allocate && w->f16_scales_ok && (w->fmt == fmt_of(Q6_K, GGUF) || w->fmt == fmt_of(Q3_K, GGUF)) && (w->k % 256) == 0 &&
         (int64_t)grid.x * grid.y * (w->k / 256) < (1ll << 30)) {
-        // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads
+        // Q6_K with the weight operand in tensor memory (persistent kernel only): three planes by TMA, d by plain loads.
+        // A Q3_K tensor runs the same kernel on Q6_K planes that hold its weights exactly.
+        if (w->fmt == fmt_of(Q3_K, GGUF)) {
+            int rc = ensure_q6_planes(ctx, w);
+            if (rc != B200Q_OK) return rc;
+            a.v = w->q6_view;
+        }
         a.a_col0 = (bn + 31) & ~31;
         a.tmem_cols = 32;
         while (a.tmem_cols < a.a_col0 + A_SLOT_COLS * STAGES) a.tmem_cols <<= 1;
@@ -1902,7 +1965,7 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
             cuuint64_t wstr[1] = {row_bytes};
             cuuint32_t wbox[2] = {(cuuint32_t)pbytes[j], (cuuint32_t)BM};
             const CUtensorMapSwizzle sw = j == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : j == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
-            r = enc(&pm[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w->view.p[j]), wdim, wstr, wbox, estr,
+            r = enc(&pm[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.v.p[j]), wdim, wstr, wbox, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return fail(B200Q_ERR_INVALID, "%s: cuTensorMapEncodeTiled (Q6_K plane %d) failed with code %d", who, j, (int)r);
         }
@@ -2058,10 +2121,35 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
 
 }  // namespace
 
+// The layouts whose block scales the upload does not scan on the host (f32 scales, f16 sub-block scales): one pass over
+// the weights themselves, on the device, the first time the question is asked. Synchronises the stream once per tensor.
+static bool weights_fit_f16(const b200q_weight* cw) {
+    if (cw->range_scanned) return cw->f16_weights_ok;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    b200q_weight* w = const_cast<b200q_weight*>(cw);
+    if (w->range_scanned) return w->f16_weights_ok;
+    b200q_ctx* ctx = w->ctx;
+    unsigned int* d_max = reinterpret_cast<unsigned int*>(ctx->d_status + 6);
+    unsigned int bits = 0x7F800000u;   // any failure below reads as "out of range": the fp32 kernels take the tensor
+    bool ok = cudaSetDevice(ctx->device) == cudaSuccess && cudaMemsetAsync(d_max, 0, sizeof(unsigned int), ctx->stream) == cudaSuccess &&
+              launch_absmax(ctx, w->fmt, w->view, w->n_elements, d_max) == B200Q_OK &&
+              cudaMemcpyAsync(&bits, d_max, sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess &&
+              cudaMemsetAsync(d_max, 0, sizeof(unsigned int), ctx->stream) == cudaSuccess &&
+              cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+    float mx;
+    memcpy(&mx, &bits, 4);
+    // the same limits as the host scan of the GGUF layouts: nothing beyond the f16 range, the largest weight not a subnormal
+    w->f16_weights_ok = ok && (mx == 0.0f || (mx <= 60000.0f && mx >= 6.2e-5f));
+    w->range_scanned = true;
+    return w->f16_weights_ok;
+}
+
 bool gemm_tc_supported(const b200q_weight* w, int m) {
-    // weights beyond the f16 range (seen by the upload's scan of the block scales) stay on the fp32 decode kernels
+    // weights beyond the f16 range (seen by the upload's scan of the block scales, or by a scan of the weights) stay on
+    // the fp32 decode kernels
     return w->orient == B200Q_ORIENT_NK && m >= 1 && (w->k % BK) == 0 && w->n_local < 0x7FFFFF00ll && w->k < (1 << 30) &&
-           w->f16_weights_ok;
+           weights_fit_f16(w);
 }
 
 // x: fp32 or bf16 [m, ldx] on the device. y: fp32 [m, ldy]. Uses the context's third scratch buffer for the

@@ -6,6 +6,8 @@
 // kernel is bound by the 4 B/weight it writes to HBM.
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace b200q {
 
 template <int F>
@@ -43,6 +45,42 @@ int launch_dequant(b200q_ctx* ctx, int fmt, const WView& v, float* d_out, int64_
         B200Q_FOR_EACH_FMT(X)
 #undef X
         default: return fail(B200Q_ERR_INVALID, "dequantize: unknown format %d", fmt);
+    }
+    B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
+    return B200Q_OK;
+}
+
+// Largest |weight| of a tensor, as float bits raised into *out with an atomic maximum (bits of non-negative floats
+// order like the floats). NaN counts as infinity. The same decode8 as the dequantise kernel.
+template <int F>
+__global__ void __launch_bounds__(256) absmax_kernel(WView v, int64_t n, unsigned int* __restrict__ out) {
+    const int64_t pieces = (n + 7) / 8;
+    float mx = 0.0f;
+    for (int64_t piece = (int64_t)blockIdx.x * 256 + threadIdx.x; piece < pieces; piece += (int64_t)gridDim.x * 256) {
+        float w[8];
+        decode8<F>(v, piece >> 2, (int)(piece & 3), w);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (piece * 8 + i < n) {
+                const float a = fabsf(w[i]);
+                mx = (a != a) ? INFINITY : fmaxf(mx, a);
+            }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(mx));
+}
+
+int launch_absmax(b200q_ctx* ctx, int fmt, const WView& v, int64_t n, unsigned int* d_out) {
+    if (n <= 0) return B200Q_OK;
+    const int64_t pieces = (n + 7) / 8;
+    const unsigned grid = (unsigned)std::min<int64_t>((pieces + 255) / 256, 148 * 8);
+    switch (fmt) {
+#define X(F) \
+    case F: absmax_kernel<F><<<grid, 256, 0, ctx->stream>>>(v, n, d_out); break;
+        B200Q_FOR_EACH_FMT(X)
+#undef X
+        default: return fail(B200Q_ERR_INVALID, "absmax: unknown format %d", fmt);
     }
     B200Q_CUDA(cudaGetLastError(), B200Q_ERR_LAUNCH);
     return B200Q_OK;

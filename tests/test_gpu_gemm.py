@@ -200,15 +200,40 @@ def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
 
 
 @pytest.mark.parametrize("case", ["mxfp4-huge", "mxfp4-tiny", "mxfp4-nan-free-mix", "q4k-big-d", "q8_0-big-d",
-                                  "mxfp6-huge", "mxfp6-tiny", "mxfp6-mixed-exponents", "mxfp6-ordinary"])
+                                  "mxfp6-huge", "mxfp6-tiny", "mxfp6-mixed-exponents", "mxfp6-ordinary",
+                                  "q3k-big-d", "q3k-huge-d", "q2k-huge-d", "rf-q4_0-huge", "rf-q4_0-tiny", "rf-q8_0-huge",
+                                  "rf-q4_0-ordinary"])
 def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
     """The tensor-memory prefill kernels form block scales in f16. The upload scans the scale bytes: a tensor whose
     scales (or weights) leave the f16 range takes the next more careful kernel, down to the fp32 decode kernels, so
-    that m > 8 gives what m <= 8 gives. Exponent bytes 0x00, 0x40, 0x90 and 0xF0; f16 d of 2000 and 30000."""
+    that m > 8 gives what m <= 8 gives. Exponent bytes 0x00, 0x40, 0x90 and 0xF0; f16 d of 2000 and 30000. The layouts
+    with f32 scales (RF) have their weights scanned on the device the first time a prefill product asks."""
     be = backend()
     n, k, m = 256, 512, 64
     rng = synth.rng_for(8800 + len(case))
-    if case.startswith("mxfp4"):
+    lay = synth.GGUF
+    if case.startswith("rf-"):
+        # RF blocks start with an f32 scale: 20 bytes (Q4_0) or 36 bytes (Q8_0) per 32 weights
+        lay = synth.RF
+        qt = synth.Q4_0 if "q4_0" in case else synth.Q8_0
+        data = synth.gen_packed(qt, lay, n * k, rng).copy()
+        blocks = data.reshape(-1, 20 if qt == synth.Q4_0 else 36)
+        if case.endswith("huge"):
+            blocks[:, 0:4] = np.frombuffer(np.float32(1.0e6).tobytes(), dtype=np.uint8)   # weights up to 8e6 / 1.3e8
+        elif case.endswith("tiny"):
+            blocks[:, 0:4] = np.frombuffer(np.float32(1.0e-9).tobytes(), dtype=np.uint8)  # every weight below the smallest f16
+    elif case.startswith("q3k"):
+        qt = synth.Q3_K
+        data = synth.gen_packed(qt, lay, n * k, rng).copy()
+        blocks = data.reshape(-1, 110)
+        d = 3000.0 if case == "q3k-big-d" else 30000.0     # d * 32 overflows f16 / weights up to 3.8e6 do
+        blocks[:, 108:110] = np.frombuffer(np.float16(d).tobytes(), dtype=np.uint8)
+    elif case.startswith("q2k"):
+        qt = synth.Q2_K
+        data = synth.gen_packed(qt, lay, n * k, rng).copy()
+        blocks = data.reshape(-1, 84)
+        blocks[:, 80:82] = np.frombuffer(np.float16(30000.0).tobytes(), dtype=np.uint8)   # weights up to 1.35e6
+    elif case.startswith("mxfp4"):
         qt = synth.MXFP4
         data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
         blocks = data.reshape(-1, 17)
@@ -243,9 +268,34 @@ def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
         blocks = data.reshape(-1, 34)
         blocks[:, 0:2] = np.frombuffer(np.float16(30000.0).tobytes(), dtype=np.uint8)     # weights up to 3.8e6
     x = synth.gen_activations(m, k, rng)
-    w = QuantizedWeight(be, data, qt, synth.GGUF, n, k)
+    w = QuantizedWeight(be, data, qt, lay, n, k)
     y = gpu_matmul(be, w, x, m)
-    ref = reference(oracle, qt, synth.GGUF, data, n, k, x)
+    ref = reference(oracle, qt, lay, data, n, k, x)
     assert np.all(np.isfinite(ref)) and np.all(np.isfinite(y))
     assert rel_err(y, ref) <= TOL
+    assert np.array_equal(gpu_matmul(be, w, x, m), y)     # the answer of the scan is kept with the tensor
+    w.free()
+
+
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 512), (1000, 1280, 300), (4096, 11008, 64)],
+                         ids=["4096x4096-m512", "ragged", "k11008-m64"])
+def test_q3k_prefill_on_q6k_planes(oracle, n, k, m):
+    """A GGUF Q3_K tensor with k % 256 == 0 runs the Q6_K tensor-memory kernel on planes that hold the same weights
+    re-encoded (q6 = q3 + 28, int8 scale sc6 - 32): sampled weight rows against the oracle, twice (the planes are
+    built by the first product and kept)."""
+    be = backend()
+    rng = synth.rng_for(8900 + m)
+    data = synth.gen_packed(synth.Q3_K, synth.GGUF, n * k, rng)
+    x = synth.gen_activations(m, k, rng)
+    w = QuantizedWeight(be, data, synth.Q3_K, synth.GGUF, n, k)
+    y = gpu_matmul(be, w, x, m)
+    rows = np.unique(np.concatenate([rng.integers(0, n, size=96), [0, n - 1]]))
+    bb = 110 * (k // 256)
+    sub = np.concatenate([data[r * bb:(r + 1) * bb] for r in rows])
+    ref = reference(oracle, synth.Q3_K, synth.GGUF, sub, len(rows), k, x)
+    scale = float(np.max(np.abs(ref)))
+    assert float(np.max(np.abs(y[:, rows] - ref))) / scale <= TOL
+    assert np.array_equal(gpu_matmul(be, w, x, m), y)
+    y1 = gpu_matmul(be, w, x[:1], 1)                       # the decode kernel still reads the tensor's own image
+    assert float(np.max(np.abs(y1[0, rows] - ref[0]))) / float(np.max(np.abs(ref[0]))) <= 1e-4
     w.free()
