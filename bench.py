@@ -280,8 +280,8 @@ def formats_leg(be, peaks, steps):
         w.free()
     return {"workload": "[8192, 8192] GGUF tensor per format, single launches (m = 1 and m = 512)",
             "note": "MXFP6_E3M2 and Q2_K have no tensor-core decode kernel (CUDA-core kernel at m = 1); Q3_K decodes re-encoded in "
-                    "Q6_K's item form (6.6 bit per weight streamed for 3.4 in the file) and prefills on Q6_K planes; MXFP6_E3M2 and Q2_K prefill on the "
-                    "shared-memory-operand tensor-core kernel", "rows": rows}
+                    "Q6_K's item form (6.6 bit per weight streamed for 3.4 in the file) and prefills on Q6_K planes; MXFP6_E3M2 prefills through an image of E2M3's form "
+                    "(f16 high bytes); Q2_K prefills on the shared-memory-operand tensor-core kernel", "rows": rows}
 
 
 def config5_leg(be, peaks, steps):

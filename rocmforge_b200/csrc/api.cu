@@ -297,7 +297,7 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
     switch (fmt) {
         case fmt_of(MXFP4, GGUF): sub = 1.f; top = 12.f; break;        // s = 2^(E-127) / 2, codes are 2 x value
         case fmt_of(MXFP6_E2M3, GGUF): sub = 8.f; top = 7.5f; break;    // the prefill converter forms (8 x value) x (s / 8)
-        case fmt_of(MXFP6_E3M2, GGUF): sub = 1.f; top = 28.f; break;
+        case fmt_of(MXFP6_E3M2, GGUF): sub = 4096.f; top = 28.f; break; // the prefill converter forms (value / 4096) x (4096 s)
         case fmt_of(Q4_K, GGUF): sub = 63.f; top = 63.f * 16.f; break; // d sc q - dmin m
         case fmt_of(Q5_K, GGUF): sub = 63.f; top = 63.f * 32.f; break;
         case fmt_of(Q6_K, GGUF): sub = 128.f; top = 128.f * 32.f; break;
@@ -308,11 +308,11 @@ static void scan_f16_ranges(int fmt, const uint8_t* blocks, int64_t n_blocks, bo
         default: return;
     }
     float smax = 0.f;
-    bool small_block = false;   // MXFP6 E2M3: a block with codes and a scale below 2^-21 (its int8 x f16 products would round)
+    bool small_block = false;   // MXFP6: a block with codes and a scale below 2^-21 (E2M3) / 2^-20 (E3M2): its f16 products would round
     for (int64_t b = 0; b < n_blocks; b++) {
         const uint8_t* p = blocks + b * I.block_bytes;
         float s;
-        if (fmt == fmt_of(MXFP6_E2M3, GGUF) && p[0] < 106) {
+        if ((fmt == fmt_of(MXFP6_E2M3, GGUF) && p[0] < 106) || (fmt == fmt_of(MXFP6_E3M2, GGUF) && p[0] < 107)) {
             for (int j = 1; j < 25 && !small_block; j++) small_block = p[j] != 0;
         }
         switch (fmt) {
@@ -544,6 +544,7 @@ int b200q_weight_free(b200q_weight* w) {
     cudaStreamSynchronize(ctx->stream);
     if (w->mx_sfa) cudaFree(w->mx_sfa);
     if (w->q6_planes) cudaFree(w->q6_planes);
+    if (w->pimg.base) cudaFree(w->pimg.base);
     if (w->arena) {
         w->arena->live--;   // the memory goes back with the arena
     } else {

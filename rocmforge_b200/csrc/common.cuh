@@ -93,6 +93,7 @@ struct b200q_weight {
     void* mx_sfa = nullptr;   // MXFP4: block scales in the chunk order of the block-scaled MMA (built on first use, own allocation)
     // GGUF Q3_K: the same weights re-encoded, exactly, as Q6_K planes for the tensor-memory prefill kernel (built on
     // first use, own allocation)
+    b200q::DImage pimg{};     // GGUF MXFP6 E3M2: image for the tensor-memory prefill kernel (built on first use, own allocation)
     void* q6_planes = nullptr;
     b200q::WView q6_view{};
     // false for the layouts whose scales the upload does not scan on the host: f16_weights_ok is then settled by a

@@ -721,6 +721,7 @@ struct SkArgs {
     const uint8_t* img;
     int img_nh;          // items per row tile
     int img_nrt;         // row tiles of 16 rows
+    int img_e3m2;        // the image's bytes are E3M2 codes spread to s00eeemm (high bytes of f16 value * 2^-12), not int8 codes
 };
 
 constexpr int SK_SLOT_FLOATS = BM * 256;
@@ -1151,20 +1152,33 @@ gemm_tmem_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         const int blk = 2 * c + nib, t4 = blk & 3;
                         const uint32_t eb = ((blk < 4 ? ex.x : ex.y) >> (8 * t4)) & 0xFFu;
                         // 2^(eb - 130) built from bits: eb <= 116 lands in the f16 subnormals, still exact down to 2^-24
-                        const __half2 S = __float2half2_rn(__uint_as_float(eb >= 4u ? (eb - 3u) << 23 : 0u));
+                        // (E3M2: 2^(eb - 115), exact for block exponents 107..130)
+                        const __half2 S = __float2half2_rn(__uint_as_float(k.img_e3m2 ? (eb + 12u) << 23 : eb >= 4u ? (eb - 3u) << 23 : 0u));
                         const uint8_t* cp = stage + (blk >> 2) * 2048 + ((8 * t4 + ((g8 + 2 * t4) & 7)) << 4);
                         const uint4 qa = *reinterpret_cast<const uint4*>(cp);
                         const uint4 qb = *reinterpret_cast<const uint4*>(cp + 512);
                         const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                         uint32_t v[16];
+                        if (k.img_e3m2) {
+                            // a byte s00eeemm in the high half of an f16 is the E3M2 value * 2^-12, subnormals included
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const uint32_t u4 = w[j] ^ 0x80808080u;
-                            uint32_t t0 = __byte_perm(u4, 0x64646464u, 0x5140), t1 = __byte_perm(u4, 0x64646464u, 0x7362);
-                            __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1152), S);
-                            __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1152), S);
-                            v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
-                            v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                            for (int j = 0; j < 8; j++) {
+                                uint32_t t0 = __byte_perm(w[j], 0u, 0x1404), t1 = __byte_perm(w[j], 0u, 0x3424);
+                                __half2 h0 = __hmul2(*reinterpret_cast<__half2*>(&t0), S);
+                                __half2 h1 = __hmul2(*reinterpret_cast<__half2*>(&t1), S);
+                                v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                                v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const uint32_t u4 = w[j] ^ 0x80808080u;
+                                uint32_t t0 = __byte_perm(u4, 0x64646464u, 0x5140), t1 = __byte_perm(u4, 0x64646464u, 0x7362);
+                                __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1152), S);
+                                __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1152), S);
+                                v[2 * j] = *reinterpret_cast<uint32_t*>(&h0);
+                                v[2 * j + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                            }
                         }
                         if ((c & 1) == 0) {
                             if (lane == 0) ok = mbar_wait(smem_u32(&empty[s >> 1]), ph ^ 1, abort_flag, a.status, 4);
@@ -1794,9 +1808,13 @@ bool mx4_tmem_path(const b200q_weight* w, int m) {
     return tiles * (w->k / 256) < (1ll << 30);
 }
 
-// GGUF MXFP6 E2M3 takes the tensor-memory kernel through its decode image (int8 codes), when the tensor has one.
+// GGUF MXFP6 E2M3 takes the tensor-memory kernel through its decode image (int8 codes), when the tensor has one; E3M2
+// through an image of the same form that only this kernel reads (built by the tensor's first prefill product).
 bool mx6_tmem_path(const b200q_weight* w, int m) {
-    if (w->fmt != fmt_of(MXFP6_E2M3, GGUF) || (w->k % 256) != 0 || !w->f16_scales_ok || !w->dimg.base || w->dimg.kind != DK_MX6) return false;
+    const bool e3m2 = w->fmt == fmt_of(MXFP6_E3M2, GGUF);
+    if ((w->fmt != fmt_of(MXFP6_E2M3, GGUF) && !e3m2) || (w->k % 256) != 0 || !w->f16_scales_ok) return false;
+    if (!e3m2 && (!w->dimg.base || w->dimg.kind != DK_MX6)) return false;
+    if (e3m2 && ((w->n_local + 15) / 16) * (w->k / 128) / 8 > 0x7FFFFFFFll) return false;   // one image-build launch
     const int bn = m >= 256 ? 256 : ((m + 15) / 16) * 16;
     const int64_t tiles = ((w->n_local + BM - 1) / BM) * (int64_t)((m + bn - 1) / bn);
     return tiles * (w->k / 256) < (1ll << 30);
@@ -2010,7 +2028,13 @@ int launch_gemm_core(b200q_ctx* ctx, const b200q_weight* w, const __half* d_x16,
         k.flags = reinterpret_cast<int*>(static_cast<uint8_t*>(ctx->sk_ws) + (size_t)ctx->sk_ctas * SK_SLOT_FLOATS * sizeof(float));
         if (++ctx->sk_epoch == 0x7FFFFFFF) ctx->sk_epoch = 1;
         k.epoch = ctx->sk_epoch;
-        k.img = w->dimg.base; k.img_nh = w->dimg.nh; k.img_nrt = w->dimg.nrt;
+        if (w->fmt == fmt_of(MXFP6_E3M2, GGUF)) {
+            b200q_weight* wm = const_cast<b200q_weight*>(w);
+            if (!wm->pimg.base && (rc = build_e3m2_prefill_image(ctx, w, &wm->pimg)) != B200Q_OK) return rc;
+            k.img = w->pimg.base; k.img_nh = w->pimg.nh; k.img_nrt = w->pimg.nrt; k.img_e3m2 = 1;
+        } else {
+            k.img = w->dimg.base; k.img_nh = w->dimg.nh; k.img_nrt = w->dimg.nrt;
+        }
         B200Q_CUDA(launch_sk(ctx, gemm_tmem_sk_kernel<6>, ctas, smem, map, map, map, map, ymap, wsmap, peers, k), B200Q_ERR_LAUNCH);
         return B200Q_OK;
     }

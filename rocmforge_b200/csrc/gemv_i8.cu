@@ -1281,8 +1281,11 @@ __global__ void __launch_bounds__(256) build_image_q6k_kernel(WView v, uint8_t* 
 }
 
 // Q8_0 (codes as stored) and MXFP6 E2M3 (codes widened to 8 * value): one thread per (item, lane).
+// e3m2 (MXFP6 only): the bytes are not int8 codes but the E3M2 code s|eee|mm spread to s00eeemm, which is the high byte of
+// the f16 holding value * 2^-12 (the tensor-memory prefill kernel's form; the integer decode kernel cannot use it).
 template <int KIND>
-__global__ void __launch_bounds__(256) build_image_s8_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items) {
+__global__ void __launch_bounds__(256) build_image_s8_kernel(WView v, uint8_t* __restrict__ img, int n_rows, int nh, int64_t n_items,
+                                                              int e3m2 = 0) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t item = idx >> 5;
     if (item >= n_items) return;
@@ -1306,7 +1309,8 @@ __global__ void __launch_bounds__(256) build_image_s8_kernel(WView v, uint8_t* _
                 for (int b = 0; b < 32; b++) {
                     const int bit = 6 * b;
                     const uint32_t comb = (uint32_t)q[bit >> 3] | ((bit >> 3) + 1 < 24 ? (uint32_t)q[(bit >> 3) + 1] << 8 : 0u);
-                    o[b] = (uint8_t)(int8_t)__float2int_rn(ocp_e2m3((comb >> (bit & 7)) & 63u) * 8.0f);
+                    const uint32_t code = (comb >> (bit & 7)) & 63u;
+                    o[b] = e3m2 ? (uint8_t)(((code & 0x20u) << 2) | (code & 0x1Fu)) : (uint8_t)(int8_t)__float2int_rn(ocp_e2m3(code) * 8.0f);
                 }
                 sc[i] = v.p[0][blk];
             }
@@ -1479,6 +1483,33 @@ int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out, uint8
     if (e != cudaSuccess) {
         if (!place) cudaFree(p);
         return cuda_fail(B200Q_ERR_LAUNCH, e, "upload: decode image");
+    }
+    *out = d;
+    return B200Q_OK;
+}
+
+// GGUF MXFP6 E3M2: an image in MXFP6 E2M3's item form for the tensor-memory prefill kernel only (own allocation).
+int build_e3m2_prefill_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out) {
+    *out = DImage{};
+    if (w->fmt != fmt_of(MXFP6_E3M2, GGUF) || w->orient != B200Q_ORIENT_NK || (w->k % 128) != 0)
+        return fail(B200Q_ERR_INVALID, "prefill image: needs a GGUF MXFP6 E3M2 NK tensor with k %% 128 == 0");
+    DImage d;
+    d.kind = DK_MX6;
+    d.item_bytes = MX6_ITEM;
+    d.nh = (int)(w->k / 128);
+    d.nrt = (int)((w->n_local + 15) / 16);
+    const int64_t n_items = (int64_t)d.nrt * d.nh;
+    d.bytes = (size_t)n_items * d.item_bytes;
+    const int64_t grid = (n_items * 32 + 255) / 256;
+    if (grid > 0x7FFFFFFF) return fail(B200Q_ERR_INVALID, "prefill image: tensor too large for one image-build launch");
+    void* p = nullptr;
+    B200Q_CUDA(cudaMalloc(&p, d.bytes + 256), B200Q_ERR_ALLOC);
+    d.base = static_cast<uint8_t*>(p);
+    build_image_s8_kernel<DK_MX6><<<(unsigned)grid, 256, 0, ctx->stream>>>(w->view, d.base, (int)w->n_local, d.nh, n_items, 1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(B200Q_ERR_LAUNCH, e, "prefill image");
     }
     *out = d;
     return B200Q_OK;

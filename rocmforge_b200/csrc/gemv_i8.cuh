@@ -18,6 +18,7 @@ bool decode_image_wanted(int fmt, int orient, int64_t n_rows, int64_t k);
 // (decode_image_bytes() bytes, 256-byte aligned) without synchronising the stream.
 int build_decode_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out, uint8_t* place = nullptr);
 size_t decode_image_bytes(int fmt, int64_t n_rows, int64_t k);
+int build_e3m2_prefill_image(b200q_ctx* ctx, const b200q_weight* w, DImage* out);
 
 // One fused dequant + matmul product inside a grouped launch of the integer decode kernel.
 struct DOp {

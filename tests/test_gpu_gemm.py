@@ -173,8 +173,9 @@ def test_config4_llama7b_q4k_prefill(oracle, n, k, m):
     w.free()
 
 
-@pytest.mark.parametrize("qt,m", [(synth.MXFP4, 64), (synth.MXFP4, 512), (synth.Q6_K, 300), (synth.Q4_0, 512)],
-                         ids=["mxfp4-m64", "mxfp4-m512", "q6k-m300", "q4_0-m512"])
+@pytest.mark.parametrize("qt,m", [(synth.MXFP4, 64), (synth.MXFP4, 512), (synth.Q6_K, 300), (synth.Q4_0, 512), (synth.MXFP6_E3M2, 512),
+                                  (synth.MXFP6_E3M2, 40)],
+                         ids=["mxfp4-m64", "mxfp4-m512", "q6k-m300", "q4_0-m512", "e3m2-m512", "e3m2-m40"])
 def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
     """[28672 x 8192] (config 5; Q6_K and Q4_0 on the same shape): MXFP4, Q6_K and Q4_0 take the persistent kernel whose weight
     operand lives in tensor memory; with 448+ tiles on 148 SMs most tiles are split between CTAs. 64 sampled
@@ -201,6 +202,7 @@ def test_config5_llama70b_shapes_on_the_tensor_memory_kernel(oracle, qt, m):
 
 @pytest.mark.parametrize("case", ["mxfp4-huge", "mxfp4-tiny", "mxfp4-nan-free-mix", "q4k-big-d", "q8_0-big-d",
                                   "mxfp6-huge", "mxfp6-tiny", "mxfp6-mixed-exponents", "mxfp6-ordinary",
+                                  "e3m2-huge", "e3m2-tiny", "e3m2-mixed-exponents", "e3m2-edge-exponents", "e3m2-ordinary",
                                   "q3k-big-d", "q3k-huge-d", "q2k-huge-d", "rf-q4_0-huge", "rf-q4_0-tiny", "rf-q8_0-huge",
                                   "rf-q4_0-ordinary"])
 def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
@@ -244,6 +246,27 @@ def test_prefill_with_block_scales_outside_the_f16_range(oracle, case):
         else:
             blocks[::7, 0] = 0x00        # a few vanishing blocks among ordinary ones
             blocks[3::11, 0] = 0x40
+    elif case.startswith("e3m2"):
+        # E3M2 reaches the tensor-memory kernel as f16 (value / 4096) times 2^(e-115): exact for e in 107..130
+        qt = synth.MXFP6_E3M2
+        data = synth.gen_packed(qt, synth.GGUF, n * k, rng).copy()
+        blocks = data.reshape(-1, 25)
+        if case == "e3m2-huge":
+            blocks[:, 0] = 0x90
+        elif case == "e3m2-tiny":
+            blocks[:, 0] = 0x40
+        elif case == "e3m2-mixed-exponents":
+            blocks[::5, 0] = 0x00        # vanishing blocks with codes among ordinary ones: not the f16 path
+            blocks[1::9, 0] = 107
+            blocks[2::9, 0] = 130
+        elif case == "e3m2-edge-exponents":
+            blocks[0::2, 0] = 107        # both ends of the exact range, every code (subnormals and 28 included)
+            blocks[1::2, 0] = 130
+            every = np.packbits(((np.arange(64)[:, None] >> np.arange(6)) & 1).astype(np.uint8).ravel(), bitorder="little")
+            blocks[0::4, 1:] = every[:24]    # codes 0..31 at either exponent ...
+            blocks[1::4, 1:] = every[:24]
+            blocks[2::4, 1:] = every[24:]    # ... and 32..63
+            blocks[3::4, 1:] = every[24:]
     elif case.startswith("mxfp6"):
         # E2M3 reaches the tensor-memory kernel as int8 codes times 2^(e-130) in f16: exact for e in 106..140
         qt = synth.MXFP6_E2M3
