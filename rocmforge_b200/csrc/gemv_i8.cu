@@ -954,8 +954,10 @@ struct Seg {
 // NW warps per CTA; MANY = activation rows on the MMA's N side (m = 2..8), else the one-row block-diagonal form.
 template <int NW, bool MANY>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
-gemv_i8_kernel(DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int n_units, int total_rt, int m,
-               int* status, int* sched, int chunk, int depth, int slot_bytes, PeerSignal sig) {
+gemv_i8_kernel(const __grid_constant__ DOp single, const DOp* __restrict__ ops, int n_ops, const int2* __restrict__ ranges, int n_units,
+               int total_rt, int m, int* status, int* sched, int chunk, int depth, int slot_bytes, const __grid_constant__ PeerSignal sig) {
+    // `single` and `sig` are indexed by lane / by peer: as grid constants they are read where the launch put them;
+    // as plain parameters every thread would first copy them to its stack (216 bytes x 75776 threads of DRAM writes)
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ DOp s_op[3];    // descriptors of the previous, the current and the next segment's product
     __shared__ int s_next;     // next work unit of the CTA
