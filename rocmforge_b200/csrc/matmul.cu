@@ -363,6 +363,29 @@ int b200q_matmul_host(b200q_ctx* ctx, const b200q_weight* w, const float* h_x, f
     return b200q_synchronize(ctx);
 }
 
+// Time per image byte of the decode kernel's item forms at m = 1, relative to Q6_K's: the formats differ in instructions
+// per byte (a Q4_K item holds the same 2048 weights as a Q6_K item in 0.72 of its bytes), and the work units of a grouped
+// launch are cut to equal TIME, not equal bytes. Q4_K's 1.2 is measured on the Q4_K_M decode step (61.1 us with 1.0,
+// 58.0 us with 1.2, rising again above 1.25); the others follow the formats' single-product rates at [28672 x 8192].
+// With several activation rows the kernel is bound by instruction issue in every format and equal bytes balance best.
+// tuning knob: B200Q_DECODE_KIND_COST="q4k,q6k,q80,mx6,mx4,q40,q5k" (the order of the kernel's item kinds)
+static double decode_kind_cost(int kind, int m) {
+    static double table[DK_COUNT] = {1.2, 1.0, 0.95, 0.95, 1.6, 1.15, 1.15};
+    static const bool parsed = [] {
+        if (const char* e = getenv("B200Q_DECODE_KIND_COST")) {
+            double v[DK_COUNT];
+            if (sscanf(e, "%lf,%lf,%lf,%lf,%lf,%lf,%lf", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5], &v[6]) == DK_COUNT) {
+                bool ok = true;
+                for (int i = 0; i < DK_COUNT; i++) ok = ok && v[i] >= 0.25 && v[i] <= 4.0;
+                if (ok) for (int i = 0; i < DK_COUNT; i++) table[i] = v[i];
+            }
+        }
+        return true;
+    }();
+    (void)parsed;
+    return (m == 1 && kind >= 0 && kind < DK_COUNT) ? table[kind] : 1.0;
+}
+
 int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, const float* const* d_x,
                        float* const* d_y, int m, b200q_batch** out) {
     if (!ctx) return fail(B200Q_ERR_INVALID, "batch_create: ctx is null");
@@ -404,7 +427,7 @@ int b200q_batch_create(b200q_ctx* ctx, int count, const b200q_weight* const* w, 
             ops[i] = make_dop(w[i], d_x[i], w[i]->k, d_y[i], w[i]->n_local);
             ops[i].rt0 = total;
             total += ops[i].nrt;
-            const double c = (double)ops[i].nh * ops[i].item_bytes;
+            const double c = (double)ops[i].nh * ops[i].item_bytes * decode_kind_cost(ops[i].kind, m);
             for (int t = 0; t < ops[i].nrt; t++) { tile_cost.push_back(c); tile_op.push_back(i); }
         }
         int n_ctas = ctx->info.sm_count * b->dl.ctas_per_sm;
