@@ -35,7 +35,7 @@ struct b200q_ctx {
     int sk_ctas = 0;
     int sk_epoch = 0;
     // while b200q_matmul_scatter runs: the same output slice in the other GPUs' full outputs (peer-mapped)
-    // set around the down projection of a SwiGLU block at m > 8: the activation conversion of the prefill product
+    // set around the down projection of a SwiGLU block at m > 32: the activation conversion of the prefill product
     // forms x * swish(act_mul) as it reads the rows (fp32, same shape and pitch as x)
     const float* act_mul = nullptr;
     int scatter_extra = 0;

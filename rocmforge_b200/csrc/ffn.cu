@@ -6,7 +6,8 @@
 // HipBackend::add_row_bias (backend.rs:924-975: one saxpy per row). Here the weights stay packed; at m <= 8 the
 // gate and up projections are ONE grouped launch of the tensor-core decode kernel (they share the activations),
 // the activation kernel runs in stream order with no host synchronisation in between, and the down projection
-// follows on the same stream. At m > 8 the three products are the prefill kernels.
+// follows on the same stream. At m > 8 the three products are the prefill kernels; at m > 32 the activation is formed
+// by the down projection's own activation conversion instead of a kernel of its own.
 #include "common.cuh"
 
 namespace b200q {
