@@ -832,14 +832,14 @@ template <bool MANY>
 __device__ __forceinline__ void store_tile(const DOp& op, int prt, const float (&acc)[4], int m, int lane) {
     const int g = lane >> 2, t = lane & 3;
     if (!MANY) {
-        if (t != 0) return;
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int row = prt * 16 + g + 8 * i;
-            if (row < op.n_rows) {
-                op.y[row] = acc[i];
-                for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][row] = acc[i];
-            }
+        // every lane of a quad holds the sums of rows g and g + 8: lanes t = 0 store the first, lanes t = 1 the second, so
+        // ONE instruction writes the tile's 64 contiguous bytes (outputs in host memory travel as one PCIe write, not two)
+        if (t > 1) return;
+        const int row = prt * 16 + g + 8 * t;
+        const float v = t ? acc[1] : acc[0];
+        if (row < op.n_rows) {
+            op.y[row] = v;
+            for (int pp = 0; pp < op.n_extra; pp++) op.y_extra[pp][row] = v;
         }
     } else {
 #pragma unroll
@@ -870,7 +870,7 @@ __device__ __forceinline__ void slot_add(const float* red, int warp, float (&acc
     const int g = lane >> 2, t = lane & 3;
     const float* s = red + warp * 128;
     if (!MANY) {
-        if (t == 0) { acc[0] += s[g * 8]; acc[1] += s[(g + 8) * 8]; }
+        acc[0] += s[g * 8]; acc[1] += s[(g + 8) * 8];   // all four lanes of a quad keep the same sums (store_tile relies on it)
     } else {
         acc[0] += s[g * 8 + 2 * t]; acc[1] += s[g * 8 + 2 * t + 1];
         acc[2] += s[(g + 8) * 8 + 2 * t]; acc[3] += s[(g + 8) * 8 + 2 * t + 1];
